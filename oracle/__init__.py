@@ -1,0 +1,384 @@
+"""ctypes/numpy front-end of the CPU oracle (test infrastructure only).
+
+The oracle is a plain-C restatement of the CPU branches of DyNet's fused-layer
+nodes (see dynet_oracle.c for the per-function reference citations).  Only the
+test-suite, the smoke check and the benchmark's CPU-baseline leg import this
+package; the shipped CUDA library never does.
+
+All arrays are float32, column-major with the batch as the slowest axis; a
+numpy array of shape (bd, ..., d1, d0) in C order has exactly that memory
+layout, so callers build arrays "reversed" (batch first).
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+f32p = C.POINTER(C.c_float)
+u32p = C.POINTER(C.c_uint32)
+
+
+def build(force=False):
+    """Compile liboracle.so next to the sources (gcc via the Makefile)."""
+    so = os.path.join(_HERE, "liboracle.so")
+    srcs = [os.path.join(_HERE, f) for f in ("dynet_oracle.c", "lstm_lm_oracle.c", "Makefile")]
+    if force or not os.path.exists(so) or any(os.path.getmtime(s) > os.path.getmtime(so) for s in srcs):
+        subprocess.check_call(["make", "-C", _HERE, "-s", "-B", "liboracle.so"])
+    return so
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        so = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(so):
+            build()
+        _LIB = C.CDLL(so)
+        _LIB.orc_sigmoid_packet.restype = C.c_float
+        _LIB.orc_sigmoid_packet.argtypes = [C.c_float]
+        _LIB.orc_sigmoid_scalar.restype = C.c_float
+        _LIB.orc_sigmoid_scalar.argtypes = [C.c_float]
+        _LIB.orc_sgd_update.restype = C.c_float
+    return _LIB
+
+
+def _f(a):
+    assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"], (a.dtype, a.flags)
+    return a.ctypes.data_as(f32p)
+
+
+def _u(a):
+    assert a.dtype == np.uint32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(u32p)
+
+
+def _shape5(a_shape):
+    """numpy shape (bd, d3, d2, d1, d0)-style (batch first) -> uint32[5] = d0..d3, bd."""
+    s = list(a_shape)
+    bd, dims = s[0], s[1:][::-1]
+    dims = dims + [1] * (4 - len(dims))
+    return (C.c_uint32 * 5)(*dims, bd)
+
+
+# ---------------- unary activations ----------------
+def unary_fwd(name, x, alpha=1.0, lam=1.0, packet=8):
+    y = np.empty_like(x)
+    n = C.c_size_t(x.size)
+    L = lib()
+    if name == "tanh":
+        L.orc_tanh_fwd(_f(x), _f(y), n)
+    elif name == "logistic":
+        L.orc_logistic_fwd(_f(x), _f(y), n, C.c_int(packet))
+    elif name == "rectify":
+        L.orc_rectify_fwd(_f(x), _f(y), n)
+    elif name == "elu":
+        L.orc_elu_fwd(_f(x), _f(y), n, C.c_float(alpha), C.c_float(lam))
+    else:
+        raise KeyError(name)
+    return y
+
+
+def unary_bwd(name, x, y, dy, dx, alpha=1.0, lam=1.0):
+    """Accumulates into dx (in place) and returns it."""
+    n = C.c_size_t(x.size)
+    L = lib()
+    if name == "tanh":
+        L.orc_tanh_bwd(_f(y), _f(dy), _f(dx), n)
+    elif name == "logistic":
+        L.orc_logistic_bwd(_f(y), _f(dy), _f(dx), n)
+    elif name == "rectify":
+        L.orc_rectify_bwd(_f(y), _f(dy), _f(dx), n)
+    elif name == "elu":
+        L.orc_elu_bwd(_f(x), _f(dy), _f(dx), n, C.c_float(alpha), C.c_float(lam))
+    else:
+        raise KeyError(name)
+    return dx
+
+
+# ---------------- cwise binary ----------------
+_OPS = {"cmult": 0, "csum": 1, "cdiv": 2}
+
+
+def cwise_fwd(op, a, b):
+    """a, b: numpy arrays shaped (bd, [d3, d2, d1,] d0) with equal rank."""
+    assert a.ndim == b.ndim
+    out_shape = tuple(max(x, y) for x, y in zip(a.shape, b.shape))
+    y = np.empty(out_shape, np.float32)
+    lib().orc_cwise_fwd(C.c_int(_OPS[op]), _f(a), _shape5(a.shape), _f(b), _shape5(b.shape), _f(y))
+    return y
+
+
+def cwise_bwd(op, a, b, dy, i, dxi):
+    lib().orc_cwise_bwd(C.c_int(_OPS[op]), _f(a), _shape5(a.shape), _f(b), _shape5(b.shape),
+                        _f(dy), C.c_uint(i), _f(dxi))
+    return dxi
+
+
+# ---------------- softmax family ----------------
+def _rcb(x):
+    """(bd, cols, rows) view parameters of a 2-D-per-batch tensor."""
+    assert x.ndim == 3
+    bd, cols, rows = x.shape
+    return C.c_uint32(rows), C.c_uint32(cols), C.c_uint32(bd)
+
+
+def softmax_fwd(x, dimension=0):
+    y = np.empty_like(x)
+    lib().orc_softmax_fwd(_f(x), _f(y), *_rcb(x), C.c_uint(dimension))
+    return y
+
+
+def softmax_bwd(y, dy, dx, dimension=0):
+    lib().orc_softmax_bwd(_f(y), _f(dy), _f(dx), *_rcb(y), C.c_uint(dimension))
+    return dx
+
+
+def logsumexp_dim_fwd(x, axis=0):
+    bd, cols, rows = x.shape
+    outer = cols if axis == 0 else rows
+    z = np.empty((bd, outer), np.float32)
+    m = np.empty((bd, outer), np.float32)
+    lib().orc_logsumexp_axis(_f(x), *_rcb(x), C.c_uint(axis), _f(m), _f(z))
+    return z, m
+
+
+def logsumexp_dim_bwd(x, z, dz, dx, axis=0):
+    lib().orc_logsumexp_dim_bwd(_f(x), _f(z), _f(dz), _f(dx), *_rcb(x), C.c_uint(axis))
+    return dx
+
+
+def log_softmax_fwd(x):
+    bd, cols, rows = x.shape
+    y = np.empty_like(x)
+    z = np.empty((bd, cols), np.float32)
+    m = np.empty((bd, cols), np.float32)
+    lib().orc_log_softmax_fwd(_f(x), _f(y), *_rcb(x), _f(z), _f(m))
+    return y
+
+
+def log_softmax_bwd(y, dy, dx):
+    lib().orc_log_softmax_bwd(_f(y), _f(dy), _f(dx), *_rcb(y))
+    return dx
+
+
+def logsumexp_nary_fwd(xs):
+    """xs: list of (bd_k, n) arrays with bd_k in {1, bd}."""
+    bd = max(x.shape[0] for x in xs)
+    n = xs[0].shape[1]
+    y = np.empty((bd, n), np.float32)
+    ptrs = (f32p * len(xs))(*[_f(x) for x in xs])
+    bds = (C.c_uint32 * len(xs))(*[x.shape[0] for x in xs])
+    lib().orc_logsumexp_nary_fwd(ptrs, bds, C.c_uint(len(xs)), C.c_size_t(n), C.c_uint32(bd), _f(y))
+    return y
+
+
+def logsumexp_nary_bwd(xs, i, y, dy, dxi):
+    bd, n = y.shape
+    lib().orc_logsumexp_nary_bwd(_f(xs[i]), C.c_uint32(xs[i].shape[0]), C.c_uint(len(xs)), _f(y),
+                                 _f(dy), C.c_size_t(n), C.c_uint32(bd), _f(dxi))
+    return dxi
+
+
+def pnls_fwd(x, ids):
+    """x: (bd, rows). Returns (loss[bd], z[bd]); raises ValueError on a bad id."""
+    bd, rows = x.shape
+    loss = np.empty(bd, np.float32)
+    z = np.empty(bd, np.float32)
+    m = np.empty(bd, np.float32)
+    rc = lib().orc_pnls_fwd(_f(x), C.c_uint32(rows), C.c_uint32(bd), _u(ids), _f(loss), _f(z), _f(m))
+    if rc != 0:
+        raise ValueError("Index error in PickNegLogSoftmax")
+    return loss, z
+
+
+def pnls_bwd(x, ids, z, dE, dx):
+    bd, rows = x.shape
+    lib().orc_pnls_bwd(_f(x), C.c_uint32(rows), C.c_uint32(bd), _u(ids), _f(z), _f(dE), _f(dx))
+    return dx
+
+
+# ---------------- norms ----------------
+def weight_norm_fwd(w, g):
+    y = np.empty_like(w)
+    lib().orc_weight_norm_fwd(_f(w), C.c_float(g), _f(y), C.c_size_t(w.size))
+    return y
+
+
+def weight_norm_bwd(w, g, y, dy, i, dxi):
+    lib().orc_weight_norm_bwd(_f(w), C.c_float(g), _f(y), _f(dy), C.c_uint(i), _f(dxi), C.c_size_t(w.size))
+    return dxi
+
+
+def moment_elems_fwd(x, order=1):
+    bd, n = x.shape
+    out = np.empty(bd, np.float32)
+    lib().orc_moment_elems_fwd(_f(x), C.c_size_t(n), C.c_uint32(bd), C.c_uint(order), _f(out))
+    return out
+
+
+def moment_elems_bwd(x, order, dE, dx):
+    bd, n = x.shape
+    lib().orc_moment_elems_bwd(_f(x), C.c_size_t(n), C.c_uint32(bd), C.c_uint(order), _f(dE), _f(dx))
+    return dx
+
+
+def std_elems_fwd(x):
+    bd, n = x.shape
+    out = np.empty(bd, np.float32)
+    lib().orc_std_elems_fwd(_f(x), C.c_size_t(n), C.c_uint32(bd), _f(out))
+    return out
+
+
+def std_elems_bwd(x, fx, dE, dx):
+    bd, n = x.shape
+    lib().orc_std_elems_bwd(_f(x), C.c_size_t(n), C.c_uint32(bd), _f(fx), _f(dE), _f(dx))
+    return dx
+
+
+def std_dim0_batch_fwd(x):
+    bd, d1, d0 = x.shape
+    out = np.empty(d1, np.float32)
+    lib().orc_std_dim0_batch_fwd(_f(x), C.c_uint32(d0), C.c_uint32(d1), C.c_uint32(bd), _f(out))
+    return out
+
+
+def layer_norm_fwd(x, g, b):
+    bd, n = x.shape
+    y = np.empty_like(x)
+    lib().orc_layer_norm_fwd(_f(x), _f(g), _f(b), _f(y), C.c_size_t(n), C.c_uint32(bd))
+    return y
+
+
+def layer_norm_bwd(x, g, dy, dx, dg, db):
+    bd, n = x.shape
+    lib().orc_layer_norm_bwd(_f(x), _f(g), _f(dy), _f(dx), _f(dg), _f(db), C.c_size_t(n), C.c_uint32(bd))
+    return dx, dg, db
+
+
+# ---------------- lookup ----------------
+def lookup_fwd(table, ids, scale=1.0):
+    """table: (V, E). Returns (n, E); raises ValueError on an out-of-range id."""
+    V, E = table.shape
+    out = np.empty((ids.size, E), np.float32)
+    rc = lib().orc_lookup_fwd(_f(table), C.c_uint32(E), C.c_uint32(V), _u(ids), C.c_uint32(ids.size),
+                              C.c_float(scale), _f(out))
+    if rc != 0:
+        raise ValueError("Out-of-bounds attempt to access index for LookupParameter")
+    return out
+
+
+def lookup_accumulate_grads(all_grads, ids, g):
+    V, E = all_grads.shape
+    lib().orc_lookup_accumulate_grads(_f(all_grads), C.c_uint32(E), _u(ids), C.c_uint32(ids.size), _f(g))
+    return all_grads
+
+
+# ---------------- LSTM nodes ----------------
+def _xs_args(xs):
+    ptrs = (f32p * len(xs))(*[_f(x) for x in xs])
+    dims = (C.c_uint32 * len(xs))(*[x.shape[1] for x in xs])
+    return ptrs, dims
+
+
+def _mask(m):
+    if m is None:
+        return None, C.c_uint32(1)
+    return _f(m), C.c_uint32(m.shape[0])
+
+
+def lstm_gates_fwd(xs, h_tm1, Wx, Wh, b, mask_x=None, mask_h=None, forget_bias=1.0,
+                   skip_matmul=False, packet=8):
+    """xs: list of (B, I_k); h_tm1: (B, H); Wx: (I, 4H); Wh: (H, 4H); b: (4H,)."""
+    B, H = h_tm1.shape
+    I = Wx.shape[0]
+    fx = np.empty((B, 4 * H), np.float32)
+    ptrs, dims = _xs_args(xs)
+    mx, mxbd = _mask(mask_x)
+    mh, mhbd = _mask(mask_h)
+    lib().orc_lstm_gates_fwd(ptrs, dims, C.c_uint(len(xs)), _f(h_tm1), _f(Wx), _f(Wh), _f(b), mx, mxbd,
+                             mh, mhbd, C.c_uint32(H), C.c_uint32(I), C.c_uint32(B),
+                             C.c_float(forget_bias), C.c_int(int(skip_matmul)), C.c_int(packet), _f(fx))
+    return fx
+
+
+def lstm_gates_bwd(xs, h_tm1, Wx, Wh, fx, dEdf, i, dxi, mask_x=None, mask_h=None):
+    B, H = h_tm1.shape
+    I = Wx.shape[0]
+    ptrs, dims = _xs_args(xs)
+    mx, mxbd = _mask(mask_x)
+    mh, mhbd = _mask(mask_h)
+    lib().orc_lstm_gates_bwd(ptrs, dims, C.c_uint(len(xs)), _f(h_tm1), _f(Wx), _f(Wh), mx, mxbd, mh,
+                             mhbd, C.c_uint32(H), C.c_uint32(I), C.c_uint32(B), _f(fx), _f(dEdf),
+                             C.c_uint(i), _f(dxi))
+    return dxi
+
+
+def lstm_c_fwd(c_tm1, gates):
+    B, H = c_tm1.shape
+    c = np.empty_like(c_tm1)
+    lib().orc_lstm_c_fwd(_f(c_tm1), _f(gates), C.c_uint32(H), C.c_uint32(B), _f(c))
+    return c
+
+
+def lstm_c_bwd(c_tm1, gates, dc, i, dxi):
+    B, H = c_tm1.shape
+    lib().orc_lstm_c_bwd(_f(c_tm1), _f(gates), C.c_uint32(H), C.c_uint32(B), _f(dc), C.c_uint(i), _f(dxi))
+    return dxi
+
+
+def lstm_h_fwd(c_t, gates):
+    B, H = c_t.shape
+    h = np.empty_like(c_t)
+    lib().orc_lstm_h_fwd(_f(c_t), _f(gates), C.c_uint32(H), C.c_uint32(B), _f(h))
+    return h
+
+
+def lstm_h_bwd(c_t, gates, dh, i, dxi):
+    B, H = c_t.shape
+    lib().orc_lstm_h_bwd(_f(c_t), _f(gates), C.c_uint32(H), C.c_uint32(B), _f(dh), C.c_uint(i), _f(dxi))
+    return dxi
+
+
+# ---------------- LSTM language model step ----------------
+class LmDims(C.Structure):
+    _fields_ = [(k, C.c_uint32) for k in ("V", "E", "H", "L", "T", "B")]
+
+
+def lm_param_shapes(V, E, H, L):
+    """(rows, cols) of every parameter tensor, in the order the oracle expects."""
+    shapes = [(E, V)]
+    for l in range(L):
+        shapes += [(4 * H, E if l == 0 else H), (4 * H, H), (4 * H, 1)]
+    shapes += [(V, H), (V, 1)]
+    return shapes
+
+
+def lstm_lm_fwdbwd(dims, params, grads, tokens, mask_x=None, mask_h=None, want_h=False):
+    """params/grads: lists of flat float32 arrays (grads accumulated in place, or None).
+
+    tokens: uint32 (T+1, B).  Returns (loss, h_states or None)."""
+    V, E, H, L, T, B = dims
+    d = LmDims(V, E, H, L, T, B)
+    pp = (f32p * len(params))(*[_f(p) for p in params])
+    gp = (f32p * len(params))(*[_f(g) for g in grads]) if grads is not None else None
+    mxp = (f32p * L)(*[_f(m) for m in mask_x]) if mask_x is not None else None
+    mhp = (f32p * L)(*[_f(m) for m in mask_h]) if mask_h is not None else None
+    loss = C.c_float(0)
+    h = np.empty((T, L, B, H), np.float32) if want_h else None
+    rc = lib().orc_lstm_lm_fwdbwd(C.byref(d), pp, gp, _u(tokens), mxp, mhp, C.byref(loss),
+                                  _f(h) if want_h else None)
+    if rc != 0:
+        raise ValueError("token id out of range")
+    return loss.value, h
+
+
+def sgd_update(params, grads, lr, clip=5.0):
+    n = len(params)
+    pp = (f32p * n)(*[_f(p) for p in params])
+    gp = (f32p * n)(*[_f(g) for g in grads])
+    sizes = (C.c_size_t * n)(*[p.size for p in params])
+    return lib().orc_sgd_update(pp, gp, sizes, C.c_uint(n), C.c_float(lr), C.c_float(clip))
