@@ -1,0 +1,210 @@
+"""ctypes binding of include/dyb200.h.
+
+Device memory is handled by the caller (the tests and the benchmark use torch CUDA tensors
+and pass ``tensor.data_ptr()``); nothing here computes on the host.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+OK, EINVAL, ERUNTIME, ECUDA, ENOMEM = 0, 1, 2, 3, 4
+
+
+class Dyb200Error(Exception):
+    """Base of the errors raised for a non-zero status."""
+
+
+class InvalidArgument(Dyb200Error, ValueError):
+    """DYB200_EINVAL: the reference throws std::invalid_argument here."""
+
+
+class RuntimeErr(Dyb200Error, RuntimeError):
+    """DYB200_ERUNTIME: the reference throws std::runtime_error here."""
+
+
+class CudaError(Dyb200Error):
+    """DYB200_ECUDA: the reference throws dynet::cuda_exception here."""
+
+
+class OutOfMemory(Dyb200Error, MemoryError):
+    """DYB200_ENOMEM: the reference throws dynet::out_of_memory here."""
+
+
+_EXC = {EINVAL: InvalidArgument, ERUNTIME: RuntimeErr, ECUDA: CudaError, ENOMEM: OutOfMemory}
+
+
+class DyTensor(C.Structure):
+    """struct dyb200_tensor"""
+    _fields_ = [("v", C.c_void_p), ("d", C.c_uint32 * 7), ("nd", C.c_uint32), ("bd", C.c_uint32)]
+
+    @staticmethod
+    def of(ptr, dims, bd=1):
+        t = DyTensor()
+        t.v = ptr
+        dims = list(dims)
+        assert len(dims) <= 7
+        for k, d in enumerate(dims):
+            t.d[k] = d
+        t.nd = len(dims)
+        t.bd = bd
+        return t
+
+
+class EluAttrs(C.Structure):
+    _fields_ = [("alpha", C.c_float), ("lam", C.c_float)]
+
+
+class DimAttrs(C.Structure):
+    _fields_ = [("dimension", C.c_uint32)]
+
+
+class PickAttrs(C.Structure):
+    _fields_ = [("ids_host", C.POINTER(C.c_uint32)), ("n", C.c_uint32)]
+
+
+class LookupAttrs(C.Structure):
+    _fields_ = [("all_values", C.c_void_p), ("vocab", C.c_uint32), ("ids_host", C.POINTER(C.c_uint32)),
+                ("n", C.c_uint32), ("weight_decay_scale", C.c_float)]
+
+
+class LstmGatesAttrs(C.Structure):
+    _fields_ = [("dropout", C.c_int32), ("weightnoise_std", C.c_float), ("forget_gate_bias", C.c_float)]
+
+
+class MomentAttrs(C.Structure):
+    _fields_ = [("dims", C.c_uint32 * 2), ("ndims", C.c_uint32), ("order", C.c_uint32),
+                ("include_batch_dim", C.c_int32), ("overwrite_n", C.c_uint32)]
+
+
+NODES = ["tanh", "logistic", "rectify", "elu", "cmult", "csum", "cdiv", "softmax", "log_softmax",
+         "logsumexp_dim", "logsumexp", "pickneglogsoftmax", "weight_norm", "moment_dim", "std_dim",
+         "layer_norm", "vanilla_lstm_gates", "vanilla_lstm_c", "vanilla_lstm_h"]
+FWD_ONLY = ["lookup"]
+OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200_ctx_check_device_errors",
+         "dyb200_ctx_launch_count", "dyb200_version", "dyb200_lookup_accumulate_grads",
+         "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm"]
+
+
+def exported_symbols():
+    """Every symbol include/dyb200.h declares."""
+    syms = list(OTHER)
+    for n in NODES:
+        syms += ["dyb200_%s_fwd" % n, "dyb200_%s_bwd" % n]
+    syms += ["dyb200_%s_fwd" % n for n in FWD_ONLY]
+    return syms
+
+
+def lib_path():
+    return os.path.join(_HERE, "libdyb200.so")
+
+
+def lib():
+    """Loads libdyb200.so; raises (no fallback) if it has not been built."""
+    global _LIB
+    if _LIB is None:
+        p = lib_path()
+        if not os.path.exists(p):
+            raise ImportError("libdyb200.so is missing: run `python -m dynet_b200.build` (nvcc, sm_100a); "
+                              "there is no CPU fallback")
+        L = C.CDLL(p)
+        tp = C.POINTER(DyTensor)
+        for n in NODES + FWD_ONLY:
+            f = getattr(L, "dyb200_%s_fwd" % n)
+            f.restype = C.c_int
+            f.argtypes = [tp, C.c_int, tp, C.c_void_p, C.c_void_p, C.c_void_p]
+        for n in NODES:
+            f = getattr(L, "dyb200_%s_bwd" % n)
+            f.restype = C.c_int
+            f.argtypes = [tp, C.c_int, tp, tp, C.c_uint, tp, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.dyb200_ctx_create.restype = C.c_int
+        L.dyb200_ctx_create.argtypes = [C.c_int, C.c_void_p, C.POINTER(C.c_void_p)]
+        L.dyb200_ctx_destroy.argtypes = [C.c_void_p]
+        L.dyb200_last_error.restype = C.c_char_p
+        L.dyb200_last_error.argtypes = [C.c_void_p]
+        L.dyb200_ctx_check_device_errors.restype = C.c_int
+        L.dyb200_ctx_check_device_errors.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
+        L.dyb200_ctx_launch_count.restype = C.c_uint64
+        L.dyb200_ctx_launch_count.argtypes = [C.c_void_p]
+        L.dyb200_version.restype = C.c_char_p
+        L.dyb200_lookup_accumulate_grads.restype = C.c_int
+        L.dyb200_lookup_accumulate_grads.argtypes = [C.c_uint, C.POINTER(C.c_uint32), C.c_void_p, C.c_void_p,
+                                                     C.c_void_p, C.c_uint, C.c_uint, C.c_void_p]
+        for n in ("dyb200_parallel_memcpy", "dyb200_parallel_accumulate"):
+            f = getattr(L, n)
+            f.restype = C.c_int
+            f.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.dyb200_gemm.restype = C.c_int
+        L.dyb200_gemm.argtypes = [C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32,
+                                  C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_int, C.c_void_p]
+        _LIB = L
+    return _LIB
+
+
+class Context:
+    """Owns one dyb200_ctx (device, stream, scratch arena)."""
+
+    def __init__(self, device=0, stream=None):
+        self.L = lib()
+        h = C.c_void_p()
+        rc = self.L.dyb200_ctx_create(device, stream, C.byref(h))
+        if rc != OK:
+            raise _EXC.get(rc, Dyb200Error)("dyb200_ctx_create(device=%d) failed with status %d: a B200 "
+                                            "(sm_100) device is required, there is no CPU fallback" % (device, rc))
+        self.h = h
+
+    def close(self):
+        if self.h:
+            self.L.dyb200_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, rc):
+        if rc != OK:
+            raise _EXC.get(rc, Dyb200Error)(self.L.dyb200_last_error(self.h).decode())
+
+    def launches(self):
+        return int(self.L.dyb200_ctx_launch_count(self.h))
+
+    def device_errors(self):
+        f = C.c_uint32(0)
+        self.check(self.L.dyb200_ctx_check_device_errors(self.h, C.byref(f)))
+        return f.value
+
+    @staticmethod
+    def _arr(ts):
+        if not ts:
+            return None, 0
+        a = (DyTensor * len(ts))(*ts)
+        return a, len(ts)
+
+    def fwd(self, node, xs, fx, attrs=None, aux=None):
+        a, n = self._arr(xs)
+        f = getattr(self.L, "dyb200_%s_fwd" % node)
+        self.check(f(a, n, C.byref(fx), C.cast(C.byref(attrs), C.c_void_p) if attrs is not None else None, aux, self.h))
+
+    def bwd(self, node, xs, fx, dEdf, i, dEdxi, attrs=None, aux=None):
+        a, n = self._arr(xs)
+        f = getattr(self.L, "dyb200_%s_bwd" % node)
+        self.check(f(a, n, C.byref(fx), C.byref(dEdf), i, C.byref(dEdxi),
+                     C.cast(C.byref(attrs), C.c_void_p) if attrs is not None else None, aux, self.h))
+
+    def lookup_accumulate_grads(self, ids_host, ids_dev_ptr, g_ptr, all_grads_ptr, dim_size, vocab):
+        n = len(ids_host)
+        arr = (C.c_uint32 * n)(*[int(i) for i in ids_host]) if n else None
+        self.check(self.L.dyb200_lookup_accumulate_grads(n, arr, ids_dev_ptr, g_ptr, all_grads_ptr, dim_size, vocab, self.h))
+
+    def parallel_memcpy(self, num_seqs, max_len, src_tbl, trg_tbl, len_tbl):
+        self.check(self.L.dyb200_parallel_memcpy(num_seqs, max_len, src_tbl, trg_tbl, len_tbl, self.h))
+
+    def parallel_accumulate(self, num_seqs, max_len, src_tbl, trg_tbl, len_tbl):
+        self.check(self.L.dyb200_parallel_accumulate(num_seqs, max_len, src_tbl, trg_tbl, len_tbl, self.h))
+
+    def gemm(self, transA, transB, M, N, K, A, lda, B, ldb, Cp, ldc, accumulate):
+        self.check(self.L.dyb200_gemm(int(transA), int(transB), M, N, K, A, lda, B, ldb, Cp, ldc, int(accumulate), self.h))

@@ -1,0 +1,115 @@
+// Shared host/device helpers for the dyb200 kernels (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/dyb200.h"
+
+#ifndef __CUDA_ARCH__
+#define DYB200_HOST_ONLY 1
+#endif
+
+struct dyb200_ctx {
+  int device;
+  cudaStream_t stream;
+  int sm_count;
+  char err[512];
+  void* scratch;         // grow-only arena for node-local temporaries
+  size_t scratch_bytes;
+  uint32_t* dev_flags;   // device error word (bit set by kernels, never traps)
+  uint64_t launches;     // kernels launched through this context
+  // 3xTF32 GEMM state (tensor maps are encoded per call; driver entry point cached)
+  void* encode_tiled;    // cuTensorMapEncodeTiled
+};
+
+// Device error bits written into ctx->dev_flags.
+#define DYB200_FLAG_BAD_INDEX 1u     // an id >= vocab/rows reached a kernel (clamped, not dereferenced)
+#define DYB200_FLAG_WAIT_TIMEOUT 2u  // a bounded mbarrier wait ran out
+
+int dyb200_fail(dyb200_ctx* ctx, int code, const char* fmt, ...);
+int dyb200_scratch(dyb200_ctx* ctx, size_t bytes, void** out);
+
+#define DYB_CHECK_ARG(ctx, cond, ...)                                    \
+  do {                                                                   \
+    if (!(cond)) return dyb200_fail((ctx), DYB200_EINVAL, __VA_ARGS__);  \
+  } while (0)
+
+#define DYB_CUDA(ctx, expr)                                                            \
+  do {                                                                                 \
+    cudaError_t e__ = (expr);                                                          \
+    if (e__ != cudaSuccess)                                                            \
+      return dyb200_fail((ctx), DYB200_ECUDA, "%s failed: %s", #expr, cudaGetErrorString(e__)); \
+  } while (0)
+
+// Counts the launch and reports a launch-configuration error as a status.
+#define DYB_LAUNCHED(ctx)                                                              \
+  do {                                                                                 \
+    (ctx)->launches++;                                                                 \
+    cudaError_t e__ = cudaGetLastError();                                              \
+    if (e__ != cudaSuccess)                                                            \
+      return dyb200_fail((ctx), DYB200_ECUDA, "kernel launch failed at %s:%d: %s", __FILE__, __LINE__, \
+                         cudaGetErrorString(e__));                                     \
+  } while (0)
+
+static inline size_t t_batch_size(const dyb200_tensor* t) {
+  size_t n = 1;
+  for (uint32_t k = 0; k < t->nd; ++k) n *= t->d[k];
+  return n;
+}
+static inline size_t t_size(const dyb200_tensor* t) { return t_batch_size(t) * t->bd; }
+static inline uint32_t t_dim(const dyb200_tensor* t, uint32_t k) { return k < t->nd ? t->d[k] : 1u; }
+static inline uint32_t t_rows(const dyb200_tensor* t) { return t_dim(t, 0); }
+static inline uint32_t t_cols(const dyb200_tensor* t) { return t_dim(t, 1); }
+__host__ __device__ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Grid for a streaming kernel: enough CTAs to cover the work, capped at a
+// multiple of the SM count (148 on B200) so every SM holds the same number.
+static inline unsigned stream_grid(const dyb200_ctx* ctx, size_t work_items, unsigned per_cta,
+                                   unsigned ctas_per_sm = 8) {
+  size_t need = (work_items + per_cta - 1) / per_cta;
+  size_t cap = (size_t)ctx->sm_count * ctas_per_sm;
+  if (need < 1) need = 1;
+  return (unsigned)(need < cap ? need : cap);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide reductions through shared memory (red must hold 32 floats).
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float r = lane < nw ? red[lane] : 0.f;
+  r = warp_sum(r);
+  return r;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float r = lane < nw ? red[lane] : -INFINITY;
+  r = warp_max(r);
+  return r;
+}
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4_stream(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4_stream(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
+
+__device__ __forceinline__ float sigmoidf_dev(float x) { return 1.0f / (1.0f + expf(-x)); }
+#endif

@@ -1,0 +1,101 @@
+// fp32 CUDA-core GEMM: the any-shape fallback behind dyb200_gemm_fused, and the dispatcher.
+// 64x64 output tile per CTA, K step 16, 4x4 register micro-tile per thread.
+#include "gemm.cuh"
+
+namespace {
+
+constexpr int TM = 64, TN = 64, TK = 16;
+
+__device__ __forceinline__ float load_a(const GemmPair& p, uint32_t m, uint32_t k, uint32_t M) {
+  if (m >= M || k >= p.K) return 0.f;
+  return p.transA ? p.A[k + (size_t)p.lda * m] : p.A[m + (size_t)p.lda * k];
+}
+__device__ __forceinline__ float load_b(const GemmPair& p, uint32_t k, uint32_t n, uint32_t N) {
+  if (n >= N || k >= p.K) return 0.f;
+  uint32_t r = p.transB ? n : k, c = p.transB ? k : n;
+  float v = p.B[r + (size_t)p.ldb * c];
+  if (p.maskB) v *= p.maskB[r + (p.mask_full ? (size_t)p.mask_ld * c : 0)];
+  return v;
+}
+
+__global__ void __launch_bounds__(256) k_gemm_simt(uint32_t M, uint32_t N, int npairs, GemmPair p0, GemmPair p1,
+                                                  GemmEpilogue epi) {
+  __shared__ float As[TK][TM + 4];
+  __shared__ float Bs[TK][TN + 4];
+  const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+  const uint32_t m0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
+  float acc[4][4] = {};
+  for (int pi = 0; pi < npairs; ++pi) {
+    const GemmPair& p = pi == 0 ? p0 : p1;
+    for (uint32_t k0 = 0; k0 < p.K; k0 += TK) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (p.transA) { int k = tid % 16, m = tid / 16 + 16 * j; As[k][m] = load_a(p, m0 + m, k0 + k, M); }
+        else { int m = tid % 64, k = tid / 64 + 4 * j; As[k][m] = load_a(p, m0 + m, k0 + k, M); }
+        if (p.transB) { int n = tid % 64, k = tid / 64 + 4 * j; Bs[k][n] = load_b(p, k0 + k, n0 + n, N); }
+        else { int k = tid % 16, n = tid / 16 + 16 * j; Bs[k][n] = load_b(p, k0 + k, n0 + n, N); }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < TK; ++k) {
+        float a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { a[i] = As[k][tx * 4 + i]; b[i] = Bs[k][ty * 4 + i]; }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+      }
+      __syncthreads();
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t n = n0 + ty * 4 + j;
+    if (n >= N) continue;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t m = m0 + tx * 4 + i;
+      if (m >= M) continue;
+      float* c = epi.C + m + (size_t)epi.ldc * n;
+      float v = acc[i][j];
+      if (epi.mode == EPI_STORE) *c = v;
+      else if (epi.mode == EPI_ACCUM) *c += v;
+      else if (epi.mode == EPI_GATES) {
+        v += epi.bias[m];
+        if (m >= epi.H && m < 2 * epi.H) v += epi.forget_bias;
+        *c = m < 3 * epi.H ? sigmoidf_dev(v) : tanhf(v);
+      } else {
+        *c += v * epi.maskC[m + (epi.maskc_full ? (size_t)epi.maskc_ld * n : 0)];
+      }
+    }
+  }
+}
+
+}  // namespace
+
+int dyb200_gemm_simt(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const GemmPair* pairs, const GemmEpilogue& epi) {
+  if (M == 0 || N == 0) return DYB200_OK;
+  GemmPair p0 = pairs[0], p1 = npairs > 1 ? pairs[1] : pairs[0];
+  dim3 grid((M + TM - 1) / TM, (N + TN - 1) / TN);
+  DYB_CHECK_ARG(ctx, grid.y <= 65535, "gemm: N too large for the CUDA-core path");
+  k_gemm_simt<<<grid, 256, 0, ctx->stream>>>(M, N, npairs, p0, p1, epi);
+  DYB_LAUNCHED(ctx);
+  return DYB200_OK;
+}
+
+int dyb200_gemm_fused(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const GemmPair* pairs, const GemmEpilogue& epi) {
+  int handled = 0;
+  int rc = dyb200_gemm_tc(ctx, M, N, npairs, pairs, epi, &handled);
+  if (handled) return rc;
+  return dyb200_gemm_simt(ctx, M, N, npairs, pairs, epi);
+}
+
+extern "C" int dyb200_gemm(int transA, int transB, uint32_t M, uint32_t N, uint32_t K, const float* A, uint32_t lda,
+                           const float* B, uint32_t ldb, float* C, uint32_t ldc, int accumulate, dyb200_ctx* ctx) {
+  DYB_CHECK_ARG(ctx, A && B && C, "gemm: null pointer");
+  DYB_CHECK_ARG(ctx, lda >= (transA ? K : M) && ldb >= (transB ? N : K) && ldc >= M, "gemm: leading dimension too small");
+  GemmPair p{A, lda, transA, B, ldb, transB, K, nullptr, 0, 0};
+  GemmEpilogue e{accumulate ? EPI_ACCUM : EPI_STORE, C, ldc, nullptr, 0, 0.f, nullptr, 0, 0};
+  return dyb200_gemm_fused(ctx, M, N, 1, &p, e);
+}

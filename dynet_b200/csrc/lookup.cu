@@ -1,0 +1,282 @@
+// LookupNode forward (embedding row gather) and LookupParameterStorage::accumulate_grads
+// (deterministic scatter-add).
+//
+// Gather: one warp per looked-up row; the row is staged through shared memory by the
+// bulk-copy (TMA) engine -- cp.async.bulk global->shared completing on an mbarrier, then
+// cp.async.bulk shared->global -- with two buffers per warp so the next row's load overlaps
+// the current row's store.  No multicast is used anywhere.  Rows that are not 16-byte
+// multiples fall back to plain loads.
+//
+// Scatter-add: (id, position) pairs are sorted by id inside one CTA (bitonic, <= 4096 pairs
+// per pass), equal ids form a segment, and one warp per (segment, 128-float column slice)
+// adds the segment's rows to the table row in ascending position -- the same order as the
+// reference's CPU loop (dynet/model.cc:735-741), with no atomics.
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "sortseg.cuh"
+
+namespace {
+
+constexpr int kGatherWarps = 8;
+constexpr int kGatherRowBytesMax = 4096;  // per buffer; 2 buffers per warp
+constexpr uint32_t kWaitLimit = 1u << 22; // bounded mbarrier wait (iterations)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Returns false if the wait ran out (the caller sets the error flag and stops).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done = 0;
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Wait until at most `N` bulk stores of this thread still READ their shared source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// ---- gather, bulk-copy staged -----------------------------------------------------------
+__global__ void __launch_bounds__(kGatherWarps * 32) k_gather_bulk(const float* __restrict__ table,
+                                                                  const uint32_t* __restrict__ ids, uint32_t n,
+                                                                  uint32_t E, uint32_t vocab, float scale,
+                                                                  float* __restrict__ out, uint32_t* flags) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ uint64_t bars[kGatherWarps][2];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t row_bytes = E * 4u;
+  unsigned char* buf0 = smem + (size_t)warp * 2 * row_bytes;
+  unsigned char* buf[2] = {buf0, buf0 + row_bytes};
+  if (lane == 0) { mbar_init(&bars[warp][0], 1); mbar_init(&bars[warp][1], 1); }
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+  const uint32_t nwarps = gridDim.x * kGatherWarps;
+  uint32_t first = blockIdx.x * kGatherWarps + warp;
+  uint32_t phase[2] = {0, 0};
+  bool ok = true;
+  // prologue: issue the first load
+  auto issue = [&](uint32_t b, int s) {
+    if (lane == 0) {
+      uint32_t id = ids[b];
+      if (id >= vocab) { atomicOr(flags, DYB200_FLAG_BAD_INDEX); id = vocab - 1; }
+      mbar_expect_tx(&bars[warp][s], row_bytes);
+      bulk_g2s(buf[s], table + (size_t)id * E, row_bytes, &bars[warp][s]);
+    }
+  };
+  int s = 0;
+  if (first < n) issue(first, 0);
+  for (uint32_t b = first; b < n && ok; b += nwarps, s ^= 1) {
+    uint32_t nb = b + nwarps;
+    if (nb < n) {
+      // buffer s^1 was the source of the store issued one iteration ago
+      if (lane == 0) bulk_wait_read<0>();
+      __syncwarp();
+      issue(nb, s ^ 1);
+    }
+    ok = mbar_wait(&bars[warp][s], phase[s]);
+    phase[s] ^= 1;
+    if (!ok) { if (lane == 0) atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT); break; }
+    float* dst = out + (size_t)b * E;
+    if (scale == 1.0f) {
+      if (lane == 0) bulk_s2g(dst, buf[s], row_bytes);
+    } else {
+      const float4* src4 = reinterpret_cast<const float4*>(buf[s]);
+      for (uint32_t i = lane; i < E / 4; i += 32) {
+        float4 v = src4[i];
+        st4_stream(dst + 4 * i, make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale));
+      }
+      __syncwarp();
+    }
+  }
+  if (lane == 0) bulk_wait_all();  // shared memory must outlive the stores that read it
+}
+
+// ---- gather, plain loads (rows that are not 16-byte multiples, or very long rows) ---------
+__global__ void __launch_bounds__(256) k_gather_plain(const float* __restrict__ table, const uint32_t* __restrict__ ids,
+                                                     uint32_t n, uint32_t E, uint32_t vocab, float scale,
+                                                     float* __restrict__ out, uint32_t* flags, int vec) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t nwarps = gridDim.x * 8;
+  for (uint32_t b = blockIdx.x * 8 + warp; b < n; b += nwarps) {
+    uint32_t id = ids[b];
+    if (id >= vocab) { if (lane == 0) atomicOr(flags, DYB200_FLAG_BAD_INDEX); id = vocab - 1; }
+    const float* src = table + (size_t)id * E;
+    float* dst = out + (size_t)b * E;
+    if (vec) {
+      for (uint32_t i = lane; i < E / 4; i += 32) {
+        float4 v = ld4(src + 4 * i);
+        st4_stream(dst + 4 * i, make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale));
+      }
+    } else {
+      for (uint32_t i = lane; i < E; i += 32) dst[i] = src[i] * scale;
+    }
+  }
+}
+
+// ---- scatter-add: sort + segment + reduce ---------------------------------------------------
+// key = id << 32 | position: sorting groups equal ids and keeps positions ascending inside a group.
+__global__ void __launch_bounds__(kSortThreads) k_sort_segments(const uint32_t* __restrict__ ids, uint32_t n,
+                                                               uint32_t base, uint32_t vocab,
+                                                               uint32_t* __restrict__ pos_sorted,
+                                                               uint32_t* __restrict__ id_sorted,
+                                                               uint32_t* __restrict__ seg_start,
+                                                               uint32_t* __restrict__ nseg, uint32_t* flags) {
+  __shared__ unsigned long long keys[kSortMax];
+  __shared__ uint32_t scan[kSortThreads];
+  uint32_t npow = 1;
+  while (npow < n) npow <<= 1;
+  for (uint32_t k = threadIdx.x; k < npow; k += kSortThreads) {
+    unsigned long long key = ~0ull;  // padding sorts last
+    if (k < n) {
+      uint32_t id = ids[base + k];
+      if (id >= vocab) { atomicOr(flags, DYB200_FLAG_BAD_INDEX); id = vocab - 1; }
+      key = ((unsigned long long)id << 32) | (base + k);
+    }
+    keys[k] = key;
+  }
+  __syncthreads();
+  sort_and_segment(keys, scan, n, npow, 32, pos_sorted, id_sorted, seg_start, nseg);
+}
+
+// One warp per (segment, slice of 128 floats): row = table row; row += g[pos] for the segment's
+// positions in ascending order; write the row back.  Loads of up to 4 source rows are issued
+// ahead of the dependent adds.
+__global__ void __launch_bounds__(256) k_segment_add(const float* __restrict__ g, float* __restrict__ all_grads,
+                                                    uint32_t E, const uint32_t* __restrict__ pos_sorted,
+                                                    const uint32_t* __restrict__ id_sorted,
+                                                    const uint32_t* __restrict__ seg_start,
+                                                    const uint32_t* __restrict__ nseg, uint32_t slices, int vec) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t U = *nseg;
+  const size_t work = (size_t)U * slices;
+  for (size_t w = (size_t)blockIdx.x * 8 + warp; w < work; w += (size_t)gridDim.x * 8) {
+    const uint32_t u = (uint32_t)(w / slices), sl = (uint32_t)(w % slices);
+    const uint32_t k0 = seg_start[u], k1 = seg_start[u + 1];
+    float* row = all_grads + (size_t)id_sorted[u] * E;
+    if (vec) {
+      const uint32_t col = sl * 128 + lane * 4;
+      if (col >= E) continue;
+      float4 acc = ld4(row + col);
+      uint32_t k = k0;
+      for (; k + 4 <= k1; k += 4) {
+        float4 v0 = ld4_stream(g + (size_t)pos_sorted[k] * E + col), v1 = ld4_stream(g + (size_t)pos_sorted[k + 1] * E + col);
+        float4 v2 = ld4_stream(g + (size_t)pos_sorted[k + 2] * E + col), v3 = ld4_stream(g + (size_t)pos_sorted[k + 3] * E + col);
+        acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
+        acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
+        acc.x += v2.x; acc.y += v2.y; acc.z += v2.z; acc.w += v2.w;
+        acc.x += v3.x; acc.y += v3.y; acc.z += v3.z; acc.w += v3.w;
+      }
+      for (; k < k1; ++k) {
+        float4 v = ld4_stream(g + (size_t)pos_sorted[k] * E + col);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      st4(row + col, acc);
+    } else {
+      for (uint32_t col = sl * 128 + lane; col < min(E, (sl + 1) * 128); col += 32) {
+        float acc = row[col];
+        for (uint32_t k = k0; k < k1; ++k) acc += g[(size_t)pos_sorted[k] * E + col];
+        row[col] = acc;
+      }
+    }
+  }
+}
+
+}  // namespace
+
+// Runs the sort + segmented-add passes using `scratch`, which must hold at least
+// dyb200_lookup_scatter_scratch_bytes(min(n, kSortMax)) bytes.
+size_t dyb200_lookup_scatter_scratch_bytes(uint32_t n_pass) { return ((size_t)3 * n_pass + 8) * sizeof(uint32_t); }
+
+int dyb200_lookup_scatter_run(dyb200_ctx* ctx, unsigned n, const unsigned* ids_dev, const float* g, float* all_grads,
+                              unsigned E, unsigned vocab, void* scratch) {
+  const int vec = (E % 4 == 0) && aligned16(g) && aligned16(all_grads);
+  const uint32_t slices = (E + 127) / 128;
+  for (uint32_t base = 0; base < n; base += kSortMax) {
+    uint32_t np = n - base < (uint32_t)kSortMax ? n - base : (uint32_t)kSortMax;
+    uint32_t* pos_sorted = (uint32_t*)scratch;
+    uint32_t* id_sorted = pos_sorted + np;
+    uint32_t* seg_start = id_sorted + np;       // np + 1 entries
+    uint32_t* nseg = seg_start + np + 1;
+    k_sort_segments<<<1, kSortThreads, 0, ctx->stream>>>(ids_dev, np, base, vocab, pos_sorted, id_sorted, seg_start, nseg, ctx->dev_flags);
+    DYB_LAUNCHED(ctx);
+    size_t work = (size_t)np * slices;  // upper bound: every position its own segment
+    k_segment_add<<<stream_grid(ctx, work, 8), 256, 0, ctx->stream>>>(g, all_grads, E, pos_sorted, id_sorted, seg_start, nseg, slices, vec);
+    DYB_LAUNCHED(ctx);
+  }
+  return DYB200_OK;
+}
+
+extern "C" {
+
+int dyb200_lookup_fwd(DYB200_FWD_ARGS) {
+  DYB_CHECK_ARG(ctx, nxs == 0 && xs == nullptr, "Failed dimension check in LookupNode::forward (no inputs expected)");
+  DYB_CHECK_ARG(ctx, attrs != nullptr && aux_mem != nullptr, "LookupNode: attrs and aux_mem (bd uint32) required");
+  const dyb200_lookup_attrs* a = (const dyb200_lookup_attrs*)attrs;
+  const uint32_t n = a->n, E = (uint32_t)t_batch_size(fx);
+  DYB_CHECK_ARG(ctx, fx->bd == n, "In LookupNode, in index vector size (%u) doesn't match batch size in expressions (%u)", n, fx->bd);
+  for (uint32_t b = 0; b < n; ++b)
+    DYB_CHECK_ARG(ctx, a->ids_host[b] < a->vocab, "Out-of-bounds attempt to access index %u for LookupParameter of size %u", a->ids_host[b], a->vocab);
+  if (n == 0 || E == 0) return DYB200_OK;
+  uint32_t* ids_dev = (uint32_t*)aux_mem;
+  DYB_CUDA(ctx, cudaMemcpyAsync(ids_dev, a->ids_host, n * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+  const bool al = aligned16(a->all_values) && aligned16(fx->v) && E % 4 == 0;
+  if (al && E * 4u <= (uint32_t)kGatherRowBytesMax) {
+    size_t smem = (size_t)kGatherWarps * 2 * E * 4;
+    static bool attr_set = false;
+    if (!attr_set) {
+      DYB_CUDA(ctx, cudaFuncSetAttribute(k_gather_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, kGatherWarps * 2 * kGatherRowBytesMax));
+      attr_set = true;
+    }
+    unsigned grid = stream_grid(ctx, n, kGatherWarps, 3);
+    k_gather_bulk<<<grid, kGatherWarps * 32, smem, ctx->stream>>>(a->all_values, ids_dev, n, E, a->vocab, a->weight_decay_scale, fx->v, ctx->dev_flags);
+  } else {
+    k_gather_plain<<<stream_grid(ctx, n, 8), 256, 0, ctx->stream>>>(a->all_values, ids_dev, n, E, a->vocab, a->weight_decay_scale, fx->v, ctx->dev_flags, al ? 1 : 0);
+  }
+  DYB_LAUNCHED(ctx);
+  return DYB200_OK;
+}
+
+int dyb200_lookup_accumulate_grads(unsigned n, const unsigned* ids_host, const unsigned* ids_dev, const float* g,
+                                   float* all_grads, unsigned dim_size, unsigned vocab, dyb200_ctx* ctx) {
+  DYB_CHECK_ARG(ctx, ids_dev != nullptr && g != nullptr && all_grads != nullptr, "accumulate_grads: null pointer");
+  if (ids_host)
+    for (unsigned b = 0; b < n; ++b)
+      DYB_CHECK_ARG(ctx, ids_host[b] < vocab, "Out-of-bounds attempt to access index %u for LookupParameter of size %u", ids_host[b], vocab);
+  if (n == 0 || dim_size == 0) return DYB200_OK;
+  uint32_t np = n < (unsigned)kSortMax ? n : (unsigned)kSortMax;
+  void* scratch;
+  int rc = dyb200_scratch(ctx, dyb200_lookup_scatter_scratch_bytes(np), &scratch);
+  if (rc) return rc;
+  return dyb200_lookup_scatter_run(ctx, n, ids_dev, g, all_grads, dim_size, vocab, scratch);
+}
+
+}  // extern "C"

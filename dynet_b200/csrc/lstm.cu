@@ -1,0 +1,315 @@
+// Fused LSTM nodes: VanillaLSTMGates, VanillaLSTMC, VanillaLSTMH.
+//
+// Gates forward is ONE GEMM launch: both products (Wx*x and Wh*h) accumulate into the same
+// output tile, dropout masks are applied to the activations as they are loaded, and the
+// epilogue adds the bias (+ forget-gate bias on rows [H,2H)) and applies sigmoid / tanh.
+// Gates backward forms the gate pre-activation gradient dgate once per call in scratch and
+// then runs one transposed GEMM (dx, dh: mask fused in the epilogue) or one outer-product
+// GEMM over the batch (dWx, dWh: mask fused in the operand load), or a deterministic batch
+// reduction (db).  C and H are single-pass 128-bit elementwise kernels over gate slices.
+#include "common.cuh"
+#include "gemm.cuh"
+#include "reduce.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// dgate = dE * g * (1 - g) on rows [0, 3H), dE * (1 - g^2) on rows [3H, 4H)
+__device__ __forceinline__ float gate_deriv(float g, float d, bool is_tanh) {
+  return is_tanh ? d * (1.f - g * g) : d * g * (1.f - g);
+}
+__global__ void __launch_bounds__(kThreads) k_gate_deriv(const float* __restrict__ fx, const float* __restrict__ dEdf,
+                                                        float* __restrict__ dg, uint32_t H, size_t total, int vec) {
+  const uint32_t G = 4 * H;
+  if (vec) {
+    size_t n4 = total / 4;
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n4; i += (size_t)gridDim.x * kThreads) {
+      float4 g = ld4(fx + 4 * i), d = ld4(dEdf + 4 * i);
+      bool t = (uint32_t)((4 * i) % G) >= 3 * H;  // H % 4 == 0, so a vector never straddles gates
+      st4(dg + 4 * i, make_float4(gate_deriv(g.x, d.x, t), gate_deriv(g.y, d.y, t), gate_deriv(g.z, d.z, t), gate_deriv(g.w, d.w, t)));
+    }
+  } else {
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (size_t)gridDim.x * kThreads)
+      dg[i] = gate_deriv(fx[i], dEdf[i], (uint32_t)(i % G) >= 3 * H);
+  }
+}
+struct GateDerivSum {  // db[r] += sum_b dgate[r, b]
+  const float *fx, *dEdf;
+  uint32_t H;
+  __device__ float operator()(size_t r, uint32_t b) const {
+    size_t k = (size_t)b * 4 * H + r;
+    return gate_deriv(fx[k], dEdf[k], r >= 3u * H);
+  }
+};
+
+// weightnoise_std > 0: the reference skips both products, so the output is act(bias) only.
+__global__ void __launch_bounds__(kThreads) k_gates_bias_only(const float* __restrict__ bias, float* __restrict__ fx,
+                                                             uint32_t H, size_t total, float forget_bias) {
+  const uint32_t G = 4 * H;
+  for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (size_t)gridDim.x * kThreads) {
+    uint32_t r = (uint32_t)(i % G);
+    float v = bias[r] + ((r >= H && r < 2 * H) ? forget_bias : 0.f);
+    fx[i] = r < 3 * H ? sigmoidf_dev(v) : tanhf(v);
+  }
+}
+
+// Concatenate k inputs along dim 0 into one I x B matrix (only used when k > 1).
+__global__ void __launch_bounds__(kThreads) k_concat_rows(const float* __restrict__ src, uint32_t d, uint32_t off,
+                                                         uint32_t I, uint32_t B, float* __restrict__ dst) {
+  size_t total = (size_t)d * B;
+  for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < total; e += (size_t)gridDim.x * kThreads) {
+    size_t b = e / d, r = e % d;
+    dst[b * I + off + r] = src[e];
+  }
+}
+
+// ---- C and H ---------------------------------------------------------------------------
+// MODE 0: c = i*g + f*c_tm1                     (VanillaLSTMC forward)
+// MODE 1: h = o * tanh(c)                       (VanillaLSTMH forward)
+template <int MODE, int VEC>
+__global__ void __launch_bounds__(kThreads) k_lstm_ch_fwd(const float* __restrict__ st, const float* __restrict__ gates,
+                                                         float* __restrict__ out, uint32_t H, size_t total) {
+  constexpr int W = VEC ? 4 : 1;
+  for (size_t e = ((size_t)blockIdx.x * kThreads + threadIdx.x) * W; e < total; e += (size_t)gridDim.x * kThreads * W) {
+    size_t b = e / H, j = e % H;
+    const float* g = gates + b * 4 * H;
+    if (VEC) {
+      float4 s = ld4_stream(st + e), r;
+      if (MODE == 0) {
+        float4 gi = ld4_stream(g + j), gf = ld4_stream(g + H + j), gg = ld4_stream(g + 3 * H + j);
+        r = make_float4(gi.x * gg.x + gf.x * s.x, gi.y * gg.y + gf.y * s.y, gi.z * gg.z + gf.z * s.z, gi.w * gg.w + gf.w * s.w);
+      } else {
+        float4 go = ld4_stream(g + 2 * H + j);
+        r = make_float4(go.x * tanhf(s.x), go.y * tanhf(s.y), go.z * tanhf(s.z), go.w * tanhf(s.w));
+      }
+      st4(out + e, r);
+    } else {
+      out[e] = MODE == 0 ? g[j] * g[3 * H + j] + g[H + j] * st[e] : g[2 * H + j] * tanhf(st[e]);
+    }
+  }
+}
+// Backward, scalar index math shared by the vector and scalar variants.
+// C, i=0: dc_tm1 += dc * f.   C, i=1: di += dc*g ; df += dc*c_tm1 ; dg += dc*i.
+// H, i=0: dc += dh * o * (1 - tanh(c)^2).   H, i=1: do += dh * tanh(c).
+template <int NODE, int VEC>
+__global__ void __launch_bounds__(kThreads) k_lstm_ch_bwd(const float* __restrict__ st, const float* __restrict__ gates,
+                                                         const float* __restrict__ d, unsigned i,
+                                                         float* __restrict__ dxi, uint32_t H, size_t total) {
+  constexpr int W = VEC ? 4 : 1;
+  for (size_t e = ((size_t)blockIdx.x * kThreads + threadIdx.x) * W; e < total; e += (size_t)gridDim.x * kThreads * W) {
+    size_t b = e / H, j = e % H;
+    const float* g = gates + b * 4 * H;
+    float* og = dxi + b * 4 * H;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      float dv = d[e + w];
+      if (NODE == 0) {
+        if (i == 0) dxi[e + w] += dv * g[H + j + w];
+        else {
+          og[j + w] += dv * g[3 * H + j + w];
+          og[H + j + w] += dv * st[e + w];
+          og[3 * H + j + w] += dv * g[j + w];
+        }
+      } else {
+        float t = tanhf(st[e + w]);
+        if (i == 0) dxi[e + w] += dv * g[2 * H + j + w] * (1.f - t * t);
+        else og[2 * H + j + w] += dv * t;
+      }
+    }
+  }
+}
+
+struct GatesArgs {
+  unsigned k;                 // number of x inputs
+  const dyb200_tensor *h, *Wx, *Wh, *b, *mx, *mh;
+  uint32_t H, I, B;
+};
+
+int parse_gates(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, const dyb200_lstm_gates_attrs* a, GatesArgs* g) {
+  DYB_CHECK_ARG(ctx, a != nullptr, "VanillaLSTMGates: attrs required");
+  const int fixed = a->dropout ? 6 : 4;
+  DYB_CHECK_ARG(ctx, nxs >= fixed + 1, "Failed input count check in VanillaLSTMGates");
+  g->k = (unsigned)(nxs - fixed);
+  g->h = &xs[g->k]; g->Wx = &xs[g->k + 1]; g->Wh = &xs[g->k + 2]; g->b = &xs[g->k + 3];
+  g->mx = a->dropout ? &xs[g->k + 4] : nullptr;
+  g->mh = a->dropout ? &xs[g->k + 5] : nullptr;
+  g->H = t_dim(g->h, 0);
+  g->I = t_dim(g->Wx, 1);
+  g->B = xs[0].bd;
+  uint32_t sum = 0;
+  for (unsigned j = 0; j < g->k; ++j) {
+    DYB_CHECK_ARG(ctx, xs[j].nd == 1, "VanillaLSTMGates: x_t[%u] expected to be a vector", j);
+    DYB_CHECK_ARG(ctx, xs[j].bd == g->B, "VanillaLSTMGates: x_t has inconsistent batch size");
+    sum += xs[j].d[0];
+  }
+  DYB_CHECK_ARG(ctx, sum == g->I, "VanillaLSTMGates: x_t has inconsistent dimension");
+  DYB_CHECK_ARG(ctx, g->h->nd == 1 && g->h->bd == g->B, "VanillaLSTMGates: h_tm1 expected to be a vector with the batch size of x_t");
+  DYB_CHECK_ARG(ctx, g->Wx->nd == 2 && g->Wx->bd == 1, "VanillaLSTMGates: Wx expected to be a matrix");
+  DYB_CHECK_ARG(ctx, g->Wh->nd == 2 && g->Wh->bd == 1, "VanillaLSTMGates: Wh expected to be a matrix");
+  DYB_CHECK_ARG(ctx, g->b->nd == 1 && g->b->bd == 1, "VanillaLSTMGates: b expected to be a vector");
+  DYB_CHECK_ARG(ctx, g->Wx->d[0] == 4 * g->H, "VanillaLSTMGates: Wx dim 0 expected %u, was %u", 4 * g->H, g->Wx->d[0]);
+  DYB_CHECK_ARG(ctx, g->Wh->d[0] == 4 * g->H, "VanillaLSTMGates: Wh dim 0 expected %u, was %u", 4 * g->H, g->Wh->d[0]);
+  DYB_CHECK_ARG(ctx, g->Wh->d[1] == g->H, "VanillaLSTMGates: Wh dim 1 expected %u, was %u", g->H, g->Wh->d[1]);
+  DYB_CHECK_ARG(ctx, g->b->d[0] == 4 * g->H, "VanillaLSTMGates: b dim expected %u, was %u", 4 * g->H, g->b->d[0]);
+  if (a->dropout) {
+    DYB_CHECK_ARG(ctx, g->mx->nd == 1 && g->mh->nd == 1, "VanillaLSTMGates: dropout masks expected to be vectors");
+    DYB_CHECK_ARG(ctx, g->mx->bd == g->B || g->mx->bd == 1, "VanillaLSTMGates: dropout_mask_x expected to have batch size 1 or %u, was %u", g->B, g->mx->bd);
+    DYB_CHECK_ARG(ctx, g->mh->bd == g->B || g->mh->bd == 1, "VanillaLSTMGates: dropout_mask_h expected to have batch size 1 or %u, was %u", g->B, g->mh->bd);
+    DYB_CHECK_ARG(ctx, g->mx->d[0] == g->I, "VanillaLSTMGates: dropout_mask_x dim 1 expected %u, was %u", g->I, g->mx->d[0]);
+    DYB_CHECK_ARG(ctx, g->mh->d[0] == g->H, "VanillaLSTMGates: dropout_mask_h dim 1 expected %u, was %u", g->H, g->mh->d[0]);
+  }
+  return DYB200_OK;
+}
+
+// x as one I x B matrix: the single input itself, or a concatenation built in `scratch`.
+int gather_x(dyb200_ctx* ctx, const dyb200_tensor* xs, const GatesArgs& g, float* scratch, const float** x_out) {
+  if (g.k == 1) { *x_out = xs[0].v; return DYB200_OK; }
+  uint32_t off = 0;
+  for (unsigned j = 0; j < g.k; ++j) {
+    size_t total = (size_t)xs[j].d[0] * g.B;
+    if (total) {
+      k_concat_rows<<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(xs[j].v, xs[j].d[0], off, g.I, g.B, scratch);
+      DYB_LAUNCHED(ctx);
+    }
+    off += xs[j].d[0];
+  }
+  *x_out = scratch;
+  return DYB200_OK;
+}
+
+int ch_check(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, const char* name) {
+  DYB_CHECK_ARG(ctx, nxs == 2, "Failed input count check in %s", name);
+  DYB_CHECK_ARG(ctx, xs[0].nd == 1 && xs[1].nd == 1, "%s: c and gates_t expected to be vectors", name);
+  DYB_CHECK_ARG(ctx, t_batch_size(&xs[0]) * 4 == t_batch_size(&xs[1]), "%s: gates_t expected 4 times as big as c_t, but %zu*4 != %zu", name, t_batch_size(&xs[0]), t_batch_size(&xs[1]));
+  DYB_CHECK_ARG(ctx, xs[0].bd == xs[1].bd, "%s: gates_t and c_t expected to have equal batch size, but %u != %u", name, xs[0].bd, xs[1].bd);
+  return DYB200_OK;
+}
+
+template <int MODE>
+int ch_fwd(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, dyb200_tensor* fx, const char* name) {
+  int rc = ch_check(ctx, xs, nxs, name);
+  if (rc) return rc;
+  uint32_t H = xs[0].d[0];
+  size_t total = (size_t)H * xs[0].bd;
+  DYB_CHECK_ARG(ctx, t_size(fx) == total, "%s: output size mismatch", name);
+  if (total == 0) return DYB200_OK;
+  bool vec = H % 4 == 0 && aligned16(xs[0].v) && aligned16(xs[1].v) && aligned16(fx->v);
+  if (vec) k_lstm_ch_fwd<MODE, 1><<<stream_grid(ctx, total / 4, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, xs[1].v, fx->v, H, total);
+  else k_lstm_ch_fwd<MODE, 0><<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, xs[1].v, fx->v, H, total);
+  DYB_LAUNCHED(ctx);
+  return DYB200_OK;
+}
+template <int NODE>
+int ch_bwd(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, const dyb200_tensor* dEdf, unsigned i, dyb200_tensor* dEdxi,
+           const char* name) {
+  int rc = ch_check(ctx, xs, nxs, name);
+  if (rc) return rc;
+  DYB_CHECK_ARG(ctx, i < 2, "%s::backward: argument index %u out of range", name, i);
+  uint32_t H = xs[0].d[0];
+  size_t total = (size_t)H * xs[0].bd;
+  DYB_CHECK_ARG(ctx, t_size(dEdf) == total && t_size(dEdxi) == (i == 0 ? total : 4 * total), "%s::backward: size mismatch", name);
+  if (total == 0) return DYB200_OK;
+  if (H % 4 == 0) k_lstm_ch_bwd<NODE, 1><<<stream_grid(ctx, total / 4, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, xs[1].v, dEdf->v, i, dEdxi->v, H, total);
+  else k_lstm_ch_bwd<NODE, 0><<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, xs[1].v, dEdf->v, i, dEdxi->v, H, total);
+  DYB_LAUNCHED(ctx);
+  return DYB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dyb200_vanilla_lstm_gates_fwd(DYB200_FWD_ARGS) {
+  (void)aux_mem;
+  const dyb200_lstm_gates_attrs* a = (const dyb200_lstm_gates_attrs*)attrs;
+  GatesArgs g;
+  int rc = parse_gates(ctx, xs, nxs, a, &g);
+  if (rc) return rc;
+  const uint32_t G = 4 * g.H;
+  DYB_CHECK_ARG(ctx, t_size(fx) == (size_t)G * g.B, "VanillaLSTMGates: output must be Dim({%u}, %u)", G, g.B);
+  if ((size_t)G * g.B == 0) return DYB200_OK;
+  if (a->weightnoise_std > 0.f) {
+    // Reference behaviour (dynet/nodes-lstm.cc:200-219): the noisy copies are built and never used.
+    size_t total = (size_t)G * g.B;
+    k_gates_bias_only<<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(g.b->v, fx->v, g.H, total, a->forget_gate_bias);
+    DYB_LAUNCHED(ctx);
+    return DYB200_OK;
+  }
+  const float* x = nullptr;
+  void* scratch = nullptr;
+  if (g.k > 1) {
+    rc = dyb200_scratch(ctx, (size_t)g.I * g.B * sizeof(float), &scratch);
+    if (rc) return rc;
+  }
+  rc = gather_x(ctx, xs, g, (float*)scratch, &x);
+  if (rc) return rc;
+  GemmPair pairs[2] = {
+      {g.Wx->v, G, 0, x, g.I, 0, g.I, g.mx ? g.mx->v : nullptr, g.I, g.mx ? g.mx->bd == g.B : 0},
+      {g.Wh->v, G, 0, g.h->v, g.H, 0, g.H, g.mh ? g.mh->v : nullptr, g.H, g.mh ? g.mh->bd == g.B : 0}};
+  GemmEpilogue epi{EPI_GATES, fx->v, G, g.b->v, g.H, a->forget_gate_bias, nullptr, 0, 0};
+  return dyb200_gemm_fused(ctx, G, g.B, 2, pairs, epi);
+}
+
+int dyb200_vanilla_lstm_gates_bwd(DYB200_BWD_ARGS) {
+  (void)aux_mem;
+  const dyb200_lstm_gates_attrs* a = (const dyb200_lstm_gates_attrs*)attrs;
+  GatesArgs g;
+  int rc = parse_gates(ctx, xs, nxs, a, &g);
+  if (rc) return rc;
+  const uint32_t G = 4 * g.H;
+  const size_t total = (size_t)G * g.B;
+  DYB_CHECK_ARG(ctx, i < g.k + 4, "VanillaLSTMGates::backward: no gradient for argument %u", i);
+  DYB_CHECK_ARG(ctx, t_size(fx) == total && t_size(dEdf) == total, "VanillaLSTMGates::backward: gates size mismatch");
+  if (total == 0) return DYB200_OK;
+  if (i == g.k + 3) {  // db
+    DYB_CHECK_ARG(ctx, t_size(dEdxi) == G, "VanillaLSTMGates::backward: db size mismatch");
+    GateDerivSum f{fx->v, dEdf->v, g.H};
+    return batch_reduce_add(ctx, f, G, g.B, dEdxi->v);
+  }
+  // scratch: dgate (G x B) [+ concatenated x (I x B)]
+  size_t dg_bytes = (total * sizeof(float) + 255) & ~(size_t)255;
+  bool need_x = (i == g.k + 1) && g.k > 1;
+  void* scratch;
+  rc = dyb200_scratch(ctx, dg_bytes + (need_x ? (size_t)g.I * g.B * sizeof(float) : 0), &scratch);
+  if (rc) return rc;
+  float* dg = (float*)scratch;
+  int vec = g.H % 4 == 0 && aligned16(fx->v) && aligned16(dEdf->v);
+  k_gate_deriv<<<stream_grid(ctx, vec ? total / 4 : total, kThreads), kThreads, 0, ctx->stream>>>(fx->v, dEdf->v, dg, g.H, total, vec);
+  DYB_LAUNCHED(ctx);
+  if (i < g.k) {  // dx_i = Wx[:, slice_i]^T dgate (.* mask slice)
+    uint32_t off = 0, di = xs[i].d[0];
+    for (unsigned j = 0; j < i; ++j) off += xs[j].d[0];
+    DYB_CHECK_ARG(ctx, t_size(dEdxi) == (size_t)di * g.B, "VanillaLSTMGates::backward: dx size mismatch");
+    GemmPair p{g.Wx->v + (size_t)off * G, G, 1, dg, G, 0, G, nullptr, 0, 0};
+    GemmEpilogue e{g.mx ? EPI_ACCUM_MASK : EPI_ACCUM, dEdxi->v, di, nullptr, 0, 0.f, g.mx ? g.mx->v + off : nullptr, g.I, g.mx ? g.mx->bd == g.B : 0};
+    return dyb200_gemm_fused(ctx, di, g.B, 1, &p, e);
+  }
+  if (i == g.k) {  // dh = Wh^T dgate (.* mask_h)
+    DYB_CHECK_ARG(ctx, t_size(dEdxi) == (size_t)g.H * g.B, "VanillaLSTMGates::backward: dh size mismatch");
+    GemmPair p{g.Wh->v, G, 1, dg, G, 0, G, nullptr, 0, 0};
+    GemmEpilogue e{g.mh ? EPI_ACCUM_MASK : EPI_ACCUM, dEdxi->v, g.H, nullptr, 0, 0.f, g.mh ? g.mh->v : nullptr, g.H, g.mh ? g.mh->bd == g.B : 0};
+    return dyb200_gemm_fused(ctx, g.H, g.B, 1, &p, e);
+  }
+  if (i == g.k + 1) {  // dWx += dgate (x .* mask_x)^T, summed over the batch
+    DYB_CHECK_ARG(ctx, t_size(dEdxi) == (size_t)G * g.I, "VanillaLSTMGates::backward: dWx size mismatch");
+    const float* x = nullptr;
+    rc = gather_x(ctx, xs, g, (float*)((char*)scratch + dg_bytes), &x);
+    if (rc) return rc;
+    GemmPair p{dg, G, 0, x, g.I, 1, g.B, g.mx ? g.mx->v : nullptr, g.I, g.mx ? g.mx->bd == g.B : 0};
+    GemmEpilogue e{EPI_ACCUM, dEdxi->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
+    return dyb200_gemm_fused(ctx, G, g.I, 1, &p, e);
+  }
+  // i == k + 2: dWh += dgate (h .* mask_h)^T
+  DYB_CHECK_ARG(ctx, t_size(dEdxi) == (size_t)G * g.H, "VanillaLSTMGates::backward: dWh size mismatch");
+  GemmPair p{dg, G, 0, g.h->v, g.H, 1, g.B, g.mh ? g.mh->v : nullptr, g.H, g.mh ? g.mh->bd == g.B : 0};
+  GemmEpilogue e{EPI_ACCUM, dEdxi->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
+  return dyb200_gemm_fused(ctx, G, g.H, 1, &p, e);
+}
+
+int dyb200_vanilla_lstm_c_fwd(DYB200_FWD_ARGS) { (void)attrs; (void)aux_mem; return ch_fwd<0>(ctx, xs, nxs, fx, "VanillaLSTMC"); }
+int dyb200_vanilla_lstm_c_bwd(DYB200_BWD_ARGS) { (void)fx; (void)attrs; (void)aux_mem; return ch_bwd<0>(ctx, xs, nxs, dEdf, i, dEdxi, "VanillaLSTMC"); }
+int dyb200_vanilla_lstm_h_fwd(DYB200_FWD_ARGS) { (void)attrs; (void)aux_mem; return ch_fwd<1>(ctx, xs, nxs, fx, "VanillaLSTMH"); }
+int dyb200_vanilla_lstm_h_bwd(DYB200_BWD_ARGS) { (void)fx; (void)attrs; (void)aux_mem; return ch_bwd<1>(ctx, xs, nxs, dEdf, i, dEdxi, "VanillaLSTMH"); }
+
+}  // extern "C"

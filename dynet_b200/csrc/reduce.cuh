@@ -1,0 +1,52 @@
+// Deterministic reduction over the batch axis: out[r] += sum_b f(r, b) for r < n.
+// Two fixed stages (ascending b inside a chunk, ascending chunk order after), so
+// the result depends only on (n, B, SM count), never on scheduling.
+#pragma once
+#include "common.cuh"
+
+template <class F>
+__global__ void __launch_bounds__(128) k_batch_reduce_partial(F f, size_t n, uint32_t B, uint32_t chunk,
+                                                             float* __restrict__ partial,
+                                                             float* __restrict__ out, int direct) {
+  size_t r = (size_t)blockIdx.x * 128 + threadIdx.x;
+  if (r >= n) return;
+  uint32_t b0 = blockIdx.y * chunk, b1 = min(B, b0 + chunk);
+  float acc = 0.f;
+  for (uint32_t b = b0; b < b1; ++b) acc += f(r, b);
+  if (direct) out[r] += acc;
+  else partial[(size_t)blockIdx.y * n + r] = acc;
+}
+
+static __global__ void __launch_bounds__(128) k_batch_reduce_final(const float* __restrict__ partial, uint32_t S,
+                                                                   size_t n, float* __restrict__ out) {
+  size_t r = (size_t)blockIdx.x * 128 + threadIdx.x;
+  if (r >= n) return;
+  float acc = 0.f;
+  for (uint32_t s = 0; s < S; ++s) acc += partial[(size_t)s * n + r];
+  out[r] += acc;
+}
+
+template <class F>
+static int batch_reduce_add(dyb200_ctx* ctx, F f, size_t n, uint32_t B, float* out) {
+  if (n == 0 || B == 0) return DYB200_OK;
+  unsigned gx = (unsigned)((n + 127) / 128);
+  unsigned want = (2u * ctx->sm_count + gx - 1) / gx;
+  unsigned S = want < 1 ? 1 : want;
+  if (S > (B + 3) / 4) S = (B + 3) / 4;
+  if (S < 1) S = 1;
+  uint32_t chunk = (B + S - 1) / S;
+  S = (B + chunk - 1) / chunk;
+  if (S == 1) {
+    k_batch_reduce_partial<<<dim3(gx, 1), 128, 0, ctx->stream>>>(f, n, B, chunk, nullptr, out, 1);
+    DYB_LAUNCHED(ctx);
+    return DYB200_OK;
+  }
+  void* scratch = nullptr;
+  int rc = dyb200_scratch(ctx, (size_t)S * n * sizeof(float), &scratch);
+  if (rc) return rc;
+  k_batch_reduce_partial<<<dim3(gx, S), 128, 0, ctx->stream>>>(f, n, B, chunk, (float*)scratch, out, 0);
+  DYB_LAUNCHED(ctx);
+  k_batch_reduce_final<<<gx, 128, 0, ctx->stream>>>((const float*)scratch, S, n, out);
+  DYB_LAUNCHED(ctx);
+  return DYB200_OK;
+}

@@ -1,0 +1,185 @@
+/*
+ * dyb200 — C ABI of the B200 (sm_100a) kernels that replace the Device_GPU
+ * instantiations of DyNet's fused-layer nodes.
+ *
+ * Every node of the reference declares
+ *     template<class MyDevice> void forward_dev_impl(const MyDevice&, const std::vector<const Tensor*>& xs, Tensor& fx) const;
+ *     template<class MyDevice> void backward_dev_impl(const MyDevice&, const std::vector<const Tensor*>& xs,
+ *                                                     const Tensor& fx, const Tensor& dEdf, unsigned i, Tensor& dEdxi) const;
+ * (dynet/nodes-def-macros.h:44-62).  For each node in scope this header exports
+ * one <node>_fwd and one <node>_bwd with exactly those arguments flattened to C:
+ * tensors become dyb200_tensor views, the node's constructor arguments become a
+ * small `attrs` struct, `aux_mem` is the node's aux_storage_size() block.
+ *
+ * Conventions (all identical to the reference):
+ *  - tensors are column-major float32 on the device, the batch is the slowest
+ *    axis (dynet/tensor-eigen.h:21-224); a dyb200_tensor does not own memory;
+ *  - backward ACCUMULATES into dEdxi (dEdxi += ...), once per argument index i
+ *    (dynet/exec.cc:262-271);
+ *  - every call returns a status; nothing aborts, traps or throws.  The C++ shim
+ *    maps DYB200_EINVAL to std::invalid_argument (DYNET_ARG_CHECK, dynet/except.h:41-46),
+ *    DYB200_ERUNTIME to std::runtime_error (dynet/except.h:60-70), DYB200_ECUDA
+ *    to dynet::cuda_exception (dynet/cuda.h:20-43) and DYB200_ENOMEM to
+ *    dynet::out_of_memory (dynet/except.h:11-14);
+ *  - kernels are launched on the context's stream (DyNet uses the legacy default
+ *    stream, dynet/devices.cc:113-114) and the call returns without synchronising
+ *    unless stated otherwise.
+ */
+#ifndef DYB200_H_
+#define DYB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DYB200_OK 0
+#define DYB200_EINVAL 1   /* bad shape / index / argument (reference: std::invalid_argument) */
+#define DYB200_ERUNTIME 2 /* unsupported configuration (reference: std::runtime_error) */
+#define DYB200_ECUDA 3    /* CUDA runtime failure, or a bounded device wait ran out */
+#define DYB200_ENOMEM 4   /* scratch arena could not grow */
+
+/* Mirror of dynet::Dim + the data pointer of dynet::Tensor (dynet/dim.h:24,301-303;
+ * dynet/tensor.h:44-130).  d[k] for k >= nd is ignored (treated as 1). */
+typedef struct dyb200_tensor {
+  float* v;
+  uint32_t d[7];
+  uint32_t nd;
+  uint32_t bd;
+} dyb200_tensor;
+
+/* Per-device state: device id, stream, a grow-only scratch arena owned by the
+ * library (stands in for the SCS pool use of the reference nodes, e.g.
+ * dynet/nodes-lstm.cc:125,234), the last error text. Not thread-safe, like the
+ * reference (one ComputationGraph per process, dynet/dynet.cc:76-79). */
+typedef struct dyb200_ctx dyb200_ctx;
+
+/* Creates the context for `device` (cudaSetDevice) using `stream` (NULL = legacy
+ * default stream, the one dynet/devices.cc:113-114 uses). */
+int dyb200_ctx_create(int device, void* stream, dyb200_ctx** out);
+int dyb200_ctx_destroy(dyb200_ctx* ctx);
+/* Text of the last non-OK status returned through this context ("" if none). */
+const char* dyb200_last_error(const dyb200_ctx* ctx);
+/* Reads (and clears) the device-side error word set by kernels that clamp an
+ * index or give up a bounded wait; synchronises the stream.  0 = clean. */
+int dyb200_ctx_check_device_errors(dyb200_ctx* ctx, uint32_t* flags_out);
+/* Number of kernels this library has launched through `ctx` so far. */
+uint64_t dyb200_ctx_launch_count(const dyb200_ctx* ctx);
+/* Library build string ("dyb200 <n> sm_100a"). */
+const char* dyb200_version(void);
+
+/* ---- attrs structs (the nodes' constructor arguments) ---- */
+typedef struct { float alpha, lambda; } dyb200_elu_attrs;               /* dynet/nodes-activations.h:46-53 */
+typedef struct { uint32_t dimension; } dyb200_dim_attrs;               /* dynet/nodes-softmaxes.h:26, nodes-logsumexp.h */
+typedef struct { const uint32_t* ids_host; uint32_t n; } dyb200_pick_attrs; /* pval / pvals, dynet/nodes-pickneglogsoftmax.h:11-36 */
+typedef struct {                                                        /* dynet/param-nodes.h:84-110 */
+  const float* all_values; /* device, Dim({E}, V) == LookupParameterStorage::all_values */
+  uint32_t vocab;          /* V */
+  const uint32_t* ids_host;
+  uint32_t n;
+  float weight_decay_scale; /* params.current_weight_decay() */
+} dyb200_lookup_attrs;
+typedef struct {                                                        /* dynet/nodes-lstm.h:9-26 */
+  int32_t dropout;
+  float weightnoise_std;
+  float forget_gate_bias;
+} dyb200_lstm_gates_attrs;
+typedef struct {                                                        /* dynet/nodes-moments.h:35-69 */
+  uint32_t dims[2];
+  uint32_t ndims;
+  uint32_t order;            /* MomentDimension only */
+  int32_t include_batch_dim;
+  uint32_t overwrite_n;
+} dyb200_moment_attrs;
+
+#define DYB200_FWD_ARGS const dyb200_tensor *xs, int nxs, dyb200_tensor *fx, const void *attrs, void *aux_mem, dyb200_ctx *ctx
+#define DYB200_BWD_ARGS const dyb200_tensor *xs, int nxs, const dyb200_tensor *fx, const dyb200_tensor *dEdf, unsigned i, dyb200_tensor *dEdxi, const void *attrs, void *aux_mem, dyb200_ctx *ctx
+
+/* ---- A12 unary activations ---- */
+int dyb200_tanh_fwd(DYB200_FWD_ARGS);      /* Tanh::forward_dev_impl, dynet/nodes-trig.cc:312-315 */
+int dyb200_tanh_bwd(DYB200_BWD_ARGS);      /* dynet/nodes-trig.cc:317-327 */
+int dyb200_logistic_fwd(DYB200_FWD_ARGS);  /* LogisticSigmoid, dynet/nodes-activations.cc:64-68 */
+int dyb200_logistic_bwd(DYB200_BWD_ARGS);  /* dynet/nodes-activations.cc:70-79 */
+int dyb200_rectify_fwd(DYB200_FWD_ARGS);   /* Rectify, dynet/nodes-activations.cc:30-34 */
+int dyb200_rectify_bwd(DYB200_BWD_ARGS);   /* dynet/nodes-activations.cc:36-45 */
+int dyb200_elu_fwd(DYB200_FWD_ARGS);       /* ExponentialLinearUnit, attrs = dyb200_elu_attrs, dynet/nodes-activations.cc:166-170 */
+int dyb200_elu_bwd(DYB200_BWD_ARGS);       /* dynet/nodes-activations.cc:172-181 */
+
+/* ---- A13 cwise binary, with per-dim and batch broadcasting ---- */
+int dyb200_cmult_fwd(DYB200_FWD_ARGS);     /* CwiseMultiply, dynet/nodes-arith-cwise.cc:196-251 */
+int dyb200_cmult_bwd(DYB200_BWD_ARGS);     /* dynet/nodes-arith-cwise.cc:253-307 */
+int dyb200_csum_fwd(DYB200_FWD_ARGS);      /* CwiseSum (layer_norm composite), dynet/nodes-arith-cwise.cc:49-97 */
+int dyb200_csum_bwd(DYB200_BWD_ARGS);      /* dynet/nodes-arith-cwise.cc:99-157 */
+int dyb200_cdiv_fwd(DYB200_FWD_ARGS);      /* CwiseQuotient (layer_norm composite), dynet/nodes-arith-cwise.cc:337-351 */
+int dyb200_cdiv_bwd(DYB200_BWD_ARGS);      /* dynet/nodes-arith-cwise.cc:353-412 */
+
+/* ---- A6-A9 softmax family ---- */
+int dyb200_softmax_fwd(DYB200_FWD_ARGS);        /* Softmax, attrs = dyb200_dim_attrs, dynet/nodes-softmaxes.cc:40-87 */
+int dyb200_softmax_bwd(DYB200_BWD_ARGS);        /* dynet/nodes-softmaxes.cc:89-131 */
+int dyb200_log_softmax_fwd(DYB200_FWD_ARGS);    /* LogSoftmax, aux_mem = 2*cols*bd floats, dynet/nodes-softmaxes.cc:156-183 */
+int dyb200_log_softmax_bwd(DYB200_BWD_ARGS);    /* dynet/nodes-softmaxes.cc:186-214 */
+int dyb200_logsumexp_dim_fwd(DYB200_FWD_ARGS);  /* LogSumExpDimension, attrs = dyb200_dim_attrs, dynet/nodes-logsumexp.cc:125-131 + tensor.cc:468-507 */
+int dyb200_logsumexp_dim_bwd(DYB200_BWD_ARGS);  /* dynet/nodes-logsumexp.cc:133-146 */
+int dyb200_logsumexp_fwd(DYB200_FWD_ARGS);      /* n-ary LogSumExp, dynet/nodes-logsumexp.cc:37-73 */
+int dyb200_logsumexp_bwd(DYB200_BWD_ARGS);      /* dynet/nodes-logsumexp.cc:75-98 */
+/* PickNegLogSoftmax: attrs = dyb200_pick_attrs; aux_mem = 2*bd floats + bd uint32
+ * (z, m, flat ids) exactly as aux_storage_size() sizes it, dynet/nodes-pickneglogsoftmax.cc:72-118 */
+int dyb200_pickneglogsoftmax_fwd(DYB200_FWD_ARGS);
+int dyb200_pickneglogsoftmax_bwd(DYB200_BWD_ARGS); /* dynet/nodes-pickneglogsoftmax.cc:120-146 */
+
+/* ---- A10-A11 normalisation ---- */
+int dyb200_weight_norm_fwd(DYB200_FWD_ARGS);   /* WeightNormalization, dynet/nodes-normalization.cc:28-41 (no host sync: g is read on the device) */
+int dyb200_weight_norm_bwd(DYB200_BWD_ARGS);   /* dynet/nodes-normalization.cc:43-66 */
+int dyb200_moment_dim_fwd(DYB200_FWD_ARGS);    /* MomentDimension, attrs = dyb200_moment_attrs, dynet/nodes-moments.cc:181-244 */
+int dyb200_moment_dim_bwd(DYB200_BWD_ARGS);    /* dynet/nodes-moments.cc:246-310 */
+int dyb200_std_dim_fwd(DYB200_FWD_ARGS);       /* StdDimension, attrs = dyb200_moment_attrs, dynet/nodes-moments.cc:434-496 */
+int dyb200_std_dim_bwd(DYB200_BWD_ARGS);       /* dynet/nodes-moments.cc:498-556 */
+/* The whole layer_norm composite (dynet/expr.cc:248-253: 8 nodes) as one kernel.
+ * xs = {x Dim(...,B), g, b (bd 1)}; normalises over all non-batch dims.  Backward
+ * index i: 0 = x, 1 = g, 2 = b.  The first backward call of a node computes all
+ * three gradients' shared row statistics again; nothing is cached across calls. */
+int dyb200_layer_norm_fwd(DYB200_FWD_ARGS);
+int dyb200_layer_norm_bwd(DYB200_BWD_ARGS);
+
+/* ---- A4-A5 embedding ---- */
+/* LookupNode::forward_dev_impl, attrs = dyb200_lookup_attrs, nxs = 0, aux_mem = bd
+ * uint32 (device copy of the ids), dynet/param-nodes.cc:304-329.  Ids are range-
+ * checked on the host (the reference checks only in its CPU branch, :323). */
+int dyb200_lookup_fwd(DYB200_FWD_ARGS);
+/* LookupParameterStorage::accumulate_grads_dev<Device_GPU>, dynet/model.cc:728-747:
+ * all_grads[:, ids[b]] += g[:, b] for b in order (deterministic: sort by id, then a
+ * segmented row reduction that adds the rows of one id in ascending b). */
+int dyb200_lookup_accumulate_grads(unsigned n, const unsigned* ids_host, const unsigned* ids_dev,
+                                   const float* g, float* all_grads, unsigned dim_size,
+                                   unsigned vocab, dyb200_ctx* ctx);
+
+/* ---- A1-A3 fused LSTM nodes ---- */
+/* VanillaLSTMGates: xs = {x_1..x_k, h_tm1, Wx, Wh, b [, mask_x, mask_h]},
+ * attrs = dyb200_lstm_gates_attrs, dynet/nodes-lstm.cc:101-235 / :237-527 */
+int dyb200_vanilla_lstm_gates_fwd(DYB200_FWD_ARGS);
+int dyb200_vanilla_lstm_gates_bwd(DYB200_BWD_ARGS);
+int dyb200_vanilla_lstm_c_fwd(DYB200_FWD_ARGS);  /* xs = {c_tm1, gates}, dynet/nodes-lstm.cc:562-589 */
+int dyb200_vanilla_lstm_c_bwd(DYB200_BWD_ARGS);  /* dynet/nodes-lstm.cc:591-615 */
+int dyb200_vanilla_lstm_h_fwd(DYB200_FWD_ARGS);  /* xs = {c_t, gates}, dynet/nodes-lstm.cc:650-668 */
+int dyb200_vanilla_lstm_h_bwd(DYB200_BWD_ARGS);  /* dynet/nodes-lstm.cc:670-703 */
+
+/* ---- A14 autobatch ragged movers (same argument meaning as dynet/gpu-ops.h:14-15;
+ * src/trg/len are DEVICE arrays of num_seqs entries, as dynet/exec.cc:346-356 uploads them) ---- */
+int dyb200_parallel_memcpy(int num_seqs, int max_len, float** src, float** trg, size_t* len, dyb200_ctx* ctx);
+/* trg[s][0..len[s]) += src[s][...]; sequences that share a target are added in
+ * ascending s (deterministic; the reference uses atomicAdd, dynet/gpu-ops.cu:121-145). */
+int dyb200_parallel_accumulate(int num_seqs, int max_len, float** src, float** trg, size_t* len, dyb200_ctx* ctx);
+
+/* ---- GEMM used by the LSTM gates (dynet/matrix-multiply.h:16-37, :97-117, :162-180) ----
+ * C[M x N] (+)= op(A) * op(B), column-major, fp32 in/out, 3xTF32 on the tensor pipe
+ * when the shape allows (else an fp32 CUDA-core kernel).  transA/transB as in BLAS. */
+int dyb200_gemm(int transA, int transB, uint32_t M, uint32_t N, uint32_t K, const float* A,
+                uint32_t lda, const float* B, uint32_t ldb, float* C, uint32_t ldc, int accumulate,
+                dyb200_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DYB200_H_ */

@@ -1,0 +1,606 @@
+"""GPU parity: every in-scope node, called through the C ABI of libdyb200.so, against the CPU
+oracle on the same seeded inputs.  Bars: bit-exact for gather / indices, 1e-5 relative for
+elementwise ops, 1e-4 for reductions, LSTM states and gradients (absolute floor for values near 0)."""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+import pytest
+
+from util import TOL_CWISE, TOL_REDUCE, assert_close, glorot, randn, rng, zipf_ids
+
+pytestmark = pytest.mark.gpu
+
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_known_answers.json")))
+
+
+@pytest.fixture(scope="module")
+def g():
+    import gpu_util
+    gpu_util.ctx()
+    return gpu_util
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from dynet_b200 import capi as c
+    return c
+
+
+SIZES = [1, 3, 31, 32, 33, 127, 128, 129, 1000, 4097, (1 << 16) + 3]
+
+
+# ------------------------------------------------------------------ unary
+@pytest.mark.parametrize("name", ["tanh", "logistic", "rectify", "elu"])
+@pytest.mark.parametrize("misalign", [0, 1])
+def test_unary(oracle, g, capi, name, misalign):
+    r = rng(100)
+    attrs = capi.EluAttrs(1.0, 1.0) if name == "elu" else None
+    for n in SIZES:
+        x = randn(r, 1, n, scale=3.0)
+        if name == "rectify":
+            x[0, ::7] = 0.0
+        dy = randn(r, 1, n)
+        dx0 = randn(r, 1, n)
+        y_ref = oracle.unary_fwd(name, x)
+        dx_ref = oracle.unary_bwd(name, x, y_ref, dy, dx0.copy())
+        dx_, y_, dy_, dxo = g.dev(x, misalign), g.dev(np.zeros_like(x), misalign), g.dev(dy, misalign), g.dev(dx0, misalign)
+        g.ctx().fwd(name, [g.T(dx_)], g.T(y_), attrs)
+        assert_close(g.host(y_), y_ref, TOL_CWISE, what="%s fwd n=%d" % (name, n))
+        if name == "rectify":
+            assert np.array_equal(g.host(y_), y_ref)
+        g.ctx().bwd(name, [g.T(dx_)], g.T(y_), g.T(dy_), 0, g.T(dxo), attrs)
+        assert_close(g.host(dxo), dx_ref, TOL_CWISE, what="%s bwd n=%d" % (name, n))
+
+
+def test_selu_constants(oracle, g, capi):
+    lam, alpha = 1.0507009873554804934193349852946, 1.6732632423543772848170429916717
+    r = rng(101)
+    x = randn(r, 2, 1001, scale=2.0)
+    y_ref = oracle.unary_fwd("elu", x, alpha, lam)
+    y = g.dev(np.zeros_like(x))
+    g.ctx().fwd("elu", [g.T(g.dev(x))], g.T(y), capi.EluAttrs(alpha, lam))
+    assert_close(g.host(y), y_ref, TOL_CWISE, what="selu")
+
+
+# ------------------------------------------------------------------ cwise binary
+CW_SHAPES = [
+    ((4, 128), (4, 128)),          # same shape, vector path
+    ((4, 130), (4, 130)),          # same shape, n % 4 != 0
+    ((5, 256), (1, 256)),          # right operand batch-broadcast (dropout mask bd=1)
+    ((1, 256), (5, 256)),          # left operand batch-broadcast
+    ((3, 2, 7), (1, 1, 7)),        # broadcast over dim 1 and batch
+    ((3, 2, 7), (3, 2, 1)),        # broadcast over dim 0
+    ((2, 3, 1), (1, 1, 5)),        # both sides broadcast
+]
+
+
+@pytest.mark.parametrize("op", ["cmult", "csum", "cdiv"])
+@pytest.mark.parametrize("sa,sb", CW_SHAPES)
+def test_cwise(oracle, g, op, sa, sb):
+    if op == "cdiv" and any(y > x for x, y in zip(sa, sb)):
+        pytest.skip("CwiseQuotient only broadcasts its right operand")
+    r = rng(110)
+    a = randn(r, *sa) + 2.5
+    b = randn(r, *sb) * 0.3 + 2.0
+    y_ref = oracle.cwise_fwd(op, a, b)
+    a_, b_ = g.dev(a), g.dev(b)
+    y_ = g.dev(np.zeros_like(y_ref))
+    g.ctx().fwd(op, [g.T(a_), g.T(b_)], g.T(y_))
+    assert_close(g.host(y_), y_ref, TOL_CWISE, what=op + " fwd")
+    dy = randn(r, *y_ref.shape)
+    for i, arg in enumerate((a, b)):
+        d0 = randn(r, *arg.shape)
+        want = oracle.cwise_bwd(op, a, b, dy, i, d0.copy())
+        d_ = g.dev(d0)
+        g.ctx().bwd(op, [g.T(a_), g.T(b_)], g.T(y_), g.T(g.dev(dy)), i, g.T(d_))
+        assert_close(g.host(d_), want, TOL_REDUCE, what="%s bwd i=%d" % (op, i))
+
+
+def test_cwise_bad_shape(g, capi):
+    a, b = g.dev(np.zeros((1, 4), np.float32)), g.dev(np.zeros((1, 3), np.float32))
+    with pytest.raises(capi.InvalidArgument):
+        g.ctx().fwd("cmult", [g.T(a), g.T(b)], g.T(g.dev(np.zeros((1, 4), np.float32))))
+
+
+# ------------------------------------------------------------------ softmax family
+@pytest.mark.parametrize("rows,cols,bd", [(1, 1, 1), (3, 2, 2), (45, 7, 3), (256, 3, 2), (257, 2, 2), (1024, 5, 2),
+                                          (4096, 3, 2), (5001, 2, 1), (10000, 1, 3)])
+def test_softmax_dim0(oracle, g, capi, rows, cols, bd):
+    r = rng(120)
+    x = randn(r, bd, cols, rows, scale=2.0)
+    y_ref = oracle.softmax_fwd(x, 0)
+    x_, y_ = g.dev(x), g.dev(np.zeros_like(x))
+    at = capi.DimAttrs(0)
+    g.ctx().fwd("softmax", [g.T(x_)], g.T(y_), at)
+    assert_close(g.host(y_), y_ref, TOL_REDUCE, floor=1e-6, what="softmax d0")
+    dy, d0 = randn(r, bd, cols, rows), randn(r, bd, cols, rows)
+    want = oracle.softmax_bwd(y_ref, dy, d0.copy(), 0)
+    d_ = g.dev(d0)
+    g.ctx().bwd("softmax", [g.T(x_)], g.T(g.dev(y_ref)), g.T(g.dev(dy)), 0, g.T(d_), at)
+    assert_close(g.host(d_), want, TOL_REDUCE, what="softmax d0 bwd")
+
+
+@pytest.mark.parametrize("rows,cols,bd", [(1, 5, 1), (7, 3, 2), (33, 200, 2), (64, 4096, 1), (9, 4500, 1)])
+def test_softmax_dim1(oracle, g, capi, rows, cols, bd):
+    r = rng(121)
+    x = randn(r, bd, cols, rows, scale=2.0)
+    y_ref = oracle.softmax_fwd(x, 1)
+    x_, y_ = g.dev(x), g.dev(np.zeros_like(x))
+    at = capi.DimAttrs(1)
+    g.ctx().fwd("softmax", [g.T(x_)], g.T(y_), at)
+    assert_close(g.host(y_), y_ref, TOL_REDUCE, floor=1e-6, what="softmax d1")
+    dy, d0 = randn(r, bd, cols, rows), randn(r, bd, cols, rows)
+    want = oracle.softmax_bwd(y_ref, dy, d0.copy(), 1)
+    d_ = g.dev(d0)
+    g.ctx().bwd("softmax", [g.T(x_)], g.T(g.dev(y_ref)), g.T(g.dev(dy)), 0, g.T(d_), at)
+    assert_close(g.host(d_), want, TOL_REDUCE, what="softmax d1 bwd")
+
+
+@pytest.mark.parametrize("rows,cols,bd", [(5, 1, 1), (45, 3, 4), (300, 2, 2), (4100, 2, 1)])
+def test_log_softmax(oracle, g, rows, cols, bd):
+    r = rng(122)
+    x = randn(r, bd, cols, rows, scale=2.0)
+    y_ref = oracle.log_softmax_fwd(x)
+    x_, y_ = g.dev(x), g.dev(np.zeros_like(x))
+    aux = g.dev(np.zeros(2 * cols * bd, np.float32))
+    g.ctx().fwd("log_softmax", [g.T(x_)], g.T(y_), None, aux.data_ptr())
+    assert_close(g.host(y_), y_ref, TOL_REDUCE, what="log_softmax")
+    dy, d0 = randn(r, bd, cols, rows), randn(r, bd, cols, rows)
+    want = oracle.log_softmax_bwd(y_ref, dy, d0.copy())
+    d_ = g.dev(d0)
+    g.ctx().bwd("log_softmax", [g.T(x_)], g.T(g.dev(y_ref)), g.T(g.dev(dy)), 0, g.T(d_), None, aux.data_ptr())
+    assert_close(g.host(d_), want, TOL_REDUCE, what="log_softmax bwd")
+
+
+@pytest.mark.parametrize("axis", [0, 1])
+@pytest.mark.parametrize("rows,cols,bd", [(6, 4, 2), (130, 70, 2), (5000, 3, 1), (3, 5000, 1)])
+def test_logsumexp_dim(oracle, g, capi, axis, rows, cols, bd):
+    r = rng(123)
+    x = randn(r, bd, cols, rows, scale=2.0)
+    z_ref, _ = oracle.logsumexp_dim_fwd(x, axis)
+    x_ = g.dev(x)
+    z_ = g.dev(np.zeros_like(z_ref))
+    at = capi.DimAttrs(axis)
+    outer = cols if axis == 0 else rows
+    g.ctx().fwd("logsumexp_dim", [g.T(x_)], g.T(z_, [outer], bd), at)
+    assert_close(g.host(z_), z_ref, TOL_REDUCE, what="logsumexp_dim")
+    dz, d0 = randn(r, *z_ref.shape), randn(r, bd, cols, rows)
+    want = oracle.logsumexp_dim_bwd(x, z_ref, dz, d0.copy(), axis)
+    d_ = g.dev(d0)
+    g.ctx().bwd("logsumexp_dim", [g.T(x_)], g.T(g.dev(z_ref), [outer], bd), g.T(g.dev(dz), [outer], bd), 0, g.T(d_), at)
+    assert_close(g.host(d_), want, TOL_REDUCE, what="logsumexp_dim bwd")
+
+
+def test_logsumexp_nary(oracle, g):
+    r = rng(124)
+    for n, bd in [(5, 3), (1000, 4)]:
+        xs = [randn(r, bd, n), randn(r, 1, n), randn(r, bd, n), randn(r, 1, n)]
+        y_ref = oracle.logsumexp_nary_fwd(xs)
+        xd = [g.dev(x) for x in xs]
+        y_ = g.dev(np.zeros_like(y_ref))
+        g.ctx().fwd("logsumexp", [g.T(t) for t in xd], g.T(y_))
+        assert_close(g.host(y_), y_ref, TOL_REDUCE, what="logsumexp nary")
+        dy = randn(r, bd, n)
+        for i in range(len(xs)):
+            d0 = randn(r, *xs[i].shape)
+            want = oracle.logsumexp_nary_bwd(xs, i, y_ref, dy, d0.copy())
+            d_ = g.dev(d0)
+            g.ctx().bwd("logsumexp", [g.T(t) for t in xd], g.T(g.dev(y_ref)), g.T(g.dev(dy)), i, g.T(d_))
+            assert_close(g.host(d_), want, TOL_REDUCE, what="logsumexp nary bwd %d" % i)
+    x1 = randn(r, 2, 9)
+    y_ = g.dev(np.zeros_like(x1))
+    g.ctx().fwd("logsumexp", [g.T(g.dev(x1))], g.T(y_))
+    assert np.array_equal(g.host(y_), x1)  # single argument: copy (nodes-logsumexp.cc:39-40)
+
+
+@pytest.mark.parametrize("rows,bd", [(1, 1), (45, 200), (1000, 7), (4096, 3), (10000, 64), (50000, 5)])
+def test_pickneglogsoftmax(oracle, g, capi, rows, bd):
+    r = rng(125)
+    x = randn(r, bd, rows, scale=2.0)
+    ids = zipf_ids(r, bd, rows)
+    loss_ref, z_ref = oracle.pnls_fwd(x, ids)
+    x_ = g.dev(x)
+    loss_ = g.dev(np.zeros(bd, np.float32))
+    aux = g.dev(np.zeros(3 * bd, np.float32))
+    ids_np, ids_p = g.u32(ids)
+    at = capi.PickAttrs(ids_p, bd)
+    g.ctx().fwd("pickneglogsoftmax", [g.T(x_, [rows], bd)], g.T(loss_, [1], bd), at, aux.data_ptr())
+    assert_close(g.host(loss_), loss_ref, TOL_REDUCE, what="pnls fwd")
+    assert_close(g.host(aux)[:bd], z_ref, TOL_REDUCE, what="pnls z")
+    dE, d0 = randn(r, bd), randn(r, bd, rows)
+    want = oracle.pnls_bwd(x, ids, z_ref, dE, d0.copy())
+    d_ = g.dev(d0)
+    g.ctx().bwd("pickneglogsoftmax", [g.T(x_, [rows], bd)], g.T(loss_, [1], bd), g.T(g.dev(dE), [1], bd), 0,
+                g.T(d_, [rows], bd), at, aux.data_ptr())
+    assert_close(g.host(d_), want, TOL_REDUCE, what="pnls bwd")
+    assert g.ctx().device_errors() == 0
+
+
+def test_pickneglogsoftmax_errors(g, capi):
+    x_ = g.dev(np.zeros((2, 5), np.float32))
+    loss_, aux = g.dev(np.zeros(2, np.float32)), g.dev(np.zeros(6, np.float32))
+    _, p = g.u32([0, 5])
+    with pytest.raises(capi.InvalidArgument):  # index out of bounds (nodes-pickneglogsoftmax.cc:91,100)
+        g.ctx().fwd("pickneglogsoftmax", [g.T(x_, [5], 2)], g.T(loss_, [1], 2), capi.PickAttrs(p, 2), aux.data_ptr())
+    _, p = g.u32([0])
+    with pytest.raises(capi.InvalidArgument):  # wrong number of ids
+        g.ctx().fwd("pickneglogsoftmax", [g.T(x_, [5], 2)], g.T(loss_, [1], 2), capi.PickAttrs(p, 1), aux.data_ptr())
+    _, p = g.u32([0, 1])
+    with pytest.raises(capi.RuntimeErr):  # multiple columns: "not yet implemented" in the reference
+        g.ctx().fwd("pickneglogsoftmax", [g.T(x_, [5, 2], 1)], g.T(loss_, [1], 1), capi.PickAttrs(p, 1), aux.data_ptr())
+
+
+# ------------------------------------------------------------------ norms
+@pytest.mark.parametrize("n", [9, 1000, 4096 * 3 + 1, 1024 * 4096])
+def test_weight_norm(oracle, g, n):
+    r = rng(130)
+    w = randn(r, n) + 0.1
+    gv = np.array([1.3], np.float32)
+    y_ref = oracle.weight_norm_fwd(w, float(gv[0]))
+    w_, g_, y_ = g.dev(w), g.dev(gv), g.dev(np.zeros_like(w))
+    xs = [g.T(w_, [n], 1), g.T(g_, [1], 1)]
+    g.ctx().fwd("weight_norm", xs, g.T(y_, [n], 1))
+    assert_close(g.host(y_), y_ref, TOL_REDUCE, floor=1e-7, what="weight_norm fwd")
+    dy = randn(r, n)
+    for i, shape in ((0, n), (1, 1)):
+        d0 = randn(r, shape)
+        want = oracle.weight_norm_bwd(w, float(gv[0]), y_ref, dy, i, d0.copy())
+        d_ = g.dev(d0)
+        g.ctx().bwd("weight_norm", xs, g.T(g.dev(y_ref), [n], 1), g.T(g.dev(dy), [n], 1), i, g.T(d_, [shape], 1))
+        assert_close(g.host(d_), want, TOL_REDUCE, floor=1e-2 if i == 1 else 1e-3, what="weight_norm bwd %d" % i)
+
+
+def test_weight_norm_golden(g):
+    c = GOLD["weight_norm_forward"]
+    w = np.asarray(c["w"], np.float32)
+    y_ = g.dev(np.zeros_like(w))
+    g.ctx().fwd("weight_norm", [g.T(g.dev(w), [3, 3], 1), g.T(g.dev(np.array([c["g"]], np.float32)), [1], 1)], g.T(y_, [3, 3], 1))
+    norm = float(np.sqrt((g.host(y_).astype(np.float64) ** 2).sum()))
+    assert abs(norm - c["expect_norm"]) <= c["tol_rel"] * c["expect_norm"]
+
+
+def test_moment_std_dim(oracle, g, capi):
+    r = rng(131)
+    # the layer_norm use: all non-batch dims reduced, batch kept
+    for n, bd in [(3, 1), (10, 4), (4096, 6), (5003, 2)]:
+        x = randn(r, bd, n) + 0.5
+        x_ = g.dev(x)
+        for order in (1, 2, 3):
+            at = capi.MomentAttrs((C.c_uint32 * 2)(0, 0), 1, order, 0, 0)
+            out = g.dev(np.zeros(bd, np.float32))
+            g.ctx().fwd("moment_dim", [g.T(x_)], g.T(out, [1], bd), at)
+            assert_close(g.host(out), oracle.moment_elems_fwd(x, order), TOL_REDUCE, what="moment %d" % order)
+            dE, d0 = randn(r, bd), randn(r, bd, n)
+            want = oracle.moment_elems_bwd(x, order, dE, d0.copy())
+            d_ = g.dev(d0)
+            g.ctx().bwd("moment_dim", [g.T(x_)], g.T(out, [1], bd), g.T(g.dev(dE), [1], bd), 0, g.T(d_), at)
+            assert_close(g.host(d_), want, TOL_REDUCE, what="moment bwd %d" % order)
+        at = capi.MomentAttrs((C.c_uint32 * 2)(0, 0), 1, 0, 0, 0)
+        out = g.dev(np.zeros(bd, np.float32))
+        g.ctx().fwd("std_dim", [g.T(x_)], g.T(out, [1], bd), at)
+        s_ref = oracle.std_elems_fwd(x)
+        assert_close(g.host(out), s_ref, TOL_REDUCE, what="std")
+        dE, d0 = randn(r, bd), randn(r, bd, n)
+        want = oracle.std_elems_bwd(x, s_ref, dE, d0.copy())
+        d_ = g.dev(d0)
+        g.ctx().bwd("std_dim", [g.T(x_)], g.T(g.dev(s_ref), [1], bd), g.T(g.dev(dE), [1], bd), 0, g.T(d_), at)
+        assert_close(g.host(d_), want, TOL_REDUCE, what="std bwd")
+
+
+def test_std_dim_value_golden(g, capi):
+    c = GOLD["std_dim_value"]
+    x = np.asarray(c["x"], np.float32).reshape(3, 3, 3)
+    y = g.dev(np.zeros(3, np.float32))
+    at = capi.MomentAttrs((C.c_uint32 * 2)(0, 0), 1, 0, 1, 0)   # std_dim(x, {0}, true)
+    g.ctx().fwd("std_dim", [g.T(g.dev(x))], g.T(y, [3], 1), at)
+    z = g.dev(np.zeros(1, np.float32))
+    at2 = capi.MomentAttrs((C.c_uint32 * 2)(0, 0), 1, 1, 0, 0)  # mean_dim(y, {0}, false)
+    g.ctx().fwd("moment_dim", [g.T(y, [3], 1)], g.T(z, [1], 1), at2)
+    want = c["expect_mean_of_std_dim0_batch"]
+    assert abs(float(g.host(z)[0]) - want) <= c["tol_rel"] * want
+
+
+@pytest.mark.parametrize("n,bd", [(3, 1), (10, 1), (130, 5), (4096, 16), (4100, 3), (9001, 2)])
+def test_layer_norm(oracle, g, n, bd):
+    r = rng(132)
+    x = randn(r, bd, n)
+    gain = r.uniform(0.5, 1.5, n).astype(np.float32)
+    bias = randn(r, n, scale=0.1)
+    y_ref = oracle.layer_norm_fwd(x, gain, bias)
+    x_, g_, b_ = g.dev(x), g.dev(gain), g.dev(bias)
+    xs = [g.T(x_), g.T(g_, [n], 1), g.T(b_, [n], 1)]
+    y_ = g.dev(np.zeros_like(x))
+    g.ctx().fwd("layer_norm", xs, g.T(y_))
+    assert_close(g.host(y_), y_ref, TOL_REDUCE, what="layer_norm fwd")
+    dy = randn(r, bd, n)
+    dx0, dg0, db0 = randn(r, bd, n), randn(r, n), randn(r, n)
+    wx, wg, wb = oracle.layer_norm_bwd(x, gain, dy, dx0.copy(), dg0.copy(), db0.copy())
+    dy_ = g.dev(dy)
+    for i, (d0, want, dims, b) in enumerate(((dx0, wx, None, None), (dg0, wg, [n], 1), (db0, wb, [n], 1))):
+        d_ = g.dev(d0)
+        g.ctx().bwd("layer_norm", xs, g.T(y_), g.T(dy_), i, g.T(d_) if dims is None else g.T(d_, dims, b))
+        assert_close(g.host(d_), want, TOL_REDUCE, floor=1e-2, what="layer_norm bwd %d" % i)
+
+
+def test_layer_norm_golden(g):
+    c = GOLD["layer_norm_forward"]
+    x = np.asarray(c["x"], np.float32).reshape(1, 3)
+    y_ = g.dev(np.zeros_like(x))
+    g.ctx().fwd("layer_norm", [g.T(g.dev(x)), g.T(g.dev(np.asarray(c["g"], np.float32)), [3], 1),
+                               g.T(g.dev(np.asarray(c["b"], np.float32)), [3], 1)], g.T(y_))
+    y = g.host(y_)
+    assert abs(float(y.sum() / 3.0)) < c["expect_abs_mean_lt"]
+    assert abs(float(np.sqrt((y.astype(np.float64) ** 2).sum() / 3.0)) - 1.0) <= c["tol_rel"]
+    v = np.arange(10).astype(np.float32)
+    y_ = g.dev(np.zeros((1, 10), np.float32))
+    g.ctx().fwd("layer_norm", [g.T(g.dev(v.reshape(1, 10))), g.T(g.dev(v), [10], 1), g.T(g.dev(v), [10], 1)], g.T(y_))
+    assert np.allclose(g.host(y_).ravel(), v / v.std() * (v - v.mean()) + v)
+
+
+def test_layer_norm_composite_nodes(oracle, g, capi):
+    """The 8-node composite of dynet/expr.cc:248-253 built from the drop-in nodes equals the fused kernel."""
+    r = rng(133)
+    n, bd = 64, 5
+    x = randn(r, bd, n)
+    gain, bias = r.uniform(0.5, 1.5, n).astype(np.float32), randn(r, n, scale=0.1)
+    c = g.ctx()
+    x_ = g.dev(x)
+    at1 = capi.MomentAttrs((C.c_uint32 * 2)(0, 0), 1, 1, 0, 0)
+    mu, sg = g.dev(np.zeros(bd, np.float32)), g.dev(np.zeros(bd, np.float32))
+    c.fwd("moment_dim", [g.T(x_)], g.T(mu, [1], bd), at1)
+    c.fwd("std_dim", [g.T(x_)], g.T(sg, [1], bd), at1)
+    neg = -mu
+    s2 = sg + np.float32(1e-8)
+    xc, q, y1, y = (g.dev(np.zeros_like(x)) for _ in range(4))
+    c.fwd("csum", [g.T(x_), g.T(neg, [1], bd)], g.T(xc))
+    c.fwd("cdiv", [g.T(xc), g.T(s2, [1], bd)], g.T(q))
+    c.fwd("cmult", [g.T(g.dev(gain), [n], 1), g.T(q)], g.T(y1))
+    c.fwd("csum", [g.T(y1), g.T(g.dev(bias), [n], 1)], g.T(y))
+    assert_close(g.host(y), oracle.layer_norm_fwd(x, gain, bias), TOL_REDUCE, what="composite layer_norm")
+
+
+# ------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("E,V,n", [(4, 9, 5), (128, 1000, 300), (512, 5000, 4096), (6, 50, 77), (1028, 64, 33), (2048, 32, 40)])
+@pytest.mark.parametrize("scale", [1.0, 0.75])
+def test_lookup_gather_bit_exact(oracle, g, capi, E, V, n, scale):
+    r = rng(140)
+    table = randn(r, V, E)
+    ids = zipf_ids(r, n, V)
+    ids[0] = V - 1
+    want = oracle.lookup_fwd(table, ids, scale)
+    tab_, out_ = g.dev(table), g.dev(np.zeros((n, E), np.float32))
+    aux = g.dev(np.zeros(n, np.float32))
+    _, p = g.u32(ids)
+    at = capi.LookupAttrs(tab_.data_ptr(), V, p, n, scale)
+    g.ctx().fwd("lookup", [], g.T(out_, [E], n), at, aux.data_ptr())
+    assert np.array_equal(g.host(out_), want)
+    assert g.ctx().device_errors() == 0
+
+
+def test_lookup_errors(g, capi):
+    tab_, out_, aux = g.dev(np.zeros((9, 4), np.float32)), g.dev(np.zeros((2, 4), np.float32)), g.dev(np.zeros(2, np.float32))
+    _, p = g.u32([1, 9])
+    with pytest.raises(capi.InvalidArgument):
+        g.ctx().fwd("lookup", [], g.T(out_, [4], 2), capi.LookupAttrs(tab_.data_ptr(), 9, p, 2, 1.0), aux.data_ptr())
+    with pytest.raises(capi.InvalidArgument):
+        g.ctx().fwd("lookup", [], g.T(out_, [4], 2), capi.LookupAttrs(tab_.data_ptr(), 9, p, 1, 1.0), aux.data_ptr())
+
+
+@pytest.mark.parametrize("E,V,n", [(4, 9, 1), (4, 9, 5), (128, 1000, 512), (512, 5000, 4096), (6, 50, 77), (64, 300, 9000)])
+def test_lookup_scatter_add(oracle, g, E, V, n):
+    r = rng(141)
+    ids = zipf_ids(r, n, V)
+    grad = randn(r, n, E)
+    acc0 = randn(r, V, E)
+    want = oracle.lookup_accumulate_grads(acc0.copy(), ids, grad)
+    acc_ = g.dev(acc0)
+    ids_dev = g.dev(ids.view(np.float32)).view(dtype=__import__("torch").int32)
+    g.ctx().lookup_accumulate_grads(ids, ids_dev.data_ptr(), g.dev(grad).data_ptr(), acc_.data_ptr(), E, V)
+    got = g.host(acc_)
+    # same summation order as the CPU loop (rows of one id added in ascending position)
+    assert np.array_equal(got, want)
+    # run to run reproducible
+    acc2 = g.dev(acc0)
+    g.ctx().lookup_accumulate_grads(ids, ids_dev.data_ptr(), g.dev(grad).data_ptr(), acc2.data_ptr(), E, V)
+    assert np.array_equal(g.host(acc2), got)
+    assert g.ctx().device_errors() == 0
+
+
+# ------------------------------------------------------------------ fused LSTM nodes
+def _gates_call(g, capi, xs, h, Wx, Wh, b, mx=None, mh=None, noise=0.0):
+    B, H = h.shape
+    d = [g.dev(x) for x in xs] + [g.dev(h), g.dev(Wx), g.dev(Wh), g.dev(b)]
+    ts = [g.T(t) for t in d[:len(xs) + 1]]
+    I = Wx.shape[0]
+    ts += [g.T(d[-3], [4 * H, I], 1), g.T(d[-2], [4 * H, H], 1), g.T(d[-1], [4 * H], 1)]
+    if mx is not None:
+        d += [g.dev(mx), g.dev(mh)]
+        ts += [g.T(d[-2]), g.T(d[-1])]
+    at = capi.LstmGatesAttrs(1 if mx is not None else 0, noise, 1.0)
+    return d, ts, at
+
+
+@pytest.mark.parametrize("name", ["lstm_node_gates_fwd", "lstm_node_gates_dropout_fwd"])
+def test_lstm_gates_golden(g, capi, name):
+    c = GOLD[name]
+    I, H, B = c["I"], c["H"], c["B"]
+    f = lambda k, *s: np.asarray(c[k], np.float32).reshape(*s)
+    mx = f("mask_x", B, I) if "mask_x" in c else None
+    mh = f("mask_h", B, H) if "mask_h" in c else None
+    d, ts, at = _gates_call(g, capi, [f("x_t", B, I)], f("h_tm1", B, H), f("Wx", I, 4 * H), f("Wh", H, 4 * H), f("b", 4 * H), mx, mh)
+    fx = g.dev(np.zeros((B, 4 * H), np.float32))
+    g.ctx().fwd("vanilla_lstm_gates", ts, g.T(fx), at)
+    got = g.host(fx).ravel()
+    for a, w in zip(got, c["expect"]):
+        assert abs(a - w) <= c["tol_rel"] * abs(w), (a, w)
+
+
+def test_lstm_c_h_golden(g):
+    for name, node, key in (("lstm_node_c_fwd", "vanilla_lstm_c", "c_tm1"), ("lstm_node_h_fwd", "vanilla_lstm_h", "c_t")):
+        c = GOLD[name]
+        H, B = c["H"], c["B"]
+        st = np.asarray(c[key], np.float32).reshape(B, H)
+        gt = np.asarray(c["gates_t"], np.float32).reshape(B, 4 * H)
+        out = g.dev(np.zeros((B, H), np.float32))
+        g.ctx().fwd(node, [g.T(g.dev(st)), g.T(g.dev(gt))], g.T(out))
+        for a, w in zip(g.host(out).ravel(), c["expect"]):
+            assert abs(a - w) <= (c["tol_abs_zero"] if w == 0 else c["tol_rel"] * abs(w)), (name, a, w)
+
+
+@pytest.mark.parametrize("I_list,H,B,masks", [([5], 3, 2, None), ([3, 2], 3, 2, "full"), ([128], 256, 32, None),
+                                              ([128], 256, 32, "bd1"), ([96, 32], 64, 17, "full"), ([512], 128, 64, "full"),
+                                              ([130], 66, 5, "bd1")])
+def test_lstm_gates_vs_oracle(oracle, g, capi, I_list, H, B, masks):
+    r = rng(150)
+    I = sum(I_list)
+    xs = [randn(r, B, i) for i in I_list]
+    h = randn(r, B, H, scale=0.5)
+    Wx, Wh = glorot(r, 4 * H, I), glorot(r, 4 * H, H)
+    b = randn(r, 4 * H, scale=0.1)
+    mx = mh = None
+    if masks:
+        mb = B if masks == "full" else 1
+        mx = ((r.random((mb, I)) < 0.8) / 0.8).astype(np.float32)
+        mh = ((r.random((mb, H)) < 0.8) / 0.8).astype(np.float32)
+    fx_ref = oracle.lstm_gates_fwd(xs, h, Wx, Wh, b, mx, mh)
+    d, ts, at = _gates_call(g, capi, xs, h, Wx, Wh, b, mx, mh)
+    fx = g.dev(np.zeros((B, 4 * H), np.float32))
+    g.ctx().fwd("vanilla_lstm_gates", ts, g.T(fx), at)
+    assert_close(g.host(fx), fx_ref, TOL_REDUCE, floor=1e-3, what="gates fwd")
+    dE = randn(r, B, 4 * H)
+    fx_r, dE_ = g.dev(fx_ref), g.dev(dE)
+    args = xs + [h, Wx, Wh, b]
+    for i, arg in enumerate(args):
+        d0 = randn(r, *arg.shape)
+        want = oracle.lstm_gates_bwd(xs, h, Wx, Wh, fx_ref, dE, i, d0.copy(), mx, mh)
+        d_ = g.dev(d0)
+        g.ctx().bwd("vanilla_lstm_gates", ts, g.T(fx_r), g.T(dE_), i, capi.DyTensor.of(d_.data_ptr(), ts[i].d[:ts[i].nd], ts[i].bd), at)
+        assert_close(g.host(d_), want, TOL_REDUCE, floor=1e-2, what="gates bwd i=%d" % i)
+
+
+def test_lstm_gates_weightnoise_and_errors(oracle, g, capi):
+    r = rng(151)
+    I, H, B = 6, 4, 3
+    xs, h = [randn(r, B, I)], randn(r, B, H)
+    Wx, Wh, b = glorot(r, 4 * H, I), glorot(r, 4 * H, H), randn(r, 4 * H)
+    d, ts, at = _gates_call(g, capi, xs, h, Wx, Wh, b, noise=0.1)
+    fx = g.dev(np.zeros((B, 4 * H), np.float32))
+    g.ctx().fwd("vanilla_lstm_gates", ts, g.T(fx), at)   # reference skips both products (nodes-lstm.cc:200-219)
+    assert_close(g.host(fx), oracle.lstm_gates_fwd(xs, h, Wx, Wh, b, skip_matmul=True), TOL_CWISE, what="weightnoise")
+    d, ts, at = _gates_call(g, capi, xs, h, Wx, Wh, b)
+    ts[2] = g.T(d[2], [4 * H + 1, I], 1)
+    with pytest.raises(capi.InvalidArgument):
+        g.ctx().fwd("vanilla_lstm_gates", ts, g.T(fx), at)
+
+
+@pytest.mark.parametrize("H,B", [(3, 2), (256, 32), (1024, 9), (130, 7)])
+def test_lstm_c_h_vs_oracle(oracle, g, H, B):
+    r = rng(152)
+    c_prev, gates = randn(r, B, H), r.uniform(0.05, 0.95, (B, 4 * H)).astype(np.float32)
+    for node, fwd, bwd in (("vanilla_lstm_c", oracle.lstm_c_fwd, oracle.lstm_c_bwd), ("vanilla_lstm_h", oracle.lstm_h_fwd, oracle.lstm_h_bwd)):
+        want = fwd(c_prev, gates)
+        xs_d = [g.dev(c_prev), g.dev(gates)]
+        xs = [g.T(t) for t in xs_d]
+        out = g.dev(np.zeros_like(c_prev))
+        g.ctx().fwd(node, xs, g.T(out))
+        assert_close(g.host(out), want, TOL_CWISE, what=node)
+        dE = randn(r, B, H)
+        for i, arg in enumerate((c_prev, gates)):
+            d0 = randn(r, *arg.shape)
+            w = bwd(c_prev, gates, dE, i, d0.copy())
+            d_ = g.dev(d0)
+            g.ctx().bwd(node, xs, g.T(out), g.T(g.dev(dE)), i, g.T(d_))
+            assert_close(g.host(d_), w, TOL_CWISE, what="%s bwd %d" % (node, i))
+
+
+def test_lstm_chain_fused_equals_builder_math(oracle, g, capi):
+    """Config-1 shape (I=128, H=256, B=32), 5 steps: h_t / c_t through the fused chain on the GPU vs the oracle."""
+    r = rng(153)
+    I, H, B, T = 128, 256, 32, 5
+    Wx, Wh, b = glorot(r, 4 * H, I), glorot(r, 4 * H, H), np.zeros(4 * H, np.float32)
+    h = c = np.zeros((B, H), np.float32)
+    hd, cd = g.dev(h), g.dev(c)
+    for t in range(T):
+        x = randn(r, B, I)
+        gr = oracle.lstm_gates_fwd([x], h, Wx, Wh, b)
+        c = oracle.lstm_c_fwd(c, gr)
+        h = oracle.lstm_h_fwd(c, gr)
+        d, ts, at = _gates_call(g, capi, [x], np.zeros_like(h), Wx, Wh, b)
+        ts[1] = g.T(hd)
+        gt = g.dev(np.zeros((B, 4 * H), np.float32))
+        g.ctx().fwd("vanilla_lstm_gates", ts, g.T(gt), at)
+        c2 = g.dev(np.zeros_like(c))
+        g.ctx().fwd("vanilla_lstm_c", [g.T(cd), g.T(gt)], g.T(c2))
+        h2 = g.dev(np.zeros_like(h))
+        g.ctx().fwd("vanilla_lstm_h", [g.T(c2), g.T(gt)], g.T(h2))
+        hd, cd = h2, c2
+        assert_close(g.host(hd), h, TOL_REDUCE, floor=1e-2, what="h_%d" % t)
+        assert_close(g.host(cd), c, TOL_REDUCE, floor=1e-2, what="c_%d" % t)
+
+
+# ------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("tA,tB,M,N,K", [(0, 0, 64, 32, 48), (1, 0, 70, 33, 129), (0, 1, 128, 65, 31), (0, 0, 1024, 32, 384),
+                                         (1, 0, 384, 32, 1024), (0, 1, 1024, 384, 32), (0, 0, 256, 256, 512)])
+def test_gemm(g, tA, tB, M, N, K):
+    r = rng(160)
+    A = randn(r, *((M, K) if tA else (K, M)))   # C-order (cols, rows) == column-major rows x cols
+    Bm = randn(r, *((K, N) if tB else (N, K)))
+    C0 = randn(r, N, M)
+    opA = A.T.astype(np.float64) if not tA else A.astype(np.float64)       # M x K
+    opB = Bm.T.astype(np.float64) if not tB else Bm.astype(np.float64)     # K x N
+    ref = opA @ opB
+    for acc in (0, 1):
+        C_ = g.dev(C0)
+        g.ctx().gemm(tA, tB, M, N, K, g.dev(A).data_ptr(), A.shape[1], g.dev(Bm).data_ptr(), Bm.shape[1], C_.data_ptr(), M, acc)
+        want = ref.T + (C0 if acc else 0)
+        assert_close(g.host(C_), want, TOL_REDUCE, floor=0.5, what="gemm %d%d acc=%d" % (tA, tB, acc))
+
+
+# ------------------------------------------------------------------ ragged movers
+def _tables(g, srcs, trgs, lens):
+    import torch
+    n = len(lens)
+    sp = torch.tensor([t.data_ptr() for t in srcs], dtype=torch.int64, device="cuda")
+    tp = torch.tensor([t.data_ptr() for t in trgs], dtype=torch.int64, device="cuda")
+    ln = torch.tensor(lens, dtype=torch.int64, device="cuda")
+    return n, sp, tp, ln
+
+
+@pytest.mark.parametrize("n_seq", [1, 7, 300, 5000])
+def test_parallel_memcpy(g, n_seq):
+    import torch
+    r = rng(170)
+    lens = [int(v) for v in r.integers(1, 1100, n_seq)]
+    src_all = g.dev(randn(r, sum(lens) + n_seq))
+    dst_all = torch.zeros(sum(lens), device="cuda")
+    srcs, trgs, off_s, off_d = [], [], 0, 0
+    for k, L in enumerate(lens):
+        srcs.append(src_all[off_s + 1:off_s + 1 + L])   # deliberately ragged alignment
+        trgs.append(dst_all[off_d:off_d + L])
+        off_s += L + 1
+        off_d += L
+    n, sp, tp, ln = _tables(g, srcs, trgs, lens)
+    g.ctx().parallel_memcpy(n, max(lens), sp.data_ptr(), tp.data_ptr(), ln.data_ptr())
+    want = torch.cat(srcs)
+    assert torch.equal(dst_all, want)
+
+
+@pytest.mark.parametrize("n_seq", [1, 9, 400, 4500])
+def test_parallel_accumulate_with_shared_targets(g, n_seq):
+    import torch
+    r = rng(171)
+    n_trg = max(1, n_seq // 3)
+    L = [int(v) for v in r.integers(1, 600, n_trg)]
+    L = [l - l % 4 if (k % 2 == 0 and l >= 4) else l for k, l in enumerate(L)]
+    trg_bufs = [g.dev(randn(r, l)) for l in L]
+    which = [int(v) for v in r.integers(0, n_trg, n_seq)]
+    srcs = [g.dev(randn(r, L[w])) for w in which]
+    want = [t.clone() for t in trg_bufs]
+    for s, w in zip(srcs, which):      # ascending slice order, like the CPU loop (exec.cc:369-378)
+        want[w] += s
+    n, sp, tp, ln = _tables(g, srcs, [trg_bufs[w] for w in which], [L[w] for w in which])
+    g.ctx().parallel_accumulate(n, max(L), sp.data_ptr(), tp.data_ptr(), ln.data_ptr())
+    for a, b in zip(trg_bufs, want):   # later sort passes continue from the target's running value
+        assert torch.equal(a, b)
