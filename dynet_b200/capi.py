@@ -84,7 +84,8 @@ NODES = ["tanh", "logistic", "rectify", "elu", "cmult", "csum", "cdiv", "softmax
 FWD_ONLY = ["lookup"]
 OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200_ctx_check_device_errors",
          "dyb200_ctx_launch_count", "dyb200_version", "dyb200_lookup_accumulate_grads",
-         "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm"]
+         "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm", "dyb200_fill", "dyb200_sum_all",
+         "dyb200_squared_norm", "dyb200_sgd_update"]
 
 
 def exported_symbols():

@@ -243,11 +243,13 @@ int dyb200_lookup_fwd(DYB200_FWD_ARGS) {
   const dyb200_lookup_attrs* a = (const dyb200_lookup_attrs*)attrs;
   const uint32_t n = a->n, E = (uint32_t)t_batch_size(fx);
   DYB_CHECK_ARG(ctx, fx->bd == n, "In LookupNode, in index vector size (%u) doesn't match batch size in expressions (%u)", n, fx->bd);
-  for (uint32_t b = 0; b < n; ++b)
-    DYB_CHECK_ARG(ctx, a->ids_host[b] < a->vocab, "Out-of-bounds attempt to access index %u for LookupParameter of size %u", a->ids_host[b], a->vocab);
   if (n == 0 || E == 0) return DYB200_OK;
   uint32_t* ids_dev = (uint32_t*)aux_mem;
-  DYB_CUDA(ctx, cudaMemcpyAsync(ids_dev, a->ids_host, n * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+  if (a->ids_host) {
+    for (uint32_t b = 0; b < n; ++b)
+      DYB_CHECK_ARG(ctx, a->ids_host[b] < a->vocab, "Out-of-bounds attempt to access index %u for LookupParameter of size %u", a->ids_host[b], a->vocab);
+    DYB_CUDA(ctx, cudaMemcpyAsync(ids_dev, a->ids_host, n * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+  }  // else: aux_mem already holds the ids on the device; the kernel clamps and flags a bad id
   const bool al = aligned16(a->all_values) && aligned16(fx->v) && E % 4 == 0;
   if (al && E * 4u <= (uint32_t)kGatherRowBytesMax) {
     size_t smem = (size_t)kGatherWarps * 2 * E * 4;

@@ -558,13 +558,15 @@ int dyb200_pickneglogsoftmax_fwd(DYB200_FWD_ARGS) {
   const dyb200_pick_attrs* p = (const dyb200_pick_attrs*)attrs;
   uint32_t rows = t_rows(&xs[0]), bd = xs[0].bd;
   DYB_CHECK_ARG(ctx, p->n == bd && fx->bd == bd, "In PickNegLogSoftmax::forward, number of elements in the passed-in index vector (%u) did not match number of elements in mini-batch elements in expression (%u)", p->n, bd);
-  for (uint32_t b = 0; b < bd; ++b)
-    DYB_CHECK_ARG(ctx, p->ids_host[b] < rows, "Index error in PickNegLogSoftmax: Index %u out of bounds for input tensor of %u rows", p->ids_host[b], rows);
   float* z = (float*)aux_mem;
   float* m = z + bd;
   uint32_t* ids_dev = (uint32_t*)(m + bd);
   // the reference stores flat indices (b * rows + id); the column kernels index per column
-  DYB_CUDA(ctx, cudaMemcpyAsync(ids_dev, p->ids_host, bd * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+  if (p->ids_host) {
+    for (uint32_t b = 0; b < bd; ++b)
+      DYB_CHECK_ARG(ctx, p->ids_host[b] < rows, "Index error in PickNegLogSoftmax: Index %u out of bounds for input tensor of %u rows", p->ids_host[b], rows);
+    DYB_CUDA(ctx, cudaMemcpyAsync(ids_dev, p->ids_host, bd * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+  }  // else: the ids are already in aux_mem on the device; the kernel clamps and flags a bad id
   ColArgs a{xs[0].v, nullptr, z, m, ids_dev, fx->v, rows, bd, nullptr};
   return run_columns<M_PNLS>(ctx, a);
 }

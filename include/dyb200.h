@@ -73,11 +73,14 @@ const char* dyb200_version(void);
 /* ---- attrs structs (the nodes' constructor arguments) ---- */
 typedef struct { float alpha, lambda; } dyb200_elu_attrs;               /* dynet/nodes-activations.h:46-53 */
 typedef struct { uint32_t dimension; } dyb200_dim_attrs;               /* dynet/nodes-softmaxes.h:26, nodes-logsumexp.h */
-typedef struct { const uint32_t* ids_host; uint32_t n; } dyb200_pick_attrs; /* pval / pvals, dynet/nodes-pickneglogsoftmax.h:11-36 */
+/* pval / pvals, dynet/nodes-pickneglogsoftmax.h:11-36.  ids_host == NULL means the caller has
+ * already placed the n ids in the node's aux_mem on the device (no host check, no H2D copy);
+ * a bad id is then clamped by the kernel and reported by dyb200_ctx_check_device_errors. */
+typedef struct { const uint32_t* ids_host; uint32_t n; } dyb200_pick_attrs;
 typedef struct {                                                        /* dynet/param-nodes.h:84-110 */
   const float* all_values; /* device, Dim({E}, V) == LookupParameterStorage::all_values */
   uint32_t vocab;          /* V */
-  const uint32_t* ids_host;
+  const uint32_t* ids_host; /* NULL: ids already in aux_mem on the device (see dyb200_pick_attrs) */
   uint32_t n;
   float weight_decay_scale; /* params.current_weight_decay() */
 } dyb200_lookup_attrs;
@@ -171,6 +174,18 @@ int dyb200_parallel_memcpy(int num_seqs, int max_len, float** src, float** trg, 
 /* trg[s][0..len[s]) += src[s][...]; sequences that share a target are added in
  * ascending s (deterministic; the reference uses atomicAdd, dynet/gpu-ops.cu:121-145). */
 int dyb200_parallel_accumulate(int num_seqs, int max_len, float** src, float** trg, size_t* len, dyb200_ctx* ctx);
+
+/* ---- glue around the hot path (not fused-layer nodes; they let a whole training step stay on the device) ---- */
+int dyb200_fill(float* p, size_t n, float value, dyb200_ctx* ctx);            /* TensorTools::constant, dynet/tensor.cc:110-120 */
+/* out[0] (+)= sum(x): the value of sum_batches(sum(errs)) over a contiguous block, dynet/nodes-arith-sum.cc (Sum, SumDimension) */
+int dyb200_sum_all(const float* x, size_t n, float* out, int accumulate, dyb200_ctx* ctx);
+/* out[0] (+)= sum(x^2): ParameterStorage::g_squared_l2norm, dynet/model.cc:547-553 */
+int dyb200_squared_norm(const float* x, size_t n, float* out, int accumulate, dyb200_ctx* ctx);
+/* SimpleSGDTrainer::update_rule with Trainer::clip_gradients folded in (dynet/training.cc:168-183, :619-622):
+ * scale = clip / sqrt(*grad_sumsq) if that norm exceeds clip (clip <= 0 disables); params -= grads * lr * scale; grads = 0
+ * (ParameterStorage::clear, dynet/model.cc:111-117).  grad_sumsq is a device scalar. */
+int dyb200_sgd_update(float* params, float* grads, size_t n, float lr, float clip_threshold, const float* grad_sumsq,
+                      dyb200_ctx* ctx);
 
 /* ---- GEMM used by the LSTM gates (dynet/matrix-multiply.h:16-37, :97-117, :162-180) ----
  * C[M x N] (+)= op(A) * op(B), column-major, fp32 in/out, 3xTF32 on the tensor pipe

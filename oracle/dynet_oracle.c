@@ -14,6 +14,10 @@
  * and a straight k-ordered GEMM instead; both agree with Eigen's packet math to
  * a few ulp, far inside the 1e-5 / 1e-4 parity classes.  The logistic sigmoid is
  * the reference's own rational packet formula (dynet/simd-functors.h:81-125).
+ * Long reductions (softmax / logsumexp / moment / norm sums) accumulate in double
+ * and round once: Eigen reduces packet- and tree-wise, never as one sequential
+ * float32 chain, and a sequential float32 sum (error growing with n, ~1e-3 at
+ * n = 4M) would be a worse stand-in for it than the correctly rounded sum.
  *
  * Parity pin: checked against the golden values in the reference's own tests
  * (tests/test-rnn.cc:245-400, tests/test-nodes.cc:2383-2435,
@@ -183,8 +187,9 @@ ORC_API void orc_softmax_fwd(const float* x, float* y, uint32_t rows, uint32_t c
       float* yc = y + c * rows;
       float m = xc[0];
       for (uint32_t r = 1; r < rows; ++r) m = xc[r] > m ? xc[r] : m;
-      float z = 0.f;
-      for (uint32_t r = 0; r < rows; ++r) { yc[r] = expf(xc[r] - m); z += yc[r]; }
+      double zd = 0.0;
+      for (uint32_t r = 0; r < rows; ++r) { yc[r] = expf(xc[r] - m); zd += yc[r]; }
+      float z = (float)zd;
       for (uint32_t r = 0; r < rows; ++r) yc[r] = yc[r] / z;
     }
   } else { /* :73-85, reduce over dim 1 */
@@ -194,11 +199,12 @@ ORC_API void orc_softmax_fwd(const float* x, float* y, uint32_t rows, uint32_t c
         float* yb = y + (size_t)b * rows * cols + r;
         float m = xb[0];
         for (uint32_t c = 1; c < cols; ++c) { float v = xb[(size_t)c * rows]; m = v > m ? v : m; }
-        float z = 0.f;
+        double zd = 0.0;
         for (uint32_t c = 0; c < cols; ++c) {
           float e = expf(xb[(size_t)c * rows] - m);
-          yb[(size_t)c * rows] = e; z += e;
+          yb[(size_t)c * rows] = e; zd += e;
         }
+        float z = (float)zd;
         for (uint32_t c = 0; c < cols; ++c) yb[(size_t)c * rows] /= z;
       }
   }
@@ -211,16 +217,18 @@ ORC_API void orc_softmax_bwd(const float* y, const float* dy, float* dx, uint32_
     for (size_t c = 0; c < ncols; ++c) {
       const float *yc = y + c * rows, *dc = dy + c * rows;
       float* xc = dx + c * rows;
-      float z = 0.f;
-      for (uint32_t r = 0; r < rows; ++r) z += yc[r] * dc[r];
+      double zd = 0.0;
+      for (uint32_t r = 0; r < rows; ++r) zd += yc[r] * dc[r];
+      float z = (float)zd;
       for (uint32_t r = 0; r < rows; ++r) xc[r] += (dc[r] - z) * yc[r];
     }
   } else {
     for (uint32_t b = 0; b < bd; ++b)
       for (uint32_t r = 0; r < rows; ++r) {
         size_t base = (size_t)b * rows * cols + r;
-        float z = 0.f;
-        for (uint32_t c = 0; c < cols; ++c) z += y[base + (size_t)c * rows] * dy[base + (size_t)c * rows];
+        double zd = 0.0;
+        for (uint32_t c = 0; c < cols; ++c) zd += y[base + (size_t)c * rows] * dy[base + (size_t)c * rows];
+        float z = (float)zd;
         for (uint32_t c = 0; c < cols; ++c) {
           size_t k = base + (size_t)c * rows;
           dx[k] += (dy[k] - z) * y[k];
@@ -243,10 +251,10 @@ ORC_API void orc_logsumexp_axis(const float* x, uint32_t rows, uint32_t cols, ui
       size_t stride = axis == 0 ? 1 : rows;
       float mv = base[0];
       for (uint32_t k = 1; k < inner; ++k) { float v = base[k * stride]; mv = v > mv ? v : mv; }
-      float s = 0.f;
+      double s = 0.0;
       for (uint32_t k = 0; k < inner; ++k) s += expf(base[k * stride] - mv);
       m[(size_t)b * outer + o] = mv;
-      z[(size_t)b * outer + o] = logf(s) + mv;
+      z[(size_t)b * outer + o] = logf((float)s) + mv;
     }
 }
 /* dynet/nodes-logsumexp.cc:136-146: dx += exp(x - z) * dz, broadcast along `axis` */
@@ -274,8 +282,9 @@ ORC_API void orc_log_softmax_bwd(const float* y, const float* dy, float* dx, uin
                                  uint32_t cols, uint32_t bd) {
   size_t ncols = (size_t)cols * bd;
   for (size_t c = 0; c < ncols; ++c) {
-    float z = 0.f;
-    for (uint32_t r = 0; r < rows; ++r) z += dy[c * rows + r];
+    double zd = 0.0;
+    for (uint32_t r = 0; r < rows; ++r) zd += dy[c * rows + r];
+    float z = (float)zd;
     for (uint32_t r = 0; r < rows; ++r) {
       size_t k = c * rows + r;
       dx[k] += (expf(y[k]) * -z) + dy[k];
@@ -351,16 +360,17 @@ ORC_API void orc_pnls_bwd(const float* x, uint32_t rows, uint32_t bd, const uint
 /* ------------------------------------------------------------------ */
 /* dynet/nodes-normalization.cc:28-41 */
 ORC_API void orc_weight_norm_fwd(const float* w, float g, float* y, size_t n) {
-  float ss = 0.f;
-  for (size_t i = 0; i < n; ++i) ss += w[i] * w[i];
-  float nrm = sqrtf(ss);
+  double ssd = 0.0;
+  for (size_t i = 0; i < n; ++i) ssd += w[i] * w[i];
+  float nrm = sqrtf((float)ssd);
   for (size_t i = 0; i < n; ++i) y[i] = (w[i] / nrm) * g;
 }
 /* dynet/nodes-normalization.cc:43-66 */
 ORC_API void orc_weight_norm_bwd(const float* w, float g, const float* y, const float* dy,
                                  unsigned i, float* dxi, size_t n) {
-  float ss = 0.f, dot = 0.f;
-  for (size_t k = 0; k < n; ++k) { ss += w[k] * w[k]; dot += dy[k] * w[k]; }
+  double ssd = 0.0, dotd = 0.0;
+  for (size_t k = 0; k < n; ++k) { ssd += w[k] * w[k]; dotd += dy[k] * w[k]; }
+  float ss = (float)ssd, dot = (float)dotd;
   if (i == 0) {
     float nrm = sqrtf(ss), t2 = dot / ss;
     for (size_t k = 0; k < n; ++k) dxi[k] += (dy[k] / nrm) * g - y[k] * t2;
@@ -379,12 +389,12 @@ ORC_API void orc_weight_norm_bwd(const float* w, float g, const float* y, const 
 /* dynet/nodes-moments.cc:181-209 (order r, dims = all, no batch) */
 ORC_API void orc_moment_elems_fwd(const float* x, size_t n, uint32_t bd, unsigned order, float* out) {
   for (uint32_t b = 0; b < bd; ++b) {
-    float s = 0.f;
+    double s = 0.0;
     for (size_t i = 0; i < n; ++i) {
       float v = x[b * n + i];
       s += order == 1 ? v : (order == 2 ? v * v : powf(v, (float)order));
     }
-    out[b] = s / (float)n;
+    out[b] = (float)s / (float)n;
   }
 }
 /* dynet/nodes-moments.cc:246-266 */
@@ -404,11 +414,11 @@ ORC_API void orc_moment_elems_bwd(const float* x, size_t n, uint32_t bd, unsigne
 ORC_API void orc_std_elems_fwd(const float* x, size_t n, uint32_t bd, float* out) {
   float fn = (float)n;
   for (uint32_t b = 0; b < bd; ++b) {
-    float s = 0.f;
+    double s = 0.0, q = 0.0;
     for (size_t i = 0; i < n; ++i) s += x[b * n + i];
-    float mean = s / fn, q = 0.f;
+    float mean = (float)s / fn;
     for (size_t i = 0; i < n; ++i) { float d = x[b * n + i] - mean; q += d * d; }
-    out[b] = sqrtf(q / fn);
+    out[b] = sqrtf((float)q / fn);
   }
 }
 /* dynet/nodes-moments.cc:498-530 with FSqrtBackward (dynet/simd-functors.h:212-226) */
@@ -416,9 +426,9 @@ ORC_API void orc_std_elems_bwd(const float* x, size_t n, uint32_t bd, const floa
                                const float* dE, float* dx) {
   float fn = (float)n;
   for (uint32_t b = 0; b < bd; ++b) {
-    float s = 0.f;
+    double s = 0.0;
     for (size_t i = 0; i < n; ++i) s += x[b * n + i];
-    float mean = s / fn;
+    float mean = (float)s / fn;
     float sb = dE[b] / (2.f * fx[b]);
     for (size_t i = 0; i < n; ++i) dx[b * n + i] += (2.f / fn) * (x[b * n + i] - mean) * sb;
   }
@@ -429,13 +439,13 @@ ORC_API void orc_std_dim0_batch_fwd(const float* x, uint32_t d0, uint32_t d1, ui
   /* reduce over dim 0 and the batch: out has d1 entries (nodes-moments.cc:464-471) */
   float fn = (float)d0 * (float)bd;
   for (uint32_t j = 0; j < d1; ++j) {
-    float s = 0.f;
+    double s = 0.0, q = 0.0;
     for (uint32_t b = 0; b < bd; ++b)
       for (uint32_t i = 0; i < d0; ++i) s += x[((size_t)b * d1 + j) * d0 + i];
-    float mean = s / fn, q = 0.f;
+    float mean = (float)s / fn;
     for (uint32_t b = 0; b < bd; ++b)
       for (uint32_t i = 0; i < d0; ++i) { float d = x[((size_t)b * d1 + j) * d0 + i] - mean; q += d * d; }
-    out[j] = sqrtf(q / fn);
+    out[j] = sqrtf((float)q / fn);
   }
 }
 
@@ -472,24 +482,25 @@ ORC_API void orc_layer_norm_bwd(const float* x, const float* g, const float* dy,
     for (size_t i = 0; i < n; ++i) db[i] += dy[b * n + i];
   /* CwiseMultiply(g, q): dg += sum_b dy*q (:270-272) */
   for (size_t i = 0; i < n; ++i) {
-    float s = 0.f;
+    double s = 0.0;
     for (uint32_t b = 0; b < bd; ++b) {
       float s2 = sg[b] + 1e-8f;
       float q = (x[b * n + i] + (-mu[b])) / s2;
       s += dy[b * n + i] * q;
     }
-    dg[i] += s;
+    dg[i] += (float)s;
   }
   for (uint32_t b = 0; b < bd; ++b) {
     float neg = -mu[b], s2 = sg[b] + 1e-8f;
     /* dq = dy * g;  cdiv i=1: ds2 -= sum(dq / s2^2 * xc) (:392-411) */
-    float ssq = s2 * s2, acc = 0.f, dneg = 0.f;
+    float ssq = s2 * s2;
+    double acc = 0.0, dneg = 0.0;
     for (size_t i = 0; i < n; ++i) {
       float dq = dy[b * n + i] * g[i];
       float xc = x[b * n + i] + neg;
       acc += dq / ssq * xc;
     }
-    float dsigma = -acc; /* ConstantPlusX passes the gradient through */
+    float dsigma = -(float)acc; /* ConstantPlusX passes the gradient through */
     /* StdDimension backward: dx += (2/n)(x - mean) * dsigma/(2 sigma) */
     float sb = dsigma / (2.f * sg[b]);
     for (size_t i = 0; i < n; ++i) dx[b * n + i] += (2.f / fn) * (x[b * n + i] - mu[b]) * sb;
@@ -500,7 +511,7 @@ ORC_API void orc_layer_norm_bwd(const float* x, const float* g, const float* dy,
       dneg += dxc;
     }
     /* Negate then MomentDimension backward: dx += dmu / n */
-    float dmu = -dneg;
+    float dmu = -(float)dneg;
     for (size_t i = 0; i < n; ++i) dx[b * n + i] += dmu / fn;
   }
   free(mu); free(sg);

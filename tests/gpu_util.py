@@ -7,6 +7,13 @@ import numpy as np
 from dynet_b200 import capi
 
 _CTX = None
+_KEEP = []   # device buffers stay alive until the test ends: kernels run asynchronously on raw pointers
+
+
+def release():
+    import torch
+    torch.cuda.synchronize()
+    _KEEP.clear()
 
 
 def ctx():
@@ -24,8 +31,11 @@ def dev(a, misalign=0):
         buf = torch.empty(a.size + misalign, dtype=torch.from_numpy(a).dtype, device="cuda")
         t = buf[misalign:misalign + a.size].view(a.shape)
         t.copy_(torch.from_numpy(a))
+        _KEEP.append(buf)
         return t
-    return torch.from_numpy(a).cuda()
+    t = torch.from_numpy(a).cuda()
+    _KEEP.append(t)
+    return t
 
 
 def zeros_like_dev(a):
