@@ -48,7 +48,26 @@ def build(force=False, verbose=False):
         list(ex.map(compile_one, jobs))
     if jobs or not os.path.exists(LIB):
         subprocess.check_call([NVCC, "-shared", "-o", LIB] + objs + ["-lcudart"])
+    build_host(force or bool(jobs))
     return LIB
+
+
+HOST = os.path.join(HERE, "host")
+HOST_LIB = os.path.join(HERE, "libdyb200_host.so")
+
+
+def build_host(force=False):
+    """C++ host layer above the C ABI: the node classes mirroring the reference interface and
+    the LSTM language-model step driver (g++, links libdyb200.so and cudart)."""
+    srcs = sorted(glob.glob(os.path.join(HOST, "*.cc")))
+    deps = srcs + glob.glob(os.path.join(HOST, "*.h")) + glob.glob(os.path.join(HERE, "..", "include", "*.h"))
+    if not force and os.path.exists(HOST_LIB) and os.path.getmtime(HOST_LIB) >= max(os.path.getmtime(d) for d in deps):
+        return HOST_LIB
+    cuda_home = os.path.dirname(os.path.dirname(NVCC))
+    subprocess.check_call(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-o", HOST_LIB] + srcs +
+                          ["-I" + os.path.join(cuda_home, "include"), "-L" + HERE, "-ldyb200",
+                           "-L" + os.path.join(cuda_home, "lib64"), "-lcudart", "-Wl,-rpath,$ORIGIN"])
+    return HOST_LIB
 
 
 if __name__ == "__main__":

@@ -1,0 +1,316 @@
+// One training step of the batched LSTM language model, driven node by node.
+//
+// Graph (examples/batching/rnnlm-batch.h:110-151 over CompactVanillaLSTMBuilder,
+// dynet/lstm.cc:1044-1080): per time step  x = lookup(C, tok[t]); per layer gates -> c -> h
+// (vanilla_lstm_gates[_dropout], vanilla_lstm_c, vanilla_lstm_h); r = bias + R * h;
+// err_t = pickneglogsoftmax(r, tok[t+1]); loss = sum_batches(sum_t err_t).
+// Forward calls each node's forward_dev_impl in topological order; backward walks the nodes in
+// reverse and calls backward_dev_impl once per differentiable argument, accumulating (+=) into
+// gradient memory that was zeroed once (dynet/exec.cc:166-284); the lookup gradients are
+// scattered after the reverse pass in time order (exec.cc:277-282).
+// Parameters are read in place (weight decay is 1), and the gradient of `bias + R*h` w.r.t. the
+// product aliases the gradient of the sum instead of being copied.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "dynet_shim.h"
+
+using namespace dynet_b200;
+
+extern "C" {
+typedef struct {
+  uint32_t V, E, H, L, T, B;
+  float lr, clip;
+  int32_t dropout;  // 0: vanilla_lstm_gates, 1: vanilla_lstm_gates_dropout (masks are inputs)
+} dyb200h_lm_config;
+}
+
+namespace {
+
+struct Arena {
+  char* base; size_t size, off;
+  template <class Tp> Tp* take(size_t n) {
+    off = (off + 255) & ~(size_t)255;
+    Tp* p = (Tp*)(base + off);
+    off += n * sizeof(Tp);
+    return p;
+  }
+};
+
+size_t param_sizes(const dyb200h_lm_config& c, std::vector<size_t>* sizes) {
+  size_t total = 0;
+  auto add = [&](size_t n) { if (sizes) sizes->push_back(n); total += n; };
+  add((size_t)c.E * c.V);
+  for (uint32_t l = 0; l < c.L; ++l) {
+    add((size_t)4 * c.H * (l == 0 ? c.E : c.H));
+    add((size_t)4 * c.H * c.H);
+    add((size_t)4 * c.H);
+  }
+  add((size_t)c.V * c.H);
+  add(c.V);
+  return total;
+}
+
+struct Lm {
+  dyb200h_lm_config c;
+  Device_GPU dev;
+  std::string err;
+  float *params, *grads;
+  std::vector<float*> p, g;       // per-tensor views into the flat buffers
+  // activations
+  uint32_t* tok;                  // (T+1) x B ids on the device
+  float *x, *gates, *cs, *hs, *r, *aux, *errs, *zeros, *ones;
+  // gradients of activations
+  float *dact, *dx, *dh, *dc, *dgates, *dr;
+  size_t dact_bytes;
+  float* scalars;                 // [0] = squared gradient norm
+  cudaStream_t stream;
+};
+
+size_t plan(const dyb200h_lm_config& c, Lm* m, char* base, size_t size) {
+  Arena a{base, size, 0};
+  const size_t HB = (size_t)c.H * c.B, GB = 4 * HB, VB = (size_t)c.V * c.B, EB = (size_t)c.E * c.B, TL = (size_t)c.T * c.L;
+  uint32_t* tok = a.take<uint32_t>((size_t)(c.T + 1) * c.B);
+  float* x = a.take<float>(c.T * EB);
+  float* gates = a.take<float>(TL * GB);
+  float* cs = a.take<float>(TL * HB);
+  float* hs = a.take<float>(TL * HB);
+  float* r = a.take<float>(c.T * VB);
+  float* aux = a.take<float>((size_t)c.T * 3 * c.B);
+  float* errs = a.take<float>((size_t)c.T * c.B);
+  float* zeros = a.take<float>(HB);
+  float* ones = a.take<float>(c.B);
+  float* scalars = a.take<float>(64);
+  float* dr = a.take<float>(VB);
+  // everything below is zeroed by one memset per backward
+  a.off = (a.off + 255) & ~(size_t)255;
+  size_t d0 = a.off;
+  float* dx = a.take<float>(c.T * EB);
+  float* dh = a.take<float>(TL * HB);
+  float* dc = a.take<float>(TL * HB);
+  float* dgates = a.take<float>(TL * GB);
+  size_t d1 = a.off;
+  if (m) {
+    m->tok = tok; m->x = x; m->gates = gates; m->cs = cs; m->hs = hs; m->r = r; m->aux = aux; m->errs = errs;
+    m->zeros = zeros; m->ones = ones; m->scalars = scalars; m->dr = dr; m->dx = dx; m->dh = dh; m->dc = dc; m->dgates = dgates;
+    m->dact = (float*)(base + d0);
+    m->dact_bytes = d1 - d0;
+  }
+  return a.off + 256;
+}
+
+#define CU(expr)                                                                              \
+  do {                                                                                        \
+    cudaError_t e__ = (expr);                                                                 \
+    if (e__ != cudaSuccess) throw cuda_exception(std::string(#expr) + ": " + cudaGetErrorString(e__)); \
+  } while (0)
+
+void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float* const* masks, float* loss_dev) {
+  const dyb200h_lm_config& c = m.c;
+  const uint32_t V = c.V, E = c.E, H = c.H, L = c.L, T = c.T, B = c.B;
+  const size_t HB = (size_t)H * B, GB = 4 * HB, VB = (size_t)V * B, EB = (size_t)E * B;
+  const Device_GPU& dev = m.dev;
+  cudaStream_t st = m.stream;
+  if (c.dropout && !masks) throw std::invalid_argument("dropout is on but no masks were given");
+
+  CU(cudaMemcpyAsync(m.tok, tokens, (size_t)(T + 1) * B * sizeof(uint32_t), on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st));
+  // place the target ids of step t where PickNegLogSoftmax expects them: aux_t = {z[B], m[B], ids[B]}
+  CU(cudaMemcpy2DAsync(m.aux + 2 * (size_t)B, 3 * (size_t)B * sizeof(float), m.tok + B, (size_t)B * sizeof(uint32_t),
+                       (size_t)B * sizeof(uint32_t), T, cudaMemcpyDeviceToDevice, st));
+
+  Tensor tC(Dim({E}, V), m.p[0]), tR(Dim({V, H}), m.p[1 + 3 * L]), tbias(Dim({V}), m.p[2 + 3 * L]);
+  Tensor tZero(Dim({H}, B), m.zeros);
+  VanillaLSTMGates gates_node(c.dropout != 0);
+  VanillaLSTMC c_node;
+  VanillaLSTMH h_node;
+  CwiseSum sum_node;
+  PickNegLogSoftmax pnls(nullptr);
+  pnls.dim = Dim({1}, B);
+
+  auto layer_xs = [&](uint32_t t, uint32_t l, Tensor* store, std::vector<const Tensor*>& xs) {
+    // store: [in, h_prev, Wx, Wh, b, mx, mh]
+    uint32_t I = l == 0 ? E : H;
+    store[0] = Tensor(Dim({I}, B), l == 0 ? m.x + t * EB : m.hs + ((size_t)t * L + l - 1) * HB);
+    store[1] = t == 0 ? tZero : Tensor(Dim({H}, B), m.hs + ((size_t)(t - 1) * L + l) * HB);
+    store[2] = Tensor(Dim({4 * H, I}), m.p[1 + 3 * l]);
+    store[3] = Tensor(Dim({4 * H, H}), m.p[2 + 3 * l]);
+    store[4] = Tensor(Dim({4 * H}), m.p[3 + 3 * l]);
+    xs = {&store[0], &store[1], &store[2], &store[3], &store[4]};
+    if (c.dropout) {
+      store[5] = Tensor(Dim({I}, B), const_cast<float*>(masks[2 * l]));
+      store[6] = Tensor(Dim({H}, B), const_cast<float*>(masks[2 * l + 1]));
+      xs.push_back(&store[5]);
+      xs.push_back(&store[6]);
+    }
+  };
+
+  // ---------------- forward ----------------
+  for (uint32_t t = 0; t < T; ++t) {
+    LookupNode look(tC, nullptr, B);
+    look.aux_mem = m.tok + (size_t)t * B;
+    Tensor xt(Dim({E}, B), m.x + t * EB);
+    look.forward_dev_impl(dev, {}, xt);
+    for (uint32_t l = 0; l < L; ++l) {
+      size_t idx = (size_t)t * L + l;
+      Tensor store[7];
+      std::vector<const Tensor*> xs;
+      layer_xs(t, l, store, xs);
+      Tensor tg(Dim({4 * H}, B), m.gates + idx * GB), tc(Dim({H}, B), m.cs + idx * HB), th(Dim({H}, B), m.hs + idx * HB);
+      gates_node.forward_dev_impl(dev, xs, tg);
+      Tensor cprev = t == 0 ? tZero : Tensor(Dim({H}, B), m.cs + ((size_t)(t - 1) * L + l) * HB);
+      c_node.forward_dev_impl(dev, {&cprev, &tg}, tc);
+      h_node.forward_dev_impl(dev, {&tc, &tg}, th);
+    }
+    Tensor htop(Dim({H}, B), m.hs + ((size_t)t * L + L - 1) * HB), rt(Dim({V}, B), m.r + t * VB);
+    // MatrixMultiply R * h, then CwiseSum(bias, R*h) in place (dynet/nodes-matrixmultiply.cc:50-59)
+    throw_status(dev, dyb200_gemm(0, 0, V, B, H, tR.v, V, htop.v, H, rt.v, V, 0, dev.ctx));
+    sum_node.forward_dev_impl(dev, {&tbias, &rt}, rt);
+    pnls.aux_mem = m.aux + (size_t)t * 3 * B;
+    Tensor et(Dim({1}, B), m.errs + (size_t)t * B);
+    pnls.forward_dev_impl(dev, {&rt}, et);
+  }
+  throw_status(dev, dyb200_sum_all(m.errs, (size_t)T * B, loss_dev, 0, dev.ctx));
+
+  // ---------------- backward ----------------
+  CU(cudaMemsetAsync(m.dact, 0, m.dact_bytes, st));
+  Tensor tgR(Dim({V, H}), m.g[1 + 3 * L]), tgbias(Dim({V}), m.g[2 + 3 * L]);
+  Tensor tones(Dim({1}, B), m.ones);
+  for (uint32_t tt = T; tt-- > 0;) {
+    size_t top = (size_t)tt * L + L - 1;
+    Tensor rt(Dim({V}, B), m.r + tt * VB), et(Dim({1}, B), m.errs + (size_t)tt * B), tdr(Dim({V}, B), m.dr);
+    Tensor htop(Dim({H}, B), m.hs + top * HB);
+    CU(cudaMemsetAsync(m.dr, 0, VB * sizeof(float), st));
+    pnls.aux_mem = m.aux + (size_t)tt * 3 * B;
+    pnls.backward_dev_impl(dev, {&rt}, et, tones, 0, tdr);
+    sum_node.backward_dev_impl(dev, {&tbias, &rt}, rt, tdr, 0, tgbias);          // dbias += sum_b dr
+    throw_status(dev, dyb200_gemm(0, 1, V, H, B, m.dr, V, htop.v, H, tgR.v, V, 1, dev.ctx));           // dR += dr h^T
+    throw_status(dev, dyb200_gemm(1, 0, H, B, V, tR.v, V, m.dr, V, m.dh + top * HB, H, 1, dev.ctx));   // dh += R^T dr
+    for (uint32_t l = L; l-- > 0;) {
+      size_t idx = (size_t)tt * L + l;
+      Tensor store[7];
+      std::vector<const Tensor*> xs;
+      layer_xs(tt, l, store, xs);
+      Tensor tg(Dim({4 * H}, B), m.gates + idx * GB), tc(Dim({H}, B), m.cs + idx * HB), th(Dim({H}, B), m.hs + idx * HB);
+      Tensor tdh(Dim({H}, B), m.dh + idx * HB), tdc(Dim({H}, B), m.dc + idx * HB), tdg(Dim({4 * H}, B), m.dgates + idx * GB);
+      Tensor cprev = tt == 0 ? tZero : Tensor(Dim({H}, B), m.cs + ((size_t)(tt - 1) * L + l) * HB);
+      h_node.backward_dev_impl(dev, {&tc, &tg}, th, tdh, 0, tdc);
+      h_node.backward_dev_impl(dev, {&tc, &tg}, th, tdh, 1, tdg);
+      if (tt > 0) {
+        Tensor tdcp(Dim({H}, B), m.dc + ((size_t)(tt - 1) * L + l) * HB);
+        c_node.backward_dev_impl(dev, {&cprev, &tg}, tc, tdc, 0, tdcp);
+      }
+      c_node.backward_dev_impl(dev, {&cprev, &tg}, tc, tdc, 1, tdg);
+      uint32_t I = l == 0 ? E : H;
+      Tensor tdin(Dim({I}, B), l == 0 ? m.dx + tt * EB : m.dh + ((size_t)tt * L + l - 1) * HB);
+      gates_node.backward_dev_impl(dev, xs, tg, tdg, 0, tdin);
+      if (tt > 0) {
+        Tensor tdhp(Dim({H}, B), m.dh + ((size_t)(tt - 1) * L + l) * HB);
+        gates_node.backward_dev_impl(dev, xs, tg, tdg, 1, tdhp);
+      }
+      Tensor gWx(Dim({4 * H, I}), m.g[1 + 3 * l]), gWh(Dim({4 * H, H}), m.g[2 + 3 * l]), gb(Dim({4 * H}), m.g[3 + 3 * l]);
+      gates_node.backward_dev_impl(dev, xs, tg, tdg, 2, gWx);
+      gates_node.backward_dev_impl(dev, xs, tg, tdg, 3, gWh);
+      gates_node.backward_dev_impl(dev, xs, tg, tdg, 4, gb);
+    }
+  }
+  Tensor tgC(Dim({E}, V), m.g[0]);
+  for (uint32_t t = 0; t < T; ++t) {
+    LookupNode look(tC, nullptr, B);
+    look.aux_mem = m.tok + (size_t)t * B;
+    Tensor tdx(Dim({E}, B), m.dx + t * EB);
+    look.accumulate_grad(dev, tdx, tgC);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t dyb200h_lm_num_params(const dyb200h_lm_config* c) { return param_sizes(*c, nullptr); }
+size_t dyb200h_lm_workspace_bytes(const dyb200h_lm_config* c) { return plan(*c, nullptr, nullptr, 0); }
+// Offsets (in floats) of the 3L+3 parameter tensors inside the flat buffer; returns their count.
+int dyb200h_lm_param_offsets(const dyb200h_lm_config* c, size_t* offsets, size_t* sizes, int cap) {
+  std::vector<size_t> sz;
+  param_sizes(*c, &sz);
+  size_t off = 0;
+  for (size_t k = 0; k < sz.size() && (int)k < cap; ++k) { offsets[k] = off; sizes[k] = sz[k]; off += sz[k]; }
+  return (int)sz.size();
+}
+
+int dyb200h_lm_create(const dyb200h_lm_config* c, float* params, float* grads, void* workspace, size_t ws_bytes,
+                      dyb200_ctx* ctx, void* stream, void** out) {
+  if (!c || !params || !grads || !workspace || !ctx || !out) return DYB200_EINVAL;
+  if (ws_bytes < plan(*c, nullptr, nullptr, 0)) return DYB200_ENOMEM;
+  Lm* m = new Lm();
+  m->c = *c;
+  m->dev.ctx = ctx;
+  m->params = params;
+  m->grads = grads;
+  m->stream = (cudaStream_t)stream;
+  std::vector<size_t> sz;
+  param_sizes(*c, &sz);
+  size_t off = 0;
+  for (size_t n : sz) { m->p.push_back(params + off); m->g.push_back(grads + off); off += n; }
+  plan(*c, m, (char*)workspace, ws_bytes);
+  int rc = dyb200_fill(m->zeros, (size_t)c->H * c->B, 0.f, ctx);
+  if (!rc) rc = dyb200_fill(m->ones, c->B, 1.f, ctx);
+  if (rc) { delete m; return rc; }
+  *out = m;
+  return DYB200_OK;
+}
+
+void dyb200h_lm_destroy(void* h) { delete (Lm*)h; }
+const char* dyb200h_lm_error(void* h) { return h ? ((Lm*)h)->err.c_str() : "null handle"; }
+
+static int guarded(Lm* m, void (*fn)(Lm&, void*), void* arg) {
+  try {
+    fn(*m, arg);
+    return DYB200_OK;
+  } catch (const std::invalid_argument& e) { m->err = e.what(); return DYB200_EINVAL;
+  } catch (const out_of_memory& e) { m->err = e.what(); return DYB200_ENOMEM;
+  } catch (const cuda_exception& e) { m->err = e.what(); return DYB200_ECUDA;
+  } catch (const std::exception& e) { m->err = e.what(); return DYB200_ERUNTIME; }
+}
+
+struct FbArgs { const uint32_t* tokens; int on_device; const float* const* masks; float* loss_dev; };
+
+// tokens: (T+1) x B ids (host, or device when tokens_on_device); masks: 2L device pointers
+// {mask_x_0, mask_h_0, mask_x_1, ...} each I_l x B / H x B, or NULL when dropout is off;
+// loss_dev: device scalar that receives sum_batches(sum_t err_t).  Gradients accumulate into `grads`.
+int dyb200h_lm_forward_backward(void* h, const uint32_t* tokens, int tokens_on_device, const float* const* masks,
+                                float* loss_dev) {
+  FbArgs a{tokens, tokens_on_device, masks, loss_dev};
+  return guarded((Lm*)h, [](Lm& m, void* p) {
+    FbArgs* a = (FbArgs*)p;
+    forward_backward(m, a->tokens, a->on_device, a->masks, a->loss_dev);
+  }, &a);
+}
+
+// Squared L2 norm of the local gradients into a device scalar (reduce it over ranks before update).
+int dyb200h_lm_grad_sumsq(void* h, float** scalar_dev_out) {
+  Lm* m = (Lm*)h;
+  size_t n = param_sizes(m->c, nullptr);
+  int rc = dyb200_squared_norm(m->grads, n, m->scalars, 0, m->dev.ctx);
+  if (rc) { m->err = dyb200_last_error(m->dev.ctx); return rc; }
+  if (scalar_dev_out) *scalar_dev_out = m->scalars;
+  return DYB200_OK;
+}
+
+// SimpleSGD update with gradient clipping from the scalar computed by dyb200h_lm_grad_sumsq; zeroes the gradients.
+int dyb200h_lm_update(void* h) {
+  Lm* m = (Lm*)h;
+  size_t n = param_sizes(m->c, nullptr);
+  int rc = dyb200_sgd_update(m->params, m->grads, n, m->c.lr, m->c.clip, m->scalars, m->dev.ctx);
+  if (rc) m->err = dyb200_last_error(m->dev.ctx);
+  return rc;
+}
+
+// Device pointer of the hidden states h[t][l] (T x L x H x B), for parity checks.
+const float* dyb200h_lm_hidden_states(void* h) { return ((Lm*)h)->hs; }
+
+}  // extern "C"

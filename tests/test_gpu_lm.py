@@ -1,0 +1,62 @@
+"""GPU parity of one LSTM language-model training step (config-4 graph at small sizes): the C++
+driver over the C ABI against the CPU oracle -- loss, every hidden state, every gradient, and the
+parameters after the clipped SGD update."""
+import numpy as np
+import pytest
+
+from util import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dims,dropout", [
+    (dict(V=97, E=32, H=64, L=2, T=4, B=8), 0.2),
+    (dict(V=50, E=20, H=12, L=1, T=3, B=5), 0.0),      # odd sizes: every kernel takes its scalar path
+    (dict(V=1000, E=128, H=256, L=2, T=6, B=32), 0.2),
+])
+def test_lm_step_matches_oracle(oracle, dims, dropout):
+    from dynet_b200 import lm
+    V, E, H, L, T, B = (dims[k] for k in "VEHLTB")
+    model = lm.LstmLm(device=0, seed=11, lr=0.1, clip=5.0, dropout=bool(dropout), **dims)
+    tokens, masks = lm.synthetic_batch(dims, seed=12, dropout=dropout)
+    params = model.params_host()
+    loss = model.forward_backward(tokens, masks)
+    grads_ref = [np.zeros_like(p) for p in params]
+    loss_ref, h_ref = oracle.lstm_lm_fwdbwd((V, E, H, L, T, B), params, grads_ref, tokens,
+                                            masks[0] if masks else None, masks[1] if masks else None, want_h=True)
+    assert abs(loss - loss_ref) <= 1e-4 * abs(loss_ref)
+    assert_close(model.hidden_states_host(), h_ref, 1e-4, floor=1e-2, what="hidden states")
+    for k, (got, want) in enumerate(zip(model.grads_host(), grads_ref)):
+        scale = max(1e-3, float(np.abs(want).max()))
+        assert_close(got, want, 1e-4, floor=scale, what="grad of tensor %d" % k)
+    assert model.ctx.device_errors() == 0
+    # trainer update (gradient clipping at 5, SimpleSGD lr 0.1) and gradient reset
+    p_ref = [p.copy() for p in params]
+    oracle.sgd_update(p_ref, grads_ref, 0.1, 5.0)
+    model.update()
+    for k, (got, want) in enumerate(zip(model.params_host(), p_ref)):
+        assert_close(got, want, 1e-5, floor=1e-1, what="param %d after update" % k)
+    assert all(float(np.abs(gr).max()) == 0.0 for gr in model.grads_host())
+    # second step on the updated parameters, tokens resident on the device this time
+    import torch
+    tok_dev = torch.from_numpy(tokens.view(np.int32)).cuda()
+    md = model.masks_to_device(masks) if masks else None
+    model.launch_forward_backward(tok_dev, md)
+    loss2 = float(model.loss_dev.item())
+    g2 = [np.zeros_like(p) for p in params]
+    loss2_ref, _ = oracle.lstm_lm_fwdbwd((V, E, H, L, T, B), p_ref, g2, tokens, masks[0] if masks else None,
+                                         masks[1] if masks else None)
+    assert abs(loss2 - loss2_ref) <= 1e-4 * abs(loss2_ref)
+    model.close()
+
+
+def test_lm_bad_token_is_reported(oracle):
+    from dynet_b200 import capi, lm
+    dims = dict(V=20, E=8, H=8, L=1, T=2, B=3)
+    model = lm.LstmLm(device=0, seed=1, dropout=False, **dims)
+    tokens, _ = lm.synthetic_batch(dims, seed=2, dropout=0.0)
+    tokens[1, 1] = 20   # out of range: device-resident ids are clamped and flagged, never dereferenced
+    model.forward_backward(tokens, None)
+    with pytest.raises(capi.CudaError):
+        model.ctx.device_errors()
+    model.close()

@@ -487,7 +487,7 @@ def test_lstm_gates_vs_oracle(oracle, g, capi, I_list, H, B, masks):
         want = oracle.lstm_gates_bwd(xs, h, Wx, Wh, fx_ref, dE, i, d0.copy(), mx, mh)
         d_ = g.dev(d0)
         g.ctx().bwd("vanilla_lstm_gates", ts, g.T(fx_r), g.T(dE_), i, capi.DyTensor.of(d_.data_ptr(), ts[i].d[:ts[i].nd], ts[i].bd), at)
-        assert_close(g.host(d_), want, TOL_REDUCE, floor=1e-2, what="gates bwd i=%d" % i)
+        assert_close(g.host(d_), want, TOL_REDUCE, floor=ACC_FLOOR, what="gates bwd i=%d" % i)
 
 
 def test_lstm_gates_weightnoise_and_errors(oracle, g, capi):
