@@ -1,0 +1,329 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: training steps of the 2-layer LSTM language model built from the fused
+nodes (embedding gather, vanilla_lstm_gates/_c/_h with dropout masks, output projection,
+PickNegLogSoftmax, their backward, deterministic embedding scatter-add, gradient all-reduce, clipped SGD).
+
+  python bench.py --gpus N --steps K --warmup W            # this implementation, one rank per GPU
+  python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU algorithm on the host cores
+
+Prints ONE JSON line (rank 0).  `value` = tokens/s with the token ids already resident in HBM;
+`e2e` = tokens/s through the same public step call with the ids copied from pinned host memory and the
+loss read back every step.  Data are synthetic: Zipf(1.1) token ids, Glorot-uniform weights.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# The configuration the metric is quoted on: 2-layer LSTM-LM, vocab 10k, embed 512, hidden 1024,
+# dropout 0.2, sequence length 35, global batch 512 sharded over the GPUs.
+WORKLOAD = dict(V=10000, E=512, H=1024, L=2, T=35)
+GLOBAL_BATCH = 512
+DROPOUT = 0.2
+METRIC = "LSTM-LM training tokens/sec (2-layer LSTM, V=10k E=512 H=1024 T=35, global batch 512, fwd+bwd+allreduce+SGD)"
+
+
+def flops_per_step(B):
+    V, E, H, L, T = (WORKLOAD[k] for k in "VEHLT")
+    fwd = 0
+    for l in range(L):
+        fwd += 2 * 4 * H * ((E if l == 0 else H) + H) * B
+    fwd += 2 * V * H * B
+    return 3 * fwd * T   # backward = 2x forward
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d.get("hbm_gbs"), "bf16_tflops": d.get("bf16_tflops"),
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def measure_tf32_peak(torch):
+    """cuBLAS TF32 dense GEMM, 8192^3, run back to back for about a second (the 3xTF32 roofline
+    denominator is this figure / 3; the peaks file only carries bf16)."""
+    n = 8192
+    a = torch.randn(n, n, device="cuda")
+    b = torch.randn(n, n, device="cuda")
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        for _ in range(3):
+            torch.matmul(a, b)
+        torch.cuda.synchronize()
+        reps = 40
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            torch.matmul(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        return 2.0 * n ** 3 * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+        del a, b
+
+
+def cpu_baseline_sample(threads, seqs_per_thread, steps=1):
+    """The CPU oracle (a port of the reference's single-threaded Eigen path) on a bounded sample of
+    the same workload: `threads` independent shards of `seqs_per_thread` sequences, full model size."""
+    import oracle
+    from dynet_b200 import lm
+    oracle.build()
+    V, E, H, L, T = (WORKLOAD[k] for k in "VEHLT")
+    params = lm.init_params(V, E, H, L, seed=1)
+    dims = dict(WORKLOAD, B=seqs_per_thread)
+    work = []
+    for k in range(threads):
+        tokens, masks = lm.synthetic_batch(dims, seed=100 + k, dropout=DROPOUT)
+        grads = [np.zeros_like(p) for p in params]
+        work.append((tokens, masks, grads))
+
+    def run(k):
+        tokens, masks, grads = work[k]
+        oracle.lstm_lm_fwdbwd((V, E, H, L, T, seqs_per_thread), params, grads, tokens, masks[0], masks[1])
+
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        ths = [threading.Thread(target=run, args=(k,)) for k in range(threads)]
+        [t.start() for t in ths]
+        [t.join() for t in ths]
+        # gradient sum over shards + clipped SGD on one thread, as rank 0 does in dynet/mp.h
+        total = [sum(w[2][i] for w in work) for i in range(len(params))]
+        oracle.sgd_update([p.copy() for p in params], total, 0.1, 5.0)
+        times.append(time.perf_counter() - t0)
+    tokens_per_step = threads * seqs_per_thread * T
+    sec = float(np.mean(times))
+    return tokens_per_step / sec, sec, tokens_per_step
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ncpu = os.cpu_count() or 1
+    threads = max(1, min(ncpu, 32))
+    seqs = 16   # per thread: enough columns that each weight matrix is reused, as in the real batch
+    # warm-up (builds the oracle, touches memory) then K bounded steps
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_baseline_sample(threads, 1, steps=1)
+    tps, sec, toks = cpu_baseline_sample(threads, seqs, steps=max(1, args.steps))
+    sample = "%d host threads x %d sequences x T=35 per step (of the 512-sequence batch), full model size" % (threads, seqs)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "lstm_lm_2x1024_v10k_t35", "global_batch": GLOBAL_BATCH, "seq_len": WORKLOAD["T"],
+                   "note": "reference CPU algorithm (oracle port; the reference itself needs Eigen b2e267dc99d4, absent here)"},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from dynet_b200 import dp, lm
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback for this arm")
+    rank, world = dp.init_process_group("nccl") if int(os.environ.get("WORLD_SIZE", "1")) > 1 else (0, 1)
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world != args.gpus and world > 1:
+        raise SystemExit("--gpus %d does not match WORLD_SIZE %d" % (args.gpus, world))
+    if GLOBAL_BATCH % world:
+        raise SystemExit("global batch %d is not divisible by %d ranks" % (GLOBAL_BATCH, world))
+    B = GLOBAL_BATCH // world
+    dims = dict(WORKLOAD, B=B)
+    V, E, H, L, T = (WORKLOAD[k] for k in "VEHLT")
+    model = lm.LstmLm(device=local_rank, seed=1, lr=0.1, clip=5.0, dropout=True, **dims)
+
+    # synthetic corpus: a few global batches of Zipf(1.1) ids; this rank keeps its columns
+    n_batches = 4
+    host_tokens, dev_tokens = [], []
+    for k in range(n_batches):
+        tokens, _ = lm.synthetic_batch(dict(WORKLOAD, B=GLOBAL_BATCH), seed=1000 + k, dropout=0.0)
+        tok, _ = dp.shard_batch(tokens, None, rank, world)
+        pinned = torch.from_numpy(tok.view(np.int32)).pin_memory()
+        host_tokens.append(pinned)
+        dev_tokens.append(pinned.cuda())
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234 + rank)
+    keep = 1.0 - DROPOUT
+
+    def draw_masks():
+        # RandomBernoulli(keep) * 1/keep per layer, fixed over the sequence (dynet/lstm.cc:964-982)
+        out = []
+        for l in range(L):
+            for n in (E if l == 0 else H, H):
+                out.append((torch.rand(B, n, device="cuda", generator=gen) < keep).float() * (1.0 / keep))
+        return out
+
+    def step(tokens):
+        masks = draw_masks()
+        model.launch_forward_backward(tokens, masks)
+        model.allreduce_grads()
+        model.update()
+        return masks
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(K, source, read_loss):
+        barrier()
+        l0 = model.ctx.launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        losses, keepalive = [], []
+        for k in range(K):
+            keepalive.append(step(source[k % n_batches]))
+            if read_loss:
+                losses.append(float(model.loss_dev.item()))   # D2H read of the step's result
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, model.ctx.launches() - l0, losses
+
+    for k in range(max(3, args.warmup)):
+        step(dev_tokens[k % n_batches])
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    model.ctx.profile_begin(1 << 16)
+    ms, launches, _ = timed(args.steps, dev_tokens, read_loss=False)
+    prof = model.ctx.profile_end()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e, _, losses = timed(args.steps, host_tokens, read_loss=True)
+    errs = model.ctx.device_errors()
+
+    tokens_per_step = GLOBAL_BATCH * T
+    value = tokens_per_step * args.steps / (ms * 1e-3)
+    e2e = tokens_per_step * args.steps / (ms_e2e * 1e-3)
+
+    if rank == 0:
+        peaks = measured_peaks()
+        tf32 = measure_tf32_peak(torch)
+        # dominant kernel = the GEMM behind the gates, the projection and their backward products
+        which = "tensor" if prof["tensor"][1] >= prof["simt"][1] and prof["tensor"][1] > 0 else "simt"
+        g_ms, g_n, g_fl = prof[which]
+        achieved = g_fl / (g_ms * 1e-3) / 1e12 if g_ms > 0 else 0.0
+        peak = tf32 / 3.0
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": achieved / peak if peak else None, "traffic": None,
+                    "kernel": "gemm_3xtf32_tcgen05" if which == "tensor" else "gemm_fp32_cuda_core",
+                    "launches": g_n, "share_of_step_time": g_ms / ms if ms else None,
+                    "peak_source": "cuBLAS TF32 8192^3 measured in this run (%.0f TFLOP/s) / 3; bf16 peak of %s: %s TFLOP/s"
+                                   % (tf32, peaks["source"], peaks["bf16_tflops"]),
+                    "useful_tflop_per_step": flops_per_step(B) * world / 1e12}
+        cb_threads = max(1, min(os.cpu_count() or 1, 32))
+        cb_tps, cb_sec, cb_tok = cpu_baseline_sample(cb_threads, 16, steps=1) if not args.no_cpu_baseline else (None, None, None)
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "lstm_lm_2x1024_v10k_t35", "global_batch": GLOBAL_BATCH, "per_gpu_batch": B,
+                       "seq_len": T, "vocab": V, "embed": E, "hidden": H, "layers": L, "dropout": DROPOUT,
+                       "parallelism": "dp%d" % world, "l2": "per-step working set (~2.5 GB of activations) exceeds the 126 MB L2"},
+            "clocks": clocks,
+            "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": int((T + 1) * B * 4 * world),
+                    "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps, "last_loss": losses[-1] if losses else None},
+            "gpu_launches": int(launches),
+            "roofline": roofline,
+            "cpu_baseline": None if cb_tps is None else {
+                "value": cb_tps, "unit": "tokens/s", "cores": cb_threads, "kind": "port",
+                "sample": "%d host threads x 16 sequences x T=35 (of the 512-sequence batch), one fwd+bwd+update step at full "
+                          "model size, %.1f s; each thread is the reference's single-threaded CPU path on its shard" % (cb_threads, cb_sec)},
+            "device_error_flags": errs,
+        }
+        print(json.dumps(line), flush=True)
+    model.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="dyb200", choices=["dyb200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -85,7 +85,7 @@ FWD_ONLY = ["lookup"]
 OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200_ctx_check_device_errors",
          "dyb200_ctx_launch_count", "dyb200_version", "dyb200_lookup_accumulate_grads",
          "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm", "dyb200_fill", "dyb200_sum_all",
-         "dyb200_squared_norm", "dyb200_sgd_update"]
+         "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end"]
 
 
 def exported_symbols():
@@ -129,6 +129,10 @@ def lib():
         L.dyb200_ctx_launch_count.restype = C.c_uint64
         L.dyb200_ctx_launch_count.argtypes = [C.c_void_p]
         L.dyb200_version.restype = C.c_char_p
+        L.dyb200_ctx_profile_begin.restype = C.c_int
+        L.dyb200_ctx_profile_begin.argtypes = [C.c_void_p, C.c_int]
+        L.dyb200_ctx_profile_end.restype = C.c_int
+        L.dyb200_ctx_profile_end.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_double)]
         L.dyb200_lookup_accumulate_grads.restype = C.c_int
         L.dyb200_lookup_accumulate_grads.argtypes = [C.c_uint, C.POINTER(C.c_uint32), C.c_void_p, C.c_void_p,
                                                      C.c_void_p, C.c_uint, C.c_uint, C.c_void_p]
@@ -172,6 +176,15 @@ class Context:
 
     def launches(self):
         return int(self.L.dyb200_ctx_launch_count(self.h))
+
+    def profile_begin(self, capacity=1 << 16):
+        self.check(self.L.dyb200_ctx_profile_begin(self.h, capacity))
+
+    def profile_end(self):
+        """Returns {"simt": (ms, launches, flops), "tensor": (...)} summed over the recorded GEMM launches."""
+        ms, n, fl = (C.c_double * 2)(), (C.c_uint64 * 2)(), (C.c_double * 2)()
+        self.check(self.L.dyb200_ctx_profile_end(self.h, ms, n, fl))
+        return {"simt": (ms[0], int(n[0]), fl[0]), "tensor": (ms[1], int(n[1]), fl[1])}
 
     def device_errors(self):
         f = C.c_uint32(0)

@@ -22,6 +22,25 @@ struct dyb200_ctx {
   uint64_t launches;     // kernels launched through this context
   // 3xTF32 GEMM state (tensor maps are encoded per call; driver entry point cached)
   void* encode_tiled;    // cuTensorMapEncodeTiled
+  // optional per-launch timing of the GEMM kernels (CUDA events on the launch stream)
+  cudaEvent_t* prof_ev;  // 2 * prof_cap events: start/stop pairs
+  double* prof_flops;    // useful FLOPs of each recorded launch
+  int* prof_path;        // 1 = tensor-pipe kernel, 0 = CUDA-core kernel
+  int prof_cap, prof_n;
+};
+
+// Brackets a GEMM launch with events when profiling is on (see dyb200_ctx_profile_begin).
+struct GemmProfScope {
+  dyb200_ctx* ctx; int slot;
+  GemmProfScope(dyb200_ctx* c, double flops, int path) : ctx(c), slot(-1) {
+    if (c->prof_ev && c->prof_n < c->prof_cap) {
+      slot = c->prof_n++;
+      c->prof_flops[slot] = flops;
+      c->prof_path[slot] = path;
+      cudaEventRecord(c->prof_ev[2 * slot], c->stream);
+    }
+  }
+  ~GemmProfScope() { if (slot >= 0) cudaEventRecord(ctx->prof_ev[2 * slot + 1], ctx->stream); }
 };
 
 // Device error bits written into ctx->dev_flags.

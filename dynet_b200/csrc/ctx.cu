@@ -75,6 +75,42 @@ int dyb200_ctx_destroy(dyb200_ctx* ctx) {
   return DYB200_OK;
 }
 
+int dyb200_ctx_profile_begin(dyb200_ctx* ctx, int capacity) {
+  DYB_CHECK_ARG(ctx, capacity > 0 && capacity <= (1 << 20), "profile_begin: capacity out of range");
+  if (ctx->prof_ev) return dyb200_fail(ctx, DYB200_ERUNTIME, "profile_begin: already profiling");
+  ctx->prof_ev = (cudaEvent_t*)calloc(2 * (size_t)capacity, sizeof(cudaEvent_t));
+  ctx->prof_flops = (double*)calloc(capacity, sizeof(double));
+  ctx->prof_path = (int*)calloc(capacity, sizeof(int));
+  if (!ctx->prof_ev || !ctx->prof_flops || !ctx->prof_path) return dyb200_fail(ctx, DYB200_ENOMEM, "profile_begin: host allocation failed");
+  for (int k = 0; k < 2 * capacity; ++k) DYB_CUDA(ctx, cudaEventCreate(&ctx->prof_ev[k]));
+  ctx->prof_cap = capacity;
+  ctx->prof_n = 0;
+  return DYB200_OK;
+}
+
+int dyb200_ctx_profile_end(dyb200_ctx* ctx, double* ms_out, uint64_t* launches_out, double* flops_out) {
+  if (!ctx->prof_ev) return dyb200_fail(ctx, DYB200_ERUNTIME, "profile_end: profiling is not on");
+  DYB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  double ms[2] = {0, 0}, fl[2] = {0, 0};
+  uint64_t cnt[2] = {0, 0};
+  for (int k = 0; k < ctx->prof_n; ++k) {
+    float t = 0.f;
+    DYB_CUDA(ctx, cudaEventElapsedTime(&t, ctx->prof_ev[2 * k], ctx->prof_ev[2 * k + 1]));
+    int p = ctx->prof_path[k] ? 1 : 0;
+    ms[p] += t; fl[p] += ctx->prof_flops[k]; cnt[p]++;
+  }
+  for (int k = 0; k < 2 * ctx->prof_cap; ++k) cudaEventDestroy(ctx->prof_ev[k]);
+  free(ctx->prof_ev); free(ctx->prof_flops); free(ctx->prof_path);
+  ctx->prof_ev = nullptr; ctx->prof_flops = nullptr; ctx->prof_path = nullptr;
+  ctx->prof_cap = ctx->prof_n = 0;
+  for (int p = 0; p < 2; ++p) {
+    if (ms_out) ms_out[p] = ms[p];
+    if (launches_out) launches_out[p] = cnt[p];
+    if (flops_out) flops_out[p] = fl[p];
+  }
+  return DYB200_OK;
+}
+
 const char* dyb200_last_error(const dyb200_ctx* ctx) { return ctx ? ctx->err : "null context"; }
 
 uint64_t dyb200_ctx_launch_count(const dyb200_ctx* ctx) { return ctx ? ctx->launches : 0; }

@@ -85,9 +85,16 @@ int dyb200_gemm_simt(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const 
 }
 
 int dyb200_gemm_fused(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const GemmPair* pairs, const GemmEpilogue& epi) {
-  int handled = 0;
-  int rc = dyb200_gemm_tc(ctx, M, N, npairs, pairs, epi, &handled);
+  double flops = 0;
+  for (int p = 0; p < npairs; ++p) flops += 2.0 * M * N * pairs[p].K;
+  int handled = 0, rc;
+  {
+    GemmProfScope scope(ctx, flops, 1);
+    rc = dyb200_gemm_tc(ctx, M, N, npairs, pairs, epi, &handled);
+    if (!handled && scope.slot >= 0) { ctx->prof_n--; scope.slot = -1; }  // nothing was launched
+  }
   if (handled) return rc;
+  GemmProfScope scope(ctx, flops, 0);
   return dyb200_gemm_simt(ctx, M, N, npairs, pairs, epi);
 }
 

@@ -67,6 +67,12 @@ const char* dyb200_last_error(const dyb200_ctx* ctx);
 int dyb200_ctx_check_device_errors(dyb200_ctx* ctx, uint32_t* flags_out);
 /* Number of kernels this library has launched through `ctx` so far. */
 uint64_t dyb200_ctx_launch_count(const dyb200_ctx* ctx);
+/* Per-launch timing of the GEMM kernels for the benchmark's roofline: between begin and end every
+ * GEMM launch (up to `capacity`) is bracketed by CUDA events on the context's stream.  end()
+ * synchronises and returns, for index 0 = CUDA-core kernel and 1 = tensor-pipe kernel, the summed
+ * device time in ms, the launch count and the useful FLOPs (2*M*N*K per product). */
+int dyb200_ctx_profile_begin(dyb200_ctx* ctx, int capacity);
+int dyb200_ctx_profile_end(dyb200_ctx* ctx, double ms_out[2], uint64_t launches_out[2], double flops_out[2]);
 /* Library build string ("dyb200 <n> sm_100a"). */
 const char* dyb200_version(void);
 
