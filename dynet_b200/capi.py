@@ -84,6 +84,7 @@ NODES = ["tanh", "logistic", "rectify", "elu", "cmult", "csum", "cdiv", "softmax
 FWD_ONLY = ["lookup"]
 OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200_ctx_check_device_errors",
          "dyb200_ctx_launch_count", "dyb200_version", "dyb200_lookup_accumulate_grads",
+         "dyb200_lookup_accumulate_grads_noalloc",
          "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm", "dyb200_fill", "dyb200_sum_all",
          "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end"]
 
@@ -136,6 +137,8 @@ def lib():
         L.dyb200_lookup_accumulate_grads.restype = C.c_int
         L.dyb200_lookup_accumulate_grads.argtypes = [C.c_uint, C.POINTER(C.c_uint32), C.c_void_p, C.c_void_p,
                                                      C.c_void_p, C.c_uint, C.c_uint, C.c_void_p]
+        L.dyb200_lookup_accumulate_grads_noalloc.restype = C.c_int
+        L.dyb200_lookup_accumulate_grads_noalloc.argtypes = L.dyb200_lookup_accumulate_grads.argtypes
         for n in ("dyb200_parallel_memcpy", "dyb200_parallel_accumulate"):
             f = getattr(L, n)
             f.restype = C.c_int
@@ -213,6 +216,12 @@ class Context:
         n = len(ids_host)
         arr = (C.c_uint32 * n)(*[int(i) for i in ids_host]) if n else None
         self.check(self.L.dyb200_lookup_accumulate_grads(n, arr, ids_dev_ptr, g_ptr, all_grads_ptr, dim_size, vocab, self.h))
+
+    def lookup_accumulate_grads_noalloc(self, ids_host, ids_dev_ptr, g_ptr, all_grads_ptr, dim_size, vocab):
+        """Same as lookup_accumulate_grads, through the entry point that never allocates device memory."""
+        n = len(ids_host)
+        arr = (C.c_uint32 * n)(*[int(i) for i in ids_host]) if n else None
+        self.check(self.L.dyb200_lookup_accumulate_grads_noalloc(n, arr, ids_dev_ptr, g_ptr, all_grads_ptr, dim_size, vocab, self.h))
 
     def parallel_memcpy(self, num_seqs, max_len, src_tbl, trg_tbl, len_tbl):
         self.check(self.L.dyb200_parallel_memcpy(num_seqs, max_len, src_tbl, trg_tbl, len_tbl, self.h))

@@ -235,7 +235,47 @@ int dyb200_lookup_scatter_run(dyb200_ctx* ctx, unsigned n, const unsigned* ids_d
   return DYB200_OK;
 }
 
+// ---- scatter-add for callers that cannot allocate ---------------------------------------------
+// Some hosts of this library may not call cudaMalloc at all: a training loop whose device memory
+// is one pool carved up at start-up (DyNet's own model: four fixed pools per device and
+// EIGEN_NO_MALLOC in the CUDA build), or code running inside a region where an allocation would
+// be an error.  For them the sort/segment tables of the scatter-add live in this fixed array
+// instead of the context's growable arena.  It is part of the library image: every GPU that loads
+// the library holds these 49,408 bytes until the process exits.
+constexpr unsigned kNoAllocMaxIds = DYB200_NOALLOC_MAX_IDS;   // one sort pass
+constexpr size_t kNoAllocBytes = ((((size_t)3 * kNoAllocMaxIds + 8) * sizeof(uint32_t)) + 255) & ~(size_t)255;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+// The array's name is only a host-side handle; kernels need its device address, looked up once
+// per device with that device current.
+constexpr int kMaxDevices = 64;
+static void* g_noalloc_addr[kMaxDevices] = {};
+
 extern "C" {
+
+int dyb200_lookup_accumulate_grads_noalloc(unsigned n, const unsigned* ids_host, const unsigned* ids_dev,
+                                           const float* g, float* all_grads, unsigned dim_size, unsigned vocab,
+                                           dyb200_ctx* ctx) {
+  DYB_CHECK_ARG(ctx, ids_dev != nullptr && g != nullptr && all_grads != nullptr, "accumulate_grads_noalloc: null pointer");
+  DYB_CHECK_ARG(ctx, n <= kNoAllocMaxIds,
+                "accumulate_grads_noalloc: %u ids exceed the fixed scratch (DYB200_NOALLOC_MAX_IDS = %u per call); "
+                "split the call or use dyb200_lookup_accumulate_grads", n, kNoAllocMaxIds);
+  if (ids_host)
+    for (unsigned b = 0; b < n; ++b)
+      DYB_CHECK_ARG(ctx, ids_host[b] < vocab, "Out-of-bounds attempt to access index %u for LookupParameter of size %u", ids_host[b], vocab);
+  DYB_CHECK_ARG(ctx, ctx->device >= 0 && ctx->device < kMaxDevices, "accumulate_grads_noalloc: device id %d not supported", ctx->device);
+  if (n == 0 || dim_size == 0) return DYB200_OK;
+  if (g_noalloc_addr[ctx->device] == nullptr) {   // first call on this device: one-time set-up
+    int cur = -1;
+    DYB_CUDA(ctx, cudaGetDevice(&cur));
+    if (cur != ctx->device) DYB_CUDA(ctx, cudaSetDevice(ctx->device));
+    void* addr = nullptr;
+    DYB_CUDA(ctx, cudaGetSymbolAddress(&addr, g_noalloc_scratch));
+    g_noalloc_addr[ctx->device] = addr;
+  }
+  // Every table entry the kernels read is written by the sort kernel of the same call, so nothing
+  // left over from an earlier call needs clearing.
+  return dyb200_lookup_scatter_run(ctx, n, ids_dev, g, all_grads, dim_size, vocab, g_noalloc_addr[ctx->device]);
+}
 
 int dyb200_lookup_fwd(DYB200_FWD_ARGS) {
   DYB_CHECK_ARG(ctx, nxs == 0 && xs == nullptr, "Failed dimension check in LookupNode::forward (no inputs expected)");

@@ -164,6 +164,24 @@ int dyb200_lookup_accumulate_grads(unsigned n, const unsigned* ids_host, const u
                                    const float* g, float* all_grads, unsigned dim_size,
                                    unsigned vocab, dyb200_ctx* ctx);
 
+/* Allocation-free variant of dyb200_lookup_accumulate_grads (no counterpart in the reference).
+ * For hosts that must not allocate device memory while training -- e.g. a DyNet-style process whose
+ * device memory is a few pools reserved at start-up, or any caller inside a region where cudaMalloc
+ * is forbidden.  Same arguments and same result as dyb200_lookup_accumulate_grads, but the sort /
+ * segment tables live in a fixed array inside the library image instead of the context's growable
+ * arena, and the call performs no cudaMalloc / cudaFree and calls no allocating routine.
+ *  - Limit: n <= DYB200_NOALLOC_MAX_IDS ids per call; a larger n returns DYB200_EINVAL.
+ *  - Cost: every GPU that loads the library keeps 49,408 bytes for that array until exit.
+ *  - The first call on a device looks up the array's device address (a one-time set-up with that
+ *    device made current); make that first call before starting any stream capture.
+ *  - All calls on a device share the array: two calls that can overlap on the GPU (different
+ *    streams, contexts or host threads) race on it.  Calls on one stream are safe, and each call
+ *    rewrites everything it reads, so nothing carries over between calls. */
+#define DYB200_NOALLOC_MAX_IDS 4096
+int dyb200_lookup_accumulate_grads_noalloc(unsigned n, const unsigned* ids_host, const unsigned* ids_dev,
+                                           const float* g, float* all_grads, unsigned dim_size,
+                                           unsigned vocab, dyb200_ctx* ctx);
+
 /* ---- A1-A3 fused LSTM nodes ---- */
 /* VanillaLSTMGates: xs = {x_1..x_k, h_tm1, Wx, Wh, b [, mask_x, mask_h]},
  * attrs = dyb200_lstm_gates_attrs, dynet/nodes-lstm.cc:101-235 / :237-527 */

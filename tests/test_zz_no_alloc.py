@@ -1,0 +1,70 @@
+"""The embedding scatter-add for callers that cannot allocate device memory.
+
+`dyb200_lookup_accumulate_grads_noalloc` keeps its sort/segment tables in a fixed array inside the
+library instead of the context's growable arena, for hosts whose device memory is reserved once at
+start-up (as DyNet's pools are) and that must not hit cudaMalloc in the training loop.  It has to
+give exactly what `dyb200_lookup_accumulate_grads` gives: here both are called through the C ABI on the
+same inputs, twice in a row (the second call reuses the array the first one left behind), and the
+size limit is checked.  This file sorts last so a run that stops at the first failure has already
+covered everything else."""
+import numpy as np
+import pytest
+
+from util import randn, rng, zipf_ids
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(ctx, fn, ids, grad, acc0):
+    import torch
+    acc = torch.from_numpy(acc0).cuda()
+    ids_dev = torch.from_numpy(ids.view(np.int32)).cuda()
+    g = torch.from_numpy(grad).cuda()
+    fn(ids, ids_dev.data_ptr(), g.data_ptr(), acc.data_ptr(), grad.shape[1], acc0.shape[0])
+    torch.cuda.synchronize()
+    return acc.cpu().numpy()
+
+
+def test_noalloc_scatter_add_matches_regular_entry_point():
+    import torch
+    from dynet_b200 import capi
+    ctx = capi.Context(0)
+    r = rng(900)
+    first = None
+    for call, (E, V, n) in enumerate([(512, 5000, 4096), (64, 300, 777)]):   # two calls in a row
+        ids = zipf_ids(r, n, V)
+        grad = randn(r, n, E)
+        acc0 = randn(r, V, E)
+        want = _run(ctx, ctx.lookup_accumulate_grads, ids, grad, acc0)
+        got = _run(ctx, ctx.lookup_accumulate_grads_noalloc, ids, grad, acc0)
+        assert np.array_equal(got, want), "call %d differs from dyb200_lookup_accumulate_grads" % call
+        if first is None:
+            first = (ids, grad, acc0, want)
+    # the first problem again, after the array was reused by a different one
+    ids, grad, acc0, want = first
+    acc = torch.from_numpy(acc0).cuda()
+    ids_dev = torch.from_numpy(ids.view(np.int32)).cuda()
+    g = torch.from_numpy(grad).cuda()
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]      # driver-level free memory: sees any cudaMalloc
+    ctx.lookup_accumulate_grads_noalloc(ids, ids_dev.data_ptr(), g.data_ptr(), acc.data_ptr(), grad.shape[1], acc0.shape[0])
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert np.array_equal(acc.cpu().numpy(), want)
+    assert ctx.device_errors() == 0
+    ctx.close()
+
+
+def test_noalloc_rejects_sizes_beyond_the_fixed_array():
+    import torch
+    from dynet_b200 import capi
+    ctx = capi.Context(0)
+    n = 4097
+    ids = np.zeros(n, np.uint32)
+    ids_dev = torch.zeros(n, dtype=torch.int32, device="cuda")
+    g = torch.zeros(n, 4, device="cuda")
+    acc = torch.zeros(8, 4, device="cuda")
+    with pytest.raises(capi.InvalidArgument, match="DYB200_NOALLOC_MAX_IDS"):
+        ctx.lookup_accumulate_grads_noalloc(ids, ids_dev.data_ptr(), g.data_ptr(), acc.data_ptr(), 4, 8)
+    assert float(acc.abs().max()) == 0.0
+    ctx.close()
