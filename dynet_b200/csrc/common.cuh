@@ -16,8 +16,14 @@ struct dyb200_ctx {
   cudaStream_t stream;
   int sm_count;
   char err[512];
-  void* scratch;         // grow-only arena for node-local temporaries
-  size_t scratch_bytes;
+  // Arena for node-local temporaries: a bump allocator that every public entry point resets
+  // (dyb200_scratch_begin) and nested helpers carve from (dyb200_scratch).  Requests that do not
+  // fit are served from overflow blocks that live until the next reset, when the main block is
+  // re-sized to the high-water mark.
+  void* scratch;
+  size_t scratch_bytes, scratch_off, scratch_peak;
+  void* overflow[64];
+  int n_overflow;
   uint32_t* dev_flags;   // device error word (bit set by kernels, never traps)
   uint64_t launches;     // kernels launched through this context
   // 3xTF32 GEMM state (tensor maps are encoded per call; driver entry point cached)
@@ -48,7 +54,8 @@ struct GemmProfScope {
 #define DYB200_FLAG_WAIT_TIMEOUT 2u  // a bounded mbarrier wait ran out
 
 int dyb200_fail(dyb200_ctx* ctx, int code, const char* fmt, ...);
-int dyb200_scratch(dyb200_ctx* ctx, size_t bytes, void** out);
+int dyb200_scratch_begin(dyb200_ctx* ctx);                      // start of a public entry point: release everything
+int dyb200_scratch(dyb200_ctx* ctx, size_t bytes, void** out);  // 256-byte aligned block, valid until the next begin
 
 #define DYB_CHECK_ARG(ctx, cond, ...)                                    \
   do {                                                                   \

@@ -14,25 +14,50 @@ int dyb200_fail(dyb200_ctx* ctx, int code, const char* fmt, ...) {
   return code;
 }
 
-// Returns a pointer to at least `bytes` of device scratch, 256-byte aligned.  The
-// arena only grows; growing synchronises the stream first so that no kernel in
-// flight still reads the old block.
-int dyb200_scratch(dyb200_ctx* ctx, size_t bytes, void** out) {
-  if (bytes > ctx->scratch_bytes) {
-    size_t want = bytes + (bytes >> 2) + (1u << 20);
+// Called at the start of every public entry point that (directly or through helpers) needs
+// temporaries.  Releases the previous call's blocks; when the previous call overflowed the main
+// block, waits for the stream, frees the overflow blocks and re-sizes the main block to the
+// high-water mark, so the steady state never allocates.
+int dyb200_scratch_begin(dyb200_ctx* ctx) {
+  if (ctx->n_overflow > 0 || ctx->scratch_peak > ctx->scratch_bytes) {
     DYB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    if (ctx->scratch) DYB_CUDA(ctx, cudaFree(ctx->scratch));
-    ctx->scratch = nullptr;
-    ctx->scratch_bytes = 0;
-    cudaError_t e = cudaMalloc(&ctx->scratch, want);
+    for (int k = 0; k < ctx->n_overflow; ++k) cudaFree(ctx->overflow[k]);
+    ctx->n_overflow = 0;
+    if (ctx->scratch_peak > ctx->scratch_bytes) {
+      if (ctx->scratch) DYB_CUDA(ctx, cudaFree(ctx->scratch));
+      ctx->scratch = nullptr;
+      ctx->scratch_bytes = 0;
+      size_t want = ctx->scratch_peak + (ctx->scratch_peak >> 2) + (1u << 20);
+      cudaError_t e = cudaMalloc(&ctx->scratch, want);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        return dyb200_fail(ctx, DYB200_ENOMEM, "scratch arena: cudaMalloc(%zu) failed: %s", want, cudaGetErrorString(e));
+      }
+      ctx->scratch_bytes = want;
+    }
+  }
+  ctx->scratch_off = 0;
+  return DYB200_OK;
+}
+
+int dyb200_scratch(dyb200_ctx* ctx, size_t bytes, void** out) {
+  size_t off = (ctx->scratch_off + 255) & ~(size_t)255;
+  if (bytes == 0) bytes = 256;
+  if (off + bytes <= ctx->scratch_bytes) {
+    *out = (char*)ctx->scratch + off;
+  } else {
+    if (ctx->n_overflow >= 64) return dyb200_fail(ctx, DYB200_ENOMEM, "scratch arena: too many overflow blocks in one call");
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
     if (e != cudaSuccess) {
       cudaGetLastError();
-      return dyb200_fail(ctx, DYB200_ENOMEM, "scratch arena: cudaMalloc(%zu) failed: %s", want,
-                         cudaGetErrorString(e));
+      return dyb200_fail(ctx, DYB200_ENOMEM, "scratch arena: cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
     }
-    ctx->scratch_bytes = want;
+    ctx->overflow[ctx->n_overflow++] = p;
+    *out = p;
   }
-  *out = ctx->scratch;
+  ctx->scratch_off = off + bytes;
+  if (ctx->scratch_off > ctx->scratch_peak) ctx->scratch_peak = ctx->scratch_off;
   return DYB200_OK;
 }
 
@@ -69,6 +94,7 @@ int dyb200_ctx_destroy(dyb200_ctx* ctx) {
   if (!ctx) return DYB200_OK;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  for (int k = 0; k < ctx->n_overflow; ++k) cudaFree(ctx->overflow[k]);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->dev_flags) cudaFree(ctx->dev_flags);
   free(ctx);

@@ -394,10 +394,13 @@ int dyb200_elu_bwd(DYB200_BWD_ARGS) {
 }
 
 int dyb200_cmult_fwd(DYB200_FWD_ARGS) { (void)attrs; (void)aux_mem; return binary_fwd<OP_MUL>(ctx, xs, nxs, fx, "CwiseMultiply"); }
-int dyb200_cmult_bwd(DYB200_BWD_ARGS) { (void)fx; (void)attrs; (void)aux_mem; return binary_bwd<OP_MUL>(ctx, xs, nxs, dEdf, i, dEdxi, "CwiseMultiply"); }
+int dyb200_cmult_bwd(DYB200_BWD_ARGS) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; } (void)fx; (void)attrs; (void)aux_mem; return binary_bwd<OP_MUL>(ctx, xs, nxs, dEdf, i, dEdxi, "CwiseMultiply"); }
 int dyb200_csum_fwd(DYB200_FWD_ARGS) { (void)attrs; (void)aux_mem; return binary_fwd<OP_SUM>(ctx, xs, nxs, fx, "CwiseSum"); }
-int dyb200_csum_bwd(DYB200_BWD_ARGS) { (void)fx; (void)attrs; (void)aux_mem; return binary_bwd<OP_SUM>(ctx, xs, nxs, dEdf, i, dEdxi, "CwiseSum"); }
+int dyb200_csum_bwd(DYB200_BWD_ARGS) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; } (void)fx; (void)attrs; (void)aux_mem; return binary_bwd<OP_SUM>(ctx, xs, nxs, dEdf, i, dEdxi, "CwiseSum"); }
 int dyb200_cdiv_fwd(DYB200_FWD_ARGS) { (void)attrs; (void)aux_mem; return binary_fwd<OP_DIV>(ctx, xs, nxs, fx, "CwiseQuotient"); }
-int dyb200_cdiv_bwd(DYB200_BWD_ARGS) { (void)fx; (void)attrs; (void)aux_mem; return binary_bwd<OP_DIV>(ctx, xs, nxs, dEdf, i, dEdxi, "CwiseQuotient"); }
+int dyb200_cdiv_bwd(DYB200_BWD_ARGS) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; } (void)fx; (void)attrs; (void)aux_mem; return binary_bwd<OP_DIV>(ctx, xs, nxs, dEdf, i, dEdxi, "CwiseQuotient"); }
 
 }  // extern "C"

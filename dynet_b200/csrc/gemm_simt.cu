@@ -87,12 +87,8 @@ int dyb200_gemm_simt(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const 
 int dyb200_gemm_fused(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const GemmPair* pairs, const GemmEpilogue& epi) {
   double flops = 0;
   for (int p = 0; p < npairs; ++p) flops += 2.0 * M * N * pairs[p].K;
-  int handled = 0, rc;
-  {
-    GemmProfScope scope(ctx, flops, 1);
-    rc = dyb200_gemm_tc(ctx, M, N, npairs, pairs, epi, &handled);
-    if (!handled && scope.slot >= 0) { ctx->prof_n--; scope.slot = -1; }  // nothing was launched
-  }
+  int handled = 0;
+  int rc = dyb200_gemm_tc(ctx, M, N, npairs, pairs, epi, &handled);
   if (handled) return rc;
   GemmProfScope scope(ctx, flops, 0);
   return dyb200_gemm_simt(ctx, M, N, npairs, pairs, epi);
@@ -100,6 +96,7 @@ int dyb200_gemm_fused(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const
 
 extern "C" int dyb200_gemm(int transA, int transB, uint32_t M, uint32_t N, uint32_t K, const float* A, uint32_t lda,
                            const float* B, uint32_t ldb, float* C, uint32_t ldc, int accumulate, dyb200_ctx* ctx) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   DYB_CHECK_ARG(ctx, A && B && C, "gemm: null pointer");
   DYB_CHECK_ARG(ctx, lda >= (transA ? K : M) && ldb >= (transB ? N : K) && ldc >= M, "gemm: leading dimension too small");
   GemmPair p{A, lda, transA, B, ldb, transB, K, nullptr, 0, 0};

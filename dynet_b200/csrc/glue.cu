@@ -89,9 +89,11 @@ static int sum_impl(const float* x, size_t n, float* out, int square, int accumu
 }
 
 int dyb200_sum_all(const float* x, size_t n, float* out, int accumulate, dyb200_ctx* ctx) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   return sum_impl(x, n, out, 0, accumulate, ctx);
 }
 int dyb200_squared_norm(const float* x, size_t n, float* out, int accumulate, dyb200_ctx* ctx) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   return sum_impl(x, n, out, 1, accumulate, ctx);
 }
 

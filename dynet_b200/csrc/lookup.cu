@@ -309,6 +309,7 @@ int dyb200_lookup_fwd(DYB200_FWD_ARGS) {
 
 int dyb200_lookup_accumulate_grads(unsigned n, const unsigned* ids_host, const unsigned* ids_dev, const float* g,
                                    float* all_grads, unsigned dim_size, unsigned vocab, dyb200_ctx* ctx) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   DYB_CHECK_ARG(ctx, ids_dev != nullptr && g != nullptr && all_grads != nullptr, "accumulate_grads: null pointer");
   if (ids_host)
     for (unsigned b = 0; b < n; ++b)

@@ -221,6 +221,7 @@ int ch_bwd(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, const dyb200_tenso
 extern "C" {
 
 int dyb200_vanilla_lstm_gates_fwd(DYB200_FWD_ARGS) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   (void)aux_mem;
   const dyb200_lstm_gates_attrs* a = (const dyb200_lstm_gates_attrs*)attrs;
   GatesArgs g;
@@ -252,6 +253,7 @@ int dyb200_vanilla_lstm_gates_fwd(DYB200_FWD_ARGS) {
 }
 
 int dyb200_vanilla_lstm_gates_bwd(DYB200_BWD_ARGS) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   (void)aux_mem;
   const dyb200_lstm_gates_attrs* a = (const dyb200_lstm_gates_attrs*)attrs;
   GatesArgs g;

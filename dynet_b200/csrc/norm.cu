@@ -335,6 +335,7 @@ int ln_check(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, size_t* n, size_
 extern "C" {
 
 int dyb200_weight_norm_fwd(DYB200_FWD_ARGS) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   (void)attrs; (void)aux_mem;
   DYB_CHECK_ARG(ctx, nxs == 2, "Failed input count check in WeightNormalization");
   DYB_CHECK_ARG(ctx, t_size(&xs[1]) == 1, "Size of gain parameter in WeightNormalization should be 1, received %zu", t_size(&xs[1]));
@@ -353,6 +354,7 @@ int dyb200_weight_norm_fwd(DYB200_FWD_ARGS) {
 }
 
 int dyb200_weight_norm_bwd(DYB200_BWD_ARGS) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   (void)attrs; (void)aux_mem;
   DYB_CHECK_ARG(ctx, nxs == 2 && i < 2, "Failed dimension check in WeightNormalization::backward");
   size_t n = t_size(&xs[0]);
@@ -414,6 +416,7 @@ int dyb200_std_dim_fwd(DYB200_FWD_ARGS) {
 }
 
 int dyb200_std_dim_bwd(DYB200_BWD_ARGS) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   (void)aux_mem;
   DYB_CHECK_ARG(ctx, nxs == 1 && i == 0, "Failed dimension check in StdDimension::backward");
   Axes ax; float n; size_t nout;
@@ -447,6 +450,7 @@ int dyb200_layer_norm_fwd(DYB200_FWD_ARGS) {
 }
 
 int dyb200_layer_norm_bwd(DYB200_BWD_ARGS) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   (void)attrs; (void)aux_mem; (void)fx;
   size_t n, ncols; int cached;
   int rc = ln_check(ctx, xs, nxs, &n, &ncols, &cached);
@@ -464,14 +468,11 @@ int dyb200_layer_norm_bwd(DYB200_BWD_ARGS) {
     LnDb f{dEdf->v, n};
     return batch_reduce_add(ctx, f, n, (uint32_t)ncols, dEdxi->v);
   }
-  // i == 1: per-column statistics first (kept in the arena after the reduction's own partials)
-  unsigned gx = (unsigned)((n + 127) / 128);
-  size_t red_bytes = ((size_t)2 * ctx->sm_count / (gx ? gx : 1) + 2) * n * sizeof(float);
-  size_t stats_off = (red_bytes + 255) & ~(size_t)255;
+  // i == 1: per-column statistics first
   void* arena;
-  rc = dyb200_scratch(ctx, stats_off + 2 * ncols * sizeof(float), &arena);
+  rc = dyb200_scratch(ctx, 2 * ncols * sizeof(float), &arena);
   if (rc) return rc;
-  float* stats = (float*)((char*)arena + stats_off);
+  float* stats = (float*)arena;
   k_layer_norm_stats<<<stream_grid(ctx, ncols, 1), kBlock, 0, ctx->stream>>>(xs[0].v, stats, (uint32_t)n, ncols, cached);
   DYB_LAUNCHED(ctx);
   LnDg f{xs[0].v, dEdf->v, stats, n};

@@ -103,6 +103,7 @@ int dyb200_parallel_memcpy(int num_seqs, int max_len, float** src, float** trg, 
 }
 
 int dyb200_parallel_accumulate(int num_seqs, int max_len, float** src, float** trg, size_t* len, dyb200_ctx* ctx) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   (void)max_len;
   DYB_CHECK_ARG(ctx, num_seqs >= 0, "parallel_accumulate: negative slice count");
   if (num_seqs == 0) return DYB200_OK;

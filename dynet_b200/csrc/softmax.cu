@@ -538,6 +538,7 @@ int dyb200_logsumexp_fwd(DYB200_FWD_ARGS) {
 }
 
 int dyb200_logsumexp_bwd(DYB200_BWD_ARGS) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   (void)attrs; (void)aux_mem;
   DYB_CHECK_ARG(ctx, nxs >= 1 && i < (unsigned)nxs, "Failed dimension check in LogSumExp::backward");
   size_t n = t_batch_size(fx), total = n * fx->bd;
