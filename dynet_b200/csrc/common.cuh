@@ -32,17 +32,20 @@ struct dyb200_ctx {
   cudaEvent_t* prof_ev;  // 2 * prof_cap events: start/stop pairs
   double* prof_flops;    // useful FLOPs of each recorded launch
   int* prof_path;        // 1 = tensor-pipe kernel, 0 = CUDA-core kernel
+  uint32_t* prof_shape;  // 4 words per launch: M, N, sum of K, epilogue mode
   int prof_cap, prof_n;
 };
 
 // Brackets a GEMM launch with events when profiling is on (see dyb200_ctx_profile_begin).
 struct GemmProfScope {
   dyb200_ctx* ctx; int slot;
-  GemmProfScope(dyb200_ctx* c, double flops, int path) : ctx(c), slot(-1) {
+  GemmProfScope(dyb200_ctx* c, double flops, int path, uint32_t M = 0, uint32_t N = 0, uint32_t K = 0, uint32_t mode = 0)
+      : ctx(c), slot(-1) {
     if (c->prof_ev && c->prof_n < c->prof_cap) {
       slot = c->prof_n++;
       c->prof_flops[slot] = flops;
       c->prof_path[slot] = path;
+      c->prof_shape[4 * slot] = M; c->prof_shape[4 * slot + 1] = N; c->prof_shape[4 * slot + 2] = K; c->prof_shape[4 * slot + 3] = mode;
       cudaEventRecord(c->prof_ev[2 * slot], c->stream);
     }
   }

@@ -107,7 +107,8 @@ int dyb200_ctx_profile_begin(dyb200_ctx* ctx, int capacity) {
   ctx->prof_ev = (cudaEvent_t*)calloc(2 * (size_t)capacity, sizeof(cudaEvent_t));
   ctx->prof_flops = (double*)calloc(capacity, sizeof(double));
   ctx->prof_path = (int*)calloc(capacity, sizeof(int));
-  if (!ctx->prof_ev || !ctx->prof_flops || !ctx->prof_path) return dyb200_fail(ctx, DYB200_ENOMEM, "profile_begin: host allocation failed");
+  ctx->prof_shape = (uint32_t*)calloc(4 * (size_t)capacity, sizeof(uint32_t));
+  if (!ctx->prof_ev || !ctx->prof_flops || !ctx->prof_path || !ctx->prof_shape) return dyb200_fail(ctx, DYB200_ENOMEM, "profile_begin: host allocation failed");
   for (int k = 0; k < 2 * capacity; ++k) DYB_CUDA(ctx, cudaEventCreate(&ctx->prof_ev[k]));
   ctx->prof_cap = capacity;
   ctx->prof_n = 0;
@@ -119,15 +120,20 @@ int dyb200_ctx_profile_end(dyb200_ctx* ctx, double* ms_out, uint64_t* launches_o
   DYB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   double ms[2] = {0, 0}, fl[2] = {0, 0};
   uint64_t cnt[2] = {0, 0};
+  const char* dump = getenv("DYB200_GEMM_PROFILE_DUMP");   // optional CSV of every recorded launch
+  FILE* df = dump ? fopen(dump, "a") : nullptr;
   for (int k = 0; k < ctx->prof_n; ++k) {
     float t = 0.f;
     DYB_CUDA(ctx, cudaEventElapsedTime(&t, ctx->prof_ev[2 * k], ctx->prof_ev[2 * k + 1]));
     int p = ctx->prof_path[k] ? 1 : 0;
     ms[p] += t; fl[p] += ctx->prof_flops[k]; cnt[p]++;
+    if (df) fprintf(df, "%d,%u,%u,%u,%u,%.6f,%.0f\n", p, ctx->prof_shape[4 * k], ctx->prof_shape[4 * k + 1], ctx->prof_shape[4 * k + 2],
+                    ctx->prof_shape[4 * k + 3], t, ctx->prof_flops[k]);
   }
+  if (df) fclose(df);
   for (int k = 0; k < 2 * ctx->prof_cap; ++k) cudaEventDestroy(ctx->prof_ev[k]);
-  free(ctx->prof_ev); free(ctx->prof_flops); free(ctx->prof_path);
-  ctx->prof_ev = nullptr; ctx->prof_flops = nullptr; ctx->prof_path = nullptr;
+  free(ctx->prof_ev); free(ctx->prof_flops); free(ctx->prof_path); free(ctx->prof_shape);
+  ctx->prof_ev = nullptr; ctx->prof_flops = nullptr; ctx->prof_path = nullptr; ctx->prof_shape = nullptr;
   ctx->prof_cap = ctx->prof_n = 0;
   for (int p = 0; p < 2; ++p) {
     if (ms_out) ms_out[p] = ms[p];

@@ -90,7 +90,7 @@ int dyb200_gemm_fused(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const
   int handled = 0;
   int rc = dyb200_gemm_tc(ctx, M, N, npairs, pairs, epi, &handled);
   if (handled) return rc;
-  GemmProfScope scope(ctx, flops, 0);
+  GemmProfScope scope(ctx, flops, 0, M, N, pairs[0].K + (npairs > 1 ? pairs[1].K : 0), (uint32_t)epi.mode);
   return dyb200_gemm_simt(ctx, M, N, npairs, pairs, epi);
 }
 

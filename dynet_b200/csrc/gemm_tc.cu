@@ -370,7 +370,7 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
   uint32_t kb0 = Kp[0] / BK, kb1 = npairs > 1 ? Kp[1] / BK : 0;
   dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
   {
-    GemmProfScope scope(ctx, flops, 1);   // times the MMA kernel alone; the packing launches show up in the step time
+    GemmProfScope scope(ctx, flops, 1, M, N, kb0 * BK + kb1 * BK, (uint32_t)epi.mode);   // times the MMA kernel alone; the packing launches show up in the step time
     k_gemm_tc<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(tm, M, N, kb0, kb1, epi, ctx->dev_flags);
   }
   DYB_LAUNCHED(ctx);
