@@ -9,7 +9,10 @@
 // applies the dropout mask, so the GEMM kernel itself only moves tiles and issues MMAs:
 //   warp 0     TMA producer: 4 tiles (A_hi, A_lo, B_hi, B_lo) per 32-wide k-block, 3-stage ring
 //   warp 1     allocates TMEM, issues 3 MMAs per 8-wide k-step, commits to the ring's mbarriers
-//   warps 2-5  epilogue: tcgen05.ld of their 32 accumulator lanes, fused epilogue, coalesced stores
+//   warps 2-9  epilogue: tcgen05.ld of their 32 accumulator lanes x 64 columns, fused epilogue,
+//              coalesced stores; read-modify-write epilogues load a whole 32-column chunk first
+// Products with few output tiles are split along K over blockIdx.z; the splits store raw partial
+// tiles and a second kernel adds them in split order and applies the epilogue (deterministic).
 // Every mbarrier wait is bounded; a wait that runs out sets DYB200_FLAG_WAIT_TIMEOUT and the
 // kernel still frees its TMEM and returns.
 #include <cuda.h>
@@ -22,7 +25,7 @@ constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
 constexpr int TILE_BYTES = BM * BK * 4;          // 16 KiB, rows of 128 bytes
 constexpr int STAGE_BYTES = 4 * TILE_BYTES;      // A_hi, A_lo, B_hi, B_lo
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + slack to align the ring to 1 KiB
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;              // TMA warp, MMA warp, 8 epilogue warps
 constexpr uint32_t kWaitLimit = 1u << 20;
 constexpr uint32_t kTmemCols = 128;
 
@@ -92,14 +95,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 }
 
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ TmapPack tm, uint32_t M, uint32_t N,
-                                                         uint32_t kb0, uint32_t kb1, GemmEpilogue epi, uint32_t* flags) {
+                                                         uint32_t kb0, uint32_t kb1, uint32_t kb_per_split,
+                                                         GemmEpilogue epi, uint32_t* flags) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
   __shared__ uint32_t tmem_base_slot;
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-  const uint32_t total = kb0 + kb1;
+  // k-blocks [kb_begin, kb_end) of the concatenated (pair 0, pair 1) range belong to this split
+  const uint32_t kb_begin = blockIdx.z * kb_per_split;
+  const uint32_t kb_end = min(kb0 + kb1, kb_begin + kb_per_split);
+  const uint32_t total = kb_end > kb_begin ? kb_end - kb_begin : 0;
+  if (gridDim.z > 1) epi.C += (size_t)blockIdx.z * epi.ldc * N;   // raw partial tile of this split (mode is EPI_STORE)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -121,7 +129,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
       for (uint32_t it = 0; it < total; ++it) {
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1)) { atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT); break; }
-        const uint32_t pair = it < kb0 ? 0 : 1, kblk = pair ? it - kb0 : it;
+        const uint32_t g = kb_begin + it;
+        const uint32_t pair = g < kb0 ? 0 : 1, kblk = pair ? g - kb0 : g;
         unsigned char* st = ring + (size_t)s * STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);
         tma_load_2d(st, &tm.t[4 * pair + 0], &full_bar[s], (int)(kblk * BK), (int)m0);
@@ -154,35 +163,51 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
       umma_commit(&accum_bar);
     }
   } else {
-    // epilogue warps 2..5 own TMEM lanes 32*(warp % 4) .. +31 (row of the tile = lane of TMEM)
-    const uint32_t quarter = warp & 3;
+    // epilogue warps 2..9: TMEM lanes 32*(warp % 4) .. +31 (row of the tile = lane of TMEM); warps 2-5
+    // take columns 0-63, warps 6-9 columns 64-127
+    const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
     const bool ok = mbar_wait(&accum_bar, 0);
     if (!ok && lane == 0) atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t m = m0 + quarter * 32 + lane;
-    if (ok && total > 0) {
+    if (ok) {
 #pragma unroll 1
-      for (uint32_t c = 0; c < BN / 32; ++c) {
+      for (uint32_t c = 2 * half; c < 2 * half + 2; ++c) {
         float v[32];
-        tmem_ld32(tmem_base + ((quarter * 32) << 16) + c * 32, v);
-        if (m < M) {
-          float bias = 0.f;
-          bool is_tanh = false;
-          if (epi.mode == EPI_GATES) {
-            bias = epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
-            is_tanh = m >= 3 * epi.H;
-          }
+        if (total > 0) tmem_ld32(tmem_base + ((quarter * 32) << 16) + c * 32, v);
+        else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const uint32_t n = n0 + c * 32 + j;
-            if (n < N) {
-              float* dst = epi.C + m + (size_t)epi.ldc * n;
-              float x = v[j];
-              if (epi.mode == EPI_STORE) *dst = x;
-              else if (epi.mode == EPI_ACCUM) *dst += x;
-              else if (epi.mode == EPI_GATES) { x += bias; *dst = is_tanh ? tanhf(x) : sigmoidf_dev(x); }
-              else *dst += x * epi.maskC[m + (epi.maskc_full ? (size_t)epi.maskc_ld * n : 0)];
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        if (m < M) {
+          const uint32_t nb = n0 + c * 32;
+          float* dst = epi.C + m + (size_t)epi.ldc * nb;
+          if (epi.mode == EPI_STORE) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[(size_t)epi.ldc * j] = v[j];
+          } else if (epi.mode == EPI_GATES) {
+            const float bias = epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
+            const bool is_tanh = m >= 3 * epi.H;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float x = v[j] + bias;
+              if (nb + j < N) dst[(size_t)epi.ldc * j] = is_tanh ? tanhf(x) : sigmoidf_dev(x);
             }
+          } else {
+            // read-modify-write: issue all loads of the chunk before the first dependent store
+            float old[32], mk[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) old[j] = nb + j < N ? __ldcg(dst + (size_t)epi.ldc * j) : 0.f;
+            if (epi.mode == EPI_ACCUM_MASK) {
+              const float* mp = epi.maskC + m + (epi.maskc_full ? (size_t)epi.maskc_ld * nb : 0);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) mk[j] = (nb + j < N) ? __ldg(mp + (epi.maskc_full ? (size_t)epi.maskc_ld * j : 0)) : 0.f;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) mk[j] = 1.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[(size_t)epi.ldc * j] = old[j] + v[j] * mk[j];
           }
         }
       }
@@ -193,6 +218,26 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- split-K second stage: C = epilogue(sum_s part[s]) in ascending split order ----------------
+__global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__ part, uint32_t S, uint32_t M, uint32_t N,
+                                                      GemmEpilogue epi) {
+  const size_t MN = (size_t)M * N;
+  for (size_t e = (size_t)blockIdx.x * 256 + threadIdx.x; e < MN; e += (size_t)gridDim.x * 256) {
+    const uint32_t m = (uint32_t)(e % M), n = (uint32_t)(e / M);
+    float acc = 0.f;
+    for (uint32_t s2 = 0; s2 < S; ++s2) acc += part[(size_t)s2 * MN + e];
+    float* dst = epi.C + m + (size_t)epi.ldc * n;
+    if (epi.mode == EPI_STORE) *dst = acc;
+    else if (epi.mode == EPI_ACCUM) *dst += acc;
+    else if (epi.mode == EPI_GATES) {
+      acc += epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
+      *dst = m < 3 * epi.H ? sigmoidf_dev(acc) : tanhf(acc);
+    } else {
+      *dst += acc * epi.maskC[m + (epi.maskc_full ? (size_t)epi.maskc_ld * n : 0)];
+    }
   }
 }
 
@@ -368,11 +413,37 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
   }
   if (npairs == 1) for (int k = 0; k < 4; ++k) tm.t[4 + k] = tm.t[k];
   uint32_t kb0 = Kp[0] / BK, kb1 = npairs > 1 ? Kp[1] / BK : 0;
-  dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
-  {
-    GemmProfScope scope(ctx, flops, 1, M, N, kb0 * BK + kb1 * BK, (uint32_t)epi.mode);   // times the MMA kernel alone; the packing launches show up in the step time
-    k_gemm_tc<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(tm, M, N, kb0, kb1, epi, ctx->dev_flags);
+  const uint32_t kb_total = kb0 + kb1;
+  dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN, 1);
+  // Split K when the output has too few tiles to occupy the SMs (e.g. dx = W^T dgate: 16-32 tiles, K = 4096).
+  const uint32_t tiles = grid.x * grid.y;
+  uint32_t S = 1;
+  if (tiles * 2 <= (uint32_t)ctx->sm_count) {
+    S = (uint32_t)ctx->sm_count / tiles;
+    if (S > kb_total / 8) S = kb_total / 8;   // at least 8 k-blocks per split
+    if (S < 1) S = 1;
   }
-  DYB_LAUNCHED(ctx);
+  uint32_t kb_per_split = (kb_total + S - 1) / S;
+  S = (kb_total + kb_per_split - 1) / kb_per_split;
+  GemmEpilogue kepi = epi;
+  float* part = nullptr;
+  if (S > 1) {
+    void* pw;
+    rc = dyb200_scratch(ctx, (size_t)S * M * N * sizeof(float), &pw);
+    if (rc) return rc;
+    part = (float*)pw;
+    kepi = GemmEpilogue{EPI_STORE, part, M, nullptr, 0, 0.f, nullptr, 0, 0};
+    grid.z = S;
+  }
+  {
+    // times the MMA kernel (and the split-K reduction); the packing launches show up in the step time
+    GemmProfScope scope(ctx, flops, 1, M, N, kb_total * BK, (uint32_t)epi.mode);
+    k_gemm_tc<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
+    DYB_LAUNCHED(ctx);
+    if (S > 1) {
+      k_splitk_reduce<<<stream_grid(ctx, (size_t)M * N, 256 * 4), 256, 0, ctx->stream>>>(part, S, M, N, epi);
+      DYB_LAUNCHED(ctx);
+    }
+  }
   return DYB200_OK;
 }
