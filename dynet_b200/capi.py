@@ -212,9 +212,12 @@ class Context:
         self.check(f(a, n, C.byref(fx), C.byref(dEdf), i, C.byref(dEdxi),
                      C.cast(C.byref(attrs), C.c_void_p) if attrs is not None else None, aux, self.h))
 
-    def lookup_accumulate_grads(self, ids_host, ids_dev_ptr, g_ptr, all_grads_ptr, dim_size, vocab):
-        n = len(ids_host)
-        arr = (C.c_uint32 * n)(*[int(i) for i in ids_host]) if n else None
+    def lookup_accumulate_grads(self, ids_host, ids_dev_ptr, g_ptr, all_grads_ptr, dim_size, vocab, n=None):
+        """ids_host may be empty with n given: the ids are then only read on the device."""
+        arr = None
+        if n is None:
+            n = len(ids_host)
+            arr = (C.c_uint32 * n)(*[int(i) for i in ids_host]) if n else None
         self.check(self.L.dyb200_lookup_accumulate_grads(n, arr, ids_dev_ptr, g_ptr, all_grads_ptr, dim_size, vocab, self.h))
 
     def lookup_accumulate_grads_noalloc(self, ids_host, ids_dev_ptr, g_ptr, all_grads_ptr, dim_size, vocab):

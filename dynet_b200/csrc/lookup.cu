@@ -8,9 +8,11 @@
 // multiples fall back to plain loads.
 //
 // Scatter-add: (id, position) pairs are sorted by id inside one CTA (bitonic, <= 4096 pairs
-// per pass), equal ids form a segment, and one warp per (segment, 128-float column slice)
-// adds the segment's rows to the table row in ascending position -- the same order as the
-// reference's CPU loop (dynet/model.cc:735-741), with no atomics.
+// per pass).  The sorted list is cut into chunks of 32 positions; one warp per (chunk, 128-float
+// column slice) adds the rows of each id in ascending position -- the order of the reference's CPU
+// loop (dynet/model.cc:735-741) -- straight into the table row when the id's run lies inside the
+// chunk, or into a per-chunk partial when a frequent id (Zipf head) spans chunks; a second pass
+// adds those partials in chunk order.  No atomics, a fixed summation tree, balanced work.
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -210,7 +212,140 @@ __global__ void __launch_bounds__(256) k_segment_add(const float* __restrict__ g
   }
 }
 
+
+// ---- scatter-add, chunked (load-balanced) variant ------------------------------------------------
+constexpr uint32_t kChunk = 32;
+
+__global__ void __launch_bounds__(kSortThreads) k_sort_ids(const uint32_t* __restrict__ ids, uint32_t n, uint32_t base,
+                                                          uint32_t vocab, uint32_t* __restrict__ pos_sorted,
+                                                          uint32_t* __restrict__ id_at, uint32_t* flags) {
+  __shared__ unsigned long long keys[kSortMax];
+  uint32_t npow = 1;
+  while (npow < n) npow <<= 1;
+  for (uint32_t k = threadIdx.x; k < npow; k += kSortThreads) {
+    unsigned long long key = ~0ull;
+    if (k < n) {
+      uint32_t id = ids[base + k];
+      if (id >= vocab) { atomicOr(flags, DYB200_FLAG_BAD_INDEX); id = vocab - 1; }
+      key = ((unsigned long long)id << 32) | (base + k);
+    }
+    keys[k] = key;
+  }
+  __syncthreads();
+  bitonic_sort_keys(keys, npow);
+  for (uint32_t k = threadIdx.x; k < n; k += kSortThreads) {
+    pos_sorted[k] = (uint32_t)keys[k];
+    id_at[k] = (uint32_t)(keys[k] >> 32);
+  }
+}
+
+__device__ __forceinline__ void add4(float4& a, const float4& b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+
+// Pass A: one warp per (chunk, slice).  A run that starts in the chunk begins from the table row
+// (so a run that also ends here reproduces the sequential CPU sum exactly); a run that started in an
+// earlier chunk begins from zero and goes to head[chunk]; a run that continues goes to tail[chunk].
+__global__ void __launch_bounds__(256) k_chunk_add(const float* __restrict__ g, float* __restrict__ all_grads, uint32_t E,
+                                                  const uint32_t* __restrict__ pos_sorted, const uint32_t* __restrict__ id_at,
+                                                  uint32_t n, uint32_t slices, float* __restrict__ head, float* __restrict__ tail) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t nchunks = (n + kChunk - 1) / kChunk;
+  const size_t work = (size_t)nchunks * slices;
+  for (size_t w = (size_t)blockIdx.x * 8 + warp; w < work; w += (size_t)gridDim.x * 8) {
+    const uint32_t c = (uint32_t)(w / slices), sl = (uint32_t)(w % slices);
+    const uint32_t k0 = c * kChunk, k1 = min(n, k0 + kChunk);
+    const uint32_t col = sl * 128 + lane * 4;
+    const bool live = col < E;   // lanes past the row end still take part in the shuffles
+    const uint32_t my_id = k0 + lane < k1 ? id_at[k0 + lane] : 0xffffffffu;
+    const uint32_t my_pos = k0 + lane < k1 ? pos_sorted[k0 + lane] : 0;
+    uint32_t cur = __shfl_sync(0xffffffffu, my_id, 0);
+    bool started_before = k0 > 0 && id_at[k0 - 1] == cur;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 acc = (started_before || !live) ? zero4 : ld4(all_grads + (size_t)cur * E + col);
+    float* hslot = head + ((size_t)c * slices + sl) * 128 + lane * 4;
+    float* tslot = tail + ((size_t)c * slices + sl) * 128 + lane * 4;
+    for (uint32_t j0 = 0; j0 < k1 - k0; j0 += 8) {
+      // the gradient rows of the next 8 positions are requested together; the adds stay in order
+      float4 rows[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint32_t pos = __shfl_sync(0xffffffffu, my_pos, (j0 + u) & 31);
+        rows[u] = (live && j0 + u < k1 - k0) ? ld4_stream(g + (size_t)pos * E + col) : zero4;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint32_t id = __shfl_sync(0xffffffffu, my_id, (j0 + u) & 31);
+        if (j0 + u < k1 - k0) {
+          if (id != cur) {   // the run of `cur` ends inside this chunk
+            if (live) {
+              if (started_before) st4(hslot, acc);
+              else st4(all_grads + (size_t)cur * E + col, acc);
+            }
+            cur = id;
+            started_before = false;
+            acc = live ? ld4(all_grads + (size_t)cur * E + col) : zero4;
+          }
+          add4(acc, rows[u]);
+        }
+      }
+    }
+    const bool continues = k1 < n && id_at[k1] == cur;
+    if (live) {
+      if (started_before) st4(hslot, acc);                           // middle or last piece
+      else if (continues) st4(tslot, acc);                           // first piece (holds the row)
+      else st4(all_grads + (size_t)cur * E + col, acc);              // whole run
+    }
+  }
+}
+// Pass B: the chunk in which a multi-chunk run starts adds the later pieces in chunk order and writes the row.
+__global__ void __launch_bounds__(256) k_chunk_combine(float* __restrict__ all_grads, uint32_t E, const uint32_t* __restrict__ id_at,
+                                                      uint32_t n, uint32_t slices, const float* __restrict__ head,
+                                                      const float* __restrict__ tail) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t nchunks = (n + kChunk - 1) / kChunk;
+  const size_t work = (size_t)nchunks * slices;
+  for (size_t w = (size_t)blockIdx.x * 8 + warp; w < work; w += (size_t)gridDim.x * 8) {
+    const uint32_t c = (uint32_t)(w / slices), sl = (uint32_t)(w % slices);
+    const uint32_t k0 = c * kChunk, k1 = min(n, k0 + kChunk);
+    const uint32_t col = sl * 128 + lane * 4;
+    if (col >= E || k1 >= n) continue;
+    const uint32_t id = id_at[k1 - 1];
+    if (id_at[k1] != id) continue;                         // last run of the chunk does not continue
+    if (id_at[k0] == id && k0 > 0 && id_at[k0 - 1] == id) continue;   // it started earlier: not the owner
+    float4 acc = ld4(tail + ((size_t)c * slices + sl) * 128 + lane * 4);
+    for (uint32_t c2 = c + 1; c2 < nchunks && id_at[c2 * kChunk] == id; ++c2)
+      add4(acc, ld4(head + ((size_t)c2 * slices + sl) * 128 + lane * 4));
+    st4(all_grads + (size_t)id * E + col, acc);
+  }
+}
+
 }  // namespace
+
+// Load-balanced path (rows that are multiples of 4 floats): scratch holds pos_sorted[np], id_at[np] and two
+// partial buffers of nchunks * slices * 128 floats.
+static size_t chunked_scratch_bytes(uint32_t np, uint32_t E) {
+  uint32_t nchunks = (np + kChunk - 1) / kChunk, slices = (E + 127) / 128;
+  return ((size_t)2 * np * sizeof(uint32_t) + 512) + (size_t)2 * nchunks * slices * 128 * sizeof(float) + 512;
+}
+static int scatter_run_chunked(dyb200_ctx* ctx, unsigned n, const unsigned* ids_dev, const float* g, float* all_grads,
+                               unsigned E, unsigned vocab, void* scratch) {
+  const uint32_t slices = (E + 127) / 128;
+  for (uint32_t base = 0; base < n; base += kSortMax) {
+    uint32_t np = n - base < (uint32_t)kSortMax ? n - base : (uint32_t)kSortMax;
+    uint32_t nchunks = (np + kChunk - 1) / kChunk;
+    uint32_t* pos_sorted = (uint32_t*)scratch;
+    uint32_t* id_at = pos_sorted + np;
+    float* head = (float*)(((uintptr_t)(id_at + np) + 255) & ~(uintptr_t)255);
+    float* tail = head + (size_t)nchunks * slices * 128;
+    k_sort_ids<<<1, kSortThreads, 0, ctx->stream>>>(ids_dev, np, base, vocab, pos_sorted, id_at, ctx->dev_flags);
+    DYB_LAUNCHED(ctx);
+    size_t work = (size_t)nchunks * slices;
+    k_chunk_add<<<stream_grid(ctx, work, 8), 256, 0, ctx->stream>>>(g, all_grads, E, pos_sorted, id_at, np, slices, head, tail);
+    DYB_LAUNCHED(ctx);
+    k_chunk_combine<<<stream_grid(ctx, work, 8), 256, 0, ctx->stream>>>(all_grads, E, id_at, np, slices, head, tail);
+    DYB_LAUNCHED(ctx);
+  }
+  return DYB200_OK;
+}
 
 // Runs the sort + segmented-add passes using `scratch`, which must hold at least
 // dyb200_lookup_scatter_scratch_bytes(min(n, kSortMax)) bytes.
@@ -317,6 +452,11 @@ int dyb200_lookup_accumulate_grads(unsigned n, const unsigned* ids_host, const u
   if (n == 0 || dim_size == 0) return DYB200_OK;
   uint32_t np = n < (unsigned)kSortMax ? n : (unsigned)kSortMax;
   void* scratch;
+  if (dim_size % 4 == 0 && aligned16(g) && aligned16(all_grads)) {
+    int rc = dyb200_scratch(ctx, chunked_scratch_bytes(np, dim_size), &scratch);
+    if (rc) return rc;
+    return scatter_run_chunked(ctx, n, ids_dev, g, all_grads, dim_size, vocab, scratch);
+  }
   int rc = dyb200_scratch(ctx, dyb200_lookup_scatter_scratch_bytes(np), &scratch);
   if (rc) return rc;
   return dyb200_lookup_scatter_run(ctx, n, ids_dev, g, all_grads, dim_size, vocab, scratch);

@@ -55,10 +55,22 @@ __global__ void __launch_bounds__(kBlock) k_weight_norm_apply(const float* __res
   __shared__ float red[32];
   float ss, dot;
   reduce_partials(partial, np, red, ss, dot);
-  const float nrm = sqrtf(ss), g = gptr[0], t2 = dot / ss;
-  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
-    if (MODE == 0) out[i] = (w[i] / nrm) * g;
-    else out[i] += (dy[i] / nrm) * g - y[i] * t2;
+  const float nrm = sqrtf(ss), g = gptr[0], t2 = dot / ss, sc = g / nrm;
+  const bool vec = aligned16(w) && aligned16(out) && (MODE == 0 || (aligned16(y) && aligned16(dy)));
+  const size_t n4 = vec ? n / 4 : 0;
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n4; i += (size_t)gridDim.x * kBlock) {
+    if (MODE == 0) {
+      float4 a = ld4(w + 4 * i);
+      st4_stream(out + 4 * i, make_float4(a.x * sc, a.y * sc, a.z * sc, a.w * sc));
+    } else {
+      float4 d = ld4_stream(dy + 4 * i), yy = ld4_stream(y + 4 * i), o = ld4_stream(out + 4 * i);
+      st4_stream(out + 4 * i, make_float4(o.x + (d.x * sc - yy.x * t2), o.y + (d.y * sc - yy.y * t2),
+                                          o.z + (d.z * sc - yy.z * t2), o.w + (d.w * sc - yy.w * t2)));
+    }
+  }
+  for (size_t i = 4 * n4 + (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
+    if (MODE == 0) out[i] = w[i] * sc;
+    else out[i] += dy[i] * sc - y[i] * t2;
   }
 }
 __global__ void __launch_bounds__(kBlock) k_weight_norm_dg(const float* __restrict__ partial, int np, float* __restrict__ dg) {
@@ -190,7 +202,7 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_fwd(const float* __restri
     L.xc = x + c * n; L.n = n; L.cached = cached;
     float mean, sigma;
     ln_stats(L, red, mean, sigma);
-    const float neg = -mean, s2 = sigma + 1e-8f;
+    const float neg = -mean, inv = 1.f / (sigma + 1e-8f);   // one reciprocal per column instead of n divisions
     float* yc = y + c * n;
     if (cached) {
       const uint32_t n4 = n / 4;
@@ -199,13 +211,13 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_fwd(const float* __restri
         uint32_t i = threadIdx.x + kBlock * k;
         if (i < n4) {
           float4 gg = ld4(g + 4 * i), bb = ld4(b + 4 * i), v = L.v[k];
-          float4 r = make_float4(gg.x * ((v.x + neg) / s2) + bb.x, gg.y * ((v.y + neg) / s2) + bb.y,
-                                 gg.z * ((v.z + neg) / s2) + bb.z, gg.w * ((v.w + neg) / s2) + bb.w);
+          float4 r = make_float4(gg.x * ((v.x + neg) * inv) + bb.x, gg.y * ((v.y + neg) * inv) + bb.y,
+                                 gg.z * ((v.z + neg) * inv) + bb.z, gg.w * ((v.w + neg) * inv) + bb.w);
           st4_stream(yc + 4 * i, r);
         }
       }
     } else {
-      for (uint32_t i = threadIdx.x; i < n; i += kBlock) yc[i] = g[i] * ((L.xc[i] + neg) / s2) + b[i];
+      for (uint32_t i = threadIdx.x; i < n; i += kBlock) yc[i] = g[i] * ((L.xc[i] + neg) * inv) + b[i];
     }
     __syncthreads();
   }
@@ -221,11 +233,11 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_bwd_x(const float* __rest
     L.xc = x + c * n; L.n = n; L.cached = cached;
     float mean, sigma;
     ln_stats(L, red, mean, sigma);
-    const float neg = -mean, s2 = sigma + 1e-8f, ssq = s2 * s2;
+    const float neg = -mean, s2 = sigma + 1e-8f, inv = 1.f / s2;
     const float* dc = dy + c * n;
     float* oc = dx + c * n;
     float4 dq[kVec];
-    float A = 0.f, Bs = 0.f;  // A = sum dq/ssq*xc ; Bs = sum dq/s2
+    float A = 0.f, Bs = 0.f;  // A = sum dq*xc (divided by s2^2 once) ; Bs = sum dq (divided by s2 once)
     if (cached) {
       const uint32_t n4 = n / 4;
 #pragma unroll
@@ -234,19 +246,19 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_bwd_x(const float* __rest
         if (i < n4) {
           float4 d = ld4_stream(dc + 4 * i), gg = ld4(g + 4 * i), v = L.v[k];
           dq[k] = make_float4(d.x * gg.x, d.y * gg.y, d.z * gg.z, d.w * gg.w);
-          A += (dq[k].x / ssq * (v.x + neg) + dq[k].y / ssq * (v.y + neg)) + (dq[k].z / ssq * (v.z + neg) + dq[k].w / ssq * (v.w + neg));
-          Bs += (dq[k].x / s2 + dq[k].y / s2) + (dq[k].z / s2 + dq[k].w / s2);
+          A += (dq[k].x * (v.x + neg) + dq[k].y * (v.y + neg)) + (dq[k].z * (v.z + neg) + dq[k].w * (v.w + neg));
+          Bs += (dq[k].x + dq[k].y) + (dq[k].z + dq[k].w);
         }
       }
     } else {
       for (uint32_t i = threadIdx.x; i < n; i += kBlock) {
         float q = dc[i] * g[i];
-        A += q / ssq * (L.xc[i] + neg);
-        Bs += q / s2;
+        A += q * (L.xc[i] + neg);
+        Bs += q;
       }
     }
-    A = block_sum(A, red);
-    Bs = block_sum(Bs, red);
+    A = block_sum(A, red) * inv * inv;
+    Bs = block_sum(Bs, red) * inv;
     const float sb = (-A) / (2.f * sigma), dmu_n = (-Bs) / fn, two_n = 2.f / fn;
     if (cached) {
       const uint32_t n4 = n / 4;
@@ -255,16 +267,16 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_bwd_x(const float* __rest
         uint32_t i = threadIdx.x + kBlock * k;
         if (i < n4) {
           float4 o = ld4_stream(oc + 4 * i), v = L.v[k];
-          o.x = ((o.x + two_n * (v.x - mean) * sb) + dq[k].x / s2) + dmu_n;
-          o.y = ((o.y + two_n * (v.y - mean) * sb) + dq[k].y / s2) + dmu_n;
-          o.z = ((o.z + two_n * (v.z - mean) * sb) + dq[k].z / s2) + dmu_n;
-          o.w = ((o.w + two_n * (v.w - mean) * sb) + dq[k].w / s2) + dmu_n;
+          o.x = ((o.x + two_n * (v.x - mean) * sb) + dq[k].x * inv) + dmu_n;
+          o.y = ((o.y + two_n * (v.y - mean) * sb) + dq[k].y * inv) + dmu_n;
+          o.z = ((o.z + two_n * (v.z - mean) * sb) + dq[k].z * inv) + dmu_n;
+          o.w = ((o.w + two_n * (v.w - mean) * sb) + dq[k].w * inv) + dmu_n;
           st4_stream(oc + 4 * i, o);
         }
       }
     } else {
       for (uint32_t i = threadIdx.x; i < n; i += kBlock)
-        oc[i] = ((oc[i] + two_n * (L.xc[i] - mean) * sb) + (dc[i] * g[i]) / s2) + dmu_n;
+        oc[i] = ((oc[i] + two_n * (L.xc[i] - mean) * sb) + (dc[i] * g[i]) * inv) + dmu_n;
     }
     __syncthreads();
   }

@@ -132,9 +132,23 @@ __global__ void __launch_bounds__(kBlock) k_col_block_vec(ColArgs a) {
 }
 
 // ---- CTA per column, any length: streaming online (max, sum) -------------------
+// The running sum is kept in base 2 relative to the running max: s = sum 2^((x - m) * log2(e)).
+// One ex2.approx per element (relative error ~2^-22 plus |x - m| * 2^-24 from the scaled argument),
+// one rescale test per 16 elements; four 128-bit loads are in flight per thread.
+constexpr float kLog2e = 1.4426950408889634f;
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void online_add(float& m, float& s, float v) {
-  if (v > m) { s = s * expf(m - v) + 1.f; m = v; }
-  else s += expf(v - m);
+  if (v > m) { s = s * ex2_approx((m - v) * kLog2e) + 1.f; m = v; }
+  else s += ex2_approx((v - m) * kLog2e);
+}
+__device__ __forceinline__ float max4(float4 v) { return fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)); }
+__device__ __forceinline__ float sumexp4(float4 v, float ml) {
+  return (ex2_approx(fmaf(v.x, kLog2e, -ml)) + ex2_approx(fmaf(v.y, kLog2e, -ml))) +
+         (ex2_approx(fmaf(v.z, kLog2e, -ml)) + ex2_approx(fmaf(v.w, kLog2e, -ml)));
 }
 template <int MODE>
 __global__ void __launch_bounds__(kBlock) k_col_stream(ColArgs a) {
@@ -148,16 +162,25 @@ __global__ void __launch_bounds__(kBlock) k_col_stream(ColArgs a) {
     uint32_t body4 = (a.rows - head) / 4;
     if (threadIdx.x < head) online_add(m, s, xc[threadIdx.x]);
     const float* xb = xc + head;
-    for (uint32_t i = threadIdx.x; i < body4; i += kBlock) {
+    uint32_t i = threadIdx.x;
+    for (; i + 3 * kBlock < body4; i += 4 * kBlock) {
+      float4 v0 = ld4_stream(xb + 4 * i), v1 = ld4_stream(xb + 4 * (i + kBlock));
+      float4 v2 = ld4_stream(xb + 4 * (i + 2 * kBlock)), v3 = ld4_stream(xb + 4 * (i + 3 * kBlock));
+      float vm = fmaxf(fmaxf(max4(v0), max4(v1)), fmaxf(max4(v2), max4(v3)));
+      if (vm > m) { s *= ex2_approx((m - vm) * kLog2e); m = vm; }
+      const float ml = m * kLog2e;
+      s += (sumexp4(v0, ml) + sumexp4(v1, ml)) + (sumexp4(v2, ml) + sumexp4(v3, ml));
+    }
+    for (; i < body4; i += kBlock) {
       float4 v = ld4_stream(xb + 4 * i);
-      float vm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-      if (vm > m) { s *= expf(m - vm); m = vm; }
-      s += (expf(v.x - m) + expf(v.y - m)) + (expf(v.z - m) + expf(v.w - m));
+      float vm = max4(v);
+      if (vm > m) { s *= ex2_approx((m - vm) * kLog2e); m = vm; }
+      s += sumexp4(v, m * kLog2e);
     }
     uint32_t t = head + 4 * body4 + threadIdx.x;
     if (t < a.rows) online_add(m, s, xc[t]);
     float mx = block_max(m, red);
-    float sc = (m == -INFINITY) ? 0.f : s * expf(m - mx);
+    float sc = (m == -INFINITY) ? 0.f : s * ex2_approx((m - mx) * kLog2e);
     float tot = block_sum(sc, red);
     finish_column<MODE>(a, c, mx, tot, threadIdx.x == 0);
     if (MODE == M_SOFTMAX || MODE == M_LOGSOFTMAX) {
@@ -281,8 +304,9 @@ __global__ void __launch_bounds__(kBlock) k_expsub_bwd(const float* __restrict__
     if (vec) {
       for (uint32_t r = r0 + 4 * threadIdx.x; r < r1; r += 4 * kBlock) {
         float4 v = ld4_stream(xc + r), o = ld4_stream(oc + r);
-        float4 res = make_float4(o.x + expf(v.x - zc) * dc, o.y + expf(v.y - zc) * dc, o.z + expf(v.z - zc) * dc,
-                                 o.w + expf(v.w - zc) * dc);
+        const float zl = zc * kLog2e;
+        float4 res = make_float4(o.x + ex2_approx(fmaf(v.x, kLog2e, -zl)) * dc, o.y + ex2_approx(fmaf(v.y, kLog2e, -zl)) * dc,
+                                 o.z + ex2_approx(fmaf(v.z, kLog2e, -zl)) * dc, o.w + ex2_approx(fmaf(v.w, kLog2e, -zl)) * dc);
         if (pick - r < 4u) {
           uint32_t k = pick - r;
           if (k == 0) res.x -= dc; else if (k == 1) res.y -= dc; else if (k == 2) res.z -= dc; else res.w -= dc;

@@ -11,6 +11,21 @@ constexpr int kSortThreads = 1024;
 // keys[0..npow) hold the n keys followed by ~0 padding; must be called by all kSortThreads
 // threads.  Outputs: payload_sorted[k] = low `shift` bits of the k-th key (truncated to 32 bits),
 // group_sorted[u] = low 32 bits of the group of segment u, seg_start[0..U] (seg_start[U] = n), *nseg = U.
+__device__ __forceinline__ void bitonic_sort_keys(unsigned long long* keys, uint32_t npow) {
+  for (uint32_t size = 2; size <= npow; size <<= 1) {
+    for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+      for (uint32_t t = threadIdx.x; t < npow / 2; t += kSortThreads) {
+        uint32_t lo = 2 * t - (t & (stride - 1));
+        uint32_t hi = lo + stride;
+        bool up = (lo & size) == 0;
+        unsigned long long a = keys[lo], b = keys[hi];
+        if ((a > b) == up) { keys[lo] = b; keys[hi] = a; }
+      }
+      __syncthreads();
+    }
+  }
+}
+
 __device__ __forceinline__ void sort_and_segment(unsigned long long* keys, uint32_t* scan, uint32_t n, uint32_t npow,
                                                  int shift, uint32_t* __restrict__ payload_sorted,
                                                  uint32_t* __restrict__ group_sorted, uint32_t* __restrict__ seg_start,

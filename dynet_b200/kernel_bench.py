@@ -1,0 +1,222 @@
+"""Per-kernel timing of the memory-bound nodes at the sizes of BASELINE configs 2 and 3.
+
+    python -m dynet_b200.kernel_bench [--only NAME] [--iters 20] [--small]
+
+Each case is called through the C ABI `iters` times on ROTATING buffer sets whose total footprint
+exceeds the 126 MB L2 (so every call reads its inputs from HBM).  The calls are captured once into a
+CUDA graph on the library's stream and the graph launch is timed with CUDA events after warm-up, so
+the figure is device time of the kernels back to back, free of per-call host overhead.  Output: one JSON line per case with the algorithmic bytes of one call,
+the average duration, achieved GB/s and its fraction of the measured copy bandwidth (MEASURED_PEAKS.json,
+fallback 6650 GB/s) and of the nominal 8000 GB/s.  `--small` shrinks every case to a few hundred MB total so
+that a profiler capture of one launch ends quickly.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+
+import numpy as np
+
+from . import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+L2_BYTES = 126 * 1024 * 1024
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class Case:
+    def __init__(self, name, nbytes, make, call, footprint):
+        self.name, self.nbytes, self.make, self.call, self.footprint = name, nbytes, make, call, footprint
+
+
+def T(t, dims, bd):
+    return capi.DyTensor.of(t.data_ptr(), dims, bd)
+
+
+def build_cases(torch, ctx, small):
+    cases = []
+    dev = "cuda"
+    R, Ccols = (1024, 4096)              # config 3: [1024, 4096] tensors; row-wise ops see Dim({4096}, 1024)
+    n = R * Ccols
+    S = 4 * n
+
+    def unary(name, attrs=None):
+        def make():
+            return dict(x=torch.randn(R, Ccols, device=dev), y=torch.empty(R, Ccols, device=dev),
+                        dy=torch.randn(R, Ccols, device=dev), dx=torch.zeros(R, Ccols, device=dev))
+        def fwd(b):
+            ctx.fwd(name, [T(b["x"], [Ccols], R)], T(b["y"], [Ccols], R), attrs)
+        def bwd(b):
+            ctx.bwd(name, [T(b["x"], [Ccols], R)], T(b["y"], [Ccols], R), T(b["dy"], [Ccols], R), 0, T(b["dx"], [Ccols], R), attrs)
+        cases.append(Case(name + "_fwd", 2 * S, make, fwd, 4 * S))
+        cases.append(Case(name + "_bwd", 4 * S, make, bwd, 4 * S))
+
+    unary("tanh"); unary("logistic"); unary("rectify"); unary("elu", capi.EluAttrs(1.0, 1.0))
+
+    # the same kernels on 8x larger tensors ([8192, 4096], 134 MB each): launch ramp-up and tail no longer dominate
+    RL = 8 * R
+    SLg = 4 * RL * Ccols
+    def mk_large():
+        return dict(x=torch.randn(RL, Ccols, device=dev), y=torch.empty(RL, Ccols, device=dev))
+    cases.append(Case("tanh_fwd_8192x4096", 2 * SLg, mk_large,
+                      lambda b: ctx.fwd("tanh", [T(b["x"], [Ccols], RL)], T(b["y"], [Ccols], RL)), 2 * SLg))
+    cases.append(Case("softmax_rows4096_fwd_8192x4096", 2 * SLg, mk_large,
+                      lambda b: ctx.fwd("softmax", [T(b["x"], [Ccols], RL)], T(b["y"], [Ccols], RL), capi.DimAttrs(0)), 2 * SLg))
+    def mk_large_ln():
+        d = mk_large()
+        d.update(g=torch.rand(Ccols, device=dev) + 0.5, b=torch.randn(Ccols, device=dev) * 0.1)
+        return d
+    cases.append(Case("layer_norm_fwd_8192x4096", 2 * SLg, mk_large_ln,
+                      lambda b: ctx.fwd("layer_norm", [T(b["x"], [Ccols], RL), T(b["g"], [Ccols], 1), T(b["b"], [Ccols], 1)],
+                                        T(b["y"], [Ccols], RL)), 2 * SLg))
+
+    def mk_cmult():
+        return dict(a=torch.randn(R, Ccols, device=dev), b=torch.randn(R, Ccols, device=dev), y=torch.empty(R, Ccols, device=dev),
+                    dy=torch.randn(R, Ccols, device=dev), da=torch.zeros(R, Ccols, device=dev))
+    cases.append(Case("cmult_fwd", 3 * S, mk_cmult,
+                      lambda b: ctx.fwd("cmult", [T(b["a"], [Ccols], R), T(b["b"], [Ccols], R)], T(b["y"], [Ccols], R)), 5 * S))
+    cases.append(Case("cmult_bwd_arg0", 4 * S, mk_cmult,
+                      lambda b: ctx.bwd("cmult", [T(b["a"], [Ccols], R), T(b["b"], [Ccols], R)], T(b["y"], [Ccols], R),
+                                        T(b["dy"], [Ccols], R), 0, T(b["da"], [Ccols], R)), 5 * S))
+
+    sm0 = capi.DimAttrs(0)
+    sm1 = capi.DimAttrs(1)
+    def mk_sm():
+        return dict(x=torch.randn(R, Ccols, device=dev), y=torch.empty(R, Ccols, device=dev),
+                    dy=torch.randn(R, Ccols, device=dev), dx=torch.zeros(R, Ccols, device=dev))
+    cases.append(Case("softmax_rows4096_fwd", 2 * S, mk_sm,
+                      lambda b: ctx.fwd("softmax", [T(b["x"], [Ccols], R)], T(b["y"], [Ccols], R), sm0), 4 * S))
+    cases.append(Case("softmax_rows4096_bwd", 4 * S, mk_sm,
+                      lambda b: ctx.bwd("softmax", [T(b["x"], [Ccols], R)], T(b["y"], [Ccols], R), T(b["dy"], [Ccols], R), 0,
+                                        T(b["dx"], [Ccols], R), sm0), 4 * S))
+    # Dim({1024, 4096}) reduced along dim 1 (strided)
+    cases.append(Case("softmax_dim1_1024x4096_fwd", 2 * S, mk_sm,
+                      lambda b: ctx.fwd("softmax", [T(b["x"], [R, Ccols], 1)], T(b["y"], [R, Ccols], 1), sm1), 4 * S))
+
+    def mk_ln():
+        return dict(x=torch.randn(R, Ccols, device=dev), g=torch.rand(Ccols, device=dev) + 0.5, b=torch.randn(Ccols, device=dev) * 0.1,
+                    y=torch.empty(R, Ccols, device=dev), dy=torch.randn(R, Ccols, device=dev), dx=torch.zeros(R, Ccols, device=dev))
+    def ln_xs(b):
+        return [T(b["x"], [Ccols], R), T(b["g"], [Ccols], 1), T(b["b"], [Ccols], 1)]
+    cases.append(Case("layer_norm_fwd", 2 * S, mk_ln, lambda b: ctx.fwd("layer_norm", ln_xs(b), T(b["y"], [Ccols], R)), 4 * S))
+    cases.append(Case("layer_norm_bwd_x", 4 * S, mk_ln,
+                      lambda b: ctx.bwd("layer_norm", ln_xs(b), T(b["y"], [Ccols], R), T(b["dy"], [Ccols], R), 0, T(b["dx"], [Ccols], R)), 4 * S))
+
+    def mk_wn():
+        return dict(w=torch.randn(R, Ccols, device=dev), g=torch.full((1,), 1.3, device=dev), y=torch.empty(R, Ccols, device=dev),
+                    dy=torch.randn(R, Ccols, device=dev), dw=torch.zeros(R, Ccols, device=dev))
+    cases.append(Case("weight_norm_fwd", 2 * S, mk_wn,
+                      lambda b: ctx.fwd("weight_norm", [T(b["w"], [R, Ccols], 1), T(b["g"], [1], 1)], T(b["y"], [R, Ccols], 1)), 4 * S))
+    cases.append(Case("weight_norm_bwd_w", 4 * S, mk_wn,
+                      lambda b: ctx.bwd("weight_norm", [T(b["w"], [R, Ccols], 1), T(b["g"], [1], 1)], T(b["y"], [R, Ccols], 1),
+                                        T(b["dy"], [R, Ccols], 1), 0, T(b["dw"], [R, Ccols], 1)), 4 * S))
+
+    # config 2: vocab 50,000, embed 512, 4,096 Zipf(1.1) ids
+    V, E, N = (50000, 512, 4096) if not small else (50000, 512, 4096)
+    rng = np.random.Generator(np.random.PCG64(7))
+    ranks = np.arange(1, V + 1, dtype=np.float64)
+    cdf = np.cumsum(ranks ** -1.1); cdf /= cdf[-1]
+    ids = np.minimum(np.searchsorted(cdf, rng.random(N)), V - 1).astype(np.uint32)
+    ids_p = ids.ctypes.data_as(C.POINTER(C.c_uint32))
+    uniq = len(np.unique(ids))
+    def mk_lookup():
+        return dict(table=torch.randn(V, E, device=dev), out=torch.empty(N, E, device=dev), aux=torch.zeros(N, dtype=torch.int32, device=dev),
+                    ids_dev=torch.from_numpy(ids.view(np.int32)).to(dev), g=torch.randn(N, E, device=dev), grads=torch.zeros(V, E, device=dev),
+                    keep=ids)
+    cases.append(Case("lookup_gather_N4096_E512", 2 * N * E * 4 + 4 * N, mk_lookup,
+                      lambda b: ctx.fwd("lookup", [], T(b["out"], [E], N), capi.LookupAttrs(b["table"].data_ptr(), V, None, N, 1.0),
+                                        b["ids_dev"].data_ptr()), 2 * V * E * 4))
+    cases.append(Case("lookup_scatter_add_N4096_E512", N * E * 4 + 2 * uniq * E * 4 + 16 * N, mk_lookup,
+                      lambda b: ctx.lookup_accumulate_grads([], b["ids_dev"].data_ptr(), b["g"].data_ptr(), b["grads"].data_ptr(), E, V, n=N),
+                      2 * V * E * 4))
+
+    # config 2 logits: Dim({50000}, 4096) = 819 MB (already > L2, one buffer set is enough)
+    Vr, Bc = (50000, 4096) if not small else (50000, 512)
+    tgt = np.minimum(np.searchsorted(cdf, rng.random(Bc)), V - 1).astype(np.uint32)
+    tgt_p = tgt.ctypes.data_as(C.POINTER(C.c_uint32))
+    SL = 4 * Vr * Bc
+    def mk_pnls():
+        aux = torch.zeros(3 * Bc, device=dev)
+        aux[2 * Bc:].view(torch.int32).copy_(torch.from_numpy(tgt.view(np.int32)))   # ids already in aux_mem on the device
+        return dict(x=torch.randn(Bc, Vr, device=dev), loss=torch.empty(Bc, device=dev), aux=aux,
+                    dE=torch.ones(Bc, device=dev), dx=torch.zeros(Bc, Vr, device=dev), z=torch.empty(Bc, device=dev), keep=tgt)
+    pa = capi.PickAttrs(None, Bc)
+    cases.append(Case("pickneglogsoftmax_fwd_50000x%d" % Bc, SL, mk_pnls,
+                      lambda b: ctx.fwd("pickneglogsoftmax", [T(b["x"], [Vr], Bc)], T(b["loss"], [1], Bc), pa, b["aux"].data_ptr()), 2 * SL))
+    cases.append(Case("pickneglogsoftmax_bwd_50000x%d" % Bc, 3 * SL, mk_pnls,
+                      lambda b: ctx.bwd("pickneglogsoftmax", [T(b["x"], [Vr], Bc)], T(b["loss"], [1], Bc), T(b["dE"], [1], Bc), 0,
+                                        T(b["dx"], [Vr], Bc), pa, b["aux"].data_ptr()), 2 * SL))
+    cases.append(Case("logsumexp_dim0_50000x%d" % Bc, SL, mk_pnls,
+                      lambda b: ctx.fwd("logsumexp_dim", [T(b["x"], [Vr], Bc)], T(b["z"], [1], Bc), capi.DimAttrs(0)), 2 * SL))
+
+    # LSTM C / H nodes at config 4 size (H = 1024, B = 512)
+    Hh, Bb = 1024, 512
+    def mk_ch():
+        return dict(c=torch.randn(Bb, Hh, device=dev), gates=torch.rand(Bb, 4 * Hh, device=dev), out=torch.empty(Bb, Hh, device=dev))
+    cases.append(Case("vanilla_lstm_c_fwd_H1024_B512", 20 * Hh * Bb, mk_ch,
+                      lambda b: ctx.fwd("vanilla_lstm_c", [T(b["c"], [Hh], Bb), T(b["gates"], [4 * Hh], Bb)], T(b["out"], [Hh], Bb)), 24 * Hh * Bb))
+    cases.append(Case("vanilla_lstm_h_fwd_H1024_B512", 12 * Hh * Bb, mk_ch,
+                      lambda b: ctx.fwd("vanilla_lstm_h", [T(b["c"], [Hh], Bb), T(b["gates"], [4 * Hh], Bb)], T(b["out"], [Hh], Bb)), 24 * Hh * Bb))
+    return cases
+
+
+def run(only=None, iters=20, small=False, out=None):
+    import torch
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(0, stream.cuda_stream)
+    peak, src = peaks()
+    results = []
+    for case in build_cases(torch, ctx, small):
+        if only and only not in case.name:
+            continue
+        nsets = max(2, min(24, int(np.ceil(2.0 * L2_BYTES / max(case.footprint, 1)))))
+        if small:
+            nsets = 2
+        with torch.cuda.stream(stream):
+            sets = [case.make() for _ in range(nsets)]
+            for k in range(3):
+                case.call(sets[k % nsets])
+            stream.synchronize()
+            l0 = ctx.launches()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for k in range(iters):
+                    case.call(sets[k % nsets])
+            launches = ctx.launches() - l0
+            graph.replay()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        gbs = case.nbytes / (ms * 1e-3) / 1e9
+        rec = {"kernel": case.name, "algorithmic_bytes": int(case.nbytes), "ms": ms, "GBps": gbs,
+               "frac_of_%s_copy_peak" % src: gbs / peak, "frac_of_8000": gbs / 8000.0,
+               "launches_per_call": launches / iters, "buffer_sets": nsets}
+        results.append(rec)
+        print(json.dumps(rec), flush=True)
+        del sets, graph
+        torch.cuda.empty_cache()
+    assert ctx.device_errors() == 0
+    if out:
+        with open(out, "w") as f:
+            json.dump(results, f, indent=1)
+    return results
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--out", default=None)
+    a = ap.parse_args()
+    run(a.only, a.iters, a.small, a.out)

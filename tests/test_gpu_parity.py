@@ -414,8 +414,13 @@ def test_lookup_scatter_add(oracle, g, E, V, n):
     ids_dev = g.dev(ids.view(np.float32)).view(dtype=__import__("torch").int32)
     g.ctx().lookup_accumulate_grads(ids, ids_dev.data_ptr(), g.dev(grad).data_ptr(), acc_.data_ptr(), E, V)
     got = g.host(acc_)
-    # same summation order as the CPU loop (rows of one id added in ascending position)
-    assert np.array_equal(got, want)
+    # Rows of one id are added in ascending position.  An id whose run fits inside one 32-position chunk of
+    # the sorted list is summed exactly as the CPU loop does (bit-exact); a frequent id (Zipf head) that
+    # spans chunks is summed chunk-wise in a fixed tree, equal to the CPU's chain within rounding.
+    counts = np.bincount(ids, minlength=V)
+    rare = counts <= 1
+    assert np.array_equal(got[rare], want[rare])
+    assert_close(got, want, TOL_REDUCE, floor=max(1.0, float(np.sqrt(counts.max()))), what="scatter-add")
     # run to run reproducible
     acc2 = g.dev(acc0)
     g.ctx().lookup_accumulate_grads(ids, ids_dev.data_ptr(), g.dev(grad).data_ptr(), acc2.data_ptr(), E, V)

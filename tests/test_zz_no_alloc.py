@@ -3,14 +3,16 @@
 `dyb200_lookup_accumulate_grads_noalloc` keeps its sort/segment tables in a fixed array inside the
 library instead of the context's growable arena, for hosts whose device memory is reserved once at
 start-up (as DyNet's pools are) and that must not hit cudaMalloc in the training loop.  It has to
-give exactly what `dyb200_lookup_accumulate_grads` gives: here both are called through the C ABI on the
-same inputs, twice in a row (the second call reuses the array the first one left behind), and the
-size limit is checked.  This file sorts last so a run that stops at the first failure has already
+give what `dyb200_lookup_accumulate_grads` gives: here both are called through the C ABI on the same
+inputs, twice in a row (the second call reuses the array the first one left behind), and the size
+limit is checked.  Both add the rows of one id in ascending position; the regular entry point sums a
+very frequent id chunk-wise, so the two agree to rounding (the 1e-4 class of the other gradient
+tests) and bit for bit on ids that occur once.  This file sorts last so a run that stops at the first failure has already
 covered everything else."""
 import numpy as np
 import pytest
 
-from util import randn, rng, zipf_ids
+from util import TOL_REDUCE, assert_close, randn, rng, zipf_ids
 
 pytestmark = pytest.mark.gpu
 
@@ -25,6 +27,13 @@ def _run(ctx, fn, ids, grad, acc0):
     return acc.cpu().numpy()
 
 
+def _same(got, want, ids, what):
+    counts = np.bincount(ids, minlength=want.shape[0])
+    once = counts <= 1
+    assert np.array_equal(got[once], want[once]), what
+    assert_close(got, want, TOL_REDUCE, floor=max(1.0, float(np.sqrt(counts.max()))), what=what)
+
+
 def test_noalloc_scatter_add_matches_regular_entry_point():
     import torch
     from dynet_b200 import capi
@@ -37,7 +46,7 @@ def test_noalloc_scatter_add_matches_regular_entry_point():
         acc0 = randn(r, V, E)
         want = _run(ctx, ctx.lookup_accumulate_grads, ids, grad, acc0)
         got = _run(ctx, ctx.lookup_accumulate_grads_noalloc, ids, grad, acc0)
-        assert np.array_equal(got, want), "call %d differs from dyb200_lookup_accumulate_grads" % call
+        _same(got, want, ids, "call %d vs dyb200_lookup_accumulate_grads" % call)
         if first is None:
             first = (ids, grad, acc0, want)
     # the first problem again, after the array was reused by a different one
@@ -50,7 +59,7 @@ def test_noalloc_scatter_add_matches_regular_entry_point():
     ctx.lookup_accumulate_grads_noalloc(ids, ids_dev.data_ptr(), g.data_ptr(), acc.data_ptr(), grad.shape[1], acc0.shape[0])
     torch.cuda.synchronize()
     assert torch.cuda.mem_get_info()[0] == free_before
-    assert np.array_equal(acc.cpu().numpy(), want)
+    _same(acc.cpu().numpy(), want, ids, "third call")
     assert ctx.device_errors() == 0
     ctx.close()
 
