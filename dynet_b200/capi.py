@@ -86,7 +86,8 @@ OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200
          "dyb200_ctx_launch_count", "dyb200_version", "dyb200_lookup_accumulate_grads",
          "dyb200_lookup_accumulate_grads_noalloc",
          "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm", "dyb200_fill", "dyb200_sum_all",
-         "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end"]
+         "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end",
+         "dyb200_ctx_param_cache", "dyb200_ctx_params_changed"]
 
 
 def exported_symbols():
@@ -130,6 +131,10 @@ def lib():
         L.dyb200_ctx_launch_count.restype = C.c_uint64
         L.dyb200_ctx_launch_count.argtypes = [C.c_void_p]
         L.dyb200_version.restype = C.c_char_p
+        L.dyb200_ctx_param_cache.restype = C.c_int
+        L.dyb200_ctx_param_cache.argtypes = [C.c_void_p, C.c_int]
+        L.dyb200_ctx_params_changed.restype = C.c_int
+        L.dyb200_ctx_params_changed.argtypes = [C.c_void_p]
         L.dyb200_ctx_profile_begin.restype = C.c_int
         L.dyb200_ctx_profile_begin.argtypes = [C.c_void_p, C.c_int]
         L.dyb200_ctx_profile_end.restype = C.c_int
@@ -145,7 +150,7 @@ def lib():
             f.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         L.dyb200_gemm.restype = C.c_int
         L.dyb200_gemm.argtypes = [C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32,
-                                  C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_int, C.c_void_p]
+                                  C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_int, C.c_uint, C.c_void_p]
         _LIB = L
     return _LIB
 
@@ -232,5 +237,11 @@ class Context:
     def parallel_accumulate(self, num_seqs, max_len, src_tbl, trg_tbl, len_tbl):
         self.check(self.L.dyb200_parallel_accumulate(num_seqs, max_len, src_tbl, trg_tbl, len_tbl, self.h))
 
-    def gemm(self, transA, transB, M, N, K, A, lda, B, ldb, Cp, ldc, accumulate):
-        self.check(self.L.dyb200_gemm(int(transA), int(transB), M, N, K, A, lda, B, ldb, Cp, ldc, int(accumulate), self.h))
+    def gemm(self, transA, transB, M, N, K, A, lda, B, ldb, Cp, ldc, accumulate, flags=0):
+        self.check(self.L.dyb200_gemm(int(transA), int(transB), M, N, K, A, lda, B, ldb, Cp, ldc, int(accumulate), flags, self.h))
+
+    def param_cache(self, enable):
+        self.check(self.L.dyb200_ctx_param_cache(self.h, int(enable)))
+
+    def params_changed(self):
+        self.check(self.L.dyb200_ctx_params_changed(self.h))

@@ -28,6 +28,16 @@ struct dyb200_ctx {
   uint64_t launches;     // kernels launched through this context
   // 3xTF32 GEMM state (tensor maps are encoded per call; driver entry point cached)
   void* encode_tiled;    // cuTensorMapEncodeTiled
+  // Optional cache of packed (hi/lo, K-major) parameter matrices, so that a weight used by every
+  // time step is split once per optimizer step instead of once per GEMM.  Off by default: when on,
+  // the caller must report every in-place parameter change (dyb200_ctx_params_changed).
+  int param_cache_on;
+  uint64_t param_version, param_tick;
+  struct ParamPack {
+    const float* src; uint32_t ld, rows, K, pitch; int k_is_fast;
+    uint64_t version, last_use;
+    float *hi, *lo; size_t floats;
+  } param_pack[24];
   // optional per-launch timing of the GEMM kernels (CUDA events on the launch stream)
   cudaEvent_t* prof_ev;  // 2 * prof_cap events: start/stop pairs
   double* prof_flops;    // useful FLOPs of each recorded launch

@@ -95,9 +95,21 @@ int dyb200_ctx_destroy(dyb200_ctx* ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   for (int k = 0; k < ctx->n_overflow; ++k) cudaFree(ctx->overflow[k]);
+  for (auto& e : ctx->param_pack) { if (e.hi) cudaFree(e.hi); if (e.lo) cudaFree(e.lo); }
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->dev_flags) cudaFree(ctx->dev_flags);
   free(ctx);
+  return DYB200_OK;
+}
+
+int dyb200_ctx_param_cache(dyb200_ctx* ctx, int enable) {
+  ctx->param_cache_on = enable ? 1 : 0;
+  ctx->param_version++;
+  return DYB200_OK;
+}
+
+int dyb200_ctx_params_changed(dyb200_ctx* ctx) {
+  ctx->param_version++;
   return DYB200_OK;
 }
 

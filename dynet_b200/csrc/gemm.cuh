@@ -12,6 +12,7 @@ struct GemmPair {
   // optional multiplicative mask on B, indexed like B's storage: element at (row r, col c)
   // of the stored matrix uses mask[r + (mask_full ? mask_ld * c : 0)]  (dropout masks, bd 1 or B)
   const float* maskB; uint32_t mask_ld; int mask_full;
+  int a_is_param;   // A is a parameter matrix: its packed form may be kept in the context's parameter cache
 };
 
 enum GemmEpiMode {

@@ -95,11 +95,12 @@ int dyb200_gemm_fused(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const
 }
 
 extern "C" int dyb200_gemm(int transA, int transB, uint32_t M, uint32_t N, uint32_t K, const float* A, uint32_t lda,
-                           const float* B, uint32_t ldb, float* C, uint32_t ldc, int accumulate, dyb200_ctx* ctx) {
+                           const float* B, uint32_t ldb, float* C, uint32_t ldc, int accumulate, unsigned flags,
+                           dyb200_ctx* ctx) {
   { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   DYB_CHECK_ARG(ctx, A && B && C, "gemm: null pointer");
   DYB_CHECK_ARG(ctx, lda >= (transA ? K : M) && ldb >= (transB ? N : K) && ldc >= M, "gemm: leading dimension too small");
-  GemmPair p{A, lda, transA, B, ldb, transB, K, nullptr, 0, 0};
+  GemmPair p{A, lda, transA, B, ldb, transB, K, nullptr, 0, 0, (flags & DYB200_GEMM_A_IS_PARAM) ? 1 : 0};
   GemmEpilogue e{accumulate ? EPI_ACCUM : EPI_STORE, C, ldc, nullptr, 0, 0.f, nullptr, 0, 0};
   return dyb200_gemm_fused(ctx, M, N, 1, &p, e);
 }

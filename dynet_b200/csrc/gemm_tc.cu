@@ -360,6 +360,48 @@ int pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_
 
 inline uint32_t round_up(uint32_t x, uint32_t m) { return (x + m - 1) / m * m; }
 
+// Returns the cached packed form of a parameter matrix, packing it first if it is new or stale.
+int cached_param_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, uint32_t pitch,
+                      float** hi, float** lo) {
+  const int cap = (int)(sizeof(ctx->param_pack) / sizeof(ctx->param_pack[0]));
+  dyb200_ctx::ParamPack* hit = nullptr;
+  dyb200_ctx::ParamPack* victim = &ctx->param_pack[0];
+  for (int k = 0; k < cap; ++k) {
+    dyb200_ctx::ParamPack* e = &ctx->param_pack[k];
+    if (e->hi && e->src == src && e->ld == ld && e->rows == rows && e->K == K && e->k_is_fast == (int)k_is_fast) { hit = e; break; }
+    if (!e->hi) { if (victim->hi) victim = e; }
+    else if (victim->hi && e->last_use < victim->last_use) victim = e;
+  }
+  dyb200_ctx::ParamPack* e = hit ? hit : victim;
+  const size_t floats = (size_t)rows * pitch;
+  if (!hit) {
+    if (e->hi && e->floats < floats) {   // evicted entry is too small: its buffers may still be read by queued kernels
+      DYB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      cudaFree(e->hi); cudaFree(e->lo);
+      e->hi = e->lo = nullptr;
+    }
+    if (!e->hi) {
+      if (cudaMalloc((void**)&e->hi, floats * sizeof(float)) != cudaSuccess || cudaMalloc((void**)&e->lo, floats * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        if (e->hi) cudaFree(e->hi);
+        e->hi = e->lo = nullptr;
+        return dyb200_fail(ctx, DYB200_ENOMEM, "parameter cache: cudaMalloc of %zu bytes failed", 2 * floats * sizeof(float));
+      }
+      e->floats = floats;
+    }
+    e->src = src; e->ld = ld; e->rows = rows; e->K = K; e->pitch = pitch; e->k_is_fast = (int)k_is_fast;
+    e->version = ~0ull;
+  }
+  if (e->version != ctx->param_version) {
+    int rc = pack(ctx, src, ld, k_is_fast, rows, K, nullptr, 0, 0, e->hi, e->lo, pitch);
+    if (rc) return rc;
+    e->version = ctx->param_version;
+  }
+  e->last_use = ++ctx->param_tick;
+  *hi = e->hi; *lo = e->lo;
+  return DYB200_OK;
+}
+
 }  // namespace
 
 int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const GemmPair* pairs, const GemmEpilogue& epi,
@@ -385,9 +427,11 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
   // scratch: per pair, 2 planes of M x Kp and 2 planes of N x Kp
   size_t need = 0;
   uint32_t Kp[2] = {0, 0};
+  bool cachedA[2] = {false, false};
   for (int p = 0; p < npairs; ++p) {
     Kp[p] = round_up(pairs[p].K, 32);
-    need += (size_t)2 * ((size_t)M + N) * Kp[p] * sizeof(float) + 4 * 256;
+    cachedA[p] = ctx->param_cache_on && pairs[p].a_is_param;
+    need += (size_t)2 * ((cachedA[p] ? 0 : (size_t)M) + N) * Kp[p] * sizeof(float) + 4 * 256;
   }
   void* scratch;
   rc = dyb200_scratch(ctx, need, &scratch);
@@ -398,11 +442,16 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
   memset(&tm, 0, sizeof(tm));
   for (int p = 0; p < npairs; ++p) {
     const GemmPair& g = pairs[p];
-    float *ahi = take((size_t)M * Kp[p]), *alo = take((size_t)M * Kp[p]);
-    float *bhi = take((size_t)N * Kp[p]), *blo = take((size_t)N * Kp[p]);
+    float *ahi, *alo;
     // A: rows = m. op(A)(m,k) = transA ? A[k + lda*m] : A[m + lda*k]  -> k is fast iff transA
-    rc = pack(ctx, g.A, g.lda, g.transA != 0, M, g.K, nullptr, 0, 0, ahi, alo, Kp[p]);
+    if (cachedA[p]) {
+      rc = cached_param_pack(ctx, g.A, g.lda, g.transA != 0, M, g.K, Kp[p], &ahi, &alo);
+    } else {
+      ahi = take((size_t)M * Kp[p]); alo = take((size_t)M * Kp[p]);
+      rc = pack(ctx, g.A, g.lda, g.transA != 0, M, g.K, nullptr, 0, 0, ahi, alo, Kp[p]);
+    }
     if (rc) return rc;
+    float *bhi = take((size_t)N * Kp[p]), *blo = take((size_t)N * Kp[p]);
     // B: rows = n. op(B)(k,n) = transB ? B[n + ldb*k] : B[k + ldb*n]  -> k is fast iff !transB
     rc = pack(ctx, g.B, g.ldb, g.transB == 0, N, g.K, g.maskB, g.mask_ld, g.mask_full, bhi, blo, Kp[p]);
     if (rc) return rc;

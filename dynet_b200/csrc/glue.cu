@@ -103,6 +103,7 @@ int dyb200_sgd_update(float* params, float* grads, size_t n, float lr, float cli
   DYB_CHECK_ARG(ctx, params && grads && grad_sumsq, "sgd_update: null pointer");
   k_sgd_update<<<stream_grid(ctx, n / 4 + 1, kBlock * 2), kBlock, 0, ctx->stream>>>(params, grads, n, lr, clip_threshold, grad_sumsq);
   DYB_LAUNCHED(ctx);
+  ctx->param_version++;   // packed copies of the parameters in the cache are stale now
   return DYB200_OK;
 }
 

@@ -246,8 +246,8 @@ int dyb200_vanilla_lstm_gates_fwd(DYB200_FWD_ARGS) {
   rc = gather_x(ctx, xs, g, (float*)scratch, &x);
   if (rc) return rc;
   GemmPair pairs[2] = {
-      {g.Wx->v, G, 0, x, g.I, 0, g.I, g.mx ? g.mx->v : nullptr, g.I, g.mx ? g.mx->bd == g.B : 0},
-      {g.Wh->v, G, 0, g.h->v, g.H, 0, g.H, g.mh ? g.mh->v : nullptr, g.H, g.mh ? g.mh->bd == g.B : 0}};
+      {g.Wx->v, G, 0, x, g.I, 0, g.I, g.mx ? g.mx->v : nullptr, g.I, g.mx ? g.mx->bd == g.B : 0, 1},
+      {g.Wh->v, G, 0, g.h->v, g.H, 0, g.H, g.mh ? g.mh->v : nullptr, g.H, g.mh ? g.mh->bd == g.B : 0, 1}};
   GemmEpilogue epi{EPI_GATES, fx->v, G, g.b->v, g.H, a->forget_gate_bias, nullptr, 0, 0};
   return dyb200_gemm_fused(ctx, G, g.B, 2, pairs, epi);
 }
@@ -283,13 +283,13 @@ int dyb200_vanilla_lstm_gates_bwd(DYB200_BWD_ARGS) {
     uint32_t off = 0, di = xs[i].d[0];
     for (unsigned j = 0; j < i; ++j) off += xs[j].d[0];
     DYB_CHECK_ARG(ctx, t_size(dEdxi) == (size_t)di * g.B, "VanillaLSTMGates::backward: dx size mismatch");
-    GemmPair p{g.Wx->v + (size_t)off * G, G, 1, dg, G, 0, G, nullptr, 0, 0};
+    GemmPair p{g.Wx->v + (size_t)off * G, G, 1, dg, G, 0, G, nullptr, 0, 0, 1};
     GemmEpilogue e{g.mx ? EPI_ACCUM_MASK : EPI_ACCUM, dEdxi->v, di, nullptr, 0, 0.f, g.mx ? g.mx->v + off : nullptr, g.I, g.mx ? g.mx->bd == g.B : 0};
     return dyb200_gemm_fused(ctx, di, g.B, 1, &p, e);
   }
   if (i == g.k) {  // dh = Wh^T dgate (.* mask_h)
     DYB_CHECK_ARG(ctx, t_size(dEdxi) == (size_t)g.H * g.B, "VanillaLSTMGates::backward: dh size mismatch");
-    GemmPair p{g.Wh->v, G, 1, dg, G, 0, G, nullptr, 0, 0};
+    GemmPair p{g.Wh->v, G, 1, dg, G, 0, G, nullptr, 0, 0, 1};
     GemmEpilogue e{g.mh ? EPI_ACCUM_MASK : EPI_ACCUM, dEdxi->v, g.H, nullptr, 0, 0.f, g.mh ? g.mh->v : nullptr, g.H, g.mh ? g.mh->bd == g.B : 0};
     return dyb200_gemm_fused(ctx, g.H, g.B, 1, &p, e);
   }
@@ -298,13 +298,13 @@ int dyb200_vanilla_lstm_gates_bwd(DYB200_BWD_ARGS) {
     const float* x = nullptr;
     rc = gather_x(ctx, xs, g, (float*)((char*)scratch + dg_bytes), &x);
     if (rc) return rc;
-    GemmPair p{dg, G, 0, x, g.I, 1, g.B, g.mx ? g.mx->v : nullptr, g.I, g.mx ? g.mx->bd == g.B : 0};
+    GemmPair p{dg, G, 0, x, g.I, 1, g.B, g.mx ? g.mx->v : nullptr, g.I, g.mx ? g.mx->bd == g.B : 0, 0};
     GemmEpilogue e{EPI_ACCUM, dEdxi->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
     return dyb200_gemm_fused(ctx, G, g.I, 1, &p, e);
   }
   // i == k + 2: dWh += dgate (h .* mask_h)^T
   DYB_CHECK_ARG(ctx, t_size(dEdxi) == (size_t)G * g.H, "VanillaLSTMGates::backward: dWh size mismatch");
-  GemmPair p{dg, G, 0, g.h->v, g.H, 1, g.B, g.mh ? g.mh->v : nullptr, g.H, g.mh ? g.mh->bd == g.B : 0};
+  GemmPair p{dg, G, 0, g.h->v, g.H, 1, g.B, g.mh ? g.mh->v : nullptr, g.H, g.mh ? g.mh->bd == g.B : 0, 0};
   GemmEpilogue e{EPI_ACCUM, dEdxi->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
   return dyb200_gemm_fused(ctx, G, g.H, 1, &p, e);
 }

@@ -168,7 +168,7 @@ void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float*
     }
     Tensor htop(Dim({H}, B), m.hs + ((size_t)t * L + L - 1) * HB), rt(Dim({V}, B), m.r + t * VB);
     // MatrixMultiply R * h, then CwiseSum(bias, R*h) in place (dynet/nodes-matrixmultiply.cc:50-59)
-    throw_status(dev, dyb200_gemm(0, 0, V, B, H, tR.v, V, htop.v, H, rt.v, V, 0, dev.ctx));
+    throw_status(dev, dyb200_gemm(0, 0, V, B, H, tR.v, V, htop.v, H, rt.v, V, 0, DYB200_GEMM_A_IS_PARAM, dev.ctx));
     sum_node.forward_dev_impl(dev, {&tbias, &rt}, rt);
     pnls.aux_mem = m.aux + (size_t)t * 3 * B;
     Tensor et(Dim({1}, B), m.errs + (size_t)t * B);
@@ -188,8 +188,8 @@ void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float*
     pnls.aux_mem = m.aux + (size_t)tt * 3 * B;
     pnls.backward_dev_impl(dev, {&rt}, et, tones, 0, tdr);
     sum_node.backward_dev_impl(dev, {&tbias, &rt}, rt, tdr, 0, tgbias);          // dbias += sum_b dr
-    throw_status(dev, dyb200_gemm(0, 1, V, H, B, m.dr, V, htop.v, H, tgR.v, V, 1, dev.ctx));           // dR += dr h^T
-    throw_status(dev, dyb200_gemm(1, 0, H, B, V, tR.v, V, m.dr, V, m.dh + top * HB, H, 1, dev.ctx));   // dh += R^T dr
+    throw_status(dev, dyb200_gemm(0, 1, V, H, B, m.dr, V, htop.v, H, tgR.v, V, 1, 0, dev.ctx));           // dR += dr h^T
+    throw_status(dev, dyb200_gemm(1, 0, H, B, V, tR.v, V, m.dr, V, m.dh + top * HB, H, 1, DYB200_GEMM_A_IS_PARAM, dev.ctx));   // dh += R^T dr
     for (uint32_t l = L; l-- > 0;) {
       size_t idx = (size_t)tt * L + l;
       Tensor store[7];
@@ -257,6 +257,9 @@ int dyb200h_lm_create(const dyb200h_lm_config* c, float* params, float* grads, v
   size_t off = 0;
   for (size_t n : sz) { m->p.push_back(params + off); m->g.push_back(grads + off); off += n; }
   plan(*c, m, (char*)workspace, ws_bytes);
+  // this driver owns the parameter updates (dyb200h_lm_update -> dyb200_sgd_update), so the packed
+  // copies of the weights can be reused across the time steps of a training step
+  dyb200_ctx_param_cache(ctx, 1);
   int rc = dyb200_fill(m->zeros, (size_t)c->H * c->B, 0.f, ctx);
   if (!rc) rc = dyb200_fill(m->ones, c->B, 1.f, ctx);
   if (rc) { delete m; return rc; }

@@ -188,6 +188,7 @@ class LstmLm:
 
     def set_params_host(self, arrays):
         self.params.copy_(self.torch.from_numpy(np.concatenate([a.ravel() for a in arrays])))
+        self.ctx.params_changed()   # the packed copies in the GEMM's parameter cache are stale
 
     def hidden_states_host(self):
         V, E, H, L, T, B = self.dims

@@ -73,6 +73,14 @@ uint64_t dyb200_ctx_launch_count(const dyb200_ctx* ctx);
  * device time in ms, the launch count and the useful FLOPs (2*M*N*K per product). */
 int dyb200_ctx_profile_begin(dyb200_ctx* ctx, int capacity);
 int dyb200_ctx_profile_end(dyb200_ctx* ctx, double ms_out[2], uint64_t launches_out[2], double flops_out[2]);
+/* Parameter cache for the tensor-pipe GEMM (off by default).  The GEMM splits every operand into
+ * TF32 hi/lo planes first; with the cache on, the planes of a PARAMETER matrix (the LSTM's Wx / Wh, or
+ * the A operand of dyb200_gemm called with DYB200_GEMM_A_IS_PARAM) are kept and reused until the
+ * parameters change.  The caller must call dyb200_ctx_params_changed after every in-place update of
+ * parameter values (dyb200_sgd_update does it itself); in a DyNet tree that is the end of
+ * Trainer::update (dynet/training.cc:195-265).  Costs up to 2x the size of each cached matrix. */
+int dyb200_ctx_param_cache(dyb200_ctx* ctx, int enable);
+int dyb200_ctx_params_changed(dyb200_ctx* ctx);
 /* Library build string ("dyb200 <n> sm_100a"). */
 const char* dyb200_version(void);
 
@@ -214,9 +222,10 @@ int dyb200_sgd_update(float* params, float* grads, size_t n, float lr, float cli
 /* ---- GEMM used by the LSTM gates (dynet/matrix-multiply.h:16-37, :97-117, :162-180) ----
  * C[M x N] (+)= op(A) * op(B), column-major, fp32 in/out, 3xTF32 on the tensor pipe
  * when the shape allows (else an fp32 CUDA-core kernel).  transA/transB as in BLAS. */
+#define DYB200_GEMM_A_IS_PARAM 1u /* flags: A is a parameter matrix (see dyb200_ctx_param_cache) */
 int dyb200_gemm(int transA, int transB, uint32_t M, uint32_t N, uint32_t K, const float* A,
                 uint32_t lda, const float* B, uint32_t ldb, float* C, uint32_t ldc, int accumulate,
-                dyb200_ctx* ctx);
+                unsigned flags, dyb200_ctx* ctx);
 
 #ifdef __cplusplus
 }
