@@ -87,7 +87,8 @@ OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200
          "dyb200_lookup_accumulate_grads_noalloc",
          "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm", "dyb200_fill", "dyb200_sum_all",
          "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end",
-         "dyb200_ctx_param_cache", "dyb200_ctx_params_changed"]
+         "dyb200_ctx_param_cache", "dyb200_ctx_params_changed", "dyb200_vanilla_lstm_fwd_fused",
+         "dyb200_vanilla_lstm_bwd_fused"]
 
 
 def exported_symbols():
@@ -131,6 +132,10 @@ def lib():
         L.dyb200_ctx_launch_count.restype = C.c_uint64
         L.dyb200_ctx_launch_count.argtypes = [C.c_void_p]
         L.dyb200_version.restype = C.c_char_p
+        L.dyb200_vanilla_lstm_fwd_fused.restype = C.c_int
+        L.dyb200_vanilla_lstm_fwd_fused.argtypes = [tp] * 8 + [C.POINTER(LstmGatesAttrs)] + [tp] * 3 + [C.c_void_p]
+        L.dyb200_vanilla_lstm_bwd_fused.restype = C.c_int
+        L.dyb200_vanilla_lstm_bwd_fused.argtypes = [tp] * 17 + [C.POINTER(LstmGatesAttrs), C.c_void_p]
         L.dyb200_ctx_param_cache.restype = C.c_int
         L.dyb200_ctx_param_cache.argtypes = [C.c_void_p, C.c_int]
         L.dyb200_ctx_params_changed.restype = C.c_int
@@ -239,6 +244,21 @@ class Context:
 
     def gemm(self, transA, transB, M, N, K, A, lda, B, ldb, Cp, ldc, accumulate, flags=0):
         self.check(self.L.dyb200_gemm(int(transA), int(transB), M, N, K, A, lda, B, ldb, Cp, ldc, int(accumulate), flags, self.h))
+
+    @staticmethod
+    def _opt(t):
+        return C.byref(t) if t is not None else None
+
+    def lstm_fwd_fused(self, x, h_tm1, c_tm1, Wx, Wh, b, mask_x, mask_h, attrs, gates, c_t, h_t):
+        o = self._opt
+        self.check(self.L.dyb200_vanilla_lstm_fwd_fused(o(x), o(h_tm1), o(c_tm1), o(Wx), o(Wh), o(b), o(mask_x), o(mask_h),
+                                                        C.byref(attrs), o(gates), o(c_t), o(h_t), self.h))
+
+    def lstm_bwd_fused(self, x, h_tm1, c_tm1, Wx, Wh, mask_x, mask_h, gates, c_t, dEdh, dEdc, dx, dh_tm1, dc_tm1, dWx, dWh, db, attrs):
+        o = self._opt
+        self.check(self.L.dyb200_vanilla_lstm_bwd_fused(o(x), o(h_tm1), o(c_tm1), o(Wx), o(Wh), o(mask_x), o(mask_h), o(gates), o(c_t),
+                                                        o(dEdh), o(dEdc), o(dx), o(dh_tm1), o(dc_tm1), o(dWx), o(dWh), o(db),
+                                                        C.byref(attrs), self.h))
 
     def param_cache(self, enable):
         self.check(self.L.dyb200_ctx_param_cache(self.h, int(enable)))

@@ -37,3 +37,15 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
                    int* handled);
 // Dispatcher: tensor path when eligible, else the CUDA-core path.
 int dyb200_gemm_fused(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const GemmPair* pairs, const GemmEpilogue& epi);
+
+// ---- pieces of the tensor path, for entry points that reuse one packed operand in several products ----
+struct PackedOp { float* hi; float* lo; uint32_t rows, K, pitch; };   // K-major TF32 hi / lo planes
+// Packs `rows x K` (element (r, k) at src[k + ld*r] when k_is_fast, else src[r + ld*k]) times an optional mask
+// into planes taken from the scratch arena (valid until the current entry point returns).
+int dyb200_tc_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K,
+                   const float* mask, uint32_t mask_ld, int mask_full, PackedOp* out);
+// Same for a parameter matrix: served from the parameter cache when it is on.
+int dyb200_tc_param(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, PackedOp* out);
+int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const PackedOp* A, const PackedOp* B,
+                          const GemmEpilogue& epi);
+bool dyb200_tc_eligible(uint32_t M, uint32_t N, double flops);

@@ -404,18 +404,27 @@ int cached_param_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_
 
 }  // namespace
 
-int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const GemmPair* pairs, const GemmEpilogue& epi,
-                   int* handled) {
-  *handled = 0;
-  if (M == 0 || N == 0 || npairs < 1 || npairs > 2) return DYB200_OK;
-  double flops = 0;
-  for (int p = 0; p < npairs; ++p) flops += 2.0 * M * N * pairs[p].K;
-  // Small products stay on the CUDA-core kernel: packing + a 128x128 tile would mostly move padding.
-  if (flops < 8.0e6 || M < 64) return DYB200_OK;
-  for (int p = 0; p < npairs; ++p) if (pairs[p].K == 0) return DYB200_OK;
-  if ((M + BM - 1) / BM > 65535u || (N + BN - 1) / BN > 65535u) return DYB200_OK;
-  *handled = 1;
+// ---- building blocks shared with the fused LSTM entry points ----------------------------------
+int dyb200_tc_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K,
+                   const float* mask, uint32_t mask_ld, int mask_full, PackedOp* out) {
+  const uint32_t pitch = round_up(K, 32);
+  void* buf;
+  int rc = dyb200_scratch(ctx, (size_t)2 * rows * pitch * sizeof(float) + 256, &buf);
+  if (rc) return rc;
+  out->hi = (float*)buf;
+  out->lo = (float*)(((uintptr_t)(out->hi + (size_t)rows * pitch) + 255) & ~(uintptr_t)255);
+  out->rows = rows; out->K = K; out->pitch = pitch;
+  return pack(ctx, src, ld, k_is_fast, rows, K, mask, mask_ld, mask_full, out->hi, out->lo, pitch);
+}
 
+int dyb200_tc_param(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, PackedOp* out) {
+  if (!ctx->param_cache_on) return dyb200_tc_pack(ctx, src, ld, k_is_fast, rows, K, nullptr, 0, 0, out);
+  out->rows = rows; out->K = K; out->pitch = round_up(K, 32);
+  return cached_param_pack(ctx, src, ld, k_is_fast, rows, K, out->pitch, &out->hi, &out->lo);
+}
+
+int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const PackedOp* A, const PackedOp* B,
+                          const GemmEpilogue& epi) {
   EncodeTiledFn enc;
   int rc = get_encoder(ctx, &enc);
   if (rc) return rc;
@@ -424,44 +433,20 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
     DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     attr_set = true;
   }
-  // scratch: per pair, 2 planes of M x Kp and 2 planes of N x Kp
-  size_t need = 0;
-  uint32_t Kp[2] = {0, 0};
-  bool cachedA[2] = {false, false};
-  for (int p = 0; p < npairs; ++p) {
-    Kp[p] = round_up(pairs[p].K, 32);
-    cachedA[p] = ctx->param_cache_on && pairs[p].a_is_param;
-    need += (size_t)2 * ((cachedA[p] ? 0 : (size_t)M) + N) * Kp[p] * sizeof(float) + 4 * 256;
-  }
-  void* scratch;
-  rc = dyb200_scratch(ctx, need, &scratch);
-  if (rc) return rc;
-  char* cur = (char*)scratch;
-  auto take = [&](size_t floats) { float* p = (float*)cur; cur += (floats * sizeof(float) + 255) & ~(size_t)255; return p; };
   TmapPack tm;
   memset(&tm, 0, sizeof(tm));
+  double flops = 0;
   for (int p = 0; p < npairs; ++p) {
-    const GemmPair& g = pairs[p];
-    float *ahi, *alo;
-    // A: rows = m. op(A)(m,k) = transA ? A[k + lda*m] : A[m + lda*k]  -> k is fast iff transA
-    if (cachedA[p]) {
-      rc = cached_param_pack(ctx, g.A, g.lda, g.transA != 0, M, g.K, Kp[p], &ahi, &alo);
-    } else {
-      ahi = take((size_t)M * Kp[p]); alo = take((size_t)M * Kp[p]);
-      rc = pack(ctx, g.A, g.lda, g.transA != 0, M, g.K, nullptr, 0, 0, ahi, alo, Kp[p]);
-    }
-    if (rc) return rc;
-    float *bhi = take((size_t)N * Kp[p]), *blo = take((size_t)N * Kp[p]);
-    // B: rows = n. op(B)(k,n) = transB ? B[n + ldb*k] : B[k + ldb*n]  -> k is fast iff !transB
-    rc = pack(ctx, g.B, g.ldb, g.transB == 0, N, g.K, g.maskB, g.mask_ld, g.mask_full, bhi, blo, Kp[p]);
-    if (rc) return rc;
-    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 0], ahi, M, g.K, Kp[p]))) return rc;
-    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 1], alo, M, g.K, Kp[p]))) return rc;
-    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 2], bhi, N, g.K, Kp[p]))) return rc;
-    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 3], blo, N, g.K, Kp[p]))) return rc;
+    DYB_CHECK_ARG(ctx, A[p].rows == M && B[p].rows == N && A[p].K == B[p].K && A[p].pitch % 32 == 0 && B[p].pitch % 32 == 0,
+                  "tensor GEMM: packed operand shapes do not match (M %u, N %u)", M, N);
+    flops += 2.0 * M * N * A[p].K;
+    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 0], A[p].hi, M, A[p].K, A[p].pitch))) return rc;
+    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 1], A[p].lo, M, A[p].K, A[p].pitch))) return rc;
+    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 2], B[p].hi, N, B[p].K, B[p].pitch))) return rc;
+    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 3], B[p].lo, N, B[p].K, B[p].pitch))) return rc;
   }
   if (npairs == 1) for (int k = 0; k < 4; ++k) tm.t[4 + k] = tm.t[k];
-  uint32_t kb0 = Kp[0] / BK, kb1 = npairs > 1 ? Kp[1] / BK : 0;
+  uint32_t kb0 = round_up(A[0].K, 32) / BK, kb1 = npairs > 1 ? round_up(A[1].K, 32) / BK : 0;
   const uint32_t kb_total = kb0 + kb1;
   dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN, 1);
   // Split K when the output has too few tiles to occupy the SMs (e.g. dx = W^T dgate: 16-32 tiles, K = 4096).
@@ -495,4 +480,32 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
     }
   }
   return DYB200_OK;
+}
+
+bool dyb200_tc_eligible(uint32_t M, uint32_t N, double flops) {
+  // Small products stay on the CUDA-core kernel: packing + a 128x128 tile would mostly move padding.
+  return !(flops < 8.0e6 || M < 64 || (M + BM - 1) / BM > 65535u || (N + BN - 1) / BN > 65535u);
+}
+
+int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const GemmPair* pairs, const GemmEpilogue& epi,
+                   int* handled) {
+  *handled = 0;
+  if (M == 0 || N == 0 || npairs < 1 || npairs > 2) return DYB200_OK;
+  double flops = 0;
+  for (int p = 0; p < npairs; ++p) flops += 2.0 * M * N * pairs[p].K;
+  if (!dyb200_tc_eligible(M, N, flops)) return DYB200_OK;
+  for (int p = 0; p < npairs; ++p) if (pairs[p].K == 0) return DYB200_OK;
+  *handled = 1;
+  PackedOp A[2], B[2];
+  for (int p = 0; p < npairs; ++p) {
+    const GemmPair& g = pairs[p];
+    // A: rows = m. op(A)(m,k) = transA ? A[k + lda*m] : A[m + lda*k]  -> k is fast iff transA
+    int rc = g.a_is_param ? dyb200_tc_param(ctx, g.A, g.lda, g.transA != 0, M, g.K, &A[p])
+                          : dyb200_tc_pack(ctx, g.A, g.lda, g.transA != 0, M, g.K, nullptr, 0, 0, &A[p]);
+    if (rc) return rc;
+    // B: rows = n. op(B)(k,n) = transB ? B[n + ldb*k] : B[k + ldb*n]  -> k is fast iff !transB
+    rc = dyb200_tc_pack(ctx, g.B, g.ldb, g.transB == 0, N, g.K, g.maskB, g.mask_ld, g.mask_full, &B[p]);
+    if (rc) return rc;
+  }
+  return dyb200_tc_gemm_packed(ctx, M, N, npairs, A, B, epi);
 }

@@ -120,6 +120,82 @@ __global__ void __launch_bounds__(kThreads) k_lstm_ch_bwd(const float* __restric
   }
 }
 
+
+// ---- fused cell kernels (used by the *_fused entry points) ---------------------------------------
+// Forward: c = i*g + f*c_tm1 and h = o*tanh(c) in one pass over the gates.
+template <int VEC>
+__global__ void __launch_bounds__(kThreads) k_lstm_cell_fwd(const float* __restrict__ c_tm1, const float* __restrict__ gates,
+                                                           float* __restrict__ c_t, float* __restrict__ h_t, uint32_t H,
+                                                           size_t total) {
+  constexpr int W = VEC ? 4 : 1;
+  for (size_t e = ((size_t)blockIdx.x * kThreads + threadIdx.x) * W; e < total; e += (size_t)gridDim.x * kThreads * W) {
+    size_t b = e / H, j = e % H;
+    const float* g = gates + b * 4 * H;
+    if (VEC) {
+      float4 cp = ld4_stream(c_tm1 + e), gi = ld4_stream(g + j), gf = ld4_stream(g + H + j), go = ld4_stream(g + 2 * H + j),
+             gg = ld4_stream(g + 3 * H + j);
+      float4 c = make_float4(gi.x * gg.x + gf.x * cp.x, gi.y * gg.y + gf.y * cp.y, gi.z * gg.z + gf.z * cp.z, gi.w * gg.w + gf.w * cp.w);
+      st4(c_t + e, c);
+      st4(h_t + e, make_float4(go.x * tanhf(c.x), go.y * tanhf(c.y), go.z * tanhf(c.z), go.w * tanhf(c.w)));
+    } else {
+      float c = g[j] * g[3 * H + j] + g[H + j] * c_tm1[e];
+      c_t[e] = c;
+      h_t[e] = g[2 * H + j] * tanhf(c);
+    }
+  }
+}
+
+// Backward of the H node, the C node and the gate non-linearities in one pass:
+//   dc = dEdc + dEdh * o * (1 - tanh(c)^2);  dc_tm1 += dc * f
+//   dpre_i = dc*g * i(1-i); dpre_f = dc*c_tm1 * f(1-f); dpre_o = dEdh*tanh(c) * o(1-o); dpre_g = dc*i * (1-g^2)
+//   db[r] += sum_b dpre[r, b]
+// One CTA owns 8 hidden units for the whole batch (thread = unit x batch lane), so the bias gradient
+// is a complete, fixed-order sum and needs no second pass.
+constexpr int kJT = 8;
+__global__ void __launch_bounds__(256) k_lstm_cell_bwd(const float* __restrict__ c_t, const float* __restrict__ c_tm1,
+                                                      const float* __restrict__ gates, const float* __restrict__ dEdh,
+                                                      const float* __restrict__ dEdc, float* __restrict__ dc_tm1,
+                                                      float* __restrict__ dpre, float* __restrict__ db, uint32_t H, uint32_t B) {
+  __shared__ float red[8][4][kJT];
+  const int jj = threadIdx.x % kJT, bl = threadIdx.x / kJT;   // 32 batch lanes
+  const uint32_t j = blockIdx.x * kJT + jj;
+  const bool live = j < H;
+  float si = 0.f, sf = 0.f, so = 0.f, sg = 0.f;
+  if (live) {
+    for (uint32_t b = bl; b < B; b += 32) {
+      const size_t e = (size_t)b * H + j;
+      const float* g = gates + (size_t)b * 4 * H;
+      const float gi = g[j], gf = g[H + j], go = g[2 * H + j], gg = g[3 * H + j];
+      const float c = c_t[e], cp = c_tm1[e], dh = dEdh[e];
+      const float t = tanhf(c);
+      float dc = dh * go * (1.f - t * t);
+      if (dEdc) dc += dEdc[e];
+      if (dc_tm1) dc_tm1[e] += dc * gf;
+      const float pi = gate_deriv(gi, dc * gg, false), pf = gate_deriv(gf, dc * cp, false);
+      const float po = gate_deriv(go, dh * t, false), pg = gate_deriv(gg, dc * gi, true);
+      float* o = dpre + (size_t)b * 4 * H;
+      o[j] = pi; o[H + j] = pf; o[2 * H + j] = po; o[3 * H + j] = pg;
+      si += pi; sf += pf; so += po; sg += pg;
+    }
+  }
+  // lanes of a warp: jj = lane % 8, four batch lanes -> fold the batch lanes, then the 8 warps
+#pragma unroll
+  for (int off = 8; off < 32; off <<= 1) {
+    si += __shfl_xor_sync(0xffffffffu, si, off); sf += __shfl_xor_sync(0xffffffffu, sf, off);
+    so += __shfl_xor_sync(0xffffffffu, so, off); sg += __shfl_xor_sync(0xffffffffu, sg, off);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane < kJT) { red[warp][0][lane] = si; red[warp][1][lane] = sf; red[warp][2][lane] = so; red[warp][3][lane] = sg; }
+  __syncthreads();
+  if (threadIdx.x < 4 * kJT) {
+    const int gate = threadIdx.x / kJT, u = threadIdx.x % kJT;
+    float acc = 0.f;
+    for (int w = 0; w < 8; ++w) acc += red[w][gate][u];
+    const uint32_t jo = blockIdx.x * kJT + u;
+    if (jo < H) db[(size_t)gate * H + jo] += acc;
+  }
+}
+
 struct GatesArgs {
   unsigned k;                 // number of x inputs
   const dyb200_tensor *h, *Wx, *Wh, *b, *mx, *mh;
@@ -307,6 +383,107 @@ int dyb200_vanilla_lstm_gates_bwd(DYB200_BWD_ARGS) {
   GemmPair p{dg, G, 0, g.h->v, g.H, 1, g.B, g.mh ? g.mh->v : nullptr, g.H, g.mh ? g.mh->bd == g.B : 0, 0};
   GemmEpilogue e{EPI_ACCUM, dEdxi->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
   return dyb200_gemm_fused(ctx, G, g.H, 1, &p, e);
+}
+
+
+// ---- fused entry points: the gates -> c -> h chain of one layer and time step in fewer launches ----
+int dyb200_vanilla_lstm_fwd_fused(const dyb200_tensor* x, const dyb200_tensor* h_tm1, const dyb200_tensor* c_tm1,
+                                  const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* b,
+                                  const dyb200_tensor* mask_x, const dyb200_tensor* mask_h,
+                                  const dyb200_lstm_gates_attrs* attrs, dyb200_tensor* gates, dyb200_tensor* c_t,
+                                  dyb200_tensor* h_t, dyb200_ctx* ctx) {
+  DYB_CHECK_ARG(ctx, x && h_tm1 && c_tm1 && Wx && Wh && b && attrs && gates && c_t && h_t, "lstm_fwd_fused: null argument");
+  DYB_CHECK_ARG(ctx, (attrs->dropout != 0) == (mask_x != nullptr && mask_h != nullptr), "lstm_fwd_fused: masks must be given exactly when dropout is set");
+  dyb200_tensor xs[7] = {*x, *h_tm1, *Wx, *Wh, *b};
+  int nxs = 5;
+  if (attrs->dropout) { xs[5] = *mask_x; xs[6] = *mask_h; nxs = 7; }
+  int rc = dyb200_vanilla_lstm_gates_fwd(xs, nxs, gates, attrs, nullptr, ctx);
+  if (rc) return rc;
+  dyb200_tensor ch[2] = {*c_tm1, *gates};
+  rc = ch_check(ctx, ch, 2, "VanillaLSTMC");
+  if (rc) return rc;
+  const uint32_t H = c_tm1->d[0];
+  const size_t total = (size_t)H * c_tm1->bd;
+  DYB_CHECK_ARG(ctx, t_size(c_t) == total && t_size(h_t) == total, "lstm_fwd_fused: c_t / h_t size mismatch");
+  if (total == 0) return DYB200_OK;
+  bool vec = H % 4 == 0 && aligned16(c_tm1->v) && aligned16(gates->v) && aligned16(c_t->v) && aligned16(h_t->v);
+  if (vec) k_lstm_cell_fwd<1><<<stream_grid(ctx, total / 4, kThreads), kThreads, 0, ctx->stream>>>(c_tm1->v, gates->v, c_t->v, h_t->v, H, total);
+  else k_lstm_cell_fwd<0><<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(c_tm1->v, gates->v, c_t->v, h_t->v, H, total);
+  DYB_LAUNCHED(ctx);
+  return DYB200_OK;
+}
+
+int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h_tm1, const dyb200_tensor* c_tm1,
+                                  const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* mask_x,
+                                  const dyb200_tensor* mask_h, const dyb200_tensor* gates, const dyb200_tensor* c_t,
+                                  const dyb200_tensor* dEdh, const dyb200_tensor* dEdc, dyb200_tensor* dx,
+                                  dyb200_tensor* dh_tm1, dyb200_tensor* dc_tm1, dyb200_tensor* dWx, dyb200_tensor* dWh,
+                                  dyb200_tensor* db, const dyb200_lstm_gates_attrs* attrs, dyb200_ctx* ctx) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
+  DYB_CHECK_ARG(ctx, x && h_tm1 && c_tm1 && Wx && Wh && gates && c_t && dEdh && dWx && dWh && db && attrs, "lstm_bwd_fused: null argument");
+  DYB_CHECK_ARG(ctx, (attrs->dropout != 0) == (mask_x != nullptr && mask_h != nullptr), "lstm_bwd_fused: masks must be given exactly when dropout is set");
+  DYB_CHECK_ARG(ctx, attrs->weightnoise_std == 0.f, "lstm_bwd_fused: weight noise is not supported by the fused path");
+  const uint32_t H = t_dim(h_tm1, 0), I = t_dim(x, 0), B = x->bd, G = 4 * H;
+  DYB_CHECK_ARG(ctx, x->nd == 1 && h_tm1->nd == 1 && h_tm1->bd == B && c_tm1->bd == B && t_dim(c_tm1, 0) == H, "lstm_bwd_fused: x / h_tm1 / c_tm1 shape mismatch");
+  DYB_CHECK_ARG(ctx, Wx->nd == 2 && Wx->d[0] == G && Wx->d[1] == I && Wh->nd == 2 && Wh->d[0] == G && Wh->d[1] == H, "lstm_bwd_fused: weight shape mismatch");
+  const size_t HB = (size_t)H * B;
+  DYB_CHECK_ARG(ctx, t_size(gates) == 4 * HB && t_size(c_t) == HB && t_size(dEdh) == HB && (!dEdc || t_size(dEdc) == HB), "lstm_bwd_fused: state size mismatch");
+  DYB_CHECK_ARG(ctx, (!dx || t_size(dx) == (size_t)I * B) && (!dh_tm1 || t_size(dh_tm1) == HB) && (!dc_tm1 || t_size(dc_tm1) == HB), "lstm_bwd_fused: gradient size mismatch");
+  DYB_CHECK_ARG(ctx, t_size(dWx) == (size_t)G * I && t_size(dWh) == (size_t)G * H && t_size(db) == G, "lstm_bwd_fused: parameter gradient size mismatch");
+  if (attrs->dropout) DYB_CHECK_ARG(ctx, (mask_x->bd == B || mask_x->bd == 1) && (mask_h->bd == B || mask_h->bd == 1) && t_dim(mask_x, 0) == I && t_dim(mask_h, 0) == H, "lstm_bwd_fused: mask shape mismatch");
+  if (HB == 0) return DYB200_OK;
+  void* sp;
+  int rc = dyb200_scratch(ctx, 4 * HB * sizeof(float), &sp);
+  if (rc) return rc;
+  float* dpre = (float*)sp;
+  k_lstm_cell_bwd<<<(H + kJT - 1) / kJT, 256, 0, ctx->stream>>>(c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr,
+                                                              dc_tm1 ? dc_tm1->v : nullptr, dpre, db->v, H, B);
+  DYB_LAUNCHED(ctx);
+  const float* mx = attrs->dropout ? mask_x->v : nullptr;
+  const float* mh = attrs->dropout ? mask_h->v : nullptr;
+  const int mx_full = attrs->dropout ? mask_x->bd == B : 0, mh_full = attrs->dropout ? mask_h->bd == B : 0;
+  const double flops_small = 2.0 * (I < H ? I : H) * (double)B * G;
+  if (dyb200_tc_eligible(I < H ? I : H, B, flops_small) && dyb200_tc_eligible(G, I < H ? I : H, flops_small)) {
+    // the gate gradient is split once per layout and shared by the four products
+    PackedOp dn, dt, wxT, whT, xt, ht;
+    if ((rc = dyb200_tc_pack(ctx, dpre, G, true, B, G, nullptr, 0, 0, &dn))) return rc;    // rows = batch, K = 4H
+    if ((rc = dyb200_tc_pack(ctx, dpre, G, false, G, B, nullptr, 0, 0, &dt))) return rc;   // rows = 4H, K = batch
+    if (dx) {
+      if ((rc = dyb200_tc_param(ctx, Wx->v, G, true, I, G, &wxT))) return rc;
+      GemmEpilogue e{mx ? EPI_ACCUM_MASK : EPI_ACCUM, dx->v, I, nullptr, 0, 0.f, mx, I, mx_full};
+      if ((rc = dyb200_tc_gemm_packed(ctx, I, B, 1, &wxT, &dn, e))) return rc;
+    }
+    if (dh_tm1) {
+      if ((rc = dyb200_tc_param(ctx, Wh->v, G, true, H, G, &whT))) return rc;
+      GemmEpilogue e{mh ? EPI_ACCUM_MASK : EPI_ACCUM, dh_tm1->v, H, nullptr, 0, 0.f, mh, H, mh_full};
+      if ((rc = dyb200_tc_gemm_packed(ctx, H, B, 1, &whT, &dn, e))) return rc;
+    }
+    if ((rc = dyb200_tc_pack(ctx, x->v, I, false, I, B, mx, I, mx_full, &xt))) return rc;       // (x .* mask_x)^T : rows = I, K = batch
+    GemmEpilogue ex{EPI_ACCUM, dWx->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
+    if ((rc = dyb200_tc_gemm_packed(ctx, G, I, 1, &dt, &xt, ex))) return rc;
+    if ((rc = dyb200_tc_pack(ctx, h_tm1->v, H, false, H, B, mh, H, mh_full, &ht))) return rc;
+    GemmEpilogue eh{EPI_ACCUM, dWh->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
+    return dyb200_tc_gemm_packed(ctx, G, H, 1, &dt, &ht, eh);
+  }
+  // small shapes: the same four products on the CUDA-core kernel
+  if (dx) {
+    GemmPair p{Wx->v, G, 1, dpre, G, 0, G, nullptr, 0, 0, 1};
+    GemmEpilogue e{mx ? EPI_ACCUM_MASK : EPI_ACCUM, dx->v, I, nullptr, 0, 0.f, mx, I, mx_full};
+    if ((rc = dyb200_gemm_fused(ctx, I, B, 1, &p, e))) return rc;
+  }
+  if (dh_tm1) {
+    GemmPair p{Wh->v, G, 1, dpre, G, 0, G, nullptr, 0, 0, 1};
+    GemmEpilogue e{mh ? EPI_ACCUM_MASK : EPI_ACCUM, dh_tm1->v, H, nullptr, 0, 0.f, mh, H, mh_full};
+    if ((rc = dyb200_gemm_fused(ctx, H, B, 1, &p, e))) return rc;
+  }
+  {
+    GemmPair p{dpre, G, 0, x->v, I, 1, B, mx, I, mx_full, 0};
+    GemmEpilogue e{EPI_ACCUM, dWx->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
+    if ((rc = dyb200_gemm_fused(ctx, G, I, 1, &p, e))) return rc;
+  }
+  GemmPair p{dpre, G, 0, h_tm1->v, H, 1, B, mh, H, mh_full, 0};
+  GemmEpilogue e{EPI_ACCUM, dWh->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
+  return dyb200_gemm_fused(ctx, G, H, 1, &p, e);
 }
 
 int dyb200_vanilla_lstm_c_fwd(DYB200_FWD_ARGS) { (void)attrs; (void)aux_mem; return ch_fwd<0>(ctx, xs, nxs, fx, "VanillaLSTMC"); }

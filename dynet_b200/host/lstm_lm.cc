@@ -27,6 +27,7 @@ typedef struct {
   uint32_t V, E, H, L, T, B;
   float lr, clip;
   int32_t dropout;  // 0: vanilla_lstm_gates, 1: vanilla_lstm_gates_dropout (masks are inputs)
+  int32_t fused;    // 0: one call per node and argument; 1: dyb200_vanilla_lstm_{fwd,bwd}_fused per layer and step
 } dyb200h_lm_config;
 }
 
@@ -161,8 +162,17 @@ void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float*
       std::vector<const Tensor*> xs;
       layer_xs(t, l, store, xs);
       Tensor tg(Dim({4 * H}, B), m.gates + idx * GB), tc(Dim({H}, B), m.cs + idx * HB), th(Dim({H}, B), m.hs + idx * HB);
-      gates_node.forward_dev_impl(dev, xs, tg);
       Tensor cprev = t == 0 ? tZero : Tensor(Dim({H}, B), m.cs + ((size_t)(t - 1) * L + l) * HB);
+      if (c.fused) {
+        dyb200_tensor cx = to_c(store[0]), chp = to_c(store[1]), ccp = to_c(cprev), cWx = to_c(store[2]), cWh = to_c(store[3]),
+                      cb = to_c(store[4]), cmx, cmh, cg = to_c(tg), cc = to_c(tc), ch = to_c(th);
+        if (c.dropout) { cmx = to_c(store[5]); cmh = to_c(store[6]); }
+        dyb200_lstm_gates_attrs at = {c.dropout ? 1 : 0, 0.f, 1.f};
+        throw_status(dev, dyb200_vanilla_lstm_fwd_fused(&cx, &chp, &ccp, &cWx, &cWh, &cb, c.dropout ? &cmx : nullptr,
+                                                        c.dropout ? &cmh : nullptr, &at, &cg, &cc, &ch, dev.ctx));
+        continue;
+      }
+      gates_node.forward_dev_impl(dev, xs, tg);
       c_node.forward_dev_impl(dev, {&cprev, &tg}, tc);
       h_node.forward_dev_impl(dev, {&tc, &tg}, th);
     }
@@ -198,6 +208,22 @@ void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float*
       Tensor tg(Dim({4 * H}, B), m.gates + idx * GB), tc(Dim({H}, B), m.cs + idx * HB), th(Dim({H}, B), m.hs + idx * HB);
       Tensor tdh(Dim({H}, B), m.dh + idx * HB), tdc(Dim({H}, B), m.dc + idx * HB), tdg(Dim({4 * H}, B), m.dgates + idx * GB);
       Tensor cprev = tt == 0 ? tZero : Tensor(Dim({H}, B), m.cs + ((size_t)(tt - 1) * L + l) * HB);
+      if (c.fused) {
+        uint32_t I2 = l == 0 ? E : H;
+        Tensor tdin2(Dim({I2}, B), l == 0 ? m.dx + tt * EB : m.dh + ((size_t)tt * L + l - 1) * HB);
+        Tensor tdhp2(Dim({H}, B), tt > 0 ? m.dh + ((size_t)(tt - 1) * L + l) * HB : nullptr);
+        Tensor tdcp2(Dim({H}, B), tt > 0 ? m.dc + ((size_t)(tt - 1) * L + l) * HB : nullptr);
+        Tensor gWx2(Dim({4 * H, I2}), m.g[1 + 3 * l]), gWh2(Dim({4 * H, H}), m.g[2 + 3 * l]), gb2(Dim({4 * H}), m.g[3 + 3 * l]);
+        dyb200_tensor cx = to_c(store[0]), chp = to_c(store[1]), ccp = to_c(cprev), cWx = to_c(store[2]), cWh = to_c(store[3]), cmx, cmh,
+                      cg = to_c(tg), cc = to_c(tc), cdh = to_c(tdh), cdc = to_c(tdc), cdx = to_c(tdin2), cdhp = to_c(tdhp2),
+                      cdcp = to_c(tdcp2), cgWx = to_c(gWx2), cgWh = to_c(gWh2), cgb = to_c(gb2);
+        if (c.dropout) { cmx = to_c(store[5]); cmh = to_c(store[6]); }
+        dyb200_lstm_gates_attrs at = {c.dropout ? 1 : 0, 0.f, 1.f};
+        throw_status(dev, dyb200_vanilla_lstm_bwd_fused(&cx, &chp, &ccp, &cWx, &cWh, c.dropout ? &cmx : nullptr, c.dropout ? &cmh : nullptr,
+                                                        &cg, &cc, &cdh, &cdc, &cdx, tt > 0 ? &cdhp : nullptr, tt > 0 ? &cdcp : nullptr,
+                                                        &cgWx, &cgWh, &cgb, &at, dev.ctx));
+        continue;
+      }
       h_node.backward_dev_impl(dev, {&tc, &tg}, th, tdh, 0, tdc);
       h_node.backward_dev_impl(dev, {&tc, &tg}, th, tdh, 1, tdg);
       if (tt > 0) {

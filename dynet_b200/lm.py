@@ -17,7 +17,7 @@ _HOST = None
 
 class LmConfig(C.Structure):
     _fields_ = [("V", C.c_uint32), ("E", C.c_uint32), ("H", C.c_uint32), ("L", C.c_uint32), ("T", C.c_uint32),
-                ("B", C.c_uint32), ("lr", C.c_float), ("clip", C.c_float), ("dropout", C.c_int32)]
+                ("B", C.c_uint32), ("lr", C.c_float), ("clip", C.c_float), ("dropout", C.c_int32), ("fused", C.c_int32)]
 
 
 def host_lib():
@@ -100,11 +100,13 @@ def synthetic_batch(dims, seed, dropout=0.2, zipf_s=1.1):
 class LstmLm:
     """2-layer (L-layer) LSTM language model training step on one GPU."""
 
-    def __init__(self, V, E, H, L, T, B, device=0, seed=0, lr=0.1, clip=5.0, dropout=True, stream=None):
+    def __init__(self, V, E, H, L, T, B, device=0, seed=0, lr=0.1, clip=5.0, dropout=True, stream=None, fused=True):
         import torch
         self.torch = torch
         self.dims = (V, E, H, L, T, B)
-        self.cfg = LmConfig(V, E, H, L, T, B, lr, clip, 1 if dropout else 0)
+        # fused=False drives every node and every backward argument separately (the drop-in contract);
+        # fused=True uses the per-layer fused entry points (same values, fewer launches)
+        self.cfg = LmConfig(V, E, H, L, T, B, lr, clip, 1 if dropout else 0, 1 if fused else 0)
         self.H = host_lib()
         self.device = torch.device("cuda", device)
         torch.cuda.set_device(self.device)

@@ -200,6 +200,28 @@ int dyb200_vanilla_lstm_c_bwd(DYB200_BWD_ARGS);  /* dynet/nodes-lstm.cc:591-615 
 int dyb200_vanilla_lstm_h_fwd(DYB200_FWD_ARGS);  /* xs = {c_t, gates}, dynet/nodes-lstm.cc:650-668 */
 int dyb200_vanilla_lstm_h_bwd(DYB200_BWD_ARGS);  /* dynet/nodes-lstm.cc:670-703 */
 
+/* Fused forms of the chain CompactVanillaLSTMBuilder emits per layer and time step
+ * (vanilla_lstm_gates[_dropout] -> vanilla_lstm_c -> vanilla_lstm_h, dynet/lstm.cc:1067-1076), for executors
+ * that recognise the pattern.  Values are those of the three nodes; only the launch count differs.
+ *  fwd: gates = VanillaLSTMGates(x, h_tm1, Wx, Wh, b [, mask_x, mask_h]); c_t = VanillaLSTMC(c_tm1, gates);
+ *       h_t = VanillaLSTMH(c_t, gates).  mask_x / mask_h are NULL exactly when attrs->dropout == 0.
+ *  bwd: given dEdh (gradient w.r.t. h_t) and dEdc (w.r.t. c_t; NULL = zero), performs what the backward calls of
+ *       the H node (i = 0, 1), the C node (i = 0, 1) and the gates node (i = 0..4) perform on a zeroed gates
+ *       gradient: dx, dh_tm1, dc_tm1, dWx, dWh, db are ACCUMULATED into (dx / dh_tm1 / dc_tm1 may be NULL when
+ *       that argument needs no gradient, e.g. the zero initial state).  The gate gradient is formed once and its
+ *       packed form is shared by the four products. */
+int dyb200_vanilla_lstm_fwd_fused(const dyb200_tensor* x, const dyb200_tensor* h_tm1, const dyb200_tensor* c_tm1,
+                                  const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* b,
+                                  const dyb200_tensor* mask_x, const dyb200_tensor* mask_h,
+                                  const dyb200_lstm_gates_attrs* attrs, dyb200_tensor* gates, dyb200_tensor* c_t,
+                                  dyb200_tensor* h_t, dyb200_ctx* ctx);
+int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h_tm1, const dyb200_tensor* c_tm1,
+                                  const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* mask_x,
+                                  const dyb200_tensor* mask_h, const dyb200_tensor* gates, const dyb200_tensor* c_t,
+                                  const dyb200_tensor* dEdh, const dyb200_tensor* dEdc, dyb200_tensor* dx,
+                                  dyb200_tensor* dh_tm1, dyb200_tensor* dc_tm1, dyb200_tensor* dWx, dyb200_tensor* dWh,
+                                  dyb200_tensor* db, const dyb200_lstm_gates_attrs* attrs, dyb200_ctx* ctx);
+
 /* ---- A14 autobatch ragged movers (same argument meaning as dynet/gpu-ops.h:14-15;
  * src/trg/len are DEVICE arrays of num_seqs entries, as dynet/exec.cc:346-356 uploads them) ---- */
 int dyb200_parallel_memcpy(int num_seqs, int max_len, float** src, float** trg, size_t* len, dyb200_ctx* ctx);

@@ -9,15 +9,16 @@ from util import assert_close
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("dims,dropout", [
     (dict(V=97, E=32, H=64, L=2, T=4, B=8), 0.2),
     (dict(V=50, E=20, H=12, L=1, T=3, B=5), 0.0),      # odd sizes: every kernel takes its scalar path
     (dict(V=1000, E=128, H=256, L=2, T=6, B=32), 0.2),
 ])
-def test_lm_step_matches_oracle(oracle, dims, dropout):
+def test_lm_step_matches_oracle(oracle, dims, dropout, fused):
     from dynet_b200 import lm
     V, E, H, L, T, B = (dims[k] for k in "VEHLTB")
-    model = lm.LstmLm(device=0, seed=11, lr=0.1, clip=5.0, dropout=bool(dropout), **dims)
+    model = lm.LstmLm(device=0, seed=11, lr=0.1, clip=5.0, dropout=bool(dropout), fused=fused, **dims)
     tokens, masks = lm.synthetic_batch(dims, seed=12, dropout=dropout)
     params = model.params_host()
     loss = model.forward_backward(tokens, masks)

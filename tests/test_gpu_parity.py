@@ -535,6 +535,52 @@ def test_lstm_c_h_vs_oracle(oracle, g, H, B):
             assert_close(g.host(d_), w, TOL_CWISE, floor=ACC_FLOOR, what="%s bwd %d" % (node, i))
 
 
+@pytest.mark.parametrize("I,H,B,masks,first", [(5, 3, 2, None, False), (128, 256, 32, "full", False), (96, 64, 17, "bd1", True),
+                                                (512, 1024, 64, "full", False), (130, 66, 5, None, False)])
+def test_lstm_fused_entry_points_equal_node_chain(oracle, g, capi, I, H, B, masks, first):
+    """dyb200_vanilla_lstm_{fwd,bwd}_fused against the oracle's gates -> c -> h node chain and its per-argument backward."""
+    r = rng(154)
+    x, h, c_prev = randn(r, B, I), randn(r, B, H, scale=0.5), randn(r, B, H, scale=0.5)
+    Wx, Wh, b = glorot(r, 4 * H, I), glorot(r, 4 * H, H), randn(r, 4 * H, scale=0.1)
+    mx = mh = None
+    if masks:
+        mb = B if masks == "full" else 1
+        mx = ((r.random((mb, I)) < 0.8) / 0.8).astype(np.float32)
+        mh = ((r.random((mb, H)) < 0.8) / 0.8).astype(np.float32)
+    gates = oracle.lstm_gates_fwd([x], h, Wx, Wh, b, mx, mh)
+    c_t = oracle.lstm_c_fwd(c_prev, gates)
+    h_t = oracle.lstm_h_fwd(c_t, gates)
+    dh, dc = randn(r, B, H), randn(r, B, H)
+    # reference backward: H node, C node, gates node, each argument separately, into random starting gradients
+    d0 = dict(x=randn(r, B, I), h=randn(r, B, H), c=randn(r, B, H), Wx=randn(r, I, 4 * H), Wh=randn(r, H, 4 * H), b=randn(r, 4 * H))
+    want = {k: v.copy() for k, v in d0.items()}
+    dc_tot = dc.copy()
+    oracle.lstm_h_bwd(c_t, gates, dh, 0, dc_tot)
+    dgates = np.zeros_like(gates)
+    oracle.lstm_h_bwd(c_t, gates, dh, 1, dgates)
+    oracle.lstm_c_bwd(c_prev, gates, dc_tot, 0, want["c"])
+    oracle.lstm_c_bwd(c_prev, gates, dc_tot, 1, dgates)
+    for i, k in enumerate(["x", "h", "Wx", "Wh", "b"]):
+        oracle.lstm_gates_bwd([x], h, Wx, Wh, gates, dgates, i, want[k], mx, mh)
+    at = capi.LstmGatesAttrs(1 if masks else 0, 0.0, 1.0)
+    D = {k: g.dev(v) for k, v in dict(x=x, h=h, c=c_prev, Wx=Wx, Wh=Wh, b=b, dh=dh, dc=dc).items()}
+    tm = (g.T(g.dev(mx)), g.T(g.dev(mh))) if masks else (None, None)
+    tx, th_, tc_ = g.T(D["x"]), g.T(D["h"]), g.T(D["c"])
+    tWx, tWh, tb = g.T(D["Wx"], [4 * H, I], 1), g.T(D["Wh"], [4 * H, H], 1), g.T(D["b"], [4 * H], 1)
+    og, oc, oh = (g.dev(np.zeros_like(a)) for a in (gates, c_t, h_t))
+    g.ctx().lstm_fwd_fused(tx, th_, tc_, tWx, tWh, tb, tm[0], tm[1], at, g.T(og), g.T(oc), g.T(oh))
+    assert_close(g.host(og), gates, TOL_REDUCE, floor=GEMM_FLOOR, what="fused gates")
+    assert_close(g.host(oc), c_t, TOL_REDUCE, floor=GEMM_FLOOR, what="fused c")
+    assert_close(g.host(oh), h_t, TOL_REDUCE, floor=GEMM_FLOOR, what="fused h")
+    G = {k: g.dev(v) for k, v in d0.items()}
+    g.ctx().lstm_bwd_fused(tx, th_, tc_, tWx, tWh, tm[0], tm[1], g.T(g.dev(gates)), g.T(g.dev(c_t)), g.T(D["dh"]), g.T(D["dc"]),
+                           g.T(G["x"]), None if first else g.T(G["h"]), None if first else g.T(G["c"]),
+                           g.T(G["Wx"], [4 * H, I], 1), g.T(G["Wh"], [4 * H, H], 1), g.T(G["b"], [4 * H], 1), at)
+    for k in ["x", "h", "c", "Wx", "Wh", "b"]:
+        ref = d0[k] if (first and k in ("h", "c")) else want[k]   # skipped arguments must stay untouched
+        assert_close(g.host(G[k]), ref, TOL_REDUCE, floor=ACC_FLOOR * (2.0 if k in ("Wx", "Wh", "b") else 1.0), what="fused d" + k)
+
+
 def test_lstm_chain_fused_equals_builder_math(oracle, g, capi):
     """Config-1 shape (I=128, H=256, B=32), 5 steps: h_t / c_t through the fused chain on the GPU vs the oracle."""
     r = rng(153)
