@@ -163,10 +163,31 @@ def build_cases(torch, ctx, small):
                       lambda b: ctx.fwd("vanilla_lstm_c", [T(b["c"], [Hh], Bb), T(b["gates"], [4 * Hh], Bb)], T(b["out"], [Hh], Bb)), 24 * Hh * Bb))
     cases.append(Case("vanilla_lstm_h_fwd_H1024_B512", 12 * Hh * Bb, mk_ch,
                       lambda b: ctx.fwd("vanilla_lstm_h", [T(b["c"], [Hh], Bb), T(b["gates"], [4 * Hh], Bb)], T(b["out"], [Hh], Bb)), 24 * Hh * Bb))
+    # tensor-bound: the gate GEMM (layer-2 shape of config 4: 4H = 4096, I = H = 1024, B = 512) and a weight-gradient product
+    Ig = Hh
+    def mk_gates():
+        sc = (6.0 / (4 * Hh + Ig)) ** 0.5
+        return dict(x=torch.randn(Bb, Ig, device=dev), h=torch.randn(Bb, Hh, device=dev) * 0.5,
+                    Wx=(torch.rand(Ig, 4 * Hh, device=dev) * 2 - 1) * sc, Wh=(torch.rand(Hh, 4 * Hh, device=dev) * 2 - 1) * sc,
+                    b=torch.zeros(4 * Hh, device=dev), mx=(torch.rand(Bb, Ig, device=dev) < 0.8).float() / 0.8,
+                    mh=(torch.rand(Bb, Hh, device=dev) < 0.8).float() / 0.8, out=torch.empty(Bb, 4 * Hh, device=dev),
+                    dW=torch.zeros(Ig, 4 * Hh, device=dev), dg=torch.randn(Bb, 4 * Hh, device=dev))
+    gat = capi.LstmGatesAttrs(1, 0.0, 1.0)
+    def gates_fwd(b):
+        xs = [T(b["x"], [Ig], Bb), T(b["h"], [Hh], Bb), T(b["Wx"], [4 * Hh, Ig], 1), T(b["Wh"], [4 * Hh, Hh], 1), T(b["b"], [4 * Hh], 1),
+              T(b["mx"], [Ig], Bb), T(b["mh"], [Hh], Bb)]
+        ctx.fwd("vanilla_lstm_gates", xs, T(b["out"], [4 * Hh], Bb), gat)
+    fl_g = 2.0 * 4 * Hh * (Ig + Hh) * Bb
+    cases.append(Case("lstm_gates_fwd_gemm_4096x512x2048", 0, mk_gates, gates_fwd, 10 ** 9))
+    cases[-1].flops = fl_g
+    def dw_gemm(b):   # dWx += dgate * x^T : M = 4H, N = I, K = B
+        ctx.gemm(0, 1, 4 * Hh, Ig, Bb, b["dg"].data_ptr(), 4 * Hh, b["x"].data_ptr(), Ig, b["dW"].data_ptr(), 4 * Hh, 1)
+    cases.append(Case("gemm_dW_4096x1024x512_accumulate", 0, mk_gates, dw_gemm, 10 ** 9))
+    cases[-1].flops = 2.0 * 4 * Hh * Ig * Bb
     return cases
 
 
-def run(only=None, iters=20, small=False, out=None):
+def run(only=None, iters=20, small=False, out=None, graph_mode=True):
     import torch
     stream = torch.cuda.Stream()
     ctx = capi.Context(0, stream.cuda_stream)
@@ -176,7 +197,7 @@ def run(only=None, iters=20, small=False, out=None):
         if only and only not in case.name:
             continue
         nsets = max(2, min(24, int(np.ceil(2.0 * L2_BYTES / max(case.footprint, 1)))))
-        if small:
+        if small or getattr(case, "flops", None):
             nsets = 2
         with torch.cuda.stream(stream):
             sets = [case.make() for _ in range(nsets)]
@@ -184,23 +205,33 @@ def run(only=None, iters=20, small=False, out=None):
                 case.call(sets[k % nsets])
             stream.synchronize()
             l0 = ctx.launches()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            graph = None
+            if graph_mode:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for k in range(iters):
+                        case.call(sets[k % nsets])
+                launches = ctx.launches() - l0
+                graph.replay()
+                stream.synchronize()
+                e0.record(stream)
+                graph.replay()
+                e1.record(stream)
+            else:   # eager calls (what a profiler capture of single launches wants)
+                e0.record(stream)
                 for k in range(iters):
                     case.call(sets[k % nsets])
-            launches = ctx.launches() - l0
-            graph.replay()
-            stream.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            graph.replay()
-            e1.record(stream)
+                e1.record(stream)
+                launches = ctx.launches() - l0
             stream.synchronize()
         ms = e0.elapsed_time(e1) / iters
         gbs = case.nbytes / (ms * 1e-3) / 1e9
         rec = {"kernel": case.name, "algorithmic_bytes": int(case.nbytes), "ms": ms, "GBps": gbs,
                "frac_of_%s_copy_peak" % src: gbs / peak, "frac_of_8000": gbs / 8000.0,
                "launches_per_call": launches / iters, "buffer_sets": nsets}
+        if getattr(case, "flops", None):
+            rec["useful_TFLOPs"] = case.flops / (ms * 1e-3) / 1e12   # whole call, operand packing included
         results.append(rec)
         print(json.dumps(rec), flush=True)
         del sets, graph
@@ -218,5 +249,6 @@ if __name__ == "__main__":
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--eager", action="store_true", help="no CUDA graph: plain launches (for profiler captures)")
     a = ap.parse_args()
-    run(a.only, a.iters, a.small, a.out)
+    run(a.only, a.iters, a.small, a.out, graph_mode=not a.eager)
