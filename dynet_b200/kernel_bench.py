@@ -137,7 +137,7 @@ def build_cases(torch, ctx, small):
                       2 * V * E * 4))
 
     # config 2 logits: Dim({50000}, 4096) = 819 MB (already > L2, one buffer set is enough)
-    Vr, Bc = (50000, 4096) if not small else (50000, 512)
+    Vr, Bc = (50000, 4096) if not small else (50000, 1024)
     tgt = np.minimum(np.searchsorted(cdf, rng.random(Bc)), V - 1).astype(np.uint32)
     tgt_p = tgt.ctypes.data_as(C.POINTER(C.c_uint32))
     SL = 4 * Vr * Bc
