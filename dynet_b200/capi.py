@@ -88,7 +88,8 @@ OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200
          "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm", "dyb200_fill", "dyb200_sum_all",
          "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end",
          "dyb200_ctx_param_cache", "dyb200_ctx_params_changed", "dyb200_vanilla_lstm_fwd_fused",
-         "dyb200_vanilla_lstm_bwd_fused"]
+         "dyb200_vanilla_lstm_bwd_fused", "dyb200_wgrad_create", "dyb200_wgrad_destroy", "dyb200_wgrad_push",
+         "dyb200_wgrad_flush"]
 
 
 def exported_symbols():
@@ -135,7 +136,16 @@ def lib():
         L.dyb200_vanilla_lstm_fwd_fused.restype = C.c_int
         L.dyb200_vanilla_lstm_fwd_fused.argtypes = [tp] * 8 + [C.POINTER(LstmGatesAttrs)] + [tp] * 3 + [C.c_void_p]
         L.dyb200_vanilla_lstm_bwd_fused.restype = C.c_int
-        L.dyb200_vanilla_lstm_bwd_fused.argtypes = [tp] * 17 + [C.POINTER(LstmGatesAttrs), C.c_void_p]
+        L.dyb200_vanilla_lstm_bwd_fused.argtypes = [tp] * 17 + [C.POINTER(LstmGatesAttrs), C.c_void_p, C.c_void_p]
+        L.dyb200_wgrad_create.restype = C.c_int
+        L.dyb200_wgrad_create.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]
+        L.dyb200_wgrad_destroy.restype = C.c_int
+        L.dyb200_wgrad_destroy.argtypes = [C.c_void_p]
+        L.dyb200_wgrad_push.restype = C.c_int
+        L.dyb200_wgrad_push.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_int,
+                                        C.c_void_p, C.c_uint32, C.c_void_p, C.c_int, C.c_void_p]
+        L.dyb200_wgrad_flush.restype = C.c_int
+        L.dyb200_wgrad_flush.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
         L.dyb200_ctx_param_cache.restype = C.c_int
         L.dyb200_ctx_param_cache.argtypes = [C.c_void_p, C.c_int]
         L.dyb200_ctx_params_changed.restype = C.c_int
@@ -254,11 +264,26 @@ class Context:
         self.check(self.L.dyb200_vanilla_lstm_fwd_fused(o(x), o(h_tm1), o(c_tm1), o(Wx), o(Wh), o(b), o(mask_x), o(mask_h),
                                                         C.byref(attrs), o(gates), o(c_t), o(h_t), self.h))
 
-    def lstm_bwd_fused(self, x, h_tm1, c_tm1, Wx, Wh, mask_x, mask_h, gates, c_t, dEdh, dEdc, dx, dh_tm1, dc_tm1, dWx, dWh, db, attrs):
+    def lstm_bwd_fused(self, x, h_tm1, c_tm1, Wx, Wh, mask_x, mask_h, gates, c_t, dEdh, dEdc, dx, dh_tm1, dc_tm1, dWx, dWh, db, attrs,
+                       deferred=None):
         o = self._opt
         self.check(self.L.dyb200_vanilla_lstm_bwd_fused(o(x), o(h_tm1), o(c_tm1), o(Wx), o(Wh), o(mask_x), o(mask_h), o(gates), o(c_t),
                                                         o(dEdh), o(dEdc), o(dx), o(dh_tm1), o(dc_tm1), o(dWx), o(dWh), o(db),
-                                                        C.byref(attrs), self.h))
+                                                        C.byref(attrs), deferred, self.h))
+
+    def wgrad_create(self, M, N0, N1, Kcap):
+        h = C.c_void_p()
+        self.check(self.L.dyb200_wgrad_create(self.h, M, N0, N1, Kcap, C.byref(h)))
+        return h
+
+    def wgrad_destroy(self, w):
+        self.L.dyb200_wgrad_destroy(w)
+
+    def wgrad_push(self, w, k, a, lda, b0, ldb0, mask0=None, mask0_full=0, b1=None, ldb1=0, mask1=None, mask1_full=0):
+        self.check(self.L.dyb200_wgrad_push(w, k, a, lda, b0, ldb0, mask0, mask0_full, b1, ldb1, mask1, mask1_full, self.h))
+
+    def wgrad_flush(self, w, C0, ldc0, C1=None, ldc1=0):
+        self.check(self.L.dyb200_wgrad_flush(w, C0, ldc0, C1, ldc1, self.h))
 
     def param_cache(self, enable):
         self.check(self.L.dyb200_ctx_param_cache(self.h, int(enable)))

@@ -49,3 +49,4 @@ int dyb200_tc_param(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fa
 int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const PackedOp* A, const PackedOp* B,
                           const GemmEpilogue& epi);
 bool dyb200_tc_eligible(uint32_t M, uint32_t N, double flops);
+struct dyb200_wgrad;

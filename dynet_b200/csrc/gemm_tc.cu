@@ -223,8 +223,30 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
 
 // ---- split-K second stage: C = epilogue(sum_s part[s]) in ascending split order ----------------
 __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__ part, uint32_t S, uint32_t M, uint32_t N,
-                                                      GemmEpilogue epi) {
+                                                      GemmEpilogue epi, int vec) {
   const size_t MN = (size_t)M * N;
+  if (vec) {   // M % 4 == 0 and 16-byte aligned C / mask: four rows of one column per thread
+    const size_t MN4 = MN / 4;
+    for (size_t q = (size_t)blockIdx.x * 256 + threadIdx.x; q < MN4; q += (size_t)gridDim.x * 256) {
+      const size_t e = 4 * q;
+      const uint32_t m = (uint32_t)(e % M), n = (uint32_t)(e / M);
+      float4 acc = ld4_stream(part + e);
+      for (uint32_t s2 = 1; s2 < S; ++s2) {
+        float4 v = ld4_stream(part + (size_t)s2 * MN + e);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      float* dst = epi.C + m + (size_t)epi.ldc * n;
+      if (epi.mode == EPI_STORE) st4(dst, acc);
+      else if (epi.mode == EPI_ACCUM) {
+        float4 o = ld4(dst);
+        st4(dst, make_float4(o.x + acc.x, o.y + acc.y, o.z + acc.z, o.w + acc.w));
+      } else {   // EPI_ACCUM_MASK
+        float4 o = ld4(dst), mk = ld4(epi.maskC + m + (epi.maskc_full ? (size_t)epi.maskc_ld * n : 0));
+        st4(dst, make_float4(o.x + acc.x * mk.x, o.y + acc.y * mk.y, o.z + acc.z * mk.z, o.w + acc.w * mk.w));
+      }
+    }
+    return;
+  }
   for (size_t e = (size_t)blockIdx.x * 256 + threadIdx.x; e < MN; e += (size_t)gridDim.x * 256) {
     const uint32_t m = (uint32_t)(e % M), n = (uint32_t)(e / M);
     float acc = 0.f;
@@ -475,7 +497,9 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     k_gemm_tc<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
     DYB_LAUNCHED(ctx);
     if (S > 1) {
-      k_splitk_reduce<<<stream_grid(ctx, (size_t)M * N, 256 * 4), 256, 0, ctx->stream>>>(part, S, M, N, epi);
+      const int vec = M % 4 == 0 && epi.ldc % 4 == 0 && aligned16(epi.C) && epi.mode != EPI_GATES &&
+                      (epi.mode != EPI_ACCUM_MASK || (aligned16(epi.maskC) && (!epi.maskc_full || epi.maskc_ld % 4 == 0)));
+      k_splitk_reduce<<<stream_grid(ctx, (size_t)M * N / 4 + 1, 256), 256, 0, ctx->stream>>>(part, S, M, N, epi, vec);
       DYB_LAUNCHED(ctx);
     }
   }
@@ -509,3 +533,86 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
   }
   return dyb200_tc_gemm_packed(ctx, M, N, npairs, A, B, epi);
 }
+
+// ---- deferred parameter-gradient products ---------------------------------------------------------
+// dW = sum_t A_t * B_t^T (A_t: M x k_t, B_t: N x k_t, both column-major) arises once per time step for
+// a parameter shared by all steps (dWx, dWh of an LSTM layer, dR of the output projection).  Instead of
+// T small products with K = batch, the packed K-major planes of every step are appended along K and ONE
+// product with K = sum k_t runs at the end: the tensor pipe sees a long reduction and C is read and
+// written once.  One A operand can serve two B operands (dWx and dWh share the gate gradient).
+struct dyb200_wgrad {
+  uint32_t M, N[2], Kcap, k;
+  PackedOp A, B[2];
+};
+
+extern "C" {
+
+int dyb200_wgrad_create(dyb200_ctx* ctx, uint32_t M, uint32_t N0, uint32_t N1, uint32_t Kcap, dyb200_wgrad** out) {
+  DYB_CHECK_ARG(ctx, out && M > 0 && N0 > 0 && Kcap > 0, "wgrad_create: bad shape");
+  dyb200_wgrad* w = (dyb200_wgrad*)calloc(1, sizeof(dyb200_wgrad));
+  if (!w) return dyb200_fail(ctx, DYB200_ENOMEM, "wgrad_create: host allocation failed");
+  w->M = M; w->N[0] = N0; w->N[1] = N1; w->Kcap = round_up(Kcap, 32); w->k = 0;
+  auto alloc = [&](PackedOp* p, uint32_t rows) -> bool {
+    p->rows = rows; p->K = 0; p->pitch = w->Kcap;
+    size_t bytes = (size_t)rows * w->Kcap * sizeof(float);
+    if (cudaMalloc((void**)&p->hi, bytes) != cudaSuccess) { cudaGetLastError(); p->hi = nullptr; return false; }
+    if (cudaMalloc((void**)&p->lo, bytes) != cudaSuccess) { cudaGetLastError(); p->lo = nullptr; return false; }
+    return true;
+  };
+  bool ok = alloc(&w->A, M) && alloc(&w->B[0], N0) && (N1 == 0 || alloc(&w->B[1], N1));
+  if (!ok) {
+    for (PackedOp* p : {&w->A, &w->B[0], &w->B[1]}) { if (p->hi) cudaFree(p->hi); if (p->lo) cudaFree(p->lo); }
+    free(w);
+    return dyb200_fail(ctx, DYB200_ENOMEM, "wgrad_create: cudaMalloc failed for M %u, N %u + %u, K %u", M, N0, N1, Kcap);
+  }
+  *out = w;
+  return DYB200_OK;
+}
+
+int dyb200_wgrad_destroy(dyb200_wgrad* w) {
+  if (!w) return DYB200_OK;
+  for (PackedOp* p : {&w->A, &w->B[0], &w->B[1]}) { if (p->hi) cudaFree(p->hi); if (p->lo) cudaFree(p->lo); }
+  free(w);
+  return DYB200_OK;
+}
+
+// Appends one step: a = A_t (M x k, leading dimension lda), b0 / b1 = B_t operands (N x k) with optional
+// multiplicative masks indexed like b (mask[r + (full ? ld * c : 0)]).
+int dyb200_wgrad_push(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda, const float* b0, uint32_t ldb0,
+                      const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1,
+                      int mask1_full, dyb200_ctx* ctx) {
+  DYB_CHECK_ARG(ctx, w && a && b0 && (w->N[1] == 0 || b1), "wgrad_push: null argument");
+  DYB_CHECK_ARG(ctx, w->k + k <= w->Kcap, "wgrad_push: %u + %u columns exceed the capacity %u", w->k, k, w->Kcap);
+  if (k == 0) return DYB200_OK;
+  int rc = pack(ctx, a, lda, false, w->M, k, nullptr, 0, 0, w->A.hi + w->k, w->A.lo + w->k, w->Kcap);
+  if (rc) return rc;
+  rc = pack(ctx, b0, ldb0, false, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + w->k, w->B[0].lo + w->k, w->Kcap);
+  if (rc) return rc;
+  if (w->N[1]) {
+    rc = pack(ctx, b1, ldb1, false, w->N[1], k, mask1, ldb1, mask1_full, w->B[1].hi + w->k, w->B[1].lo + w->k, w->Kcap);
+    if (rc) return rc;
+  }
+  w->k += k;
+  return DYB200_OK;
+}
+
+// C0 += A * B0^T (and C1 += A * B1^T) over everything pushed since the last flush; empties the accumulator.
+int dyb200_wgrad_flush(dyb200_wgrad* w, float* C0, uint32_t ldc0, float* C1, uint32_t ldc1, dyb200_ctx* ctx) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
+  DYB_CHECK_ARG(ctx, w && C0 && (w->N[1] == 0 || C1), "wgrad_flush: null argument");
+  if (w->k == 0) return DYB200_OK;
+  PackedOp A = w->A;
+  A.K = w->k;
+  for (int j = 0; j < 2; ++j) {
+    if (w->N[j] == 0) continue;
+    PackedOp B = w->B[j];
+    B.K = w->k;
+    GemmEpilogue e{EPI_ACCUM, j == 0 ? C0 : C1, j == 0 ? ldc0 : ldc1, nullptr, 0, 0.f, nullptr, 0, 0};
+    int rc = dyb200_tc_gemm_packed(ctx, w->M, w->N[j], 1, &A, &B, e);
+    if (rc) return rc;
+  }
+  w->k = 0;
+  return DYB200_OK;
+}
+
+}  // extern "C"

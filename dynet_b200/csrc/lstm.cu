@@ -418,9 +418,10 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
                                   const dyb200_tensor* mask_h, const dyb200_tensor* gates, const dyb200_tensor* c_t,
                                   const dyb200_tensor* dEdh, const dyb200_tensor* dEdc, dyb200_tensor* dx,
                                   dyb200_tensor* dh_tm1, dyb200_tensor* dc_tm1, dyb200_tensor* dWx, dyb200_tensor* dWh,
-                                  dyb200_tensor* db, const dyb200_lstm_gates_attrs* attrs, dyb200_ctx* ctx) {
+                                  dyb200_tensor* db, const dyb200_lstm_gates_attrs* attrs, dyb200_wgrad* deferred,
+                                  dyb200_ctx* ctx) {
   { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
-  DYB_CHECK_ARG(ctx, x && h_tm1 && c_tm1 && Wx && Wh && gates && c_t && dEdh && dWx && dWh && db && attrs, "lstm_bwd_fused: null argument");
+  DYB_CHECK_ARG(ctx, x && h_tm1 && c_tm1 && Wx && Wh && gates && c_t && dEdh && (deferred || (dWx && dWh)) && db && attrs, "lstm_bwd_fused: null argument");
   DYB_CHECK_ARG(ctx, (attrs->dropout != 0) == (mask_x != nullptr && mask_h != nullptr), "lstm_bwd_fused: masks must be given exactly when dropout is set");
   DYB_CHECK_ARG(ctx, attrs->weightnoise_std == 0.f, "lstm_bwd_fused: weight noise is not supported by the fused path");
   const uint32_t H = t_dim(h_tm1, 0), I = t_dim(x, 0), B = x->bd, G = 4 * H;
@@ -429,7 +430,7 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
   const size_t HB = (size_t)H * B;
   DYB_CHECK_ARG(ctx, t_size(gates) == 4 * HB && t_size(c_t) == HB && t_size(dEdh) == HB && (!dEdc || t_size(dEdc) == HB), "lstm_bwd_fused: state size mismatch");
   DYB_CHECK_ARG(ctx, (!dx || t_size(dx) == (size_t)I * B) && (!dh_tm1 || t_size(dh_tm1) == HB) && (!dc_tm1 || t_size(dc_tm1) == HB), "lstm_bwd_fused: gradient size mismatch");
-  DYB_CHECK_ARG(ctx, t_size(dWx) == (size_t)G * I && t_size(dWh) == (size_t)G * H && t_size(db) == G, "lstm_bwd_fused: parameter gradient size mismatch");
+  DYB_CHECK_ARG(ctx, (deferred || (t_size(dWx) == (size_t)G * I && t_size(dWh) == (size_t)G * H)) && t_size(db) == G, "lstm_bwd_fused: parameter gradient size mismatch");
   if (attrs->dropout) DYB_CHECK_ARG(ctx, (mask_x->bd == B || mask_x->bd == 1) && (mask_h->bd == B || mask_h->bd == 1) && t_dim(mask_x, 0) == I && t_dim(mask_h, 0) == H, "lstm_bwd_fused: mask shape mismatch");
   if (HB == 0) return DYB200_OK;
   void* sp;
@@ -443,11 +444,15 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
   const float* mh = attrs->dropout ? mask_h->v : nullptr;
   const int mx_full = attrs->dropout ? mask_x->bd == B : 0, mh_full = attrs->dropout ? mask_h->bd == B : 0;
   const double flops_small = 2.0 * (I < H ? I : H) * (double)B * G;
+  if (deferred) {
+    // weight gradients: append (dgate, x .* mask_x, h .* mask_h) to the accumulator; one product at flush time
+    rc = dyb200_wgrad_push(deferred, B, dpre, G, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx);
+    if (rc) return rc;
+  }
   if (dyb200_tc_eligible(I < H ? I : H, B, flops_small) && dyb200_tc_eligible(G, I < H ? I : H, flops_small)) {
     // the gate gradient is split once per layout and shared by the four products
     PackedOp dn, dt, wxT, whT, xt, ht;
     if ((rc = dyb200_tc_pack(ctx, dpre, G, true, B, G, nullptr, 0, 0, &dn))) return rc;    // rows = batch, K = 4H
-    if ((rc = dyb200_tc_pack(ctx, dpre, G, false, G, B, nullptr, 0, 0, &dt))) return rc;   // rows = 4H, K = batch
     if (dx) {
       if ((rc = dyb200_tc_param(ctx, Wx->v, G, true, I, G, &wxT))) return rc;
       GemmEpilogue e{mx ? EPI_ACCUM_MASK : EPI_ACCUM, dx->v, I, nullptr, 0, 0.f, mx, I, mx_full};
@@ -458,6 +463,8 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
       GemmEpilogue e{mh ? EPI_ACCUM_MASK : EPI_ACCUM, dh_tm1->v, H, nullptr, 0, 0.f, mh, H, mh_full};
       if ((rc = dyb200_tc_gemm_packed(ctx, H, B, 1, &whT, &dn, e))) return rc;
     }
+    if (deferred) return DYB200_OK;
+    if ((rc = dyb200_tc_pack(ctx, dpre, G, false, G, B, nullptr, 0, 0, &dt))) return rc;   // rows = 4H, K = batch
     if ((rc = dyb200_tc_pack(ctx, x->v, I, false, I, B, mx, I, mx_full, &xt))) return rc;       // (x .* mask_x)^T : rows = I, K = batch
     GemmEpilogue ex{EPI_ACCUM, dWx->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
     if ((rc = dyb200_tc_gemm_packed(ctx, G, I, 1, &dt, &xt, ex))) return rc;
@@ -476,6 +483,7 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
     GemmEpilogue e{mh ? EPI_ACCUM_MASK : EPI_ACCUM, dh_tm1->v, H, nullptr, 0, 0.f, mh, H, mh_full};
     if ((rc = dyb200_gemm_fused(ctx, H, B, 1, &p, e))) return rc;
   }
+  if (deferred) return DYB200_OK;
   {
     GemmPair p{dpre, G, 0, x->v, I, 1, B, mx, I, mx_full, 0};
     GemmEpilogue e{EPI_ACCUM, dWx->v, G, nullptr, 0, 0.f, nullptr, 0, 0};

@@ -71,6 +71,13 @@ struct Lm {
   size_t dact_bytes;
   float* scalars;                 // [0] = squared gradient norm
   cudaStream_t stream;
+  // fused driver: weight-gradient products deferred to the end of the backward pass (one per parameter)
+  std::vector<dyb200_wgrad*> wg_layer;   // per layer: A = gate gradient, B0 = x .* mask_x, B1 = h_tm1 .* mask_h
+  dyb200_wgrad* wg_R = nullptr;          // A = d(logits), B0 = h_top
+  ~Lm() {
+    for (auto w : wg_layer) dyb200_wgrad_destroy(w);
+    dyb200_wgrad_destroy(wg_R);
+  }
 };
 
 size_t plan(const dyb200h_lm_config& c, Lm* m, char* base, size_t size) {
@@ -198,7 +205,8 @@ void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float*
     pnls.aux_mem = m.aux + (size_t)tt * 3 * B;
     pnls.backward_dev_impl(dev, {&rt}, et, tones, 0, tdr);
     sum_node.backward_dev_impl(dev, {&tbias, &rt}, rt, tdr, 0, tgbias);          // dbias += sum_b dr
-    throw_status(dev, dyb200_gemm(0, 1, V, H, B, m.dr, V, htop.v, H, tgR.v, V, 1, 0, dev.ctx));           // dR += dr h^T
+    if (c.fused) throw_status(dev, dyb200_wgrad_push(m.wg_R, B, m.dr, V, htop.v, H, nullptr, 0, nullptr, 0, nullptr, 0, dev.ctx));
+    else throw_status(dev, dyb200_gemm(0, 1, V, H, B, m.dr, V, htop.v, H, tgR.v, V, 1, 0, dev.ctx));   // dR += dr h^T
     throw_status(dev, dyb200_gemm(1, 0, H, B, V, tR.v, V, m.dr, V, m.dh + top * HB, H, 1, DYB200_GEMM_A_IS_PARAM, dev.ctx));   // dh += R^T dr
     for (uint32_t l = L; l-- > 0;) {
       size_t idx = (size_t)tt * L + l;
@@ -221,7 +229,7 @@ void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float*
         dyb200_lstm_gates_attrs at = {c.dropout ? 1 : 0, 0.f, 1.f};
         throw_status(dev, dyb200_vanilla_lstm_bwd_fused(&cx, &chp, &ccp, &cWx, &cWh, c.dropout ? &cmx : nullptr, c.dropout ? &cmh : nullptr,
                                                         &cg, &cc, &cdh, &cdc, &cdx, tt > 0 ? &cdhp : nullptr, tt > 0 ? &cdcp : nullptr,
-                                                        &cgWx, &cgWh, &cgb, &at, dev.ctx));
+                                                        &cgWx, &cgWh, &cgb, &at, m.wg_layer[l], dev.ctx));
         continue;
       }
       h_node.backward_dev_impl(dev, {&tc, &tg}, th, tdh, 0, tdc);
@@ -245,11 +253,24 @@ void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float*
     }
   }
   Tensor tgC(Dim({E}, V), m.g[0]);
-  for (uint32_t t = 0; t < T; ++t) {
-    LookupNode look(tC, nullptr, B);
-    look.aux_mem = m.tok + (size_t)t * B;
-    Tensor tdx(Dim({E}, B), m.dx + t * EB);
+  if (c.fused) {
+    // the deferred weight-gradient products: one per parameter matrix, K = T * B
+    for (uint32_t l = 0; l < L; ++l)
+      throw_status(dev, dyb200_wgrad_flush(m.wg_layer[l], m.g[1 + 3 * l], 4 * H, m.g[2 + 3 * l], 4 * H, dev.ctx));
+    throw_status(dev, dyb200_wgrad_flush(m.wg_R, tgR.v, V, nullptr, 0, dev.ctx));
+    // All T lookups share the table, so their accumulate_grads calls fold into one over the T*B ids in time
+    // order: each table row still receives its rows in the order of the per-step calls.
+    LookupNode look(tC, nullptr, T * B);
+    look.aux_mem = m.tok;
+    Tensor tdx(Dim({E}, T * B), m.dx);
     look.accumulate_grad(dev, tdx, tgC);
+  } else {
+    for (uint32_t t = 0; t < T; ++t) {
+      LookupNode look(tC, nullptr, B);
+      look.aux_mem = m.tok + (size_t)t * B;
+      Tensor tdx(Dim({E}, B), m.dx + t * EB);
+      look.accumulate_grad(dev, tdx, tgC);
+    }
   }
 }
 
@@ -286,7 +307,17 @@ int dyb200h_lm_create(const dyb200h_lm_config* c, float* params, float* grads, v
   // this driver owns the parameter updates (dyb200h_lm_update -> dyb200_sgd_update), so the packed
   // copies of the weights can be reused across the time steps of a training step
   dyb200_ctx_param_cache(ctx, 1);
-  int rc = dyb200_fill(m->zeros, (size_t)c->H * c->B, 0.f, ctx);
+  int rc = DYB200_OK;
+  if (c->fused) {
+    for (uint32_t l = 0; l < c->L && !rc; ++l) {
+      dyb200_wgrad* w = nullptr;
+      rc = dyb200_wgrad_create(ctx, 4 * c->H, l == 0 ? c->E : c->H, c->H, c->T * c->B, &w);
+      if (!rc) m->wg_layer.push_back(w);
+    }
+    if (!rc) rc = dyb200_wgrad_create(ctx, c->V, c->H, 0, c->T * c->B, &m->wg_R);
+    if (rc) { delete m; return rc; }
+  }
+  rc = dyb200_fill(m->zeros, (size_t)c->H * c->B, 0.f, ctx);
   if (!rc) rc = dyb200_fill(m->ones, c->B, 1.f, ctx);
   if (rc) { delete m; return rc; }
   *out = m;

@@ -209,7 +209,9 @@ int dyb200_vanilla_lstm_h_bwd(DYB200_BWD_ARGS);  /* dynet/nodes-lstm.cc:670-703 
  *       the H node (i = 0, 1), the C node (i = 0, 1) and the gates node (i = 0..4) perform on a zeroed gates
  *       gradient: dx, dh_tm1, dc_tm1, dWx, dWh, db are ACCUMULATED into (dx / dh_tm1 / dc_tm1 may be NULL when
  *       that argument needs no gradient, e.g. the zero initial state).  The gate gradient is formed once and its
- *       packed form is shared by the four products. */
+ *       packed form is shared by the four products.  With `deferred` non-NULL (a dyb200_wgrad created with
+ *       M = 4H, N0 = I, N1 = H, see below) the two weight-gradient products are not run: their operands are
+ *       appended to the accumulator and dWx / dWh (which may then be NULL) are produced by dyb200_wgrad_flush. */
 int dyb200_vanilla_lstm_fwd_fused(const dyb200_tensor* x, const dyb200_tensor* h_tm1, const dyb200_tensor* c_tm1,
                                   const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* b,
                                   const dyb200_tensor* mask_x, const dyb200_tensor* mask_h,
@@ -220,7 +222,23 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
                                   const dyb200_tensor* mask_h, const dyb200_tensor* gates, const dyb200_tensor* c_t,
                                   const dyb200_tensor* dEdh, const dyb200_tensor* dEdc, dyb200_tensor* dx,
                                   dyb200_tensor* dh_tm1, dyb200_tensor* dc_tm1, dyb200_tensor* dWx, dyb200_tensor* dWh,
-                                  dyb200_tensor* db, const dyb200_lstm_gates_attrs* attrs, dyb200_ctx* ctx);
+                                  dyb200_tensor* db, const dyb200_lstm_gates_attrs* attrs, struct dyb200_wgrad* deferred,
+                                  dyb200_ctx* ctx);
+
+/* Deferred parameter-gradient products.  A parameter shared by all time steps (Wx, Wh of an LSTM layer; the
+ * output projection) receives dW += A_t * B_t^T from every step (dynet/nodes-lstm.cc:419-500: dgate * x^T summed over
+ * the batch; dynet/nodes-matrixmultiply.cc:61-74).  An accumulator keeps the packed operands of every step side by
+ * side and runs ONE product with K = sum of the steps' batch sizes at flush time: the same sum in a different
+ * association (parity class 1e-4), a much better shape for the tensor pipe.  One A operand may feed two products
+ * (N1 > 0): dWx and dWh of a layer share the gate gradient.  push: a is M x k, b0 / b1 are N0 x k / N1 x k, all
+ * column-major; mask0 / mask1 multiply b0 / b1 elementwise (batch size 1 when *_full is 0). */
+typedef struct dyb200_wgrad dyb200_wgrad;
+int dyb200_wgrad_create(dyb200_ctx* ctx, uint32_t M, uint32_t N0, uint32_t N1, uint32_t Kcap, dyb200_wgrad** out);
+int dyb200_wgrad_destroy(dyb200_wgrad* w);
+int dyb200_wgrad_push(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda, const float* b0, uint32_t ldb0,
+                      const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1,
+                      int mask1_full, dyb200_ctx* ctx);
+int dyb200_wgrad_flush(dyb200_wgrad* w, float* C0, uint32_t ldc0, float* C1, uint32_t ldc1, dyb200_ctx* ctx);
 
 /* ---- A14 autobatch ragged movers (same argument meaning as dynet/gpu-ops.h:14-15;
  * src/trg/len are DEVICE arrays of num_seqs entries, as dynet/exec.cc:346-356 uploads them) ---- */

@@ -639,6 +639,33 @@ def test_gemm_3xtf32_accuracy(g):
     assert rel.max() < 2e-6, rel.max()
 
 
+def test_deferred_weight_gradient(g):
+    """dyb200_wgrad: T pushes of (A_t, B0_t .* mask, B1_t) then one flush == sum_t A_t B_t^T added to C (float64 reference)."""
+    r = rng(162)
+    M, N0, N1, T = 192, 96, 40, 5
+    ks = [32, 32, 32, 32, 20]
+    w = g.ctx().wgrad_create(M, N0, N1, sum(ks))
+    C0, C1 = randn(r, N0, M), randn(r, N1, M)
+    ref0, ref1 = C0.astype(np.float64), C1.astype(np.float64)
+    for t, k in enumerate(ks):
+        A, B0, B1 = randn(r, k, M), randn(r, k, N0), randn(r, k, N1)
+        m0 = ((r.random((k, N0)) < 0.8) / 0.8).astype(np.float32)      # full-batch mask
+        m1 = ((r.random((1, N1)) < 0.8) / 0.8).astype(np.float32)      # batch-1 mask
+        g.ctx().wgrad_push(w, k, g.dev(A).data_ptr(), M, g.dev(B0).data_ptr(), N0, g.dev(m0).data_ptr(), 1,
+                           g.dev(B1).data_ptr(), N1, g.dev(m1).data_ptr(), 0)
+        ref0 += (B0 * m0).astype(np.float64).T @ A.astype(np.float64)
+        ref1 += (B1 * m1).astype(np.float64).T @ A.astype(np.float64)
+    C0_, C1_ = g.dev(C0), g.dev(C1)
+    g.ctx().wgrad_flush(w, C0_.data_ptr(), M, C1_.data_ptr(), M)
+    assert_close(g.host(C0_), ref0, TOL_REDUCE, floor=2.0, what="deferred dW0")
+    assert_close(g.host(C1_), ref1, TOL_REDUCE, floor=2.0, what="deferred dW1")
+    g.ctx().wgrad_flush(w, C0_.data_ptr(), M, C1_.data_ptr(), M)   # empty accumulator: no change
+    assert_close(g.host(C0_), ref0, TOL_REDUCE, floor=2.0, what="deferred dW0 after empty flush")
+    import torch
+    torch.cuda.synchronize()
+    g.ctx().wgrad_destroy(w)
+
+
 # ------------------------------------------------------------------ ragged movers
 def _tables(g, srcs, trgs, lens):
     import torch
