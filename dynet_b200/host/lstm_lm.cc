@@ -74,7 +74,15 @@ struct Lm {
   // fused driver: weight-gradient products deferred to the end of the backward pass (one per parameter)
   std::vector<dyb200_wgrad*> wg_layer;   // per layer: A = gate gradient, B0 = x .* mask_x, B1 = h_tm1 .* mask_h
   dyb200_wgrad* wg_R = nullptr;          // A = d(logits), B0 = h_top
+  // CUDA-graph replay of the whole forward + backward pass (optional): the ~1400 launches of a step are
+  // captured once and re-issued with one cudaGraphLaunch; inputs live at fixed addresses (tok, mask_buf).
+  bool use_graph = false;
+  cudaGraphExec_t graph_exec = nullptr;
+  float* graph_loss = nullptr;
+  uint64_t graph_launches = 0;
+  std::vector<float*> mask_buf;          // 2L buffers: mask_x_l (I_l x B), mask_h_l (H x B)
   ~Lm() {
+    if (graph_exec) cudaGraphExecDestroy(graph_exec);
     for (auto w : wg_layer) dyb200_wgrad_destroy(w);
     dyb200_wgrad_destroy(wg_R);
   }
@@ -94,6 +102,11 @@ size_t plan(const dyb200h_lm_config& c, Lm* m, char* base, size_t size) {
   float* zeros = a.take<float>(HB);
   float* ones = a.take<float>(c.B);
   float* scalars = a.take<float>(64);
+  std::vector<float*> mask_buf;
+  for (uint32_t l = 0; l < c.L; ++l) {
+    mask_buf.push_back(a.take<float>((size_t)(l == 0 ? c.E : c.H) * c.B));
+    mask_buf.push_back(a.take<float>(HB));
+  }
   float* dr = a.take<float>(VB);
   // everything below is zeroed by one memset per backward
   a.off = (a.off + 255) & ~(size_t)255;
@@ -108,6 +121,7 @@ size_t plan(const dyb200h_lm_config& c, Lm* m, char* base, size_t size) {
     m->zeros = zeros; m->ones = ones; m->scalars = scalars; m->dr = dr; m->dx = dx; m->dh = dh; m->dc = dc; m->dgates = dgates;
     m->dact = (float*)(base + d0);
     m->dact_bytes = d1 - d0;
+    m->mask_buf = mask_buf;
   }
   return a.off + 256;
 }
@@ -118,15 +132,13 @@ size_t plan(const dyb200h_lm_config& c, Lm* m, char* base, size_t size) {
     if (e__ != cudaSuccess) throw cuda_exception(std::string(#expr) + ": " + cudaGetErrorString(e__)); \
   } while (0)
 
-void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float* const* masks, float* loss_dev) {
+// Everything of a step after its inputs are in place (token ids in m.tok, masks at `masks`).
+void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   const dyb200h_lm_config& c = m.c;
   const uint32_t V = c.V, E = c.E, H = c.H, L = c.L, T = c.T, B = c.B;
   const size_t HB = (size_t)H * B, GB = 4 * HB, VB = (size_t)V * B, EB = (size_t)E * B;
   const Device_GPU& dev = m.dev;
   cudaStream_t st = m.stream;
-  if (c.dropout && !masks) throw std::invalid_argument("dropout is on but no masks were given");
-
-  CU(cudaMemcpyAsync(m.tok, tokens, (size_t)(T + 1) * B * sizeof(uint32_t), on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st));
   // place the target ids of step t where PickNegLogSoftmax expects them: aux_t = {z[B], m[B], ids[B]}
   CU(cudaMemcpy2DAsync(m.aux + 2 * (size_t)B, 3 * (size_t)B * sizeof(float), m.tok + B, (size_t)B * sizeof(uint32_t),
                        (size_t)B * sizeof(uint32_t), T, cudaMemcpyDeviceToDevice, st));
@@ -274,6 +286,47 @@ void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float*
   }
 }
 
+void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float* const* masks, float* loss_dev) {
+  const dyb200h_lm_config& c = m.c;
+  cudaStream_t st = m.stream;
+  if (c.dropout && !masks) throw std::invalid_argument("dropout is on but no masks were given");
+  CU(cudaMemcpyAsync(m.tok, tokens, (size_t)(c.T + 1) * c.B * sizeof(uint32_t), on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st));
+  if (!m.use_graph) { step_body(m, masks, loss_dev); return; }
+
+  // graph mode: masks are staged into the driver's own buffers so that the captured kernels see fixed addresses
+  std::vector<const float*> fixed;
+  if (c.dropout) {
+    for (uint32_t l = 0; l < c.L; ++l)
+      for (int k = 0; k < 2; ++k) {
+        float* dst = m.mask_buf[2 * l + k];
+        size_t n = (size_t)(k == 0 ? (l == 0 ? c.E : c.H) : c.H) * c.B;
+        if (masks[2 * l + k] != dst) CU(cudaMemcpyAsync(dst, masks[2 * l + k], n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+        fixed.push_back(dst);
+      }
+  }
+  if (m.graph_exec && m.graph_loss != loss_dev) { cudaGraphExecDestroy(m.graph_exec); m.graph_exec = nullptr; }
+  if (!m.graph_exec) {
+    if (st == nullptr) throw std::runtime_error("graph mode needs a non-default stream (the legacy stream cannot be captured)");
+    uint64_t l0 = dyb200_ctx_launch_count(m.dev.ctx);
+    CU(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    cudaGraph_t graph = nullptr;
+    try {
+      step_body(m, c.dropout ? fixed.data() : nullptr, loss_dev);
+    } catch (...) {
+      cudaStreamEndCapture(st, &graph);
+      if (graph) cudaGraphDestroy(graph);
+      throw;
+    }
+    CU(cudaStreamEndCapture(st, &graph));
+    cudaError_t e = cudaGraphInstantiate(&m.graph_exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) throw cuda_exception(std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+    m.graph_loss = loss_dev;
+    m.graph_launches = dyb200_ctx_launch_count(m.dev.ctx) - l0;
+  }
+  CU(cudaGraphLaunch(m.graph_exec, st));
+}
+
 }  // namespace
 
 extern "C" {
@@ -368,6 +421,24 @@ int dyb200h_lm_update(void* h) {
   int rc = dyb200_sgd_update(m->params, m->grads, n, m->c.lr, m->c.clip, m->scalars, m->dev.ctx);
   if (rc) m->err = dyb200_last_error(m->dev.ctx);
   return rc;
+}
+
+// Graph mode: capture forward + backward once (on the next call) and replay it afterwards.  Call it after at least one
+// eager step (scratch arena and parameter cache at their final sizes) and only with a non-default stream; while it is on,
+// the library's per-launch GEMM timing must be off.  Returns the kernels per replay through dyb200h_lm_graph_launches.
+int dyb200h_lm_set_graph(void* h, int enable) {
+  Lm* m = (Lm*)h;
+  m->use_graph = enable != 0;
+  if (!enable && m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
+  return DYB200_OK;
+}
+uint64_t dyb200h_lm_graph_launches(void* h) { return ((Lm*)h)->graph_launches; }
+// Device pointers of the 2L mask buffers the graph reads (write the masks there to avoid the staging copy).
+int dyb200h_lm_mask_buffers(void* h, float** out, int cap) {
+  Lm* m = (Lm*)h;
+  int n = (int)m->mask_buf.size();
+  for (int k = 0; k < n && k < cap; ++k) out[k] = m->mask_buf[k];
+  return n;
 }
 
 // Device pointer of the hidden states h[t][l] (T x L x H x B), for parity checks.

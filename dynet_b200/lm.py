@@ -46,6 +46,12 @@ def host_lib():
         L.dyb200h_lm_grad_sumsq.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
         L.dyb200h_lm_update.restype = C.c_int
         L.dyb200h_lm_update.argtypes = [C.c_void_p]
+        L.dyb200h_lm_set_graph.restype = C.c_int
+        L.dyb200h_lm_set_graph.argtypes = [C.c_void_p, C.c_int]
+        L.dyb200h_lm_graph_launches.restype = C.c_uint64
+        L.dyb200h_lm_graph_launches.argtypes = [C.c_void_p]
+        L.dyb200h_lm_mask_buffers.restype = C.c_int
+        L.dyb200h_lm_mask_buffers.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int]
         L.dyb200h_lm_hidden_states.restype = C.c_void_p
         L.dyb200h_lm_hidden_states.argtypes = [C.c_void_p]
         _HOST = L
@@ -168,6 +174,25 @@ class LstmLm:
         self._keep = md
         self.launch_forward_backward(tokens, md)
         return float(self.loss_dev.item())
+
+    def set_graph(self, enable):
+        """Replay forward + backward as one CUDA graph (needs a non-default stream and one eager step before)."""
+        self._check(self.H.dyb200h_lm_set_graph(self.h, int(enable)))
+
+    def graph_launches(self):
+        return int(self.H.dyb200h_lm_graph_launches(self.h))
+
+    def mask_buffers(self):
+        """The driver's own 2L mask buffers as torch views into the workspace (mask_x_l is [B, I_l], mask_h_l [B, H])."""
+        V, E, H, L, T, B = self.dims
+        ptrs = (C.c_void_p * (2 * L))()
+        n = self.H.dyb200h_lm_mask_buffers(self.h, ptrs, 2 * L)
+        out, base = [], self.workspace.data_ptr()
+        for k in range(n):
+            cols = (E if k == 0 else H) if k % 2 == 0 else H
+            off = ptrs[k] - base
+            out.append(self.workspace[off:off + 4 * B * cols].view(self.torch.float32).view(B, cols))
+        return out
 
     def allreduce_grads(self):
         """Sum the flat gradient buffer over the data-parallel ranks (NCCL over NVLink)."""
