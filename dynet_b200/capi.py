@@ -73,6 +73,10 @@ class LstmGatesAttrs(C.Structure):
     _fields_ = [("dropout", C.c_int32), ("weightnoise_std", C.c_float), ("forget_gate_bias", C.c_float)]
 
 
+class AffineAttrs(C.Structure):
+    _fields_ = [("flags", C.c_uint)]
+
+
 class MomentAttrs(C.Structure):
     _fields_ = [("dims", C.c_uint32 * 2), ("ndims", C.c_uint32), ("order", C.c_uint32),
                 ("include_batch_dim", C.c_int32), ("overwrite_n", C.c_uint32)]
@@ -80,7 +84,7 @@ class MomentAttrs(C.Structure):
 
 NODES = ["tanh", "logistic", "rectify", "elu", "cmult", "csum", "cdiv", "softmax", "log_softmax",
          "logsumexp_dim", "logsumexp", "pickneglogsoftmax", "weight_norm", "moment_dim", "std_dim",
-         "layer_norm", "vanilla_lstm_gates", "vanilla_lstm_c", "vanilla_lstm_h"]
+         "layer_norm", "vanilla_lstm_gates", "vanilla_lstm_c", "vanilla_lstm_h", "matmul", "affine_transform"]
 FWD_ONLY = ["lookup"]
 OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200_ctx_check_device_errors",
          "dyb200_ctx_launch_count", "dyb200_version", "dyb200_lookup_accumulate_grads",

@@ -19,7 +19,8 @@ enum GemmEpiMode {
   EPI_STORE = 0,      // C = acc
   EPI_ACCUM = 1,      // C += acc
   EPI_GATES = 2,      // C = act(acc + bias[m] + (H <= m < 2H ? forget_bias : 0)); sigmoid for m < 3H, tanh above
-  EPI_ACCUM_MASK = 3  // C += acc * maskC[m + (maskc_full ? maskc_ld * n : 0)]
+  EPI_ACCUM_MASK = 3, // C += acc * maskC[m + (maskc_full ? maskc_ld * n : 0)]
+  EPI_BIAS = 4        // C = acc + bias[m]   (column vector broadcast over the N columns)
 };
 
 struct GemmEpilogue {

@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(uint32_t M, uint32_t N, int n
       float* c = epi.C + m + (size_t)epi.ldc * n;
       float v = acc[i][j];
       if (epi.mode == EPI_STORE) *c = v;
+      else if (epi.mode == EPI_BIAS) *c = v + epi.bias[m];
       else if (epi.mode == EPI_ACCUM) *c += v;
       else if (epi.mode == EPI_GATES) {
         v += epi.bias[m];

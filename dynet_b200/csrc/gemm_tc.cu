@@ -185,6 +185,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
           if (epi.mode == EPI_STORE) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) if (nb + j < N) dst[(size_t)epi.ldc * j] = v[j];
+          } else if (epi.mode == EPI_BIAS) {
+            const float bias = epi.bias[m];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[(size_t)epi.ldc * j] = v[j] + bias;
           } else if (epi.mode == EPI_GATES) {
             const float bias = epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
             const bool is_tanh = m >= 3 * epi.H;
@@ -237,7 +241,10 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
       }
       float* dst = epi.C + m + (size_t)epi.ldc * n;
       if (epi.mode == EPI_STORE) st4(dst, acc);
-      else if (epi.mode == EPI_ACCUM) {
+      else if (epi.mode == EPI_BIAS) {
+        float4 b = ld4(epi.bias + m);
+        st4(dst, make_float4(acc.x + b.x, acc.y + b.y, acc.z + b.z, acc.w + b.w));
+      } else if (epi.mode == EPI_ACCUM) {
         float4 o = ld4(dst);
         st4(dst, make_float4(o.x + acc.x, o.y + acc.y, o.z + acc.z, o.w + acc.w));
       } else {   // EPI_ACCUM_MASK
@@ -253,6 +260,7 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
     for (uint32_t s2 = 0; s2 < S; ++s2) acc += part[(size_t)s2 * MN + e];
     float* dst = epi.C + m + (size_t)epi.ldc * n;
     if (epi.mode == EPI_STORE) *dst = acc;
+    else if (epi.mode == EPI_BIAS) *dst = acc + epi.bias[m];
     else if (epi.mode == EPI_ACCUM) *dst += acc;
     else if (epi.mode == EPI_GATES) {
       acc += epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
@@ -498,6 +506,7 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     DYB_LAUNCHED(ctx);
     if (S > 1) {
       const int vec = M % 4 == 0 && epi.ldc % 4 == 0 && aligned16(epi.C) && epi.mode != EPI_GATES &&
+                      (epi.mode != EPI_BIAS || aligned16(epi.bias)) &&
                       (epi.mode != EPI_ACCUM_MASK || (aligned16(epi.maskC) && (!epi.maskc_full || epi.maskc_ld % 4 == 0)));
       k_splitk_reduce<<<stream_grid(ctx, (size_t)M * N / 4 + 1, 256), 256, 0, ctx->stream>>>(part, S, M, N, epi, vec);
       DYB_LAUNCHED(ctx);

@@ -172,6 +172,8 @@ struct VanillaLSTMGates : Node {
   DYB200_NODE_COMMON(VanillaLSTMGates)
 };
 struct VanillaLSTMC : Node { DYB200_NODE_COMMON(VanillaLSTMC) };
+struct MatrixMultiply : Node { DYB200_NODE_COMMON(MatrixMultiply) };     // dynet/nodes-matrixmultiply.h
+struct AffineTransform : Node { DYB200_NODE_COMMON(AffineTransform) };   // dynet/nodes-affinetransform.h
 struct VanillaLSTMH : Node { DYB200_NODE_COMMON(VanillaLSTMH) };
 
 // dynet::gpu::parallel_memcpy / parallel_accumulate (dynet/gpu-ops.h:14-15)

@@ -238,6 +238,30 @@ Dim VanillaLSTMH::dim_forward(const std::vector<Dim>& xs) const { return lstm_ch
 SIMPLE_NODE(VanillaLSTMC, vanilla_lstm_c, NO_ATTRS)
 SIMPLE_NODE(VanillaLSTMH, vanilla_lstm_h, NO_ATTRS)
 
+// ---- MatrixMultiply / AffineTransform ----
+Dim MatrixMultiply::dim_forward(const std::vector<Dim>& xs) const {   // dynet/nodes-matrixmultiply.cc:21-27
+  ARG_CHECK(xs.size() == 2, "Failed input count check in MatrixMultiply");
+  ARG_CHECK(xs[0].cols() == xs[1].rows(), "Mismatched input dimensions in MatrixMultiply");
+  ARG_CHECK(xs[0].nd <= 2 && xs[1].nd <= 2, "Cannot multiply tensors of dimension higher than 2");
+  if (xs[1].ndims() == 1) return Dim({xs[0].rows()}, std::max(xs[0].bd, xs[1].bd));
+  return Dim({xs[0].rows(), xs[1].cols()}, std::max(xs[0].bd, xs[1].bd));
+}
+SIMPLE_NODE(MatrixMultiply, matmul, NO_ATTRS)
+Dim AffineTransform::dim_forward(const std::vector<Dim>& xs) const {  // dynet/nodes-affinetransform.cc:23-38
+  ARG_CHECK((xs.size() - 1) % 2 == 0, "Bad number of inputs in AffineTransform");
+  if (xs.size() == 1) return xs[0];
+  ARG_CHECK(xs[0].rows() == xs[1].rows() && xs[1].cols() == xs[2].rows(), "Bad dimensions for AffineTransform");
+  unsigned bd = std::max(std::max(xs[0].bd, xs[1].bd), xs[2].bd);
+  Dim d = xs[2].cols() != 1 ? Dim({xs[0].rows(), xs[2].cols()}, bd) : Dim({xs[0].rows()}, bd);
+  for (size_t i = 3; i < xs.size(); i += 2) {
+    ARG_CHECK(xs[i].cols() == xs[i + 1].rows() && d.rows() == xs[i].rows() && d.cols() == xs[i + 1].cols(),
+              "Bad dimensions for AffineTransform");
+    d.bd = std::max(std::max(d.bd, xs[i].bd), xs[i + 1].bd);
+  }
+  return d;
+}
+SIMPLE_NODE(AffineTransform, affine_transform, NO_ATTRS)
+
 namespace gpu {
 void parallel_memcpy(const Device_GPU& dev, int num_seqs, int max_len, float** src, float** trg, size_t* len) {
   throw_status(dev, dyb200_parallel_memcpy(num_seqs, max_len, src, trg, len, dev.ctx));

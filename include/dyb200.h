@@ -267,6 +267,20 @@ int dyb200_gemm(int transA, int transB, uint32_t M, uint32_t N, uint32_t K, cons
                 uint32_t lda, const float* B, uint32_t ldb, float* C, uint32_t ldc, int accumulate,
                 unsigned flags, dyb200_ctx* ctx);
 
+/* ---- MatrixMultiply and AffineTransform nodes (the callers of the products above) ----
+ * xs of MatrixMultiply = {A, B}; xs of AffineTransform = {bias, A1, B1, A2, B2, ...}: fx = bias + sum_k A_k * B_k,
+ * the bias block tiled over the columns / batch elements of fx when it is smaller (its batch size must then be 1,
+ * as on the reference's CPU path).  A left operand with one batch element multiplies all batch columns of the right
+ * operand in one product; otherwise the batch elements are multiplied one by one.  Backward: bias gradient summed
+ * over the tiles, dA += dEdf * B^T, dB += A^T * dEdf.  attrs may be NULL. */
+typedef struct {
+  unsigned flags; /* DYB200_GEMM_A_IS_PARAM: the left operands are parameter matrices (see dyb200_ctx_param_cache) */
+} dyb200_affine_attrs;
+int dyb200_matmul_fwd(DYB200_FWD_ARGS);            /* MatrixMultiply::forward_dev_impl, dynet/nodes-matrixmultiply.cc:50-56 */
+int dyb200_matmul_bwd(DYB200_BWD_ARGS);            /* dynet/nodes-matrixmultiply.cc:58-74 */
+int dyb200_affine_transform_fwd(DYB200_FWD_ARGS);  /* AffineTransform::forward_dev_impl, dynet/nodes-affinetransform.cc:77-110 */
+int dyb200_affine_transform_bwd(DYB200_BWD_ARGS);  /* dynet/nodes-affinetransform.cc:112-157 */
+
 #ifdef __cplusplus
 }
 #endif

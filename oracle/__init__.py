@@ -343,6 +343,52 @@ def lstm_h_bwd(c_t, gates, dh, i, dxi):
     return dxi
 
 
+# ---------------- MatrixMultiply / AffineTransform ----------------
+class OrcMat(C.Structure):
+    _fields_ = [("v", f32p), ("rows", C.c_uint32), ("cols", C.c_uint32), ("bd", C.c_uint32)]
+
+
+def _mats(xs):
+    """xs: arrays shaped (bd, cols, rows) (column-major matrices, batch slowest); None = absent bias."""
+    arr = (OrcMat * len(xs))()
+    for k, x in enumerate(xs):
+        if x is None:
+            arr[k] = OrcMat(None, 0, 0, 1)
+        else:
+            assert x.ndim == 3 and x.dtype == np.float32 and x.flags.c_contiguous
+            arr[k] = OrcMat(_f(x), x.shape[2], x.shape[1], x.shape[0])
+    return arr
+
+
+def affine_fwd(xs):
+    """fx = xs[0] (tiled) + sum_k xs[2k+1] * xs[2k+2]."""
+    rows = xs[1].shape[2]
+    cols = xs[2].shape[1]
+    bd = max(x.shape[0] for x in xs if x is not None)
+    fx = np.empty((bd, cols, rows), np.float32)
+    rc = lib().orc_affine_fwd(_mats(xs), C.c_uint(len(xs)), _f(fx), C.c_uint32(rows), C.c_uint32(cols), C.c_uint32(bd))
+    if rc:
+        raise ValueError("AffineTransform: bias broadcasting with a mini-batched bias is not implemented")
+    return fx
+
+
+def affine_bwd(xs, dEdf, i, dxi):
+    bd, cols, rows = dEdf.shape
+    rc = lib().orc_affine_bwd(_mats(xs), C.c_uint(len(xs)), _f(dEdf), C.c_uint32(rows), C.c_uint32(cols),
+                              C.c_uint32(bd), C.c_uint(i), _f(dxi))
+    if rc:
+        raise ValueError("AffineTransform: bias broadcasting with a mini-batched bias is not implemented")
+    return dxi
+
+
+def matmul_fwd(a, b):
+    return affine_fwd([None, a, b])
+
+
+def matmul_bwd(a, b, dEdf, i, dxi):
+    return affine_bwd([None, a, b], dEdf, i + 1, dxi)
+
+
 # ---------------- LSTM language model step ----------------
 class LmDims(C.Structure):
     _fields_ = [(k, C.c_uint32) for k in ("V", "E", "H", "L", "T", "B")]

@@ -596,6 +596,73 @@ ORC_API void orc_gemm_tn_acc(const float* l, const float* r, float* y, size_t M,
 ORC_API void orc_gemm_nt_acc(const float* l, const float* r, float* y, size_t M, size_t N, size_t K) { gemm_nt_acc(l, r, y, M, N, K); }
 
 /* ------------------------------------------------------------------ */
+/* MatrixMultiply / AffineTransform nodes                               */
+/* ------------------------------------------------------------------ */
+/* A matrix argument: rows x cols x bd, column-major, batch slowest. */
+typedef struct { const float* v; uint32_t rows, cols, bd; } orc_mat;
+static const float* mat_batch(const orc_mat* t, uint32_t b) { return t->v + (size_t)(b % t->bd) * t->rows * t->cols; }
+
+/* y = beta*y + l*r   (dynet/matrix-multiply.h:45-94, CPU branch without MKL) */
+static void mm_fwd(const orc_mat* l, const orc_mat* r, float* y, uint32_t ybd, float beta) {
+  size_t M = l->rows, K = l->cols, N = r->cols, ysz = M * N * ybd;
+  for (size_t e = 0; e < ysz; ++e) y[e] = beta * y[e];
+  if (l->bd == 1 && r->bd == ybd) gemm_nn_acc(l->v, r->v, y, M, K, N * ybd);
+  else for (uint32_t b = 0; b < ybd; ++b) gemm_nn_acc(mat_batch(l, b), mat_batch(r, b), y + (size_t)b * M * N, M, K, N);
+}
+/* y += l^T * r   (dynet/matrix-multiply.h:117-156) */
+static void mm_transp_l_acc(const orc_mat* l, const orc_mat* r, float* y, uint32_t ybd) {
+  uint32_t max_b = l->bd > r->bd ? l->bd : r->bd;
+  size_t M = l->rows, K = l->cols, N = r->cols;
+  if (l->bd == 1 && ybd == r->bd) gemm_tn_acc(l->v, r->v, y, M, K, N * ybd);
+  else for (uint32_t b = 0; b < max_b; ++b) gemm_tn_acc(mat_batch(l, b), mat_batch(r, b), y + (size_t)(b % ybd) * K * N, M, K, N);
+}
+/* y += l * r^T   (dynet/matrix-multiply.h:180-219) */
+static void mm_transp_r_acc(const orc_mat* l, const orc_mat* r, float* y, uint32_t ybd) {
+  uint32_t max_b = l->bd > r->bd ? l->bd : r->bd;
+  size_t M = l->rows, N = l->cols, K = r->rows;
+  if (ybd == 1 && l->bd == r->bd) gemm_nt_acc(l->v, r->v, y, M, N * l->bd, K);
+  else for (uint32_t b = 0; b < max_b; ++b) gemm_nt_acc(mat_batch(l, b), mat_batch(r, b), y + (size_t)(b % ybd) * M * K, M, N, K);
+}
+
+/* AffineTransform::forward_dev_impl (dynet/nodes-affinetransform.cc:77-110): xs = {bias, A1, B1, A2, B2, ...};
+ * the bias block is tiled over fx (CPU branch: bias.bd must be 1 when it is smaller than fx);
+ * with nxs == 2 and a null bias this is MatrixMultiply::forward_dev_impl (dynet/nodes-matrixmultiply.cc:50-56). */
+ORC_API int orc_affine_fwd(const orc_mat* xs, unsigned nxs, float* fx, uint32_t frows, uint32_t fcols, uint32_t fbd) {
+  size_t fsz = (size_t)frows * fcols * fbd;
+  if (xs[0].v) {
+    size_t bsz = (size_t)xs[0].rows * xs[0].cols * xs[0].bd;
+    if (bsz != fsz && xs[0].bd != 1) return 1;
+    for (size_t o = 0; o < fsz; o += bsz) memcpy(fx + o, xs[0].v, sizeof(float) * (fsz - o < bsz ? fsz - o : bsz));
+  } else {
+    memset(fx, 0, sizeof(float) * fsz);
+  }
+  for (unsigned i = 1; i + 1 < nxs; i += 2) mm_fwd(&xs[i], &xs[i + 1], fx, fbd, 1.0f);
+  return 0;
+}
+/* AffineTransform::backward_dev_impl (dynet/nodes-affinetransform.cc:112-157) and
+ * MatrixMultiply::backward_dev_impl (dynet/nodes-matrixmultiply.cc:58-74); dxi accumulates. */
+ORC_API int orc_affine_bwd(const orc_mat* xs, unsigned nxs, const float* dEdf, uint32_t frows, uint32_t fcols, uint32_t fbd,
+                           unsigned i, float* dxi) {
+  (void)nxs;
+  orc_mat d = {dEdf, frows, fcols, fbd};
+  if (i == 0) {
+    size_t dx = (size_t)xs[0].rows * xs[0].cols * xs[0].bd, df = (size_t)frows * fcols * fbd;
+    if (dx != df && xs[0].bd != 1) return 1;
+    /* every output element sums its chunks in ascending order, in double, rounded once */
+    for (size_t r = 0; r < dx; ++r) {
+      double acc = 0.0;
+      for (size_t o = r; o < df; o += dx) acc += dEdf[o];
+      dxi[r] += (float)acc;
+    }
+  } else if (i % 2 == 1) {
+    mm_transp_r_acc(&d, &xs[i + 1], dxi, xs[i].bd);
+  } else {
+    mm_transp_l_acc(&xs[i - 1], &d, dxi, xs[i].bd);
+  }
+  return 0;
+}
+
+/* ------------------------------------------------------------------ */
 /* A1: VanillaLSTMGates                                                 */
 /* ------------------------------------------------------------------ */
 /* Inputs x_1..x_k (dims xdims[j], batch B) are concatenated along dim 0 to I

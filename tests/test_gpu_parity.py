@@ -712,3 +712,81 @@ def test_parallel_accumulate_with_shared_targets(g, n_seq):
     g.ctx().parallel_accumulate(n, max(L), sp.data_ptr(), tp.data_ptr(), ln.data_ptr())
     for a, b in zip(trg_bufs, want):   # later sort passes continue from the target's running value
         assert torch.equal(a, b)
+
+
+# ------------------------------------------------------------------ MatrixMultiply / AffineTransform
+# (bd, cols, rows) of {bias, A, B[, A2, B2]}; None = MatrixMultiply.  The first block are the shapes of the
+# reference's gradient tests (tests/test-nodes.cc:431-505); the rest reach the tensor-pipe kernel.
+AFFINE_SHAPES = {
+    "multiply": [None, (1, 1, 3), (1, 3, 1)],
+    "multiply_batch": [None, (1, 1, 3), (2, 3, 1)],
+    "affine": [(1, 1, 3), (1, 1, 3), (1, 1, 1)],
+    "affine_batch": [(1, 1, 3), (2, 1, 3), (1, 1, 1)],
+    "affine_batch_col": [(1, 3, 1), (1, 1, 1), (2, 3, 1)],
+    "affine_batch2": [(2, 3, 1), (1, 1, 1), (1, 3, 1)],
+    "affine_batch3": [(1, 1, 3), (1, 3, 3), (2, 1, 3)],
+    "two_products": [(1, 1, 4), (1, 3, 4), (3, 2, 3), (1, 5, 4), (3, 2, 5)],
+    "both_batched": [(1, 1, 4), (3, 2, 4), (3, 5, 2)],
+    "full_bias": [(5, 1, 130), (1, 70, 130), (5, 1, 70)],
+    "projection": [(1, 1, 1000), (1, 256, 1000), (192, 1, 256)],          # b + R h, the output layer's shape class
+    "projection_odd": [(1, 1, 1001), (1, 250, 1001), (67, 1, 250)],
+    "matmul_wide": [None, (1, 384, 512), (1, 640, 384)],
+    "matmul_batched_left": [None, (3, 128, 256), (3, 130, 128)],
+    "matrix_bias_tiled": [(1, 4, 256), (1, 128, 256), (6, 4, 128)],
+}
+
+
+@pytest.mark.parametrize("case", sorted(AFFINE_SHAPES))
+def test_affine_matmul(oracle, g, capi, case):
+    r = rng(sum(map(ord, case)))
+    shapes = AFFINE_SHAPES[case]
+    xs = [None if s is None else randn(r, *s, scale=0.5) for s in shapes]
+    node = "matmul" if xs[0] is None else "affine_transform"
+    args = xs[1:] if xs[0] is None else xs
+    y_ref = oracle.affine_fwd(xs)
+    dev_args = [g.dev(a) for a in args]
+    ts = [g.T(d, [a.shape[2], a.shape[1]], a.shape[0]) for d, a in zip(dev_args, args)]
+    y = g.dev(np.full_like(y_ref, 7.0))
+    ty = g.T(y, [y_ref.shape[2], y_ref.shape[1]], y_ref.shape[0])
+    g.ctx().fwd(node, ts, ty)
+    assert_close(g.host(y), y_ref, TOL_REDUCE, floor=GEMM_FLOOR * 10, what=case + " fwd")
+    dy = randn(r, *y_ref.shape)
+    tdy = g.T(g.dev(dy), [dy.shape[2], dy.shape[1]], dy.shape[0])
+    off = 1 if xs[0] is None else 0
+    for i, a in enumerate(args):
+        d0 = randn(r, *a.shape)
+        want = oracle.affine_bwd(xs, dy, i + off, d0.copy())
+        dx = g.dev(d0)
+        g.ctx().bwd(node, ts, ty, tdy, i, g.T(dx, [a.shape[2], a.shape[1]], a.shape[0]))
+        scale = max(1.0, float(np.abs(want).max()) * 0.05)
+        assert_close(g.host(dx), want, TOL_REDUCE, floor=scale, what="%s bwd arg %d" % (case, i))
+    assert g.ctx().device_errors() == 0
+
+
+def test_affine_param_cache_matches_uncached(g, capi):
+    """With the parameter cache on and the left operand flagged as a parameter, results are bitwise the same."""
+    r = rng(77)
+    R, h, b = randn(r, 1, 256, 1024, scale=0.1), randn(r, 128, 1, 256), randn(r, 1, 1, 1024)
+    dev_args = [g.dev(a) for a in (b, R, h)]
+    ts = [g.T(d, [a.shape[2], a.shape[1]], a.shape[0]) for d, a in zip(dev_args, (b, R, h))]
+    y0, y1 = g.dev(np.zeros((128, 1, 1024), np.float32)), g.dev(np.zeros((128, 1, 1024), np.float32))
+    g.ctx().fwd("affine_transform", ts, g.T(y0, [1024], 128))
+    g.ctx().param_cache(True)
+    try:
+        at = capi.AffineAttrs(1)
+        for _ in range(2):
+            g.ctx().fwd("affine_transform", ts, g.T(y1, [1024], 128), at)
+        assert np.array_equal(g.host(y0), g.host(y1))
+    finally:
+        g.ctx().param_cache(False)
+
+
+def test_affine_rejects_bad_shapes(g, capi):
+    r = rng(78)
+    b, A, Bm = randn(r, 2, 1, 3), randn(r, 1, 4, 3), randn(r, 2, 5, 4)
+    y = g.dev(np.zeros((2, 5, 3), np.float32))
+    ts = [g.T(g.dev(a), [a.shape[2], a.shape[1]], a.shape[0]) for a in (b, A, Bm)]
+    with pytest.raises(ValueError):     # mini-batched bias broadcast over columns: refused as on the CPU path
+        g.ctx().fwd("affine_transform", ts, g.T(y, [3, 5], 2))
+    with pytest.raises(ValueError):     # inner dimensions differ
+        g.ctx().fwd("matmul", [ts[1], ts[1]], g.T(y, [3, 5], 2))

@@ -290,3 +290,59 @@ def test_fused_chain_equals_unfused_builder_math(oracle):
         h2 = o_ * np.tanh(c2)
         assert_close(h, h2, 1e-5, floor=1e-2, what="h_%d" % t)
         assert_close(c, c2, 1e-5, floor=1e-2, what="c_%d" % t)
+
+
+# ---------------------------------------------------------------- MatrixMultiply / AffineTransform
+def _np_affine(xs):
+    """float64 numpy statement of bias + sum A_k B_k with DyNet's batch rules (arrays are (bd, cols, rows))."""
+    bd = max(x.shape[0] for x in xs if x is not None)
+    rows, cols = xs[1].shape[2], xs[2].shape[1]
+    y = np.zeros((bd, cols, rows))
+    if xs[0] is not None:
+        y += np.resize(xs[0].astype(np.float64).ravel(), y.size).reshape(y.shape)
+    for k in range(1, len(xs), 2):
+        for b in range(bd):
+            A = xs[k][b % xs[k].shape[0]].astype(np.float64).T          # rows x K
+            Bm = xs[k + 1][b % xs[k + 1].shape[0]].astype(np.float64).T  # K x cols
+            y[b] += (A @ Bm).T
+    return y
+
+
+# shapes of tests/test-nodes.cc:431-505 (multiply, multiply_batch, affine, affine_batch, affine_batch_col,
+# affine_batch2, affine_batch3) as (bd, cols, rows) triples for {bias, A, B}; None = MatrixMultiply
+AFFINE_CASES = {
+    "multiply": [None, (1, 1, 3), (1, 3, 1)],
+    "multiply_batch": [None, (1, 1, 3), (2, 3, 1)],
+    "affine": [(1, 1, 3), (1, 1, 3), (1, 1, 1)],
+    "affine_batch": [(1, 1, 3), (2, 1, 3), (1, 1, 1)],
+    "affine_batch_col": [(1, 3, 1), (1, 1, 1), (2, 3, 1)],
+    "affine_batch2": [(2, 3, 1), (1, 1, 1), (1, 3, 1)],
+    "affine_batch3": [(1, 1, 3), (1, 3, 3), (2, 1, 3)],
+    "two_products": [(1, 1, 4), (1, 3, 4), (3, 2, 3), (1, 5, 4), (3, 2, 5)],
+    "both_batched": [(1, 1, 4), (3, 2, 4), (3, 5, 2)],
+}
+
+
+@pytest.mark.parametrize("case", sorted(AFFINE_CASES))
+def test_affine_matmul_value_and_gradient(oracle, case):
+    r = rng(sum(map(ord, case)))
+    xs = [None if s is None else randn(r, *s) + 0.3 for s in AFFINE_CASES[case]]
+    y = oracle.affine_fwd(xs)
+    assert_close(y, _np_affine(xs), 1e-5, floor=1.0, what=case)
+    live = [k for k, x in enumerate(xs) if x is not None]
+
+    def f(vals):
+        full = list(xs)
+        for k, v in zip(live, vals):
+            full[k] = v
+        return sq(oracle.affine_fwd(full))
+
+    fd_check(f, [xs[k] for k in live],
+             lambda j: oracle.affine_bwd(xs, 2 * y, live[j], np.zeros_like(xs[live[j]])))
+
+
+def test_affine_rejects_batched_bias_broadcast(oracle):
+    r = rng(5)
+    xs = [randn(r, 2, 1, 3), randn(r, 1, 4, 3), randn(r, 2, 5, 4)]   # bias {3} x2 under a {3,5} x2 result
+    with pytest.raises(ValueError):
+        oracle.affine_fwd(xs)
