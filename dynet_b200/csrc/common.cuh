@@ -34,7 +34,7 @@ struct dyb200_ctx {
   int param_cache_on;
   uint64_t param_version, param_tick;
   struct ParamPack {
-    const float* src; uint32_t ld, rows, K, pitch; int k_is_fast;
+    const float* src; const float* src2; uint32_t ld, rows, rows2, K, pitch; int k_is_fast;   // src2 / rows2: a second matrix stacked below the first
     uint64_t version, last_use;
     float *hi, *lo; size_t floats;
   } param_pack[24];

@@ -28,7 +28,21 @@ struct GemmEpilogue {
   float* C; uint32_t ldc;
   const float* bias; uint32_t H; float forget_bias;
   const float* maskC; uint32_t maskc_ld; int maskc_full;
+  // Optional second destination: rows m >= split_m go to C2 (row m - split_m) with their own leading dimension and
+  // mask; split_m = 0 disables it.  Lets one product with stacked A operands ([Wx; Wh]^T) feed two tensors.
+  uint32_t split_m = 0;
+  float* C2 = nullptr; uint32_t ldc2 = 0;
+  const float* maskC2 = nullptr; uint32_t maskc2_ld = 0; int maskc2_full = 0;
 };
+// Row m of the product -> destination pointer of column 0, leading dimension and mask of that row.
+struct EpiRow { float* c; uint32_t ldc; const float* mask; uint32_t mask_ld; int mask_full; };
+__host__ __device__ inline EpiRow epi_row(const GemmEpilogue& e, uint32_t m) {
+  if (e.split_m && m >= e.split_m) {
+    const uint32_t r = m - e.split_m;
+    return EpiRow{e.C2 + r, e.ldc2, e.maskC2 ? e.maskC2 + r : nullptr, e.maskc2_ld, e.maskc2_full};
+  }
+  return EpiRow{e.C + m, e.ldc, e.maskC ? e.maskC + m : nullptr, e.maskc_ld, e.maskc_full};
+}
 
 // fp32 CUDA-core path: any shape, any alignment.
 int dyb200_gemm_simt(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const GemmPair* pairs, const GemmEpilogue& epi);
@@ -41,13 +55,31 @@ int dyb200_gemm_fused(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const
 
 // ---- pieces of the tensor path, for entry points that reuse one packed operand in several products ----
 struct PackedOp { float* hi; float* lo; uint32_t rows, K, pitch; };   // K-major TF32 hi / lo planes
+// A queue of packing work that one kernel launch executes (several small operands per launch).
+constexpr int kMaxPackJobs = 8;
+struct PackJob {
+  const float* src; const float* mask; float* hi; float* lo;
+  uint32_t ld, rows, K, mask_ld, pitch, gx;
+  int k_is_fast, mask_full, vec;
+};
+struct PackJobs { PackJob job[kMaxPackJobs]; uint32_t start[kMaxPackJobs + 1]; int n; };
+inline void dyb200_tc_pack_begin(PackJobs* b) { b->n = 0; b->start[0] = 0; }
+int dyb200_tc_pack_flush(dyb200_ctx* ctx, PackJobs* batch);
 // Packs `rows x K` (element (r, k) at src[k + ld*r] when k_is_fast, else src[r + ld*k]) times an optional mask
-// into planes taken from the scratch arena (valid until the current entry point returns).
+// into planes taken from the scratch arena (valid until the current entry point returns).  With a batch the work is
+// only queued: the planes are filled when the batch is flushed.
 int dyb200_tc_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K,
-                   const float* mask, uint32_t mask_ld, int mask_full, PackedOp* out);
+                   const float* mask, uint32_t mask_ld, int mask_full, PackedOp* out, PackJobs* batch = nullptr);
 // Same for a parameter matrix: served from the parameter cache when it is on.
 int dyb200_tc_param(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, PackedOp* out);
+// Two parameter matrices with the same K and leading dimension stacked along the rows: rows [0, rows) from src,
+// rows [rows, rows + rows2) from src2.
+int dyb200_tc_param2(dyb200_ctx* ctx, const float* src, uint32_t rows, const float* src2, uint32_t rows2, uint32_t ld,
+                     bool k_is_fast, uint32_t K, PackedOp* out);
 int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const PackedOp* A, const PackedOp* B,
                           const GemmEpilogue& epi);
 bool dyb200_tc_eligible(uint32_t M, uint32_t N, double flops);
 struct dyb200_wgrad;
+int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda, const float* b0, uint32_t ldb0,
+                              const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1,
+                              int mask1_full, dyb200_ctx* ctx, PackJobs* batch);

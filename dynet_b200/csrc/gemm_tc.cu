@@ -181,37 +181,40 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         }
         if (m < M) {
           const uint32_t nb = n0 + c * 32;
-          float* dst = epi.C + m + (size_t)epi.ldc * nb;
+          const EpiRow row = epi_row(epi, m);
+          const size_t ldc = row.ldc;
+          float* dst = row.c + ldc * nb;
           if (epi.mode == EPI_STORE) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[(size_t)epi.ldc * j] = v[j];
+            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = v[j];
           } else if (epi.mode == EPI_BIAS) {
             const float bias = epi.bias[m];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[(size_t)epi.ldc * j] = v[j] + bias;
+            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = v[j] + bias;
           } else if (epi.mode == EPI_GATES) {
             const float bias = epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
             const bool is_tanh = m >= 3 * epi.H;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               float x = v[j] + bias;
-              if (nb + j < N) dst[(size_t)epi.ldc * j] = is_tanh ? tanhf(x) : sigmoidf_dev(x);
+              if (nb + j < N) dst[ldc * j] = is_tanh ? tanhf(x) : sigmoidf_dev(x);
             }
           } else {
             // read-modify-write: issue all loads of the chunk before the first dependent store
             float old[32], mk[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) old[j] = nb + j < N ? __ldcg(dst + (size_t)epi.ldc * j) : 0.f;
+            for (int j = 0; j < 32; ++j) old[j] = nb + j < N ? __ldcg(dst + ldc * j) : 0.f;
             if (epi.mode == EPI_ACCUM_MASK) {
-              const float* mp = epi.maskC + m + (epi.maskc_full ? (size_t)epi.maskc_ld * nb : 0);
+              const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
+              const float* mp = row.mask + mstep * nb;
 #pragma unroll
-              for (int j = 0; j < 32; ++j) mk[j] = (nb + j < N) ? __ldg(mp + (epi.maskc_full ? (size_t)epi.maskc_ld * j : 0)) : 0.f;
+              for (int j = 0; j < 32; ++j) mk[j] = (nb + j < N) ? __ldg(mp + mstep * j) : 0.f;
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) mk[j] = 1.f;
             }
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[(size_t)epi.ldc * j] = old[j] + v[j] * mk[j];
+            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = old[j] + v[j] * mk[j];
           }
         }
       }
@@ -239,7 +242,8 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
         float4 v = ld4_stream(part + (size_t)s2 * MN + e);
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
       }
-      float* dst = epi.C + m + (size_t)epi.ldc * n;
+      const EpiRow row = epi_row(epi, m);   // split_m is a multiple of 4 here: the four rows share a destination
+      float* dst = row.c + (size_t)row.ldc * n;
       if (epi.mode == EPI_STORE) st4(dst, acc);
       else if (epi.mode == EPI_BIAS) {
         float4 b = ld4(epi.bias + m);
@@ -248,7 +252,7 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
         float4 o = ld4(dst);
         st4(dst, make_float4(o.x + acc.x, o.y + acc.y, o.z + acc.z, o.w + acc.w));
       } else {   // EPI_ACCUM_MASK
-        float4 o = ld4(dst), mk = ld4(epi.maskC + m + (epi.maskc_full ? (size_t)epi.maskc_ld * n : 0));
+        float4 o = ld4(dst), mk = ld4(row.mask + (row.mask_full ? (size_t)row.mask_ld * n : 0));
         st4(dst, make_float4(o.x + acc.x * mk.x, o.y + acc.y * mk.y, o.z + acc.z * mk.z, o.w + acc.w * mk.w));
       }
     }
@@ -258,7 +262,8 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
     const uint32_t m = (uint32_t)(e % M), n = (uint32_t)(e / M);
     float acc = 0.f;
     for (uint32_t s2 = 0; s2 < S; ++s2) acc += part[(size_t)s2 * MN + e];
-    float* dst = epi.C + m + (size_t)epi.ldc * n;
+    const EpiRow row = epi_row(epi, m);
+    float* dst = row.c + (size_t)row.ldc * n;
     if (epi.mode == EPI_STORE) *dst = acc;
     else if (epi.mode == EPI_BIAS) *dst = acc + epi.bias[m];
     else if (epi.mode == EPI_ACCUM) *dst += acc;
@@ -266,7 +271,7 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
       acc += epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
       *dst = m < 3 * epi.H ? sigmoidf_dev(acc) : tanhf(acc);
     } else {
-      *dst += acc * epi.maskC[m + (epi.maskc_full ? (size_t)epi.maskc_ld * n : 0)];
+      *dst += acc * row.mask[row.mask_full ? (size_t)row.mask_ld * n : 0];
     }
   }
 }
@@ -279,40 +284,50 @@ __device__ __forceinline__ void split_tf32(float v, float& hi, float& lo) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(v - hi));
   lo = __uint_as_float(l);
 }
-// Source element (r, k) at src[k + ld * r] (k is the fast index): rows stay rows.
-__global__ void __launch_bounds__(256) k_pack_straight(const float* __restrict__ src, uint32_t ld, uint32_t rows, uint32_t K,
-                                                      const float* __restrict__ mask, uint32_t mask_ld, int mask_full,
-                                                      float* __restrict__ hi, float* __restrict__ lo, uint32_t pitch, int vec) {
-  const uint32_t r = blockIdx.y;
-  if (vec) {
-    for (uint32_t k = (blockIdx.x * 256 + threadIdx.x) * 4; k < K; k += gridDim.x * 1024) {
-      float4 v = ld4(src + k + (size_t)ld * r);
-      if (mask) {
-        float4 mk = ld4(mask + k + (mask_full ? (size_t)mask_ld * r : 0));
-        v.x *= mk.x; v.y *= mk.y; v.z *= mk.z; v.w *= mk.w;
-      }
-      float4 h, l;
-      split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
-      st4(hi + k + (size_t)pitch * r, h);
-      st4(lo + k + (size_t)pitch * r, l);
-    }
-  } else {
-    for (uint32_t k = blockIdx.x * 256 + threadIdx.x; k < K; k += gridDim.x * 256) {
-      float v = src[k + (size_t)ld * r];
-      if (mask) v *= mask[k + (mask_full ? (size_t)mask_ld * r : 0)];
-      float h, l;
-      split_tf32(v, h, l);
-      hi[k + (size_t)pitch * r] = h;
-      lo[k + (size_t)pitch * r] = l;
-    }
-  }
-}
-// Source element (r, k) at src[r + ld * k] (r is the fast index): 32 x 32 tiles transposed through shared memory.
-__global__ void __launch_bounds__(256) k_pack_transpose(const float* __restrict__ src, uint32_t ld, uint32_t rows, uint32_t K,
-                                                       const float* __restrict__ mask, uint32_t mask_ld, int mask_full,
-                                                       float* __restrict__ hi, float* __restrict__ lo, uint32_t pitch) {
+// One launch packs up to kMaxPackJobs operands.  A job is cut into units of one CTA each: for a source whose
+// k index is fast (element (r, k) at src[k + ld * r]) a unit is 1024 consecutive k of one row; for a source whose
+// row index is fast (element (r, k) at src[r + ld * k]) a unit is a 32 x 32 tile transposed through shared memory.
+__global__ void __launch_bounds__(256) k_pack_multi(const PackJobs jobs) {
   __shared__ float tile[32][33];
-  const uint32_t r0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  int j = 0;
+#pragma unroll
+  for (int q = 1; q < kMaxPackJobs; ++q) if (q < jobs.n && blockIdx.x >= jobs.start[q]) j = q;
+  const PackJob& job = jobs.job[j];
+  const uint32_t unit = blockIdx.x - jobs.start[j];
+  const float* __restrict__ src = job.src;
+  const float* __restrict__ mask = job.mask;
+  float* __restrict__ hi = job.hi;
+  float* __restrict__ lo = job.lo;
+  const uint32_t ld = job.ld, rows = job.rows, K = job.K, pitch = job.pitch, mask_ld = job.mask_ld;
+  const int mask_full = job.mask_full;
+  if (job.k_is_fast) {
+    const uint32_t r = unit / job.gx, bx = unit % job.gx;
+    if (job.vec) {
+      const uint32_t k = (bx * 256 + threadIdx.x) * 4;
+      if (k < K) {
+        float4 v = ld4(src + k + (size_t)ld * r);
+        if (mask) {
+          float4 mk = ld4(mask + k + (mask_full ? (size_t)mask_ld * r : 0));
+          v.x *= mk.x; v.y *= mk.y; v.z *= mk.z; v.w *= mk.w;
+        }
+        float4 h, l;
+        split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+        st4(hi + k + (size_t)pitch * r, h);
+        st4(lo + k + (size_t)pitch * r, l);
+      }
+    } else {
+      for (uint32_t k = bx * 1024 + threadIdx.x; k < min(K, (bx + 1) * 1024); k += 256) {
+        float v = src[k + (size_t)ld * r];
+        if (mask) v *= mask[k + (mask_full ? (size_t)mask_ld * r : 0)];
+        float h, l;
+        split_tf32(v, h, l);
+        hi[k + (size_t)pitch * r] = h;
+        lo[k + (size_t)pitch * r] = l;
+      }
+    }
+    return;
+  }
+  const uint32_t r0 = (unit % job.gx) * 32, k0 = (unit / job.gx) * 32;
   const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -365,45 +380,60 @@ int make_map(dyb200_ctx* ctx, EncodeTiledFn enc, CUtensorMap* map, float* plane,
   return DYB200_OK;
 }
 
-int pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, const float* mask,
-         uint32_t mask_ld, int mask_full, float* hi, float* lo, uint32_t pitch) {
-  if (k_is_fast) {
-    int vec = (K % 4 == 0) && (ld % 4 == 0) && aligned16(src) && (!mask || ((mask_ld % 4 == 0 || !mask_full) && aligned16(mask)));
-    unsigned gx = (K + 1023) / 1024;
-    if (gx < 1) gx = 1;
-    // grid.y is limited to 65535 rows per launch
-    for (uint32_t r0 = 0; r0 < rows; r0 += 65535) {
-      uint32_t nr = rows - r0 < 65535 ? rows - r0 : 65535;
-      k_pack_straight<<<dim3(gx, nr), 256, 0, ctx->stream>>>(src + (size_t)ld * r0, ld, nr, K,
-                                                           mask ? mask + (mask_full ? (size_t)mask_ld * r0 : 0) : nullptr, mask_ld,
-                                                           mask_full, hi + (size_t)pitch * r0, lo + (size_t)pitch * r0, pitch, vec);
-      DYB_LAUNCHED(ctx);
-    }
-  } else {
-    dim3 grid((rows + 31) / 32, (K + 31) / 32);
-    DYB_CHECK_ARG(ctx, grid.y <= 65535, "pack: K too large");
-    k_pack_transpose<<<grid, 256, 0, ctx->stream>>>(src, ld, rows, K, mask, mask_ld, mask_full, hi, lo, pitch);
-    DYB_LAUNCHED(ctx);
-  }
+int pack_flush_impl(dyb200_ctx* ctx, PackJobs* jobs) {
+  if (jobs->n == 0) return DYB200_OK;
+  const uint32_t total = jobs->start[jobs->n];
+  k_pack_multi<<<total, 256, 0, ctx->stream>>>(*jobs);
+  jobs->n = 0;
+  jobs->start[0] = 0;
+  DYB_LAUNCHED(ctx);
   return DYB200_OK;
+}
+
+// Queues one operand in `batch` (launching the queue first when it is full); with batch == nullptr it is packed at once.
+int pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, const float* mask,
+         uint32_t mask_ld, int mask_full, float* hi, float* lo, uint32_t pitch, PackJobs* batch = nullptr) {
+  if (rows == 0 || K == 0) return DYB200_OK;
+  PackJobs local;
+  local.n = 0; local.start[0] = 0;
+  PackJobs* q = batch ? batch : &local;
+  if (q->n == kMaxPackJobs) { int rc = pack_flush_impl(ctx, q); if (rc) return rc; }
+  PackJob& j = q->job[q->n];
+  j.src = src; j.mask = mask; j.hi = hi; j.lo = lo;
+  j.ld = ld; j.rows = rows; j.K = K; j.mask_ld = mask_ld; j.pitch = pitch;
+  j.k_is_fast = k_is_fast ? 1 : 0; j.mask_full = mask_full;
+  uint64_t units;
+  if (k_is_fast) {
+    j.vec = (K % 4 == 0) && (ld % 4 == 0) && aligned16(src) && (!mask || ((mask_ld % 4 == 0 || !mask_full) && aligned16(mask)));
+    j.gx = (K + 1023) / 1024;
+    units = (uint64_t)j.gx * rows;
+  } else {
+    j.vec = 0;
+    j.gx = (rows + 31) / 32;
+    units = (uint64_t)j.gx * ((K + 31) / 32);
+  }
+  DYB_CHECK_ARG(ctx, (uint64_t)q->start[q->n] + units < 0x7fffffffull, "pack: operand too large (%u x %u)", rows, K);
+  q->start[q->n + 1] = q->start[q->n] + (uint32_t)units;
+  q->n++;
+  return batch ? DYB200_OK : pack_flush_impl(ctx, q);
 }
 
 inline uint32_t round_up(uint32_t x, uint32_t m) { return (x + m - 1) / m * m; }
 
 // Returns the cached packed form of a parameter matrix, packing it first if it is new or stale.
 int cached_param_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, uint32_t pitch,
-                      float** hi, float** lo) {
+                      float** hi, float** lo, const float* src2 = nullptr, uint32_t rows2 = 0) {
   const int cap = (int)(sizeof(ctx->param_pack) / sizeof(ctx->param_pack[0]));
   dyb200_ctx::ParamPack* hit = nullptr;
   dyb200_ctx::ParamPack* victim = &ctx->param_pack[0];
   for (int k = 0; k < cap; ++k) {
     dyb200_ctx::ParamPack* e = &ctx->param_pack[k];
-    if (e->hi && e->src == src && e->ld == ld && e->rows == rows && e->K == K && e->k_is_fast == (int)k_is_fast) { hit = e; break; }
+    if (e->hi && e->src == src && e->src2 == src2 && e->rows2 == rows2 && e->ld == ld && e->rows == rows && e->K == K && e->k_is_fast == (int)k_is_fast) { hit = e; break; }
     if (!e->hi) { if (victim->hi) victim = e; }
     else if (victim->hi && e->last_use < victim->last_use) victim = e;
   }
   dyb200_ctx::ParamPack* e = hit ? hit : victim;
-  const size_t floats = (size_t)rows * pitch;
+  const size_t floats = (size_t)(rows + rows2) * pitch;
   if (!hit) {
     if (e->hi && e->floats < floats) {   // evicted entry is too small: its buffers may still be read by queued kernels
       DYB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -419,11 +449,15 @@ int cached_param_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_
       }
       e->floats = floats;
     }
-    e->src = src; e->ld = ld; e->rows = rows; e->K = K; e->pitch = pitch; e->k_is_fast = (int)k_is_fast;
+    e->src = src; e->src2 = src2; e->rows2 = rows2; e->ld = ld; e->rows = rows; e->K = K; e->pitch = pitch; e->k_is_fast = (int)k_is_fast;
     e->version = ~0ull;
   }
   if (e->version != ctx->param_version) {
-    int rc = pack(ctx, src, ld, k_is_fast, rows, K, nullptr, 0, 0, e->hi, e->lo, pitch);
+    PackJobs batch;
+    dyb200_tc_pack_begin(&batch);
+    int rc = pack(ctx, src, ld, k_is_fast, rows, K, nullptr, 0, 0, e->hi, e->lo, pitch, &batch);
+    if (!rc && rows2) rc = pack(ctx, src2, ld, k_is_fast, rows2, K, nullptr, 0, 0, e->hi + (size_t)rows * pitch, e->lo + (size_t)rows * pitch, pitch, &batch);
+    if (!rc) rc = pack_flush_impl(ctx, &batch);
     if (rc) return rc;
     e->version = ctx->param_version;
   }
@@ -435,8 +469,10 @@ int cached_param_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_
 }  // namespace
 
 // ---- building blocks shared with the fused LSTM entry points ----------------------------------
+int dyb200_tc_pack_flush(dyb200_ctx* ctx, PackJobs* batch) { return pack_flush_impl(ctx, batch); }
+
 int dyb200_tc_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K,
-                   const float* mask, uint32_t mask_ld, int mask_full, PackedOp* out) {
+                   const float* mask, uint32_t mask_ld, int mask_full, PackedOp* out, PackJobs* batch) {
   const uint32_t pitch = round_up(K, 32);
   void* buf;
   int rc = dyb200_scratch(ctx, (size_t)2 * rows * pitch * sizeof(float) + 256, &buf);
@@ -444,13 +480,31 @@ int dyb200_tc_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fas
   out->hi = (float*)buf;
   out->lo = (float*)(((uintptr_t)(out->hi + (size_t)rows * pitch) + 255) & ~(uintptr_t)255);
   out->rows = rows; out->K = K; out->pitch = pitch;
-  return pack(ctx, src, ld, k_is_fast, rows, K, mask, mask_ld, mask_full, out->hi, out->lo, pitch);
+  return pack(ctx, src, ld, k_is_fast, rows, K, mask, mask_ld, mask_full, out->hi, out->lo, pitch, batch);
 }
 
 int dyb200_tc_param(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, PackedOp* out) {
-  if (!ctx->param_cache_on) return dyb200_tc_pack(ctx, src, ld, k_is_fast, rows, K, nullptr, 0, 0, out);
+  if (!ctx->param_cache_on) return dyb200_tc_pack(ctx, src, ld, k_is_fast, rows, K, nullptr, 0, 0, out, nullptr);
   out->rows = rows; out->K = K; out->pitch = round_up(K, 32);
   return cached_param_pack(ctx, src, ld, k_is_fast, rows, K, out->pitch, &out->hi, &out->lo);
+}
+
+int dyb200_tc_param2(dyb200_ctx* ctx, const float* src, uint32_t rows, const float* src2, uint32_t rows2, uint32_t ld,
+                     bool k_is_fast, uint32_t K, PackedOp* out) {
+  const uint32_t pitch = round_up(K, 32);
+  out->rows = rows + rows2; out->K = K; out->pitch = pitch;
+  if (ctx->param_cache_on) return cached_param_pack(ctx, src, ld, k_is_fast, rows, K, pitch, &out->hi, &out->lo, src2, rows2);
+  void* buf;
+  int rc = dyb200_scratch(ctx, (size_t)2 * out->rows * pitch * sizeof(float) + 256, &buf);
+  if (rc) return rc;
+  out->hi = (float*)buf;
+  out->lo = (float*)(((uintptr_t)(out->hi + (size_t)out->rows * pitch) + 255) & ~(uintptr_t)255);
+  PackJobs batch;
+  dyb200_tc_pack_begin(&batch);
+  rc = pack(ctx, src, ld, k_is_fast, rows, K, nullptr, 0, 0, out->hi, out->lo, pitch, &batch);
+  if (!rc) rc = pack(ctx, src2, ld, k_is_fast, rows2, K, nullptr, 0, 0, out->hi + (size_t)rows * pitch, out->lo + (size_t)rows * pitch, pitch, &batch);
+  if (!rc) rc = pack_flush_impl(ctx, &batch);
+  return rc;
 }
 
 int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const PackedOp* A, const PackedOp* B,
@@ -496,7 +550,7 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     rc = dyb200_scratch(ctx, (size_t)S * M * N * sizeof(float), &pw);
     if (rc) return rc;
     part = (float*)pw;
-    kepi = GemmEpilogue{EPI_STORE, part, M, nullptr, 0, 0.f, nullptr, 0, 0};
+    kepi = GemmEpilogue{EPI_STORE, part, M, nullptr, 0, 0.f, nullptr, 0, 0};   // (no second destination)
     grid.z = S;
   }
   {
@@ -505,9 +559,12 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     k_gemm_tc<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
     DYB_LAUNCHED(ctx);
     if (S > 1) {
-      const int vec = M % 4 == 0 && epi.ldc % 4 == 0 && aligned16(epi.C) && epi.mode != EPI_GATES &&
-                      (epi.mode != EPI_BIAS || aligned16(epi.bias)) &&
-                      (epi.mode != EPI_ACCUM_MASK || (aligned16(epi.maskC) && (!epi.maskc_full || epi.maskc_ld % 4 == 0)));
+      int vec = M % 4 == 0 && epi.ldc % 4 == 0 && aligned16(epi.C) && epi.mode != EPI_GATES &&
+                (epi.mode != EPI_BIAS || aligned16(epi.bias)) &&
+                (epi.mode != EPI_ACCUM_MASK || (aligned16(epi.maskC) && (!epi.maskc_full || epi.maskc_ld % 4 == 0)));
+      if (epi.split_m)
+        vec = vec && epi.split_m % 4 == 0 && epi.ldc2 % 4 == 0 && aligned16(epi.C2) &&
+              (epi.mode != EPI_ACCUM_MASK || (aligned16(epi.maskC2) && (!epi.maskc2_full || epi.maskc2_ld % 4 == 0)));
       k_splitk_reduce<<<stream_grid(ctx, (size_t)M * N / 4 + 1, 256), 256, 0, ctx->stream>>>(part, S, M, N, epi, vec);
       DYB_LAUNCHED(ctx);
     }
@@ -530,16 +587,20 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
   for (int p = 0; p < npairs; ++p) if (pairs[p].K == 0) return DYB200_OK;
   *handled = 1;
   PackedOp A[2], B[2];
+  PackJobs batch;   // all operands that need packing go out in one launch
+  dyb200_tc_pack_begin(&batch);
   for (int p = 0; p < npairs; ++p) {
     const GemmPair& g = pairs[p];
     // A: rows = m. op(A)(m,k) = transA ? A[k + lda*m] : A[m + lda*k]  -> k is fast iff transA
     int rc = g.a_is_param ? dyb200_tc_param(ctx, g.A, g.lda, g.transA != 0, M, g.K, &A[p])
-                          : dyb200_tc_pack(ctx, g.A, g.lda, g.transA != 0, M, g.K, nullptr, 0, 0, &A[p]);
+                          : dyb200_tc_pack(ctx, g.A, g.lda, g.transA != 0, M, g.K, nullptr, 0, 0, &A[p], &batch);
     if (rc) return rc;
     // B: rows = n. op(B)(k,n) = transB ? B[n + ldb*k] : B[k + ldb*n]  -> k is fast iff !transB
-    rc = dyb200_tc_pack(ctx, g.B, g.ldb, g.transB == 0, N, g.K, g.maskB, g.mask_ld, g.mask_full, &B[p]);
+    rc = dyb200_tc_pack(ctx, g.B, g.ldb, g.transB == 0, N, g.K, g.maskB, g.mask_ld, g.mask_full, &B[p], &batch);
     if (rc) return rc;
   }
+  int rcf = dyb200_tc_pack_flush(ctx, &batch);
+  if (rcf) return rcf;
   return dyb200_tc_gemm_packed(ctx, M, N, npairs, A, B, epi);
 }
 
@@ -553,6 +614,25 @@ struct dyb200_wgrad {
   uint32_t M, N[2], Kcap, k;
   PackedOp A, B[2];
 };
+
+// Same as dyb200_wgrad_push, but the packing work is queued in `batch` (the caller launches it).
+int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda, const float* b0, uint32_t ldb0,
+                              const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1,
+                              int mask1_full, dyb200_ctx* ctx, PackJobs* batch) {
+  DYB_CHECK_ARG(ctx, w && a && b0 && (w->N[1] == 0 || b1), "wgrad_push: null argument");
+  DYB_CHECK_ARG(ctx, w->k + k <= w->Kcap, "wgrad_push: %u + %u columns exceed the capacity %u", w->k, k, w->Kcap);
+  if (k == 0) return DYB200_OK;
+  int rc = pack(ctx, a, lda, false, w->M, k, nullptr, 0, 0, w->A.hi + w->k, w->A.lo + w->k, w->Kcap, batch);
+  if (rc) return rc;
+  rc = pack(ctx, b0, ldb0, false, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + w->k, w->B[0].lo + w->k, w->Kcap, batch);
+  if (rc) return rc;
+  if (w->N[1]) {
+    rc = pack(ctx, b1, ldb1, false, w->N[1], k, mask1, ldb1, mask1_full, w->B[1].hi + w->k, w->B[1].lo + w->k, w->Kcap, batch);
+    if (rc) return rc;
+  }
+  w->k += k;
+  return DYB200_OK;
+}
 
 extern "C" {
 
@@ -590,19 +670,11 @@ int dyb200_wgrad_destroy(dyb200_wgrad* w) {
 int dyb200_wgrad_push(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda, const float* b0, uint32_t ldb0,
                       const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1,
                       int mask1_full, dyb200_ctx* ctx) {
-  DYB_CHECK_ARG(ctx, w && a && b0 && (w->N[1] == 0 || b1), "wgrad_push: null argument");
-  DYB_CHECK_ARG(ctx, w->k + k <= w->Kcap, "wgrad_push: %u + %u columns exceed the capacity %u", w->k, k, w->Kcap);
-  if (k == 0) return DYB200_OK;
-  int rc = pack(ctx, a, lda, false, w->M, k, nullptr, 0, 0, w->A.hi + w->k, w->A.lo + w->k, w->Kcap);
+  PackJobs batch;
+  dyb200_tc_pack_begin(&batch);
+  int rc = dyb200_wgrad_push_batched(w, k, a, lda, b0, ldb0, mask0, mask0_full, b1, ldb1, mask1, mask1_full, ctx, &batch);
   if (rc) return rc;
-  rc = pack(ctx, b0, ldb0, false, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + w->k, w->B[0].lo + w->k, w->Kcap);
-  if (rc) return rc;
-  if (w->N[1]) {
-    rc = pack(ctx, b1, ldb1, false, w->N[1], k, mask1, ldb1, mask1_full, w->B[1].hi + w->k, w->B[1].lo + w->k, w->Kcap);
-    if (rc) return rc;
-  }
-  w->k += k;
-  return DYB200_OK;
+  return dyb200_tc_pack_flush(ctx, &batch);
 }
 
 // C0 += A * B0^T (and C1 += A * B1^T) over everything pushed since the last flush; empties the accumulator.

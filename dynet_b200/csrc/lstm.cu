@@ -444,21 +444,30 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
   const float* mh = attrs->dropout ? mask_h->v : nullptr;
   const int mx_full = attrs->dropout ? mask_x->bd == B : 0, mh_full = attrs->dropout ? mask_h->bd == B : 0;
   const double flops_small = 2.0 * (I < H ? I : H) * (double)B * G;
+  const bool tensor_path = dyb200_tc_eligible(I < H ? I : H, B, flops_small) && dyb200_tc_eligible(G, I < H ? I : H, flops_small);
+  PackJobs batch;   // every operand split of this call goes out in one launch
+  dyb200_tc_pack_begin(&batch);
+  PackedOp dn, dt, wxT, whT, xt, ht;
   if (deferred) {
     // weight gradients: append (dgate, x .* mask_x, h .* mask_h) to the accumulator; one product at flush time
-    rc = dyb200_wgrad_push(deferred, B, dpre, G, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx);
+    rc = dyb200_wgrad_push_batched(deferred, B, dpre, G, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx, &batch);
     if (rc) return rc;
   }
-  if (dyb200_tc_eligible(I < H ? I : H, B, flops_small) && dyb200_tc_eligible(G, I < H ? I : H, flops_small)) {
+  if (tensor_path && (rc = dyb200_tc_pack(ctx, dpre, G, true, B, G, nullptr, 0, 0, &dn, &batch))) return rc;    // rows = batch, K = 4H
+  if ((rc = dyb200_tc_pack_flush(ctx, &batch))) return rc;
+  if (tensor_path) {
     // the gate gradient is split once per layout and shared by the four products
-    PackedOp dn, dt, wxT, whT, xt, ht;
-    if ((rc = dyb200_tc_pack(ctx, dpre, G, true, B, G, nullptr, 0, 0, &dn))) return rc;    // rows = batch, K = 4H
-    if (dx) {
+    if (dx && dh_tm1) {
+      // dx and dh_tm1 in one product: [Wx; Wh]^T (I + H rows) times the gate gradient, rows routed to the two tensors
+      if ((rc = dyb200_tc_param2(ctx, Wx->v, I, Wh->v, H, G, true, G, &wxT))) return rc;
+      GemmEpilogue e{mx ? EPI_ACCUM_MASK : EPI_ACCUM, dx->v, I, nullptr, 0, 0.f, mx, I, mx_full};
+      e.split_m = I; e.C2 = dh_tm1->v; e.ldc2 = H; e.maskC2 = mh; e.maskc2_ld = H; e.maskc2_full = mh_full;
+      if ((rc = dyb200_tc_gemm_packed(ctx, I + H, B, 1, &wxT, &dn, e))) return rc;
+    } else if (dx) {
       if ((rc = dyb200_tc_param(ctx, Wx->v, G, true, I, G, &wxT))) return rc;
       GemmEpilogue e{mx ? EPI_ACCUM_MASK : EPI_ACCUM, dx->v, I, nullptr, 0, 0.f, mx, I, mx_full};
       if ((rc = dyb200_tc_gemm_packed(ctx, I, B, 1, &wxT, &dn, e))) return rc;
-    }
-    if (dh_tm1) {
+    } else if (dh_tm1) {
       if ((rc = dyb200_tc_param(ctx, Wh->v, G, true, H, G, &whT))) return rc;
       GemmEpilogue e{mh ? EPI_ACCUM_MASK : EPI_ACCUM, dh_tm1->v, H, nullptr, 0, 0.f, mh, H, mh_full};
       if ((rc = dyb200_tc_gemm_packed(ctx, H, B, 1, &whT, &dn, e))) return rc;

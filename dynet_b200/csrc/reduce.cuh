@@ -12,7 +12,15 @@ __global__ void __launch_bounds__(128) k_batch_reduce_partial(F f, size_t n, uin
   if (r >= n) return;
   uint32_t b0 = blockIdx.y * chunk, b1 = min(B, b0 + chunk);
   float acc = 0.f;
-  for (uint32_t b = b0; b < b1; ++b) acc += f(r, b);
+  uint32_t b = b0;
+  for (; b + 8 <= b1; b += 8) {   // eight loads in flight, summed in ascending order
+    float v[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) v[q] = f(r, b + q);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc += v[q];
+  }
+  for (; b < b1; ++b) acc += f(r, b);
   if (direct) out[r] += acc;
   else partial[(size_t)blockIdx.y * n + r] = acc;
 }
@@ -30,9 +38,9 @@ template <class F>
 static int batch_reduce_add(dyb200_ctx* ctx, F f, size_t n, uint32_t B, float* out) {
   if (n == 0 || B == 0) return DYB200_OK;
   unsigned gx = (unsigned)((n + 127) / 128);
-  unsigned want = (2u * ctx->sm_count + gx - 1) / gx;
+  unsigned want = (16u * ctx->sm_count + gx - 1) / gx;   // about 16 CTAs of 128 threads per SM
   unsigned S = want < 1 ? 1 : want;
-  if (S > (B + 3) / 4) S = (B + 3) / 4;
+  if (S > (B + 15) / 16) S = (B + 15) / 16;
   if (S < 1) S = 1;
   uint32_t chunk = (B + S - 1) / S;
   S = (B + chunk - 1) / chunk;

@@ -8,8 +8,9 @@
 // reverse and calls backward_dev_impl once per differentiable argument, accumulating (+=) into
 // gradient memory that was zeroed once (dynet/exec.cc:166-284); the lookup gradients are
 // scattered after the reverse pass in time order (exec.cc:277-282).
-// Parameters are read in place (weight decay is 1), and the gradient of `bias + R*h` w.r.t. the
-// product aliases the gradient of the sum instead of being copied.
+// Parameters are read in place (weight decay is 1).  With `fused` set, Gates + C + H of a step are one call,
+// weight gradients are deferred to one product per parameter, and the output layer (affine_transform +
+// pickneglogsoftmax), which does not feed back into the recurrence, runs once over all T*B columns.
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -73,7 +74,6 @@ struct Lm {
   cudaStream_t stream;
   // fused driver: weight-gradient products deferred to the end of the backward pass (one per parameter)
   std::vector<dyb200_wgrad*> wg_layer;   // per layer: A = gate gradient, B0 = x .* mask_x, B1 = h_tm1 .* mask_h
-  dyb200_wgrad* wg_R = nullptr;          // A = d(logits), B0 = h_top
   // CUDA-graph replay of the whole forward + backward pass (optional): the ~1400 launches of a step are
   // captured once and re-issued with one cudaGraphLaunch; inputs live at fixed addresses (tok, mask_buf).
   bool use_graph = false;
@@ -84,7 +84,6 @@ struct Lm {
   ~Lm() {
     if (graph_exec) cudaGraphExecDestroy(graph_exec);
     for (auto w : wg_layer) dyb200_wgrad_destroy(w);
-    dyb200_wgrad_destroy(wg_R);
   }
 };
 
@@ -100,14 +99,14 @@ size_t plan(const dyb200h_lm_config& c, Lm* m, char* base, size_t size) {
   float* aux = a.take<float>((size_t)c.T * 3 * c.B);
   float* errs = a.take<float>((size_t)c.T * c.B);
   float* zeros = a.take<float>(HB);
-  float* ones = a.take<float>(c.B);
+  float* ones = a.take<float>((size_t)c.T * c.B);
   float* scalars = a.take<float>(64);
   std::vector<float*> mask_buf;
   for (uint32_t l = 0; l < c.L; ++l) {
     mask_buf.push_back(a.take<float>((size_t)(l == 0 ? c.E : c.H) * c.B));
     mask_buf.push_back(a.take<float>(HB));
   }
-  float* dr = a.take<float>(VB);
+  float* dr = a.take<float>(c.fused ? c.T * VB : VB);   // d(logits): all steps at once in the fused driver
   // everything below is zeroed by one memset per backward
   a.off = (a.off + 255) & ~(size_t)255;
   size_t d0 = a.off;
@@ -139,24 +138,31 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   const size_t HB = (size_t)H * B, GB = 4 * HB, VB = (size_t)V * B, EB = (size_t)E * B;
   const Device_GPU& dev = m.dev;
   cudaStream_t st = m.stream;
-  // place the target ids of step t where PickNegLogSoftmax expects them: aux_t = {z[B], m[B], ids[B]}
-  CU(cudaMemcpy2DAsync(m.aux + 2 * (size_t)B, 3 * (size_t)B * sizeof(float), m.tok + B, (size_t)B * sizeof(uint32_t),
-                       (size_t)B * sizeof(uint32_t), T, cudaMemcpyDeviceToDevice, st));
+  const uint32_t TB = T * B;
+  // activations of layer l at time t sit at block l * T + t: every layer's states are one H x (T*B) matrix
+  auto at = [T](uint32_t t, uint32_t l) { return (size_t)l * T + t; };
+  // place the target ids where PickNegLogSoftmax expects them: aux = {z[n], m[n], ids[n]} with n = B per step,
+  // or n = T*B when the output layer runs once over all time steps
+  if (c.fused)
+    CU(cudaMemcpyAsync(m.aux + 2 * (size_t)TB, m.tok + B, (size_t)TB * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st));
+  else
+    CU(cudaMemcpy2DAsync(m.aux + 2 * (size_t)B, 3 * (size_t)B * sizeof(float), m.tok + B, (size_t)B * sizeof(uint32_t),
+                         (size_t)B * sizeof(uint32_t), T, cudaMemcpyDeviceToDevice, st));
 
   Tensor tC(Dim({E}, V), m.p[0]), tR(Dim({V, H}), m.p[1 + 3 * L]), tbias(Dim({V}), m.p[2 + 3 * L]);
   Tensor tZero(Dim({H}, B), m.zeros);
   VanillaLSTMGates gates_node(c.dropout != 0);
   VanillaLSTMC c_node;
   VanillaLSTMH h_node;
-  CwiseSum sum_node;
+  AffineTransform affine;
   PickNegLogSoftmax pnls(nullptr);
   pnls.dim = Dim({1}, B);
 
   auto layer_xs = [&](uint32_t t, uint32_t l, Tensor* store, std::vector<const Tensor*>& xs) {
     // store: [in, h_prev, Wx, Wh, b, mx, mh]
     uint32_t I = l == 0 ? E : H;
-    store[0] = Tensor(Dim({I}, B), l == 0 ? m.x + t * EB : m.hs + ((size_t)t * L + l - 1) * HB);
-    store[1] = t == 0 ? tZero : Tensor(Dim({H}, B), m.hs + ((size_t)(t - 1) * L + l) * HB);
+    store[0] = Tensor(Dim({I}, B), l == 0 ? m.x + t * EB : m.hs + at(t, l - 1) * HB);
+    store[1] = t == 0 ? tZero : Tensor(Dim({H}, B), m.hs + at(t - 1, l) * HB);
     store[2] = Tensor(Dim({4 * H, I}), m.p[1 + 3 * l]);
     store[3] = Tensor(Dim({4 * H, H}), m.p[2 + 3 * l]);
     store[4] = Tensor(Dim({4 * H}), m.p[3 + 3 * l]);
@@ -170,18 +176,26 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   };
 
   // ---------------- forward ----------------
+  if (c.fused) {   // the T lookups read one table: one gather over the T*B ids
+    LookupNode look(tC, nullptr, TB);
+    look.aux_mem = m.tok;
+    Tensor xall(Dim({E}, TB), m.x);
+    look.forward_dev_impl(dev, {}, xall);
+  }
   for (uint32_t t = 0; t < T; ++t) {
-    LookupNode look(tC, nullptr, B);
-    look.aux_mem = m.tok + (size_t)t * B;
-    Tensor xt(Dim({E}, B), m.x + t * EB);
-    look.forward_dev_impl(dev, {}, xt);
+    if (!c.fused) {
+      LookupNode look(tC, nullptr, B);
+      look.aux_mem = m.tok + (size_t)t * B;
+      Tensor xt(Dim({E}, B), m.x + t * EB);
+      look.forward_dev_impl(dev, {}, xt);
+    }
     for (uint32_t l = 0; l < L; ++l) {
-      size_t idx = (size_t)t * L + l;
+      size_t idx = at(t, l);
       Tensor store[7];
       std::vector<const Tensor*> xs;
       layer_xs(t, l, store, xs);
       Tensor tg(Dim({4 * H}, B), m.gates + idx * GB), tc(Dim({H}, B), m.cs + idx * HB), th(Dim({H}, B), m.hs + idx * HB);
-      Tensor cprev = t == 0 ? tZero : Tensor(Dim({H}, B), m.cs + ((size_t)(t - 1) * L + l) * HB);
+      Tensor cprev = t == 0 ? tZero : Tensor(Dim({H}, B), m.cs + at(t - 1, l) * HB);
       if (c.fused) {
         dyb200_tensor cx = to_c(store[0]), chp = to_c(store[1]), ccp = to_c(cprev), cWx = to_c(store[2]), cWh = to_c(store[3]),
                       cb = to_c(store[4]), cmx, cmh, cg = to_c(tg), cc = to_c(tc), ch = to_c(th);
@@ -195,44 +209,65 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
       c_node.forward_dev_impl(dev, {&cprev, &tg}, tc);
       h_node.forward_dev_impl(dev, {&tc, &tg}, th);
     }
-    Tensor htop(Dim({H}, B), m.hs + ((size_t)t * L + L - 1) * HB), rt(Dim({V}, B), m.r + t * VB);
-    // MatrixMultiply R * h, then CwiseSum(bias, R*h) in place (dynet/nodes-matrixmultiply.cc:50-59)
-    throw_status(dev, dyb200_gemm(0, 0, V, B, H, tR.v, V, htop.v, H, rt.v, V, 0, DYB200_GEMM_A_IS_PARAM, dev.ctx));
-    sum_node.forward_dev_impl(dev, {&tbias, &rt}, rt);
+    if (c.fused) continue;
+    Tensor htop(Dim({H}, B), m.hs + at(t, L - 1) * HB), rt(Dim({V}, B), m.r + t * VB);
+    // r = affine_transform({bias, R, h}) (examples/batching/rnnlm-batch.h:132)
+    affine.forward_dev_impl(dev, {&tbias, &tR, &htop}, rt);
     pnls.aux_mem = m.aux + (size_t)t * 3 * B;
     Tensor et(Dim({1}, B), m.errs + (size_t)t * B);
     pnls.forward_dev_impl(dev, {&rt}, et);
+  }
+  // The output layer does not feed back into the recurrence: in the fused driver it runs once over the
+  // H x (T*B) matrix of top-layer states (same values per column as the per-step nodes).
+  Tensor hall(Dim({H}, TB), m.hs + at(0, L - 1) * HB), rall(Dim({V}, TB), m.r), eall(Dim({1}, TB), m.errs);
+  const dyb200_affine_attrs R_is_param = {DYB200_GEMM_A_IS_PARAM};
+  if (c.fused) {
+    dyb200_tensor cxs[3] = {to_c(tbias), to_c(tR), to_c(hall)}, cr = to_c(rall);
+    throw_status(dev, dyb200_affine_transform_fwd(cxs, 3, &cr, &R_is_param, nullptr, dev.ctx));
+    pnls.dim = Dim({1}, TB);
+    pnls.aux_mem = m.aux;
+    pnls.forward_dev_impl(dev, {&rall}, eall);
   }
   throw_status(dev, dyb200_sum_all(m.errs, (size_t)T * B, loss_dev, 0, dev.ctx));
 
   // ---------------- backward ----------------
   CU(cudaMemsetAsync(m.dact, 0, m.dact_bytes, st));
   Tensor tgR(Dim({V, H}), m.g[1 + 3 * L]), tgbias(Dim({V}), m.g[2 + 3 * L]);
+  if (c.fused) {
+    Tensor tones(Dim({1}, TB), m.ones), tdr(Dim({V}, TB), m.dr), tdhall(Dim({H}, TB), m.dh + at(0, L - 1) * HB);
+    CU(cudaMemsetAsync(m.dr, 0, (size_t)T * VB * sizeof(float), st));
+    pnls.backward_dev_impl(dev, {&rall}, eall, tones, 0, tdr);
+    dyb200_tensor cxs[3] = {to_c(tbias), to_c(tR), to_c(hall)}, cr = to_c(rall), cdr = to_c(tdr);
+    dyb200_tensor cgb = to_c(tgbias), cgR = to_c(tgR), cdh = to_c(tdhall);
+    throw_status(dev, dyb200_affine_transform_bwd(cxs, 3, &cr, &cdr, 0, &cgb, &R_is_param, nullptr, dev.ctx));   // dbias += sum_columns dr
+    throw_status(dev, dyb200_affine_transform_bwd(cxs, 3, &cr, &cdr, 1, &cgR, &R_is_param, nullptr, dev.ctx));   // dR += dr h^T
+    throw_status(dev, dyb200_affine_transform_bwd(cxs, 3, &cr, &cdr, 2, &cdh, &R_is_param, nullptr, dev.ctx));   // dh += R^T dr
+  }
   Tensor tones(Dim({1}, B), m.ones);
   for (uint32_t tt = T; tt-- > 0;) {
-    size_t top = (size_t)tt * L + L - 1;
-    Tensor rt(Dim({V}, B), m.r + tt * VB), et(Dim({1}, B), m.errs + (size_t)tt * B), tdr(Dim({V}, B), m.dr);
-    Tensor htop(Dim({H}, B), m.hs + top * HB);
-    CU(cudaMemsetAsync(m.dr, 0, VB * sizeof(float), st));
-    pnls.aux_mem = m.aux + (size_t)tt * 3 * B;
-    pnls.backward_dev_impl(dev, {&rt}, et, tones, 0, tdr);
-    sum_node.backward_dev_impl(dev, {&tbias, &rt}, rt, tdr, 0, tgbias);          // dbias += sum_b dr
-    if (c.fused) throw_status(dev, dyb200_wgrad_push(m.wg_R, B, m.dr, V, htop.v, H, nullptr, 0, nullptr, 0, nullptr, 0, dev.ctx));
-    else throw_status(dev, dyb200_gemm(0, 1, V, H, B, m.dr, V, htop.v, H, tgR.v, V, 1, 0, dev.ctx));   // dR += dr h^T
-    throw_status(dev, dyb200_gemm(1, 0, H, B, V, tR.v, V, m.dr, V, m.dh + top * HB, H, 1, DYB200_GEMM_A_IS_PARAM, dev.ctx));   // dh += R^T dr
+    if (!c.fused) {
+      Tensor rt(Dim({V}, B), m.r + tt * VB), et(Dim({1}, B), m.errs + (size_t)tt * B), tdr(Dim({V}, B), m.dr);
+      Tensor htop(Dim({H}, B), m.hs + at(tt, L - 1) * HB), tdhtop(Dim({H}, B), m.dh + at(tt, L - 1) * HB);
+      CU(cudaMemsetAsync(m.dr, 0, VB * sizeof(float), st));
+      pnls.aux_mem = m.aux + (size_t)tt * 3 * B;
+      pnls.backward_dev_impl(dev, {&rt}, et, tones, 0, tdr);
+      affine.backward_dev_impl(dev, {&tbias, &tR, &htop}, rt, tdr, 0, tgbias);   // dbias += sum_b dr
+      affine.backward_dev_impl(dev, {&tbias, &tR, &htop}, rt, tdr, 1, tgR);      // dR += dr h^T
+      affine.backward_dev_impl(dev, {&tbias, &tR, &htop}, rt, tdr, 2, tdhtop);   // dh += R^T dr
+    }
     for (uint32_t l = L; l-- > 0;) {
-      size_t idx = (size_t)tt * L + l;
+      size_t idx = at(tt, l);
       Tensor store[7];
       std::vector<const Tensor*> xs;
       layer_xs(tt, l, store, xs);
       Tensor tg(Dim({4 * H}, B), m.gates + idx * GB), tc(Dim({H}, B), m.cs + idx * HB), th(Dim({H}, B), m.hs + idx * HB);
       Tensor tdh(Dim({H}, B), m.dh + idx * HB), tdc(Dim({H}, B), m.dc + idx * HB), tdg(Dim({4 * H}, B), m.dgates + idx * GB);
-      Tensor cprev = tt == 0 ? tZero : Tensor(Dim({H}, B), m.cs + ((size_t)(tt - 1) * L + l) * HB);
+      Tensor cprev = tt == 0 ? tZero : Tensor(Dim({H}, B), m.cs + at(tt - 1, l) * HB);
       if (c.fused) {
         uint32_t I2 = l == 0 ? E : H;
-        Tensor tdin2(Dim({I2}, B), l == 0 ? m.dx + tt * EB : m.dh + ((size_t)tt * L + l - 1) * HB);
-        Tensor tdhp2(Dim({H}, B), tt > 0 ? m.dh + ((size_t)(tt - 1) * L + l) * HB : nullptr);
-        Tensor tdcp2(Dim({H}, B), tt > 0 ? m.dc + ((size_t)(tt - 1) * L + l) * HB : nullptr);
+        Tensor tdin2(Dim({I2}, B), l == 0 ? m.dx + tt * EB : m.dh + at(tt, l - 1) * HB);
+        Tensor tdhp2(Dim({H}, B), tt > 0 ? m.dh + at(tt - 1, l) * HB : nullptr);
+        Tensor tdcp2(Dim({H}, B), tt > 0 ? m.dc + at(tt - 1, l) * HB : nullptr);
         Tensor gWx2(Dim({4 * H, I2}), m.g[1 + 3 * l]), gWh2(Dim({4 * H, H}), m.g[2 + 3 * l]), gb2(Dim({4 * H}), m.g[3 + 3 * l]);
         dyb200_tensor cx = to_c(store[0]), chp = to_c(store[1]), ccp = to_c(cprev), cWx = to_c(store[2]), cWh = to_c(store[3]), cmx, cmh,
                       cg = to_c(tg), cc = to_c(tc), cdh = to_c(tdh), cdc = to_c(tdc), cdx = to_c(tdin2), cdhp = to_c(tdhp2),
@@ -247,15 +282,15 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
       h_node.backward_dev_impl(dev, {&tc, &tg}, th, tdh, 0, tdc);
       h_node.backward_dev_impl(dev, {&tc, &tg}, th, tdh, 1, tdg);
       if (tt > 0) {
-        Tensor tdcp(Dim({H}, B), m.dc + ((size_t)(tt - 1) * L + l) * HB);
+        Tensor tdcp(Dim({H}, B), m.dc + at(tt - 1, l) * HB);
         c_node.backward_dev_impl(dev, {&cprev, &tg}, tc, tdc, 0, tdcp);
       }
       c_node.backward_dev_impl(dev, {&cprev, &tg}, tc, tdc, 1, tdg);
       uint32_t I = l == 0 ? E : H;
-      Tensor tdin(Dim({I}, B), l == 0 ? m.dx + tt * EB : m.dh + ((size_t)tt * L + l - 1) * HB);
+      Tensor tdin(Dim({I}, B), l == 0 ? m.dx + tt * EB : m.dh + at(tt, l - 1) * HB);
       gates_node.backward_dev_impl(dev, xs, tg, tdg, 0, tdin);
       if (tt > 0) {
-        Tensor tdhp(Dim({H}, B), m.dh + ((size_t)(tt - 1) * L + l) * HB);
+        Tensor tdhp(Dim({H}, B), m.dh + at(tt - 1, l) * HB);
         gates_node.backward_dev_impl(dev, xs, tg, tdg, 1, tdhp);
       }
       Tensor gWx(Dim({4 * H, I}), m.g[1 + 3 * l]), gWh(Dim({4 * H, H}), m.g[2 + 3 * l]), gb(Dim({4 * H}), m.g[3 + 3 * l]);
@@ -269,7 +304,6 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
     // the deferred weight-gradient products: one per parameter matrix, K = T * B
     for (uint32_t l = 0; l < L; ++l)
       throw_status(dev, dyb200_wgrad_flush(m.wg_layer[l], m.g[1 + 3 * l], 4 * H, m.g[2 + 3 * l], 4 * H, dev.ctx));
-    throw_status(dev, dyb200_wgrad_flush(m.wg_R, tgR.v, V, nullptr, 0, dev.ctx));
     // All T lookups share the table, so their accumulate_grads calls fold into one over the T*B ids in time
     // order: each table row still receives its rows in the order of the per-step calls.
     LookupNode look(tC, nullptr, T * B);
@@ -367,11 +401,11 @@ int dyb200h_lm_create(const dyb200h_lm_config* c, float* params, float* grads, v
       rc = dyb200_wgrad_create(ctx, 4 * c->H, l == 0 ? c->E : c->H, c->H, c->T * c->B, &w);
       if (!rc) m->wg_layer.push_back(w);
     }
-    if (!rc) rc = dyb200_wgrad_create(ctx, c->V, c->H, 0, c->T * c->B, &m->wg_R);
+
     if (rc) { delete m; return rc; }
   }
   rc = dyb200_fill(m->zeros, (size_t)c->H * c->B, 0.f, ctx);
-  if (!rc) rc = dyb200_fill(m->ones, c->B, 1.f, ctx);
+  if (!rc) rc = dyb200_fill(m->ones, (size_t)c->T * c->B, 1.f, ctx);
   if (rc) { delete m; return rc; }
   *out = m;
   return DYB200_OK;

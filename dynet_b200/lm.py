@@ -225,4 +225,4 @@ class LstmLm:
         base = self.workspace.data_ptr()
         off = ptr - base
         out.copy_(self.workspace[off:off + 4 * n].view(self.torch.float32))
-        return out.cpu().numpy().reshape(T, L, B, H)
+        return out.cpu().numpy().reshape(L, T, B, H).transpose(1, 0, 2, 3)   # stored layer-major
