@@ -275,6 +275,24 @@ def run_gpu(args):
     prof = model.ctx.profile_end()
     errs = model.ctx.device_errors()
     launches = launches_per_step * args.steps
+    # where a step's time goes (this rank, 5 more steps, CUDA events between the phases; not part of any headline number)
+    if not args.no_graph:
+        model.set_graph(True)
+    phases = np.zeros(4)
+    for k in range(5):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        ev[0].record(stream)
+        draw_masks()
+        ev[1].record(stream)
+        model.launch_forward_backward(dev_tokens[k % n_batches], masks)
+        ev[2].record(stream)
+        model.allreduce_grads()
+        ev[3].record(stream)
+        model.update()
+        ev[4].record(stream)
+        torch.cuda.synchronize()
+        phases += [ev[q].elapsed_time(ev[q + 1]) for q in range(4)]
+    phases /= 5
 
     tokens_per_step = GLOBAL_BATCH * T
     value = tokens_per_step * args.steps / (ms * 1e-3)
@@ -313,6 +331,8 @@ def run_gpu(args):
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": int((T + 1) * B * 4 * world),
                     "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps, "last_loss": losses[-1] if losses else None},
             "gpu_launches": int(launches),
+            "phases_ms": {"mask_draw": float(phases[0]), "fwd_bwd": float(phases[1]), "allreduce": float(phases[2]),
+                          "clip_update": float(phases[3]), "note": "rank 0, 5 extra steps after the timed regions"},
             "roofline": roofline,
             "cpu_baseline": None if cb_tps is None else {
                 "value": cb_tps, "unit": "tokens/s", "cores": cb_threads, "kind": "port",
