@@ -73,6 +73,31 @@ class LstmGatesAttrs(C.Structure):
     _fields_ = [("dropout", C.c_int32), ("weightnoise_std", C.c_float), ("forget_gate_bias", C.c_float)]
 
 
+class PickRangeAttrs(C.Structure):
+    _fields_ = [("start", C.c_uint), ("end", C.c_uint), ("dim", C.c_uint)]
+
+
+class SumDimAttrs(C.Structure):
+    _fields_ = [("dims", C.c_uint * 2), ("ndims", C.c_uint), ("include_batch_dim", C.c_int)]
+
+
+class ConstAttrs(C.Structure):
+    _fields_ = [("c", C.c_float)]
+
+
+class BernoulliAttrs(C.Structure):
+    _fields_ = [("p", C.c_float), ("scale", C.c_float), ("seed", C.c_uint64), ("offset", C.c_uint64)]
+
+
+class TrainerHyper(C.Structure):
+    _fields_ = [("learning_rate", C.c_float), ("clip_threshold", C.c_float), ("weight_decay", C.c_float),
+                ("momentum", C.c_float), ("epsilon", C.c_float), ("rho", C.c_float), ("beta_1", C.c_float),
+                ("beta_2", C.c_float), ("updates", C.c_uint64)]
+
+
+RULES = {"sgd": 0, "momentum": 1, "adagrad": 2, "adadelta": 3, "rmsprop": 4, "adam": 5, "amsgrad": 6}
+
+
 class AffineAttrs(C.Structure):
     _fields_ = [("flags", C.c_uint)]
 
@@ -84,13 +109,14 @@ class MomentAttrs(C.Structure):
 
 NODES = ["tanh", "logistic", "rectify", "elu", "cmult", "csum", "cdiv", "softmax", "log_softmax",
          "logsumexp_dim", "logsumexp", "pickneglogsoftmax", "weight_norm", "moment_dim", "std_dim",
-         "layer_norm", "vanilla_lstm_gates", "vanilla_lstm_c", "vanilla_lstm_h", "matmul", "affine_transform"]
-FWD_ONLY = ["lookup"]
+         "layer_norm", "vanilla_lstm_gates", "vanilla_lstm_c", "vanilla_lstm_h", "matmul", "affine_transform",
+         "pick_range", "concatenate", "sum", "sum_dim", "squared_norm", "negate", "constant_plus_x", "constant_minus_x"]
+FWD_ONLY = ["lookup", "random_bernoulli"]
 OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200_ctx_check_device_errors",
          "dyb200_ctx_launch_count", "dyb200_version", "dyb200_lookup_accumulate_grads",
          "dyb200_lookup_accumulate_grads_noalloc",
          "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm", "dyb200_fill", "dyb200_sum_all",
-         "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end",
+         "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_trainer_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end",
          "dyb200_ctx_param_cache", "dyb200_ctx_params_changed", "dyb200_vanilla_lstm_fwd_fused",
          "dyb200_vanilla_lstm_bwd_fused", "dyb200_wgrad_create", "dyb200_wgrad_destroy", "dyb200_wgrad_push",
          "dyb200_wgrad_flush"]
@@ -167,6 +193,9 @@ def lib():
             f = getattr(L, n)
             f.restype = C.c_int
             f.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.dyb200_trainer_update.restype = C.c_int
+        L.dyb200_trainer_update.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
+                                            C.POINTER(TrainerHyper), C.c_void_p, C.c_int, C.c_void_p]
         L.dyb200_gemm.restype = C.c_int
         L.dyb200_gemm.argtypes = [C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32,
                                   C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_int, C.c_uint, C.c_void_p]
@@ -288,6 +317,12 @@ class Context:
 
     def wgrad_flush(self, w, C0, ldc0, C1=None, ldc1=0):
         self.check(self.L.dyb200_wgrad_flush(w, C0, ldc0, C1, ldc1, self.h))
+
+    def trainer_update(self, rule, params, grads, states, n, hyper, grad_sumsq=None, zero_grads=True):
+        """rule: key of RULES; params / grads / states / grad_sumsq: device pointers (ints)."""
+        st = list(states) + [None] * (3 - len(states))
+        self.check(self.L.dyb200_trainer_update(RULES[rule], params, grads, st[0], st[1], st[2], n, C.byref(hyper), grad_sumsq,
+                                                int(zero_grads), self.h))
 
     def param_cache(self, enable):
         self.check(self.L.dyb200_ctx_param_cache(self.h, int(enable)))

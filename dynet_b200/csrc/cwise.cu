@@ -19,6 +19,11 @@ struct FElu {
   float alpha, lambda;
   __device__ float operator()(float x) const { return lambda * (x > 0.f ? x : alpha * expm1f(x)); }
 };
+struct FNegate { __device__ float operator()(float x) const { return -x; } };
+struct FConstPlus { float c; __device__ float operator()(float x) const { return x + c; } };
+struct FConstMinus { float c; __device__ float operator()(float x) const { return c - x; } };
+struct BPass { __device__ float operator()(float, float d) const { return d; } };
+struct BNeg { __device__ float operator()(float, float d) const { return -d; } };
 // backward: g(a, d) where a is fx (tanh/logistic/rectify) or x (elu)
 struct BTanh { __device__ float operator()(float t, float d) const { return (1.f - t * t) * d; } };
 struct BLogistic { __device__ float operator()(float t, float d) const { return (1.f - t) * t * d; } };
@@ -380,6 +385,21 @@ int dyb200_logistic_fwd(DYB200_FWD_ARGS) { (void)attrs; (void)aux_mem; return un
 int dyb200_logistic_bwd(DYB200_BWD_ARGS) { (void)xs; (void)nxs; (void)attrs; (void)aux_mem; return unary_bwd(ctx, fx->v, dEdf, i, dEdxi, BLogistic{}, "LogisticSigmoid"); }
 int dyb200_rectify_fwd(DYB200_FWD_ARGS) { (void)attrs; (void)aux_mem; return unary_fwd(ctx, xs, nxs, fx, FRectify{}, "Rectify"); }
 int dyb200_rectify_bwd(DYB200_BWD_ARGS) { (void)xs; (void)nxs; (void)attrs; (void)aux_mem; return unary_bwd(ctx, fx->v, dEdf, i, dEdxi, BRectify{}, "Rectify"); }
+// Negate, ConstantPlusX, ConstantMinusX: the backward pass needs no saved value (dEdf stands in for it)
+int dyb200_negate_fwd(DYB200_FWD_ARGS) { (void)attrs; (void)aux_mem; return unary_fwd(ctx, xs, nxs, fx, FNegate{}, "Negate"); }
+int dyb200_negate_bwd(DYB200_BWD_ARGS) { (void)xs; (void)nxs; (void)fx; (void)attrs; (void)aux_mem; return unary_bwd(ctx, dEdf->v, dEdf, i, dEdxi, BNeg{}, "Negate"); }
+int dyb200_constant_plus_x_fwd(DYB200_FWD_ARGS) {
+  (void)aux_mem;
+  DYB_CHECK_ARG(ctx, attrs != nullptr, "ConstantPlusX: attrs (c) required");
+  return unary_fwd(ctx, xs, nxs, fx, FConstPlus{((const dyb200_const_attrs*)attrs)->c}, "ConstantPlusX");
+}
+int dyb200_constant_plus_x_bwd(DYB200_BWD_ARGS) { (void)xs; (void)nxs; (void)fx; (void)attrs; (void)aux_mem; return unary_bwd(ctx, dEdf->v, dEdf, i, dEdxi, BPass{}, "ConstantPlusX"); }
+int dyb200_constant_minus_x_fwd(DYB200_FWD_ARGS) {
+  (void)aux_mem;
+  DYB_CHECK_ARG(ctx, attrs != nullptr, "ConstantMinusX: attrs (c) required");
+  return unary_fwd(ctx, xs, nxs, fx, FConstMinus{((const dyb200_const_attrs*)attrs)->c}, "ConstantMinusX");
+}
+int dyb200_constant_minus_x_bwd(DYB200_BWD_ARGS) { (void)xs; (void)nxs; (void)fx; (void)attrs; (void)aux_mem; return unary_bwd(ctx, dEdf->v, dEdf, i, dEdxi, BNeg{}, "ConstantMinusX"); }
 int dyb200_elu_fwd(DYB200_FWD_ARGS) {
   (void)aux_mem;
   DYB_CHECK_ARG(ctx, attrs != nullptr, "ExponentialLinearUnit: attrs (alpha, lambda) required");

@@ -172,6 +172,34 @@ struct VanillaLSTMGates : Node {
   DYB200_NODE_COMMON(VanillaLSTMGates)
 };
 struct VanillaLSTMC : Node { DYB200_NODE_COMMON(VanillaLSTMC) };
+struct PickRange : Node {                                                 // dynet/nodes-select.h
+  unsigned start, end, dim;
+  PickRange(unsigned s, unsigned e, unsigned d = 0) : start(s), end(e), dim(d) {}
+  DYB200_NODE_COMMON(PickRange)
+};
+struct Concatenate : Node {                                               // dynet/nodes-concat.h
+  unsigned dimension;
+  explicit Concatenate(unsigned d = 0) : dimension(d) {}
+  DYB200_NODE_COMMON(Concatenate)
+};
+struct Sum : Node { DYB200_NODE_COMMON(Sum) };                            // dynet/nodes-arith-sum.h
+struct SumDimension : Node {
+  std::vector<unsigned> dims; bool include_batch_dim;
+  SumDimension(const std::vector<unsigned>& d, bool b) : dims(d), include_batch_dim(b) {}
+  DYB200_NODE_COMMON(SumDimension)
+};
+struct SquaredNorm : Node { DYB200_NODE_COMMON(SquaredNorm) };            // dynet/nodes-norms.h
+struct Negate : Node { DYB200_NODE_COMMON(Negate) };                      // dynet/nodes-arith-unary.h
+struct ConstantPlusX : Node {                                             // dynet/nodes-arith-const.h
+  float c;
+  explicit ConstantPlusX(float v) : c(v) {}
+  DYB200_NODE_COMMON(ConstantPlusX)
+};
+struct ConstantMinusX : Node {
+  float c;
+  explicit ConstantMinusX(float v) : c(v) {}
+  DYB200_NODE_COMMON(ConstantMinusX)
+};
 struct MatrixMultiply : Node { DYB200_NODE_COMMON(MatrixMultiply) };     // dynet/nodes-matrixmultiply.h
 struct AffineTransform : Node { DYB200_NODE_COMMON(AffineTransform) };   // dynet/nodes-affinetransform.h
 struct VanillaLSTMH : Node { DYB200_NODE_COMMON(VanillaLSTMH) };

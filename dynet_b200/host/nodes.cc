@@ -36,19 +36,17 @@ dyb200_tensor to_c(const Tensor& t) {
 }
 
 void call_fwd(fwd_fn f, const Device_GPU& dev, const std::vector<const Tensor*>& xs, Tensor& fx, const void* attrs, void* aux) {
-  dyb200_tensor cx[16];
-  ARG_CHECK(xs.size() <= 16, "too many arguments");
+  std::vector<dyb200_tensor> cx(xs.size());
   for (size_t k = 0; k < xs.size(); ++k) cx[k] = to_c(*xs[k]);
   dyb200_tensor cf = to_c(fx);
-  throw_status(dev, f(xs.empty() ? nullptr : cx, (int)xs.size(), &cf, attrs, aux, dev.ctx));
+  throw_status(dev, f(xs.empty() ? nullptr : cx.data(), (int)xs.size(), &cf, attrs, aux, dev.ctx));
 }
 void call_bwd(bwd_fn f, const Device_GPU& dev, const std::vector<const Tensor*>& xs, const Tensor& fx, const Tensor& dEdf,
               unsigned i, Tensor& dEdxi, const void* attrs, void* aux) {
-  dyb200_tensor cx[16];
-  ARG_CHECK(xs.size() <= 16, "too many arguments");
+  std::vector<dyb200_tensor> cx(xs.size());
   for (size_t k = 0; k < xs.size(); ++k) cx[k] = to_c(*xs[k]);
   dyb200_tensor cf = to_c(fx), cd = to_c(dEdf), co = to_c(dEdxi);
-  throw_status(dev, f(xs.empty() ? nullptr : cx, (int)xs.size(), &cf, &cd, i, &co, attrs, aux, dev.ctx));
+  throw_status(dev, f(xs.empty() ? nullptr : cx.data(), (int)xs.size(), &cf, &cd, i, &co, attrs, aux, dev.ctx));
 }
 
 #define SIMPLE_NODE(CLS, CNAME, ...)                                                                             \
@@ -237,6 +235,70 @@ Dim VanillaLSTMC::dim_forward(const std::vector<Dim>& xs) const { return lstm_ch
 Dim VanillaLSTMH::dim_forward(const std::vector<Dim>& xs) const { return lstm_ch_dim(xs, "VanillaLSTMH"); }
 SIMPLE_NODE(VanillaLSTMC, vanilla_lstm_c, NO_ATTRS)
 SIMPLE_NODE(VanillaLSTMH, vanilla_lstm_h, NO_ATTRS)
+
+// ---- glue nodes ----
+Dim PickRange::dim_forward(const std::vector<Dim>& xs) const {         // dynet/nodes-select.cc:206-212
+  ARG_CHECK(xs.size() == 1, "Failed input count check in PickRange");
+  ARG_CHECK(dim < xs[0].nd && start < end && xs[0][dim] >= end, "Bad input dimensions or range in PickRange: range(" << start << ", " << end << ") with dim=" << dim);
+  Dim ret = xs[0];
+  ret.d[dim] = end - start;
+  return ret;
+}
+SIMPLE_NODE(PickRange, pick_range, dyb200_pick_range_attrs at = {start, end, dim}; const void* attrs_ptr = &at)
+Dim Concatenate::dim_forward(const std::vector<Dim>& xs) const {       // dynet/nodes-concat.cc:25-40
+  ARG_CHECK(!xs.empty(), "Concatenate needs at least one argument");
+  unsigned new_rows = 0;
+  Dim dr = xs[0];
+  if (dr.nd < dimension + 1) { for (unsigned k = dr.nd; k < dimension + 1; ++k) dr.d[k] = 1; dr.nd = dimension + 1; }
+  for (Dim c : xs) {
+    if (c.nd < dr.nd) { for (unsigned k = c.nd; k < dr.nd; ++k) c.d[k] = 1; c.nd = dr.nd; }
+    ARG_CHECK(c.nd == dr.nd, "Bad input dimensions in Concatenate");
+    new_rows += c[dimension];
+    for (unsigned k = 0; k < dr.nd; ++k) ARG_CHECK(k == dimension || c.d[k] == dr.d[k], "Bad input dimensions in Concatenate");
+    dr.bd = std::max(dr.bd, c.bd);
+  }
+  dr.d[dimension] = new_rows;
+  return dr;
+}
+SIMPLE_NODE(Concatenate, concatenate, dyb200_dim_attrs at = {dimension}; const void* attrs_ptr = &at)
+Dim Sum::dim_forward(const std::vector<Dim>& xs) const {               // dynet/nodes-arith-sum.cc:22-33
+  ARG_CHECK(xs.size() > 0, "Zero-length vector passed to Sum");
+  Dim d = xs[0];
+  for (size_t i = 1; i < xs.size(); ++i) {
+    ARG_CHECK(d.batch_size() == xs[i].batch_size(), "Mismatched input dimensions in Sum");
+    d.bd = std::max(xs[i].bd, d.bd);
+  }
+  return d;
+}
+SIMPLE_NODE(Sum, sum, NO_ATTRS)
+Dim SumDimension::dim_forward(const std::vector<Dim>& xs) const {      // dynet/nodes-arith-sum.cc:182-193
+  ARG_CHECK(xs.size() == 1, "Failed input count check in SumDimension");
+  ARG_CHECK(xs[0].nd <= 3, "SumDimension implemented up to tensors of order 3 (with minibatch) for now");
+  ARG_CHECK(dims.size() <= 2, "Number of dimensions to reduce (excluding batch dimension) implemented up to 2 in SumDimension");
+  ARG_CHECK(!dims.empty() || include_batch_dim, "At least one dimension has to be reduced (including batch dimension) in SumDimension");
+  Dim ret;
+  for (unsigned k = 0; k < xs[0].nd; ++k) {
+    bool removed = false;
+    for (unsigned d : dims) { ARG_CHECK(d <= xs[0].nd, "dimension " << d << " is out of bounds in SumDimension"); removed = removed || d == k; }
+    if (!removed) ret.d[ret.nd++] = xs[0].d[k];
+  }
+  ret.bd = include_batch_dim ? 1 : xs[0].bd;
+  return ret;
+}
+static dyb200_sum_dim_attrs sum_dim_attrs(const std::vector<unsigned>& dims, bool b) {
+  dyb200_sum_dim_attrs a = {{0, 0}, (unsigned)dims.size(), b ? 1 : 0};
+  for (size_t k = 0; k < dims.size() && k < 2; ++k) a.dims[k] = dims[k];
+  return a;
+}
+SIMPLE_NODE(SumDimension, sum_dim, dyb200_sum_dim_attrs at = sum_dim_attrs(dims, include_batch_dim); const void* attrs_ptr = &at)
+Dim SquaredNorm::dim_forward(const std::vector<Dim>& xs) const {       // dynet/nodes-norms.cc:22-25
+  ARG_CHECK(xs.size() == 1, "Failed input count check in SquaredNorm");
+  return Dim({1}, xs[0].bd);
+}
+SIMPLE_NODE(SquaredNorm, squared_norm, NO_ATTRS)
+UNARY_DIM(Negate) SIMPLE_NODE(Negate, negate, NO_ATTRS)
+UNARY_DIM(ConstantPlusX) SIMPLE_NODE(ConstantPlusX, constant_plus_x, dyb200_const_attrs at = {c}; const void* attrs_ptr = &at)
+UNARY_DIM(ConstantMinusX) SIMPLE_NODE(ConstantMinusX, constant_minus_x, dyb200_const_attrs at = {c}; const void* attrs_ptr = &at)
 
 // ---- MatrixMultiply / AffineTransform ----
 Dim MatrixMultiply::dim_forward(const std::vector<Dim>& xs) const {   // dynet/nodes-matrixmultiply.cc:21-27

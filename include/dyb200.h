@@ -259,6 +259,27 @@ int dyb200_squared_norm(const float* x, size_t n, float* out, int accumulate, dy
 int dyb200_sgd_update(float* params, float* grads, size_t n, float lr, float clip_threshold, const float* grad_sumsq,
                       dyb200_ctx* ctx);
 
+/* Trainer update rules over a flat buffer (dynet/training.cc: SimpleSGD :619-622, MomentumSGD :669-673, Adagrad :735-739,
+ * Adadelta :802-808, RMSProp :883-888, Adam :955-961, Amsgrad :1034-1041), with Trainer::clip_gradients (:168-183) folded in:
+ * gscale = clip_threshold / sqrt(*grad_sumsq) when that norm exceeds clip_threshold (grad_sumsq NULL or clip_threshold <= 0:
+ * no clipping).  state0..2 are the rule's shadow buffers (momentum; Adagrad / RMSProp: squared-gradient accumulator;
+ * Adadelta: hg, hd; Adam: m, v; Amsgrad: m, v, vhat), NULL where the rule has none.  weight_decay is
+ * model->get_weight_decay().current_weight_decay() (1 when unused); updates = Trainer::updates before this update.
+ * zero_grads != 0 clears the gradient in the same pass (ParameterStorage::clear, dynet/model.cc:111-117); otherwise the
+ * rules that rewrite the gradient in the reference (all but SGD and momentum) leave the same values in it. */
+enum { DYB200_RULE_SGD = 0, DYB200_RULE_MOMENTUM = 1, DYB200_RULE_ADAGRAD = 2, DYB200_RULE_ADADELTA = 3, DYB200_RULE_RMSPROP = 4,
+       DYB200_RULE_ADAM = 5, DYB200_RULE_AMSGRAD = 6 };
+typedef struct {
+  float learning_rate, clip_threshold, weight_decay;
+  float momentum;          /* MomentumSGD */
+  float epsilon;           /* Adagrad, Adadelta, RMSProp, Adam, Amsgrad */
+  float rho;               /* Adadelta, RMSProp */
+  float beta_1, beta_2;    /* Adam, Amsgrad */
+  uint64_t updates;        /* Adam, Amsgrad: number of updates done so far */
+} dyb200_trainer_hyper;
+int dyb200_trainer_update(int rule, float* params, float* grads, float* state0, float* state1, float* state2, size_t n,
+                          const dyb200_trainer_hyper* hyper, const float* grad_sumsq, int zero_grads, dyb200_ctx* ctx);
+
 /* ---- GEMM used by the LSTM gates (dynet/matrix-multiply.h:16-37, :97-117, :162-180) ----
  * C[M x N] (+)= op(A) * op(B), column-major, fp32 in/out, 3xTF32 on the tensor pipe
  * when the shape allows (else an fp32 CUDA-core kernel).  transA/transB as in BLAS. */
@@ -280,6 +301,32 @@ int dyb200_matmul_fwd(DYB200_FWD_ARGS);            /* MatrixMultiply::forward_de
 int dyb200_matmul_bwd(DYB200_BWD_ARGS);            /* dynet/nodes-matrixmultiply.cc:58-74 */
 int dyb200_affine_transform_fwd(DYB200_FWD_ARGS);  /* AffineTransform::forward_dev_impl, dynet/nodes-affinetransform.cc:77-110 */
 int dyb200_affine_transform_bwd(DYB200_BWD_ARGS);  /* dynet/nodes-affinetransform.cc:112-157 */
+
+/* ---- glue nodes around the fused layers ----------------------------------------------------------- */
+typedef struct { unsigned start, end, dim; } dyb200_pick_range_attrs;                    /* PickRange(start, end, dim) */
+typedef struct { unsigned dims[2]; unsigned ndims; int include_batch_dim; } dyb200_sum_dim_attrs;   /* SumDimension(dims, b) */
+typedef struct { float c; } dyb200_const_attrs;                                          /* ConstantPlusX / ConstantMinusX */
+/* RandomBernoulli(p, scale): element e = (u_e < p) ? scale : 0 with u_e from Philox-4x32-10 keyed by `seed` at counter
+ * offset + e / 4.  The reference draws from std::mt19937 (CPU) or cuRAND's default generator (GPU); only the distribution
+ * is the same, so parity runs feed masks in instead of drawing them. */
+typedef struct { float p, scale; uint64_t seed, offset; } dyb200_bernoulli_attrs;
+int dyb200_pick_range_fwd(DYB200_FWD_ARGS);        /* dynet/nodes-select.cc:229-240 */
+int dyb200_pick_range_bwd(DYB200_BWD_ARGS);        /* dynet/nodes-select.cc:243-259 */
+int dyb200_concatenate_fwd(DYB200_FWD_ARGS);       /* attrs = dyb200_dim_attrs; dynet/nodes-concat.cc:51-68 */
+int dyb200_concatenate_bwd(DYB200_BWD_ARGS);       /* dynet/nodes-concat.cc:70-90 */
+int dyb200_sum_fwd(DYB200_FWD_ARGS);               /* n-ary Sum, dynet/nodes-arith-sum.cc:66-114 */
+int dyb200_sum_bwd(DYB200_BWD_ARGS);               /* dynet/nodes-arith-sum.cc:116-137 */
+int dyb200_sum_dim_fwd(DYB200_FWD_ARGS);           /* SumDimension (sum_dim, sum_batches), dynet/nodes-arith-sum.cc:198-217 */
+int dyb200_sum_dim_bwd(DYB200_BWD_ARGS);           /* dynet/nodes-arith-sum.cc:219-248 */
+int dyb200_squared_norm_fwd(DYB200_FWD_ARGS);      /* dynet/nodes-norms.cc:30-34 */
+int dyb200_squared_norm_bwd(DYB200_BWD_ARGS);      /* dynet/nodes-norms.cc:36-46 */
+int dyb200_negate_fwd(DYB200_FWD_ARGS);            /* dynet/nodes-arith-unary.cc:195-198 */
+int dyb200_negate_bwd(DYB200_BWD_ARGS);            /* dynet/nodes-arith-unary.cc:200-209 */
+int dyb200_constant_plus_x_fwd(DYB200_FWD_ARGS);   /* attrs = dyb200_const_attrs; dynet/nodes-arith-const.cc:62-65 */
+int dyb200_constant_plus_x_bwd(DYB200_BWD_ARGS);   /* dynet/nodes-arith-const.cc:67-75 */
+int dyb200_constant_minus_x_fwd(DYB200_FWD_ARGS);  /* dynet/nodes-arith-const.cc:29-32 */
+int dyb200_constant_minus_x_bwd(DYB200_BWD_ARGS);  /* dynet/nodes-arith-const.cc:34-42 */
+int dyb200_random_bernoulli_fwd(DYB200_FWD_ARGS);  /* dynet/nodes-random.cc:100-104 (no backward: arity 0) */
 
 #ifdef __cplusplus
 }

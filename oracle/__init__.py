@@ -428,3 +428,128 @@ def sgd_update(params, grads, lr, clip=5.0):
     gp = (f32p * n)(*[_f(g) for g in grads])
     sizes = (C.c_size_t * n)(*[p.size for p in params])
     return lib().orc_sgd_update(pp, gp, sizes, C.c_uint(n), C.c_float(lr), C.c_float(clip))
+
+
+RULES = {"sgd": 0, "momentum": 1, "adagrad": 2, "adadelta": 3, "rmsprop": 4, "adam": 5, "amsgrad": 6}
+
+
+def clip_scale(grads, clip_threshold):
+    """Trainer::clip_gradients (dynet/training.cc:168-183): clip / ||g|| when the global norm exceeds clip."""
+    gg = float(np.sqrt(sum(float((g.astype(np.float64) ** 2).sum()) for g in grads)))
+    return np.float32(clip_threshold / gg) if clip_threshold > 0 and gg > clip_threshold else np.float32(1.0)
+
+
+def trainer_update(rule, p, g, states, lr=0.1, gscale=1.0, wd=1.0, momentum=0.9, eps=1e-8, rho=0.95, beta_1=0.9,
+                   beta_2=0.999, updates=0):
+    """In-place update of p (and g, states) by the reference's rule; all arrays float32 of one size."""
+    st = [_f(s) for s in states] + [None] * (3 - len(states))
+    lib().orc_trainer_update(C.c_int(RULES[rule]), _f(p), _f(g), st[0], st[1], st[2], C.c_size_t(p.size), C.c_float(lr),
+                             C.c_float(gscale), C.c_float(wd), C.c_float(momentum), C.c_float(eps), C.c_float(rho),
+                             C.c_float(beta_1), C.c_float(beta_2), C.c_ulonglong(updates))
+    return p
+
+
+# ---------------- glue nodes (plain numpy; arrays are (bd, ..., d1, d0): batch first, C order == column-major) ----------------
+def _axis(x, dim):
+    """numpy axis of DyNet dimension `dim` of an array shaped (bd, d_{nd-1}, ..., d0)."""
+    return x.ndim - 1 - dim
+
+
+def pick_range_fwd(x, start, end, dim=0):
+    """PickRange::forward_dev_impl (dynet/nodes-select.cc:229-240): slice [start, end) of dimension dim."""
+    idx = [slice(None)] * x.ndim
+    idx[_axis(x, dim)] = slice(start, end)
+    return np.ascontiguousarray(x[tuple(idx)])
+
+
+def pick_range_bwd(x_shape, start, end, dim, dEdf, dxi):
+    """dynet/nodes-select.cc:243-259: dEdxi[slice] += dEdf."""
+    idx = [slice(None)] * len(x_shape)
+    idx[len(x_shape) - 1 - dim] = slice(start, end)
+    dxi[tuple(idx)] += dEdf
+    return dxi
+
+
+def concatenate_fwd(xs, dimension=0):
+    """Concatenate::forward_dev_impl (dynet/nodes-concat.cc:51-68); batch-1 inputs are broadcast."""
+    bd = max(x.shape[0] for x in xs)
+    parts = [np.broadcast_to(x, (bd,) + x.shape[1:]) for x in xs]
+    return np.ascontiguousarray(np.concatenate(parts, axis=_axis(xs[0], dimension)))
+
+
+def concatenate_bwd(xs, dimension, dEdf, i, dxi):
+    """dynet/nodes-concat.cc:70-90: the slice of dEdf that came from argument i, summed over the batch if it was broadcast."""
+    ax = _axis(xs[0], dimension)
+    off = sum(x.shape[ax] for x in xs[:i])
+    idx = [slice(None)] * dEdf.ndim
+    idx[ax] = slice(off, off + xs[i].shape[ax])
+    part = dEdf[tuple(idx)]
+    if xs[i].shape[0] == dEdf.shape[0]:
+        dxi += part
+    else:
+        dxi += part.astype(np.float64).sum(axis=0, keepdims=True).astype(np.float32)
+    return dxi
+
+
+def sum_fwd(xs):
+    """Sum::forward_dev_impl (dynet/nodes-arith-sum.cc:66-114), float32 in the reference's grouping."""
+    bd = max(x.shape[0] for x in xs)
+    if all(x.shape[0] == xs[0].shape[0] for x in xs):
+        def grp(g):
+            s = g[0].copy()
+            for a in g[1:]:
+                s = s + a
+            return s
+        fx = grp(xs[:4])
+        if len(xs) > 4:
+            rem = (len(xs) - 4) % 4
+            if rem:
+                fx = fx + grp(xs[4:4 + rem])
+            for q in range(4 + rem, len(xs), 4):
+                fx = fx + grp(xs[q:q + 4])
+        return fx
+    fx = np.zeros((bd,) + xs[0].shape[1:], np.float32)
+    for x in xs:
+        fx = fx + x          # numpy broadcasts the batch-1 arguments
+    return fx
+
+
+def sum_bwd(dEdf, dxi):
+    """dynet/nodes-arith-sum.cc:116-137."""
+    if dxi.shape[0] == dEdf.shape[0]:
+        dxi += dEdf
+    else:
+        dxi += dEdf.astype(np.float64).sum(axis=0, keepdims=True).astype(np.float32)
+    return dxi
+
+
+def sum_dim_fwd(x, dims, include_batch_dim=False):
+    """SumDimension::forward_dev_impl (dynet/nodes-arith-sum.cc:198-217); long sums in double, rounded once."""
+    axes = tuple(_axis(x, d) for d in dims) + ((0,) if include_batch_dim else ())
+    y = x.astype(np.float64).sum(axis=axes, keepdims=True).astype(np.float32)
+    # removed dimensions vanish from the Dim; the batch axis stays as 1
+    keep = [0] + [a for a in range(1, x.ndim) if a not in axes]
+    return np.ascontiguousarray(y.reshape([y.shape[a] for a in keep]))
+
+
+def sum_dim_bwd(x_shape, dims, include_batch_dim, dEdf, dxi):
+    """dynet/nodes-arith-sum.cc:219-248: dEdxi += broadcast(dEdf)."""
+    nd = len(x_shape)
+    shape = list(x_shape)
+    for d in dims:
+        shape[nd - 1 - d] = 1
+    if include_batch_dim:
+        shape[0] = 1
+    dxi += dEdf.reshape(shape)
+    return dxi
+
+
+def squared_norm_fwd(x):
+    """SquaredNorm::forward_dev_impl (dynet/nodes-norms.cc:30-34): one value per batch element."""
+    return (x.reshape(x.shape[0], -1).astype(np.float64) ** 2).sum(axis=1).astype(np.float32).reshape(-1, 1)
+
+
+def squared_norm_bwd(x, dEdf, dxi):
+    """dynet/nodes-norms.cc:36-46: dEdxi += x * dEdf[b] * 2."""
+    dxi += x * dEdf.reshape((-1,) + (1,) * (x.ndim - 1)) * np.float32(2.0)
+    return dxi

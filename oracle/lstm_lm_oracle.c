@@ -195,3 +195,55 @@ ORC_API float orc_sgd_update(float* const* p, float* const* g, const size_t* siz
   }
   return gg;
 }
+
+/* Trainer update rules, one statement per reference statement, each rounded to float32
+ * (dynet/training.cc: SimpleSGD :619-622, MomentumSGD :669-673, Adagrad :735-739, Adadelta :802-808,
+ * RMSProp :883-888, Adam :955-961, Amsgrad :1034-1041).  rule: 0 sgd, 1 momentum, 2 adagrad, 3 adadelta,
+ * 4 rmsprop, 5 adam, 6 amsgrad.  gscale is Trainer::clip_gradients' factor (:168-183); wd the
+ * weight-decay divisor; updates the number of updates done before this one.  The gradient is left as the
+ * rule leaves it (rules 2-6 rewrite it). */
+ORC_API void orc_trainer_update(int rule, float* p, float* g, float* s0, float* s1, float* s2, size_t n, float lr,
+                                float gscale, float wd, float momentum, float eps, float rho, float beta_1,
+                                float beta_2, unsigned long long updates) {
+  float lr_t = (float)(lr * sqrt(1 - pow(beta_2, (double)updates + 1)) / (1 - pow(beta_1, (double)updates + 1)) / wd);
+  for (size_t k = 0; k < n; ++k) {
+    switch (rule) {
+      case 0: p[k] -= g[k] * (lr * gscale / wd); break;
+      case 1:
+        s0[k] = s0[k] * momentum - g[k] * (lr * gscale);
+        p[k] += s0[k] / wd;
+        break;
+      case 2:
+        g[k] = g[k] * gscale;
+        s0[k] += g[k] * g[k];
+        p[k] += g[k] / sqrtf(s0[k] + eps) * (-lr / wd);
+        break;
+      case 3:
+        g[k] = g[k] * gscale;
+        s0[k] = s0[k] * rho + g[k] * g[k] * (1.f - rho);
+        g[k] = -g[k] * sqrtf(s1[k] + eps) / sqrtf(s0[k] + eps);
+        s1[k] = s1[k] * rho + g[k] * g[k] * (1.f - rho);
+        p[k] += g[k] / wd;
+        break;
+      case 4:
+        g[k] = g[k] * gscale;
+        s0[k] = s0[k] * rho + g[k] * g[k] * (1.f - rho);
+        g[k] = -g[k] / sqrtf(s0[k] + eps);
+        p[k] += lr * g[k] / wd;
+        break;
+      case 5:
+        g[k] = g[k] * gscale;
+        s0[k] = s0[k] * beta_1 + g[k] * (1.f - beta_1);
+        s1[k] = s1[k] * beta_2 + g[k] * g[k] * (1.f - beta_2);
+        p[k] -= s0[k] / (sqrtf(s1[k]) + eps) * lr_t;
+        break;
+      default:
+        g[k] = g[k] * gscale;
+        s0[k] = s0[k] * beta_1 + g[k] * (1.f - beta_1);
+        s1[k] = s1[k] * beta_2 + g[k] * g[k] * (1.f - beta_2);
+        s2[k] = s2[k] > s1[k] ? s2[k] : s1[k];
+        p[k] -= s0[k] / (sqrtf(s2[k]) + eps) * lr_t;
+        break;
+    }
+  }
+}

@@ -790,3 +790,179 @@ def test_affine_rejects_bad_shapes(g, capi):
         g.ctx().fwd("affine_transform", ts, g.T(y, [3, 5], 2))
     with pytest.raises(ValueError):     # inner dimensions differ
         g.ctx().fwd("matmul", [ts[1], ts[1]], g.T(y, [3, 5], 2))
+
+
+# ------------------------------------------------------------------ trainer update rules
+TRAINER_HP = {
+    "sgd": dict(lr=0.1), "momentum": dict(lr=0.01, momentum=0.9), "adagrad": dict(lr=0.1, eps=1e-20),
+    "adadelta": dict(lr=1.0, eps=1e-6, rho=0.95), "rmsprop": dict(lr=0.1, eps=1e-20, rho=0.95),
+    "adam": dict(lr=0.001, beta_1=0.9, beta_2=0.999, eps=1e-8), "amsgrad": dict(lr=0.001, beta_1=0.9, beta_2=0.999, eps=1e-8),
+}
+TRAINER_STATES = {"sgd": 0, "momentum": 1, "adagrad": 1, "adadelta": 2, "rmsprop": 1, "adam": 2, "amsgrad": 3}
+
+
+@pytest.mark.parametrize("rule", sorted(TRAINER_HP))
+@pytest.mark.parametrize("n,misalign", [(1, 0), (1003, 1), ((1 << 20) + 5, 0)])
+def test_trainer_update(oracle, g, capi, rule, n, misalign):
+    """Three consecutive updates (clipping active on the first) against the reference's statements on the CPU."""
+    r = rng(500 + n)
+    hp = TRAINER_HP[rule]
+    p = randn(r, n)
+    states = [np.abs(randn(r, n)) * 0.1 for _ in range(TRAINER_STATES[rule])]
+    p_d = g.dev(p, misalign)
+    s_d = [g.dev(s, misalign) for s in states]
+    sumsq = g.dev(np.zeros(1, np.float32))
+    for upd in range(3):
+        grad = randn(r, n, scale=3.0 if upd == 0 else 0.01)
+        g_d = g.dev(grad, misalign)
+        gscale = oracle.clip_scale([grad], 5.0)
+        oracle.trainer_update(rule, p, grad, states, gscale=gscale, wd=1.0, updates=upd, momentum=hp.get("momentum", 0.9),
+                              eps=hp.get("eps", 1e-8), rho=hp.get("rho", 0.95), beta_1=hp.get("beta_1", 0.9),
+                              beta_2=hp.get("beta_2", 0.999), lr=hp["lr"])
+        hyper = capi.TrainerHyper(hp["lr"], 5.0, 1.0, hp.get("momentum", 0.9), hp.get("eps", 1e-8), hp.get("rho", 0.95),
+                                  hp.get("beta_1", 0.9), hp.get("beta_2", 0.999), upd)
+        g.ctx().check(g.ctx().L.dyb200_squared_norm(g_d.data_ptr(), n, sumsq.data_ptr(), 0, g.ctx().h))
+        g.ctx().trainer_update(rule, p_d.data_ptr(), g_d.data_ptr(), [s.data_ptr() for s in s_d], n, hyper, sumsq.data_ptr(),
+                               zero_grads=(upd == 2))
+        assert_close(g.host(p_d), p, 2e-5, floor=1.0, what="%s params after update %d" % (rule, upd))
+        for k, s in enumerate(states):
+            assert_close(g.host(s_d[k]), s, 2e-5, floor=0.1, what="%s state %d after update %d" % (rule, k, upd))
+        if upd == 2:
+            assert not g.host(g_d).any()
+        elif rule not in ("sgd", "momentum"):
+            assert_close(g.host(g_d), grad, 2e-5, floor=0.1, what="%s rewritten gradient" % rule)
+
+
+# ------------------------------------------------------------------ glue nodes
+def _t(g, d):
+    """DyTensor of a torch tensor shaped (bd, ..., d1, d0)."""
+    return g.T(d)
+
+
+@pytest.mark.parametrize("shape,start,end,dim", [((4, 1, 8), 2, 6, 0), ((3, 5, 7), 1, 3, 1), ((2, 4, 130), 1, 129, 0),
+                                                 ((64, 1, 4096), 1024, 2048, 0), ((2, 3, 4, 8), 1, 2, 2)])
+def test_pick_range(oracle, g, capi, shape, start, end, dim):
+    r = rng(610)
+    x = randn(r, *shape)
+    want = oracle.pick_range_fwd(x, start, end, dim)
+    x_d, y_d = g.dev(x), g.dev(np.zeros_like(want))
+    at = capi.PickRangeAttrs(start, end, dim)
+    g.ctx().fwd("pick_range", [_t(g, x_d)], _t(g, y_d), at)
+    assert np.array_equal(g.host(y_d), want)
+    dy, dx0 = randn(r, *want.shape), randn(r, *shape)
+    dx_d = g.dev(dx0)
+    g.ctx().bwd("pick_range", [_t(g, x_d)], _t(g, y_d), _t(g, g.dev(dy)), 0, _t(g, dx_d), at)
+    assert np.array_equal(g.host(dx_d), oracle.pick_range_bwd(shape, start, end, dim, dy, dx0.copy()))
+
+
+@pytest.mark.parametrize("shapes,dimension", [([(4, 1, 8), (4, 1, 3)], 0), ([(3, 2, 4), (1, 5, 4)], 1),
+                                              ([(32, 1, 512), (32, 1, 1024), (1, 1, 4)], 0), ([(2, 3, 4), (2, 3, 4)], 2)])
+def test_concatenate(oracle, g, capi, shapes, dimension):
+    r = rng(611)
+    if dimension == 2:   # concatenating along a new trailing dimension: give the inputs an explicit size-1 axis
+        shapes = [(s[0], 1) + s[1:] for s in shapes]
+    xs = [randn(r, *s) for s in shapes]
+    want = oracle.concatenate_fwd(xs, dimension)
+    devs = [g.dev(x) for x in xs]
+    y_d = g.dev(np.zeros_like(want))
+    at = capi.DimAttrs(dimension)
+    g.ctx().fwd("concatenate", [_t(g, d) for d in devs], _t(g, y_d), at)
+    assert np.array_equal(g.host(y_d), want)
+    dy = randn(r, *want.shape)
+    dy_d = g.dev(dy)
+    for i, x in enumerate(xs):
+        d0 = randn(r, *x.shape)
+        dx_d = g.dev(d0)
+        g.ctx().bwd("concatenate", [_t(g, d) for d in devs], _t(g, y_d), _t(g, dy_d), i, _t(g, dx_d), at)
+        assert_close(g.host(dx_d), oracle.concatenate_bwd(xs, dimension, dy, i, d0.copy()), TOL_REDUCE, floor=ACC_FLOOR,
+                     what="concatenate bwd %d" % i)
+
+
+@pytest.mark.parametrize("nargs,mixed", [(1, False), (2, False), (3, False), (4, False), (5, False), (7, False), (11, False), (50, False), (3, True)])
+def test_sum_nary(oracle, g, capi, nargs, mixed):
+    r = rng(612 + nargs)
+    xs = [randn(r, 1 if (mixed and k == 1) else 4, 1, 300) for k in range(nargs)]
+    want = oracle.sum_fwd(xs)
+    devs = [g.dev(x) for x in xs]
+    y_d = g.dev(np.zeros_like(want))
+    g.ctx().fwd("sum", [_t(g, d) for d in devs], _t(g, y_d))
+    if mixed:
+        assert_close(g.host(y_d), want, TOL_CWISE, floor=1.0, what="sum mixed")
+    else:
+        assert np.array_equal(g.host(y_d), want)    # same grouping as the reference: bit-exact
+    dy = randn(r, *want.shape)
+    for i in (0, min(1, nargs - 1)):
+        d0 = randn(r, *xs[i].shape)
+        dx_d = g.dev(d0)
+        g.ctx().bwd("sum", [_t(g, d) for d in devs], _t(g, y_d), _t(g, g.dev(dy)), i, _t(g, dx_d))
+        assert_close(g.host(dx_d), oracle.sum_bwd(dy, d0.copy()), TOL_REDUCE, floor=ACC_FLOOR, what="sum bwd")
+
+
+@pytest.mark.parametrize("shape,dims,ib", [((3, 4, 5), (0,), False), ((3, 4, 5), (1,), True), ((3, 4, 5), (0, 1), False),
+                                           ((512, 1, 35), (), True), ((16, 1, 4096), (0,), False), ((2, 3, 4, 5), (2,), False),
+                                           ((5, 2, 3), (0, 1), True)])
+def test_sum_dim(oracle, g, capi, shape, dims, ib):
+    r = rng(613)
+    x = randn(r, *shape)
+    want = oracle.sum_dim_fwd(x, dims, ib)
+    x_d, y_d = g.dev(x), g.dev(np.zeros_like(want))
+    at = capi.SumDimAttrs((C.c_uint * 2)(*(list(dims) + [0] * (2 - len(dims)))), len(dims), int(ib))
+    nd = len(shape) - 1
+    tx = g.T(x_d)
+    ty = capi.DyTensor.of(y_d.data_ptr(), list(want.shape[1:][::-1]), want.shape[0])
+    g.ctx().fwd("sum_dim", [tx], ty, at)
+    assert_close(g.host(y_d), want, TOL_REDUCE, floor=1.0, what="sum_dim fwd")
+    dy, d0 = randn(r, *want.shape), randn(r, *shape)
+    dx_d = g.dev(d0)
+    tdy = capi.DyTensor.of(g.dev(dy).data_ptr(), list(want.shape[1:][::-1]), want.shape[0])
+    g.ctx().bwd("sum_dim", [tx], ty, tdy, 0, g.T(dx_d), at)
+    assert_close(g.host(dx_d), oracle.sum_dim_bwd(shape, dims, ib, dy, d0.copy()), TOL_CWISE, floor=ACC_FLOOR, what="sum_dim bwd")
+
+
+@pytest.mark.parametrize("shape", [(32, 1, 256), (1, 1, 1), (3, 7, 33), (2, 1, 100003)])
+def test_squared_norm(oracle, g, capi, shape):
+    r = rng(614)
+    x = randn(r, *shape)
+    want = oracle.squared_norm_fwd(x)
+    x_d, y_d = g.dev(x), g.dev(np.zeros_like(want))
+    g.ctx().fwd("squared_norm", [g.T(x_d)], g.T(y_d))
+    assert_close(g.host(y_d), want, TOL_REDUCE, what="squared_norm fwd")
+    dy, d0 = randn(r, *want.shape), randn(r, *shape)
+    dx_d = g.dev(d0)
+    g.ctx().bwd("squared_norm", [g.T(x_d)], g.T(y_d), g.T(g.dev(dy)), 0, g.T(dx_d))
+    assert_close(g.host(dx_d), oracle.squared_norm_bwd(x, dy, d0.copy()), TOL_CWISE, floor=ACC_FLOOR, what="squared_norm bwd")
+
+
+@pytest.mark.parametrize("name,c", [("negate", 0.0), ("constant_plus_x", 1e-8), ("constant_plus_x", 2.5), ("constant_minus_x", 1.0)])
+def test_const_unary(g, capi, name, c):
+    r = rng(615)
+    x = randn(r, 3, 1001)
+    want = {"negate": -x, "constant_plus_x": x + np.float32(c), "constant_minus_x": np.float32(c) - x}[name]
+    x_d, y_d = g.dev(x), g.dev(np.zeros_like(x))
+    at = None if name == "negate" else capi.ConstAttrs(c)
+    g.ctx().fwd(name, [g.T(x_d)], g.T(y_d), at)
+    assert np.array_equal(g.host(y_d), want)
+    dy, d0 = randn(r, *x.shape), randn(r, *x.shape)
+    dx_d = g.dev(d0)
+    g.ctx().bwd(name, [g.T(x_d)], g.T(y_d), g.T(g.dev(dy)), 0, g.T(dx_d), at)
+    assert np.array_equal(g.host(dx_d), d0 + dy if name == "constant_plus_x" else d0 - dy)
+
+
+def test_random_bernoulli(g, capi):
+    """Values are 0 or scale, the keep rate matches p, equal seeds repeat and different offsets differ."""
+    n = 1 << 20
+    y = g.dev(np.zeros((1, n + 3), np.float32))
+    def draw(seed, offset, p=0.8, scale=1.25):
+        g.ctx().fwd("random_bernoulli", [], g.T(y), capi.BernoulliAttrs(p, scale, seed, offset))
+        return g.host(y).copy()
+    a = draw(7, 0)
+    assert set(np.unique(a)) == {0.0, 1.25}
+    assert abs((a != 0).mean() - 0.8) < 4 * np.sqrt(0.8 * 0.2 / a.size)
+    assert np.array_equal(a, draw(7, 0))
+    b = draw(7, (n + 3 + 3) // 4)
+    assert 0.6 < (a == b).mean() < 0.75          # independent draws agree with probability p^2 + (1-p)^2 = 0.68
+    assert not np.array_equal(a, draw(8, 0))
+    assert not draw(7, 0, p=0.0).any() and draw(7, 0, p=1.0, scale=2.0).min() == 2.0
+    # neighbouring elements are uncorrelated
+    k = (a[0, :-1] != 0).astype(np.float64); l = (a[0, 1:] != 0).astype(np.float64)
+    assert abs(np.corrcoef(k, l)[0, 1]) < 0.01

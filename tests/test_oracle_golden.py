@@ -346,3 +346,91 @@ def test_affine_rejects_batched_bias_broadcast(oracle):
     xs = [randn(r, 2, 1, 3), randn(r, 1, 4, 3), randn(r, 2, 5, 4)]   # bias {3} x2 under a {3,5} x2 result
     with pytest.raises(ValueError):
         oracle.affine_fwd(xs)
+
+
+# ---------------------------------------------------------------- trainer update rules
+# defaults of the reference's constructors (dynet/training.h:318, :405, :448, :489, :531, :573, :619)
+TRAINER_DEFAULTS = {
+    "sgd": dict(lr=0.1), "momentum": dict(lr=0.01, momentum=0.9), "adagrad": dict(lr=0.1, eps=1e-20),
+    "adadelta": dict(lr=1.0, eps=1e-6, rho=0.95), "rmsprop": dict(lr=0.1, eps=1e-20, rho=0.95),
+    "adam": dict(lr=0.001, beta_1=0.9, beta_2=0.999, eps=1e-8), "amsgrad": dict(lr=0.001, beta_1=0.9, beta_2=0.999, eps=1e-8),
+}
+N_STATES = {"sgd": 0, "momentum": 1, "adagrad": 1, "adadelta": 2, "rmsprop": 1, "adam": 2, "amsgrad": 3}
+
+
+@pytest.mark.parametrize("rule", sorted(TRAINER_DEFAULTS))
+def test_trainer_direction(oracle, rule):
+    """tests/test-trainers.cc:53-85: one update on z = ones . x (gradient = ones) must lower z."""
+    p = f32([1.1, -2.2, 3.3])
+    g = np.ones(3, np.float32)
+    states = [np.zeros(3, np.float32) for _ in range(N_STATES[rule])]
+    before = float(p.sum())
+    oracle.trainer_update(rule, p, g, states, gscale=oracle.clip_scale([g], 5.0), **TRAINER_DEFAULTS[rule])
+    assert float(p.sum()) < before
+
+
+def test_momentum_velocity_known_answer(oracle):
+    """tests/test-trainers.cc:141-155: MomentumSGDTrainer(pc, 1.0), gradient of ones -> velocity exactly -1."""
+    p, g, v = np.zeros(3, np.float32), np.ones(3, np.float32), np.zeros(3, np.float32)
+    oracle.trainer_update("momentum", p, g, [v], lr=1.0, momentum=0.9)
+    assert np.array_equal(v, -np.ones(3, np.float32))
+    assert np.array_equal(p, -np.ones(3, np.float32))
+
+
+def test_trainer_rules_against_float64(oracle):
+    r = rng(321)
+    n = 257
+    for rule, hp in TRAINER_DEFAULTS.items():
+        p, g = randn(r, n), randn(r, n)
+        st = [np.abs(randn(r, n)) * 0.1 for _ in range(N_STATES[rule])]
+        p0, g0, s0 = p.astype(np.float64), g.astype(np.float64) * 0.5, [s.astype(np.float64) for s in st]
+        oracle.trainer_update(rule, p, g, st, gscale=0.5, wd=1.0, updates=3, **hp)
+        lr = hp["lr"]
+        if rule == "sgd":
+            want = p0 - g0 * lr
+        elif rule == "momentum":
+            want = p0 + (s0[0] * hp["momentum"] - g0 * lr)
+        elif rule == "adagrad":
+            want = p0 - lr * g0 / np.sqrt(s0[0] + g0 * g0 + hp["eps"])
+        elif rule == "rmsprop":
+            want = p0 - lr * g0 / np.sqrt(s0[0] * hp["rho"] + g0 * g0 * (1 - hp["rho"]) + hp["eps"])
+        elif rule == "adadelta":
+            hg = s0[0] * hp["rho"] + g0 * g0 * (1 - hp["rho"])
+            want = p0 - g0 * np.sqrt(s0[1] + hp["eps"]) / np.sqrt(hg + hp["eps"])
+        else:
+            m = s0[0] * hp["beta_1"] + g0 * (1 - hp["beta_1"])
+            v = s0[1] * hp["beta_2"] + g0 * g0 * (1 - hp["beta_2"])
+            if rule == "amsgrad":
+                v = np.maximum(s0[2], v)
+            lr_t = lr * np.sqrt(1 - hp["beta_2"] ** 4) / (1 - hp["beta_1"] ** 4)
+            want = p0 - m / (np.sqrt(v) + hp["eps"]) * lr_t
+        assert_close(p, want, 1e-5, floor=1.0, what=rule)
+
+
+# ---------------------------------------------------------------- glue nodes
+def test_glue_nodes_gradients(oracle):
+    """Finite-difference rule of dynet/grad-check.cc on the numpy restatements of PickRange, Concatenate, Sum,
+    SumDimension and SquaredNorm (the reference checks them the same way, tests/test-nodes.cc)."""
+    r = rng(42)
+    x = randn(r, 2, 3, 5)
+    y = oracle.pick_range_fwd(x, 1, 4, 0)
+    assert y.shape == (2, 3, 3)
+    fd_check(lambda v: sq(oracle.pick_range_fwd(v[0], 1, 4, 0)), [x],
+             lambda i: oracle.pick_range_bwd(x.shape, 1, 4, 0, 2 * y, np.zeros_like(x)))
+    a, b = randn(r, 3, 2, 4), randn(r, 1, 5, 4)
+    c = oracle.concatenate_fwd([a, b], 1)
+    assert c.shape == (3, 7, 4)
+    args = [a, b]
+    fd_check(lambda v: sq(oracle.concatenate_fwd(v, 1)), args,
+             lambda i: oracle.concatenate_bwd(args, 1, 2 * c, i, np.zeros_like(args[i])))
+    xs = [randn(r, 2, 6) for _ in range(6)] + [randn(r, 1, 6)]
+    s = oracle.sum_fwd(xs)
+    fd_check(lambda v: sq(oracle.sum_fwd(v)), xs, lambda i: oracle.sum_bwd(2 * s, np.zeros_like(xs[i])))
+    t = randn(r, 3, 4, 5)
+    for dims, ib in [((0,), False), ((1,), True), ((0, 1), False), ((), True)]:
+        z = oracle.sum_dim_fwd(t, dims, ib)
+        fd_check(lambda v: sq(oracle.sum_dim_fwd(v[0], dims, ib)), [t],
+                 lambda i: oracle.sum_dim_bwd(t.shape, dims, ib, 2 * z, np.zeros_like(t)))
+    n = oracle.squared_norm_fwd(t)
+    fd_check(lambda v: sq(oracle.squared_norm_fwd(v[0])), [t],
+             lambda i: oracle.squared_norm_bwd(t, 2 * n, np.zeros_like(t)))
