@@ -193,6 +193,15 @@ def lib():
             f = getattr(L, n)
             f.restype = C.c_int
             f.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        # every pointer-taking entry point gets explicit argtypes: without them ctypes passes Python ints as 32-bit C ints
+        L.dyb200_fill.restype = C.c_int
+        L.dyb200_fill.argtypes = [C.c_void_p, C.c_size_t, C.c_float, C.c_void_p]
+        for name in ("dyb200_sum_all", "dyb200_squared_norm"):
+            f = getattr(L, name)
+            f.restype = C.c_int
+            f.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_int, C.c_void_p]
+        L.dyb200_sgd_update.restype = C.c_int
+        L.dyb200_sgd_update.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_float, C.c_void_p, C.c_void_p]
         L.dyb200_trainer_update.restype = C.c_int
         L.dyb200_trainer_update.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                             C.POINTER(TrainerHyper), C.c_void_p, C.c_int, C.c_void_p]
@@ -317,6 +326,12 @@ class Context:
 
     def wgrad_flush(self, w, C0, ldc0, C1=None, ldc1=0):
         self.check(self.L.dyb200_wgrad_flush(w, C0, ldc0, C1, ldc1, self.h))
+
+    def squared_norm(self, x_ptr, n, out_ptr, accumulate=False):
+        self.check(self.L.dyb200_squared_norm(x_ptr, n, out_ptr, int(accumulate), self.h))
+
+    def sum_all(self, x_ptr, n, out_ptr, accumulate=False):
+        self.check(self.L.dyb200_sum_all(x_ptr, n, out_ptr, int(accumulate), self.h))
 
     def trainer_update(self, rule, params, grads, states, n, hyper, grad_sumsq=None, zero_grads=True):
         """rule: key of RULES; params / grads / states / grad_sumsq: device pointers (ints)."""

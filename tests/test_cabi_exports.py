@@ -41,3 +41,13 @@ def test_no_cpu_fallback_without_gpu(built):
         pytest.skip("a GPU is present")
     with pytest.raises(capi.Dyb200Error):
         capi.Context(0)
+
+
+def test_every_binding_declares_its_argument_types(built):
+    """ctypes passes a Python int as a 32-bit C int unless argtypes says otherwise: a device pointer given to an
+    undeclared function is truncated.  Every entry point the binding exposes must therefore carry argtypes."""
+    from dynet_b200 import capi
+    L = capi.lib()
+    no_args = {"dyb200_version"}
+    untyped = [s for s in capi.exported_symbols() if s not in no_args and getattr(L, s).argtypes is None]
+    assert not untyped, untyped

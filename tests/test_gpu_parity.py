@@ -821,7 +821,7 @@ def test_trainer_update(oracle, g, capi, rule, n, misalign):
                               beta_2=hp.get("beta_2", 0.999), lr=hp["lr"])
         hyper = capi.TrainerHyper(hp["lr"], 5.0, 1.0, hp.get("momentum", 0.9), hp.get("eps", 1e-8), hp.get("rho", 0.95),
                                   hp.get("beta_1", 0.9), hp.get("beta_2", 0.999), upd)
-        g.ctx().check(g.ctx().L.dyb200_squared_norm(g_d.data_ptr(), n, sumsq.data_ptr(), 0, g.ctx().h))
+        g.ctx().squared_norm(g_d.data_ptr(), n, sumsq.data_ptr())
         g.ctx().trainer_update(rule, p_d.data_ptr(), g_d.data_ptr(), [s.data_ptr() for s in s_d], n, hyper, sumsq.data_ptr(),
                                zero_grads=(upd == 2))
         assert_close(g.host(p_d), p, 2e-5, floor=1.0, what="%s params after update %d" % (rule, upd))
