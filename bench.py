@@ -211,15 +211,14 @@ def run_gpu(args):
         pinned = torch.from_numpy(tok.view(np.int32)).pin_memory()
         host_tokens.append(pinned)
         dev_tokens.append(pinned.cuda())
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(1234 + rank)
     keep = 1.0 - DROPOUT
     masks = model.mask_buffers()          # the driver's own buffers: fixed addresses, so the step can be a CUDA graph
+    mask_step = [0]
 
     def draw_masks():
         # RandomBernoulli(keep) * 1/keep per layer, fixed over the sequence (dynet/lstm.cc:964-982), drawn every step
-        for mk in masks:
-            mk.copy_((torch.rand(mk.shape, device="cuda", generator=gen) < keep).float() * (1.0 / keep))
+        model.draw_masks(keep, 1234 + rank, mask_step[0])
+        mask_step[0] += 1
 
     def step(tokens):
         draw_masks()

@@ -194,6 +194,24 @@ class LstmLm:
             out.append(self.workspace[off:off + 4 * B * cols].view(self.torch.float32).view(B, cols))
         return out
 
+    def draw_masks(self, keep, seed, step):
+        """Fresh dropout masks in the driver's buffers: RandomBernoulli(keep, 1/keep) per layer input and hidden state
+        (dynet/lstm.cc:964-982), one launch per mask; `step` selects a disjoint stretch of the random stream."""
+        from . import capi
+        bufs = self.mask_buffers()
+        off = 0
+        for k, mk in enumerate(bufs):
+            n = mk.numel()
+            at = capi.BernoulliAttrs(float(keep), 1.0 / float(keep), int(seed), int(step) * self._mask_quads + off)
+            self.ctx.fwd("random_bernoulli", [], capi.DyTensor.of(mk.data_ptr(), [mk.shape[1]], mk.shape[0]), at)
+            off += (n + 3) // 4
+        return bufs
+
+    @property
+    def _mask_quads(self):
+        V, E, H, L, T, B = self.dims
+        return sum(((B * ((E if l == 0 else H)) + 3) // 4) + ((B * H + 3) // 4) for l in range(L))
+
     def allreduce_grads(self):
         """Sum the flat gradient buffer over the data-parallel ranks (NCCL over NVLink)."""
         import torch.distributed as dist
