@@ -151,4 +151,7 @@ __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<floa
 __device__ __forceinline__ void st4_stream(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
 
 __device__ __forceinline__ float sigmoidf_dev(float x) { return 1.0f / (1.0f + expf(-x)); }
+// c = i g + f c_tm1 and h = o tanh(c) with one fixed rounding sequence, shared by every kernel that forms them
+__device__ __forceinline__ float lstm_cell_c(float i, float g, float f, float c_tm1) { return __fmaf_rn(i, g, __fmul_rn(f, c_tm1)); }
+__device__ __forceinline__ float lstm_cell_h(float o, float c) { return __fmul_rn(o, tanhf(c)); }
 #endif

@@ -20,7 +20,11 @@ enum GemmEpiMode {
   EPI_ACCUM = 1,      // C += acc
   EPI_GATES = 2,      // C = act(acc + bias[m] + (H <= m < 2H ? forget_bias : 0)); sigmoid for m < 3H, tanh above
   EPI_ACCUM_MASK = 3, // C += acc * maskC[m + (maskc_full ? maskc_ld * n : 0)]
-  EPI_BIAS = 4        // C = acc + bias[m]   (column vector broadcast over the N columns)
+  EPI_BIAS = 4,       // C = acc + bias[m]   (column vector broadcast over the N columns)
+  // The A operand was packed with interleaved gate rows (dyb200_tc_param_gates): tile t, row 32 q + l is gate q
+  // (i, f, o, g) of hidden unit u = 32 t + l.  gates[q H + u, n] = act(acc + bias + forget bias) as in EPI_GATES,
+  // then c_out[u, n] = i g + f c_prev[u, n] and h_out[u, n] = o tanh(c) (VanillaLSTMC / VanillaLSTMH forward).
+  EPI_LSTM_CELL = 5
 };
 
 struct GemmEpilogue {
@@ -33,6 +37,8 @@ struct GemmEpilogue {
   uint32_t split_m = 0;
   float* C2 = nullptr; uint32_t ldc2 = 0;
   const float* maskC2 = nullptr; uint32_t maskc2_ld = 0; int maskc2_full = 0;
+  // EPI_LSTM_CELL only: previous cell state and the two outputs, all H x N with leading dimension H
+  const float* c_prev = nullptr; float* c_out = nullptr; float* h_out = nullptr;
 };
 // Row m of the product -> destination pointer of column 0, leading dimension and mask of that row.
 struct EpiRow { float* c; uint32_t ldc; const float* mask; uint32_t mask_ld; int mask_full; };
@@ -57,9 +63,10 @@ int dyb200_gemm_fused(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const
 struct PackedOp { float* hi; float* lo; uint32_t rows, K, pitch; };   // K-major TF32 hi / lo planes
 // A queue of packing work that one kernel launch executes (several small operands per launch).
 constexpr int kMaxPackJobs = 8;
+constexpr int kLayoutGates = 2;
 struct PackJob {
   const float* src; const float* mask; float* hi; float* lo;
-  uint32_t ld, rows, K, mask_ld, pitch, gx;
+  uint32_t ld, rows, K, mask_ld, pitch, gx, perm_H;
   int k_is_fast, mask_full, vec;
 };
 struct PackJobs { PackJob job[kMaxPackJobs]; uint32_t start[kMaxPackJobs + 1]; int n; };
@@ -72,6 +79,10 @@ int dyb200_tc_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fas
                    const float* mask, uint32_t mask_ld, int mask_full, PackedOp* out, PackJobs* batch = nullptr);
 // Same for a parameter matrix: served from the parameter cache when it is on.
 int dyb200_tc_param(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, PackedOp* out);
+// A gate weight matrix (rows = 4H, element (r, k) at src[r + ld * k]) with its rows interleaved for EPI_LSTM_CELL.
+int dyb200_tc_param_gates(dyb200_ctx* ctx, const float* src, uint32_t ld, uint32_t rows, uint32_t K, PackedOp* out);
+// Number of K splits dyb200_tc_gemm_packed will use for this shape (1 = the epilogue runs in the MMA kernel).
+uint32_t dyb200_tc_splits(const dyb200_ctx* ctx, uint32_t M, uint32_t N, uint32_t kb_total);
 // Two parameter matrices with the same K and leading dimension stacked along the rows: rows [0, rows) from src,
 // rows [rows, rows + rows2) from src2.
 int dyb200_tc_param2(dyb200_ctx* ctx, const float* src, uint32_t rows, const float* src2, uint32_t rows2, uint32_t ld,

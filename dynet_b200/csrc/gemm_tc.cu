@@ -8,9 +8,11 @@
 // kernel that also brings the operand to K-major order (the reduction index contiguous) and
 // applies the dropout mask, so the GEMM kernel itself only moves tiles and issues MMAs:
 //   warp 0     TMA producer: 4 tiles (A_hi, A_lo, B_hi, B_lo) per 32-wide k-block, 3-stage ring
-//   warp 1     allocates TMEM, issues 3 MMAs per 8-wide k-step, commits to the ring's mbarriers
-//   warps 2-9  epilogue: tcgen05.ld of their 32 accumulator lanes x 64 columns, fused epilogue,
-//              coalesced stores; read-modify-write epilogues load a whole 32-column chunk first
+//   warp 1     allocates TMEM, issues 3 MMAs per 8-wide k-step, commits to the ring's mbarriers;
+//              the accumulation chain is cut every kChunkKB k-blocks (two TMEM accumulators, used alternately)
+//   warps 2-9  add every finished chunk (tcgen05.ld of their 32 accumulator lanes x 64 columns) into fp32
+//              registers, then run the fused epilogue with coalesced stores; read-modify-write epilogues load
+//              a whole 32-column chunk first; the LSTM epilogue also forms c and h (gates exchanged in smem)
 // Products with few output tiles are split along K over blockIdx.z; the splits store raw partial
 // tiles and a second kernel adds them in split order and applies the epilogue (deterministic).
 // Every mbarrier wait is bounded; a wait that runs out sets DYB200_FLAG_WAIT_TIMEOUT and the
@@ -27,7 +29,13 @@ constexpr int STAGE_BYTES = 4 * TILE_BYTES;      // A_hi, A_lo, B_hi, B_lo
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + slack to align the ring to 1 KiB
 constexpr int kThreads = 320;              // TMA warp, MMA warp, 8 epilogue warps
 constexpr uint32_t kWaitLimit = 1u << 20;
-constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kTmemCols = 256;       // two 128-column accumulators, used alternately       // two 128-column accumulators, used alternately
+// k-blocks accumulated in TMEM before the sum moves to registers.  Measured against a float64 product (randn operands,
+// worst element / rms of the result): one unbroken chain 1.9e-5 at K = 2048 and 1.6e-4 at K = 17920 (biased towards
+// zero); chains of 8 k-blocks 8.7e-6 at both, against 2.6e-6 .. 9.3e-6 for cuBLAS SGEMM.  Each flush costs about
+// 0.4 us of tensor-pipe time (4 % at this setting).
+constexpr uint32_t kChunkKB = 8;
+constexpr uint32_t kEpiWarps = 8;
 
 struct TmapPack { CUtensorMap t[8]; };   // pair p: t[4p] = A_hi, A_lo, B_hi, B_lo
 
@@ -94,11 +102,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ TmapPack tm, uint32_t M, uint32_t N,
                                                          uint32_t kb0, uint32_t kb1, uint32_t kb_per_split,
                                                          GemmEpilogue epi, uint32_t* flags) {
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -107,11 +119,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
   const uint32_t kb_begin = blockIdx.z * kb_per_split;
   const uint32_t kb_end = min(kb0 + kb1, kb_begin + kb_per_split);
   const uint32_t total = kb_end > kb_begin ? kb_end - kb_begin : 0;
+  const uint32_t nchunks = (total + kChunkKB - 1) / kChunkKB;
   if (gridDim.z > 1) epi.C += (size_t)blockIdx.z * epi.ldc * N;   // raw partial tile of this split (mode is EPI_STORE)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    mbar_init(&accum_bar, 1);
+    for (int q = 0; q < 2; ++q) { mbar_init(&acc_full[q], 1); mbar_init(&acc_empty[q], kEpiWarps); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -126,8 +139,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
 
   if (warp == 0) {
     if (lane == 0) {
+      uint32_t s = 0, ph = 0;
       for (uint32_t it = 0; it < total; ++it) {
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1)) { atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT); break; }
         const uint32_t g = kb_begin + it;
         const uint32_t pair = g < kb0 ? 0 : 1, kblk = pair ? g - kb0 : g;
@@ -137,85 +150,183 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         tma_load_2d(st + TILE_BYTES, &tm.t[4 * pair + 1], &full_bar[s], (int)(kblk * BK), (int)m0);
         tma_load_2d(st + 2 * TILE_BYTES, &tm.t[4 * pair + 2], &full_bar[s], (int)(kblk * BK), (int)n0);
         tma_load_2d(st + 3 * TILE_BYTES, &tm.t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), (int)n0);
+        if (++s == STAGES) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // This one thread issues every MMA of the tile, and the tensor pipe is only as busy as this loop is short:
+      // descriptors of the three stages are built once, stage / phase / chunk counters are carried instead of divided,
+      // and the 12 MMAs of a k-block go out in one block of PTX.
       // instruction descriptor: D = f32, A = B = tf32, both K-major, N = 128, M = 128
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      bool ok = true;
-      for (uint32_t it = 0; it < total && ok; ++it) {
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-        if (!mbar_wait(&full_bar[s], ph)) { atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT); ok = false; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t base = smem_u32(ring + (size_t)s * STAGE_BYTES);
-        const uint64_t a_hi = umma_desc(base), a_lo = umma_desc(base + TILE_BYTES);
-        const uint64_t b_hi = umma_desc(base + 2 * TILE_BYTES), b_lo = umma_desc(base + 3 * TILE_BYTES);
+      uint64_t d_a_hi[STAGES], d_a_lo[STAGES], d_b_hi[STAGES], d_b_lo[STAGES];
 #pragma unroll
-        for (uint32_t j = 0; j < BK / 8; ++j) {   // one MMA consumes 8 tf32 = 32 bytes of K: +2 in descriptor units
-          const uint64_t adv = 2 * j;
-          umma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (it | j) != 0);
-          umma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1);
-          umma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1);
-        }
-        umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
+      for (int q = 0; q < STAGES; ++q) {
+        const uint32_t base = smem_u32(ring + (size_t)q * STAGE_BYTES);
+        d_a_hi[q] = umma_desc(base); d_a_lo[q] = umma_desc(base + TILE_BYTES);
+        d_b_hi[q] = umma_desc(base + 2 * TILE_BYTES); d_b_lo[q] = umma_desc(base + 3 * TILE_BYTES);
       }
-      umma_commit(&accum_bar);
+      // The tensor core truncates when it aligns addends to the accumulator, a bias that grows with the length of
+      // the accumulation chain.  So the chain is cut every kChunkKB k-blocks: chunk c accumulates into TMEM buffer
+      // c & 1 from zero, and the epilogue warps add finished chunks into fp32 registers with ordinary rounding.
+      uint32_t s = 0, ph = 0, in_chunk = 0, chunk = 0, buf = 0;
+      for (uint32_t it = 0; it < total; ++it) {
+        if (in_chunk == 0 && chunk >= 2) {   // buffer reuse: the epilogue warps must have drained chunk - 2
+          if (!mbar_wait(&acc_empty[buf], ((chunk >> 1) - 1) & 1)) { atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT); break; }
+        }
+        if (!mbar_wait(&full_bar[s], ph)) { atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT); break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint64_t a_hi, a_lo, b_hi, b_lo;   // select without dynamic register indexing
+        if (s == 0) { a_hi = d_a_hi[0]; a_lo = d_a_lo[0]; b_hi = d_b_hi[0]; b_lo = d_b_lo[0]; }
+        else if (s == 1) { a_hi = d_a_hi[1]; a_lo = d_a_lo[1]; b_hi = d_b_hi[1]; b_lo = d_b_lo[1]; }
+        else { a_hi = d_a_hi[2]; a_lo = d_a_lo[2]; b_hi = d_b_hi[2]; b_lo = d_b_lo[2]; }
+        const uint32_t acc = tmem_base + buf * BN;
+        // one MMA consumes 8 tf32 = 32 bytes of K: +2 in descriptor units per k8 step
+        asm volatile(
+            "{\n\t.reg .pred pf, pt;\n\t.reg .b64 xa, xb, ya, yb;\n\t"
+            "setp.ne.b32 pf, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %2, %3, %5, pf;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %4, %5, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %3, %5, pt;\n\t"
+            "add.s64 xa, %1, 2;\n\tadd.s64 xb, %2, 2;\n\tadd.s64 ya, %3, 2;\n\tadd.s64 yb, %4, 2;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t"
+            "add.s64 xa, %1, 4;\n\tadd.s64 xb, %2, 4;\n\tadd.s64 ya, %3, 4;\n\tadd.s64 yb, %4, 4;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t"
+            "add.s64 xa, %1, 6;\n\tadd.s64 xb, %2, 6;\n\tadd.s64 ya, %3, 6;\n\tadd.s64 yb, %4, 6;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t}"
+            ::"r"(acc), "l"(a_hi), "l"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(in_chunk)
+            : "memory");
+        umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
+        const bool chunk_ends = in_chunk == kChunkKB - 1 || it == total - 1;
+        if (chunk_ends) { umma_commit(&acc_full[buf]); in_chunk = 0; ++chunk; buf ^= 1; }
+        else ++in_chunk;
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
     }
   } else {
     // epilogue warps 2..9: TMEM lanes 32*(warp % 4) .. +31 (row of the tile = lane of TMEM); warps 2-5
     // take columns 0-63, warps 6-9 columns 64-127
     const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
-    const bool ok = mbar_wait(&accum_bar, 0);
-    if (!ok && lane == 0) atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t m = m0 + quarter * 32 + lane;
-    if (ok) {
-#pragma unroll 1
-      for (uint32_t c = 2 * half; c < 2 * half + 2; ++c) {
-        float v[32];
-        if (total > 0) tmem_ld32(tmem_base + ((quarter * 32) << 16) + c * 32, v);
-        else {
+    // EPI_LSTM_CELL: previous cell state of this thread's 8 columns per chunk, fetched while the MMAs run
+    float cprev[2][8];
+    if (epi.mode == EPI_LSTM_CELL) {
+      const uint32_t u = blockIdx.x * 32 + lane;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+      for (int cl = 0; cl < 2; ++cl)
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const uint32_t n = n0 + (2 * half + cl) * 32 + quarter * 8 + jj;
+          cprev[cl][jj] = n < N ? __ldg(epi.c_prev + u + (size_t)epi.H * n) : 0.f;
         }
-        if (m < M) {
-          const uint32_t nb = n0 + c * 32;
-          const EpiRow row = epi_row(epi, m);
-          const size_t ldc = row.ldc;
-          float* dst = row.c + ldc * nb;
-          if (epi.mode == EPI_STORE) {
+    }
+    float sum[64];   // this thread's row of the tile, columns [64 half, 64 half + 64)
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = v[j];
-          } else if (epi.mode == EPI_BIAS) {
-            const float bias = epi.bias[m];
+    for (int j = 0; j < 64; ++j) sum[j] = 0.f;
+    bool ok = true;
+#pragma unroll 1
+    for (uint32_t c = 0; c < nchunks; ++c) {
+      const uint32_t buf = c & 1;
+      if (!mbar_wait(&acc_full[buf], (c >> 1) & 1)) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // (two 32-column loads: one 64-column load per flush measured slower)
+      float v[32];
+      const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32) << 16) + 2 * half * 32;
+      tmem_ld32(taddr, v);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = v[j] + bias;
-          } else if (epi.mode == EPI_GATES) {
-            const float bias = epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
-            const bool is_tanh = m >= 3 * epi.H;
+      for (int j = 0; j < 32; ++j) sum[j] += v[j];
+      tmem_ld32(taddr + 32, v);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float x = v[j] + bias;
-              if (nb + j < N) dst[ldc * j] = is_tanh ? tanhf(x) : sigmoidf_dev(x);
-            }
-          } else {
-            // read-modify-write: issue all loads of the chunk before the first dependent store
-            float old[32], mk[32];
+      for (int j = 0; j < 32; ++j) sum[32 + j] += v[j];
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+    if (!ok && lane == 0) atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT);
+    if (epi.mode == EPI_LSTM_CELL) {
+      // The tile holds gates i, f, o, g (TMEM lane quarter q) of hidden units 32 * blockIdx.x + lane.  The four warps
+      // of a column half exchange their activated gates through the (now idle) operand ring and each then forms
+      // c and h for 8 of the 32 columns of the chunk.  Every warp reaches both named barriers whatever its wait did.
+      uint32_t all_ok;
+      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, %2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1u + half) : "memory");
+      if (all_ok) {
+        float* ex = reinterpret_cast<float*>(ring) + half * (4 * 32 * 32);
+        const uint32_t u = blockIdx.x * 32 + lane, grow = quarter * epi.H + u;
+        const float bias = epi.bias[grow] + (quarter == 1 ? epi.forget_bias : 0.f);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) old[j] = nb + j < N ? __ldcg(dst + ldc * j) : 0.f;
-            if (epi.mode == EPI_ACCUM_MASK) {
-              const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
-              const float* mp = row.mask + mstep * nb;
+        for (int cl = 0; cl < 2; ++cl) {
+          const uint32_t nb = n0 + (2 * half + cl) * 32;
+          float* dst = epi.C + grow + (size_t)epi.ldc * nb;
 #pragma unroll
-              for (int j = 0; j < 32; ++j) mk[j] = (nb + j < N) ? __ldg(mp + mstep * j) : 0.f;
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) mk[j] = 1.f;
-            }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = old[j] + v[j] * mk[j];
+          for (int j = 0; j < 32; ++j) {
+            const float x = sum[cl * 32 + j] + bias;
+            const float a = quarter == 3 ? tanhf(x) : sigmoidf_dev(x);
+            if (nb + j < N) dst[(size_t)epi.ldc * j] = a;
+            ex[(quarter * 32 + j) * 32 + lane] = a;
           }
+          asm volatile("barrier.cta.sync %0, 128;" ::"r"(1u + half) : "memory");
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) {
+            const uint32_t j = quarter * 8 + jj, n = nb + j;
+            const float gi = ex[(0 * 32 + j) * 32 + lane], gf = ex[(1 * 32 + j) * 32 + lane];
+            const float go = ex[(2 * 32 + j) * 32 + lane], gg = ex[(3 * 32 + j) * 32 + lane];
+            if (n < N) {
+              const size_t e = u + (size_t)epi.H * n;
+              const float cn = lstm_cell_c(gi, gg, gf, cprev[cl][jj]);
+              epi.c_out[e] = cn;
+              epi.h_out[e] = lstm_cell_h(go, cn);
+            }
+          }
+          asm volatile("barrier.cta.sync %0, 128;" ::"r"(1u + half) : "memory");
+        }
+      }
+    } else if (ok && m < M) {
+      const EpiRow row = epi_row(epi, m);
+      const size_t ldc = row.ldc;
+#pragma unroll
+      for (int cl = 0; cl < 2; ++cl) {
+        const uint32_t nb = n0 + (2 * half + cl) * 32;
+        float* dst = row.c + ldc * nb;
+        float* v = sum + cl * 32;
+        if (epi.mode == EPI_STORE) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = v[j];
+        } else if (epi.mode == EPI_BIAS) {
+          const float bias = epi.bias[m];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = v[j] + bias;
+        } else if (epi.mode == EPI_GATES) {
+          const float bias = epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
+          const bool is_tanh = m >= 3 * epi.H;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = v[j] + bias;
+            if (nb + j < N) dst[ldc * j] = is_tanh ? tanhf(x) : sigmoidf_dev(x);
+          }
+        } else {
+          // read-modify-write: all loads of the 32-column chunk are issued before the first dependent store
+          if (epi.mode == EPI_ACCUM_MASK) {
+            const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
+            const float* mp = row.mask + mstep * nb;
+            float mk[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mk[j] = (nb + j < N) ? __ldg(mp + mstep * j) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= mk[j];
+          }
+          float old[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) old[j] = nb + j < N ? __ldcg(dst + ldc * j) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = old[j] + v[j];
         }
       }
     }
@@ -346,8 +457,10 @@ __global__ void __launch_bounds__(256) k_pack_multi(const PackJobs jobs) {
     if (r < rows && k < K) {
       float h, l;
       split_tf32(tile[tx][ty + 8 * i], h, l);
-      hi[k + (size_t)pitch * r] = h;
-      lo[k + (size_t)pitch * r] = l;
+      uint32_t rd = r;
+      if (job.perm_H) { const uint32_t q = r / job.perm_H, u = r % job.perm_H; rd = 128 * (u / 32) + 32 * q + (u % 32); }
+      hi[k + (size_t)pitch * rd] = h;
+      lo[k + (size_t)pitch * rd] = l;
     }
   }
 }
@@ -391,8 +504,12 @@ int pack_flush_impl(dyb200_ctx* ctx, PackJobs* jobs) {
 }
 
 // Queues one operand in `batch` (launching the queue first when it is full); with batch == nullptr it is packed at once.
-int pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, const float* mask,
+// layout: 0 = the row index is fast in the source, 1 = the k index is fast, kLayoutGates = row index fast and the
+// rows = 4H gate rows are written interleaved (destination row 128 t + 32 q + l <- source row q H + 32 t + l) so that
+// every 128-row tile holds the four gates of 32 hidden units.
+int pack(dyb200_ctx* ctx, const float* src, uint32_t ld, int layout, uint32_t rows, uint32_t K, const float* mask,
          uint32_t mask_ld, int mask_full, float* hi, float* lo, uint32_t pitch, PackJobs* batch = nullptr) {
+  const bool k_is_fast = layout == 1;
   if (rows == 0 || K == 0) return DYB200_OK;
   PackJobs local;
   local.n = 0; local.start[0] = 0;
@@ -402,6 +519,7 @@ int pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_
   j.src = src; j.mask = mask; j.hi = hi; j.lo = lo;
   j.ld = ld; j.rows = rows; j.K = K; j.mask_ld = mask_ld; j.pitch = pitch;
   j.k_is_fast = k_is_fast ? 1 : 0; j.mask_full = mask_full;
+  j.perm_H = layout == kLayoutGates ? rows / 4 : 0;
   uint64_t units;
   if (k_is_fast) {
     j.vec = (K % 4 == 0) && (ld % 4 == 0) && aligned16(src) && (!mask || ((mask_ld % 4 == 0 || !mask_full) && aligned16(mask)));
@@ -421,7 +539,7 @@ int pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_
 inline uint32_t round_up(uint32_t x, uint32_t m) { return (x + m - 1) / m * m; }
 
 // Returns the cached packed form of a parameter matrix, packing it first if it is new or stale.
-int cached_param_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, uint32_t pitch,
+int cached_param_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, int k_is_fast, uint32_t rows, uint32_t K, uint32_t pitch,
                       float** hi, float** lo, const float* src2 = nullptr, uint32_t rows2 = 0) {
   const int cap = (int)(sizeof(ctx->param_pack) / sizeof(ctx->param_pack[0]));
   dyb200_ctx::ParamPack* hit = nullptr;
@@ -480,13 +598,36 @@ int dyb200_tc_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fas
   out->hi = (float*)buf;
   out->lo = (float*)(((uintptr_t)(out->hi + (size_t)rows * pitch) + 255) & ~(uintptr_t)255);
   out->rows = rows; out->K = K; out->pitch = pitch;
-  return pack(ctx, src, ld, k_is_fast, rows, K, mask, mask_ld, mask_full, out->hi, out->lo, pitch, batch);
+  return pack(ctx, src, ld, k_is_fast ? 1 : 0, rows, K, mask, mask_ld, mask_full, out->hi, out->lo, pitch, batch);
 }
 
 int dyb200_tc_param(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, PackedOp* out) {
   if (!ctx->param_cache_on) return dyb200_tc_pack(ctx, src, ld, k_is_fast, rows, K, nullptr, 0, 0, out, nullptr);
   out->rows = rows; out->K = K; out->pitch = round_up(K, 32);
-  return cached_param_pack(ctx, src, ld, k_is_fast, rows, K, out->pitch, &out->hi, &out->lo);
+  return cached_param_pack(ctx, src, ld, k_is_fast ? 1 : 0, rows, K, out->pitch, &out->hi, &out->lo);
+}
+
+int dyb200_tc_param_gates(dyb200_ctx* ctx, const float* src, uint32_t ld, uint32_t rows, uint32_t K, PackedOp* out) {
+  const uint32_t pitch = round_up(K, 32);
+  out->rows = rows; out->K = K; out->pitch = pitch;
+  if (ctx->param_cache_on) return cached_param_pack(ctx, src, ld, kLayoutGates, rows, K, pitch, &out->hi, &out->lo);
+  void* buf;
+  int rc = dyb200_scratch(ctx, (size_t)2 * rows * pitch * sizeof(float) + 256, &buf);
+  if (rc) return rc;
+  out->hi = (float*)buf;
+  out->lo = (float*)(((uintptr_t)(out->hi + (size_t)rows * pitch) + 255) & ~(uintptr_t)255);
+  return pack(ctx, src, ld, kLayoutGates, rows, K, nullptr, 0, 0, out->hi, out->lo, pitch, nullptr);
+}
+
+uint32_t dyb200_tc_splits(const dyb200_ctx* ctx, uint32_t M, uint32_t N, uint32_t kb_total) {
+  const uint32_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  uint32_t S = 1;
+  if (tiles * 2 <= (uint32_t)ctx->sm_count) {
+    S = (uint32_t)ctx->sm_count / tiles;
+    if (S > kb_total / 8) S = kb_total / 8;   // at least 8 k-blocks per split
+    if (S < 1) S = 1;
+  }
+  return S;
 }
 
 int dyb200_tc_param2(dyb200_ctx* ctx, const float* src, uint32_t rows, const float* src2, uint32_t rows2, uint32_t ld,
@@ -534,13 +675,9 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   const uint32_t kb_total = kb0 + kb1;
   dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN, 1);
   // Split K when the output has too few tiles to occupy the SMs (e.g. dx = W^T dgate: 16-32 tiles, K = 4096).
-  const uint32_t tiles = grid.x * grid.y;
-  uint32_t S = 1;
-  if (tiles * 2 <= (uint32_t)ctx->sm_count) {
-    S = (uint32_t)ctx->sm_count / tiles;
-    if (S > kb_total / 8) S = kb_total / 8;   // at least 8 k-blocks per split
-    if (S < 1) S = 1;
-  }
+  uint32_t S = dyb200_tc_splits(ctx, M, N, kb_total);
+  DYB_CHECK_ARG(ctx, epi.mode != EPI_LSTM_CELL || (S == 1 && M % BM == 0 && epi.H * 4 == M),
+                "tensor GEMM: the LSTM-cell epilogue needs whole tiles of interleaved gate rows and no K split");
   uint32_t kb_per_split = (kb_total + S - 1) / S;
   S = (kb_total + kb_per_split - 1) / kb_per_split;
   GemmEpilogue kepi = epi;

@@ -78,14 +78,14 @@ __global__ void __launch_bounds__(kThreads) k_lstm_ch_fwd(const float* __restric
       float4 s = ld4_stream(st + e), r;
       if (MODE == 0) {
         float4 gi = ld4_stream(g + j), gf = ld4_stream(g + H + j), gg = ld4_stream(g + 3 * H + j);
-        r = make_float4(gi.x * gg.x + gf.x * s.x, gi.y * gg.y + gf.y * s.y, gi.z * gg.z + gf.z * s.z, gi.w * gg.w + gf.w * s.w);
+        r = make_float4(lstm_cell_c(gi.x, gg.x, gf.x, s.x), lstm_cell_c(gi.y, gg.y, gf.y, s.y), lstm_cell_c(gi.z, gg.z, gf.z, s.z), lstm_cell_c(gi.w, gg.w, gf.w, s.w));
       } else {
         float4 go = ld4_stream(g + 2 * H + j);
-        r = make_float4(go.x * tanhf(s.x), go.y * tanhf(s.y), go.z * tanhf(s.z), go.w * tanhf(s.w));
+        r = make_float4(lstm_cell_h(go.x, s.x), lstm_cell_h(go.y, s.y), lstm_cell_h(go.z, s.z), lstm_cell_h(go.w, s.w));
       }
       st4(out + e, r);
     } else {
-      out[e] = MODE == 0 ? g[j] * g[3 * H + j] + g[H + j] * st[e] : g[2 * H + j] * tanhf(st[e]);
+      out[e] = MODE == 0 ? lstm_cell_c(g[j], g[3 * H + j], g[H + j], st[e]) : lstm_cell_h(g[2 * H + j], st[e]);
     }
   }
 }
@@ -134,13 +134,13 @@ __global__ void __launch_bounds__(kThreads) k_lstm_cell_fwd(const float* __restr
     if (VEC) {
       float4 cp = ld4_stream(c_tm1 + e), gi = ld4_stream(g + j), gf = ld4_stream(g + H + j), go = ld4_stream(g + 2 * H + j),
              gg = ld4_stream(g + 3 * H + j);
-      float4 c = make_float4(gi.x * gg.x + gf.x * cp.x, gi.y * gg.y + gf.y * cp.y, gi.z * gg.z + gf.z * cp.z, gi.w * gg.w + gf.w * cp.w);
+      float4 c = make_float4(lstm_cell_c(gi.x, gg.x, gf.x, cp.x), lstm_cell_c(gi.y, gg.y, gf.y, cp.y), lstm_cell_c(gi.z, gg.z, gf.z, cp.z), lstm_cell_c(gi.w, gg.w, gf.w, cp.w));
       st4(c_t + e, c);
-      st4(h_t + e, make_float4(go.x * tanhf(c.x), go.y * tanhf(c.y), go.z * tanhf(c.z), go.w * tanhf(c.w)));
+      st4(h_t + e, make_float4(lstm_cell_h(go.x, c.x), lstm_cell_h(go.y, c.y), lstm_cell_h(go.z, c.z), lstm_cell_h(go.w, c.w)));
     } else {
-      float c = g[j] * g[3 * H + j] + g[H + j] * c_tm1[e];
+      float c = lstm_cell_c(g[j], g[3 * H + j], g[H + j], c_tm1[e]);
       c_t[e] = c;
-      h_t[e] = g[2 * H + j] * tanhf(c);
+      h_t[e] = lstm_cell_h(g[2 * H + j], c);
     }
   }
 }
@@ -397,14 +397,43 @@ int dyb200_vanilla_lstm_fwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
   dyb200_tensor xs[7] = {*x, *h_tm1, *Wx, *Wh, *b};
   int nxs = 5;
   if (attrs->dropout) { xs[5] = *mask_x; xs[6] = *mask_h; nxs = 7; }
+  const uint32_t H = c_tm1->d[0];
+  const size_t total = (size_t)H * c_tm1->bd;
+  DYB_CHECK_ARG(ctx, t_size(c_t) == total && t_size(h_t) == total, "lstm_fwd_fused: c_t / h_t size mismatch");
+  {
+    // One kernel for the whole step when the shape gives whole tiles of interleaved gate rows and no K split:
+    // W x + U h on the tensor pipe, bias + sigmoid / tanh, and the c / h update in its epilogue.
+    const uint32_t I = t_dim(x, 0), B = x->bd, G = 4 * H;
+    const bool shapes_ok = x->nd == 1 && h_tm1->nd == 1 && t_dim(h_tm1, 0) == H && h_tm1->bd == B && c_tm1->bd == B && Wx->nd == 2 &&
+                           Wx->d[0] == G && Wx->d[1] == I && Wh->nd == 2 && Wh->d[0] == G && Wh->d[1] == H && t_size(b) == G &&
+                           t_size(gates) == (size_t)G * B &&
+                           (!attrs->dropout || ((mask_x->bd == B || mask_x->bd == 1) && (mask_h->bd == B || mask_h->bd == 1) &&
+                                                t_dim(mask_x, 0) == I && t_dim(mask_h, 0) == H));
+    const uint32_t kb = (I + 31) / 32 + (H + 31) / 32;
+    if (shapes_ok && attrs->weightnoise_std == 0.f && H % 32 == 0 && I > 0 && B > 0 && dyb200_tc_eligible(G, B, 2.0 * G * B * (I + H)) &&
+        dyb200_tc_splits(ctx, G, B, kb) == 1) {
+      { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
+      PackedOp A[2], Bp[2];
+      int rc;
+      if ((rc = dyb200_tc_param_gates(ctx, Wx->v, G, G, I, &A[0]))) return rc;
+      if ((rc = dyb200_tc_param_gates(ctx, Wh->v, G, G, H, &A[1]))) return rc;
+      PackJobs batch;
+      dyb200_tc_pack_begin(&batch);
+      const float* mx = attrs->dropout ? mask_x->v : nullptr;
+      const float* mh = attrs->dropout ? mask_h->v : nullptr;
+      if ((rc = dyb200_tc_pack(ctx, x->v, I, true, B, I, mx, I, mx ? mask_x->bd == B : 0, &Bp[0], &batch))) return rc;
+      if ((rc = dyb200_tc_pack(ctx, h_tm1->v, H, true, B, H, mh, H, mh ? mask_h->bd == B : 0, &Bp[1], &batch))) return rc;
+      if ((rc = dyb200_tc_pack_flush(ctx, &batch))) return rc;
+      GemmEpilogue e{EPI_LSTM_CELL, gates->v, G, b->v, H, attrs->forget_gate_bias, nullptr, 0, 0};
+      e.c_prev = c_tm1->v; e.c_out = c_t->v; e.h_out = h_t->v;
+      return dyb200_tc_gemm_packed(ctx, G, B, 2, A, Bp, e);
+    }
+  }
   int rc = dyb200_vanilla_lstm_gates_fwd(xs, nxs, gates, attrs, nullptr, ctx);
   if (rc) return rc;
   dyb200_tensor ch[2] = {*c_tm1, *gates};
   rc = ch_check(ctx, ch, 2, "VanillaLSTMC");
   if (rc) return rc;
-  const uint32_t H = c_tm1->d[0];
-  const size_t total = (size_t)H * c_tm1->bd;
-  DYB_CHECK_ARG(ctx, t_size(c_t) == total && t_size(h_t) == total, "lstm_fwd_fused: c_t / h_t size mismatch");
   if (total == 0) return DYB200_OK;
   bool vec = H % 4 == 0 && aligned16(c_tm1->v) && aligned16(gates->v) && aligned16(c_t->v) && aligned16(h_t->v);
   if (vec) k_lstm_cell_fwd<1><<<stream_grid(ctx, total / 4, kThreads), kThreads, 0, ctx->stream>>>(c_tm1->v, gates->v, c_t->v, h_t->v, H, total);

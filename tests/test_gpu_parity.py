@@ -966,3 +966,38 @@ def test_random_bernoulli(g, capi):
     # neighbouring elements are uncorrelated
     k = (a[0, :-1] != 0).astype(np.float64); l = (a[0, 1:] != 0).astype(np.float64)
     assert abs(np.corrcoef(k, l)[0, 1]) < 0.01
+
+
+@pytest.mark.parametrize("I,H,B,masks", [(512, 1024, 300, "full"), (256, 1024, 384, None)])
+def test_lstm_fwd_fused_cell_epilogue(oracle, g, capi, I, H, B, masks):
+    """Shapes that give whole tiles and no K split take the one-kernel path (gate GEMM with the c / h update in its
+    epilogue).  Its gates, c and h must equal the three nodes called one after the other bit for bit, and the oracle
+    within the LSTM-state tolerance."""
+    r = rng(155)
+    x, h, c_prev = randn(r, B, I), randn(r, B, H, scale=0.5), randn(r, B, H, scale=0.5)
+    Wx, Wh, b = glorot(r, 4 * H, I), glorot(r, 4 * H, H), randn(r, 4 * H, scale=0.1)
+    mx = mh = None
+    if masks:
+        mx = ((r.random((B, I)) < 0.8) / 0.8).astype(np.float32)
+        mh = ((r.random((B, H)) < 0.8) / 0.8).astype(np.float32)
+    gates = oracle.lstm_gates_fwd([x], h, Wx, Wh, b, mx, mh)
+    c_t = oracle.lstm_c_fwd(c_prev, gates)
+    h_t = oracle.lstm_h_fwd(c_t, gates)
+    at = capi.LstmGatesAttrs(1 if masks else 0, 0.0, 1.0)
+    D = {k: g.dev(v) for k, v in dict(x=x, h=h, c=c_prev, Wx=Wx, Wh=Wh, b=b).items()}
+    tm = [g.T(g.dev(mx)), g.T(g.dev(mh))] if masks else []
+    tx, th_, tc_ = g.T(D["x"]), g.T(D["h"]), g.T(D["c"])
+    tWx, tWh, tb = g.T(D["Wx"], [4 * H, I], 1), g.T(D["Wh"], [4 * H, H], 1), g.T(D["b"], [4 * H], 1)
+    og, oc, oh = (g.dev(np.full_like(a, 9.0)) for a in (gates, c_t, h_t))
+    g.ctx().lstm_fwd_fused(tx, th_, tc_, tWx, tWh, tb, tm[0] if masks else None, tm[1] if masks else None, at, g.T(og), g.T(oc), g.T(oh))
+    ng, nc, nh = (g.dev(np.zeros_like(a)) for a in (gates, c_t, h_t))
+    g.ctx().fwd("vanilla_lstm_gates", [tx, th_, tWx, tWh, tb] + tm, g.T(ng), at)
+    g.ctx().fwd("vanilla_lstm_c", [tc_, g.T(ng)], g.T(nc))
+    g.ctx().fwd("vanilla_lstm_h", [g.T(nc), g.T(ng)], g.T(nh))
+    assert np.array_equal(g.host(og), g.host(ng))
+    assert np.array_equal(g.host(oc), g.host(nc))
+    assert np.array_equal(g.host(oh), g.host(nh))
+    assert_close(g.host(og), gates, TOL_REDUCE, floor=GEMM_FLOOR, what="gates")
+    assert_close(g.host(oc), c_t, TOL_REDUCE, floor=GEMM_FLOOR, what="c")
+    assert_close(g.host(oh), h_t, TOL_REDUCE, floor=GEMM_FLOOR, what="h")
+    assert g.ctx().device_errors() == 0
