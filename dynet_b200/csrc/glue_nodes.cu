@@ -161,14 +161,18 @@ __device__ __forceinline__ void philox4x32_10(uint32_t c[4], uint32_t k0, uint32
 // y[e] = (u_e < p) ? scale : 0, u_e uniform in [0, 1) from 24 random bits
 __global__ void __launch_bounds__(kThreads) k_bernoulli(float* __restrict__ y, size_t n, float p, float scale, uint64_t seed, uint64_t offset) {
   const size_t n4 = (n + 3) / 4;
+  const bool vec = aligned16(y);
   for (size_t q = (size_t)blockIdx.x * kThreads + threadIdx.x; q < n4; q += (size_t)gridDim.x * kThreads) {
     const uint64_t ctr = offset + q;
     uint32_t c[4] = {(uint32_t)ctr, (uint32_t)(ctr >> 32), 0u, 0u};
     philox4x32_10(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+    float v[4];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const size_t e = 4 * q + k;
-      if (e < n) y[e] = ((float)(c[k] >> 8) * (1.0f / 16777216.0f) < p) ? scale : 0.f;
+    for (int k = 0; k < 4; ++k) v[k] = ((float)(c[k] >> 8) * (1.0f / 16777216.0f) < p) ? scale : 0.f;
+    if (vec && 4 * q + 3 < n) st4_stream(y + 4 * q, make_float4(v[0], v[1], v[2], v[3]));
+    else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) if (4 * q + k < n) y[4 * q + k] = v[k];
     }
   }
 }

@@ -184,6 +184,55 @@ def build_cases(torch, ctx, small):
         ctx.gemm(0, 1, 4 * Hh, Ig, Bb, b["dg"].data_ptr(), 4 * Hh, b["x"].data_ptr(), Ig, b["dW"].data_ptr(), 4 * Hh, 1)
     cases.append(Case("gemm_dW_4096x1024x512_accumulate", 0, mk_gates, dw_gemm, 10 ** 9))
     cases[-1].flops = 2.0 * 4 * Hh * Ig * Bb
+    # the same step through the fused entry point: one kernel forms gates, c and h (c / h update in the GEMM epilogue)
+    def mk_fused():
+        b = mk_gates()
+        b.update(c_prev=torch.randn(Bb, Hh, device=dev) * 0.5, c=torch.empty(Bb, Hh, device=dev), hh=torch.empty(Bb, Hh, device=dev))
+        return b
+    def fused_fwd(b):
+        ctx.lstm_fwd_fused(T(b["x"], [Ig], Bb), T(b["h"], [Hh], Bb), T(b["c_prev"], [Hh], Bb), T(b["Wx"], [4 * Hh, Ig], 1),
+                           T(b["Wh"], [4 * Hh, Hh], 1), T(b["b"], [4 * Hh], 1), T(b["mx"], [Ig], Bb), T(b["mh"], [Hh], Bb), gat,
+                           T(b["out"], [4 * Hh], Bb), T(b["c"], [Hh], Bb), T(b["hh"], [Hh], Bb))
+    cases.append(Case("lstm_fwd_fused_gates_c_h_4096x512x2048", 0, mk_fused, fused_fwd, 10 ** 9))
+    cases[-1].flops = fl_g
+    # output layer of config 4 over all time steps: r = bias + R h, M = V = 10000, N = T*B = 17920, K = H = 1024
+    Vv, TB = 10000, 17920
+    def mk_aff():
+        return dict(R=torch.randn(Hh, Vv, device=dev) * 0.02, h=torch.randn(TB, Hh, device=dev) * 0.5, b=torch.zeros(Vv, device=dev),
+                    r=torch.empty(TB, Vv, device=dev))
+    def aff_fwd(b):
+        ctx.fwd("affine_transform", [T(b["b"], [Vv], 1), T(b["R"], [Vv, Hh], 1), T(b["h"], [Hh], TB)], T(b["r"], [Vv], TB))
+    cases.append(Case("affine_transform_fwd_10000x17920x1024", 0, mk_aff, aff_fwd, 10 ** 9))
+    cases[-1].flops = 2.0 * Vv * TB * Hh
+
+    # trainer update rules over the config-4 parameter buffer (30.06 M floats)
+    NP = 30_060_000 if not small else 1 << 20
+    def mk_tr():
+        return dict(p=torch.randn(NP, device=dev), g=torch.randn(NP, device=dev) * 0.01, m=torch.zeros(NP, device=dev),
+                    v=torch.zeros(NP, device=dev), ss=torch.ones(1, device=dev))
+    hyp = capi.TrainerHyper(0.001, 5.0, 1.0, 0.9, 1e-8, 0.95, 0.9, 0.999, 3)
+    cases.append(Case("trainer_sgd_clip_zero_30M", 16 * NP, mk_tr,
+                      lambda b: ctx.trainer_update("sgd", b["p"].data_ptr(), b["g"].data_ptr(), [], NP, hyp, b["ss"].data_ptr(), True), 16 * NP))
+    cases.append(Case("trainer_adam_clip_zero_30M", 32 * NP, mk_tr,
+                      lambda b: ctx.trainer_update("adam", b["p"].data_ptr(), b["g"].data_ptr(), [b["m"].data_ptr(), b["v"].data_ptr()], NP, hyp,
+                                                   b["ss"].data_ptr(), True), 32 * NP))
+    cases.append(Case("squared_norm_30M", 4 * NP, mk_tr,
+                      lambda b: ctx.squared_norm(b["g"].data_ptr(), NP, b["ss"].data_ptr()), 4 * NP))
+    # glue nodes at LSTM-builder sizes: concatenate(h_fwd, h_bwd) and pick_range of the gates, 4096 x 4096
+    Rg, Bg = (4096, 4096) if not small else (256, 256)
+    def mk_glue():
+        return dict(a=torch.randn(Bg, Rg, device=dev), b=torch.randn(Bg, Rg, device=dev), cat=torch.empty(Bg, 2 * Rg, device=dev),
+                    part=torch.empty(Bg, Rg // 4, device=dev), s=torch.empty(1, Rg, device=dev), msk=torch.empty(Bg, Rg, device=dev))
+    SG = 4 * Rg * Bg
+    cases.append(Case("concatenate_2x4096_B4096", 4 * SG, mk_glue,
+                      lambda b: ctx.fwd("concatenate", [T(b["a"], [Rg], Bg), T(b["b"], [Rg], Bg)], T(b["cat"], [2 * Rg], Bg), capi.DimAttrs(0)), 4 * SG))
+    cases.append(Case("pick_range_quarter_of_4096_B4096", SG // 2, mk_glue,
+                      lambda b: ctx.fwd("pick_range", [T(b["a"], [Rg], Bg)], T(b["part"], [Rg // 4], Bg), capi.PickRangeAttrs(Rg // 4, Rg // 2, 0)), SG))
+    cases.append(Case("sum_batches_4096_B4096", SG, mk_glue,
+                      lambda b: ctx.fwd("sum_dim", [T(b["a"], [Rg], Bg)], T(b["s"], [Rg], 1),
+                                        capi.SumDimAttrs((C.c_uint * 2)(0, 0), 0, 1)), SG))
+    cases.append(Case("random_bernoulli_4096_B4096", SG, mk_glue,
+                      lambda b: ctx.fwd("random_bernoulli", [], T(b["msk"], [Rg], Bg), capi.BernoulliAttrs(0.8, 1.25, 7, 0)), SG))
     return cases
 
 
@@ -191,6 +240,7 @@ def run(only=None, iters=20, small=False, out=None, graph_mode=True):
     import torch
     stream = torch.cuda.Stream()
     ctx = capi.Context(0, stream.cuda_stream)
+    ctx.param_cache(True)   # as in training: weight matrices are split once (during warm-up), not in every timed call
     peak, src = peaks()
     results = []
     for case in build_cases(torch, ctx, small):
