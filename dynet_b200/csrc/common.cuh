@@ -24,7 +24,8 @@ struct dyb200_ctx {
   size_t scratch_bytes, scratch_off, scratch_peak;
   void* overflow[64];
   int n_overflow;
-  uint32_t* dev_flags;   // device error word (bit set by kernels, never traps)
+  uint32_t* dev_flags;   // device words: [0] error bits (set by kernels, never traps); [DYB200_DEV_COUNTER0 ..) arrival counters
+                         // of kernels whose last CTA finishes a reduction (zero between launches: the last CTA resets them)
   uint64_t launches;     // kernels launched through this context
   // 3xTF32 GEMM state (tensor maps are encoded per call; driver entry point cached)
   void* encode_tiled;    // cuTensorMapEncodeTiled
@@ -62,6 +63,9 @@ struct GemmProfScope {
   ~GemmProfScope() { if (slot >= 0) cudaEventRecord(ctx->prof_ev[2 * slot + 1], ctx->stream); }
 };
 
+#define DYB200_DEV_WORDS 2048
+#define DYB200_DEV_COUNTER0 64
+#define DYB200_DEV_COUNTERS (DYB200_DEV_WORDS - DYB200_DEV_COUNTER0)
 // Device error bits written into ctx->dev_flags.
 #define DYB200_FLAG_BAD_INDEX 1u     // an id >= vocab/rows reached a kernel (clamped, not dereferenced)
 #define DYB200_FLAG_WAIT_TIMEOUT 2u  // a bounded mbarrier wait ran out
@@ -151,6 +155,14 @@ __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<floa
 __device__ __forceinline__ void st4_stream(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
 
 __device__ __forceinline__ float sigmoidf_dev(float x) { return 1.0f / (1.0f + expf(-x)); }
+// x = hi + lo with hi = tf32(x) and lo = tf32(x - hi): the two operand planes of the 3xTF32 products
+__device__ __forceinline__ void split_tf32(float v, float& hi, float& lo) {
+  uint32_t h, l;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
+  hi = __uint_as_float(h);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(v - hi));
+  lo = __uint_as_float(l);
+}
 // c = i g + f c_tm1 and h = o tanh(c) with one fixed rounding sequence, shared by every kernel that forms them
 __device__ __forceinline__ float lstm_cell_c(float i, float g, float f, float c_tm1) { return __fmaf_rn(i, g, __fmul_rn(f, c_tm1)); }
 __device__ __forceinline__ float lstm_cell_h(float o, float c) { return __fmul_rn(o, tanhf(c)); }

@@ -82,7 +82,7 @@ int dyb200_ctx_create(int device, void* stream, dyb200_ctx** out) {
   c->device = device;
   c->stream = (cudaStream_t)stream;
   c->sm_count = prop.multiProcessorCount;
-  if (cudaMalloc((void**)&c->dev_flags, 256) != cudaSuccess || cudaMemset(c->dev_flags, 0, 256) != cudaSuccess) {
+  if (cudaMalloc((void**)&c->dev_flags, DYB200_DEV_WORDS * 4) != cudaSuccess || cudaMemset(c->dev_flags, 0, DYB200_DEV_WORDS * 4) != cudaSuccess) {
     free(c);
     return DYB200_ENOMEM;
   }

@@ -90,7 +90,14 @@ int dyb200_tc_param2(dyb200_ctx* ctx, const float* src, uint32_t rows, const flo
 int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const PackedOp* A, const PackedOp* B,
                           const GemmEpilogue& epi);
 bool dyb200_tc_eligible(uint32_t M, uint32_t N, double flops);
+// Planes of `rows x K` taken from the scratch arena, left for the caller's kernel to fill.
+int dyb200_tc_planes(dyb200_ctx* ctx, uint32_t rows, uint32_t K, PackedOp* out);
 struct dyb200_wgrad;
+int dyb200_wgrad_reserve(dyb200_wgrad* w, uint32_t k, float** a_hi, float** a_lo, uint32_t* pitch, const float* b0, uint32_t ldb0,
+                         const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1, int mask1_full,
+                         dyb200_ctx* ctx, PackJobs* batch);
+uint32_t dyb200_wgrad_rows(const dyb200_wgrad* w);
+uint32_t dyb200_wgrad_fill(const dyb200_wgrad* w);
 int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda, const float* b0, uint32_t ldb0,
                               const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1,
                               int mask1_full, dyb200_ctx* ctx, PackJobs* batch);

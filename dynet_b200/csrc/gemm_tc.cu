@@ -388,13 +388,6 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
 }
 
 // ---- operand packing: fp32 (masked, possibly transposed) -> K-major hi / lo planes ------------
-__device__ __forceinline__ void split_tf32(float v, float& hi, float& lo) {
-  uint32_t h, l;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
-  hi = __uint_as_float(h);
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(v - hi));
-  lo = __uint_as_float(l);
-}
 // One launch packs up to kMaxPackJobs operands.  A job is cut into units of one CTA each: for a source whose
 // k index is fast (element (r, k) at src[k + ld * r]) a unit is 1024 consecutive k of one row; for a source whose
 // row index is fast (element (r, k) at src[r + ld * k]) a unit is a 32 x 32 tile transposed through shared memory.
@@ -601,6 +594,17 @@ int dyb200_tc_pack(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fas
   return pack(ctx, src, ld, k_is_fast ? 1 : 0, rows, K, mask, mask_ld, mask_full, out->hi, out->lo, pitch, batch);
 }
 
+int dyb200_tc_planes(dyb200_ctx* ctx, uint32_t rows, uint32_t K, PackedOp* out) {
+  const uint32_t pitch = round_up(K, 32);
+  void* buf;
+  int rc = dyb200_scratch(ctx, (size_t)2 * rows * pitch * sizeof(float) + 256, &buf);
+  if (rc) return rc;
+  out->hi = (float*)buf;
+  out->lo = (float*)(((uintptr_t)(out->hi + (size_t)rows * pitch) + 255) & ~(uintptr_t)255);
+  out->rows = rows; out->K = K; out->pitch = pitch;
+  return DYB200_OK;
+}
+
 int dyb200_tc_param(dyb200_ctx* ctx, const float* src, uint32_t ld, bool k_is_fast, uint32_t rows, uint32_t K, PackedOp* out) {
   if (!ctx->param_cache_on) return dyb200_tc_pack(ctx, src, ld, k_is_fast, rows, K, nullptr, 0, 0, out, nullptr);
   out->rows = rows; out->K = K; out->pitch = round_up(K, 32);
@@ -770,6 +774,26 @@ int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint3
   w->k += k;
   return DYB200_OK;
 }
+
+// For a producer that writes the A planes of the next k columns itself: where they go, and the B operands queued as in
+// dyb200_wgrad_push_batched.  The accumulator advances by k.
+int dyb200_wgrad_reserve(dyb200_wgrad* w, uint32_t k, float** a_hi, float** a_lo, uint32_t* pitch, const float* b0, uint32_t ldb0,
+                         const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1, int mask1_full,
+                         dyb200_ctx* ctx, PackJobs* batch) {
+  DYB_CHECK_ARG(ctx, w && b0 && (w->N[1] == 0 || b1), "wgrad_reserve: null argument");
+  DYB_CHECK_ARG(ctx, w->k + k <= w->Kcap, "wgrad_reserve: %u + %u columns exceed the capacity %u", w->k, k, w->Kcap);
+  *a_hi = w->A.hi + w->k; *a_lo = w->A.lo + w->k; *pitch = w->Kcap;
+  int rc = pack(ctx, b0, ldb0, 0, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + w->k, w->B[0].lo + w->k, w->Kcap, batch);
+  if (rc) return rc;
+  if (w->N[1]) {
+    rc = pack(ctx, b1, ldb1, 0, w->N[1], k, mask1, ldb1, mask1_full, w->B[1].hi + w->k, w->B[1].lo + w->k, w->Kcap, batch);
+    if (rc) return rc;
+  }
+  w->k += k;
+  return DYB200_OK;
+}
+uint32_t dyb200_wgrad_rows(const dyb200_wgrad* w) { return w->M; }
+uint32_t dyb200_wgrad_fill(const dyb200_wgrad* w) { return w->k; }
 
 extern "C" {
 

@@ -196,6 +196,111 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd(const float* __restrict__
   }
 }
 
+// The same pass for shapes with H % 64 == 0 and B % 32 == 0, laid out for bandwidth: a CTA owns a tile of 64 hidden
+// units x 32 batch columns; threads read float4 along the hidden index (coalesced), and the tile of gate gradients
+// goes through shared memory so that it can also be written transposed.  Outputs, each optional except dc_tm1's
+// accumulate: dpre (fp32, [4H x B]); the K-major TF32 hi / lo planes of dpre in both layouts the products need
+// (dn: rows = batch, K = 4H, same indexing as dpre; dt: rows = 4H, K = batch, at column k0 of planes with pitch
+// dt_pitch), which saves the packing pass over dpre; db += row sums, formed as per-tile partial sums that the last
+// CTA of each 64-unit stripe to arrive adds in ascending tile order (deterministic; counters[] returns to zero).
+constexpr int kCT_J = 64, kCT_B = 32;
+__global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __restrict__ c_t, const float* __restrict__ c_tm1,
+                                                            const float* __restrict__ gates, const float* __restrict__ dEdh,
+                                                            const float* __restrict__ dEdc, float* __restrict__ dc_tm1,
+                                                            float* __restrict__ dpre, float* __restrict__ dn_hi, float* __restrict__ dn_lo,
+                                                            uint32_t dn_pitch, float* __restrict__ dt_hi, float* __restrict__ dt_lo,
+                                                            uint32_t dt_pitch, float* __restrict__ db, float* __restrict__ part,
+                                                            uint32_t* __restrict__ counters, uint32_t H, uint32_t B) {
+  __shared__ float tile[4][kCT_J][kCT_B + 1];
+  __shared__ uint32_t is_last;
+  const uint32_t j0 = blockIdx.x * kCT_J, b0 = blockIdx.y * kCT_B;
+  const uint32_t tq = threadIdx.x & 15, tb = threadIdx.x >> 4;   // hidden-unit quad, batch lane (two columns each)
+  const uint32_t j = j0 + 4 * tq;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const uint32_t bl = tb + 16 * half, b = b0 + bl;
+    const size_t e = (size_t)b * H + j;
+    const float* g = gates + (size_t)b * 4 * H + j;
+    const float4 gi = ld4(g), gf = ld4(g + H), go = ld4(g + 2 * H), gg = ld4(g + 3 * H);
+    const float4 c = ld4(c_t + e), cp = ld4(c_tm1 + e), dh = ld4(dEdh + e);
+    const float4 dcin = dEdc ? ld4(dEdc + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 dcp = dc_tm1 ? ld4(dc_tm1 + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float pi[4], pf[4], po[4], pg[4];
+    const float gi_[4] = {gi.x, gi.y, gi.z, gi.w}, gf_[4] = {gf.x, gf.y, gf.z, gf.w}, go_[4] = {go.x, go.y, go.z, go.w},
+                gg_[4] = {gg.x, gg.y, gg.z, gg.w}, c_[4] = {c.x, c.y, c.z, c.w}, cp_[4] = {cp.x, cp.y, cp.z, cp.w},
+                dh_[4] = {dh.x, dh.y, dh.z, dh.w}, dci_[4] = {dcin.x, dcin.y, dcin.z, dcin.w};
+    float dcp_[4] = {dcp.x, dcp.y, dcp.z, dcp.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float t = tanhf(c_[q]);
+      float dc = dh_[q] * go_[q] * (1.f - t * t);
+      if (dEdc) dc += dci_[q];
+      dcp_[q] += dc * gf_[q];
+      pi[q] = gate_deriv(gi_[q], dc * gg_[q], false);
+      pf[q] = gate_deriv(gf_[q], dc * cp_[q], false);
+      po[q] = gate_deriv(go_[q], dh_[q] * t, false);
+      pg[q] = gate_deriv(gg_[q], dc * gi_[q], true);
+      tile[0][4 * tq + q][bl] = pi[q]; tile[1][4 * tq + q][bl] = pf[q];
+      tile[2][4 * tq + q][bl] = po[q]; tile[3][4 * tq + q][bl] = pg[q];
+    }
+    if (dc_tm1) st4(dc_tm1 + e, make_float4(dcp_[0], dcp_[1], dcp_[2], dcp_[3]));
+    if (dpre) {
+      float* o = dpre + (size_t)b * 4 * H + j;
+      st4(o, make_float4(pi[0], pi[1], pi[2], pi[3])); st4(o + H, make_float4(pf[0], pf[1], pf[2], pf[3]));
+      st4(o + 2 * H, make_float4(po[0], po[1], po[2], po[3])); st4(o + 3 * H, make_float4(pg[0], pg[1], pg[2], pg[3]));
+    }
+    if (dn_hi) {
+      const size_t o = (size_t)b * dn_pitch + j;
+      float hi[4], lo[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) split_tf32(pi[q], hi[q], lo[q]);
+      st4(dn_hi + o, make_float4(hi[0], hi[1], hi[2], hi[3])); st4(dn_lo + o, make_float4(lo[0], lo[1], lo[2], lo[3]));
+#pragma unroll
+      for (int q = 0; q < 4; ++q) split_tf32(pf[q], hi[q], lo[q]);
+      st4(dn_hi + o + H, make_float4(hi[0], hi[1], hi[2], hi[3])); st4(dn_lo + o + H, make_float4(lo[0], lo[1], lo[2], lo[3]));
+#pragma unroll
+      for (int q = 0; q < 4; ++q) split_tf32(po[q], hi[q], lo[q]);
+      st4(dn_hi + o + 2 * H, make_float4(hi[0], hi[1], hi[2], hi[3])); st4(dn_lo + o + 2 * H, make_float4(lo[0], lo[1], lo[2], lo[3]));
+#pragma unroll
+      for (int q = 0; q < 4; ++q) split_tf32(pg[q], hi[q], lo[q]);
+      st4(dn_hi + o + 3 * H, make_float4(hi[0], hi[1], hi[2], hi[3])); st4(dn_lo + o + 3 * H, make_float4(lo[0], lo[1], lo[2], lo[3]));
+    }
+  }
+  __syncthreads();
+  // transposed write-out and row sums: warp w takes rows w, w + 8, ... of the 256 (gate, unit) rows; lane = batch column
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (uint32_t r = warp; r < 4 * kCT_J; r += 8) {
+    const uint32_t gate = r / kCT_J, jl = r % kCT_J;
+    const float v = tile[gate][jl][lane];
+    const size_t row = (size_t)gate * H + j0 + jl;
+    if (dt_hi) {
+      float hi, lo;
+      split_tf32(v, hi, lo);
+      dt_hi[row * dt_pitch + b0 + lane] = hi;
+      dt_lo[row * dt_pitch + b0 + lane] = lo;
+    }
+    const float s = warp_sum(v);
+    if (lane == 0) part[(size_t)blockIdx.y * 4 * H + row] = s;
+  }
+  // the last CTA of this stripe of hidden units adds the partial sums of all batch tiles, in tile order
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t seen = atomicAdd(&counters[blockIdx.x], 1u);
+    is_last = seen == gridDim.y - 1;
+    if (is_last) counters[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    const uint32_t r = threadIdx.x;   // 256 threads = 4 gates x 64 units
+    const size_t row = (size_t)(r / kCT_J) * H + j0 + r % kCT_J;
+    float acc = 0.f;
+    for (uint32_t t = 0; t < gridDim.y; ++t) acc += __ldcg(part + (size_t)t * 4 * H + row);
+    db[row] += acc;
+  }
+}
+
 struct GatesArgs {
   unsigned k;                 // number of x inputs
   const dyb200_tensor *h, *Wx, *Wh, *b, *mx, *mh;
@@ -462,27 +567,55 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
   DYB_CHECK_ARG(ctx, (deferred || (t_size(dWx) == (size_t)G * I && t_size(dWh) == (size_t)G * H)) && t_size(db) == G, "lstm_bwd_fused: parameter gradient size mismatch");
   if (attrs->dropout) DYB_CHECK_ARG(ctx, (mask_x->bd == B || mask_x->bd == 1) && (mask_h->bd == B || mask_h->bd == 1) && t_dim(mask_x, 0) == I && t_dim(mask_h, 0) == H, "lstm_bwd_fused: mask shape mismatch");
   if (HB == 0) return DYB200_OK;
-  void* sp;
-  int rc = dyb200_scratch(ctx, 4 * HB * sizeof(float), &sp);
-  if (rc) return rc;
-  float* dpre = (float*)sp;
-  k_lstm_cell_bwd<<<(H + kJT - 1) / kJT, 256, 0, ctx->stream>>>(c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr,
-                                                              dc_tm1 ? dc_tm1->v : nullptr, dpre, db->v, H, B);
-  DYB_LAUNCHED(ctx);
   const float* mx = attrs->dropout ? mask_x->v : nullptr;
   const float* mh = attrs->dropout ? mask_h->v : nullptr;
   const int mx_full = attrs->dropout ? mask_x->bd == B : 0, mh_full = attrs->dropout ? mask_h->bd == B : 0;
   const double flops_small = 2.0 * (I < H ? I : H) * (double)B * G;
   const bool tensor_path = dyb200_tc_eligible(I < H ? I : H, B, flops_small) && dyb200_tc_eligible(G, I < H ? I : H, flops_small);
+  int rc;
   PackJobs batch;   // every operand split of this call goes out in one launch
   dyb200_tc_pack_begin(&batch);
   PackedOp dn, dt, wxT, whT, xt, ht;
-  if (deferred) {
-    // weight gradients: append (dgate, x .* mask_x, h .* mask_h) to the accumulator; one product at flush time
-    rc = dyb200_wgrad_push_batched(deferred, B, dpre, G, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx, &batch);
-    if (rc) return rc;
+  // Bandwidth-shaped pass for whole tiles: it writes the split planes of the gate gradient itself.
+  const bool tiled = tensor_path && H % kCT_J == 0 && B % kCT_B == 0 && H / kCT_J <= DYB200_DEV_COUNTERS && aligned16(c_t->v) &&
+                     aligned16(c_tm1->v) && aligned16(gates->v) && aligned16(dEdh->v) && (!dEdc || aligned16(dEdc->v)) &&
+                     (!dc_tm1 || aligned16(dc_tm1->v)) && (!deferred || dyb200_wgrad_fill(deferred) % 32 == 0);
+  float* dpre = nullptr;
+  if (tiled) {
+    if ((rc = dyb200_tc_planes(ctx, B, G, &dn))) return rc;
+    float *a_hi = nullptr, *a_lo = nullptr;
+    uint32_t a_pitch = 0;
+    if (deferred) {
+      DYB_CHECK_ARG(ctx, dyb200_wgrad_rows(deferred) == G, "lstm_bwd_fused: the deferred accumulator has %u rows, the layer %u", dyb200_wgrad_rows(deferred), G);
+      if ((rc = dyb200_wgrad_reserve(deferred, B, &a_hi, &a_lo, &a_pitch, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx, &batch))) return rc;
+    } else {
+      if ((rc = dyb200_tc_planes(ctx, G, B, &dt))) return rc;
+      a_hi = dt.hi; a_lo = dt.lo; a_pitch = dt.pitch;
+    }
+    void* pp;
+    if ((rc = dyb200_scratch(ctx, (size_t)(B / kCT_B) * G * sizeof(float), &pp))) return rc;
+    k_lstm_cell_bwd_tiled<<<dim3(H / kCT_J, B / kCT_B), 256, 0, ctx->stream>>>(
+        c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr, dc_tm1 ? dc_tm1->v : nullptr, nullptr, dn.hi, dn.lo, dn.pitch,
+        a_hi, a_lo, a_pitch, db->v, (float*)pp, ctx->dev_flags + DYB200_DEV_COUNTER0, H, B);
+    DYB_LAUNCHED(ctx);
+  } else {
+    void* sp;
+    if ((rc = dyb200_scratch(ctx, 4 * HB * sizeof(float), &sp))) return rc;
+    dpre = (float*)sp;
+    k_lstm_cell_bwd<<<(H + kJT - 1) / kJT, 256, 0, ctx->stream>>>(c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr,
+                                                                dc_tm1 ? dc_tm1->v : nullptr, dpre, db->v, H, B);
+    DYB_LAUNCHED(ctx);
+    if (deferred) {
+      // weight gradients: append (dgate, x .* mask_x, h .* mask_h) to the accumulator; one product at flush time
+      rc = dyb200_wgrad_push_batched(deferred, B, dpre, G, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx, &batch);
+      if (rc) return rc;
+    }
+    if (tensor_path && (rc = dyb200_tc_pack(ctx, dpre, G, true, B, G, nullptr, 0, 0, &dn, &batch))) return rc;    // rows = batch, K = 4H
   }
-  if (tensor_path && (rc = dyb200_tc_pack(ctx, dpre, G, true, B, G, nullptr, 0, 0, &dn, &batch))) return rc;    // rows = batch, K = 4H
+  if (tiled && !deferred) {   // the immediate weight-gradient products need (x .* mask_x)^T and (h .* mask_h)^T
+    if ((rc = dyb200_tc_pack(ctx, x->v, I, false, I, B, mx, I, mx_full, &xt, &batch))) return rc;
+    if ((rc = dyb200_tc_pack(ctx, h_tm1->v, H, false, H, B, mh, H, mh_full, &ht, &batch))) return rc;
+  }
   if ((rc = dyb200_tc_pack_flush(ctx, &batch))) return rc;
   if (tensor_path) {
     // the gate gradient is split once per layout and shared by the four products
@@ -502,11 +635,13 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
       if ((rc = dyb200_tc_gemm_packed(ctx, H, B, 1, &whT, &dn, e))) return rc;
     }
     if (deferred) return DYB200_OK;
-    if ((rc = dyb200_tc_pack(ctx, dpre, G, false, G, B, nullptr, 0, 0, &dt))) return rc;   // rows = 4H, K = batch
-    if ((rc = dyb200_tc_pack(ctx, x->v, I, false, I, B, mx, I, mx_full, &xt))) return rc;       // (x .* mask_x)^T : rows = I, K = batch
+    if (!tiled) {   // (the tiled pass has written dt, and xt / ht went out with the batch above)
+      if ((rc = dyb200_tc_pack(ctx, dpre, G, false, G, B, nullptr, 0, 0, &dt))) return rc;   // rows = 4H, K = batch
+      if ((rc = dyb200_tc_pack(ctx, x->v, I, false, I, B, mx, I, mx_full, &xt))) return rc;       // (x .* mask_x)^T : rows = I, K = batch
+      if ((rc = dyb200_tc_pack(ctx, h_tm1->v, H, false, H, B, mh, H, mh_full, &ht))) return rc;
+    }
     GemmEpilogue ex{EPI_ACCUM, dWx->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
     if ((rc = dyb200_tc_gemm_packed(ctx, G, I, 1, &dt, &xt, ex))) return rc;
-    if ((rc = dyb200_tc_pack(ctx, h_tm1->v, H, false, H, B, mh, H, mh_full, &ht))) return rc;
     GemmEpilogue eh{EPI_ACCUM, dWh->v, G, nullptr, 0, 0.f, nullptr, 0, 0};
     return dyb200_tc_gemm_packed(ctx, G, H, 1, &dt, &ht, eh);
   }
