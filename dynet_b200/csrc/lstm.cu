@@ -296,7 +296,15 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __rest
     const uint32_t r = threadIdx.x;   // 256 threads = 4 gates x 64 units
     const size_t row = (size_t)(r / kCT_J) * H + j0 + r % kCT_J;
     float acc = 0.f;
-    for (uint32_t t = 0; t < gridDim.y; ++t) acc += __ldcg(part + (size_t)t * 4 * H + row);
+    uint32_t t = 0;
+    for (; t + 8 <= gridDim.y; t += 8) {   // eight loads in flight, added in tile order
+      float v[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[q] = __ldcg(part + (size_t)(t + q) * 4 * H + row);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc += v[q];
+    }
+    for (; t < gridDim.y; ++t) acc += __ldcg(part + (size_t)t * 4 * H + row);
     db[row] += acc;
   }
 }
