@@ -387,6 +387,41 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
   }
 }
 
+// Split-K second stage of the LSTM forward product (EPI_LSTM_CELL): rows are the interleaved gate rows of
+// dyb200_tc_param_gates.  One thread owns four consecutive hidden units of one column: it adds the partial tiles in
+// split order, applies bias + sigmoid / tanh, writes the four gate rows and forms c and h.
+__global__ void __launch_bounds__(256) k_splitk_reduce_cell(const float* __restrict__ part, uint32_t S, uint32_t M, uint32_t N,
+                                                           GemmEpilogue epi) {
+  const uint32_t H = epi.H, H4 = H / 4;
+  const size_t MN = (size_t)M * N, total = (size_t)H4 * N;
+  for (size_t q = (size_t)blockIdx.x * 256 + threadIdx.x; q < total; q += (size_t)gridDim.x * 256) {
+    const uint32_t u = 4 * (uint32_t)(q % H4), n = (uint32_t)(q / H4);
+    const uint32_t row0 = 128 * (u / 32) + (u % 32);   // interleaved row of gate 0; gate g is 32 g rows further
+    float4 a[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const float* p = part + row0 + 32 * g + (size_t)M * n;
+      a[g] = ld4_stream(p);
+      for (uint32_t s2 = 1; s2 < S; ++s2) {
+        const float4 v = ld4_stream(p + (size_t)s2 * MN);
+        a[g].x += v.x; a[g].y += v.y; a[g].z += v.z; a[g].w += v.w;
+      }
+      const float4 b = ld4(epi.bias + (size_t)g * H + u);
+      const float fb = g == 1 ? epi.forget_bias : 0.f;
+      a[g].x += b.x + fb; a[g].y += b.y + fb; a[g].z += b.z + fb; a[g].w += b.w + fb;
+      if (g == 3) a[g] = make_float4(tanhf(a[g].x), tanhf(a[g].y), tanhf(a[g].z), tanhf(a[g].w));
+      else a[g] = make_float4(sigmoidf_dev(a[g].x), sigmoidf_dev(a[g].y), sigmoidf_dev(a[g].z), sigmoidf_dev(a[g].w));
+      st4(epi.C + (size_t)g * H + u + (size_t)epi.ldc * n, a[g]);
+    }
+    const size_t e = u + (size_t)H * n;
+    const float4 cp = ld4(epi.c_prev + e);
+    const float4 c = make_float4(lstm_cell_c(a[0].x, a[3].x, a[1].x, cp.x), lstm_cell_c(a[0].y, a[3].y, a[1].y, cp.y),
+                                 lstm_cell_c(a[0].z, a[3].z, a[1].z, cp.z), lstm_cell_c(a[0].w, a[3].w, a[1].w, cp.w));
+    st4(epi.c_out + e, c);
+    st4(epi.h_out + e, make_float4(lstm_cell_h(a[2].x, c.x), lstm_cell_h(a[2].y, c.y), lstm_cell_h(a[2].z, c.z), lstm_cell_h(a[2].w, c.w)));
+  }
+}
+
 // ---- operand packing: fp32 (masked, possibly transposed) -> K-major hi / lo planes ------------
 // One launch packs up to kMaxPackJobs operands.  A job is cut into units of one CTA each: for a source whose
 // k index is fast (element (r, k) at src[k + ld * r]) a unit is 1024 consecutive k of one row; for a source whose
@@ -680,8 +715,9 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN, 1);
   // Split K when the output has too few tiles to occupy the SMs (e.g. dx = W^T dgate: 16-32 tiles, K = 4096).
   uint32_t S = dyb200_tc_splits(ctx, M, N, kb_total);
-  DYB_CHECK_ARG(ctx, epi.mode != EPI_LSTM_CELL || (S == 1 && M % BM == 0 && epi.H * 4 == M),
-                "tensor GEMM: the LSTM-cell epilogue needs whole tiles of interleaved gate rows and no K split");
+  DYB_CHECK_ARG(ctx, epi.mode != EPI_LSTM_CELL || (M % BM == 0 && epi.H * 4 == M && epi.ldc % 4 == 0 && aligned16(epi.C) &&
+                                                      aligned16(epi.bias) && aligned16(epi.c_prev) && aligned16(epi.c_out) && aligned16(epi.h_out)),
+                "tensor GEMM: the LSTM-cell epilogue needs whole tiles of interleaved gate rows and 16-byte aligned tensors");
   uint32_t kb_per_split = (kb_total + S - 1) / S;
   S = (kb_total + kb_per_split - 1) / kb_per_split;
   GemmEpilogue kepi = epi;
@@ -699,7 +735,10 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     GemmProfScope scope(ctx, flops, 1, M, N, kb_total * BK, (uint32_t)epi.mode);
     k_gemm_tc<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
     DYB_LAUNCHED(ctx);
-    if (S > 1) {
+    if (S > 1 && epi.mode == EPI_LSTM_CELL) {
+      k_splitk_reduce_cell<<<stream_grid(ctx, (size_t)M / 16 * N + 1, 256), 256, 0, ctx->stream>>>(part, S, M, N, epi);
+      DYB_LAUNCHED(ctx);
+    } else if (S > 1) {
       int vec = M % 4 == 0 && epi.ldc % 4 == 0 && aligned16(epi.C) && epi.mode != EPI_GATES &&
                 (epi.mode != EPI_BIAS || aligned16(epi.bias)) &&
                 (epi.mode != EPI_ACCUM_MASK || (aligned16(epi.maskC) && (!epi.maskc_full || epi.maskc_ld % 4 == 0)));

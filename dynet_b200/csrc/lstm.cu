@@ -514,8 +514,8 @@ int dyb200_vanilla_lstm_fwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
   const size_t total = (size_t)H * c_tm1->bd;
   DYB_CHECK_ARG(ctx, t_size(c_t) == total && t_size(h_t) == total, "lstm_fwd_fused: c_t / h_t size mismatch");
   {
-    // One kernel for the whole step when the shape gives whole tiles of interleaved gate rows and no K split:
-    // W x + U h on the tensor pipe, bias + sigmoid / tanh, and the c / h update in its epilogue.
+    // W x + U h on the tensor pipe with interleaved gate rows, so that bias + sigmoid / tanh AND the c / h update run in
+    // the product's epilogue: inside the MMA kernel when K is not split, else in the split-K reduction.
     const uint32_t I = t_dim(x, 0), B = x->bd, G = 4 * H;
     const bool shapes_ok = x->nd == 1 && h_tm1->nd == 1 && t_dim(h_tm1, 0) == H && h_tm1->bd == B && c_tm1->bd == B && Wx->nd == 2 &&
                            Wx->d[0] == G && Wx->d[1] == I && Wh->nd == 2 && Wh->d[0] == G && Wh->d[1] == H && t_size(b) == G &&
@@ -523,8 +523,9 @@ int dyb200_vanilla_lstm_fwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
                            (!attrs->dropout || ((mask_x->bd == B || mask_x->bd == 1) && (mask_h->bd == B || mask_h->bd == 1) &&
                                                 t_dim(mask_x, 0) == I && t_dim(mask_h, 0) == H));
     const uint32_t kb = (I + 31) / 32 + (H + 31) / 32;
+    (void)kb;
     if (shapes_ok && attrs->weightnoise_std == 0.f && H % 32 == 0 && I > 0 && B > 0 && dyb200_tc_eligible(G, B, 2.0 * G * B * (I + H)) &&
-        dyb200_tc_splits(ctx, G, B, kb) == 1) {
+        aligned16(gates->v) && aligned16(b->v) && aligned16(c_tm1->v) && aligned16(c_t->v) && aligned16(h_t->v)) {
       { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
       PackedOp A[2], Bp[2];
       int rc;

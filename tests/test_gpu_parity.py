@@ -968,11 +968,11 @@ def test_random_bernoulli(g, capi):
     assert abs(np.corrcoef(k, l)[0, 1]) < 0.01
 
 
-@pytest.mark.parametrize("I,H,B,masks", [(512, 1024, 300, "full"), (256, 1024, 384, None)])
+@pytest.mark.parametrize("I,H,B,masks", [(512, 1024, 300, "full"), (256, 1024, 384, None), (512, 1024, 64, "full"), (256, 512, 96, None)])
 def test_lstm_fwd_fused_cell_epilogue(oracle, g, capi, I, H, B, masks):
-    """Shapes that give whole tiles and no K split take the one-kernel path (gate GEMM with the c / h update in its
-    epilogue).  Its gates, c and h must equal the three nodes called one after the other bit for bit, and the oracle
-    within the LSTM-state tolerance."""
+    """The fused forward forms c and h in the epilogue of the gate product: inside the MMA kernel for shapes without a
+    K split (the first two), in the split-K reduction otherwise (the last two).  Gates, c and h must equal the three
+    nodes called one after the other bit for bit, and the oracle within the LSTM-state tolerance."""
     r = rng(155)
     x, h, c_prev = randn(r, B, I), randn(r, B, H, scale=0.5), randn(r, B, H, scale=0.5)
     Wx, Wh, b = glorot(r, 4 * H, I), glorot(r, 4 * H, H), randn(r, 4 * H, scale=0.1)
