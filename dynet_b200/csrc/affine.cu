@@ -19,6 +19,7 @@ constexpr int kThreads = 256;
 // dst[e] = src[e % period]
 __global__ void __launch_bounds__(kThreads) k_tile_copy(const float* __restrict__ src, size_t period, float* __restrict__ dst,
                                                         size_t n, int vec) {
+  dyb_grid_dep_sync();
   if (vec) {
     const size_t n4 = n / 4;
     for (size_t q = (size_t)blockIdx.x * kThreads + threadIdx.x; q < n4; q += (size_t)gridDim.x * kThreads)
@@ -30,6 +31,7 @@ __global__ void __launch_bounds__(kThreads) k_tile_copy(const float* __restrict_
 
 // dst[e] += src[e]
 __global__ void __launch_bounds__(kThreads) k_add_into(const float* __restrict__ src, float* __restrict__ dst, size_t n, int vec) {
+  dyb_grid_dep_sync();
   if (vec) {
     const size_t n4 = n / 4;
     for (size_t q = (size_t)blockIdx.x * kThreads + threadIdx.x; q < n4; q += (size_t)gridDim.x * kThreads) {
@@ -175,7 +177,7 @@ int dyb200_affine_transform_fwd(DYB200_FWD_ARGS) {
     DYB_CUDA(ctx, cudaMemcpyAsync(fx->v, xs[0].v, fx_size * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
   } else {
     const int vec = b_size % 4 == 0 && aligned16(xs[0].v) && aligned16(fx->v);
-    k_tile_copy<<<stream_grid(ctx, fx_size / 4 + 1, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, b_size, fx->v, fx_size, vec);
+    dyb_launch(k_tile_copy, stream_grid(ctx, fx_size / 4 + 1, kThreads), kThreads, 0, ctx, xs[0].v, b_size, fx->v, fx_size, vec);
     DYB_LAUNCHED(ctx);
   }
   for (int k = first; k < nxs; k += 2) {
@@ -196,7 +198,7 @@ int dyb200_affine_transform_bwd(DYB200_BWD_ARGS) {
     const size_t dx_size = t_size(dEdxi), df_size = t_size(dEdf);
     if (dx_size == df_size) {
       const int vec = dx_size % 4 == 0 && aligned16(dEdf->v) && aligned16(dEdxi->v);
-      k_add_into<<<stream_grid(ctx, dx_size / 4 + 1, kThreads), kThreads, 0, ctx->stream>>>(dEdf->v, dEdxi->v, dx_size, vec);
+      dyb_launch(k_add_into, stream_grid(ctx, dx_size / 4 + 1, kThreads), kThreads, 0, ctx, dEdf->v, dEdxi->v, dx_size, vec);
       DYB_LAUNCHED(ctx);
       return DYB200_OK;
     }

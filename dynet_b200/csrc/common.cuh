@@ -32,6 +32,7 @@ struct dyb200_ctx {
   // Optional cache of packed (hi/lo, K-major) parameter matrices, so that a weight used by every
   // time step is split once per optimizer step instead of once per GEMM.  Off by default: when on,
   // the caller must report every in-place parameter change (dyb200_ctx_params_changed).
+  int pdl;               // launch kernels with programmatic stream serialization (see dyb_launch)
   int param_cache_on;
   uint64_t param_version, param_tick;
   struct ParamPack {
@@ -118,6 +119,26 @@ static inline unsigned stream_grid(const dyb200_ctx* ctx, size_t work_items, uns
 }
 
 #ifdef __CUDACC__
+// Every kernel goes out through this helper.  With programmatic dependent launch on (dyb200_ctx::pdl), a kernel may be
+// scheduled while its predecessor in the stream is still running: its launch latency and whatever it does before
+// dyb_grid_dep_sync() overlap the predecessor's tail; nothing after that call runs before the predecessor has completed
+// and its writes are visible.  With it off the launch is an ordinary stream-ordered one and the device call is a no-op.
+template <class... KArgs, class... Args>
+inline void dyb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, dyb200_ctx* ctx, Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // a failure is picked up by DYB_LAUNCHED (cudaGetLastError)
+}
+__device__ __forceinline__ void dyb_grid_dep_sync() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

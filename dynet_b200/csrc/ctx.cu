@@ -102,6 +102,12 @@ int dyb200_ctx_destroy(dyb200_ctx* ctx) {
   return DYB200_OK;
 }
 
+int dyb200_ctx_dependent_launch(dyb200_ctx* ctx, int enable) {
+  if (!ctx) return DYB200_EINVAL;
+  ctx->pdl = enable ? 1 : 0;
+  return DYB200_OK;
+}
+
 int dyb200_ctx_param_cache(dyb200_ctx* ctx, int enable) {
   ctx->param_cache_on = enable ? 1 : 0;
   ctx->param_version++;

@@ -36,6 +36,7 @@ struct BElu {
 template <class F>
 __global__ void __launch_bounds__(kThreads) k_unary_fwd(const float* __restrict__ x, float* __restrict__ y,
                                                        size_t n4, size_t n, F f) {
+  dyb_grid_dep_sync();
   const size_t stride = (size_t)gridDim.x * kThreads * kUnroll;
   for (size_t base = (size_t)blockIdx.x * kThreads * kUnroll + threadIdx.x; base < n4; base += stride) {
     float4 v[kUnroll];
@@ -61,6 +62,7 @@ __global__ void __launch_bounds__(kThreads) k_unary_fwd(const float* __restrict_
 template <class F>
 __global__ void __launch_bounds__(kThreads) k_unary_fwd_scalar(const float* __restrict__ x, float* __restrict__ y,
                                                               size_t n, F f) {
+  dyb_grid_dep_sync();
   for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (size_t)gridDim.x * kThreads)
     y[i] = f(x[i]);
 }
@@ -68,6 +70,7 @@ __global__ void __launch_bounds__(kThreads) k_unary_fwd_scalar(const float* __re
 template <class G>
 __global__ void __launch_bounds__(kThreads) k_unary_bwd(const float* __restrict__ a, const float* __restrict__ dy,
                                                        float* __restrict__ dx, size_t n4, size_t n, G g) {
+  dyb_grid_dep_sync();
   const size_t stride = (size_t)gridDim.x * kThreads * kUnroll;
   for (size_t base = (size_t)blockIdx.x * kThreads * kUnroll + threadIdx.x; base < n4; base += stride) {
     float4 va[kUnroll], vd[kUnroll], vx[kUnroll];
@@ -94,6 +97,7 @@ __global__ void __launch_bounds__(kThreads) k_unary_bwd(const float* __restrict_
 template <class G>
 __global__ void __launch_bounds__(kThreads) k_unary_bwd_scalar(const float* __restrict__ a, const float* __restrict__ dy,
                                                               float* __restrict__ dx, size_t n, G g) {
+  dyb_grid_dep_sync();
   for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (size_t)gridDim.x * kThreads)
     dx[i] += g(a[i], dy[i]);
 }
@@ -106,9 +110,9 @@ int unary_fwd(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, dyb200_tensor* 
   if (n == 0) return DYB200_OK;
   if (aligned16(xs[0].v) && aligned16(fx->v)) {
     size_t n4 = n / 4;
-    k_unary_fwd<<<stream_grid(ctx, n4 ? n4 : 1, kThreads * kUnroll), kThreads, 0, ctx->stream>>>(xs[0].v, fx->v, n4, n, f);
+    dyb_launch(k_unary_fwd<F>, stream_grid(ctx, n4 ? n4 : 1, kThreads * kUnroll), kThreads, 0, ctx, xs[0].v, fx->v, n4, n, f);
   } else {
-    k_unary_fwd_scalar<<<stream_grid(ctx, n, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, fx->v, n, f);
+    dyb_launch(k_unary_fwd_scalar<F>, stream_grid(ctx, n, kThreads), kThreads, 0, ctx, xs[0].v, fx->v, n, f);
   }
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
@@ -122,9 +126,9 @@ int unary_bwd(dyb200_ctx* ctx, const float* a, const dyb200_tensor* dEdf, unsign
   if (n == 0) return DYB200_OK;
   if (aligned16(a) && aligned16(dEdf->v) && aligned16(dEdxi->v)) {
     size_t n4 = n / 4;
-    k_unary_bwd<<<stream_grid(ctx, n4 ? n4 : 1, kThreads * kUnroll), kThreads, 0, ctx->stream>>>(a, dEdf->v, dEdxi->v, n4, n, g);
+    dyb_launch(k_unary_bwd<G>, stream_grid(ctx, n4 ? n4 : 1, kThreads * kUnroll), kThreads, 0, ctx, a, dEdf->v, dEdxi->v, n4, n, g);
   } else {
-    k_unary_bwd_scalar<<<stream_grid(ctx, n, kThreads), kThreads, 0, ctx->stream>>>(a, dEdf->v, dEdxi->v, n, g);
+    dyb_launch(k_unary_bwd_scalar<G>, stream_grid(ctx, n, kThreads), kThreads, 0, ctx, a, dEdf->v, dEdxi->v, n, g);
   }
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
@@ -154,6 +158,7 @@ __host__ __device__ inline size_t shape5_size(const Shape5& s) {
 template <int OP, bool SWAP>
 __global__ void __launch_bounds__(kThreads) k_bin_fwd_vec(const float* __restrict__ a, const float* __restrict__ b,
                                                          float* __restrict__ y, size_t n4, size_t period4) {
+  dyb_grid_dep_sync();
   const size_t stride = (size_t)gridDim.x * kThreads * kUnroll;
   for (size_t base = (size_t)blockIdx.x * kThreads * kUnroll + threadIdx.x; base < n4; base += stride) {
     float4 va[kUnroll], vb[kUnroll];
@@ -192,6 +197,7 @@ template <int OP>
 __global__ void __launch_bounds__(kThreads) k_bin_fwd_generic(const float* __restrict__ a, Shape5 sa,
                                                              const float* __restrict__ b, Shape5 sb,
                                                              float* __restrict__ y, Shape5 so, size_t total) {
+  dyb_grid_dep_sync();
   for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < total; e += (size_t)gridDim.x * kThreads)
     y[e] = bin_fwd<OP>(a[bidx(e, so, sa)], b[bidx(e, so, sb)]);
 }
@@ -203,6 +209,7 @@ __global__ void __launch_bounds__(kThreads) k_bin_bwd_noreduce(const float* __re
                                                               const float* __restrict__ b, Shape5 sb,
                                                               const float* __restrict__ dy, Shape5 so, size_t total,
                                                               unsigned i, float* __restrict__ dxi) {
+  dyb_grid_dep_sync();
   for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < total; e += (size_t)gridDim.x * kThreads)
     dxi[e] += bin_bwd<OP>(a[bidx(e, so, sa)], b[bidx(e, so, sb)], dy[e], i);
 }
@@ -214,6 +221,7 @@ __global__ void __launch_bounds__(kThreads) k_bin_bwd_vec(const float* __restric
                                                          const float* __restrict__ b, size_t pb4,
                                                          const float* __restrict__ dy, size_t n4, unsigned i,
                                                          float* __restrict__ dxi) {
+  dyb_grid_dep_sync();
   const size_t stride = (size_t)gridDim.x * kThreads * kUnroll;
   for (size_t base = (size_t)blockIdx.x * kThreads * kUnroll + threadIdx.x; base < n4; base += stride) {
     float4 va[kUnroll], vb[kUnroll], vd[kUnroll], vx[kUnroll];
@@ -247,6 +255,7 @@ __global__ void __launch_bounds__(kThreads) k_bin_bwd_reduce(const float* __rest
                                                             const float* __restrict__ b, Shape5 sb,
                                                             const float* __restrict__ dy, Shape5 so, unsigned i,
                                                             float* __restrict__ dxi, size_t ni) {
+  dyb_grid_dep_sync();
   const Shape5& si = i == 0 ? sa : sb;
   for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < ni; e += (size_t)gridDim.x * kThreads) {
     // unravel e in the shape of argument i
@@ -327,12 +336,12 @@ int binary_fwd(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, dyb200_tensor*
     unsigned grid = stream_grid(ctx, n4, kThreads * kUnroll);
     if (sa.s[4] >= sb.s[4]) {
       size_t period4 = (sb.s[4] == so.s[4] ? total : n) / 4;
-      k_bin_fwd_vec<OP, false><<<grid, kThreads, 0, ctx->stream>>>(xs[0].v, xs[1].v, fx->v, n4, period4);
+      dyb_launch(k_bin_fwd_vec<OP, false>, grid, kThreads, 0, ctx, xs[0].v, xs[1].v, fx->v, n4, period4);
     } else {
-      k_bin_fwd_vec<OP, true><<<grid, kThreads, 0, ctx->stream>>>(xs[1].v, xs[0].v, fx->v, n4, n / 4);
+      dyb_launch(k_bin_fwd_vec<OP, true>, grid, kThreads, 0, ctx, xs[1].v, xs[0].v, fx->v, n4, n / 4);
     }
   } else {
-    k_bin_fwd_generic<OP><<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, sa, xs[1].v, sb, fx->v, so, total);
+    dyb_launch(k_bin_fwd_generic<OP>, stream_grid(ctx, total, kThreads), kThreads, 0, ctx, xs[0].v, sa, xs[1].v, sb, fx->v, so, total);
   }
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
@@ -357,12 +366,12 @@ int binary_bwd(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, const dyb200_t
       aligned16(dEdxi->v)) {
     size_t n4 = total / 4;
     size_t pa4 = (sa.s[4] == so.s[4] ? total : n) / 4, pb4 = (sb.s[4] == so.s[4] ? total : n) / 4;
-    k_bin_bwd_vec<OP><<<stream_grid(ctx, n4, kThreads * kUnroll), kThreads, 0, ctx->stream>>>(xs[0].v, pa4, xs[1].v, pb4, dEdf->v, n4, i, dEdxi->v);
+    dyb_launch(k_bin_bwd_vec<OP>, stream_grid(ctx, n4, kThreads * kUnroll), kThreads, 0, ctx, xs[0].v, pa4, xs[1].v, pb4, dEdf->v, n4, i, dEdxi->v);
     DYB_LAUNCHED(ctx);
     return DYB200_OK;
   }
   if (!need_reduce) {
-    k_bin_bwd_noreduce<OP><<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, sa, xs[1].v, sb, dEdf->v, so, total, i, dEdxi->v);
+    dyb_launch(k_bin_bwd_noreduce<OP>, stream_grid(ctx, total, kThreads), kThreads, 0, ctx, xs[0].v, sa, xs[1].v, sb, dEdf->v, so, total, i, dEdxi->v);
     DYB_LAUNCHED(ctx);
     return DYB200_OK;
   }
@@ -370,7 +379,7 @@ int binary_bwd(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, const dyb200_t
     BatchBwd<OP> f{xs[0].v, xs[1].v, dEdf->v, n, i, sa.s[4], sb.s[4]};
     return batch_reduce_add(ctx, f, n, so.s[4], dEdxi->v);
   }
-  k_bin_bwd_reduce<OP><<<stream_grid(ctx, ni, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, sa, xs[1].v, sb, dEdf->v, so, i, dEdxi->v, ni);
+  dyb_launch(k_bin_bwd_reduce<OP>, stream_grid(ctx, ni, kThreads), kThreads, 0, ctx, xs[0].v, sa, xs[1].v, sb, dEdf->v, so, i, dEdxi->v, ni);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }

@@ -20,6 +20,7 @@ __device__ __forceinline__ float load_b(const GemmPair& p, uint32_t k, uint32_t 
 
 __global__ void __launch_bounds__(256) k_gemm_simt(uint32_t M, uint32_t N, int npairs, GemmPair p0, GemmPair p1,
                                                   GemmEpilogue epi) {
+  dyb_grid_dep_sync();
   __shared__ float As[TK][TM + 4];
   __shared__ float Bs[TK][TN + 4];
   const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
@@ -80,7 +81,7 @@ int dyb200_gemm_simt(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const 
   GemmPair p0 = pairs[0], p1 = npairs > 1 ? pairs[1] : pairs[0];
   dim3 grid((M + TM - 1) / TM, (N + TN - 1) / TN);
   DYB_CHECK_ARG(ctx, grid.y <= 65535, "gemm: N too large for the CUDA-core path");
-  k_gemm_simt<<<grid, 256, 0, ctx->stream>>>(M, N, npairs, p0, p1, epi);
+  dyb_launch(k_gemm_simt, grid, 256, 0, ctx, M, N, npairs, p0, p1, epi);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }

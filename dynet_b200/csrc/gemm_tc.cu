@@ -109,6 +109,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ TmapPack tm, uint32_t M, uint32_t N,
                                                          uint32_t kb0, uint32_t kb1, uint32_t kb_per_split,
                                                          GemmEpilogue epi, uint32_t* flags) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // (the wait comes after the prologue, below)
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
@@ -136,6 +137,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
+  // Barrier initialisation and the TMEM allocation above may overlap the previous kernel of the stream; nothing below
+  // (TMA loads, c_prev prefetch, stores) starts before that kernel has completed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     if (lane == 0) {
@@ -342,6 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
 // ---- split-K second stage: C = epilogue(sum_s part[s]) in ascending split order ----------------
 __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__ part, uint32_t S, uint32_t M, uint32_t N,
                                                       GemmEpilogue epi, int vec) {
+  dyb_grid_dep_sync();
   const size_t MN = (size_t)M * N;
   if (vec) {   // M % 4 == 0 and 16-byte aligned C / mask: four rows of one column per thread
     const size_t MN4 = MN / 4;
@@ -392,6 +397,7 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
 // split order, applies bias + sigmoid / tanh, writes the four gate rows and forms c and h.
 __global__ void __launch_bounds__(256) k_splitk_reduce_cell(const float* __restrict__ part, uint32_t S, uint32_t M, uint32_t N,
                                                            GemmEpilogue epi) {
+  dyb_grid_dep_sync();
   const uint32_t H = epi.H, H4 = H / 4;
   const size_t MN = (size_t)M * N, total = (size_t)H4 * N;
   for (size_t q = (size_t)blockIdx.x * 256 + threadIdx.x; q < total; q += (size_t)gridDim.x * 256) {
@@ -427,6 +433,7 @@ __global__ void __launch_bounds__(256) k_splitk_reduce_cell(const float* __restr
 // k index is fast (element (r, k) at src[k + ld * r]) a unit is 1024 consecutive k of one row; for a source whose
 // row index is fast (element (r, k) at src[r + ld * k]) a unit is a 32 x 32 tile transposed through shared memory.
 __global__ void __launch_bounds__(256) k_pack_multi(const PackJobs jobs) {
+  dyb_grid_dep_sync();
   __shared__ float tile[32][33];
   int j = 0;
 #pragma unroll
@@ -524,7 +531,7 @@ int make_map(dyb200_ctx* ctx, EncodeTiledFn enc, CUtensorMap* map, float* plane,
 int pack_flush_impl(dyb200_ctx* ctx, PackJobs* jobs) {
   if (jobs->n == 0) return DYB200_OK;
   const uint32_t total = jobs->start[jobs->n];
-  k_pack_multi<<<total, 256, 0, ctx->stream>>>(*jobs);
+  dyb_launch(k_pack_multi, total, 256, 0, ctx, *jobs);
   jobs->n = 0;
   jobs->start[0] = 0;
   DYB_LAUNCHED(ctx);
@@ -733,10 +740,10 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   {
     // times the MMA kernel (and the split-K reduction); the packing launches show up in the step time
     GemmProfScope scope(ctx, flops, 1, M, N, kb_total * BK, (uint32_t)epi.mode);
-    k_gemm_tc<<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
+    dyb_launch(k_gemm_tc, grid, kThreads, SMEM_BYTES, ctx, tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
     DYB_LAUNCHED(ctx);
     if (S > 1 && epi.mode == EPI_LSTM_CELL) {
-      k_splitk_reduce_cell<<<stream_grid(ctx, (size_t)M / 16 * N + 1, 256), 256, 0, ctx->stream>>>(part, S, M, N, epi);
+      dyb_launch(k_splitk_reduce_cell, stream_grid(ctx, (size_t)M / 16 * N + 1, 256), 256, 0, ctx, part, S, M, N, epi);
       DYB_LAUNCHED(ctx);
     } else if (S > 1) {
       int vec = M % 4 == 0 && epi.ldc % 4 == 0 && aligned16(epi.C) && epi.mode != EPI_GATES &&
@@ -745,7 +752,7 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
       if (epi.split_m)
         vec = vec && epi.split_m % 4 == 0 && epi.ldc2 % 4 == 0 && aligned16(epi.C2) &&
               (epi.mode != EPI_ACCUM_MASK || (aligned16(epi.maskC2) && (!epi.maskc2_full || epi.maskc2_ld % 4 == 0)));
-      k_splitk_reduce<<<stream_grid(ctx, (size_t)M * N / 4 + 1, 256), 256, 0, ctx->stream>>>(part, S, M, N, epi, vec);
+      dyb_launch(k_splitk_reduce, stream_grid(ctx, (size_t)M * N / 4 + 1, 256), 256, 0, ctx, part, S, M, N, epi, vec);
       DYB_LAUNCHED(ctx);
     }
   }

@@ -9,12 +9,14 @@ namespace {
 constexpr int kBlock = 256;
 
 __global__ void __launch_bounds__(kBlock) k_fill(float* __restrict__ p, size_t n, float v) {
+  dyb_grid_dep_sync();
   for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) p[i] = v;
 }
 
 // partial[blk] = sum over this CTA's grid-stride slice of x (SQUARE: of x^2)
 template <bool SQUARE>
 __global__ void __launch_bounds__(kBlock) k_sum_partial(const float* __restrict__ x, size_t n, float* __restrict__ partial) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   float acc = 0.f;
   if (aligned16(x)) {
@@ -36,6 +38,7 @@ __global__ void __launch_bounds__(kBlock) k_sum_partial(const float* __restrict_
 }
 __global__ void __launch_bounds__(kBlock) k_sum_final(const float* __restrict__ partial, int np, float* __restrict__ out,
                                                      int accumulate) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   float acc = 0.f;
   for (int k = threadIdx.x; k < np; k += kBlock) acc += partial[k];
@@ -47,6 +50,7 @@ __global__ void __launch_bounds__(kBlock) k_sum_final(const float* __restrict__ 
 // sumsq[0] holds the squared global gradient norm (already reduced over ranks when data-parallel).
 __global__ void __launch_bounds__(kBlock) k_sgd_update(float* __restrict__ p, float* __restrict__ g, size_t n, float lr,
                                                       float clip, const float* __restrict__ sumsq) {
+  dyb_grid_dep_sync();
   float gg = sqrtf(sumsq[0]);
   float gscale = (clip > 0.f && gg > clip) ? clip / gg : 1.f;
   float step = lr * gscale;
@@ -69,7 +73,7 @@ extern "C" {
 int dyb200_fill(float* p, size_t n, float value, dyb200_ctx* ctx) {
   if (n == 0) return DYB200_OK;
   DYB_CHECK_ARG(ctx, p != nullptr, "fill: null pointer");
-  k_fill<<<stream_grid(ctx, n, kBlock * 4), kBlock, 0, ctx->stream>>>(p, n, value);
+  dyb_launch(k_fill, stream_grid(ctx, n, kBlock * 4), kBlock, 0, ctx, p, n, value);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -80,10 +84,10 @@ static int sum_impl(const float* x, size_t n, float* out, int square, int accumu
   void* partial;
   int rc = dyb200_scratch(ctx, np * sizeof(float), &partial);
   if (rc) return rc;
-  if (square) k_sum_partial<true><<<np, kBlock, 0, ctx->stream>>>(x, n, (float*)partial);
-  else k_sum_partial<false><<<np, kBlock, 0, ctx->stream>>>(x, n, (float*)partial);
+  if (square) dyb_launch(k_sum_partial<true>, np, kBlock, 0, ctx, x, n, (float*)partial);
+  else dyb_launch(k_sum_partial<false>, np, kBlock, 0, ctx, x, n, (float*)partial);
   DYB_LAUNCHED(ctx);
-  k_sum_final<<<1, kBlock, 0, ctx->stream>>>((const float*)partial, np, out, accumulate);
+  dyb_launch(k_sum_final, 1, kBlock, 0, ctx, (const float*)partial, np, out, accumulate);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -101,7 +105,7 @@ int dyb200_sgd_update(float* params, float* grads, size_t n, float lr, float cli
                       dyb200_ctx* ctx) {
   if (n == 0) return DYB200_OK;
   DYB_CHECK_ARG(ctx, params && grads && grad_sumsq, "sgd_update: null pointer");
-  k_sgd_update<<<stream_grid(ctx, n / 4 + 1, kBlock * 2), kBlock, 0, ctx->stream>>>(params, grads, n, lr, clip_threshold, grad_sumsq);
+  dyb_launch(k_sgd_update, stream_grid(ctx, n / 4 + 1, kBlock * 2), kBlock, 0, ctx, params, grads, n, lr, clip_threshold, grad_sumsq);
   DYB_LAUNCHED(ctx);
   ctx->param_version++;   // packed copies of the parameters in the cache are stale now
   return DYB200_OK;

@@ -19,6 +19,7 @@ constexpr int kThreads = 256;
 template <int ADD>
 __global__ void __launch_bounds__(kThreads) k_copy2d(const float* __restrict__ src, size_t src_pitch, size_t src_rows,
                                                      float* __restrict__ dst, size_t dst_pitch, size_t row_len, size_t rows, int vec) {
+  dyb_grid_dep_sync();
   if (vec) {
     const size_t len4 = row_len / 4, total = len4 * rows;
     for (size_t q = (size_t)blockIdx.x * kThreads + threadIdx.x; q < total; q += (size_t)gridDim.x * kThreads) {
@@ -44,8 +45,8 @@ int copy2d(dyb200_ctx* ctx, const float* src, size_t src_pitch, size_t src_rows,
   if (row_len == 0 || rows == 0) return DYB200_OK;
   const int vec = row_len % 4 == 0 && src_pitch % 4 == 0 && dst_pitch % 4 == 0 && aligned16(src) && aligned16(dst);
   const unsigned grid = stream_grid(ctx, row_len * rows / (vec ? 4 : 1) + 1, kThreads);
-  if (add) k_copy2d<1><<<grid, kThreads, 0, ctx->stream>>>(src, src_pitch, src_rows, dst, dst_pitch, row_len, rows, vec);
-  else k_copy2d<0><<<grid, kThreads, 0, ctx->stream>>>(src, src_pitch, src_rows, dst, dst_pitch, row_len, rows, vec);
+  if (add) dyb_launch(k_copy2d<1>, grid, kThreads, 0, ctx, src, src_pitch, src_rows, dst, dst_pitch, row_len, rows, vec);
+  else dyb_launch(k_copy2d<0>, grid, kThreads, 0, ctx, src, src_pitch, src_rows, dst, dst_pitch, row_len, rows, vec);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -74,6 +75,7 @@ struct BatchOf {   // f(r, b) = v[r + n * b]
 struct SumArgs { const float* x[4]; size_t size[4]; int n; };
 template <int ACC>
 __global__ void __launch_bounds__(kThreads) k_sum_group(const SumArgs a, float* __restrict__ fx, size_t n) {
+  dyb_grid_dep_sync();
   for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < n; e += (size_t)gridDim.x * kThreads) {
     float s = a.x[0][e % a.size[0]];
     for (int k = 1; k < a.n; ++k) s += a.x[k][e % a.size[k]];
@@ -85,6 +87,7 @@ __global__ void __launch_bounds__(kThreads) k_sum_group(const SumArgs a, float* 
 // (lower dimension innermost), batch outermost.
 struct Dims4 { uint32_t d[4]; uint32_t red[4]; };
 __global__ void __launch_bounds__(kThreads) k_sum_dims(const float* __restrict__ x, float* __restrict__ y, const Dims4 s, size_t n_out) {
+  dyb_grid_dep_sync();
   for (size_t o = (size_t)blockIdx.x * kThreads + threadIdx.x; o < n_out; o += (size_t)gridDim.x * kThreads) {
     uint32_t idx[4]; size_t rem = o;
     for (int k = 0; k < 4; ++k) {
@@ -105,6 +108,7 @@ __global__ void __launch_bounds__(kThreads) k_sum_dims(const float* __restrict__
 }
 // dEdxi[e] += dEdf[index of e with the reduced coordinates dropped]
 __global__ void __launch_bounds__(kThreads) k_sum_dims_bwd(const float* __restrict__ dy, float* __restrict__ dx, const Dims4 s, size_t n_in) {
+  dyb_grid_dep_sync();
   for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < n_in; e += (size_t)gridDim.x * kThreads) {
     size_t rem = e, o = 0, mul = 1;
     for (int k = 0; k < 4; ++k) {
@@ -116,6 +120,7 @@ __global__ void __launch_bounds__(kThreads) k_sum_dims_bwd(const float* __restri
 }
 // Sum over dimension 0 (contiguous): one warp per output element.
 __global__ void __launch_bounds__(kThreads) k_sum_dim0(const float* __restrict__ x, float* __restrict__ y, uint32_t d0, size_t n_out) {
+  dyb_grid_dep_sync();
   const size_t warp = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5, nw = ((size_t)gridDim.x * kThreads) >> 5;
   const int lane = threadIdx.x & 31;
   for (size_t o = warp; o < n_out; o += nw) {
@@ -129,6 +134,7 @@ __global__ void __launch_bounds__(kThreads) k_sum_dim0(const float* __restrict__
 
 // y[b] = sum_i x[i, b]^2 : one CTA per batch element
 __global__ void __launch_bounds__(kThreads) k_squared_norm(const float* __restrict__ x, float* __restrict__ y, size_t n) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   const float* c = x + (size_t)blockIdx.x * n;
   float acc = 0.f;
@@ -142,6 +148,7 @@ __global__ void __launch_bounds__(kThreads) k_squared_norm(const float* __restri
 }
 __global__ void __launch_bounds__(kThreads) k_squared_norm_bwd(const float* __restrict__ x, const float* __restrict__ dy,
                                                                float* __restrict__ dx, size_t n, size_t total) {
+  dyb_grid_dep_sync();
   for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < total; e += (size_t)gridDim.x * kThreads)
     dx[e] += x[e] * dy[e / n] * 2.0f;
 }
@@ -160,6 +167,7 @@ __device__ __forceinline__ void philox4x32_10(uint32_t c[4], uint32_t k0, uint32
 }
 // y[e] = (u_e < p) ? scale : 0, u_e uniform in [0, 1) from 24 random bits
 __global__ void __launch_bounds__(kThreads) k_bernoulli(float* __restrict__ y, size_t n, float p, float scale, uint64_t seed, uint64_t offset) {
+  dyb_grid_dep_sync();
   const size_t n4 = (n + 3) / 4;
   const bool vec = aligned16(y);
   for (size_t q = (size_t)blockIdx.x * kThreads + threadIdx.x; q < n4; q += (size_t)gridDim.x * kThreads) {
@@ -256,8 +264,8 @@ int dyb200_sum_fwd(DYB200_FWD_ARGS) {
   auto group = [&](int first, int count, bool acc) -> int {
     SumArgs a; a.n = count;
     for (int k = 0; k < 4; ++k) { a.x[k] = k < count ? xs[first + k].v : nullptr; a.size[k] = k < count ? t_size(&xs[first + k]) : 1; }
-    if (acc) k_sum_group<1><<<grid, kThreads, 0, ctx->stream>>>(a, fx->v, n);
-    else k_sum_group<0><<<grid, kThreads, 0, ctx->stream>>>(a, fx->v, n);
+    if (acc) dyb_launch(k_sum_group<1>, grid, kThreads, 0, ctx, a, fx->v, n);
+    else dyb_launch(k_sum_group<0>, grid, kThreads, 0, ctx, a, fx->v, n);
     DYB_LAUNCHED(ctx);
     return DYB200_OK;
   };
@@ -317,9 +325,9 @@ int dyb200_sum_dim_fwd(DYB200_FWD_ARGS) {
     return batch_reduce_add(ctx, BatchOf{xs[0].v, n_out}, n_out, xs[0].bd, fx->v);
   }
   if (a->ndims == 1 && a->dims[0] == 0 && !a->include_batch_dim && s.d[0] >= 32) {
-    k_sum_dim0<<<stream_grid(ctx, n_out, kThreads / 32), kThreads, 0, ctx->stream>>>(xs[0].v, fx->v, s.d[0], n_out);
+    dyb_launch(k_sum_dim0, stream_grid(ctx, n_out, kThreads / 32), kThreads, 0, ctx, xs[0].v, fx->v, s.d[0], n_out);
   } else {
-    k_sum_dims<<<stream_grid(ctx, n_out, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, fx->v, s, n_out);
+    dyb_launch(k_sum_dims, stream_grid(ctx, n_out, kThreads), kThreads, 0, ctx, xs[0].v, fx->v, s, n_out);
   }
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
@@ -335,7 +343,7 @@ int dyb200_sum_dim_bwd(DYB200_BWD_ARGS) {
   DYB_CHECK_ARG(ctx, t_size(dEdf) == n_out, "SumDimension: gradient size mismatch");
   const size_t n_in = t_size(dEdxi);
   if (n_in == 0) return DYB200_OK;
-  k_sum_dims_bwd<<<stream_grid(ctx, n_in, kThreads), kThreads, 0, ctx->stream>>>(dEdf->v, dEdxi->v, s, n_in);
+  dyb_launch(k_sum_dims_bwd, stream_grid(ctx, n_in, kThreads), kThreads, 0, ctx, dEdf->v, dEdxi->v, s, n_in);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -344,7 +352,7 @@ int dyb200_squared_norm_fwd(DYB200_FWD_ARGS) {
   (void)aux_mem; (void)attrs;
   DYB_CHECK_ARG(ctx, nxs == 1 && fx && fx->v && xs[0].v && t_size(fx) == xs[0].bd, "SquaredNorm: one input and a {1} x batch output required");
   if (xs[0].bd == 0) return DYB200_OK;
-  k_squared_norm<<<xs[0].bd, kThreads, 0, ctx->stream>>>(xs[0].v, fx->v, t_batch_size(&xs[0]));
+  dyb_launch(k_squared_norm, xs[0].bd, kThreads, 0, ctx, xs[0].v, fx->v, t_batch_size(&xs[0]));
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -355,7 +363,7 @@ int dyb200_squared_norm_bwd(DYB200_BWD_ARGS) {
                 "SquaredNorm: bad backward arguments");
   const size_t total = t_size(&xs[0]);
   if (total == 0) return DYB200_OK;
-  k_squared_norm_bwd<<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, dEdf->v, dEdxi->v, t_batch_size(&xs[0]), total);
+  dyb_launch(k_squared_norm_bwd, stream_grid(ctx, total, kThreads), kThreads, 0, ctx, xs[0].v, dEdf->v, dEdxi->v, t_batch_size(&xs[0]), total);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -367,7 +375,7 @@ int dyb200_random_bernoulli_fwd(DYB200_FWD_ARGS) {
   DYB_CHECK_ARG(ctx, a->p >= 0.f && a->p <= 1.f, "RandomBernoulli: p = %g is not a probability", (double)a->p);
   const size_t n = t_size(fx);
   if (n == 0) return DYB200_OK;
-  k_bernoulli<<<stream_grid(ctx, n / 4 + 1, kThreads), kThreads, 0, ctx->stream>>>(fx->v, n, a->p, a->scale, a->seed, a->offset);
+  dyb_launch(k_bernoulli, stream_grid(ctx, n / 4 + 1, kThreads), kThreads, 0, ctx, fx->v, n, a->p, a->scale, a->seed, a->offset);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }

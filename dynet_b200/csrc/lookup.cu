@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(kGatherWarps * 32) k_gather_bulk(const float* 
                                                                   const uint32_t* __restrict__ ids, uint32_t n,
                                                                   uint32_t E, uint32_t vocab, float scale,
                                                                   float* __restrict__ out, uint32_t* flags) {
+  dyb_grid_dep_sync();
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t bars[kGatherWarps][2];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -126,6 +127,7 @@ __global__ void __launch_bounds__(kGatherWarps * 32) k_gather_bulk(const float* 
 __global__ void __launch_bounds__(256) k_gather_plain(const float* __restrict__ table, const uint32_t* __restrict__ ids,
                                                      uint32_t n, uint32_t E, uint32_t vocab, float scale,
                                                      float* __restrict__ out, uint32_t* flags, int vec) {
+  dyb_grid_dep_sync();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t nwarps = gridDim.x * 8;
   for (uint32_t b = blockIdx.x * 8 + warp; b < n; b += nwarps) {
@@ -152,6 +154,7 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_segments(const uint32_t* 
                                                                uint32_t* __restrict__ id_sorted,
                                                                uint32_t* __restrict__ seg_start,
                                                                uint32_t* __restrict__ nseg, uint32_t* flags) {
+  dyb_grid_dep_sync();
   __shared__ unsigned long long keys[kSortMax];
   __shared__ uint32_t scan[kSortThreads];
   uint32_t npow = 1;
@@ -177,6 +180,7 @@ __global__ void __launch_bounds__(256) k_segment_add(const float* __restrict__ g
                                                     const uint32_t* __restrict__ id_sorted,
                                                     const uint32_t* __restrict__ seg_start,
                                                     const uint32_t* __restrict__ nseg, uint32_t slices, int vec) {
+  dyb_grid_dep_sync();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t U = *nseg;
   const size_t work = (size_t)U * slices;
@@ -219,6 +223,7 @@ constexpr uint32_t kChunk = 32;
 __global__ void __launch_bounds__(kSortThreads) k_sort_ids(const uint32_t* __restrict__ ids, uint32_t n, uint32_t base,
                                                           uint32_t vocab, uint32_t* __restrict__ pos_sorted,
                                                           uint32_t* __restrict__ id_at, uint32_t* flags) {
+  dyb_grid_dep_sync();
   __shared__ unsigned long long keys[kSortMax];
   uint32_t npow = 1;
   while (npow < n) npow <<= 1;
@@ -247,6 +252,7 @@ __device__ __forceinline__ void add4(float4& a, const float4& b) { a.x += b.x; a
 __global__ void __launch_bounds__(256) k_chunk_add(const float* __restrict__ g, float* __restrict__ all_grads, uint32_t E,
                                                   const uint32_t* __restrict__ pos_sorted, const uint32_t* __restrict__ id_at,
                                                   uint32_t n, uint32_t slices, float* __restrict__ head, float* __restrict__ tail) {
+  dyb_grid_dep_sync();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t nchunks = (n + kChunk - 1) / kChunk;
   const size_t work = (size_t)nchunks * slices;
@@ -300,6 +306,7 @@ __global__ void __launch_bounds__(256) k_chunk_add(const float* __restrict__ g, 
 __global__ void __launch_bounds__(256) k_chunk_combine(float* __restrict__ all_grads, uint32_t E, const uint32_t* __restrict__ id_at,
                                                       uint32_t n, uint32_t slices, const float* __restrict__ head,
                                                       const float* __restrict__ tail) {
+  dyb_grid_dep_sync();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t nchunks = (n + kChunk - 1) / kChunk;
   const size_t work = (size_t)nchunks * slices;
@@ -336,12 +343,12 @@ static int scatter_run_chunked(dyb200_ctx* ctx, unsigned n, const unsigned* ids_
     uint32_t* id_at = pos_sorted + np;
     float* head = (float*)(((uintptr_t)(id_at + np) + 255) & ~(uintptr_t)255);
     float* tail = head + (size_t)nchunks * slices * 128;
-    k_sort_ids<<<1, kSortThreads, 0, ctx->stream>>>(ids_dev, np, base, vocab, pos_sorted, id_at, ctx->dev_flags);
+    dyb_launch(k_sort_ids, 1, kSortThreads, 0, ctx, ids_dev, np, base, vocab, pos_sorted, id_at, ctx->dev_flags);
     DYB_LAUNCHED(ctx);
     size_t work = (size_t)nchunks * slices;
-    k_chunk_add<<<stream_grid(ctx, work, 8), 256, 0, ctx->stream>>>(g, all_grads, E, pos_sorted, id_at, np, slices, head, tail);
+    dyb_launch(k_chunk_add, stream_grid(ctx, work, 8), 256, 0, ctx, g, all_grads, E, pos_sorted, id_at, np, slices, head, tail);
     DYB_LAUNCHED(ctx);
-    k_chunk_combine<<<stream_grid(ctx, work, 8), 256, 0, ctx->stream>>>(all_grads, E, id_at, np, slices, head, tail);
+    dyb_launch(k_chunk_combine, stream_grid(ctx, work, 8), 256, 0, ctx, all_grads, E, id_at, np, slices, head, tail);
     DYB_LAUNCHED(ctx);
   }
   return DYB200_OK;
@@ -361,10 +368,10 @@ int dyb200_lookup_scatter_run(dyb200_ctx* ctx, unsigned n, const unsigned* ids_d
     uint32_t* id_sorted = pos_sorted + np;
     uint32_t* seg_start = id_sorted + np;       // np + 1 entries
     uint32_t* nseg = seg_start + np + 1;
-    k_sort_segments<<<1, kSortThreads, 0, ctx->stream>>>(ids_dev, np, base, vocab, pos_sorted, id_sorted, seg_start, nseg, ctx->dev_flags);
+    dyb_launch(k_sort_segments, 1, kSortThreads, 0, ctx, ids_dev, np, base, vocab, pos_sorted, id_sorted, seg_start, nseg, ctx->dev_flags);
     DYB_LAUNCHED(ctx);
     size_t work = (size_t)np * slices;  // upper bound: every position its own segment
-    k_segment_add<<<stream_grid(ctx, work, 8), 256, 0, ctx->stream>>>(g, all_grads, E, pos_sorted, id_sorted, seg_start, nseg, slices, vec);
+    dyb_launch(k_segment_add, stream_grid(ctx, work, 8), 256, 0, ctx, g, all_grads, E, pos_sorted, id_sorted, seg_start, nseg, slices, vec);
     DYB_LAUNCHED(ctx);
   }
   return DYB200_OK;
@@ -434,9 +441,9 @@ int dyb200_lookup_fwd(DYB200_FWD_ARGS) {
       attr_set = true;
     }
     unsigned grid = stream_grid(ctx, n, kGatherWarps, 3);
-    k_gather_bulk<<<grid, kGatherWarps * 32, smem, ctx->stream>>>(a->all_values, ids_dev, n, E, a->vocab, a->weight_decay_scale, fx->v, ctx->dev_flags);
+    dyb_launch(k_gather_bulk, grid, kGatherWarps * 32, smem, ctx, a->all_values, ids_dev, n, E, a->vocab, a->weight_decay_scale, fx->v, ctx->dev_flags);
   } else {
-    k_gather_plain<<<stream_grid(ctx, n, 8), 256, 0, ctx->stream>>>(a->all_values, ids_dev, n, E, a->vocab, a->weight_decay_scale, fx->v, ctx->dev_flags, al ? 1 : 0);
+    dyb_launch(k_gather_plain, stream_grid(ctx, n, 8), 256, 0, ctx, a->all_values, ids_dev, n, E, a->vocab, a->weight_decay_scale, fx->v, ctx->dev_flags, al ? 1 : 0);
   }
   DYB_LAUNCHED(ctx);
   return DYB200_OK;

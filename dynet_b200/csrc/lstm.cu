@@ -21,6 +21,7 @@ __device__ __forceinline__ float gate_deriv(float g, float d, bool is_tanh) {
 }
 __global__ void __launch_bounds__(kThreads) k_gate_deriv(const float* __restrict__ fx, const float* __restrict__ dEdf,
                                                         float* __restrict__ dg, uint32_t H, size_t total, int vec) {
+  dyb_grid_dep_sync();
   const uint32_t G = 4 * H;
   if (vec) {
     size_t n4 = total / 4;
@@ -46,6 +47,7 @@ struct GateDerivSum {  // db[r] += sum_b dgate[r, b]
 // weightnoise_std > 0: the reference skips both products, so the output is act(bias) only.
 __global__ void __launch_bounds__(kThreads) k_gates_bias_only(const float* __restrict__ bias, float* __restrict__ fx,
                                                              uint32_t H, size_t total, float forget_bias) {
+  dyb_grid_dep_sync();
   const uint32_t G = 4 * H;
   for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (size_t)gridDim.x * kThreads) {
     uint32_t r = (uint32_t)(i % G);
@@ -57,6 +59,7 @@ __global__ void __launch_bounds__(kThreads) k_gates_bias_only(const float* __res
 // Concatenate k inputs along dim 0 into one I x B matrix (only used when k > 1).
 __global__ void __launch_bounds__(kThreads) k_concat_rows(const float* __restrict__ src, uint32_t d, uint32_t off,
                                                          uint32_t I, uint32_t B, float* __restrict__ dst) {
+  dyb_grid_dep_sync();
   size_t total = (size_t)d * B;
   for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < total; e += (size_t)gridDim.x * kThreads) {
     size_t b = e / d, r = e % d;
@@ -70,6 +73,7 @@ __global__ void __launch_bounds__(kThreads) k_concat_rows(const float* __restric
 template <int MODE, int VEC>
 __global__ void __launch_bounds__(kThreads) k_lstm_ch_fwd(const float* __restrict__ st, const float* __restrict__ gates,
                                                          float* __restrict__ out, uint32_t H, size_t total) {
+  dyb_grid_dep_sync();
   constexpr int W = VEC ? 4 : 1;
   for (size_t e = ((size_t)blockIdx.x * kThreads + threadIdx.x) * W; e < total; e += (size_t)gridDim.x * kThreads * W) {
     size_t b = e / H, j = e % H;
@@ -96,6 +100,7 @@ template <int NODE, int VEC>
 __global__ void __launch_bounds__(kThreads) k_lstm_ch_bwd(const float* __restrict__ st, const float* __restrict__ gates,
                                                          const float* __restrict__ d, unsigned i,
                                                          float* __restrict__ dxi, uint32_t H, size_t total) {
+  dyb_grid_dep_sync();
   constexpr int W = VEC ? 4 : 1;
   for (size_t e = ((size_t)blockIdx.x * kThreads + threadIdx.x) * W; e < total; e += (size_t)gridDim.x * kThreads * W) {
     size_t b = e / H, j = e % H;
@@ -127,6 +132,7 @@ template <int VEC>
 __global__ void __launch_bounds__(kThreads) k_lstm_cell_fwd(const float* __restrict__ c_tm1, const float* __restrict__ gates,
                                                            float* __restrict__ c_t, float* __restrict__ h_t, uint32_t H,
                                                            size_t total) {
+  dyb_grid_dep_sync();
   constexpr int W = VEC ? 4 : 1;
   for (size_t e = ((size_t)blockIdx.x * kThreads + threadIdx.x) * W; e < total; e += (size_t)gridDim.x * kThreads * W) {
     size_t b = e / H, j = e % H;
@@ -156,6 +162,7 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd(const float* __restrict__
                                                       const float* __restrict__ gates, const float* __restrict__ dEdh,
                                                       const float* __restrict__ dEdc, float* __restrict__ dc_tm1,
                                                       float* __restrict__ dpre, float* __restrict__ db, uint32_t H, uint32_t B) {
+  dyb_grid_dep_sync();
   __shared__ float red[8][4][kJT];
   const int jj = threadIdx.x % kJT, bl = threadIdx.x / kJT;   // 32 batch lanes
   const uint32_t j = blockIdx.x * kJT + jj;
@@ -211,6 +218,7 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __rest
                                                             uint32_t dn_pitch, float* __restrict__ dt_hi, float* __restrict__ dt_lo,
                                                             uint32_t dt_pitch, float* __restrict__ db, float* __restrict__ part,
                                                             uint32_t* __restrict__ counters, uint32_t H, uint32_t B) {
+  dyb_grid_dep_sync();
   __shared__ float tile[4][kCT_J][kCT_B + 1];
   __shared__ uint32_t is_last;
   const uint32_t j0 = blockIdx.x * kCT_J, b0 = blockIdx.y * kCT_B;
@@ -358,7 +366,7 @@ int gather_x(dyb200_ctx* ctx, const dyb200_tensor* xs, const GatesArgs& g, float
   for (unsigned j = 0; j < g.k; ++j) {
     size_t total = (size_t)xs[j].d[0] * g.B;
     if (total) {
-      k_concat_rows<<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(xs[j].v, xs[j].d[0], off, g.I, g.B, scratch);
+      dyb_launch(k_concat_rows, stream_grid(ctx, total, kThreads), kThreads, 0, ctx, xs[j].v, xs[j].d[0], off, g.I, g.B, scratch);
       DYB_LAUNCHED(ctx);
     }
     off += xs[j].d[0];
@@ -384,8 +392,8 @@ int ch_fwd(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, dyb200_tensor* fx,
   DYB_CHECK_ARG(ctx, t_size(fx) == total, "%s: output size mismatch", name);
   if (total == 0) return DYB200_OK;
   bool vec = H % 4 == 0 && aligned16(xs[0].v) && aligned16(xs[1].v) && aligned16(fx->v);
-  if (vec) k_lstm_ch_fwd<MODE, 1><<<stream_grid(ctx, total / 4, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, xs[1].v, fx->v, H, total);
-  else k_lstm_ch_fwd<MODE, 0><<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, xs[1].v, fx->v, H, total);
+  if (vec) dyb_launch(k_lstm_ch_fwd<MODE, 1>, stream_grid(ctx, total / 4, kThreads), kThreads, 0, ctx, xs[0].v, xs[1].v, fx->v, H, total);
+  else dyb_launch(k_lstm_ch_fwd<MODE, 0>, stream_grid(ctx, total, kThreads), kThreads, 0, ctx, xs[0].v, xs[1].v, fx->v, H, total);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -399,8 +407,8 @@ int ch_bwd(dyb200_ctx* ctx, const dyb200_tensor* xs, int nxs, const dyb200_tenso
   size_t total = (size_t)H * xs[0].bd;
   DYB_CHECK_ARG(ctx, t_size(dEdf) == total && t_size(dEdxi) == (i == 0 ? total : 4 * total), "%s::backward: size mismatch", name);
   if (total == 0) return DYB200_OK;
-  if (H % 4 == 0) k_lstm_ch_bwd<NODE, 1><<<stream_grid(ctx, total / 4, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, xs[1].v, dEdf->v, i, dEdxi->v, H, total);
-  else k_lstm_ch_bwd<NODE, 0><<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(xs[0].v, xs[1].v, dEdf->v, i, dEdxi->v, H, total);
+  if (H % 4 == 0) dyb_launch(k_lstm_ch_bwd<NODE, 1>, stream_grid(ctx, total / 4, kThreads), kThreads, 0, ctx, xs[0].v, xs[1].v, dEdf->v, i, dEdxi->v, H, total);
+  else dyb_launch(k_lstm_ch_bwd<NODE, 0>, stream_grid(ctx, total, kThreads), kThreads, 0, ctx, xs[0].v, xs[1].v, dEdf->v, i, dEdxi->v, H, total);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -422,7 +430,7 @@ int dyb200_vanilla_lstm_gates_fwd(DYB200_FWD_ARGS) {
   if (a->weightnoise_std > 0.f) {
     // Reference behaviour (dynet/nodes-lstm.cc:200-219): the noisy copies are built and never used.
     size_t total = (size_t)G * g.B;
-    k_gates_bias_only<<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(g.b->v, fx->v, g.H, total, a->forget_gate_bias);
+    dyb_launch(k_gates_bias_only, stream_grid(ctx, total, kThreads), kThreads, 0, ctx, g.b->v, fx->v, g.H, total, a->forget_gate_bias);
     DYB_LAUNCHED(ctx);
     return DYB200_OK;
   }
@@ -466,7 +474,7 @@ int dyb200_vanilla_lstm_gates_bwd(DYB200_BWD_ARGS) {
   if (rc) return rc;
   float* dg = (float*)scratch;
   int vec = g.H % 4 == 0 && aligned16(fx->v) && aligned16(dEdf->v);
-  k_gate_deriv<<<stream_grid(ctx, vec ? total / 4 : total, kThreads), kThreads, 0, ctx->stream>>>(fx->v, dEdf->v, dg, g.H, total, vec);
+  dyb_launch(k_gate_deriv, stream_grid(ctx, vec ? total / 4 : total, kThreads), kThreads, 0, ctx, fx->v, dEdf->v, dg, g.H, total, vec);
   DYB_LAUNCHED(ctx);
   if (i < g.k) {  // dx_i = Wx[:, slice_i]^T dgate (.* mask slice)
     uint32_t off = 0, di = xs[i].d[0];
@@ -550,8 +558,8 @@ int dyb200_vanilla_lstm_fwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
   if (rc) return rc;
   if (total == 0) return DYB200_OK;
   bool vec = H % 4 == 0 && aligned16(c_tm1->v) && aligned16(gates->v) && aligned16(c_t->v) && aligned16(h_t->v);
-  if (vec) k_lstm_cell_fwd<1><<<stream_grid(ctx, total / 4, kThreads), kThreads, 0, ctx->stream>>>(c_tm1->v, gates->v, c_t->v, h_t->v, H, total);
-  else k_lstm_cell_fwd<0><<<stream_grid(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(c_tm1->v, gates->v, c_t->v, h_t->v, H, total);
+  if (vec) dyb_launch(k_lstm_cell_fwd<1>, stream_grid(ctx, total / 4, kThreads), kThreads, 0, ctx, c_tm1->v, gates->v, c_t->v, h_t->v, H, total);
+  else dyb_launch(k_lstm_cell_fwd<0>, stream_grid(ctx, total, kThreads), kThreads, 0, ctx, c_tm1->v, gates->v, c_t->v, h_t->v, H, total);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -603,7 +611,7 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
     }
     void* pp;
     if ((rc = dyb200_scratch(ctx, (size_t)(B / kCT_B) * G * sizeof(float), &pp))) return rc;
-    k_lstm_cell_bwd_tiled<<<dim3(H / kCT_J, B / kCT_B), 256, 0, ctx->stream>>>(
+    dyb_launch(k_lstm_cell_bwd_tiled, dim3(H / kCT_J, B / kCT_B), 256, 0, ctx, 
         c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr, dc_tm1 ? dc_tm1->v : nullptr, nullptr, dn.hi, dn.lo, dn.pitch,
         a_hi, a_lo, a_pitch, db->v, (float*)pp, ctx->dev_flags + DYB200_DEV_COUNTER0, H, B);
     DYB_LAUNCHED(ctx);
@@ -611,7 +619,7 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
     void* sp;
     if ((rc = dyb200_scratch(ctx, 4 * HB * sizeof(float), &sp))) return rc;
     dpre = (float*)sp;
-    k_lstm_cell_bwd<<<(H + kJT - 1) / kJT, 256, 0, ctx->stream>>>(c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr,
+    dyb_launch(k_lstm_cell_bwd, (H + kJT - 1) / kJT, 256, 0, ctx, c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr,
                                                                 dc_tm1 ? dc_tm1->v : nullptr, dpre, db->v, H, B);
     DYB_LAUNCHED(ctx);
     if (deferred) {

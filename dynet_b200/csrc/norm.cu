@@ -15,6 +15,7 @@ constexpr int kColMax = kBlock * 4 * kVec;
 // partial[2*blk] = sum w^2 ; partial[2*blk+1] = sum w*d (d may be null)
 __global__ void __launch_bounds__(kBlock) k_sumsq_dot_partial(const float* __restrict__ w, const float* __restrict__ d,
                                                              size_t n, float* __restrict__ partial) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   float ss = 0.f, dot = 0.f;
   const bool vec = aligned16(w) && (d == nullptr || aligned16(d));
@@ -52,6 +53,7 @@ __global__ void __launch_bounds__(kBlock) k_weight_norm_apply(const float* __res
                                                              const float* __restrict__ y, const float* __restrict__ dy,
                                                              float* __restrict__ out, size_t n,
                                                              const float* __restrict__ partial, int np) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   float ss, dot;
   reduce_partials(partial, np, red, ss, dot);
@@ -74,6 +76,7 @@ __global__ void __launch_bounds__(kBlock) k_weight_norm_apply(const float* __res
   }
 }
 __global__ void __launch_bounds__(kBlock) k_weight_norm_dg(const float* __restrict__ partial, int np, float* __restrict__ dg) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   float ss, dot;
   reduce_partials(partial, np, red, ss, dot);
@@ -94,6 +97,7 @@ __device__ __forceinline__ float mpow(float v, uint32_t order) {
 template <int MODE>
 __global__ void __launch_bounds__(kBlock) k_moment_generic(const float* __restrict__ x, Axes ax, uint32_t order, float n,
                                                           float* __restrict__ out, size_t nout) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   for (size_t o = blockIdx.x; o < nout; o += gridDim.x) {
     // base offset of this output element
@@ -134,6 +138,7 @@ __global__ void __launch_bounds__(kBlock) k_moment_bwd_generic(const float* __re
                                                               const float* __restrict__ fx, const float* __restrict__ dE,
                                                               const float* __restrict__ mean, float* __restrict__ dx,
                                                               size_t total) {
+  dyb_grid_dep_sync();
   for (size_t e = (size_t)blockIdx.x * kBlock + threadIdx.x; e < total; e += (size_t)gridDim.x * kBlock) {
     size_t t = e, o = 0, ostride = 1;
     for (int k = 0; k < 4; ++k) {
@@ -196,6 +201,7 @@ __device__ __forceinline__ void ln_stats(LnLoad& L, float* red, float& mean, flo
 __global__ void __launch_bounds__(kBlock) k_layer_norm_fwd(const float* __restrict__ x, const float* __restrict__ g,
                                                           const float* __restrict__ b, float* __restrict__ y,
                                                           uint32_t n, size_t ncols, int cached) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   for (size_t c = blockIdx.x; c < ncols; c += gridDim.x) {
     LnLoad L;
@@ -226,6 +232,7 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_fwd(const float* __restri
 __global__ void __launch_bounds__(kBlock) k_layer_norm_bwd_x(const float* __restrict__ x, const float* __restrict__ g,
                                                             const float* __restrict__ dy, float* __restrict__ dx,
                                                             uint32_t n, size_t ncols, int cached) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   const float fn = (float)n;
   for (size_t c = blockIdx.x; c < ncols; c += gridDim.x) {
@@ -284,6 +291,7 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_bwd_x(const float* __rest
 
 __global__ void __launch_bounds__(kBlock) k_layer_norm_stats(const float* __restrict__ x, float* __restrict__ stats,
                                                             uint32_t n, size_t ncols, int cached) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   for (size_t c = blockIdx.x; c < ncols; c += gridDim.x) {
     LnLoad L;
@@ -358,9 +366,9 @@ int dyb200_weight_norm_fwd(DYB200_FWD_ARGS) {
   void* partial;
   int rc = dyb200_scratch(ctx, 2 * np * sizeof(float), &partial);
   if (rc) return rc;
-  k_sumsq_dot_partial<<<np, kBlock, 0, ctx->stream>>>(xs[0].v, nullptr, n, (float*)partial);
+  dyb_launch(k_sumsq_dot_partial, np, kBlock, 0, ctx, xs[0].v, nullptr, n, (float*)partial);
   DYB_LAUNCHED(ctx);
-  k_weight_norm_apply<0><<<stream_grid(ctx, n, kBlock * 4), kBlock, 0, ctx->stream>>>(xs[0].v, xs[1].v, nullptr, nullptr, fx->v, n, (const float*)partial, np);
+  dyb_launch(k_weight_norm_apply<0>, stream_grid(ctx, n, kBlock * 4), kBlock, 0, ctx, xs[0].v, xs[1].v, nullptr, nullptr, fx->v, n, (const float*)partial, np);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -376,10 +384,10 @@ int dyb200_weight_norm_bwd(DYB200_BWD_ARGS) {
   void* partial;
   int rc = dyb200_scratch(ctx, 2 * np * sizeof(float), &partial);
   if (rc) return rc;
-  k_sumsq_dot_partial<<<np, kBlock, 0, ctx->stream>>>(xs[0].v, dEdf->v, n, (float*)partial);
+  dyb_launch(k_sumsq_dot_partial, np, kBlock, 0, ctx, xs[0].v, dEdf->v, n, (float*)partial);
   DYB_LAUNCHED(ctx);
-  if (i == 0) k_weight_norm_apply<1><<<stream_grid(ctx, n, kBlock * 4), kBlock, 0, ctx->stream>>>(xs[0].v, xs[1].v, fx->v, dEdf->v, dEdxi->v, n, (const float*)partial, np);
-  else k_weight_norm_dg<<<1, kBlock, 0, ctx->stream>>>((const float*)partial, np, dEdxi->v);
+  if (i == 0) dyb_launch(k_weight_norm_apply<1>, stream_grid(ctx, n, kBlock * 4), kBlock, 0, ctx, xs[0].v, xs[1].v, fx->v, dEdf->v, dEdxi->v, n, (const float*)partial, np);
+  else dyb_launch(k_weight_norm_dg, 1, kBlock, 0, ctx, (const float*)partial, np, dEdxi->v);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -394,7 +402,7 @@ int dyb200_moment_dim_fwd(DYB200_FWD_ARGS) {
   DYB_CHECK_ARG(ctx, a->order >= 1, "Order of moment should be >=1 in MomentDimension (received %u)", a->order);
   DYB_CHECK_ARG(ctx, t_size(fx) == nout, "MomentDimension: output size mismatch");
   if (nout == 0) return DYB200_OK;
-  k_moment_generic<0><<<stream_grid(ctx, nout, 1), kBlock, 0, ctx->stream>>>(xs[0].v, ax, a->order, n, fx->v, nout);
+  dyb_launch(k_moment_generic<0>, stream_grid(ctx, nout, 1), kBlock, 0, ctx, xs[0].v, ax, a->order, n, fx->v, nout);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -409,7 +417,7 @@ int dyb200_moment_dim_bwd(DYB200_BWD_ARGS) {
   size_t total = t_size(&xs[0]);
   DYB_CHECK_ARG(ctx, t_size(dEdf) == nout && t_size(dEdxi) == total, "MomentDimension::backward: size mismatch");
   if (total == 0) return DYB200_OK;
-  k_moment_bwd_generic<0><<<stream_grid(ctx, total, kBlock), kBlock, 0, ctx->stream>>>(xs[0].v, ax, a->order, n, nullptr, dEdf->v, nullptr, dEdxi->v, total);
+  dyb_launch(k_moment_bwd_generic<0>, stream_grid(ctx, total, kBlock), kBlock, 0, ctx, xs[0].v, ax, a->order, n, nullptr, dEdf->v, nullptr, dEdxi->v, total);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -422,7 +430,7 @@ int dyb200_std_dim_fwd(DYB200_FWD_ARGS) {
   if (rc) return rc;
   DYB_CHECK_ARG(ctx, t_size(fx) == nout, "StdDimension: output size mismatch");
   if (nout == 0) return DYB200_OK;
-  k_moment_generic<1><<<stream_grid(ctx, nout, 1), kBlock, 0, ctx->stream>>>(xs[0].v, ax, 2, n, fx->v, nout);
+  dyb_launch(k_moment_generic<1>, stream_grid(ctx, nout, 1), kBlock, 0, ctx, xs[0].v, ax, 2, n, fx->v, nout);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -441,9 +449,9 @@ int dyb200_std_dim_bwd(DYB200_BWD_ARGS) {
   void* mean;
   rc = dyb200_scratch(ctx, nout * sizeof(float), &mean);
   if (rc) return rc;
-  k_moment_generic<0><<<stream_grid(ctx, nout, 1), kBlock, 0, ctx->stream>>>(xs[0].v, ax, 1, n, (float*)mean, nout);
+  dyb_launch(k_moment_generic<0>, stream_grid(ctx, nout, 1), kBlock, 0, ctx, xs[0].v, ax, 1, n, (float*)mean, nout);
   DYB_LAUNCHED(ctx);
-  k_moment_bwd_generic<1><<<stream_grid(ctx, total, kBlock), kBlock, 0, ctx->stream>>>(xs[0].v, ax, 2, n, fx->v, dEdf->v, (const float*)mean, dEdxi->v, total);
+  dyb_launch(k_moment_bwd_generic<1>, stream_grid(ctx, total, kBlock), kBlock, 0, ctx, xs[0].v, ax, 2, n, fx->v, dEdf->v, (const float*)mean, dEdxi->v, total);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -456,7 +464,7 @@ int dyb200_layer_norm_fwd(DYB200_FWD_ARGS) {
   DYB_CHECK_ARG(ctx, t_size(fx) == n * ncols, "layer_norm: output size mismatch");
   if (n * ncols == 0) return DYB200_OK;
   cached = cached && aligned16(fx->v);
-  k_layer_norm_fwd<<<stream_grid(ctx, ncols, 1), kBlock, 0, ctx->stream>>>(xs[0].v, xs[1].v, xs[2].v, fx->v, (uint32_t)n, ncols, cached);
+  dyb_launch(k_layer_norm_fwd, stream_grid(ctx, ncols, 1), kBlock, 0, ctx, xs[0].v, xs[1].v, xs[2].v, fx->v, (uint32_t)n, ncols, cached);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -472,7 +480,7 @@ int dyb200_layer_norm_bwd(DYB200_BWD_ARGS) {
   if (n * ncols == 0) return DYB200_OK;
   if (i == 0) {
     cached = cached && aligned16(dEdf->v) && aligned16(dEdxi->v);
-    k_layer_norm_bwd_x<<<stream_grid(ctx, ncols, 1), kBlock, 0, ctx->stream>>>(xs[0].v, xs[1].v, dEdf->v, dEdxi->v, (uint32_t)n, ncols, cached);
+    dyb_launch(k_layer_norm_bwd_x, stream_grid(ctx, ncols, 1), kBlock, 0, ctx, xs[0].v, xs[1].v, dEdf->v, dEdxi->v, (uint32_t)n, ncols, cached);
     DYB_LAUNCHED(ctx);
     return DYB200_OK;
   }
@@ -485,7 +493,7 @@ int dyb200_layer_norm_bwd(DYB200_BWD_ARGS) {
   rc = dyb200_scratch(ctx, 2 * ncols * sizeof(float), &arena);
   if (rc) return rc;
   float* stats = (float*)arena;
-  k_layer_norm_stats<<<stream_grid(ctx, ncols, 1), kBlock, 0, ctx->stream>>>(xs[0].v, stats, (uint32_t)n, ncols, cached);
+  dyb_launch(k_layer_norm_stats, stream_grid(ctx, ncols, 1), kBlock, 0, ctx, xs[0].v, stats, (uint32_t)n, ncols, cached);
   DYB_LAUNCHED(ctx);
   LnDg f{xs[0].v, dEdf->v, stats, n};
   return batch_reduce_add(ctx, f, n, (uint32_t)ncols, dEdxi->v);

@@ -15,6 +15,7 @@ constexpr int kThreads = 128;
 
 __global__ void __launch_bounds__(kThreads) k_ragged_copy(int num_seqs, float* const* __restrict__ src,
                                                          float* const* __restrict__ trg, const size_t* __restrict__ len) {
+  dyb_grid_dep_sync();
   for (int s = blockIdx.x; s < num_seqs; s += gridDim.x) {
     const float* a = src[s];
     float* b = trg[s];
@@ -34,6 +35,7 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_targets(float* const* __r
                                                               uint32_t* __restrict__ slice_sorted,
                                                               uint32_t* __restrict__ group_sorted,
                                                               uint32_t* __restrict__ seg_start, uint32_t* __restrict__ nseg) {
+  dyb_grid_dep_sync();
   __shared__ unsigned long long keys[kSortMax];
   __shared__ uint32_t scan[kSortThreads];
   uint32_t npow = 1;
@@ -52,6 +54,7 @@ __global__ void __launch_bounds__(kThreads) k_ragged_accumulate(float* const* __
                                                                const uint32_t* __restrict__ slice_sorted,
                                                                const uint32_t* __restrict__ seg_start,
                                                                const uint32_t* __restrict__ nseg) {
+  dyb_grid_dep_sync();
   const uint32_t U = *nseg;
   for (uint32_t u = blockIdx.x; u < U; u += gridDim.x) {
     const uint32_t k0 = seg_start[u], k1 = seg_start[u + 1];
@@ -97,7 +100,7 @@ int dyb200_parallel_memcpy(int num_seqs, int max_len, float** src, float** trg, 
   DYB_CHECK_ARG(ctx, num_seqs >= 0, "parallel_memcpy: negative slice count");
   if (num_seqs == 0) return DYB200_OK;
   DYB_CHECK_ARG(ctx, src && trg && len, "parallel_memcpy: null table");
-  k_ragged_copy<<<stream_grid(ctx, (size_t)num_seqs, 1, 16), kThreads, 0, ctx->stream>>>(num_seqs, src, trg, len);
+  dyb_launch(k_ragged_copy, stream_grid(ctx, (size_t)num_seqs, 1, 16), kThreads, 0, ctx, num_seqs, src, trg, len);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -118,9 +121,9 @@ int dyb200_parallel_accumulate(int num_seqs, int max_len, float** src, float** t
     uint32_t* group_sorted = slice_sorted + n;
     uint32_t* seg_start = group_sorted + n;
     uint32_t* nseg = seg_start + n + 1;
-    k_sort_targets<<<1, kSortThreads, 0, ctx->stream>>>(trg, n, base, slice_sorted, group_sorted, seg_start, nseg);
+    dyb_launch(k_sort_targets, 1, kSortThreads, 0, ctx, trg, n, base, slice_sorted, group_sorted, seg_start, nseg);
     DYB_LAUNCHED(ctx);
-    k_ragged_accumulate<<<stream_grid(ctx, n, 1, 16), kThreads, 0, ctx->stream>>>(src, trg, len, base, slice_sorted, seg_start, nseg);
+    dyb_launch(k_ragged_accumulate, stream_grid(ctx, n, 1, 16), kThreads, 0, ctx, src, trg, len, base, slice_sorted, seg_start, nseg);
     DYB_LAUNCHED(ctx);
   }
   return DYB200_OK;

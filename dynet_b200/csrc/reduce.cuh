@@ -8,6 +8,7 @@ template <class F>
 __global__ void __launch_bounds__(128) k_batch_reduce_partial(F f, size_t n, uint32_t B, uint32_t chunk,
                                                              float* __restrict__ partial,
                                                              float* __restrict__ out, int direct) {
+  dyb_grid_dep_sync();
   size_t r = (size_t)blockIdx.x * 128 + threadIdx.x;
   if (r >= n) return;
   uint32_t b0 = blockIdx.y * chunk, b1 = min(B, b0 + chunk);
@@ -27,6 +28,7 @@ __global__ void __launch_bounds__(128) k_batch_reduce_partial(F f, size_t n, uin
 
 static __global__ void __launch_bounds__(128) k_batch_reduce_final(const float* __restrict__ partial, uint32_t S,
                                                                    size_t n, float* __restrict__ out) {
+  dyb_grid_dep_sync();
   size_t r = (size_t)blockIdx.x * 128 + threadIdx.x;
   if (r >= n) return;
   float acc = 0.f;
@@ -45,16 +47,16 @@ static int batch_reduce_add(dyb200_ctx* ctx, F f, size_t n, uint32_t B, float* o
   uint32_t chunk = (B + S - 1) / S;
   S = (B + chunk - 1) / chunk;
   if (S == 1) {
-    k_batch_reduce_partial<<<dim3(gx, 1), 128, 0, ctx->stream>>>(f, n, B, chunk, nullptr, out, 1);
+    dyb_launch(k_batch_reduce_partial<F>, dim3(gx, 1), 128, 0, ctx, f, n, B, chunk, nullptr, out, 1);
     DYB_LAUNCHED(ctx);
     return DYB200_OK;
   }
   void* scratch = nullptr;
   int rc = dyb200_scratch(ctx, (size_t)S * n * sizeof(float), &scratch);
   if (rc) return rc;
-  k_batch_reduce_partial<<<dim3(gx, S), 128, 0, ctx->stream>>>(f, n, B, chunk, (float*)scratch, out, 0);
+  dyb_launch(k_batch_reduce_partial<F>, dim3(gx, S), 128, 0, ctx, f, n, B, chunk, (float*)scratch, out, 0);
   DYB_LAUNCHED(ctx);
-  k_batch_reduce_final<<<gx, 128, 0, ctx->stream>>>((const float*)scratch, S, n, out);
+  dyb_launch(k_batch_reduce_final, gx, 128, 0, ctx, (const float*)scratch, S, n, out);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }

@@ -49,6 +49,7 @@ __device__ __forceinline__ void finish_column(const ColArgs& a, size_t c, float 
 // ---- warp per column, rows <= 256 ------------------------------------------
 template <int MODE>
 __global__ void __launch_bounds__(kBlock) k_col_warp(ColArgs a) {
+  dyb_grid_dep_sync();
   const int lane = threadIdx.x & 31;
   const size_t warps = (size_t)gridDim.x * (kBlock / 32);
   for (size_t c = (size_t)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); c < a.ncols; c += warps) {
@@ -87,6 +88,7 @@ __global__ void __launch_bounds__(kBlock) k_col_warp(ColArgs a) {
 // ---- CTA per column, rows <= 4096, 16-byte aligned columns --------------------
 template <int MODE>
 __global__ void __launch_bounds__(kBlock) k_col_block_vec(ColArgs a) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   const uint32_t rows4 = a.rows / 4;
   for (size_t c = blockIdx.x; c < a.ncols; c += gridDim.x) {
@@ -152,6 +154,7 @@ __device__ __forceinline__ float sumexp4(float4 v, float ml) {
 }
 template <int MODE>
 __global__ void __launch_bounds__(kBlock) k_col_stream(ColArgs a) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   for (size_t c = blockIdx.x; c < a.ncols; c += gridDim.x) {
     const float* xc = a.x + c * a.rows;
@@ -198,11 +201,11 @@ int run_columns(dyb200_ctx* ctx, ColArgs a) {
   if (a.ncols == 0 || a.rows == 0) return DYB200_OK;
   a.flags = ctx->dev_flags;
   if (a.rows <= kWarpRowsMax) {
-    k_col_warp<MODE><<<stream_grid(ctx, a.ncols, kBlock / 32), kBlock, 0, ctx->stream>>>(a);
+    dyb_launch(k_col_warp<MODE>, stream_grid(ctx, a.ncols, kBlock / 32), kBlock, 0, ctx, a);
   } else if (a.rows <= kBlockRowsMax && a.rows % 4 == 0 && aligned16(a.x) && (a.y == nullptr || aligned16(a.y))) {
-    k_col_block_vec<MODE><<<stream_grid(ctx, a.ncols, 1), kBlock, 0, ctx->stream>>>(a);
+    dyb_launch(k_col_block_vec<MODE>, stream_grid(ctx, a.ncols, 1), kBlock, 0, ctx, a);
   } else {
-    k_col_stream<MODE><<<stream_grid(ctx, a.ncols, 1), kBlock, 0, ctx->stream>>>(a);
+    dyb_launch(k_col_stream<MODE>, stream_grid(ctx, a.ncols, 1), kBlock, 0, ctx, a);
   }
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
@@ -213,6 +216,7 @@ int run_columns(dyb200_ctx* ctx, ColArgs a) {
 template <bool LOGSM>
 __global__ void __launch_bounds__(kBlock) k_col_bwd(const float* __restrict__ y, const float* __restrict__ dy,
                                                    float* __restrict__ dx, uint32_t rows, size_t ncols) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   for (size_t c = blockIdx.x; c < ncols; c += gridDim.x) {
     const float *yc = y + c * rows, *dc = dy + c * rows;
@@ -228,6 +232,7 @@ __global__ void __launch_bounds__(kBlock) k_col_bwd(const float* __restrict__ y,
 template <bool LOGSM>
 __global__ void __launch_bounds__(kBlock) k_col_bwd_warp(const float* __restrict__ y, const float* __restrict__ dy,
                                                         float* __restrict__ dx, uint32_t rows, size_t ncols) {
+  dyb_grid_dep_sync();
   const int lane = threadIdx.x & 31;
   const size_t warps = (size_t)gridDim.x * (kBlock / 32);
   for (size_t c = (size_t)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); c < ncols; c += warps) {
@@ -244,6 +249,7 @@ __global__ void __launch_bounds__(kBlock) k_col_bwd_warp(const float* __restrict
 template <bool LOGSM>
 __global__ void __launch_bounds__(kBlock) k_col_bwd_vec(const float* __restrict__ y, const float* __restrict__ dy,
                                                        float* __restrict__ dx, uint32_t rows, size_t ncols) {
+  dyb_grid_dep_sync();
   __shared__ float red[32];
   const uint32_t rows4 = rows / 4;
   for (size_t c = blockIdx.x; c < ncols; c += gridDim.x) {
@@ -279,10 +285,10 @@ __global__ void __launch_bounds__(kBlock) k_col_bwd_vec(const float* __restrict_
 template <bool LOGSM>
 int run_col_bwd(dyb200_ctx* ctx, const float* y, const float* dy, float* dx, uint32_t rows, size_t ncols) {
   if (rows == 0 || ncols == 0) return DYB200_OK;
-  if (rows <= 128) k_col_bwd_warp<LOGSM><<<stream_grid(ctx, ncols, kBlock / 32), kBlock, 0, ctx->stream>>>(y, dy, dx, rows, ncols);
+  if (rows <= 128) dyb_launch(k_col_bwd_warp<LOGSM>, stream_grid(ctx, ncols, kBlock / 32), kBlock, 0, ctx, y, dy, dx, rows, ncols);
   else if (rows <= kBlockRowsMax && rows % 4 == 0 && aligned16(y) && aligned16(dy) && aligned16(dx))
-    k_col_bwd_vec<LOGSM><<<stream_grid(ctx, ncols, 1), kBlock, 0, ctx->stream>>>(y, dy, dx, rows, ncols);
-  else k_col_bwd<LOGSM><<<stream_grid(ctx, ncols, 1), kBlock, 0, ctx->stream>>>(y, dy, dx, rows, ncols);
+    dyb_launch(k_col_bwd_vec<LOGSM>, stream_grid(ctx, ncols, 1), kBlock, 0, ctx, y, dy, dx, rows, ncols);
+  else dyb_launch(k_col_bwd<LOGSM>, stream_grid(ctx, ncols, 1), kBlock, 0, ctx, y, dy, dx, rows, ncols);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -293,6 +299,7 @@ __global__ void __launch_bounds__(kBlock) k_expsub_bwd(const float* __restrict__
                                                       const float* __restrict__ dz, const uint32_t* __restrict__ ids,
                                                       float* __restrict__ dx, uint32_t rows, size_t ncols,
                                                       uint32_t chunks_per_col, uint32_t chunk, int vec) {
+  dyb_grid_dep_sync();
   size_t work = (size_t)ncols * chunks_per_col;
   for (size_t w = blockIdx.x; w < work; w += gridDim.x) {
     size_t c = w / chunks_per_col;
@@ -328,7 +335,7 @@ int run_expsub_bwd(dyb200_ctx* ctx, const float* x, const float* z, const float*
   int vec = rows % 4 == 0 && aligned16(x) && aligned16(dx);
   uint32_t chunk = 4 * kBlock * 4;  // 4096 rows per CTA pass
   uint32_t cpc = (rows + chunk - 1) / chunk;
-  k_expsub_bwd<<<stream_grid(ctx, ncols * cpc, 1), kBlock, 0, ctx->stream>>>(x, z, dz, ids, dx, rows, ncols, cpc, chunk, vec);
+  dyb_launch(k_expsub_bwd, stream_grid(ctx, ncols * cpc, 1), kBlock, 0, ctx, x, z, dz, ids, dx, rows, ncols, cpc, chunk, vec);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -353,6 +360,7 @@ template <int MODE>
 __global__ void __launch_bounds__(kRT * kCL) k_row(const float* __restrict__ x, const float* __restrict__ aux_in,
                                                   float* __restrict__ out, float* __restrict__ z_out,
                                                   uint32_t rows, uint32_t cols) {
+  dyb_grid_dep_sync();
   __shared__ float sm[kRT][kCL];
   const int ri = threadIdx.x % kRT, cj = threadIdx.x / kRT;
   const uint32_t r = blockIdx.x * kRT + ri;
@@ -430,6 +438,7 @@ struct NaryArgs {
   int k;
 };
 __global__ void __launch_bounds__(kBlock) k_lse_nary_fwd(NaryArgs a, float* __restrict__ y, size_t n, uint32_t bd) {
+  dyb_grid_dep_sync();
   size_t total = n * bd;
   for (size_t e = (size_t)blockIdx.x * kBlock + threadIdx.x; e < total; e += (size_t)gridDim.x * kBlock) {
     size_t r = e % n;
@@ -443,6 +452,7 @@ __global__ void __launch_bounds__(kBlock) k_lse_nary_fwd(NaryArgs a, float* __re
 __global__ void __launch_bounds__(kBlock) k_lse_nary_bwd(const float* __restrict__ xi, const float* __restrict__ y,
                                                         const float* __restrict__ dy, float* __restrict__ dxi,
                                                         size_t total, int identity) {
+  dyb_grid_dep_sync();
   for (size_t e = (size_t)blockIdx.x * kBlock + threadIdx.x; e < total; e += (size_t)gridDim.x * kBlock)
     dxi[e] += identity ? dy[e] : expf(xi[e] - y[e]) * dy[e];
 }
@@ -475,7 +485,7 @@ int dyb200_softmax_fwd(DYB200_FWD_ARGS) {
     ColArgs a{xs[0].v, fx->v, nullptr, nullptr, nullptr, nullptr, rows, (size_t)cols * bd, nullptr};
     return run_columns<M_SOFTMAX>(ctx, a);
   }
-  k_row<R_SOFTMAX><<<dim3((rows + kRT - 1) / kRT, bd), kRT * kCL, 0, ctx->stream>>>(xs[0].v, nullptr, fx->v, nullptr, rows, cols);
+  dyb_launch(k_row<R_SOFTMAX>, dim3((rows + kRT - 1) / kRT, bd), kRT * kCL, 0, ctx, xs[0].v, nullptr, fx->v, nullptr, rows, cols);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -488,7 +498,7 @@ int dyb200_softmax_bwd(DYB200_BWD_ARGS) {
   uint32_t rows = t_rows(fx), cols = t_cols(fx), bd = fx->bd;
   if (t_size(fx) == 0) return DYB200_OK;
   if (dimension == 0) return run_col_bwd<false>(ctx, fx->v, dEdf->v, dEdxi->v, rows, (size_t)cols * bd);
-  k_row<R_SOFTMAX_BWD><<<dim3((rows + kRT - 1) / kRT, bd), kRT * kCL, 0, ctx->stream>>>(fx->v, dEdf->v, dEdxi->v, nullptr, rows, cols);
+  dyb_launch(k_row<R_SOFTMAX_BWD>, dim3((rows + kRT - 1) / kRT, bd), kRT * kCL, 0, ctx, fx->v, dEdf->v, dEdxi->v, nullptr, rows, cols);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -525,7 +535,7 @@ int dyb200_logsumexp_dim_fwd(DYB200_FWD_ARGS) {
     ColArgs a{xs[0].v, nullptr, fx->v, nullptr, nullptr, nullptr, rows, (size_t)cols * bd, nullptr};
     return run_columns<M_LSE>(ctx, a);
   }
-  k_row<R_LSE><<<dim3((rows + kRT - 1) / kRT, bd), kRT * kCL, 0, ctx->stream>>>(xs[0].v, nullptr, nullptr, fx->v, rows, cols);
+  dyb_launch(k_row<R_LSE>, dim3((rows + kRT - 1) / kRT, bd), kRT * kCL, 0, ctx, xs[0].v, nullptr, nullptr, fx->v, rows, cols);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -538,7 +548,7 @@ int dyb200_logsumexp_dim_bwd(DYB200_BWD_ARGS) {
   DYB_CHECK_ARG(ctx, t_size(dEdxi) == t_size(&xs[0]) && t_size(dEdf) == t_size(fx), "LogSumExpDimension::backward: size mismatch");
   if (t_size(&xs[0]) == 0) return DYB200_OK;
   if (dimension == 0) return run_expsub_bwd(ctx, xs[0].v, fx->v, dEdf->v, nullptr, dEdxi->v, rows, (size_t)cols * bd);
-  k_row<R_LSE_BWD><<<dim3((rows + kRT - 1) / kRT, bd), kRT * kCL, 0, ctx->stream>>>(xs[0].v, fx->v, dEdxi->v, dEdf->v, rows, cols);
+  dyb_launch(k_row<R_LSE_BWD>, dim3((rows + kRT - 1) / kRT, bd), kRT * kCL, 0, ctx, xs[0].v, fx->v, dEdxi->v, dEdf->v, rows, cols);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -556,7 +566,7 @@ int dyb200_logsumexp_fwd(DYB200_FWD_ARGS) {
   }
   size_t total = n * fx->bd;
   if (total == 0) return DYB200_OK;
-  k_lse_nary_fwd<<<stream_grid(ctx, total, kBlock), kBlock, 0, ctx->stream>>>(a, fx->v, n, fx->bd);
+  dyb_launch(k_lse_nary_fwd, stream_grid(ctx, total, kBlock), kBlock, 0, ctx, a, fx->v, n, fx->bd);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
@@ -568,7 +578,7 @@ int dyb200_logsumexp_bwd(DYB200_BWD_ARGS) {
   size_t n = t_batch_size(fx), total = n * fx->bd;
   if (total == 0) return DYB200_OK;
   if (nxs == 1 || xs[i].bd == fx->bd) {
-    k_lse_nary_bwd<<<stream_grid(ctx, total, kBlock), kBlock, 0, ctx->stream>>>(xs[i].v, fx->v, dEdf->v, dEdxi->v, total, nxs == 1);
+    dyb_launch(k_lse_nary_bwd, stream_grid(ctx, total, kBlock), kBlock, 0, ctx, xs[i].v, fx->v, dEdf->v, dEdxi->v, total, nxs == 1);
     DYB_LAUNCHED(ctx);
     return DYB200_OK;
   }

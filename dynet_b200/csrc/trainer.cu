@@ -68,6 +68,7 @@ template <int RULE> struct NStates { static constexpr int v = RULE == DYB200_RUL
 
 template <int RULE>
 __global__ void __launch_bounds__(kBlock) k_trainer_update(const RuleArgs a) {
+  dyb_grid_dep_sync();
   float gscale = 1.f;
   if (a.sumsq && a.h.clip_threshold > 0.f) {
     const float gg = sqrtf(a.sumsq[0]);
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(kBlock) k_trainer_update(const RuleArgs a) {
 
 template <int RULE>
 int launch(dyb200_ctx* ctx, const RuleArgs& a) {
-  k_trainer_update<RULE><<<stream_grid(ctx, a.n / 4 + 1, kBlock * 2), kBlock, 0, ctx->stream>>>(a);
+  dyb_launch(k_trainer_update<RULE>, stream_grid(ctx, a.n / 4 + 1, kBlock * 2), kBlock, 0, ctx, a);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }

@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -394,6 +395,12 @@ int dyb200h_lm_create(const dyb200h_lm_config* c, float* params, float* grads, v
   // this driver owns the parameter updates (dyb200h_lm_update -> dyb200_sgd_update), so the packed
   // copies of the weights can be reused across the time steps of a training step
   dyb200_ctx_param_cache(ctx, 1);
+  // kernels of a step form one dependent chain: let each be scheduled while its predecessor drains
+  // (environment DYB200_PDL=0 turns it off)
+  {
+    const char* e = getenv("DYB200_PDL");
+    dyb200_ctx_dependent_launch(ctx, (e && atoi(e) == 0) ? 0 : 1);
+  }
   int rc = DYB200_OK;
   if (c->fused) {
     for (uint32_t l = 0; l < c->L && !rc; ++l) {

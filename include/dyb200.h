@@ -80,6 +80,11 @@ int dyb200_ctx_profile_end(dyb200_ctx* ctx, double ms_out[2], uint64_t launches_
  * parameter values (dyb200_sgd_update does it itself); in a DyNet tree that is the end of
  * Trainer::update (dynet/training.cc:195-265).  Costs up to 2x the size of each cached matrix. */
 int dyb200_ctx_param_cache(dyb200_ctx* ctx, int enable);
+/* Programmatic dependent launch (off by default).  When on, every kernel of this library is launched so that it may be
+ * scheduled while its predecessor in the stream still runs; each kernel waits, before its first memory access, until that
+ * predecessor has completed (griddepcontrol.wait), so results do not change - only launch latency overlaps.  Work that other
+ * code puts into the same stream between two calls is ordered as usual. */
+int dyb200_ctx_dependent_launch(dyb200_ctx* ctx, int enable);
 int dyb200_ctx_params_changed(dyb200_ctx* ctx);
 /* Library build string ("dyb200 <n> sm_100a"). */
 const char* dyb200_version(void);
