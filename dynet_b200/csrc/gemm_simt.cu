@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(uint32_t M, uint32_t N, int n
       else if (epi.mode == EPI_GATES) {
         v += epi.bias[m];
         if (m >= epi.H && m < 2 * epi.H) v += epi.forget_bias;
-        *c = m < 3 * epi.H ? sigmoidf_dev(v) : tanhf(v);
+        *c = m < 3 * epi.H ? gate_sigmoid(v) : gate_tanh(v);
       } else {
         *c += v * epi.maskC[m + (epi.maskc_full ? (size_t)epi.maskc_ld * n : 0)];
       }

@@ -11,8 +11,10 @@
 //   warp 1     allocates TMEM, issues 3 MMAs per 8-wide k-step, commits to the ring's mbarriers;
 //              the accumulation chain is cut every kChunkKB k-blocks (two TMEM accumulators, used alternately)
 //   warps 2-9  add every finished chunk (tcgen05.ld of their 32 accumulator lanes x 64 columns) into fp32
-//              registers, then run the fused epilogue with coalesced stores; read-modify-write epilogues load
-//              a whole 32-column chunk first; the LSTM epilogue also forms c and h (gates exchanged in smem)
+//              registers, park the finished tile in the idle operand ring and run the epilogue as a short
+//              cooperative loop over it: 16-byte accesses along the rows (whole 512-byte tile columns per warp),
+//              read-modify-write epilogues with 8 loads in flight; the LSTM epilogue reads the four gates of a
+//              hidden unit from the tile and also forms c and h
 // Products with few output tiles are split along K over blockIdx.z; the splits store raw partial
 // tiles and a second kernel adds them in split order and applies the epilogue (deterministic).
 // Every mbarrier wait is bounded; a wait that runs out sets DYB200_FLAG_WAIT_TIMEOUT and the
@@ -218,18 +220,17 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     // epilogue warps 2..9: TMEM lanes 32*(warp % 4) .. +31 (row of the tile = lane of TMEM); warps 2-5
     // take columns 0-63, warps 6-9 columns 64-127
     const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
-    const uint32_t m = m0 + quarter * 32 + lane;
-    // EPI_LSTM_CELL: previous cell state of this thread's 8 columns per chunk, fetched while the MMAs run
-    float cprev[2][8];
+    const uint32_t te = threadIdx.x - 64;   // 0..255 among the epilogue threads
+    // EPI_LSTM_CELL: in the cooperative pass below this thread owns hidden units [4 (te % 8), +4) of the tile's 32 for
+    // the columns te / 8 + 32 k; their previous cell states are fetched now, while the MMAs run
+    float4 cprev[4];
     if (epi.mode == EPI_LSTM_CELL) {
-      const uint32_t u = blockIdx.x * 32 + lane;
+      const uint32_t u = blockIdx.x * 32 + 4 * (te & 7);
 #pragma unroll
-      for (int cl = 0; cl < 2; ++cl)
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          const uint32_t n = n0 + (2 * half + cl) * 32 + quarter * 8 + jj;
-          cprev[cl][jj] = n < N ? __ldg(epi.c_prev + u + (size_t)epi.H * n) : 0.f;
-        }
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t n = n0 + (te >> 3) + 32 * k;
+        cprev[k] = n < N ? ld4(epi.c_prev + u + (size_t)epi.H * n) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
     float sum[64];   // this thread's row of the tile, columns [64 half, 64 half + 64)
 #pragma unroll
@@ -254,83 +255,120 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
     if (!ok && lane == 0) atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT);
-    if (epi.mode == EPI_LSTM_CELL) {
-      // The tile holds gates i, f, o, g (TMEM lane quarter q) of hidden units 32 * blockIdx.x + lane.  The four warps
-      // of a column half exchange their activated gates through the (now idle) operand ring and each then forms
-      // c and h for 8 of the 32 columns of the chunk.  Every warp reaches both named barriers whatever its wait did.
-      uint32_t all_ok;
-      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, %2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                   : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1u + half) : "memory");
-      if (all_ok) {
-        float* ex = reinterpret_cast<float*>(ring) + half * (4 * 32 * 32);
-        const uint32_t u = blockIdx.x * 32 + lane, grow = quarter * epi.H + u;
-        const float bias = epi.bias[grow] + (quarter == 1 ? epi.forget_bias : 0.f);
+    // The tile goes through shared memory (the operand ring is idle once the last chunk has been drained: every MMA
+    // has completed and no TMA load is in flight), stored like C: column-major, 128 rows per column.  The pass that
+    // follows is a short rolled loop in which consecutive threads take consecutive rows, so global accesses are
+    // 16-byte vectors covering whole 512-byte columns of the tile.  Every epilogue warp reaches the named barrier,
+    // whatever its waits did; a failed wait anywhere cancels the stores.
+    float* tile = reinterpret_cast<float*>(ring);
+    {
+      float* col = tile + (size_t)(64 * half) * BM + quarter * 32 + lane;
 #pragma unroll
-        for (int cl = 0; cl < 2; ++cl) {
-          const uint32_t nb = n0 + (2 * half + cl) * 32;
-          float* dst = epi.C + grow + (size_t)epi.ldc * nb;
+      for (int j = 0; j < 64; ++j) col[(size_t)j * BM] = sum[j];
+    }
+    uint32_t all_ok;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, 1, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
+    if (all_ok) {
+      if (epi.mode == EPI_LSTM_CELL) {
+        // rows 32 q + l of the tile are gate q (i, f, o, g) of hidden unit 32 blockIdx.x + l
+        const uint32_t l = 4 * (te & 7), u = blockIdx.x * 32 + l;
+        float4 bias[4];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float x = sum[cl * 32 + j] + bias;
-            const float a = quarter == 3 ? tanhf(x) : sigmoidf_dev(x);
-            if (nb + j < N) dst[(size_t)epi.ldc * j] = a;
-            ex[(quarter * 32 + j) * 32 + lane] = a;
+        for (int q = 0; q < 4; ++q) {
+          bias[q] = ld4(epi.bias + (size_t)q * epi.H + u);
+          if (q == 1) { bias[q].x += epi.forget_bias; bias[q].y += epi.forget_bias; bias[q].z += epi.forget_bias; bias[q].w += epi.forget_bias; }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t c = (te >> 3) + 32 * k, n = n0 + c;
+          if (n < N) {
+            float4 g[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 a = ld4(tile + (size_t)c * BM + 32 * q + l);
+              const float4 x = make_float4(a.x + bias[q].x, a.y + bias[q].y, a.z + bias[q].z, a.w + bias[q].w);
+              g[q] = q == 3 ? make_float4(gate_tanh(x.x), gate_tanh(x.y), gate_tanh(x.z), gate_tanh(x.w))
+                            : make_float4(gate_sigmoid(x.x), gate_sigmoid(x.y), gate_sigmoid(x.z), gate_sigmoid(x.w));
+              st4(epi.C + (size_t)q * epi.H + u + (size_t)epi.ldc * n, g[q]);
+            }
+            const size_t e = u + (size_t)epi.H * n;
+            const float4 cn = make_float4(lstm_cell_c(g[0].x, g[3].x, g[1].x, cprev[k].x), lstm_cell_c(g[0].y, g[3].y, g[1].y, cprev[k].y),
+                                          lstm_cell_c(g[0].z, g[3].z, g[1].z, cprev[k].z), lstm_cell_c(g[0].w, g[3].w, g[1].w, cprev[k].w));
+            st4(epi.c_out + e, cn);
+            st4(epi.h_out + e, make_float4(lstm_cell_h(g[2].x, cn.x), lstm_cell_h(g[2].y, cn.y), lstm_cell_h(g[2].z, cn.z), lstm_cell_h(g[2].w, cn.w)));
           }
-          asm volatile("barrier.cta.sync %0, 128;" ::"r"(1u + half) : "memory");
+        }
+      } else {
+        const bool vec = (M & 3) == 0 && (epi.split_m & 3) == 0 && (epi.ldc & 3) == 0 && aligned16(epi.C) &&
+                         (epi.split_m == 0 || ((epi.ldc2 & 3) == 0 && aligned16(epi.C2))) &&
+                         (epi.mode != EPI_BIAS || aligned16(epi.bias)) && (epi.mode != EPI_GATES || (aligned16(epi.bias) && (epi.H & 3) == 0)) &&
+                         (epi.mode != EPI_ACCUM_MASK ||
+                          (aligned16(epi.maskC) && (!epi.maskc_full || (epi.maskc_ld & 3) == 0) &&
+                           (epi.split_m == 0 || (aligned16(epi.maskC2) && (!epi.maskc2_full || (epi.maskc2_ld & 3) == 0)))));
+        if (vec) {
+          // 32 row quads x 128 columns; a thread keeps its row quad and walks the columns te / 32 + 8 k
+          const uint32_t rq = te & 31, m = m0 + 4 * rq;
+          if (m < M) {
+            const EpiRow row = epi_row(epi, m);
+            const size_t ldc = row.ldc;
+            float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (epi.mode == EPI_BIAS || epi.mode == EPI_GATES) bias = ld4(epi.bias + m);
+            if (epi.mode == EPI_GATES && m >= epi.H && m < 2 * epi.H) { bias.x += epi.forget_bias; bias.y += epi.forget_bias; bias.z += epi.forget_bias; bias.w += epi.forget_bias; }
+            const bool is_tanh = m >= 3 * epi.H;
+            const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
+#pragma unroll 1
+            for (uint32_t c0 = te >> 5; c0 < BN; c0 += 64) {   // two batches of 8 columns, loads first
+              float4 v[8], old[8], mk[8];
 #pragma unroll
-          for (int jj = 0; jj < 8; ++jj) {
-            const uint32_t j = quarter * 8 + jj, n = nb + j;
-            const float gi = ex[(0 * 32 + j) * 32 + lane], gf = ex[(1 * 32 + j) * 32 + lane];
-            const float go = ex[(2 * 32 + j) * 32 + lane], gg = ex[(3 * 32 + j) * 32 + lane];
-            if (n < N) {
-              const size_t e = u + (size_t)epi.H * n;
-              const float cn = lstm_cell_c(gi, gg, gf, cprev[cl][jj]);
-              epi.c_out[e] = cn;
-              epi.h_out[e] = lstm_cell_h(go, cn);
+              for (int k = 0; k < 8; ++k) {
+                const uint32_t c = c0 + 8 * k, n = n0 + c;
+                v[k] = ld4(tile + (size_t)c * BM + 4 * rq);
+                if (epi.mode == EPI_ACCUM || epi.mode == EPI_ACCUM_MASK) old[k] = n < N ? __ldcg(reinterpret_cast<const float4*>(row.c + ldc * n)) : v[k];
+                if (epi.mode == EPI_ACCUM_MASK) mk[k] = n < N ? ld4(row.mask + mstep * n) : v[k];
+              }
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const uint32_t n = n0 + c0 + 8 * k;
+                if (n >= N) continue;
+                float4 r = v[k];
+                if (epi.mode == EPI_BIAS) { r.x += bias.x; r.y += bias.y; r.z += bias.z; r.w += bias.w; }
+                else if (epi.mode == EPI_GATES) {
+                  r = make_float4(r.x + bias.x, r.y + bias.y, r.z + bias.z, r.w + bias.w);
+                  r = is_tanh ? make_float4(gate_tanh(r.x), gate_tanh(r.y), gate_tanh(r.z), gate_tanh(r.w))
+                              : make_float4(gate_sigmoid(r.x), gate_sigmoid(r.y), gate_sigmoid(r.z), gate_sigmoid(r.w));
+                } else if (epi.mode == EPI_ACCUM) { r.x += old[k].x; r.y += old[k].y; r.z += old[k].z; r.w += old[k].w; }
+                else if (epi.mode == EPI_ACCUM_MASK) {
+                  r = make_float4(old[k].x + r.x * mk[k].x, old[k].y + r.y * mk[k].y, old[k].z + r.z * mk[k].z, old[k].w + r.w * mk[k].w);
+                }
+                st4(row.c + ldc * n, r);
+              }
             }
           }
-          asm volatile("barrier.cta.sync %0, 128;" ::"r"(1u + half) : "memory");
-        }
-      }
-    } else if (ok && m < M) {
-      const EpiRow row = epi_row(epi, m);
-      const size_t ldc = row.ldc;
-#pragma unroll
-      for (int cl = 0; cl < 2; ++cl) {
-        const uint32_t nb = n0 + (2 * half + cl) * 32;
-        float* dst = row.c + ldc * nb;
-        float* v = sum + cl * 32;
-        if (epi.mode == EPI_STORE) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = v[j];
-        } else if (epi.mode == EPI_BIAS) {
-          const float bias = epi.bias[m];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = v[j] + bias;
-        } else if (epi.mode == EPI_GATES) {
-          const float bias = epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
-          const bool is_tanh = m >= 3 * epi.H;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = v[j] + bias;
-            if (nb + j < N) dst[ldc * j] = is_tanh ? tanhf(x) : sigmoidf_dev(x);
-          }
         } else {
-          // read-modify-write: all loads of the 32-column chunk are issued before the first dependent store
-          if (epi.mode == EPI_ACCUM_MASK) {
+          // any shape / alignment: one row per thread pair of columns, scalar accesses
+          const uint32_t r = te & 127, m = m0 + r;
+          if (m < M) {
+            const EpiRow row = epi_row(epi, m);
+            const size_t ldc = row.ldc;
+            float bias = 0.f;
+            if (epi.mode == EPI_BIAS || epi.mode == EPI_GATES) bias = epi.bias[m];
+            if (epi.mode == EPI_GATES && m >= epi.H && m < 2 * epi.H) bias += epi.forget_bias;
+            const bool is_tanh = m >= 3 * epi.H;
             const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
-            const float* mp = row.mask + mstep * nb;
-            float mk[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) mk[j] = (nb + j < N) ? __ldg(mp + mstep * j) : 0.f;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] *= mk[j];
+#pragma unroll 4
+            for (uint32_t c = te >> 7; c < BN; c += 2) {
+              const uint32_t n = n0 + c;
+              if (n >= N) break;
+              float v = tile[(size_t)c * BM + r];
+              float* dst = row.c + ldc * n;
+              if (epi.mode == EPI_STORE) *dst = v;
+              else if (epi.mode == EPI_BIAS) *dst = v + bias;
+              else if (epi.mode == EPI_GATES) *dst = is_tanh ? gate_tanh(v + bias) : gate_sigmoid(v + bias);
+              else if (epi.mode == EPI_ACCUM) *dst += v;
+              else *dst += v * row.mask[mstep * n];
+            }
           }
-          float old[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) old[j] = nb + j < N ? __ldcg(dst + ldc * j) : 0.f;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) if (nb + j < N) dst[ldc * j] = old[j] + v[j];
         }
       }
     }

@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(kThreads) k_gates_bias_only(const float* __res
   for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (size_t)gridDim.x * kThreads) {
     uint32_t r = (uint32_t)(i % G);
     float v = bias[r] + ((r >= H && r < 2 * H) ? forget_bias : 0.f);
-    fx[i] = r < 3 * H ? sigmoidf_dev(v) : tanhf(v);
+    fx[i] = r < 3 * H ? gate_sigmoid(v) : gate_tanh(v);
   }
 }
 
