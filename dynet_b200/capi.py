@@ -118,7 +118,7 @@ OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200
          "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm", "dyb200_fill", "dyb200_sum_all",
          "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_trainer_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end",
          "dyb200_ctx_param_cache", "dyb200_ctx_params_changed", "dyb200_ctx_dependent_launch", "dyb200_vanilla_lstm_fwd_fused",
-         "dyb200_vanilla_lstm_bwd_fused", "dyb200_wgrad_create", "dyb200_wgrad_destroy", "dyb200_wgrad_push",
+         "dyb200_vanilla_lstm_bwd_fused", "dyb200_vanilla_lstm_fwd_fused_at", "dyb200_vanilla_lstm_bwd_fused_at", "dyb200_wgrad_create", "dyb200_wgrad_destroy", "dyb200_wgrad_push",
          "dyb200_wgrad_flush"]
 
 
@@ -167,6 +167,10 @@ def lib():
         L.dyb200_vanilla_lstm_fwd_fused.argtypes = [tp] * 8 + [C.POINTER(LstmGatesAttrs)] + [tp] * 3 + [C.c_void_p]
         L.dyb200_vanilla_lstm_bwd_fused.restype = C.c_int
         L.dyb200_vanilla_lstm_bwd_fused.argtypes = [tp] * 17 + [C.POINTER(LstmGatesAttrs), C.c_void_p, C.c_void_p]
+        L.dyb200_vanilla_lstm_fwd_fused_at.restype = C.c_int
+        L.dyb200_vanilla_lstm_fwd_fused_at.argtypes = [tp] * 8 + [C.POINTER(LstmGatesAttrs)] + [tp] * 3 + [C.c_void_p, C.c_uint32, C.c_void_p]
+        L.dyb200_vanilla_lstm_bwd_fused_at.restype = C.c_int
+        L.dyb200_vanilla_lstm_bwd_fused_at.argtypes = [tp] * 17 + [C.POINTER(LstmGatesAttrs), C.c_void_p, C.c_uint32, C.c_void_p]
         L.dyb200_wgrad_create.restype = C.c_int
         L.dyb200_wgrad_create.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]
         L.dyb200_wgrad_destroy.restype = C.c_int
@@ -314,6 +318,20 @@ class Context:
         self.check(self.L.dyb200_vanilla_lstm_bwd_fused(o(x), o(h_tm1), o(c_tm1), o(Wx), o(Wh), o(mask_x), o(mask_h), o(gates), o(c_t),
                                                         o(dEdh), o(dEdc), o(dx), o(dh_tm1), o(dc_tm1), o(dWx), o(dWh), o(db),
                                                         C.byref(attrs), deferred, self.h))
+
+    WGRAD_APPEND = 0xffffffff
+
+    def lstm_fwd_fused_at(self, x, h_tm1, c_tm1, Wx, Wh, b, mask_x, mask_h, attrs, gates, c_t, h_t, deferred, col):
+        o = self._opt
+        self.check(self.L.dyb200_vanilla_lstm_fwd_fused_at(o(x), o(h_tm1), o(c_tm1), o(Wx), o(Wh), o(b), o(mask_x), o(mask_h),
+                                                           C.byref(attrs), o(gates), o(c_t), o(h_t), deferred, col, self.h))
+
+    def lstm_bwd_fused_at(self, x, h_tm1, c_tm1, Wx, Wh, mask_x, mask_h, gates, c_t, dEdh, dEdc, dx, dh_tm1, dc_tm1, dWx, dWh, db, attrs,
+                          deferred, col):
+        o = self._opt
+        self.check(self.L.dyb200_vanilla_lstm_bwd_fused_at(o(x), o(h_tm1), o(c_tm1), o(Wx), o(Wh), o(mask_x), o(mask_h), o(gates), o(c_t),
+                                                           o(dEdh), o(dEdc), o(dx), o(dh_tm1), o(dc_tm1), o(dWx), o(dWh), o(db),
+                                                           C.byref(attrs), deferred, col, self.h))
 
     def wgrad_create(self, M, N0, N1, Kcap):
         h = C.c_void_p()

@@ -96,6 +96,10 @@ struct dyb200_wgrad;
 int dyb200_wgrad_reserve(dyb200_wgrad* w, uint32_t k, float** a_hi, float** a_lo, uint32_t* pitch, const float* b0, uint32_t ldb0,
                          const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1, int mask1_full,
                          dyb200_ctx* ctx, PackJobs* batch);
+int dyb200_wgrad_push_b_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const float* b0, uint32_t ldb0, const float* mask0, int mask0_full,
+                           const float* b1, uint32_t ldb1, const float* mask1, int mask1_full, dyb200_ctx* ctx, PackJobs* batch);
+int dyb200_wgrad_reserve_a_at(dyb200_wgrad* w, uint32_t col, uint32_t k, float** a_hi, float** a_lo, uint32_t* pitch, dyb200_ctx* ctx);
+int dyb200_wgrad_pack_a_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const float* a, uint32_t lda, dyb200_ctx* ctx, PackJobs* batch);
 uint32_t dyb200_wgrad_rows(const dyb200_wgrad* w);
 uint32_t dyb200_wgrad_fill(const dyb200_wgrad* w);
 int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda, const float* b0, uint32_t ldb0,

@@ -836,7 +836,9 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
 // product with K = sum k_t runs at the end: the tensor pipe sees a long reduction and C is read and
 // written once.  One A operand can serve two B operands (dWx and dWh share the gate gradient).
 struct dyb200_wgrad {
-  uint32_t M, N[2], Kcap, k;
+  uint32_t M, N[2], Kcap;
+  uint32_t k;    // columns of A filled so far (the product at flush time runs over [0, k))
+  uint32_t kb;   // columns of the B operands filled so far
   PackedOp A, B[2];
 };
 
@@ -856,6 +858,7 @@ int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint3
     if (rc) return rc;
   }
   w->k += k;
+  w->kb = w->k;
   return DYB200_OK;
 }
 
@@ -874,6 +877,35 @@ int dyb200_wgrad_reserve(dyb200_wgrad* w, uint32_t k, float** a_hi, float** a_lo
     if (rc) return rc;
   }
   w->k += k;
+  w->kb = w->k;
+  return DYB200_OK;
+}
+// Explicit column positions, for callers that fill the B operands (the layer inputs) during the forward pass and the A
+// operand (the gate gradient) during the backward pass: step t of a sequence uses columns [t * k, (t + 1) * k) both times.
+int dyb200_wgrad_push_b_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const float* b0, uint32_t ldb0, const float* mask0, int mask0_full,
+                           const float* b1, uint32_t ldb1, const float* mask1, int mask1_full, dyb200_ctx* ctx, PackJobs* batch) {
+  DYB_CHECK_ARG(ctx, w && b0 && (w->N[1] == 0 || b1), "wgrad_push_b_at: null argument");
+  DYB_CHECK_ARG(ctx, (uint64_t)col + k <= w->Kcap, "wgrad_push_b_at: columns [%u, %u) exceed the capacity %u", col, col + k, w->Kcap);
+  int rc = pack(ctx, b0, ldb0, 0, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + col, w->B[0].lo + col, w->Kcap, batch);
+  if (rc) return rc;
+  if (w->N[1]) {
+    rc = pack(ctx, b1, ldb1, 0, w->N[1], k, mask1, ldb1, mask1_full, w->B[1].hi + col, w->B[1].lo + col, w->Kcap, batch);
+    if (rc) return rc;
+  }
+  if (col + k > w->kb) w->kb = col + k;
+  return DYB200_OK;
+}
+int dyb200_wgrad_reserve_a_at(dyb200_wgrad* w, uint32_t col, uint32_t k, float** a_hi, float** a_lo, uint32_t* pitch, dyb200_ctx* ctx) {
+  DYB_CHECK_ARG(ctx, w && (uint64_t)col + k <= w->Kcap, "wgrad_reserve_a_at: columns [%u, %u) exceed the capacity", col, col + k);
+  *a_hi = w->A.hi + col; *a_lo = w->A.lo + col; *pitch = w->Kcap;
+  if (col + k > w->k) w->k = col + k;
+  return DYB200_OK;
+}
+int dyb200_wgrad_pack_a_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const float* a, uint32_t lda, dyb200_ctx* ctx, PackJobs* batch) {
+  DYB_CHECK_ARG(ctx, w && a && (uint64_t)col + k <= w->Kcap, "wgrad_pack_a_at: columns [%u, %u) exceed the capacity", col, col + k);
+  int rc = pack(ctx, a, lda, 0, w->M, k, nullptr, 0, 0, w->A.hi + col, w->A.lo + col, w->Kcap, batch);
+  if (rc) return rc;
+  if (col + k > w->k) w->k = col + k;
   return DYB200_OK;
 }
 uint32_t dyb200_wgrad_rows(const dyb200_wgrad* w) { return w->M; }
@@ -885,7 +917,7 @@ int dyb200_wgrad_create(dyb200_ctx* ctx, uint32_t M, uint32_t N0, uint32_t N1, u
   DYB_CHECK_ARG(ctx, out && M > 0 && N0 > 0 && Kcap > 0, "wgrad_create: bad shape");
   dyb200_wgrad* w = (dyb200_wgrad*)calloc(1, sizeof(dyb200_wgrad));
   if (!w) return dyb200_fail(ctx, DYB200_ENOMEM, "wgrad_create: host allocation failed");
-  w->M = M; w->N[0] = N0; w->N[1] = N1; w->Kcap = round_up(Kcap, 32); w->k = 0;
+  w->M = M; w->N[0] = N0; w->N[1] = N1; w->Kcap = round_up(Kcap, 32); w->k = 0; w->kb = 0;
   auto alloc = [&](PackedOp* p, uint32_t rows) -> bool {
     p->rows = rows; p->K = 0; p->pitch = w->Kcap;
     size_t bytes = (size_t)rows * w->Kcap * sizeof(float);
@@ -926,7 +958,8 @@ int dyb200_wgrad_push(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda,
 int dyb200_wgrad_flush(dyb200_wgrad* w, float* C0, uint32_t ldc0, float* C1, uint32_t ldc1, dyb200_ctx* ctx) {
   { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   DYB_CHECK_ARG(ctx, w && C0 && (w->N[1] == 0 || C1), "wgrad_flush: null argument");
-  if (w->k == 0) return DYB200_OK;
+  if (w->k == 0) { w->kb = 0; return DYB200_OK; }
+  DYB_CHECK_ARG(ctx, w->kb >= w->k, "wgrad_flush: the B operands cover %u columns, the A operand %u", w->kb, w->k);
   PackedOp A = w->A;
   A.K = w->k;
   for (int j = 0; j < 2; ++j) {
@@ -938,6 +971,7 @@ int dyb200_wgrad_flush(dyb200_wgrad* w, float* C0, uint32_t ldc0, float* C1, uin
     if (rc) return rc;
   }
   w->k = 0;
+  w->kb = 0;
   return DYB200_OK;
 }
 

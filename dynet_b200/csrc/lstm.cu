@@ -513,6 +513,14 @@ int dyb200_vanilla_lstm_fwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
                                   const dyb200_tensor* mask_x, const dyb200_tensor* mask_h,
                                   const dyb200_lstm_gates_attrs* attrs, dyb200_tensor* gates, dyb200_tensor* c_t,
                                   dyb200_tensor* h_t, dyb200_ctx* ctx) {
+  return dyb200_vanilla_lstm_fwd_fused_at(x, h_tm1, c_tm1, Wx, Wh, b, mask_x, mask_h, attrs, gates, c_t, h_t, nullptr, 0, ctx);
+}
+
+int dyb200_vanilla_lstm_fwd_fused_at(const dyb200_tensor* x, const dyb200_tensor* h_tm1, const dyb200_tensor* c_tm1,
+                                     const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* b,
+                                     const dyb200_tensor* mask_x, const dyb200_tensor* mask_h,
+                                     const dyb200_lstm_gates_attrs* attrs, dyb200_tensor* gates, dyb200_tensor* c_t,
+                                     dyb200_tensor* h_t, dyb200_wgrad* deferred, uint32_t deferred_col, dyb200_ctx* ctx) {
   DYB_CHECK_ARG(ctx, x && h_tm1 && c_tm1 && Wx && Wh && b && attrs && gates && c_t && h_t, "lstm_fwd_fused: null argument");
   DYB_CHECK_ARG(ctx, (attrs->dropout != 0) == (mask_x != nullptr && mask_h != nullptr), "lstm_fwd_fused: masks must be given exactly when dropout is set");
   dyb200_tensor xs[7] = {*x, *h_tm1, *Wx, *Wh, *b};
@@ -545,6 +553,11 @@ int dyb200_vanilla_lstm_fwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
       const float* mh = attrs->dropout ? mask_h->v : nullptr;
       if ((rc = dyb200_tc_pack(ctx, x->v, I, true, B, I, mx, I, mx ? mask_x->bd == B : 0, &Bp[0], &batch))) return rc;
       if ((rc = dyb200_tc_pack(ctx, h_tm1->v, H, true, B, H, mh, H, mh ? mask_h->bd == B : 0, &Bp[1], &batch))) return rc;
+      if (deferred) {   // the same inputs, transposed, are the B operands of this step's weight-gradient products
+        DYB_CHECK_ARG(ctx, dyb200_wgrad_rows(deferred) == G, "lstm_fwd_fused: the deferred accumulator has %u rows, the layer %u", dyb200_wgrad_rows(deferred), G);
+        if ((rc = dyb200_wgrad_push_b_at(deferred, deferred_col, B, x->v, I, mx, mx ? mask_x->bd == B : 0, h_tm1->v, H, mh,
+                                         mh ? mask_h->bd == B : 0, ctx, &batch))) return rc;
+      }
       if ((rc = dyb200_tc_pack_flush(ctx, &batch))) return rc;
       GemmEpilogue e{EPI_LSTM_CELL, gates->v, G, b->v, H, attrs->forget_gate_bias, nullptr, 0, 0};
       e.c_prev = c_tm1->v; e.c_out = c_t->v; e.h_out = h_t->v;
@@ -553,6 +566,15 @@ int dyb200_vanilla_lstm_fwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
   }
   int rc = dyb200_vanilla_lstm_gates_fwd(xs, nxs, gates, attrs, nullptr, ctx);
   if (rc) return rc;
+  if (deferred) {
+    PackJobs batch;
+    dyb200_tc_pack_begin(&batch);
+    const float* mx = attrs->dropout ? mask_x->v : nullptr;
+    const float* mh = attrs->dropout ? mask_h->v : nullptr;
+    if ((rc = dyb200_wgrad_push_b_at(deferred, deferred_col, x->bd, x->v, t_dim(x, 0), mx, mx ? mask_x->bd == x->bd : 0, h_tm1->v,
+                                     t_dim(h_tm1, 0), mh, mh ? mask_h->bd == x->bd : 0, ctx, &batch))) return rc;
+    if ((rc = dyb200_tc_pack_flush(ctx, &batch))) return rc;
+  }
   dyb200_tensor ch[2] = {*c_tm1, *gates};
   rc = ch_check(ctx, ch, 2, "VanillaLSTMC");
   if (rc) return rc;
@@ -571,6 +593,21 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
                                   dyb200_tensor* dh_tm1, dyb200_tensor* dc_tm1, dyb200_tensor* dWx, dyb200_tensor* dWh,
                                   dyb200_tensor* db, const dyb200_lstm_gates_attrs* attrs, dyb200_wgrad* deferred,
                                   dyb200_ctx* ctx) {
+  return dyb200_vanilla_lstm_bwd_fused_at(x, h_tm1, c_tm1, Wx, Wh, mask_x, mask_h, gates, c_t, dEdh, dEdc, dx, dh_tm1, dc_tm1, dWx, dWh, db,
+                                          attrs, deferred, DYB200_WGRAD_APPEND, ctx);
+}
+
+int dyb200_vanilla_lstm_bwd_fused_at(const dyb200_tensor* x, const dyb200_tensor* h_tm1, const dyb200_tensor* c_tm1,
+                                     const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* mask_x,
+                                     const dyb200_tensor* mask_h, const dyb200_tensor* gates, const dyb200_tensor* c_t,
+                                     const dyb200_tensor* dEdh, const dyb200_tensor* dEdc, dyb200_tensor* dx,
+                                     dyb200_tensor* dh_tm1, dyb200_tensor* dc_tm1, dyb200_tensor* dWx, dyb200_tensor* dWh,
+                                     dyb200_tensor* db, const dyb200_lstm_gates_attrs* attrs, dyb200_wgrad* deferred,
+                                     uint32_t deferred_col, dyb200_ctx* ctx) {
+  // deferred_col == DYB200_WGRAD_APPEND: this call appends the gate gradient AND the layer inputs to the accumulator;
+  // otherwise the inputs of this step were placed at that column by dyb200_vanilla_lstm_fwd_fused_at and only the gate
+  // gradient is written there.
+  const bool at_col = deferred && deferred_col != DYB200_WGRAD_APPEND;
   { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   DYB_CHECK_ARG(ctx, x && h_tm1 && c_tm1 && Wx && Wh && gates && c_t && dEdh && (deferred || (dWx && dWh)) && db && attrs, "lstm_bwd_fused: null argument");
   DYB_CHECK_ARG(ctx, (attrs->dropout != 0) == (mask_x != nullptr && mask_h != nullptr), "lstm_bwd_fused: masks must be given exactly when dropout is set");
@@ -596,7 +633,7 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
   // Bandwidth-shaped pass for whole tiles: it writes the split planes of the gate gradient itself.
   const bool tiled = tensor_path && H % kCT_J == 0 && B % kCT_B == 0 && H / kCT_J <= DYB200_DEV_COUNTERS && aligned16(c_t->v) &&
                      aligned16(c_tm1->v) && aligned16(gates->v) && aligned16(dEdh->v) && (!dEdc || aligned16(dEdc->v)) &&
-                     (!dc_tm1 || aligned16(dc_tm1->v)) && (!deferred || dyb200_wgrad_fill(deferred) % 32 == 0);
+                     (!dc_tm1 || aligned16(dc_tm1->v)) && (!deferred || (at_col ? deferred_col : dyb200_wgrad_fill(deferred)) % 32 == 0);
   float* dpre = nullptr;
   if (tiled) {
     if ((rc = dyb200_tc_planes(ctx, B, G, &dn))) return rc;
@@ -604,7 +641,9 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
     uint32_t a_pitch = 0;
     if (deferred) {
       DYB_CHECK_ARG(ctx, dyb200_wgrad_rows(deferred) == G, "lstm_bwd_fused: the deferred accumulator has %u rows, the layer %u", dyb200_wgrad_rows(deferred), G);
-      if ((rc = dyb200_wgrad_reserve(deferred, B, &a_hi, &a_lo, &a_pitch, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx, &batch))) return rc;
+      if (at_col) rc = dyb200_wgrad_reserve_a_at(deferred, deferred_col, B, &a_hi, &a_lo, &a_pitch, ctx);
+      else rc = dyb200_wgrad_reserve(deferred, B, &a_hi, &a_lo, &a_pitch, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx, &batch);
+      if (rc) return rc;
     } else {
       if ((rc = dyb200_tc_planes(ctx, G, B, &dt))) return rc;
       a_hi = dt.hi; a_lo = dt.lo; a_pitch = dt.pitch;
@@ -624,7 +663,8 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
     DYB_LAUNCHED(ctx);
     if (deferred) {
       // weight gradients: append (dgate, x .* mask_x, h .* mask_h) to the accumulator; one product at flush time
-      rc = dyb200_wgrad_push_batched(deferred, B, dpre, G, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx, &batch);
+      if (at_col) rc = dyb200_wgrad_pack_a_at(deferred, deferred_col, B, dpre, G, ctx, &batch);
+      else rc = dyb200_wgrad_push_batched(deferred, B, dpre, G, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx, &batch);
       if (rc) return rc;
     }
     if (tensor_path && (rc = dyb200_tc_pack(ctx, dpre, G, true, B, G, nullptr, 0, 0, &dn, &batch))) return rc;    // rows = batch, K = 4H

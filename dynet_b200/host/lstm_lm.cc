@@ -202,8 +202,9 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
                       cb = to_c(store[4]), cmx, cmh, cg = to_c(tg), cc = to_c(tc), ch = to_c(th);
         if (c.dropout) { cmx = to_c(store[5]); cmh = to_c(store[6]); }
         dyb200_lstm_gates_attrs at = {c.dropout ? 1 : 0, 0.f, 1.f};
-        throw_status(dev, dyb200_vanilla_lstm_fwd_fused(&cx, &chp, &ccp, &cWx, &cWh, &cb, c.dropout ? &cmx : nullptr,
-                                                        c.dropout ? &cmh : nullptr, &at, &cg, &cc, &ch, dev.ctx));
+        // (the inputs of this step are also placed in the layer's weight-gradient accumulator, at the step's columns)
+        throw_status(dev, dyb200_vanilla_lstm_fwd_fused_at(&cx, &chp, &ccp, &cWx, &cWh, &cb, c.dropout ? &cmx : nullptr,
+                                                           c.dropout ? &cmh : nullptr, &at, &cg, &cc, &ch, m.wg_layer[l], t * B, dev.ctx));
         continue;
       }
       gates_node.forward_dev_impl(dev, xs, tg);
@@ -275,9 +276,9 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
                       cdcp = to_c(tdcp2), cgWx = to_c(gWx2), cgWh = to_c(gWh2), cgb = to_c(gb2);
         if (c.dropout) { cmx = to_c(store[5]); cmh = to_c(store[6]); }
         dyb200_lstm_gates_attrs at = {c.dropout ? 1 : 0, 0.f, 1.f};
-        throw_status(dev, dyb200_vanilla_lstm_bwd_fused(&cx, &chp, &ccp, &cWx, &cWh, c.dropout ? &cmx : nullptr, c.dropout ? &cmh : nullptr,
-                                                        &cg, &cc, &cdh, &cdc, &cdx, tt > 0 ? &cdhp : nullptr, tt > 0 ? &cdcp : nullptr,
-                                                        &cgWx, &cgWh, &cgb, &at, m.wg_layer[l], dev.ctx));
+        throw_status(dev, dyb200_vanilla_lstm_bwd_fused_at(&cx, &chp, &ccp, &cWx, &cWh, c.dropout ? &cmx : nullptr, c.dropout ? &cmh : nullptr,
+                                                           &cg, &cc, &cdh, &cdc, &cdx, tt > 0 ? &cdhp : nullptr, tt > 0 ? &cdcp : nullptr,
+                                                           &cgWx, &cgWh, &cgb, &at, m.wg_layer[l], tt * B, dev.ctx));
         continue;
       }
       h_node.backward_dev_impl(dev, {&tc, &tg}, th, tdh, 0, tdc);

@@ -230,6 +230,26 @@ int dyb200_vanilla_lstm_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h
                                   dyb200_tensor* db, const dyb200_lstm_gates_attrs* attrs, struct dyb200_wgrad* deferred,
                                   dyb200_ctx* ctx);
 
+/* The same two calls for a caller that knows the time step: with `deferred` non-NULL the forward call also places the
+ * layer inputs (x .* mask_x, h_tm1 .* mask_h: the B operands of this step's weight-gradient products) at columns
+ * [deferred_col, deferred_col + batch) of the accumulator, in the same launch that splits them for the gate product, and
+ * the backward call writes only the gate gradient there - no operand-splitting launch remains in the backward step.
+ * Use the same column for a step in both calls (e.g. t * batch).  deferred_col = DYB200_WGRAD_APPEND in the backward call
+ * gives the behaviour of dyb200_vanilla_lstm_bwd_fused. */
+#define DYB200_WGRAD_APPEND 0xffffffffu
+int dyb200_vanilla_lstm_fwd_fused_at(const dyb200_tensor* x, const dyb200_tensor* h_tm1, const dyb200_tensor* c_tm1,
+                                     const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* b,
+                                     const dyb200_tensor* mask_x, const dyb200_tensor* mask_h,
+                                     const dyb200_lstm_gates_attrs* attrs, dyb200_tensor* gates, dyb200_tensor* c_t,
+                                     dyb200_tensor* h_t, struct dyb200_wgrad* deferred, uint32_t deferred_col, dyb200_ctx* ctx);
+int dyb200_vanilla_lstm_bwd_fused_at(const dyb200_tensor* x, const dyb200_tensor* h_tm1, const dyb200_tensor* c_tm1,
+                                     const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* mask_x,
+                                     const dyb200_tensor* mask_h, const dyb200_tensor* gates, const dyb200_tensor* c_t,
+                                     const dyb200_tensor* dEdh, const dyb200_tensor* dEdc, dyb200_tensor* dx,
+                                     dyb200_tensor* dh_tm1, dyb200_tensor* dc_tm1, dyb200_tensor* dWx, dyb200_tensor* dWh,
+                                     dyb200_tensor* db, const dyb200_lstm_gates_attrs* attrs, struct dyb200_wgrad* deferred,
+                                     uint32_t deferred_col, dyb200_ctx* ctx);
+
 /* Deferred parameter-gradient products.  A parameter shared by all time steps (Wx, Wh of an LSTM layer; the
  * output projection) receives dW += A_t * B_t^T from every step (dynet/nodes-lstm.cc:419-500: dgate * x^T summed over
  * the batch; dynet/nodes-matrixmultiply.cc:61-74).  An accumulator keeps the packed operands of every step side by

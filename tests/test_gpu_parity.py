@@ -1001,3 +1001,61 @@ def test_lstm_fwd_fused_cell_epilogue(oracle, g, capi, I, H, B, masks):
     assert_close(g.host(oc), c_t, TOL_REDUCE, floor=GEMM_FLOOR, what="c")
     assert_close(g.host(oh), h_t, TOL_REDUCE, floor=GEMM_FLOOR, what="h")
     assert g.ctx().device_errors() == 0
+
+
+@pytest.mark.parametrize("I,H,B", [(64, 64, 32), (128, 256, 64), (96, 64, 17)])
+def test_lstm_fused_at_columns_equals_append(g, capi, I, H, B):
+    """Two time steps through the *_fused_at pair (the forward call places the layer inputs at the step's columns of the
+    accumulator, the backward call only the gate gradient, in reverse time order) give the weight gradients of the append
+    form, in which every backward call pushes both."""
+    r = rng(156)
+    T = 2
+    Wx, Wh, b = glorot(r, 4 * H, I), glorot(r, 4 * H, H), randn(r, 4 * H, scale=0.1)
+    mx = ((r.random((B, I)) < 0.8) / 0.8).astype(np.float32)
+    mh = ((r.random((B, H)) < 0.8) / 0.8).astype(np.float32)
+    xs = [randn(r, B, I) for _ in range(T)]
+    dhs = [randn(r, B, H) for _ in range(T)]
+    at = capi.LstmGatesAttrs(1, 0.0, 1.0)
+    D = {k: g.dev(v) for k, v in dict(Wx=Wx, Wh=Wh, b=b, mx=mx, mh=mh).items()}
+    tWx, tWh, tb, tmx, tmh = g.T(D["Wx"], [4 * H, I], 1), g.T(D["Wh"], [4 * H, H], 1), g.T(D["b"], [4 * H], 1), g.T(D["mx"]), g.T(D["mh"])
+
+    def run(mode):
+        import torch
+        w = g.ctx().wgrad_create(4 * H, I, H, T * B)
+        try:
+            h = [torch.zeros(B, H, device="cuda")] + [torch.empty(B, H, device="cuda") for _ in range(T)]
+            c = [torch.zeros(B, H, device="cuda")] + [torch.empty(B, H, device="cuda") for _ in range(T)]
+            gates = [torch.empty(B, 4 * H, device="cuda") for _ in range(T)]
+            xd = [g.dev(x) for x in xs]
+            for t in range(T):
+                args = (g.T(xd[t]), g.T(h[t]), g.T(c[t]), tWx, tWh, tb, tmx, tmh, at, g.T(gates[t]), g.T(c[t + 1]), g.T(h[t + 1]))
+                if mode == "at":
+                    g.ctx().lstm_fwd_fused_at(*args, w, t * B)
+                else:
+                    g.ctx().lstm_fwd_fused(*args)
+            dh = [g.dev(d) for d in dhs]
+            dc = [torch.zeros(B, H, device="cuda") for _ in range(T)]
+            dx = [torch.zeros(B, I, device="cuda") for _ in range(T)]
+            db = torch.zeros(4 * H, device="cuda")
+            for t in range(T - 1, -1, -1):
+                args = (g.T(xd[t]), g.T(h[t]), g.T(c[t]), tWx, tWh, tmx, tmh, g.T(gates[t]), g.T(c[t + 1]), g.T(dh[t]), g.T(dc[t]), g.T(dx[t]),
+                        None if t == 0 else g.T(dh[t - 1]), None if t == 0 else g.T(dc[t - 1]), None, None, g.T(db, [4 * H], 1), at)
+                if mode == "at":
+                    g.ctx().lstm_bwd_fused_at(*args, w, t * B)
+                else:
+                    g.ctx().lstm_bwd_fused(*args, w)
+            dWx, dWh = torch.zeros(I, 4 * H, device="cuda"), torch.zeros(H, 4 * H, device="cuda")
+            g.ctx().wgrad_flush(w, dWx.data_ptr(), 4 * H, dWh.data_ptr(), 4 * H)
+            torch.cuda.synchronize()
+            return [g.host(v) for v in (dWx, dWh, db, dx[0], dx[1], h[T], c[T])]
+        finally:
+            g.ctx().wgrad_destroy(w)
+
+    a, p = run("at"), run("append")
+    names = ["dWx", "dWh", "db", "dx0", "dx1", "h", "c"]
+    for name, u, v in zip(names, a, p):
+        if name in ("dWx", "dWh"):     # the steps sit in a different order along K: same sum, different association
+            assert_close(u, v, TOL_REDUCE, floor=max(1.0, float(np.abs(v).max()) * 0.05), what=name)
+        else:
+            assert np.array_equal(u, v), name
+    assert g.ctx().device_errors() == 0
