@@ -442,14 +442,25 @@ __global__ void __launch_bounds__(256) k_splitk_reduce_cell(const float* __restr
     const uint32_t u = 4 * (uint32_t)(q % H4), n = (uint32_t)(q / H4);
     const uint32_t row0 = 128 * (u / 32) + (u % 32);   // interleaved row of gate 0; gate g is 32 g rows further
     float4 a[4];
+    // all loads of up to four splits are issued before the first add (this kernel is latency-bound at small batch)
+    for (uint32_t s0 = 0; s0 < S; s0 += 4) {
+      float4 v[4][4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          v[k][g] = s0 + k < S ? ld4_stream(part + row0 + 32 * g + (size_t)M * n + (size_t)(s0 + k) * MN) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (s0 == 0) a[g] = v[0][g];
+        else { a[g].x += v[0][g].x; a[g].y += v[0][g].y; a[g].z += v[0][g].z; a[g].w += v[0][g].w; }
+#pragma unroll
+        for (int k = 1; k < 4; ++k)
+          if (s0 + k < S) { a[g].x += v[k][g].x; a[g].y += v[k][g].y; a[g].z += v[k][g].z; a[g].w += v[k][g].w; }
+      }
+    }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      const float* p = part + row0 + 32 * g + (size_t)M * n;
-      a[g] = ld4_stream(p);
-      for (uint32_t s2 = 1; s2 < S; ++s2) {
-        const float4 v = ld4_stream(p + (size_t)s2 * MN);
-        a[g].x += v.x; a[g].y += v.y; a[g].z += v.z; a[g].w += v.w;
-      }
       const float4 b = ld4(epi.bias + (size_t)g * H + u);
       const float fb = g == 1 ? epi.forget_bias : 0.f;
       a[g].x += b.x + fb; a[g].y += b.y + fb; a[g].z += b.z + fb; a[g].w += b.w + fb;

@@ -211,6 +211,8 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd(const float* __restrict__
 // dt_pitch), which saves the packing pass over dpre; db += row sums, formed as per-tile partial sums that the last
 // CTA of each 64-unit stripe to arrive adds in ascending tile order (deterministic; counters[] returns to zero).
 constexpr int kCT_J = 64, kCT_B = 32;
+// JT = hidden units per tile: 64 (two columns per thread) or, for grids that would leave most SMs idle, 32 (one column)
+template <int JT>
 __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __restrict__ c_t, const float* __restrict__ c_tm1,
                                                             const float* __restrict__ gates, const float* __restrict__ dEdh,
                                                             const float* __restrict__ dEdc, float* __restrict__ dc_tm1,
@@ -219,14 +221,15 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __rest
                                                             uint32_t dt_pitch, float* __restrict__ db, float* __restrict__ part,
                                                             uint32_t* __restrict__ counters, uint32_t H, uint32_t B) {
   dyb_grid_dep_sync();
-  __shared__ float tile[4][kCT_J][kCT_B + 1];
+  __shared__ float tile[4][JT][kCT_B + 1];
   __shared__ uint32_t is_last;
-  const uint32_t j0 = blockIdx.x * kCT_J, b0 = blockIdx.y * kCT_B;
-  const uint32_t tq = threadIdx.x & 15, tb = threadIdx.x >> 4;   // hidden-unit quad, batch lane (two columns each)
+  constexpr int kQuads = JT / 4, kLanes = 256 / kQuads, kCols = kCT_B / kLanes;   // 16 x 16 x 2 or 8 x 32 x 1
+  const uint32_t j0 = blockIdx.x * JT, b0 = blockIdx.y * kCT_B;
+  const uint32_t tq = threadIdx.x % kQuads, tb = threadIdx.x / kQuads;   // hidden-unit quad, batch lane
   const uint32_t j = j0 + 4 * tq;
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const uint32_t bl = tb + 16 * half, b = b0 + bl;
+  for (int half = 0; half < kCols; ++half) {
+    const uint32_t bl = tb + kLanes * half, b = b0 + bl;
     const size_t e = (size_t)b * H + j;
     const float* g = gates + (size_t)b * 4 * H + j;
     const float4 gi = ld4(g), gf = ld4(g + H), go = ld4(g + 2 * H), gg = ld4(g + 3 * H);
@@ -277,8 +280,8 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __rest
   __syncthreads();
   // transposed write-out and row sums: warp w takes rows w, w + 8, ... of the 256 (gate, unit) rows; lane = batch column
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (uint32_t r = warp; r < 4 * kCT_J; r += 8) {
-    const uint32_t gate = r / kCT_J, jl = r % kCT_J;
+  for (uint32_t r = warp; r < 4 * JT; r += 8) {
+    const uint32_t gate = r / JT, jl = r % JT;
     const float v = tile[gate][jl][lane];
     const size_t row = (size_t)gate * H + j0 + jl;
     if (dt_hi) {
@@ -299,10 +302,10 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __rest
     if (is_last) counters[blockIdx.x] = 0;
   }
   __syncthreads();
-  if (is_last) {
+  if (is_last && threadIdx.x < 4 * JT) {
     __threadfence();
-    const uint32_t r = threadIdx.x;   // 256 threads = 4 gates x 64 units
-    const size_t row = (size_t)(r / kCT_J) * H + j0 + r % kCT_J;
+    const uint32_t r = threadIdx.x;   // one thread per (gate, unit) row of the stripe
+    const size_t row = (size_t)(r / JT) * H + j0 + r % JT;
     float acc = 0.f;
     uint32_t t = 0;
     for (; t + 8 <= gridDim.y; t += 8) {   // eight loads in flight, added in tile order
@@ -650,9 +653,16 @@ int dyb200_vanilla_lstm_bwd_fused_at(const dyb200_tensor* x, const dyb200_tensor
     }
     void* pp;
     if ((rc = dyb200_scratch(ctx, (size_t)(B / kCT_B) * G * sizeof(float), &pp))) return rc;
-    dyb_launch(k_lstm_cell_bwd_tiled, dim3(H / kCT_J, B / kCT_B), 256, 0, ctx, 
-        c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr, dc_tm1 ? dc_tm1->v : nullptr, nullptr, dn.hi, dn.lo, dn.pitch,
-        a_hi, a_lo, a_pitch, db->v, (float*)pp, ctx->dev_flags + DYB200_DEV_COUNTER0, H, B);
+    // half-height tiles when full ones would leave most SMs without a CTA (small per-GPU batches)
+    const bool small_grid = (H / kCT_J) * (B / kCT_B) < (uint32_t)ctx->sm_count && H / 32 <= DYB200_DEV_COUNTERS;
+    if (small_grid)
+      dyb_launch(k_lstm_cell_bwd_tiled<32>, dim3(H / 32, B / kCT_B), 256, 0, ctx,
+                 c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr, dc_tm1 ? dc_tm1->v : nullptr, nullptr, dn.hi, dn.lo, dn.pitch,
+                 a_hi, a_lo, a_pitch, db->v, (float*)pp, ctx->dev_flags + DYB200_DEV_COUNTER0, H, B);
+    else
+      dyb_launch(k_lstm_cell_bwd_tiled<kCT_J>, dim3(H / kCT_J, B / kCT_B), 256, 0, ctx,
+                 c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr, dc_tm1 ? dc_tm1->v : nullptr, nullptr, dn.hi, dn.lo, dn.pitch,
+                 a_hi, a_lo, a_pitch, db->v, (float*)pp, ctx->dev_flags + DYB200_DEV_COUNTER0, H, B);
     DYB_LAUNCHED(ctx);
   } else {
     void* sp;
