@@ -58,6 +58,11 @@ def build_cases(torch, ctx, small):
         cases.append(Case(name + "_bwd", 4 * S, make, bwd, 4 * S))
 
     unary("tanh"); unary("logistic"); unary("rectify"); unary("elu", capi.EluAttrs(1.0, 1.0))
+    # yardstick, not a library kernel: a plain device copy of one config-3 tensor (what 2S of traffic can reach at this size;
+    # the 6551 GB/s peak was measured on 2 GB buffers)
+    def mk_copy():
+        return dict(x=torch.randn(R, Ccols, device=dev), y=torch.empty(R, Ccols, device=dev))
+    cases.append(Case("copy_reference_1024x4096", 2 * S, mk_copy, lambda b: b["y"].copy_(b["x"]), 2 * S))
 
     # the same kernels on 8x larger tensors ([8192, 4096], 134 MB each): launch ramp-up and tail no longer dominate
     RL = 8 * R

@@ -1059,3 +1059,29 @@ def test_lstm_fused_at_columns_equals_append(g, capi, I, H, B):
         else:
             assert np.array_equal(u, v), name
     assert g.ctx().device_errors() == 0
+
+
+def test_new_entry_points_reject_bad_arguments(g, capi):
+    """Argument errors come back as the reference's exception class (std::invalid_argument), never as a fault."""
+    r = rng(616)
+    x = g.dev(randn(r, 2, 3, 5))
+    y = g.dev(np.zeros((2, 3, 5), np.float32))
+    with pytest.raises(ValueError):     # PickRange: end beyond the dimension (nodes-select.cc:208)
+        g.ctx().fwd("pick_range", [g.T(x)], g.T(y), capi.PickRangeAttrs(2, 9, 0))
+    with pytest.raises(ValueError):     # PickRange: empty range
+        g.ctx().fwd("pick_range", [g.T(x)], g.T(y), capi.PickRangeAttrs(3, 3, 0))
+    with pytest.raises(ValueError):     # Concatenate: the other dimensions differ
+        g.ctx().fwd("concatenate", [g.T(x), g.T(g.dev(randn(r, 2, 4, 5)))], g.T(y), capi.DimAttrs(0))
+    with pytest.raises(ValueError):     # Sum: mismatched input dimensions
+        g.ctx().fwd("sum", [g.T(x), g.T(g.dev(randn(r, 2, 3, 4)))], g.T(y))
+    with pytest.raises(ValueError):     # SumDimension: nothing to reduce
+        g.ctx().fwd("sum_dim", [g.T(x)], g.T(y), capi.SumDimAttrs((C.c_uint * 2)(0, 0), 0, 0))
+    with pytest.raises(ValueError):     # RandomBernoulli: p is not a probability
+        g.ctx().fwd("random_bernoulli", [], g.T(y), capi.BernoulliAttrs(1.5, 1.0, 1, 0))
+    p_, g_ = g.dev(randn(r, 16)), g.dev(randn(r, 16))
+    hyper = capi.TrainerHyper(0.1, 5.0, 1.0, 0.9, 1e-8, 0.95, 0.9, 0.999, 0)
+    with pytest.raises(ValueError):     # Adam without its two state buffers
+        g.ctx().trainer_update("adam", p_.data_ptr(), g_.data_ptr(), [], 16, hyper)
+    with pytest.raises(ValueError):     # a zero weight-decay divisor
+        g.ctx().trainer_update("sgd", p_.data_ptr(), g_.data_ptr(), [], 16, capi.TrainerHyper(0.1, 5.0, 0.0, 0.9, 1e-8, 0.95, 0.9, 0.999, 0))
+    assert g.ctx().device_errors() == 0
