@@ -108,6 +108,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// BNT = columns of the output tile: 128, or 64 for products with N <= 64 (small per-GPU batches), where a 128-wide tile
+// would spend half of every MMA and half of the B traffic on padding.
+template <int BNT>
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ TmapPack tm, uint32_t M, uint32_t N,
                                                          uint32_t kb0, uint32_t kb1, uint32_t kb_per_split,
                                                          GemmEpilogue epi, uint32_t* flags) {
@@ -117,7 +120,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
   __shared__ uint32_t tmem_base_slot;
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  constexpr int TILE_B_BYTES = BNT * BK * 4;                      // one B plane of a stage
+  constexpr int STAGE_TX = 2 * TILE_BYTES + 2 * TILE_B_BYTES;     // bytes a stage receives (stages stay STAGE_BYTES apart)
+  const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * BNT;
   // k-blocks [kb_begin, kb_end) of the concatenated (pair 0, pair 1) range belong to this split
   const uint32_t kb_begin = blockIdx.z * kb_per_split;
   const uint32_t kb_end = min(kb0 + kb1, kb_begin + kb_per_split);
@@ -151,11 +156,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         const uint32_t g = kb_begin + it;
         const uint32_t pair = g < kb0 ? 0 : 1, kblk = pair ? g - kb0 : g;
         unsigned char* st = ring + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        mbar_expect_tx(&full_bar[s], STAGE_TX);
         tma_load_2d(st, &tm.t[4 * pair + 0], &full_bar[s], (int)(kblk * BK), (int)m0);
         tma_load_2d(st + TILE_BYTES, &tm.t[4 * pair + 1], &full_bar[s], (int)(kblk * BK), (int)m0);
         tma_load_2d(st + 2 * TILE_BYTES, &tm.t[4 * pair + 2], &full_bar[s], (int)(kblk * BK), (int)n0);
-        tma_load_2d(st + 3 * TILE_BYTES, &tm.t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), (int)n0);
+        tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), (int)n0);
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
     }
@@ -164,14 +169,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
       // This one thread issues every MMA of the tile, and the tensor pipe is only as busy as this loop is short:
       // descriptors of the three stages are built once, stage / phase / chunk counters are carried instead of divided,
       // and the 12 MMAs of a k-block go out in one block of PTX.
-      // instruction descriptor: D = f32, A = B = tf32, both K-major, N = 128, M = 128
-      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      // instruction descriptor: D = f32, A = B = tf32, both K-major, N = BNT, M = 128
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       uint64_t d_a_hi[STAGES], d_a_lo[STAGES], d_b_hi[STAGES], d_b_lo[STAGES];
 #pragma unroll
       for (int q = 0; q < STAGES; ++q) {
         const uint32_t base = smem_u32(ring + (size_t)q * STAGE_BYTES);
         d_a_hi[q] = umma_desc(base); d_a_lo[q] = umma_desc(base + TILE_BYTES);
-        d_b_hi[q] = umma_desc(base + 2 * TILE_BYTES); d_b_lo[q] = umma_desc(base + 3 * TILE_BYTES);
+        d_b_hi[q] = umma_desc(base + 2 * TILE_BYTES); d_b_lo[q] = umma_desc(base + 2 * TILE_BYTES + TILE_B_BYTES);
       }
       // The tensor core truncates when it aligns addends to the accumulator, a bias that grows with the length of
       // the accumulation chain.  So the chain is cut every kChunkKB k-blocks: chunk c accumulates into TMEM buffer
@@ -227,7 +232,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     if (epi.mode == EPI_LSTM_CELL) {
       const uint32_t u = blockIdx.x * 32 + 4 * (te & 7);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
+      for (int k = 0; k < BNT / 32; ++k) {
         const uint32_t n = n0 + (te >> 3) + 32 * k;
         cprev[k] = n < N ? ld4(epi.c_prev + u + (size_t)epi.H * n) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
@@ -241,15 +246,17 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
       const uint32_t buf = c & 1;
       if (!mbar_wait(&acc_full[buf], (c >> 1) & 1)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // (two 32-column loads: one 64-column load per flush measured slower)
-      float v[32];
-      const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32) << 16) + 2 * half * 32;
-      tmem_ld32(taddr, v);
+      if (64 * half < BNT) {   // (with a 64-column tile the second column half does not exist)
+        // (two 32-column loads: one 64-column load per flush measured slower)
+        float v[32];
+        const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32) << 16) + 2 * half * 32;
+        tmem_ld32(taddr, v);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) sum[j] += v[j];
-      tmem_ld32(taddr + 32, v);
+        for (int j = 0; j < 32; ++j) sum[j] += v[j];
+        tmem_ld32(taddr + 32, v);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) sum[32 + j] += v[j];
+        for (int j = 0; j < 32; ++j) sum[32 + j] += v[j];
+      }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -261,7 +268,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     // 16-byte vectors covering whole 512-byte columns of the tile.  Every epilogue warp reaches the named barrier,
     // whatever its waits did; a failed wait anywhere cancels the stores.
     float* tile = reinterpret_cast<float*>(ring);
-    {
+    if (64 * half < BNT) {
       float* col = tile + (size_t)(64 * half) * BM + quarter * 32 + lane;
 #pragma unroll
       for (int j = 0; j < 64; ++j) col[(size_t)j * BM] = sum[j];
@@ -280,7 +287,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
           if (q == 1) { bias[q].x += epi.forget_bias; bias[q].y += epi.forget_bias; bias[q].z += epi.forget_bias; bias[q].w += epi.forget_bias; }
         }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < BNT / 32; ++k) {
           const uint32_t c = (te >> 3) + 32 * k, n = n0 + c;
           if (n < N) {
             float4 g[4];
@@ -318,7 +325,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             const bool is_tanh = m >= 3 * epi.H;
             const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
 #pragma unroll 1
-            for (uint32_t c0 = te >> 5; c0 < BN; c0 += 64) {   // two batches of 8 columns, loads first
+            for (uint32_t c0 = te >> 5; c0 < BNT; c0 += 64) {   // batches of 8 columns, loads first
               float4 v[8], old[8], mk[8];
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
@@ -357,7 +364,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             const bool is_tanh = m >= 3 * epi.H;
             const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
 #pragma unroll 4
-            for (uint32_t c = te >> 7; c < BN; c += 2) {
+            for (uint32_t c = te >> 7; c < BNT; c += 2) {
               const uint32_t n = n0 + c;
               if (n >= N) break;
               float v = tile[(size_t)c * BM + r];
@@ -566,10 +573,11 @@ int get_encoder(dyb200_ctx* ctx, EncodeTiledFn* fn) {
 }
 
 // Plane of `rows` rows and K valid floats per row, row pitch `pitch` floats; box = 32 (k) x 128 (rows).
-int make_map(dyb200_ctx* ctx, EncodeTiledFn enc, CUtensorMap* map, float* plane, uint32_t rows, uint32_t K, uint32_t pitch) {
+int make_map(dyb200_ctx* ctx, EncodeTiledFn enc, CUtensorMap* map, float* plane, uint32_t rows, uint32_t K, uint32_t pitch,
+             uint32_t box_rows = BM) {
   cuuint64_t dims[2] = {K, rows};
   cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
-  cuuint32_t box[2] = {BK, BM};
+  cuuint32_t box[2] = {BK, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, plane, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -714,8 +722,11 @@ int dyb200_tc_param_gates(dyb200_ctx* ctx, const float* src, uint32_t ld, uint32
   return pack(ctx, src, ld, kLayoutGates, rows, K, nullptr, 0, 0, out->hi, out->lo, pitch, nullptr);
 }
 
+inline uint32_t tile_cols(uint32_t N) { return N <= 64 ? 64 : BN; }
+
 uint32_t dyb200_tc_splits(const dyb200_ctx* ctx, uint32_t M, uint32_t N, uint32_t kb_total) {
-  const uint32_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const uint32_t bn = tile_cols(N);
+  const uint32_t tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
   uint32_t S = 1;
   if (tiles * 2 <= (uint32_t)ctx->sm_count) {
     S = (uint32_t)ctx->sm_count / tiles;
@@ -750,9 +761,11 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {
-    DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     attr_set = true;
   }
+  const uint32_t bn = tile_cols(N);
   TmapPack tm;
   memset(&tm, 0, sizeof(tm));
   double flops = 0;
@@ -762,13 +775,13 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     flops += 2.0 * M * N * A[p].K;
     if ((rc = make_map(ctx, enc, &tm.t[4 * p + 0], A[p].hi, M, A[p].K, A[p].pitch))) return rc;
     if ((rc = make_map(ctx, enc, &tm.t[4 * p + 1], A[p].lo, M, A[p].K, A[p].pitch))) return rc;
-    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 2], B[p].hi, N, B[p].K, B[p].pitch))) return rc;
-    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 3], B[p].lo, N, B[p].K, B[p].pitch))) return rc;
+    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 2], B[p].hi, N, B[p].K, B[p].pitch, bn))) return rc;
+    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 3], B[p].lo, N, B[p].K, B[p].pitch, bn))) return rc;
   }
   if (npairs == 1) for (int k = 0; k < 4; ++k) tm.t[4 + k] = tm.t[k];
   uint32_t kb0 = round_up(A[0].K, 32) / BK, kb1 = npairs > 1 ? round_up(A[1].K, 32) / BK : 0;
   const uint32_t kb_total = kb0 + kb1;
-  dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN, 1);
+  dim3 grid((M + BM - 1) / BM, (N + bn - 1) / bn, 1);
   // Split K when the output has too few tiles to occupy the SMs (e.g. dx = W^T dgate: 16-32 tiles, K = 4096).
   uint32_t S = dyb200_tc_splits(ctx, M, N, kb_total);
   DYB_CHECK_ARG(ctx, epi.mode != EPI_LSTM_CELL || (M % BM == 0 && epi.H * 4 == M && epi.ldc % 4 == 0 && aligned16(epi.C) &&
@@ -789,7 +802,8 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   {
     // times the MMA kernel (and the split-K reduction); the packing launches show up in the step time
     GemmProfScope scope(ctx, flops, 1, M, N, kb_total * BK, (uint32_t)epi.mode);
-    dyb_launch(k_gemm_tc, grid, kThreads, SMEM_BYTES, ctx, tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
+    if (bn == 64) dyb_launch(k_gemm_tc<64>, grid, kThreads, SMEM_BYTES, ctx, tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
+    else dyb_launch(k_gemm_tc<128>, grid, kThreads, SMEM_BYTES, ctx, tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
     DYB_LAUNCHED(ctx);
     if (S > 1 && epi.mode == EPI_LSTM_CELL) {
       dyb_launch(k_splitk_reduce_cell, stream_grid(ctx, (size_t)M / 16 * N + 1, 256), 256, 0, ctx, part, S, M, N, epi);
