@@ -309,13 +309,13 @@ def run_gpu(args):
                     "frac": achieved / peak if peak else None,
                     # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the most frequent GEMM shape (the fused
                     # LSTM forward, M4096 N512 K2048), from the ncu capture summarised under profiles/; `achieved` averages all shapes
-                    "traffic": 81.57e6,
+                    "traffic": 81.97e6,
                     "kernel": "gemm_3xtf32_tcgen05" if which == "tensor" else "gemm_fp32_cuda_core",
                     "launches": g_n, "share_of_step_time": g_ms / ms_prof if ms_prof else None,
                     "measured_over": "the same %d steps issued launch by launch (%.2f ms/step) right after the timed region, "
                                      "which replays them as one CUDA graph" % (args.steps, ms_prof / args.steps),
-                    "traffic_note": "bytes per launch of the LSTM-forward GEMM shape (ncu: 77.8 MB read + 3.8 MB written = packed operands "
-                                    "and c_prev exactly once; algorithmic operand bytes 77.6 MB); tensor-bound kernel, DRAM at 15 % of peak",
+                    "traffic_note": "bytes per launch of the LSTM-forward GEMM shape (ncu: 77.7 MB read + 4.3 MB written = packed operands "
+                                    "and c_prev exactly once; algorithmic operand bytes 77.6 MB); tensor-bound kernel, DRAM at 19 % of peak",
                     "peak_source": "cuBLAS TF32 8192^3 measured in this run (%.0f TFLOP/s) / 3; bf16 peak of %s: %s TFLOP/s"
                                    % (tf32, peaks["source"], peaks["bf16_tflops"]),
                     "useful_tflop_per_step": flops_per_step(B) * world / 1e12}
