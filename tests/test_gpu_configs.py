@@ -170,7 +170,7 @@ def test_config3_full_size_sweep(oracle, g, capi, op):
         ctx.fwd(op, [g.T(x_)], g.T(y_), attrs)
         ctx.bwd(op, [g.T(x_)], g.T(y_), g.T(g.dev(up)), 0, g.T(d_), attrs)
         assert_close(g.host(y_), y_ref, 1e-5, floor=2e-2, what=op)
-        # (1 - y^2) amplifies a one-ulp difference of y near |y| = 1; judged against the O(1) scale of dy
+        # (1 - y^2) amplifies a one-ulp difference of y near |y| = 1; compared against the O(1) scale of dy
         assert_close(g.host(d_), d_ref, 1e-5, floor=0.1, what=op + " bwd")
     elif op == "cmult":
         b = randn(r, R, Cn)

@@ -13,12 +13,12 @@ from util import TOL_CWISE, TOL_REDUCE, assert_close, glorot, randn, rng, zipf_i
 pytestmark = pytest.mark.gpu
 
 # Backward results are dEdxi_before + gradient with dEdxi_before ~ N(0,1): rounding of the O(1) terms
-# (one ulp ~ 1e-7) sets the achievable absolute error, so sums that cancel are judged against that scale.
+# (one ulp ~ 1e-7) sets the achievable absolute error, so sums that cancel are compared against that scale.
 ACC_FLOOR = 0.25
 # Gate pre-activations are O(1) sums of hundreds of products.  The tensor pipe adds into its fp32
 # accumulator with truncation, so the 3xTF32 GEMM is good to ~1e-5 of that scale (measured: 7e-6
 # worst case over 32k outputs at K = 640), and the CPU sigmoid itself is a rational fit good to ~2e-7
-# absolute; gate / state values near zero are therefore judged against 0.1, not against themselves.
+# absolute; gate / state values near zero are therefore compared against 0.1, not against themselves.
 GEMM_FLOOR = 0.1
 
 GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_known_answers.json")))
