@@ -105,3 +105,40 @@ def test_lm_graph_replay_matches_eager(oracle):
         assert abs(loss_after - loss_ref) <= 1e-4 * abs(loss_ref)
         assert model.ctx.device_errors() == 0
         model.close()
+
+
+@pytest.mark.parametrize("rule", ["momentum", "adam"])
+def test_lm_training_with_other_trainers(oracle, rule):
+    """Three training steps with MomentumSGD / Adam: the gradients come from the LM driver, the clipped update from
+    dyb200_squared_norm + dyb200_trainer_update over the flat parameter buffer; the oracle applies the reference's
+    update statements tensor by tensor.  Parameters must agree after every step."""
+    import torch
+    from dynet_b200 import capi, lm
+    dims = dict(V=200, E=32, H=64, L=2, T=4, B=16)
+    V, E, H, L, T, B = (dims[k] for k in "VEHLTB")
+    hp = dict(momentum=dict(lr=0.01, momentum=0.9), adam=dict(lr=0.001, beta_1=0.9, beta_2=0.999, eps=1e-8))[rule]
+    nstate = 1 if rule == "momentum" else 2
+    model = lm.LstmLm(device=0, seed=5, dropout=False, **dims)
+    n = model.params.numel()
+    states = [torch.zeros(n, device="cuda") for _ in range(nstate)]
+    sumsq = torch.zeros(1, device="cuda")
+    p_ref = model.params_host()
+    s_ref = [[np.zeros_like(p) for p in p_ref] for _ in range(nstate)]
+    for step in range(3):
+        tokens, _ = lm.synthetic_batch(dims, seed=40 + step, dropout=0.0)
+        model.forward_backward(tokens, None)
+        g_ref = [np.zeros_like(p) for p in p_ref]
+        oracle.lstm_lm_fwdbwd((V, E, H, L, T, B), p_ref, g_ref, tokens, None, None)
+        gscale = oracle.clip_scale(g_ref, 5.0)
+        for k in range(len(p_ref)):
+            oracle.trainer_update(rule, p_ref[k], g_ref[k], [s[k] for s in s_ref], gscale=gscale, updates=step, **hp)
+        hyper = capi.TrainerHyper(hp["lr"], 5.0, 1.0, hp.get("momentum", 0.9), hp.get("eps", 1e-8), 0.95, hp.get("beta_1", 0.9),
+                                  hp.get("beta_2", 0.999), step)
+        model.ctx.squared_norm(model.grads.data_ptr(), n, sumsq.data_ptr())
+        model.ctx.trainer_update(rule, model.params.data_ptr(), model.grads.data_ptr(), [s.data_ptr() for s in states], n, hyper,
+                                 sumsq.data_ptr(), zero_grads=True)
+        for k, (got, want) in enumerate(zip(model.params_host(), p_ref)):
+            assert_close(got, want, 1e-4, floor=1e-1, what="%s: param %d after step %d" % (rule, k, step))
+        assert not model.grads_host()[0].any()
+    assert model.ctx.device_errors() == 0
+    model.close()
