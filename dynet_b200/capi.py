@@ -132,7 +132,8 @@ def exported_symbols():
 
 
 def lib_path():
-    return os.path.join(_HERE, "libdyb200.so")
+    """The in-tree library; DYB200_LIB names another build of it (kernel experiments)."""
+    return os.environ.get("DYB200_LIB") or os.path.join(_HERE, "libdyb200.so")
 
 
 def lib():

@@ -17,9 +17,12 @@
 //              hidden unit from the tile and also forms c and h
 // Products with few output tiles are split along K over blockIdx.z; the splits store raw partial
 // tiles and a second kernel adds them in split order and applies the epilogue (deterministic).
+// Products with more tiles than SMs run on a persistent variant (one CTA per SM walks the tiles) whose
+// epilogue overlaps the next tile's main loop.
 // Every mbarrier wait is bounded; a wait that runs out sets DYB200_FLAG_WAIT_TIMEOUT and the
 // kernel still frees its TMEM and returns.
 #include <cuda.h>
+#include <math.h>
 
 #include "gemm.cuh"
 
@@ -108,6 +111,143 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// The 12 MMAs of one 32-wide k-block (3 products x 4 k-steps of 8) as one block of PTX.  The first MMA accumulates iff
+// `accumulate` is non-zero (0 opens a new accumulation chain).
+__device__ __forceinline__ void issue_kblock(uint32_t acc, uint64_t a_hi, uint64_t a_lo, uint64_t b_hi, uint64_t b_lo,
+                                             uint32_t idesc, uint32_t accumulate) {
+  // one MMA consumes 8 tf32 = 32 bytes of K: +2 in descriptor units per k8 step
+  asm volatile(
+      "{\n\t.reg .pred pf, pt;\n\t.reg .b64 xa, xb, ya, yb;\n\t"
+      "setp.ne.b32 pf, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %2, %3, %5, pf;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %4, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %3, %5, pt;\n\t"
+      "add.s64 xa, %1, 2;\n\tadd.s64 xb, %2, 2;\n\tadd.s64 ya, %3, 2;\n\tadd.s64 yb, %4, 2;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t"
+      "add.s64 xa, %1, 4;\n\tadd.s64 xb, %2, 4;\n\tadd.s64 ya, %3, 4;\n\tadd.s64 yb, %4, 4;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t"
+      "add.s64 xa, %1, 6;\n\tadd.s64 xb, %2, 6;\n\tadd.s64 ya, %3, 6;\n\tadd.s64 yb, %4, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t}"
+      ::"r"(acc), "l"(a_hi), "l"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The cooperative pass over NC finished columns parked in shared memory (column-major, BM rows per column): called by
+// NT epilogue threads (te = 0..NT-1).  mt is the tile's row-block index (m0 = BM mt), n0 the global column of the first
+// parked column, cprev the previous cell states the caller fetched for EPI_LSTM_CELL (hidden units
+// [32 mt + 4 (te % 8), +4), columns n0 + te / 8 + (NT / 8) k).
+template <int NC, int NT>
+__device__ __forceinline__ void epilogue_pass(const GemmEpilogue& epi, const float* tile, uint32_t te, uint32_t mt, uint32_t m0,
+                                              uint32_t n0, uint32_t M, uint32_t N, const float4 (&cprev)[4]) {
+  if (epi.mode == EPI_LSTM_CELL) {
+    // rows 32 q + l of the tile are gate q (i, f, o, g) of hidden unit 32 mt + l
+    const uint32_t l = 4 * (te & 7), u = mt * 32 + l;
+    float4 bias[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      bias[q] = ld4(epi.bias + (size_t)q * epi.H + u);
+      if (q == 1) { bias[q].x += epi.forget_bias; bias[q].y += epi.forget_bias; bias[q].z += epi.forget_bias; bias[q].w += epi.forget_bias; }
+    }
+#pragma unroll
+    for (int k = 0; k < NC / (NT / 8); ++k) {
+      const uint32_t c = (te >> 3) + (NT / 8) * k, n = n0 + c;
+      if (n < N) {
+        float4 g[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float4 a = ld4(tile + (size_t)c * BM + 32 * q + l);
+          const float4 x = make_float4(a.x + bias[q].x, a.y + bias[q].y, a.z + bias[q].z, a.w + bias[q].w);
+          g[q] = q == 3 ? make_float4(gate_tanh(x.x), gate_tanh(x.y), gate_tanh(x.z), gate_tanh(x.w))
+                        : make_float4(gate_sigmoid(x.x), gate_sigmoid(x.y), gate_sigmoid(x.z), gate_sigmoid(x.w));
+          st4(epi.C + (size_t)q * epi.H + u + (size_t)epi.ldc * n, g[q]);
+        }
+        const size_t e = u + (size_t)epi.H * n;
+        const float4 cn = make_float4(lstm_cell_c(g[0].x, g[3].x, g[1].x, cprev[k].x), lstm_cell_c(g[0].y, g[3].y, g[1].y, cprev[k].y),
+                                      lstm_cell_c(g[0].z, g[3].z, g[1].z, cprev[k].z), lstm_cell_c(g[0].w, g[3].w, g[1].w, cprev[k].w));
+        st4(epi.c_out + e, cn);
+        st4(epi.h_out + e, make_float4(lstm_cell_h(g[2].x, cn.x), lstm_cell_h(g[2].y, cn.y), lstm_cell_h(g[2].z, cn.z), lstm_cell_h(g[2].w, cn.w)));
+      }
+    }
+  } else {
+    const bool vec = (M & 3) == 0 && (epi.split_m & 3) == 0 && (epi.ldc & 3) == 0 && aligned16(epi.C) &&
+                     (epi.split_m == 0 || ((epi.ldc2 & 3) == 0 && aligned16(epi.C2))) &&
+                     (epi.mode != EPI_BIAS || aligned16(epi.bias)) && (epi.mode != EPI_GATES || (aligned16(epi.bias) && (epi.H & 3) == 0)) &&
+                     (epi.mode != EPI_ACCUM_MASK ||
+                      (aligned16(epi.maskC) && (!epi.maskc_full || (epi.maskc_ld & 3) == 0) &&
+                       (epi.split_m == 0 || (aligned16(epi.maskC2) && (!epi.maskc2_full || (epi.maskc2_ld & 3) == 0)))));
+    if (vec) {
+      // 32 row quads x NC columns; a thread keeps its row quad and walks the columns te / 32 + (NT / 32) k
+      const uint32_t rq = te & 31, m = m0 + 4 * rq;
+      if (m < M) {
+        const EpiRow row = epi_row(epi, m);
+        const size_t ldc = row.ldc;
+        float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (epi.mode == EPI_BIAS || epi.mode == EPI_GATES) bias = ld4(epi.bias + m);
+        if (epi.mode == EPI_GATES && m >= epi.H && m < 2 * epi.H) { bias.x += epi.forget_bias; bias.y += epi.forget_bias; bias.z += epi.forget_bias; bias.w += epi.forget_bias; }
+        const bool is_tanh = m >= 3 * epi.H;
+        const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
+#pragma unroll 1
+        for (uint32_t c0 = te >> 5; c0 < NC; c0 += 8 * (NT / 32)) {   // batches of 8 columns, loads first
+          float4 v[8], old[8], mk[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t c = c0 + (NT / 32) * k, n = n0 + c;
+            v[k] = ld4(tile + (size_t)c * BM + 4 * rq);
+            if (epi.mode == EPI_ACCUM || epi.mode == EPI_ACCUM_MASK) old[k] = n < N ? __ldcg(reinterpret_cast<const float4*>(row.c + ldc * n)) : v[k];
+            if (epi.mode == EPI_ACCUM_MASK) mk[k] = n < N ? ld4(row.mask + mstep * n) : v[k];
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t n = n0 + c0 + (NT / 32) * k;
+            if (n >= N) continue;
+            float4 r = v[k];
+            if (epi.mode == EPI_BIAS) { r.x += bias.x; r.y += bias.y; r.z += bias.z; r.w += bias.w; }
+            else if (epi.mode == EPI_GATES) {
+              r = make_float4(r.x + bias.x, r.y + bias.y, r.z + bias.z, r.w + bias.w);
+              r = is_tanh ? make_float4(gate_tanh(r.x), gate_tanh(r.y), gate_tanh(r.z), gate_tanh(r.w))
+                          : make_float4(gate_sigmoid(r.x), gate_sigmoid(r.y), gate_sigmoid(r.z), gate_sigmoid(r.w));
+            } else if (epi.mode == EPI_ACCUM) { r.x += old[k].x; r.y += old[k].y; r.z += old[k].z; r.w += old[k].w; }
+            else if (epi.mode == EPI_ACCUM_MASK) {
+              r = make_float4(old[k].x + r.x * mk[k].x, old[k].y + r.y * mk[k].y, old[k].z + r.z * mk[k].z, old[k].w + r.w * mk[k].w);
+            }
+            st4(row.c + ldc * n, r);
+          }
+        }
+      }
+    } else {
+      // any shape / alignment: one row per thread pair of columns, scalar accesses
+      const uint32_t r = te & 127, m = m0 + r;
+      if (m < M) {
+        const EpiRow row = epi_row(epi, m);
+        const size_t ldc = row.ldc;
+        float bias = 0.f;
+        if (epi.mode == EPI_BIAS || epi.mode == EPI_GATES) bias = epi.bias[m];
+        if (epi.mode == EPI_GATES && m >= epi.H && m < 2 * epi.H) bias += epi.forget_bias;
+        const bool is_tanh = m >= 3 * epi.H;
+        const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
+#pragma unroll 4
+        for (uint32_t c = te >> 7; c < NC; c += NT / 128) {
+          const uint32_t n = n0 + c;
+          if (n >= N) break;
+          float v = tile[(size_t)c * BM + r];
+          float* dst = row.c + ldc * n;
+          if (epi.mode == EPI_STORE) *dst = v;
+          else if (epi.mode == EPI_BIAS) *dst = v + bias;
+          else if (epi.mode == EPI_GATES) *dst = is_tanh ? gate_tanh(v + bias) : gate_sigmoid(v + bias);
+          else if (epi.mode == EPI_ACCUM) *dst += v;
+          else *dst += v * row.mask[mstep * n];
+        }
+      }
+    }
+  }
+}
+
 // BNT = columns of the output tile: 128, or 64 for products with N <= 64 (small per-GPU batches), where a 128-wide tile
 // would spend half of every MMA and half of the B traffic on padding.
 template <int BNT>
@@ -193,27 +333,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         else if (s == 1) { a_hi = d_a_hi[1]; a_lo = d_a_lo[1]; b_hi = d_b_hi[1]; b_lo = d_b_lo[1]; }
         else { a_hi = d_a_hi[2]; a_lo = d_a_lo[2]; b_hi = d_b_hi[2]; b_lo = d_b_lo[2]; }
         const uint32_t acc = tmem_base + buf * BN;
-        // one MMA consumes 8 tf32 = 32 bytes of K: +2 in descriptor units per k8 step
-        asm volatile(
-            "{\n\t.reg .pred pf, pt;\n\t.reg .b64 xa, xb, ya, yb;\n\t"
-            "setp.ne.b32 pf, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %2, %3, %5, pf;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %4, %5, pt;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %3, %5, pt;\n\t"
-            "add.s64 xa, %1, 2;\n\tadd.s64 xb, %2, 2;\n\tadd.s64 ya, %3, 2;\n\tadd.s64 yb, %4, 2;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t"
-            "add.s64 xa, %1, 4;\n\tadd.s64 xb, %2, 4;\n\tadd.s64 ya, %3, 4;\n\tadd.s64 yb, %4, 4;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t"
-            "add.s64 xa, %1, 6;\n\tadd.s64 xb, %2, 6;\n\tadd.s64 ya, %3, 6;\n\tadd.s64 yb, %4, 6;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t}"
-            ::"r"(acc), "l"(a_hi), "l"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(in_chunk)
-            : "memory");
+        issue_kblock(acc, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk);
         umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
         const bool chunk_ends = in_chunk == kChunkKB - 1 || it == total - 1;
         if (chunk_ends) { umma_commit(&acc_full[buf]); in_chunk = 0; ++chunk; buf ^= 1; }
@@ -277,107 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, 1, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
     if (all_ok) {
-      if (epi.mode == EPI_LSTM_CELL) {
-        // rows 32 q + l of the tile are gate q (i, f, o, g) of hidden unit 32 blockIdx.x + l
-        const uint32_t l = 4 * (te & 7), u = blockIdx.x * 32 + l;
-        float4 bias[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          bias[q] = ld4(epi.bias + (size_t)q * epi.H + u);
-          if (q == 1) { bias[q].x += epi.forget_bias; bias[q].y += epi.forget_bias; bias[q].z += epi.forget_bias; bias[q].w += epi.forget_bias; }
-        }
-#pragma unroll
-        for (int k = 0; k < BNT / 32; ++k) {
-          const uint32_t c = (te >> 3) + 32 * k, n = n0 + c;
-          if (n < N) {
-            float4 g[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float4 a = ld4(tile + (size_t)c * BM + 32 * q + l);
-              const float4 x = make_float4(a.x + bias[q].x, a.y + bias[q].y, a.z + bias[q].z, a.w + bias[q].w);
-              g[q] = q == 3 ? make_float4(gate_tanh(x.x), gate_tanh(x.y), gate_tanh(x.z), gate_tanh(x.w))
-                            : make_float4(gate_sigmoid(x.x), gate_sigmoid(x.y), gate_sigmoid(x.z), gate_sigmoid(x.w));
-              st4(epi.C + (size_t)q * epi.H + u + (size_t)epi.ldc * n, g[q]);
-            }
-            const size_t e = u + (size_t)epi.H * n;
-            const float4 cn = make_float4(lstm_cell_c(g[0].x, g[3].x, g[1].x, cprev[k].x), lstm_cell_c(g[0].y, g[3].y, g[1].y, cprev[k].y),
-                                          lstm_cell_c(g[0].z, g[3].z, g[1].z, cprev[k].z), lstm_cell_c(g[0].w, g[3].w, g[1].w, cprev[k].w));
-            st4(epi.c_out + e, cn);
-            st4(epi.h_out + e, make_float4(lstm_cell_h(g[2].x, cn.x), lstm_cell_h(g[2].y, cn.y), lstm_cell_h(g[2].z, cn.z), lstm_cell_h(g[2].w, cn.w)));
-          }
-        }
-      } else {
-        const bool vec = (M & 3) == 0 && (epi.split_m & 3) == 0 && (epi.ldc & 3) == 0 && aligned16(epi.C) &&
-                         (epi.split_m == 0 || ((epi.ldc2 & 3) == 0 && aligned16(epi.C2))) &&
-                         (epi.mode != EPI_BIAS || aligned16(epi.bias)) && (epi.mode != EPI_GATES || (aligned16(epi.bias) && (epi.H & 3) == 0)) &&
-                         (epi.mode != EPI_ACCUM_MASK ||
-                          (aligned16(epi.maskC) && (!epi.maskc_full || (epi.maskc_ld & 3) == 0) &&
-                           (epi.split_m == 0 || (aligned16(epi.maskC2) && (!epi.maskc2_full || (epi.maskc2_ld & 3) == 0)))));
-        if (vec) {
-          // 32 row quads x 128 columns; a thread keeps its row quad and walks the columns te / 32 + 8 k
-          const uint32_t rq = te & 31, m = m0 + 4 * rq;
-          if (m < M) {
-            const EpiRow row = epi_row(epi, m);
-            const size_t ldc = row.ldc;
-            float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (epi.mode == EPI_BIAS || epi.mode == EPI_GATES) bias = ld4(epi.bias + m);
-            if (epi.mode == EPI_GATES && m >= epi.H && m < 2 * epi.H) { bias.x += epi.forget_bias; bias.y += epi.forget_bias; bias.z += epi.forget_bias; bias.w += epi.forget_bias; }
-            const bool is_tanh = m >= 3 * epi.H;
-            const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
-#pragma unroll 1
-            for (uint32_t c0 = te >> 5; c0 < BNT; c0 += 64) {   // batches of 8 columns, loads first
-              float4 v[8], old[8], mk[8];
-#pragma unroll
-              for (int k = 0; k < 8; ++k) {
-                const uint32_t c = c0 + 8 * k, n = n0 + c;
-                v[k] = ld4(tile + (size_t)c * BM + 4 * rq);
-                if (epi.mode == EPI_ACCUM || epi.mode == EPI_ACCUM_MASK) old[k] = n < N ? __ldcg(reinterpret_cast<const float4*>(row.c + ldc * n)) : v[k];
-                if (epi.mode == EPI_ACCUM_MASK) mk[k] = n < N ? ld4(row.mask + mstep * n) : v[k];
-              }
-#pragma unroll
-              for (int k = 0; k < 8; ++k) {
-                const uint32_t n = n0 + c0 + 8 * k;
-                if (n >= N) continue;
-                float4 r = v[k];
-                if (epi.mode == EPI_BIAS) { r.x += bias.x; r.y += bias.y; r.z += bias.z; r.w += bias.w; }
-                else if (epi.mode == EPI_GATES) {
-                  r = make_float4(r.x + bias.x, r.y + bias.y, r.z + bias.z, r.w + bias.w);
-                  r = is_tanh ? make_float4(gate_tanh(r.x), gate_tanh(r.y), gate_tanh(r.z), gate_tanh(r.w))
-                              : make_float4(gate_sigmoid(r.x), gate_sigmoid(r.y), gate_sigmoid(r.z), gate_sigmoid(r.w));
-                } else if (epi.mode == EPI_ACCUM) { r.x += old[k].x; r.y += old[k].y; r.z += old[k].z; r.w += old[k].w; }
-                else if (epi.mode == EPI_ACCUM_MASK) {
-                  r = make_float4(old[k].x + r.x * mk[k].x, old[k].y + r.y * mk[k].y, old[k].z + r.z * mk[k].z, old[k].w + r.w * mk[k].w);
-                }
-                st4(row.c + ldc * n, r);
-              }
-            }
-          }
-        } else {
-          // any shape / alignment: one row per thread pair of columns, scalar accesses
-          const uint32_t r = te & 127, m = m0 + r;
-          if (m < M) {
-            const EpiRow row = epi_row(epi, m);
-            const size_t ldc = row.ldc;
-            float bias = 0.f;
-            if (epi.mode == EPI_BIAS || epi.mode == EPI_GATES) bias = epi.bias[m];
-            if (epi.mode == EPI_GATES && m >= epi.H && m < 2 * epi.H) bias += epi.forget_bias;
-            const bool is_tanh = m >= 3 * epi.H;
-            const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
-#pragma unroll 4
-            for (uint32_t c = te >> 7; c < BNT; c += 2) {
-              const uint32_t n = n0 + c;
-              if (n >= N) break;
-              float v = tile[(size_t)c * BM + r];
-              float* dst = row.c + ldc * n;
-              if (epi.mode == EPI_STORE) *dst = v;
-              else if (epi.mode == EPI_BIAS) *dst = v + bias;
-              else if (epi.mode == EPI_GATES) *dst = is_tanh ? gate_tanh(v + bias) : gate_sigmoid(v + bias);
-              else if (epi.mode == EPI_ACCUM) *dst += v;
-              else *dst += v * row.mask[mstep * n];
-            }
-          }
-        }
-      }
+      epilogue_pass<BNT, 256>(epi, tile, te, blockIdx.x, m0, n0, M, N, cprev);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -385,6 +405,196 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- persistent variant for products with more tiles than SMs -----------------------------------------------------------
+// One CTA per SM walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ... (the same order in which the one-tile kernel's
+// CTAs would run, so CTAs that share operand tiles still work on the same k-blocks at the same time).  The epilogue of a
+// tile runs while the TMA and MMA warps are already on the next one: the finished tile waits in the epilogue warps'
+// registers (the TMEM accumulators are free again as soon as their last chunk is drained) and goes through a 32 KiB
+// staging buffer beside the operand ring, one 64-column half at a time: warps 2-5 park and write out columns 0-63, then
+// warps 6-9 columns 64-127.  What this saves is the pipeline fill and the epilogue of every tile but the last, about
+// 9 us per tile: a third of the time of the output layer's product (K = 1024, 75 tiles per SM).
+constexpr int SMEM_PERSIST_BYTES = SMEM_BYTES + BM * 64 * 4;
+// Four accumulators (all 512 TMEM columns): the MMA warp may run four chunks - a whole tile of the output layer's
+// product - ahead of the epilogue warps, which drain nothing while they write out the previous tile.
+constexpr uint32_t kPersistBufs = 4;
+
+// The two single-thread roles are functions of their own: their loops pace the tensor pipe and keep their own registers.
+template <int BNT>
+__device__ __noinline__ void persist_producer(const TmapPack* tm, unsigned char* ring, uint64_t* full_bar, uint64_t* empty_bar,
+                                              uint32_t tiles, uint32_t tiles_m, uint32_t kb0, uint32_t kb1, uint32_t* flags) {
+  constexpr int TILE_B_BYTES = BNT * BK * 4;
+  constexpr int STAGE_TX = 2 * TILE_BYTES + 2 * TILE_B_BYTES;
+  const uint32_t kb = kb0 + kb1;
+  uint32_t s = 0, ph = 0;
+  bool fail = false;
+  for (uint32_t tile = blockIdx.x; tile < tiles && !fail; tile += gridDim.x) {
+    const uint32_t m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BNT;
+    for (uint32_t g = 0; g < kb; ++g) {
+      if (!mbar_wait(&empty_bar[s], ph ^ 1)) { fail = true; break; }
+      const uint32_t pair = g < kb0 ? 0 : 1, kblk = pair ? g - kb0 : g;
+      unsigned char* st = ring + (size_t)s * STAGE_BYTES;
+      mbar_expect_tx(&full_bar[s], STAGE_TX);
+      tma_load_2d(st, &tm->t[4 * pair + 0], &full_bar[s], (int)(kblk * BK), (int)m0);
+      tma_load_2d(st + TILE_BYTES, &tm->t[4 * pair + 1], &full_bar[s], (int)(kblk * BK), (int)m0);
+      tma_load_2d(st + 2 * TILE_BYTES, &tm->t[4 * pair + 2], &full_bar[s], (int)(kblk * BK), (int)n0);
+      tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm->t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), (int)n0);
+      if (++s == STAGES) { s = 0; ph ^= 1; }
+    }
+  }
+  if (fail) atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT);
+}
+
+template <int BNT>
+__device__ __noinline__ void persist_issue(unsigned char* ring, uint64_t* full_bar, uint64_t* empty_bar, uint64_t* acc_full,
+                                           uint64_t* acc_empty, uint32_t tmem_base, uint32_t tiles, uint32_t kb, uint32_t* flags) {
+  constexpr int TILE_B_BYTES = BNT * BK * 4;
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  uint64_t d_a_hi[STAGES], d_a_lo[STAGES], d_b_hi[STAGES], d_b_lo[STAGES];
+#pragma unroll
+  for (int q = 0; q < STAGES; ++q) {
+    const uint32_t base = smem_u32(ring + (size_t)q * STAGE_BYTES);
+    d_a_hi[q] = umma_desc(base); d_a_lo[q] = umma_desc(base + TILE_BYTES);
+    d_b_hi[q] = umma_desc(base + 2 * TILE_BYTES); d_b_lo[q] = umma_desc(base + 2 * TILE_BYTES + TILE_B_BYTES);
+  }
+  // stage, phase and chunk counters run on across tiles; an accumulation chain never crosses a tile boundary
+  uint32_t s = 0, ph = 0, chunk = 0, buf = 0;
+  bool fail = false;
+  for (uint32_t tile = blockIdx.x; tile < tiles && !fail; tile += gridDim.x) {
+    uint32_t in_chunk = 0;
+    for (uint32_t it = 0; it < kb; ++it) {
+      if (in_chunk == 0 && chunk >= kPersistBufs) {
+        if (!mbar_wait(&acc_empty[buf], ((chunk / kPersistBufs) - 1) & 1)) { fail = true; break; }
+      }
+      if (!mbar_wait(&full_bar[s], ph)) { fail = true; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint64_t a_hi, a_lo, b_hi, b_lo;
+      if (s == 0) { a_hi = d_a_hi[0]; a_lo = d_a_lo[0]; b_hi = d_b_hi[0]; b_lo = d_b_lo[0]; }
+      else if (s == 1) { a_hi = d_a_hi[1]; a_lo = d_a_lo[1]; b_hi = d_b_hi[1]; b_lo = d_b_lo[1]; }
+      else { a_hi = d_a_hi[2]; a_lo = d_a_lo[2]; b_hi = d_b_hi[2]; b_lo = d_b_lo[2]; }
+      const uint32_t acc = tmem_base + buf * BN;
+      issue_kblock(acc, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk);
+      umma_commit(&empty_bar[s]);
+      const bool chunk_ends = in_chunk == kChunkKB - 1 || it == kb - 1;
+      if (chunk_ends) { umma_commit(&acc_full[buf]); in_chunk = 0; ++chunk; buf = chunk % kPersistBufs; }
+      else ++in_chunk;
+      if (++s == STAGES) { s = 0; ph ^= 1; }
+    }
+  }
+  if (fail) atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT);
+}
+
+__device__ __forceinline__ void bar_sync(uint32_t id, uint32_t count) { asm volatile("barrier.cta.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+__device__ __forceinline__ void bar_arrive(uint32_t id, uint32_t count) { asm volatile("barrier.cta.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+
+template <int BNT>
+__global__ void __launch_bounds__(kThreads, 1) k_gemm_persist(const __grid_constant__ TmapPack tm, uint32_t M, uint32_t N,
+                                                              uint32_t kb0, uint32_t kb1, uint32_t tiles_m, uint32_t tiles,
+                                                              GemmEpilogue epi, uint32_t* flags) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[kPersistBufs], acc_empty[kPersistBufs];
+  __shared__ uint32_t tmem_base_slot;
+  unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* stage = reinterpret_cast<float*>(ring + (size_t)STAGES * STAGE_BYTES);   // 64 columns x BM rows
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t kb = kb0 + kb1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (uint32_t q = 0; q < kPersistBufs; ++q) { mbar_init(&acc_full[q], 1); mbar_init(&acc_empty[q], kEpiWarps); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kPersistBufs * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane == 0) persist_producer<BNT>(&tm, ring, full_bar, empty_bar, tiles, tiles_m, kb0, kb1, flags);
+  } else if (warp == 1) {
+    if (lane == 0) persist_issue<BNT>(ring, full_bar, empty_bar, acc_full, acc_empty, tmem_base, tiles, kb, flags);
+  } else {
+    // epilogue warps 2..9: TMEM lanes 32 (warp % 4) .. +31; warps 2-5 hold columns 0-63 of the tile, warps 6-9 columns 64-127
+    const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
+    const uint32_t th = (threadIdx.x - 64) & 127;   // 0..127 within this half's four warps
+    const bool has_cols = 64 * half < BNT;
+    const uint32_t nchunks = (kb + kChunkKB - 1) / kChunkKB;
+    uint32_t cg = 0;   // chunks drained so far (selects the TMEM buffer and the barrier phase)
+    bool ok = true;
+#pragma unroll 1
+    for (uint32_t tile = blockIdx.x, j = 0; tile < tiles; tile += gridDim.x, ++j) {
+      const uint32_t mt = tile % tiles_m, m0 = mt * BM, n0 = (tile / tiles_m) * BNT + 64 * half;
+      float sum[64];
+#pragma unroll
+      for (int q = 0; q < 64; ++q) sum[q] = 0.f;
+#pragma unroll 1
+      for (uint32_t c = 0; c < nchunks; ++c, ++cg) {
+        const uint32_t buf = cg % kPersistBufs;
+        if (!ok) continue;
+        if (!mbar_wait(&acc_full[buf], (cg / kPersistBufs) & 1)) { ok = false; continue; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (has_cols) {
+          float v[32];
+          const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32) << 16) + 2 * half * 32;
+          tmem_ld32(taddr, v);
+#pragma unroll
+          for (int q = 0; q < 32; ++q) sum[q] += v[q];
+          tmem_ld32(taddr + 32, v);
+#pragma unroll
+          for (int q = 0; q < 32; ++q) sum[32 + q] += v[q];
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      }
+      if (!has_cols) continue;   // (64-column tiles: warps 6-9 only take part in the accumulator hand-shake)
+      // The staging buffer is free once the other half has written out its columns of the previous turn (128-column
+      // tiles), or once this half's own warps have all left the previous pass (64-column tiles).
+      if (BNT == 128) {
+        if (half == 1) bar_sync(2, 256);
+        else if (j > 0) bar_sync(4, 256);
+      } else if (j > 0) {
+        bar_sync(2, 128);
+      }
+      {
+        float* col = stage + quarter * 32 + lane;
+#pragma unroll
+        for (int q = 0; q < 64; ++q) col[(size_t)q * BM] = sum[q];
+      }
+      float4 cprev[4];
+      if (epi.mode == EPI_LSTM_CELL) {
+        const uint32_t u = mt * 32 + 4 * (th & 7);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t n = n0 + (th >> 3) + 16 * k;
+          cprev[k] = n < N ? ld4(epi.c_prev + u + (size_t)epi.H * n) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+      uint32_t all_ok;
+      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, %2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1u + 2u * half) : "memory");
+      if (all_ok) epilogue_pass<64, 128>(epi, stage, th, mt, m0, n0, M, N, cprev);
+      if (BNT == 128) {
+        if (half == 0) bar_arrive(2, 256);
+        else if (tile + gridDim.x < tiles) bar_arrive(4, 256);
+      }
+    }
+    if (!ok && lane == 0) atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kPersistBufs * BN) : "memory");
   }
 }
 
@@ -724,16 +934,29 @@ int dyb200_tc_param_gates(dyb200_ctx* ctx, const float* src, uint32_t ld, uint32
 
 inline uint32_t tile_cols(uint32_t N) { return N <= 64 ? 64 : BN; }
 
+// Number of K splits: the one a small cost model says is fastest.  A launch takes waves x (k-blocks per CTA x 0.66 us +
+// 9 us of pipeline fill and epilogue), with waves = ceil(tiles x S / SMs); S > 1 adds the second kernel that sums the S
+// partial products into C ((S + 2) M N floats through HBM + a launch).  Measured on B200: the model is within 2 us of
+// the per-step LSTM products (dx / dh: 64 or 48 tiles, K = 4096 -> S = 2 and 3) and it removes most of the partly filled
+// last wave of the long-K products (dW: 256 tiles, 560 k-blocks, 1.73 waves -> S = 4, 6.92 waves).
 uint32_t dyb200_tc_splits(const dyb200_ctx* ctx, uint32_t M, uint32_t N, uint32_t kb_total) {
   const uint32_t bn = tile_cols(N);
   const uint32_t tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-  uint32_t S = 1;
-  if (tiles * 2 <= (uint32_t)ctx->sm_count) {
-    S = (uint32_t)ctx->sm_count / tiles;
-    if (S > kb_total / 8) S = kb_total / 8;   // at least 8 k-blocks per split
-    if (S < 1) S = 1;
+  const double sms = (double)ctx->sm_count, t_kb = bn == 64 ? 0.40 : 0.66, t_fixed = 9.0;
+  const double mn_bytes = 4.0 * (double)M * (double)N;
+  uint32_t best = 1;
+  double best_t = 0;
+  for (uint32_t S = 1; S <= 8; ++S) {
+    if (S > 1 && kb_total / S < 8) break;   // at least 8 k-blocks per split
+    const uint32_t kb_split = (kb_total + S - 1) / S;
+    const uint32_t S_eff = (kb_total + kb_split - 1) / kb_split;
+    if (S_eff != S) continue;
+    const double waves = ceil((double)tiles * S / sms);
+    double t = waves * (kb_split * t_kb + t_fixed);
+    if (S > 1) t += (S + 2) * mn_bytes / 5.0e6 + 5.0;   // bytes / (5 TB/s) in us
+    if (S == 1 || t < best_t * 0.97) { best = S; best_t = t; }   // a split must win by 3 %
   }
-  return S;
+  return best;
 }
 
 int dyb200_tc_param2(dyb200_ctx* ctx, const float* src, uint32_t rows, const float* src2, uint32_t rows2, uint32_t ld,
@@ -782,11 +1005,11 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   uint32_t kb0 = round_up(A[0].K, 32) / BK, kb1 = npairs > 1 ? round_up(A[1].K, 32) / BK : 0;
   const uint32_t kb_total = kb0 + kb1;
   dim3 grid((M + BM - 1) / BM, (N + bn - 1) / bn, 1);
-  // Split K when the output has too few tiles to occupy the SMs (e.g. dx = W^T dgate: 16-32 tiles, K = 4096).
-  uint32_t S = dyb200_tc_splits(ctx, M, N, kb_total);
   DYB_CHECK_ARG(ctx, epi.mode != EPI_LSTM_CELL || (M % BM == 0 && epi.H * 4 == M && epi.ldc % 4 == 0 && aligned16(epi.C) &&
                                                       aligned16(epi.bias) && aligned16(epi.c_prev) && aligned16(epi.c_out) && aligned16(epi.h_out)),
                 "tensor GEMM: the LSTM-cell epilogue needs whole tiles of interleaved gate rows and 16-byte aligned tensors");
+  // Split K when the output has too few tiles to occupy the SMs (e.g. dx = W^T dgate: 16-32 tiles, K = 4096).
+  uint32_t S = dyb200_tc_splits(ctx, M, N, kb_total);
   uint32_t kb_per_split = (kb_total + S - 1) / S;
   S = (kb_total + kb_per_split - 1) / kb_per_split;
   GemmEpilogue kepi = epi;
@@ -798,6 +1021,22 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     part = (float*)pw;
     kepi = GemmEpilogue{EPI_STORE, part, M, nullptr, 0, 0.f, nullptr, 0, 0};   // (no second destination)
     grid.z = S;
+  }
+  static int persist = -1;   // DYB200_PERSISTENT=0: one CTA per tile for every product
+  if (persist < 0) { const char* e = getenv("DYB200_PERSISTENT"); persist = (e && e[0] == '0') ? 0 : 1; }
+  if (persist && S == 1 && grid.x * grid.y > (uint32_t)ctx->sm_count) {
+    static bool attr_set2 = false;
+    if (!attr_set2) {
+      DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_persist<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PERSIST_BYTES));
+      DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_persist<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PERSIST_BYTES));
+      attr_set2 = true;
+    }
+    GemmProfScope scope(ctx, flops, 1, M, N, kb_total * BK, (uint32_t)epi.mode);
+    const uint32_t tiles = grid.x * grid.y;
+    if (bn == 64) dyb_launch(k_gemm_persist<64>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles, epi, ctx->dev_flags);
+    else dyb_launch(k_gemm_persist<128>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles, epi, ctx->dev_flags);
+    DYB_LAUNCHED(ctx);
+    return DYB200_OK;
   }
   {
     // times the MMA kernel (and the split-K reduction); the packing launches show up in the step time

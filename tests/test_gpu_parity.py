@@ -607,8 +607,11 @@ def test_lstm_chain_fused_equals_builder_math(oracle, g, capi):
 
 
 # ------------------------------------------------------------------ GEMM
+# (the last three have more 128 x 128 / 128 x 64 tiles than a B200 has SMs: the persistent kernel, with a ragged last
+# row / column block, two tiles per CTA on some SMs and one on others, and the 64-column tile)
 @pytest.mark.parametrize("tA,tB,M,N,K", [(0, 0, 64, 32, 48), (1, 0, 70, 33, 129), (0, 1, 128, 65, 31), (0, 0, 1024, 32, 384),
-                                         (1, 0, 384, 32, 1024), (0, 1, 1024, 384, 32), (0, 0, 256, 256, 512)])
+                                         (1, 0, 384, 32, 1024), (0, 1, 1024, 384, 32), (0, 0, 256, 256, 512),
+                                         (0, 0, 2000, 1500, 300), (1, 1, 1930, 2300, 70), (0, 0, 19300, 48, 96)])
 def test_gemm(g, tA, tB, M, N, K):
     r = rng(160)
     A = randn(r, *((M, K) if tA else (K, M)))   # C-order (cols, rows) == column-major rows x cols
@@ -730,6 +733,7 @@ AFFINE_SHAPES = {
     "full_bias": [(5, 1, 130), (1, 70, 130), (5, 1, 70)],
     "projection": [(1, 1, 1000), (1, 256, 1000), (192, 1, 256)],          # b + R h, the output layer's shape class
     "projection_odd": [(1, 1, 1001), (1, 250, 1001), (67, 1, 250)],
+    "projection_many_tiles": [(1, 1, 2100), (1, 200, 2100), (1700, 1, 200)],   # 17 x 14 tiles: the persistent kernel, bias epilogue
     "matmul_wide": [None, (1, 384, 512), (1, 640, 384)],
     "matmul_batched_left": [None, (3, 128, 256), (3, 130, 128)],
     "matrix_bias_tiled": [(1, 4, 256), (1, 128, 256), (6, 4, 128)],
@@ -968,11 +972,13 @@ def test_random_bernoulli(g, capi):
     assert abs(np.corrcoef(k, l)[0, 1]) < 0.01
 
 
-@pytest.mark.parametrize("I,H,B,masks", [(512, 1024, 300, "full"), (256, 1024, 384, None), (512, 1024, 64, "full"), (256, 512, 96, None)])
+@pytest.mark.parametrize("I,H,B,masks", [(512, 1024, 300, "full"), (256, 1024, 384, None), (512, 1024, 64, "full"), (256, 512, 96, None),
+                                         (128, 1024, 700, "full")])
 def test_lstm_fwd_fused_cell_epilogue(oracle, g, capi, I, H, B, masks):
     """The fused forward forms c and h in the epilogue of the gate product: inside the MMA kernel for shapes without a
-    K split (the first two), in the split-K reduction otherwise (the last two).  Gates, c and h must equal the three
-    nodes called one after the other bit for bit, and the oracle within the LSTM-state tolerance."""
+    K split (the first two), in the split-K reduction for the next two, and in the persistent kernel for the last one
+    (32 x 6 tiles, more than SMs).  Gates, c and h must equal the three nodes called one after the other bit for bit, and
+    the oracle within the LSTM-state tolerance."""
     r = rng(155)
     x, h, c_prev = randn(r, B, I), randn(r, B, H, scale=0.5), randn(r, B, H, scale=0.5)
     Wx, Wh, b = glorot(r, 4 * H, I), glorot(r, 4 * H, H), randn(r, 4 * H, scale=0.1)
