@@ -119,7 +119,7 @@ OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200
          "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_trainer_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end",
          "dyb200_ctx_param_cache", "dyb200_ctx_params_changed", "dyb200_ctx_dependent_launch", "dyb200_vanilla_lstm_fwd_fused",
          "dyb200_vanilla_lstm_bwd_fused", "dyb200_vanilla_lstm_fwd_fused_at", "dyb200_vanilla_lstm_bwd_fused_at", "dyb200_wgrad_create", "dyb200_wgrad_destroy", "dyb200_wgrad_push",
-         "dyb200_wgrad_flush"]
+         "dyb200_wgrad_flush", "dyb200_softmax_output_bwd_fused"]
 
 
 def exported_symbols():
@@ -212,6 +212,8 @@ def lib():
         L.dyb200_trainer_update.restype = C.c_int
         L.dyb200_trainer_update.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                             C.POINTER(TrainerHyper), C.c_void_p, C.c_int, C.c_void_p]
+        L.dyb200_softmax_output_bwd_fused.restype = C.c_int
+        L.dyb200_softmax_output_bwd_fused.argtypes = [tp, tp, tp, tp, C.c_void_p, tp, tp, tp, tp, C.c_uint32, C.c_void_p]
         L.dyb200_gemm.restype = C.c_int
         L.dyb200_gemm.argtypes = [C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32,
                                   C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_int, C.c_uint, C.c_void_p]
@@ -333,6 +335,12 @@ class Context:
         self.check(self.L.dyb200_vanilla_lstm_bwd_fused_at(o(x), o(h_tm1), o(c_tm1), o(Wx), o(Wh), o(mask_x), o(mask_h), o(gates), o(c_t),
                                                            o(dEdh), o(dEdc), o(dx), o(dh_tm1), o(dc_tm1), o(dWx), o(dWh), o(db),
                                                            C.byref(attrs), deferred, col, self.h))
+
+    def softmax_output_bwd_fused(self, x, h, R, dEdf, aux_ptr, dR, db, dh, dx_scratch=None, flags=0):
+        """Backward of PickNegLogSoftmax(affine_transform({b, R, h})) in one call (DyTensor arguments, aux_ptr: device pointer)."""
+        o = self._opt
+        self.check(self.L.dyb200_softmax_output_bwd_fused(o(x), o(h), o(R), o(dEdf), aux_ptr, o(dR), o(db), o(dh), o(dx_scratch),
+                                                          flags, self.h))
 
     def wgrad_create(self, M, N0, N1, Kcap):
         h = C.c_void_p()

@@ -9,6 +9,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "gemm.cuh"
 #include "reduce.cuh"
 
 namespace {
@@ -340,6 +341,102 @@ int run_expsub_bwd(dyb200_ctx* ctx, const float* x, const float* z, const float*
   return DYB200_OK;
 }
 
+// ---- PickNegLogSoftmax backward written directly as GEMM operands ------------------------------------------------------
+// d[r, c] = exp(x[r, c] - z[c]) dz[c]  (- dz[c] at the picked row): the same value k_expsub_bwd adds into a zeroed tensor,
+// but stored only as the hi / lo TF32 planes of the two products that consume it in the backward pass of
+// x = b + R h:  "straight" planes bh / bl [c][r] (reduction index = r, for dh += R^T d) and transposed planes ah / al
+// [r][c] (reduction index = c, for dR += d h^T), plus the sums over the 64 columns of the tile for the bias gradient.
+// One 64 x 64 tile per CTA: 16-byte accesses along r on the way in, along c on the way out, transposed through shared
+// memory.  x is read once; nothing else of d reaches HBM (the fp32 tensor, its zero fill and two packing passes go).
+struct ChunkOfPart {   // f(r, b) = v[r + n * b]
+  const float* v; size_t n;
+  __device__ float operator()(size_t r, uint32_t b) const { return v[r + n * (size_t)b]; }
+};
+
+__global__ void __launch_bounds__(256) k_softmax_bwd_split(const float* __restrict__ x, const float* __restrict__ z,
+                                                           const float* __restrict__ dz, const uint32_t* __restrict__ ids,
+                                                           uint32_t rows, uint32_t ncols, float* __restrict__ bh,
+                                                           float* __restrict__ bl, uint32_t pitch_b, float* __restrict__ ah,
+                                                           float* __restrict__ al, uint32_t pitch_a,
+                                                           float* __restrict__ colsum_part, int vec_in, int vec_out) {
+  dyb_grid_dep_sync();
+  __shared__ float tile[64][65];   // [column][row]
+  const uint32_t r0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
+  {
+    const uint32_t rq = threadIdx.x & 15, cl = threadIdx.x >> 4;
+    const uint32_t r = r0 + 4 * rq;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const uint32_t c = c0 + cl + 16 * p;
+      float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < ncols && r < rows) {
+        const float zc = z[c], dc = dz[c];
+        const uint32_t pick = ids ? ids[c] : 0xffffffffu;
+        const float* xc = x + (size_t)c * rows;
+        if (vec_in) {   // rows % 4 == 0: the four rows exist; same arithmetic as the vector path of k_expsub_bwd
+          const float4 v = ld4_stream(xc + r);
+          const float zl = zc * kLog2e;
+          d = make_float4(ex2_approx(fmaf(v.x, kLog2e, -zl)) * dc, ex2_approx(fmaf(v.y, kLog2e, -zl)) * dc,
+                          ex2_approx(fmaf(v.z, kLog2e, -zl)) * dc, ex2_approx(fmaf(v.w, kLog2e, -zl)) * dc);
+          if (pick - r < 4u) {
+            const uint32_t k = pick - r;
+            if (k == 0) d.x -= dc; else if (k == 1) d.y -= dc; else if (k == 2) d.z -= dc; else d.w -= dc;
+          }
+          float4 h, l;
+          split_tf32(d.x, h.x, l.x); split_tf32(d.y, h.y, l.y); split_tf32(d.z, h.z, l.z); split_tf32(d.w, h.w, l.w);
+          st4(bh + (size_t)c * pitch_b + r, h);
+          st4(bl + (size_t)c * pitch_b + r, l);
+        } else {        // same arithmetic as its scalar path
+          float e[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (r + k < rows) {
+              e[k] = expf(xc[r + k] - zc) * dc;
+              if (r + k == pick) e[k] -= dc;
+              float h, l;
+              split_tf32(e[k], h, l);
+              bh[(size_t)c * pitch_b + r + k] = h;
+              bl[(size_t)c * pitch_b + r + k] = l;
+            }
+          }
+          d = make_float4(e[0], e[1], e[2], e[3]);
+        }
+      }
+      float* t = &tile[cl + 16 * p][4 * rq];
+      t[0] = d.x; t[1] = d.y; t[2] = d.z; t[3] = d.w;
+    }
+  }
+  __syncthreads();
+  {
+    const uint32_t cq = threadIdx.x & 15, rl = threadIdx.x >> 4;
+    const uint32_t c = c0 + 4 * cq;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const uint32_t rr = rl + 16 * p, r = r0 + rr;
+      const float4 d = make_float4(tile[4 * cq][rr], tile[4 * cq + 1][rr], tile[4 * cq + 2][rr], tile[4 * cq + 3][rr]);
+      float s = (d.x + d.y) + (d.z + d.w);   // (columns past ncols hold zeros)
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      s += __shfl_xor_sync(0xffffffffu, s, 8);
+      if (r >= rows) continue;
+      if (cq == 0) colsum_part[(size_t)blockIdx.y * rows + r] = s;
+      if (c >= ncols) continue;
+      float4 h, l;
+      split_tf32(d.x, h.x, l.x); split_tf32(d.y, h.y, l.y); split_tf32(d.z, h.z, l.z); split_tf32(d.w, h.w, l.w);
+      float* ph = ah + (size_t)r * pitch_a + c;
+      float* pl = al + (size_t)r * pitch_a + c;
+      if (vec_out) { st4(ph, h); st4(pl, l); }   // ncols % 4 == 0: the four columns exist
+      else {
+        ph[0] = h.x; pl[0] = l.x;
+        if (c + 1 < ncols) { ph[1] = h.y; pl[1] = l.y; }
+        if (c + 2 < ncols) { ph[2] = h.z; pl[2] = l.z; }
+        if (c + 3 < ncols) { ph[3] = h.w; pl[3] = l.w; }
+      }
+    }
+  }
+}
+
 // ---- reductions along dim 1 (strided): 8 rows x 128 lanes per CTA -------------
 constexpr int kRT = 8, kCL = 128, kRowVals = 32;  // registers hold cols <= 4096
 enum RowMode { R_SOFTMAX, R_LSE, R_SOFTMAX_BWD, R_LSE_BWD };
@@ -615,6 +712,62 @@ int dyb200_pickneglogsoftmax_bwd(DYB200_BWD_ARGS) {
   const float* z = (const float*)aux_mem;
   const uint32_t* ids_dev = (const uint32_t*)(z + 2 * (size_t)bd);
   return run_expsub_bwd(ctx, xs[0].v, z, dEdf->v, ids_dev, dEdxi->v, rows, bd);
+}
+
+int dyb200_softmax_output_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h, const dyb200_tensor* R,
+                                    const dyb200_tensor* dEdf, const void* aux_mem, dyb200_tensor* dR, dyb200_tensor* db,
+                                    dyb200_tensor* dh, dyb200_tensor* dx_scratch, uint32_t flags, dyb200_ctx* ctx) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
+  DYB_CHECK_ARG(ctx, x && h && R && dEdf && aux_mem && dR && db && dh && x->v && h->v && R->v && dEdf->v && dR->v && db->v && dh->v,
+                "softmax_output_bwd_fused: null argument");
+  const uint32_t V = t_rows(x), H = t_rows(h), n = x->bd;
+  DYB_CHECK_ARG(ctx, t_cols(x) == 1 && t_cols(h) == 1 && h->bd == n && R->nd == 2 && R->bd == 1 && R->d[0] == V && R->d[1] == H &&
+                     t_size(dEdf) == n && t_size(dR) == (size_t)V * H && t_size(db) == V && t_size(dh) == (size_t)H * n,
+                "softmax_output_bwd_fused: shape mismatch (x %u x %u, h %u x %u)", V, n, H, h->bd);
+  if (V == 0 || n == 0 || H == 0) return DYB200_OK;
+  const float* z = (const float*)aux_mem;
+  const uint32_t* ids_dev = (const uint32_t*)(z + 2 * (size_t)n);
+  const double flops = 2.0 * V * (double)H * n;
+  if (!(dyb200_tc_eligible(V, H, flops) && dyb200_tc_eligible(H, n, flops))) {
+    // small shapes: the node-by-node sequence through the caller's tensor
+    DYB_CHECK_ARG(ctx, dx_scratch && dx_scratch->v && t_size(dx_scratch) == (size_t)V * n,
+                  "softmax_output_bwd_fused: shapes this small need the V x n scratch tensor");
+    DYB_CUDA(ctx, cudaMemsetAsync(dx_scratch->v, 0, (size_t)V * n * sizeof(float), ctx->stream));
+    int rc = run_expsub_bwd(ctx, x->v, z, dEdf->v, ids_dev, dx_scratch->v, V, n);
+    if (rc) return rc;
+    dyb200_tensor dv = *x;   // the gradient of x, with x's shape
+    dv.v = dx_scratch->v;
+    dyb200_tensor xs[3] = {*db, *R, *h};
+    dyb200_affine_attrs at = {flags};
+    for (unsigned i = 0; i < 3 && !rc; ++i)
+      rc = dyb200_affine_transform_bwd(xs, 3, x, &dv, i, i == 0 ? db : i == 1 ? dR : dh, &at, nullptr, ctx);
+    return rc;
+  }
+  int rc;
+  PackedOp dA, dB, hT, RT;
+  if ((rc = dyb200_tc_planes(ctx, V, n, &dA))) return rc;   // rows = vocabulary, reduction over the columns
+  if ((rc = dyb200_tc_planes(ctx, n, V, &dB))) return rc;   // rows = columns, reduction over the vocabulary
+  const dim3 grid((V + 63) / 64, (n + 63) / 64);
+  void* part;
+  if ((rc = dyb200_scratch(ctx, (size_t)grid.y * V * sizeof(float), &part))) return rc;
+  const int vec_in = V % 4 == 0 && aligned16(x->v), vec_out = n % 4 == 0;
+  DYB_CHECK_ARG(ctx, grid.y <= 65535u, "softmax_output_bwd_fused: too many columns (%u)", n);
+  dyb_launch(k_softmax_bwd_split, grid, 256, 0, ctx, x->v, z, dEdf->v, ids_dev, V, n, dB.hi, dB.lo, dB.pitch, dA.hi, dA.lo, dA.pitch,
+             (float*)part, vec_in, vec_out);
+  DYB_LAUNCHED(ctx);
+  if ((rc = batch_reduce_add(ctx, ChunkOfPart{(const float*)part, V}, V, grid.y, db->v))) return rc;   // db += sum over column tiles
+  // dR += d h^T : M = V, N = H, K = n
+  if ((rc = dyb200_tc_pack(ctx, h->v, H, false, H, n, nullptr, 0, 0, &hT, nullptr))) return rc;
+  {
+    GemmEpilogue e{EPI_ACCUM, dR->v, V, nullptr, 0, 0.f, nullptr, 0, 0};
+    if ((rc = dyb200_tc_gemm_packed(ctx, V, H, 1, &dA, &hT, e))) return rc;
+  }
+  // dh += R^T d : M = H, N = n, K = V
+  if (flags & DYB200_GEMM_A_IS_PARAM) rc = dyb200_tc_param(ctx, R->v, V, true, H, V, &RT);
+  else rc = dyb200_tc_pack(ctx, R->v, V, true, H, V, nullptr, 0, 0, &RT, nullptr);
+  if (rc) return rc;
+  GemmEpilogue e{EPI_ACCUM, dh->v, H, nullptr, 0, 0.f, nullptr, 0, 0};
+  return dyb200_tc_gemm_packed(ctx, H, n, 1, &RT, &dB, e);
 }
 
 }  // extern "C"

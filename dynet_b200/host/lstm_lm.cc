@@ -237,13 +237,11 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   Tensor tgR(Dim({V, H}), m.g[1 + 3 * L]), tgbias(Dim({V}), m.g[2 + 3 * L]);
   if (c.fused) {
     Tensor tones(Dim({1}, TB), m.ones), tdr(Dim({V}, TB), m.dr), tdhall(Dim({H}, TB), m.dh + at(0, L - 1) * HB);
-    CU(cudaMemsetAsync(m.dr, 0, (size_t)T * VB * sizeof(float), st));
-    pnls.backward_dev_impl(dev, {&rall}, eall, tones, 0, tdr);
-    dyb200_tensor cxs[3] = {to_c(tbias), to_c(tR), to_c(hall)}, cr = to_c(rall), cdr = to_c(tdr);
+    // PickNegLogSoftmax backward and the three AffineTransform backward calls (dbias += sum_columns dr, dR += dr h^T,
+    // dh += R^T dr) in one: dr is written straight into the operand layouts of the two products
+    dyb200_tensor cr = to_c(rall), ch = to_c(hall), cR = to_c(tR), cones = to_c(tones), cdr = to_c(tdr);
     dyb200_tensor cgb = to_c(tgbias), cgR = to_c(tgR), cdh = to_c(tdhall);
-    throw_status(dev, dyb200_affine_transform_bwd(cxs, 3, &cr, &cdr, 0, &cgb, &R_is_param, nullptr, dev.ctx));   // dbias += sum_columns dr
-    throw_status(dev, dyb200_affine_transform_bwd(cxs, 3, &cr, &cdr, 1, &cgR, &R_is_param, nullptr, dev.ctx));   // dR += dr h^T
-    throw_status(dev, dyb200_affine_transform_bwd(cxs, 3, &cr, &cdr, 2, &cdh, &R_is_param, nullptr, dev.ctx));   // dh += R^T dr
+    throw_status(dev, dyb200_softmax_output_bwd_fused(&cr, &ch, &cR, &cones, m.aux, &cgR, &cgb, &cdh, &cdr, DYB200_GEMM_A_IS_PARAM, dev.ctx));
   }
   Tensor tones(Dim({1}, B), m.ones);
   for (uint32_t tt = T; tt-- > 0;) {

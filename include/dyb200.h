@@ -150,6 +150,18 @@ int dyb200_logsumexp_bwd(DYB200_BWD_ARGS);      /* dynet/nodes-logsumexp.cc:75-9
  * (z, m, flat ids) exactly as aux_storage_size() sizes it, dynet/nodes-pickneglogsoftmax.cc:72-118 */
 int dyb200_pickneglogsoftmax_fwd(DYB200_FWD_ARGS);
 int dyb200_pickneglogsoftmax_bwd(DYB200_BWD_ARGS); /* dynet/nodes-pickneglogsoftmax.cc:120-146 */
+/* Optional, beyond node granularity: the backward pass of loss_c = PickNegLogSoftmax(x_c), x = affine_transform({b, R, h})
+ * (the output layer of examples/batching/rnnlm-batch.h:132-135) in one call.  Value-equivalent to
+ * dyb200_pickneglogsoftmax_bwd into a zeroed d(x) followed by dyb200_affine_transform_bwd for i = 0, 1, 2
+ * (dynet/nodes-pickneglogsoftmax.cc:120-146, dynet/nodes-affinetransform.cc:120-157), but d(x) is never stored as a
+ * tensor: one pass over x writes it as the split operands of the two products (dR += d h^T, dh += R^T d) and as
+ * per-tile column sums for db.  x: Dim({V}, n) logits; h: Dim({H}, n); R: Dim({V, H}); dEdf: n loss gradients; aux_mem:
+ * the PickNegLogSoftmax node's aux_mem as left by its forward call; dR, db, dh are accumulated into.  dx_scratch
+ * (Dim({V}, n), overwritten) is only used for shapes too small for the tensor-pipe products and may be NULL otherwise.
+ * flags: DYB200_GEMM_A_IS_PARAM when R is a parameter and the parameter cache is on. */
+int dyb200_softmax_output_bwd_fused(const dyb200_tensor* x, const dyb200_tensor* h, const dyb200_tensor* R,
+                                    const dyb200_tensor* dEdf, const void* aux_mem, dyb200_tensor* dR, dyb200_tensor* db,
+                                    dyb200_tensor* dh, dyb200_tensor* dx_scratch, uint32_t flags, dyb200_ctx* ctx);
 
 /* ---- A10-A11 normalisation ---- */
 int dyb200_weight_norm_fwd(DYB200_FWD_ARGS);   /* WeightNormalization, dynet/nodes-normalization.cc:28-41 (no host sync: g is read on the device) */

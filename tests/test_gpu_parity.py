@@ -233,6 +233,52 @@ def test_pickneglogsoftmax(oracle, g, capi, rows, bd):
     assert g.ctx().device_errors() == 0
 
 
+@pytest.mark.parametrize("V,H,n", [(1000, 256, 192), (1001, 250, 67), (2100, 128, 1300), (40, 16, 8)])
+def test_softmax_output_bwd_fused(oracle, g, capi, V, H, n):
+    """dyb200_softmax_output_bwd_fused == PickNegLogSoftmax backward into a zeroed d(x), then AffineTransform backward
+    for the bias, R and h.  Vector and scalar paths (V, n multiples of 4 or not), a tile grid with a ragged edge, and a
+    shape small enough for the node-by-node path through the scratch tensor.  The two products see bitwise the same
+    operands, so dR and dh are equal bit for bit; the bias gradient is summed in another order."""
+    r = rng(V + n)
+    b, R, h = randn(r, 1, 1, V, scale=0.1), randn(r, 1, H, V, scale=0.1), randn(r, n, 1, H, scale=0.5)
+    ids = zipf_ids(r, n, V)
+    x = oracle.affine_fwd([b, R, h])                    # (n, 1, V)
+    loss_ref, z_ref = oracle.pnls_fwd(x[:, 0, :], ids)
+    dE = randn(r, n)
+    dx_ref = oracle.pnls_bwd(x[:, 0, :], ids, z_ref, dE, np.zeros((n, V), np.float32))
+    g0 = [randn(r, *a.shape, scale=0.1) for a in (b, R, h)]
+    want = [oracle.affine_bwd([b, R, h], dx_ref[:, None, :], i, g0[i].copy()) for i in range(3)]
+    ctx = g.ctx()
+    tb, tR, th_ = g.T(g.dev(b), [V], 1), g.T(g.dev(R), [V, H], 1), g.T(g.dev(h), [H], n)
+    x_ = g.dev(np.zeros((n, V), np.float32))
+    tx = g.T(x_, [V], n)
+    ctx.fwd("affine_transform", [tb, tR, th_], tx)
+    loss_, aux = g.dev(np.zeros(n, np.float32)), g.dev(np.zeros(3 * n, np.float32))
+    ids_np, ids_p = g.u32(ids)
+    at = capi.PickAttrs(ids_p, n)
+    ctx.fwd("pickneglogsoftmax", [tx], g.T(loss_, [1], n), at, aux.data_ptr())
+    tdE = g.T(g.dev(dE), [1], n)
+    # node by node
+    dx_ = g.dev(np.zeros((n, V), np.float32))
+    ctx.bwd("pickneglogsoftmax", [tx], g.T(loss_, [1], n), tdE, 0, g.T(dx_, [V], n), at, aux.data_ptr())
+    node = [g.dev(a) for a in g0]
+    shapes = [([V], 1), ([V, H], 1), ([H], n)]
+    for i in range(3):
+        ctx.bwd("affine_transform", [tb, tR, th_], tx, g.T(dx_, [V], n), i, g.T(node[i], *shapes[i]))
+    # fused
+    fused = [g.dev(a) for a in g0]
+    scratch = g.dev(np.full((n, V), 3.0, np.float32))
+    ctx.softmax_output_bwd_fused(tx, th_, tR, tdE, aux.data_ptr(), g.T(fused[1], *shapes[1]), g.T(fused[0], *shapes[0]),
+                                 g.T(fused[2], *shapes[2]), g.T(scratch, [V], n))
+    assert np.array_equal(g.host(fused[1]), g.host(node[1]))
+    assert np.array_equal(g.host(fused[2]), g.host(node[2]))
+    for i, what in enumerate(("db", "dR", "dh")):
+        scale = max(1e-2, float(np.abs(want[i]).max()) * 0.05)
+        assert_close(g.host(fused[i]), want[i], TOL_REDUCE, floor=scale, what="fused " + what)
+        assert_close(g.host(fused[i]), g.host(node[i]), 1e-5, floor=scale, what="fused vs nodes " + what)
+    assert ctx.device_errors() == 0
+
+
 def test_pickneglogsoftmax_errors(g, capi):
     x_ = g.dev(np.zeros((2, 5), np.float32))
     loss_, aux = g.dev(np.zeros(2, np.float32)), g.dev(np.zeros(6, np.float32))
