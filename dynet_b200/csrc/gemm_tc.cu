@@ -142,9 +142,11 @@ __device__ __forceinline__ void issue_kblock(uint32_t acc, uint64_t a_hi, uint64
 // NT epilogue threads (te = 0..NT-1).  mt is the tile's row-block index (m0 = BM mt), n0 the global column of the first
 // parked column, cprev the previous cell states the caller fetched for EPI_LSTM_CELL (hidden units
 // [32 mt + 4 (te % 8), +4), columns n0 + te / 8 + (NT / 8) k).
+// Only columns [c_lo, c_hi) of the parked tile are written out (the whole tile: 0, NC).
 template <int NC, int NT>
 __device__ __forceinline__ void epilogue_pass(const GemmEpilogue& epi, const float* tile, uint32_t te, uint32_t mt, uint32_t m0,
-                                              uint32_t n0, uint32_t M, uint32_t N, const float4 (&cprev)[4]) {
+                                              uint32_t n0, uint32_t M, uint32_t N, const float4 (&cprev)[4],
+                                              uint32_t c_lo = 0, uint32_t c_hi = NC) {
   if (epi.mode == EPI_LSTM_CELL) {
     // rows 32 q + l of the tile are gate q (i, f, o, g) of hidden unit 32 mt + l
     const uint32_t l = 4 * (te & 7), u = mt * 32 + l;
@@ -157,7 +159,7 @@ __device__ __forceinline__ void epilogue_pass(const GemmEpilogue& epi, const flo
 #pragma unroll
     for (int k = 0; k < NC / (NT / 8); ++k) {
       const uint32_t c = (te >> 3) + (NT / 8) * k, n = n0 + c;
-      if (n < N) {
+      if (n < N && c >= c_lo && c < c_hi) {
         float4 g[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -193,19 +195,20 @@ __device__ __forceinline__ void epilogue_pass(const GemmEpilogue& epi, const flo
         const bool is_tanh = m >= 3 * epi.H;
         const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
 #pragma unroll 1
-        for (uint32_t c0 = te >> 5; c0 < NC; c0 += 8 * (NT / 32)) {   // batches of 8 columns, loads first
+        for (uint32_t c0 = c_lo + (te >> 5); c0 < c_hi; c0 += 8 * (NT / 32)) {   // batches of 8 columns, loads first
           float4 v[8], old[8], mk[8];
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t c = c0 + (NT / 32) * k, n = n0 + c;
-            v[k] = ld4(tile + (size_t)c * BM + 4 * rq);
-            if (epi.mode == EPI_ACCUM || epi.mode == EPI_ACCUM_MASK) old[k] = n < N ? __ldcg(reinterpret_cast<const float4*>(row.c + ldc * n)) : v[k];
-            if (epi.mode == EPI_ACCUM_MASK) mk[k] = n < N ? ld4(row.mask + mstep * n) : v[k];
+            const bool live = n < N && c < c_hi;
+            v[k] = ld4(tile + (size_t)min(c, (uint32_t)NC - 1) * BM + 4 * rq);
+            if (epi.mode == EPI_ACCUM || epi.mode == EPI_ACCUM_MASK) old[k] = live ? __ldcg(reinterpret_cast<const float4*>(row.c + ldc * n)) : v[k];
+            if (epi.mode == EPI_ACCUM_MASK) mk[k] = live ? ld4(row.mask + mstep * n) : v[k];
           }
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            const uint32_t n = n0 + c0 + (NT / 32) * k;
-            if (n >= N) continue;
+            const uint32_t c = c0 + (NT / 32) * k, n = n0 + c;
+            if (n >= N || c >= c_hi) continue;
             float4 r = v[k];
             if (epi.mode == EPI_BIAS) { r.x += bias.x; r.y += bias.y; r.z += bias.z; r.w += bias.w; }
             else if (epi.mode == EPI_GATES) {
@@ -232,7 +235,7 @@ __device__ __forceinline__ void epilogue_pass(const GemmEpilogue& epi, const flo
         const bool is_tanh = m >= 3 * epi.H;
         const size_t mstep = row.mask_full ? (size_t)row.mask_ld : 0;
 #pragma unroll 4
-        for (uint32_t c = te >> 7; c < NC; c += NT / 128) {
+        for (uint32_t c = c_lo + (te >> 7); c < c_hi; c += NT / 128) {
           const uint32_t n = n0 + c;
           if (n >= N) break;
           float v = tile[(size_t)c * BM + r];
@@ -250,7 +253,10 @@ __device__ __forceinline__ void epilogue_pass(const GemmEpilogue& epi, const flo
 
 // BNT = columns of the output tile: 128, or 64 for products with N <= 64 (small per-GPU batches), where a 128-wide tile
 // would spend half of every MMA and half of the B traffic on padding.
-template <int BNT>
+// CLUSTER: the gridDim.z K-splits of a tile form one thread-block cluster (1 x 1 x S); every CTA parks its partial tile in
+// its own shared memory, and CTA r adds all partial tiles of its 1 / S of the columns through distributed shared memory, in
+// split order, and runs the epilogue on that slice - no workspace round trip and no second kernel.
+template <int BNT, bool CLUSTER>
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ TmapPack tm, uint32_t M, uint32_t N,
                                                          uint32_t kb0, uint32_t kb1, uint32_t kb_per_split,
                                                          GemmEpilogue epi, uint32_t* flags) {
@@ -268,7 +274,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
   const uint32_t kb_end = min(kb0 + kb1, kb_begin + kb_per_split);
   const uint32_t total = kb_end > kb_begin ? kb_end - kb_begin : 0;
   const uint32_t nchunks = (total + kChunkKB - 1) / kChunkKB;
-  if (gridDim.z > 1) epi.C += (size_t)blockIdx.z * epi.ldc * N;   // raw partial tile of this split (mode is EPI_STORE)
+  if (!CLUSTER && gridDim.z > 1) epi.C += (size_t)blockIdx.z * epi.ldc * N;   // raw partial tile of this split (mode is EPI_STORE)
+  __shared__ uint32_t split_ok;   // CLUSTER: this CTA's partial tile is complete
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -303,6 +310,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), (int)n0);
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
+    }
+    if (CLUSTER) {   // all lanes: the two cluster barriers of the epilogue warps (see there)
+      __syncwarp();
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -340,6 +352,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         else ++in_chunk;
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
+    }
+    if (CLUSTER) {
+      __syncwarp();
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
   } else {
     // epilogue warps 2..9: TMEM lanes 32*(warp % 4) .. +31 (row of the tile = lane of TMEM); warps 2-5
@@ -396,8 +413,49 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     uint32_t all_ok;
     asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, 1, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
-    if (all_ok) {
-      epilogue_pass<BNT, 256>(epi, tile, te, blockIdx.x, m0, n0, M, N, cprev);
+    if (!CLUSTER) {
+      if (all_ok) epilogue_pass<BNT, 256>(epi, tile, te, blockIdx.x, m0, n0, M, N, cprev);
+    } else {
+      // every thread of every CTA of the cluster takes part in the two cluster barriers below (the TMA and MMA warps
+      // reach them further down); between them rank 0 reads the other CTAs' tiles
+      if (te == 0) split_ok = all_ok;
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+      {
+        // Rank r (= blockIdx.z: the cluster is 1 x 1 x gridDim.z) finishes columns [c_lo, c_hi) of the tile: it adds the
+        // S partial tiles of that slice in split order (the order of the split-K reduction kernel), its own from its
+        // shared memory and the others through distributed shared memory, and runs the epilogue on the slice.
+        const uint32_t S = gridDim.z, rank = blockIdx.z;
+        const uint32_t w = ((BNT + S - 1) / S + 7) & ~7u;
+        const uint32_t c_lo = min(rank * w, (uint32_t)BNT), c_hi = min(c_lo + w, (uint32_t)BNT);
+        uint32_t ok_all = all_ok, base[8];
+        for (uint32_t r = 0; r < S; ++r) {
+          uint32_t ra, v;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(&split_ok)), "r"(r));
+          asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(ra) : "memory");
+          ok_all &= v;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base[r & 7]) : "r"(smem_u32(tile)), "r"(r));
+        }
+        if (ok_all) {
+          const uint32_t f_lo = c_lo * (BM / 4), f_hi = c_hi * (BM / 4);   // 16-byte pieces of the slice
+          float4* t4 = reinterpret_cast<float4*>(tile);
+          for (uint32_t f = f_lo + te; f < f_hi; f += 256) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t r = 0; r < S; ++r) {
+              float4 pv;
+              asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(pv.x), "=f"(pv.y), "=f"(pv.z), "=f"(pv.w) : "r"(base[r & 7] + 16u * f) : "memory");
+              if (r == 0) acc = pv;
+              else { acc.x += pv.x; acc.y += pv.y; acc.z += pv.z; acc.w += pv.w; }
+            }
+            t4[f] = acc;
+          }
+          asm volatile("barrier.cta.sync 1, 256;" ::: "memory");   // the pass below reads other threads' pieces
+          epilogue_pass<BNT, 256>(epi, tile, te, blockIdx.x, m0, n0, M, N, cprev, c_lo, c_hi);
+        } else if (te == 0 && rank == 0) {
+          atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT);
+        }
+      }
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");   // every tile stays until all ranks have read it
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -984,8 +1042,8 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {
-    DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     attr_set = true;
   }
   const uint32_t bn = tile_cols(N);
@@ -1014,6 +1072,42 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   S = (kb_total + kb_per_split - 1) / kb_per_split;
   GemmEpilogue kepi = epi;
   float* part = nullptr;
+  // K splits as one thread-block cluster per tile (partial tiles meet in distributed shared memory) when every cluster
+  // of the launch can be resident at once; DYB200_CLUSTER_SPLITK=0 keeps the workspace + second-kernel form.
+  static int cluster_on = -1;
+  if (cluster_on < 0) { const char* e = getenv("DYB200_CLUSTER_SPLITK"); cluster_on = (e && e[0] == '0') ? 0 : 1; }
+  if (S > 1 && S <= 8 && cluster_on) {
+    static bool attr_set3 = false;
+    if (!attr_set3) {
+      DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      attr_set3 = true;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid.x, grid.y, S); cfg.blockDim = dim3(kThreads, 1, 1); cfg.dynamicSmemBytes = SMEM_BYTES; cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = S;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    static int max_clusters[2][9];   // [tile width][S], 0 = not asked yet
+    int& mc = max_clusters[bn == 64 ? 0 : 1][S];
+    if (mc == 0) {
+      int n = 0;
+      cudaError_t e = bn == 64 ? cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<64, true>, &cfg)
+                               : cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<128, true>, &cfg);
+      if (e != cudaSuccess) { (void)cudaGetLastError(); n = -1; }
+      mc = n > 0 ? n : -1;
+    }
+    if (mc > 0 && grid.x * grid.y <= (uint32_t)mc) {
+      GemmProfScope scope(ctx, flops, 1, M, N, kb_total * BK, (uint32_t)epi.mode);
+      if (bn == 64) cudaLaunchKernelEx(&cfg, k_gemm_tc<64, true>, tm, M, N, kb0, kb1, kb_per_split, epi, ctx->dev_flags);
+      else cudaLaunchKernelEx(&cfg, k_gemm_tc<128, true>, tm, M, N, kb0, kb1, kb_per_split, epi, ctx->dev_flags);
+      DYB_LAUNCHED(ctx);
+      return DYB200_OK;
+    }
+  }
   if (S > 1) {
     void* pw;
     rc = dyb200_scratch(ctx, (size_t)S * M * N * sizeof(float), &pw);
@@ -1041,8 +1135,8 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   {
     // times the MMA kernel (and the split-K reduction); the packing launches show up in the step time
     GemmProfScope scope(ctx, flops, 1, M, N, kb_total * BK, (uint32_t)epi.mode);
-    if (bn == 64) dyb_launch(k_gemm_tc<64>, grid, kThreads, SMEM_BYTES, ctx, tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
-    else dyb_launch(k_gemm_tc<128>, grid, kThreads, SMEM_BYTES, ctx, tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
+    if (bn == 64) dyb_launch(k_gemm_tc<64, false>, grid, kThreads, SMEM_BYTES, ctx, tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
+    else dyb_launch(k_gemm_tc<128, false>, grid, kThreads, SMEM_BYTES, ctx, tm, M, N, kb0, kb1, kb_per_split, kepi, ctx->dev_flags);
     DYB_LAUNCHED(ctx);
     if (S > 1 && epi.mode == EPI_LSTM_CELL) {
       dyb_launch(k_splitk_reduce_cell, stream_grid(ctx, (size_t)M / 16 * N + 1, 256), 256, 0, ctx, part, S, M, N, epi);

@@ -183,6 +183,14 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
     Tensor xall(Dim({E}, TB), m.x);
     look.forward_dev_impl(dev, {}, xall);
   }
+  // Order of the (time step, layer) calls.  The node-by-node driver goes time step by time step like the reference's
+  // graph.  The fused driver finishes a layer over all time steps before it starts the next one (layer l at step t needs
+  // layer l - 1 at step t and layer l at step t - 1, which both orders provide): the split weight planes of one layer
+  // (50 and 67 MB) then stay in the 126 MB L2 from step to step instead of alternating with the other layer's, which
+  // matters when the per-GPU batch is small and the products are bound by weight traffic.  Same values either way.
+  static const bool time_major_env = getenv("DYB200_LM_TIME_MAJOR") != nullptr;
+  const bool layer_major = c.fused && !time_major_env;
+  for (uint32_t pass = 0; pass < (layer_major ? L : 1u); ++pass)
   for (uint32_t t = 0; t < T; ++t) {
     if (!c.fused) {
       LookupNode look(tC, nullptr, B);
@@ -190,7 +198,7 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
       Tensor xt(Dim({E}, B), m.x + t * EB);
       look.forward_dev_impl(dev, {}, xt);
     }
-    for (uint32_t l = 0; l < L; ++l) {
+    for (uint32_t l = layer_major ? pass : 0u; l < (layer_major ? pass + 1 : L); ++l) {
       size_t idx = at(t, l);
       Tensor store[7];
       std::vector<const Tensor*> xs;
@@ -244,6 +252,7 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
     throw_status(dev, dyb200_softmax_output_bwd_fused(&cr, &ch, &cR, &cones, m.aux, &cgR, &cgb, &cdh, &cdr, DYB200_GEMM_A_IS_PARAM, dev.ctx));
   }
   Tensor tones(Dim({1}, B), m.ones);
+  for (uint32_t pass = 0; pass < (layer_major ? L : 1u); ++pass)
   for (uint32_t tt = T; tt-- > 0;) {
     if (!c.fused) {
       Tensor rt(Dim({V}, B), m.r + tt * VB), et(Dim({1}, B), m.errs + (size_t)tt * B), tdr(Dim({V}, B), m.dr);
@@ -255,7 +264,7 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
       affine.backward_dev_impl(dev, {&tbias, &tR, &htop}, rt, tdr, 1, tgR);      // dR += dr h^T
       affine.backward_dev_impl(dev, {&tbias, &tR, &htop}, rt, tdr, 2, tdhtop);   // dh += R^T dr
     }
-    for (uint32_t l = L; l-- > 0;) {
+    for (uint32_t l = layer_major ? L - pass : L; l-- > (layer_major ? L - pass - 1 : 0u);) {
       size_t idx = at(tt, l);
       Tensor store[7];
       std::vector<const Tensor*> xs;
