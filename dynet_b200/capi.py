@@ -117,7 +117,7 @@ OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200
          "dyb200_lookup_accumulate_grads_noalloc",
          "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm", "dyb200_fill", "dyb200_sum_all",
          "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_trainer_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end",
-         "dyb200_ctx_param_cache", "dyb200_ctx_params_changed", "dyb200_ctx_dependent_launch", "dyb200_vanilla_lstm_fwd_fused",
+         "dyb200_ctx_param_cache", "dyb200_ctx_params_changed", "dyb200_ctx_dependent_launch", "dyb200_ctx_cluster_splitk", "dyb200_vanilla_lstm_fwd_fused",
          "dyb200_vanilla_lstm_bwd_fused", "dyb200_vanilla_lstm_fwd_fused_at", "dyb200_vanilla_lstm_bwd_fused_at", "dyb200_wgrad_create", "dyb200_wgrad_destroy", "dyb200_wgrad_push",
          "dyb200_wgrad_flush", "dyb200_softmax_output_bwd_fused"]
 
@@ -185,6 +185,8 @@ def lib():
         L.dyb200_ctx_param_cache.argtypes = [C.c_void_p, C.c_int]
         L.dyb200_ctx_dependent_launch.restype = C.c_int
         L.dyb200_ctx_dependent_launch.argtypes = [C.c_void_p, C.c_int]
+        L.dyb200_ctx_cluster_splitk.restype = C.c_int
+        L.dyb200_ctx_cluster_splitk.argtypes = [C.c_void_p, C.c_int]
         L.dyb200_ctx_params_changed.restype = C.c_int
         L.dyb200_ctx_params_changed.argtypes = [C.c_void_p]
         L.dyb200_ctx_profile_begin.restype = C.c_int
@@ -367,6 +369,9 @@ class Context:
         st = list(states) + [None] * (3 - len(states))
         self.check(self.L.dyb200_trainer_update(RULES[rule], params, grads, st[0], st[1], st[2], n, C.byref(hyper), grad_sumsq,
                                                 int(zero_grads), self.h))
+
+    def cluster_splitk(self, enable):
+        self.check(self.L.dyb200_ctx_cluster_splitk(self.h, int(bool(enable))))
 
     def dependent_launch(self, enable):
         self.check(self.L.dyb200_ctx_dependent_launch(self.h, int(enable)))

@@ -33,6 +33,7 @@ struct dyb200_ctx {
   // time step is split once per optimizer step instead of once per GEMM.  Off by default: when on,
   // the caller must report every in-place parameter change (dyb200_ctx_params_changed).
   int pdl;               // launch kernels with programmatic stream serialization (see dyb_launch)
+  int cluster_splitk;    // K splits of a tensor-pipe product as one thread-block cluster per tile (see dyb200_ctx_cluster_splitk)
   int param_cache_on;
   uint64_t param_version, param_tick;
   struct ParamPack {

@@ -82,6 +82,7 @@ int dyb200_ctx_create(int device, void* stream, dyb200_ctx** out) {
   c->device = device;
   c->stream = (cudaStream_t)stream;
   c->sm_count = prop.multiProcessorCount;
+  { const char* e = getenv("DYB200_CLUSTER_SPLITK"); c->cluster_splitk = (e && e[0] == '0') ? 0 : 1; }
   if (cudaMalloc((void**)&c->dev_flags, DYB200_DEV_WORDS * 4) != cudaSuccess || cudaMemset(c->dev_flags, 0, DYB200_DEV_WORDS * 4) != cudaSuccess) {
     free(c);
     return DYB200_ENOMEM;
@@ -105,6 +106,12 @@ int dyb200_ctx_destroy(dyb200_ctx* ctx) {
 int dyb200_ctx_dependent_launch(dyb200_ctx* ctx, int enable) {
   if (!ctx) return DYB200_EINVAL;
   ctx->pdl = enable ? 1 : 0;
+  return DYB200_OK;
+}
+
+int dyb200_ctx_cluster_splitk(dyb200_ctx* ctx, int enable) {
+  if (!ctx) return DYB200_EINVAL;
+  ctx->cluster_splitk = enable ? 1 : 0;
   return DYB200_OK;
 }
 

@@ -698,7 +698,7 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
     else if (epi.mode == EPI_ACCUM) *dst += acc;
     else if (epi.mode == EPI_GATES) {
       acc += epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
-      *dst = m < 3 * epi.H ? sigmoidf_dev(acc) : tanhf(acc);
+      *dst = m < 3 * epi.H ? gate_sigmoid(acc) : gate_tanh(acc);   // (the activations of every gate epilogue)
     } else {
       *dst += acc * row.mask[row.mask_full ? (size_t)row.mask_ld * n : 0];
     }
@@ -739,8 +739,8 @@ __global__ void __launch_bounds__(256) k_splitk_reduce_cell(const float* __restr
       const float4 b = ld4(epi.bias + (size_t)g * H + u);
       const float fb = g == 1 ? epi.forget_bias : 0.f;
       a[g].x += b.x + fb; a[g].y += b.y + fb; a[g].z += b.z + fb; a[g].w += b.w + fb;
-      if (g == 3) a[g] = make_float4(tanhf(a[g].x), tanhf(a[g].y), tanhf(a[g].z), tanhf(a[g].w));
-      else a[g] = make_float4(sigmoidf_dev(a[g].x), sigmoidf_dev(a[g].y), sigmoidf_dev(a[g].z), sigmoidf_dev(a[g].w));
+      if (g == 3) a[g] = make_float4(gate_tanh(a[g].x), gate_tanh(a[g].y), gate_tanh(a[g].z), gate_tanh(a[g].w));
+      else a[g] = make_float4(gate_sigmoid(a[g].x), gate_sigmoid(a[g].y), gate_sigmoid(a[g].z), gate_sigmoid(a[g].w));
       st4(epi.C + (size_t)g * H + u + (size_t)epi.ldc * n, a[g]);
     }
     const size_t e = u + (size_t)H * n;
@@ -1073,10 +1073,8 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   GemmEpilogue kepi = epi;
   float* part = nullptr;
   // K splits as one thread-block cluster per tile (partial tiles meet in distributed shared memory) when every cluster
-  // of the launch can be resident at once; DYB200_CLUSTER_SPLITK=0 keeps the workspace + second-kernel form.
-  static int cluster_on = -1;
-  if (cluster_on < 0) { const char* e = getenv("DYB200_CLUSTER_SPLITK"); cluster_on = (e && e[0] == '0') ? 0 : 1; }
-  if (S > 1 && S <= 8 && cluster_on) {
+  // of the launch can be resident at once; dyb200_ctx_cluster_splitk(ctx, 0) keeps the workspace + second-kernel form.
+  if (S > 1 && S <= 8 && ctx->cluster_splitk) {
     static bool attr_set3 = false;
     if (!attr_set3) {
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));

@@ -85,6 +85,10 @@ int dyb200_ctx_param_cache(dyb200_ctx* ctx, int enable);
  * predecessor has completed (griddepcontrol.wait), so results do not change - only launch latency overlaps.  Work that other
  * code puts into the same stream between two calls is ordered as usual. */
 int dyb200_ctx_dependent_launch(dyb200_ctx* ctx, int enable);
+/* K splits of a tensor-pipe product as one thread-block cluster per output tile, reduced through distributed shared memory
+ * (on by default; the environment variable DYB200_CLUSTER_SPLITK=0 changes the default of new contexts).  Off: the splits
+ * go through a workspace and a second kernel.  Results are bitwise the same either way. */
+int dyb200_ctx_cluster_splitk(dyb200_ctx* ctx, int enable);
 int dyb200_ctx_params_changed(dyb200_ctx* ctx);
 /* Library build string ("dyb200 <n> sm_100a"). */
 const char* dyb200_version(void);

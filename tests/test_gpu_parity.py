@@ -673,6 +673,29 @@ def test_gemm(g, tA, tB, M, N, K):
         assert_close(g.host(C_), want, TOL_REDUCE, floor=0.1 * K ** 0.5 + 1.0, what="gemm %d%d acc=%d" % (tA, tB, acc))
 
 
+@pytest.mark.parametrize("M,N,K,acc", [(2048, 512, 4096, 1), (1536, 512, 4096, 1), (4096, 64, 2048, 0), (1024, 200, 1100, 1), (512, 96, 3000, 0)])
+def test_gemm_cluster_split_equals_workspace_split(g, M, N, K, acc):
+    """Products whose K is split: the cluster form (partial tiles reduced through distributed shared memory) and the
+    workspace form (second kernel) add the partial tiles in the same order, so they agree bit for bit."""
+    r = rng(M + N + K)
+    A, Bm, C0 = randn(r, K, M), randn(r, N, K), randn(r, N, M)
+    ctx = g.ctx()
+    A_, B_ = g.dev(A), g.dev(Bm)
+    outs = []
+    try:
+        for on in (1, 0):
+            ctx.cluster_splitk(on)
+            C_ = g.dev(C0)
+            ctx.gemm(0, 0, M, N, K, A_.data_ptr(), M, B_.data_ptr(), K, C_.data_ptr(), M, acc)
+            outs.append(g.host(C_).copy())
+    finally:
+        ctx.cluster_splitk(1)
+    assert np.array_equal(outs[0], outs[1])
+    ref = Bm.astype(np.float64) @ A.astype(np.float64) + (C0 if acc else 0)
+    assert_close(outs[0], ref, TOL_REDUCE, floor=0.1 * K ** 0.5 + 1.0, what="split gemm")
+    assert ctx.device_errors() == 0
+
+
 def test_gemm_3xtf32_accuracy(g):
     """Error of the tensor-pipe GEMM against float64, relative to sum_k |a||b| (the scale of the
     reduction): 3xTF32 keeps it below 2e-6; one plain TF32 pass would sit near 5e-4."""
@@ -1049,6 +1072,14 @@ def test_lstm_fwd_fused_cell_epilogue(oracle, g, capi, I, H, B, masks):
     assert np.array_equal(g.host(og), g.host(ng))
     assert np.array_equal(g.host(oc), g.host(nc))
     assert np.array_equal(g.host(oh), g.host(nh))
+    # K splits through a workspace and a second kernel instead of a cluster: the same bits
+    wg, wc, wh = (g.dev(np.full_like(a, 5.0)) for a in (gates, c_t, h_t))
+    try:
+        g.ctx().cluster_splitk(0)
+        g.ctx().lstm_fwd_fused(tx, th_, tc_, tWx, tWh, tb, tm[0] if masks else None, tm[1] if masks else None, at, g.T(wg), g.T(wc), g.T(wh))
+    finally:
+        g.ctx().cluster_splitk(1)
+    assert np.array_equal(g.host(wg), g.host(og)) and np.array_equal(g.host(wc), g.host(oc)) and np.array_equal(g.host(wh), g.host(oh))
     assert_close(g.host(og), gates, TOL_REDUCE, floor=GEMM_FLOOR, what="gates")
     assert_close(g.host(oc), c_t, TOL_REDUCE, floor=GEMM_FLOOR, what="c")
     assert_close(g.host(oh), h_t, TOL_REDUCE, floor=GEMM_FLOOR, what="h")
