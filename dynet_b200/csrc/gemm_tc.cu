@@ -992,29 +992,53 @@ int dyb200_tc_param_gates(dyb200_ctx* ctx, const float* src, uint32_t ld, uint32
 
 inline uint32_t tile_cols(uint32_t N) { return N <= 64 ? 64 : BN; }
 
-// Number of K splits: the one a small cost model says is fastest.  A launch takes waves x (k-blocks per CTA x 0.66 us +
-// 9 us of pipeline fill and epilogue), with waves = ceil(tiles x S / SMs); S > 1 adds the second kernel that sums the S
-// partial products into C ((S + 2) M N floats through HBM + a launch).  Measured on B200: the model is within 2 us of
-// the per-step LSTM products (dx / dh: 64 or 48 tiles, K = 4096 -> S = 2 and 3) and it removes most of the partly filled
-// last wave of the long-K products (dW: 256 tiles, 560 k-blocks, 1.73 waves -> S = 4, 6.92 waves).
+// Cost model of one launch (us): waves x (k-blocks per CTA x t_kb + 9 us of pipeline fill and epilogue), waves =
+// ceil(tiles x S / SMs); S > 1 adds the second kernel that sums the S partial products into C ((S + 2) M N floats through
+// HBM + a launch).  Measured on B200: within 2 us of the per-step LSTM products (dx / dh: 64 or 48 tiles, K = 4096 ->
+// S = 2 and 3).
+static double split_cost(double sms, uint32_t tiles, uint32_t kb_total, uint32_t S, double t_kb, double mn_bytes) {
+  const uint32_t kb_split = (kb_total + S - 1) / S;
+  double t = ceil((double)tiles * S / sms) * (kb_split * t_kb + 9.0);
+  if (S > 1) t += (S + 2) * mn_bytes / 5.0e6 + 5.0;   // bytes / (5 TB/s) in us
+  return t;
+}
+static uint32_t best_split(double sms, uint32_t tiles, uint32_t kb_total, double t_kb, double mn_bytes, double* cost) {
+  uint32_t best = 1;
+  double best_t = split_cost(sms, tiles, kb_total, 1, t_kb, mn_bytes);
+  for (uint32_t S = 2; S <= 8; ++S) {
+    if (kb_total / S < 8) break;   // at least 8 k-blocks per split
+    const uint32_t kb_split = (kb_total + S - 1) / S;
+    if ((kb_total + kb_split - 1) / kb_split != S) continue;
+    const double t = split_cost(sms, tiles, kb_total, S, t_kb, mn_bytes);
+    if (t < best_t * 0.97) { best = S; best_t = t; }   // a split must win by 3 %
+  }
+  if (cost) *cost = best_t;
+  return best;
+}
+// The partly filled last round of a many-tile product can run as a product of its own (see dyb200_tc_gemm_packed) when its
+// tiles lie in one column of tiles and K is long.
+static bool tail_can_run_apart(const dyb200_ctx* ctx, uint32_t tiles_m, uint32_t tiles, uint32_t kb_total, uint32_t bn) {
+  const uint32_t tail = tiles % (uint32_t)ctx->sm_count;
+  return tiles > (uint32_t)ctx->sm_count && tail > 0 && tail <= tiles_m && 2 * tail <= (uint32_t)ctx->sm_count && kb_total >= 64 && bn == BN;
+}
+
+// Number of K splits of a product: the one the cost model says is fastest.  For a product with more tiles than SMs the
+// unsplit form is the persistent kernel (epilogues overlapped, ~3 us left per tile) with its last round split apart.
 uint32_t dyb200_tc_splits(const dyb200_ctx* ctx, uint32_t M, uint32_t N, uint32_t kb_total) {
   const uint32_t bn = tile_cols(N);
-  const uint32_t tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-  const double sms = (double)ctx->sm_count, t_kb = bn == 64 ? 0.40 : 0.66, t_fixed = 9.0;
+  const uint32_t tiles_m = (M + BM - 1) / BM, tiles = tiles_m * ((N + bn - 1) / bn);
+  const double sms = (double)ctx->sm_count, t_kb = bn == 64 ? 0.40 : 0.66;
   const double mn_bytes = 4.0 * (double)M * (double)N;
-  uint32_t best = 1;
-  double best_t = 0;
-  for (uint32_t S = 1; S <= 8; ++S) {
-    if (S > 1 && kb_total / S < 8) break;   // at least 8 k-blocks per split
-    const uint32_t kb_split = (kb_total + S - 1) / S;
-    const uint32_t S_eff = (kb_total + kb_split - 1) / kb_split;
-    if (S_eff != S) continue;
-    const double waves = ceil((double)tiles * S / sms);
-    double t = waves * (kb_split * t_kb + t_fixed);
-    if (S > 1) t += (S + 2) * mn_bytes / 5.0e6 + 5.0;   // bytes / (5 TB/s) in us
-    if (S == 1 || t < best_t * 0.97) { best = S; best_t = t; }   // a split must win by 3 %
+  double cost;
+  const uint32_t S = best_split(sms, tiles, kb_total, t_kb, mn_bytes, &cost);
+  if (S > 1 && tail_can_run_apart(ctx, tiles_m, tiles, kb_total, bn)) {
+    const uint32_t tail = tiles % (uint32_t)ctx->sm_count;
+    double tail_cost;
+    best_split(sms, tail, kb_total, t_kb, mn_bytes * tail / tiles, &tail_cost);
+    const double persistent = (tiles / (uint32_t)ctx->sm_count) * (kb_total * t_kb + 3.0) + tail_cost;
+    if (persistent < cost) return 1;
   }
-  return best;
+  return S;
 }
 
 int dyb200_tc_param2(dyb200_ctx* ctx, const float* src, uint32_t rows, const float* src2, uint32_t rows2, uint32_t ld,
@@ -1117,18 +1141,38 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   static int persist = -1;   // DYB200_PERSISTENT=0: one CTA per tile for every product
   if (persist < 0) { const char* e = getenv("DYB200_PERSISTENT"); persist = (e && e[0] == '0') ? 0 : 1; }
   if (persist && S == 1 && grid.x * grid.y > (uint32_t)ctx->sm_count) {
+    // A partly filled last round (dR: 632 tiles = 4 rounds of 148 + 40) would keep 108 SMs idle for a whole tile time.
+    // When those last tiles lie in one column of tiles and K is long, the persistent kernel stops before them and they
+    // run as a product of their own (the sub-matrices of the same operands), which the cost model splits along K.
+    uint32_t tiles_run = grid.x * grid.y;
+    const uint32_t tail = tiles_run % (uint32_t)ctx->sm_count;
+    const bool plain_epi = (epi.mode == EPI_STORE || epi.mode == EPI_ACCUM || epi.mode == EPI_BIAS) && epi.split_m == 0;
+    const bool tail_apart = plain_epi && tail_can_run_apart(ctx, grid.x, tiles_run, kb_total, bn);
+    if (tail_apart) tiles_run -= tail;
     static bool attr_set2 = false;
     if (!attr_set2) {
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_persist<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PERSIST_BYTES));
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_persist<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PERSIST_BYTES));
       attr_set2 = true;
     }
-    GemmProfScope scope(ctx, flops, 1, M, N, kb_total * BK, (uint32_t)epi.mode);
-    const uint32_t tiles = grid.x * grid.y;
-    if (bn == 64) dyb_launch(k_gemm_persist<64>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles, epi, ctx->dev_flags);
-    else dyb_launch(k_gemm_persist<128>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles, epi, ctx->dev_flags);
-    DYB_LAUNCHED(ctx);
-    return DYB200_OK;
+    {
+      GemmProfScope scope(ctx, flops * ((double)tiles_run / (grid.x * grid.y)), 1, M, N, kb_total * BK, (uint32_t)epi.mode);
+      if (bn == 64) dyb_launch(k_gemm_persist<64>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, epi, ctx->dev_flags);
+      else dyb_launch(k_gemm_persist<128>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, epi, ctx->dev_flags);
+      DYB_LAUNCHED(ctx);
+    }
+    if (!tail_apart) return DYB200_OK;
+    // the last `tail` row blocks of the last column of tiles
+    const uint32_t m_off = (grid.x - tail) * BM, n_off = (grid.y - 1) * bn;
+    PackedOp A2[2], B2[2];
+    for (int p = 0; p < npairs; ++p) {
+      A2[p] = A[p]; A2[p].rows = M - m_off; A2[p].hi += (size_t)m_off * A[p].pitch; A2[p].lo += (size_t)m_off * A[p].pitch;
+      B2[p] = B[p]; B2[p].rows = N - n_off; B2[p].hi += (size_t)n_off * B[p].pitch; B2[p].lo += (size_t)n_off * B[p].pitch;
+    }
+    GemmEpilogue e2 = epi;
+    e2.C += m_off + (size_t)epi.ldc * n_off;
+    if (epi.mode == EPI_BIAS) e2.bias += m_off;
+    return dyb200_tc_gemm_packed(ctx, M - m_off, N - n_off, npairs, A2, B2, e2);
   }
   {
     // times the MMA kernel (and the split-K reduction); the packing launches show up in the step time
