@@ -479,17 +479,34 @@ constexpr int SMEM_PERSIST_BYTES = SMEM_BYTES + BM * 64 * 4;
 // product - ahead of the epilogue warps, which drain nothing while they write out the previous tile.
 constexpr uint32_t kPersistBufs = 4;
 
+// Tile order.  gm == 0: row block fastest (the launch order of the one-tile kernel).  gm > 0: groups of gm row blocks, row
+// block fastest within a group, then the column block, then the next group.  The 148 tiles in flight then touch gm A
+// blocks and ~148 / gm B blocks instead of all A blocks and two B blocks, and the A blocks of a group stay in L2 while
+// the B blocks stream past them (output layer, gm = 16: 25 MB of operands per round instead of 83 MB).
+__device__ __forceinline__ void persist_tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t gm, uint32_t& mt,
+                                                    uint32_t& nt) {
+  if (gm == 0) { mt = tile % tiles_m; nt = tile / tiles_m; return; }
+  const uint32_t per_group = gm * tiles_n;
+  const uint32_t g = tile / per_group, r = tile - g * per_group;
+  const uint32_t rows = min(gm, tiles_m - g * gm);   // the last group may be lower
+  nt = r / rows;
+  mt = g * gm + r % rows;
+}
+
 // The two single-thread roles are functions of their own: their loops pace the tensor pipe and keep their own registers.
 template <int BNT>
 __device__ __noinline__ void persist_producer(const TmapPack* tm, unsigned char* ring, uint64_t* full_bar, uint64_t* empty_bar,
-                                              uint32_t tiles, uint32_t tiles_m, uint32_t kb0, uint32_t kb1, uint32_t* flags) {
+                                              uint32_t tiles, uint32_t tiles_m, uint32_t tiles_n, uint32_t gm, uint32_t kb0,
+                                              uint32_t kb1, uint32_t* flags) {
   constexpr int TILE_B_BYTES = BNT * BK * 4;
   constexpr int STAGE_TX = 2 * TILE_BYTES + 2 * TILE_B_BYTES;
   const uint32_t kb = kb0 + kb1;
   uint32_t s = 0, ph = 0;
   bool fail = false;
   for (uint32_t tile = blockIdx.x; tile < tiles && !fail; tile += gridDim.x) {
-    const uint32_t m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BNT;
+    uint32_t mt, nt;
+    persist_tile_coords(tile, tiles_m, tiles_n, gm, mt, nt);
+    const uint32_t m0 = mt * BM, n0 = nt * BNT;
     for (uint32_t g = 0; g < kb; ++g) {
       if (!mbar_wait(&empty_bar[s], ph ^ 1)) { fail = true; break; }
       const uint32_t pair = g < kb0 ? 0 : 1, kblk = pair ? g - kb0 : g;
@@ -550,7 +567,7 @@ __device__ __forceinline__ void bar_arrive(uint32_t id, uint32_t count) { asm vo
 template <int BNT>
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_persist(const __grid_constant__ TmapPack tm, uint32_t M, uint32_t N,
                                                               uint32_t kb0, uint32_t kb1, uint32_t tiles_m, uint32_t tiles,
-                                                              GemmEpilogue epi, uint32_t* flags) {
+                                                              uint32_t gm, GemmEpilogue epi, uint32_t* flags) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[kPersistBufs], acc_empty[kPersistBufs];
@@ -577,7 +594,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_persist(const __grid_const
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
-    if (lane == 0) persist_producer<BNT>(&tm, ring, full_bar, empty_bar, tiles, tiles_m, kb0, kb1, flags);
+    if (lane == 0) persist_producer<BNT>(&tm, ring, full_bar, empty_bar, tiles, tiles_m, (N + BNT - 1) / BNT, gm, kb0, kb1, flags);
   } else if (warp == 1) {
     if (lane == 0) persist_issue<BNT>(ring, full_bar, empty_bar, acc_full, acc_empty, tmem_base, tiles, kb, flags);
   } else {
@@ -590,7 +607,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_persist(const __grid_const
     bool ok = true;
 #pragma unroll 1
     for (uint32_t tile = blockIdx.x, j = 0; tile < tiles; tile += gridDim.x, ++j) {
-      const uint32_t mt = tile % tiles_m, m0 = mt * BM, n0 = (tile / tiles_m) * BNT + 64 * half;
+      uint32_t mt, nt;
+      persist_tile_coords(tile, tiles_m, (N + BNT - 1) / BNT, gm, mt, nt);
+      const uint32_t m0 = mt * BM, n0 = nt * BNT + 64 * half;
       float sum[64];
 #pragma unroll
       for (int q = 0; q < 64; ++q) sum[q] = 0.f;
@@ -1157,8 +1176,14 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     }
     {
       GemmProfScope scope(ctx, flops * ((double)tiles_run / (grid.x * grid.y)), 1, M, N, kb_total * BK, (uint32_t)epi.mode);
-      if (bn == 64) dyb_launch(k_gemm_persist<64>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, epi, ctx->dev_flags);
-      else dyb_launch(k_gemm_persist<128>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, epi, ctx->dev_flags);
+      // grouped tile order when the A operand has many row blocks (unless the last round runs apart, which relies on the
+      // row-block-fastest order); DYB200_PERSIST_GROUP overrides the group height (0 = row block fastest)
+      static int group_env = -2;
+      if (group_env == -2) { const char* e = getenv("DYB200_PERSIST_GROUP"); group_env = e ? atoi(e) : -1; }
+      uint32_t gm = (!tail_apart && grid.x > 16) ? 16u : 0u;
+      if (group_env >= 0 && !tail_apart) gm = (uint32_t)group_env;
+      if (bn == 64) dyb_launch(k_gemm_persist<64>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, gm, epi, ctx->dev_flags);
+      else dyb_launch(k_gemm_persist<128>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, gm, epi, ctx->dev_flags);
       DYB_LAUNCHED(ctx);
     }
     if (!tail_apart) return DYB200_OK;

@@ -210,6 +210,23 @@ def build_cases(torch, ctx, small):
     cases.append(Case("affine_transform_fwd_10000x17920x1024", 0, mk_aff, aff_fwd, 10 ** 9))
     cases[-1].flops = 2.0 * Vv * TB * Hh
 
+    # backward of the same output layer in one call: PickNegLogSoftmax gradient written as the operands of dR and dh
+    # (k_softmax_bwd_split: 4 V n bytes in, 16 V n bytes out), then the two products
+    nB = TB if not small else 4096
+    def mk_outbwd():
+        tgt = rng.integers(0, Vv, size=nB).astype(np.uint32)
+        aux = torch.zeros(3 * nB, device=dev)
+        aux[:nB] = 9.3                                                     # logsumexp of each column (any plausible value)
+        aux[2 * nB:].view(torch.int32).copy_(torch.from_numpy(tgt.view(np.int32)))
+        return dict(x=torch.randn(nB, Vv, device=dev), h=torch.randn(nB, Hh, device=dev) * 0.5, R=torch.randn(Hh, Vv, device=dev) * 0.02,
+                    dE=torch.ones(nB, device=dev), aux=aux, dR=torch.zeros(Hh, Vv, device=dev), db=torch.zeros(Vv, device=dev),
+                    dh=torch.zeros(nB, Hh, device=dev))
+    def outbwd(b):
+        ctx.softmax_output_bwd_fused(T(b["x"], [Vv], nB), T(b["h"], [Hh], nB), T(b["R"], [Vv, Hh], 1), T(b["dE"], [1], nB), b["aux"].data_ptr(),
+                                     T(b["dR"], [Vv, Hh], 1), T(b["db"], [Vv], 1), T(b["dh"], [Hh], nB))
+    cases.append(Case("softmax_output_bwd_fused_10000x%dx1024" % nB, 0, mk_outbwd, outbwd, 10 ** 9))
+    cases[-1].flops = 4.0 * Vv * nB * Hh
+
     # trainer update rules over the config-4 parameter buffer (30.06 M floats)
     NP = 30_060_000 if not small else 1 << 20
     def mk_tr():
