@@ -283,6 +283,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  if (threadIdx.x == 32 * 2) {   // (an epilogue thread, idle until the first chunk is done) descriptors of the first loads
+#pragma unroll
+    for (int q = 0; q < 8; ++q) asm volatile("prefetch.tensormap [%0];" ::"l"(&tm.t[q]) : "memory");
+  }
   if (warp == 1) {   // the whole warp allocates the accumulator columns
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
