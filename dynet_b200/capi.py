@@ -119,7 +119,7 @@ OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200
          "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_trainer_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end",
          "dyb200_ctx_param_cache", "dyb200_ctx_params_changed", "dyb200_ctx_dependent_launch", "dyb200_ctx_cluster_splitk", "dyb200_vanilla_lstm_fwd_fused",
          "dyb200_vanilla_lstm_bwd_fused", "dyb200_vanilla_lstm_fwd_fused_at", "dyb200_vanilla_lstm_bwd_fused_at", "dyb200_wgrad_create", "dyb200_wgrad_destroy", "dyb200_wgrad_push",
-         "dyb200_wgrad_flush", "dyb200_softmax_output_bwd_fused"]
+         "dyb200_wgrad_flush", "dyb200_wgrad_pack_inputs", "dyb200_softmax_output_bwd_fused"]
 
 
 def exported_symbols():
@@ -214,6 +214,8 @@ def lib():
         L.dyb200_trainer_update.restype = C.c_int
         L.dyb200_trainer_update.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                             C.POINTER(TrainerHyper), C.c_void_p, C.c_int, C.c_void_p]
+        L.dyb200_wgrad_pack_inputs.restype = C.c_int
+        L.dyb200_wgrad_pack_inputs.argtypes = [C.c_void_p, tp, tp, C.c_uint32, C.c_void_p]
         L.dyb200_softmax_output_bwd_fused.restype = C.c_int
         L.dyb200_softmax_output_bwd_fused.argtypes = [tp, tp, tp, tp, C.c_void_p, tp, tp, tp, tp, C.c_uint32, C.c_void_p]
         L.dyb200_gemm.restype = C.c_int
@@ -343,6 +345,9 @@ class Context:
         o = self._opt
         self.check(self.L.dyb200_softmax_output_bwd_fused(o(x), o(h), o(R), o(dEdf), aux_ptr, o(dR), o(db), o(dh), o(dx_scratch),
                                                           flags, self.h))
+
+    def wgrad_pack_inputs(self, w, x_all, mask_x, step):
+        self.check(self.L.dyb200_wgrad_pack_inputs(w, self._opt(x_all), self._opt(mask_x), step, self.h))
 
     def wgrad_create(self, M, N0, N1, Kcap):
         h = C.c_void_p()

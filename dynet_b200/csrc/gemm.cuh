@@ -39,7 +39,30 @@ struct GemmEpilogue {
   const float* maskC2 = nullptr; uint32_t maskc2_ld = 0; int maskc2_full = 0;
   // EPI_LSTM_CELL only: previous cell state and the two outputs, all H x N with leading dimension H
   const float* c_prev = nullptr; float* c_out = nullptr; float* h_out = nullptr;
+  // EPI_LSTM_CELL, optional: h .* hmask also goes out as the split operands of its consumers: straight planes (row =
+  // batch column, reduction index = hidden unit) for the next time step's gate product and transposed planes (row = hidden
+  // unit, reduction index = batch column) for the layer's weight-gradient product.  All 16-byte aligned, H % 4 == 0.
+  float* hn_hi = nullptr; float* hn_lo = nullptr; uint32_t hn_pitch = 0;
+  float* ht_hi = nullptr; float* ht_lo = nullptr; uint32_t ht_pitch = 0;
+  const float* hmask = nullptr; uint32_t hmask_ld = 0; int hmask_full = 0;
 };
+#ifdef __CUDACC__
+// h .* mask of four hidden units [u, u + 4) of batch column n, written as operand planes (see GemmEpilogue::hn_hi).
+__device__ __forceinline__ void epi_emit_h(const GemmEpilogue& epi, uint32_t u, uint32_t n, float4 h) {
+  if (epi.hmask) {
+    const float4 mk = *reinterpret_cast<const float4*>(epi.hmask + u + (epi.hmask_full ? (size_t)epi.hmask_ld * n : 0));
+    h.x *= mk.x; h.y *= mk.y; h.z *= mk.z; h.w *= mk.w;
+  }
+  float4 hi, lo;
+  split_tf32(h.x, hi.x, lo.x); split_tf32(h.y, hi.y, lo.y); split_tf32(h.z, hi.z, lo.z); split_tf32(h.w, hi.w, lo.w);
+  *reinterpret_cast<float4*>(epi.hn_hi + (size_t)n * epi.hn_pitch + u) = hi;
+  *reinterpret_cast<float4*>(epi.hn_lo + (size_t)n * epi.hn_pitch + u) = lo;
+  float* th = epi.ht_hi + (size_t)u * epi.ht_pitch + n;
+  float* tl = epi.ht_lo + (size_t)u * epi.ht_pitch + n;
+  th[0] = hi.x; th[epi.ht_pitch] = hi.y; th[2 * (size_t)epi.ht_pitch] = hi.z; th[3 * (size_t)epi.ht_pitch] = hi.w;
+  tl[0] = lo.x; tl[epi.ht_pitch] = lo.y; tl[2 * (size_t)epi.ht_pitch] = lo.z; tl[3 * (size_t)epi.ht_pitch] = lo.w;
+}
+#endif
 // Row m of the product -> destination pointer of column 0, leading dimension and mask of that row.
 struct EpiRow { float* c; uint32_t ldc; const float* mask; uint32_t mask_ld; int mask_full; };
 __host__ __device__ inline EpiRow epi_row(const GemmEpilogue& e, uint32_t m) {
@@ -67,6 +90,7 @@ constexpr int kLayoutGates = 2;
 struct PackJob {
   const float* src; const float* mask; float* hi; float* lo;
   uint32_t ld, rows, K, mask_ld, pitch, gx, perm_H;
+  uint32_t mask_period;   // > 0: a full mask repeats every mask_period batch columns (one mask for every time step of a sequence)
   int k_is_fast, mask_full, vec;
 };
 struct PackJobs { PackJob job[kMaxPackJobs]; uint32_t start[kMaxPackJobs + 1]; int n; };
@@ -101,6 +125,14 @@ int dyb200_wgrad_push_b_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const floa
 int dyb200_wgrad_reserve_a_at(dyb200_wgrad* w, uint32_t col, uint32_t k, float** a_hi, float** a_lo, uint32_t* pitch, dyb200_ctx* ctx);
 int dyb200_wgrad_pack_a_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const float* a, uint32_t lda, dyb200_ctx* ctx, PackJobs* batch);
 uint32_t dyb200_wgrad_rows(const dyb200_wgrad* w);
+// Pre-split sequence inputs (dyb200_wgrad_pack_inputs): the forward operand planes of the step that starts at column `col`,
+// when they are available.  x: rows [col, col + k) of the planes filled by dyb200_wgrad_pack_inputs; h: the planes the
+// previous step's LSTM epilogue wrote for this column.  Return false when the caller has to split that input itself.
+bool dyb200_wgrad_x_planes(const dyb200_wgrad* w, uint32_t col, uint32_t k, PackedOp* out);
+bool dyb200_wgrad_h_planes(const dyb200_wgrad* w, uint32_t col, uint32_t k, PackedOp* out);
+// Destinations for the split planes of the NEXT step's h input (the step that starts at column col + k), or false when
+// there is no next step or the inputs were not pre-split.  Marks those planes as the h input of column col + k.
+bool dyb200_wgrad_next_h(dyb200_wgrad* w, uint32_t col, uint32_t k, GemmEpilogue* epi);
 uint32_t dyb200_wgrad_fill(const dyb200_wgrad* w);
 int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda, const float* b0, uint32_t ldb0,
                               const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1,

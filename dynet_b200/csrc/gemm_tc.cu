@@ -173,7 +173,9 @@ __device__ __forceinline__ void epilogue_pass(const GemmEpilogue& epi, const flo
         const float4 cn = make_float4(lstm_cell_c(g[0].x, g[3].x, g[1].x, cprev[k].x), lstm_cell_c(g[0].y, g[3].y, g[1].y, cprev[k].y),
                                       lstm_cell_c(g[0].z, g[3].z, g[1].z, cprev[k].z), lstm_cell_c(g[0].w, g[3].w, g[1].w, cprev[k].w));
         st4(epi.c_out + e, cn);
-        st4(epi.h_out + e, make_float4(lstm_cell_h(g[2].x, cn.x), lstm_cell_h(g[2].y, cn.y), lstm_cell_h(g[2].z, cn.z), lstm_cell_h(g[2].w, cn.w)));
+        const float4 hv = make_float4(lstm_cell_h(g[2].x, cn.x), lstm_cell_h(g[2].y, cn.y), lstm_cell_h(g[2].z, cn.z), lstm_cell_h(g[2].w, cn.w));
+        st4(epi.h_out + e, hv);
+        if (epi.hn_hi) epi_emit_h(epi, u, n, hv);
       }
     }
   } else {
@@ -771,7 +773,9 @@ __global__ void __launch_bounds__(256) k_splitk_reduce_cell(const float* __restr
     const float4 c = make_float4(lstm_cell_c(a[0].x, a[3].x, a[1].x, cp.x), lstm_cell_c(a[0].y, a[3].y, a[1].y, cp.y),
                                  lstm_cell_c(a[0].z, a[3].z, a[1].z, cp.z), lstm_cell_c(a[0].w, a[3].w, a[1].w, cp.w));
     st4(epi.c_out + e, c);
-    st4(epi.h_out + e, make_float4(lstm_cell_h(a[2].x, c.x), lstm_cell_h(a[2].y, c.y), lstm_cell_h(a[2].z, c.z), lstm_cell_h(a[2].w, c.w)));
+    const float4 hv = make_float4(lstm_cell_h(a[2].x, c.x), lstm_cell_h(a[2].y, c.y), lstm_cell_h(a[2].z, c.z), lstm_cell_h(a[2].w, c.w));
+    st4(epi.h_out + e, hv);
+    if (epi.hn_hi) epi_emit_h(epi, u, n, hv);
   }
 }
 
@@ -793,14 +797,16 @@ __global__ void __launch_bounds__(256) k_pack_multi(const PackJobs jobs) {
   float* __restrict__ lo = job.lo;
   const uint32_t ld = job.ld, rows = job.rows, K = job.K, pitch = job.pitch, mask_ld = job.mask_ld;
   const int mask_full = job.mask_full;
+  const uint32_t mask_period = job.mask_period;
   if (job.k_is_fast) {
     const uint32_t r = unit / job.gx, bx = unit % job.gx;
+    const uint32_t mr = mask_period ? r % mask_period : r;   // batch column of the mask
     if (job.vec) {
       const uint32_t k = (bx * 256 + threadIdx.x) * 4;
       if (k < K) {
         float4 v = ld4(src + k + (size_t)ld * r);
         if (mask) {
-          float4 mk = ld4(mask + k + (mask_full ? (size_t)mask_ld * r : 0));
+          float4 mk = ld4(mask + k + (mask_full ? (size_t)mask_ld * mr : 0));
           v.x *= mk.x; v.y *= mk.y; v.z *= mk.z; v.w *= mk.w;
         }
         float4 h, l;
@@ -811,7 +817,7 @@ __global__ void __launch_bounds__(256) k_pack_multi(const PackJobs jobs) {
     } else {
       for (uint32_t k = bx * 1024 + threadIdx.x; k < min(K, (bx + 1) * 1024); k += 256) {
         float v = src[k + (size_t)ld * r];
-        if (mask) v *= mask[k + (mask_full ? (size_t)mask_ld * r : 0)];
+        if (mask) v *= mask[k + (mask_full ? (size_t)mask_ld * mr : 0)];
         float h, l;
         split_tf32(v, h, l);
         hi[k + (size_t)pitch * r] = h;
@@ -828,7 +834,7 @@ __global__ void __launch_bounds__(256) k_pack_multi(const PackJobs jobs) {
     float v = 0.f;
     if (r < rows && k < K) {
       v = src[r + (size_t)ld * k];
-      if (mask) v *= mask[r + (mask_full ? (size_t)mask_ld * k : 0)];
+      if (mask) v *= mask[r + (mask_full ? (size_t)mask_ld * (mask_period ? k % mask_period : k) : 0)];
     }
     tile[ty + 8 * i][tx] = v;
   }
@@ -891,7 +897,8 @@ int pack_flush_impl(dyb200_ctx* ctx, PackJobs* jobs) {
 // rows = 4H gate rows are written interleaved (destination row 128 t + 32 q + l <- source row q H + 32 t + l) so that
 // every 128-row tile holds the four gates of 32 hidden units.
 int pack(dyb200_ctx* ctx, const float* src, uint32_t ld, int layout, uint32_t rows, uint32_t K, const float* mask,
-         uint32_t mask_ld, int mask_full, float* hi, float* lo, uint32_t pitch, PackJobs* batch = nullptr) {
+         uint32_t mask_ld, int mask_full, float* hi, float* lo, uint32_t pitch, PackJobs* batch = nullptr,
+         uint32_t mask_period = 0) {
   const bool k_is_fast = layout == 1;
   if (rows == 0 || K == 0) return DYB200_OK;
   PackJobs local;
@@ -901,7 +908,7 @@ int pack(dyb200_ctx* ctx, const float* src, uint32_t ld, int layout, uint32_t ro
   PackJob& j = q->job[q->n];
   j.src = src; j.mask = mask; j.hi = hi; j.lo = lo;
   j.ld = ld; j.rows = rows; j.K = K; j.mask_ld = mask_ld; j.pitch = pitch;
-  j.k_is_fast = k_is_fast ? 1 : 0; j.mask_full = mask_full;
+  j.k_is_fast = k_is_fast ? 1 : 0; j.mask_full = mask_full; j.mask_period = mask_period;
   j.perm_H = layout == kLayoutGates ? rows / 4 : 0;
   uint64_t units;
   if (k_is_fast) {
@@ -1269,6 +1276,12 @@ struct dyb200_wgrad {
   uint32_t k;    // columns of A filled so far (the product at flush time runs over [0, k))
   uint32_t kb;   // columns of the B operands filled so far
   PackedOp A, B[2];
+  // Pre-split sequence inputs (dyb200_wgrad_pack_inputs): forward operand planes, one row per column of the sequence.
+  // X: x .* mask_x of all columns; Hs: h_tm1 .* mask_h, rows [c, c + batch) = input of the step that starts at column c,
+  // written by the LSTM epilogue of the step before.  x_cols = columns of X that are valid; h_col = the column whose Hs
+  // rows (and B[1] columns) the last forward call wrote; step = columns per step of that sequence.
+  PackedOp X, Hs;
+  uint32_t x_cols, h_col, step;
 };
 
 // Same as dyb200_wgrad_push, but the packing work is queued in `batch` (the caller launches it).
@@ -1313,9 +1326,10 @@ int dyb200_wgrad_reserve(dyb200_wgrad* w, uint32_t k, float** a_hi, float** a_lo
 // operand (the gate gradient) during the backward pass: step t of a sequence uses columns [t * k, (t + 1) * k) both times.
 int dyb200_wgrad_push_b_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const float* b0, uint32_t ldb0, const float* mask0, int mask0_full,
                            const float* b1, uint32_t ldb1, const float* mask1, int mask1_full, dyb200_ctx* ctx, PackJobs* batch) {
-  DYB_CHECK_ARG(ctx, w && b0 && (w->N[1] == 0 || b1), "wgrad_push_b_at: null argument");
+  // (b0 == nullptr: the first operand's columns are already in place, see dyb200_wgrad_pack_inputs)
+  DYB_CHECK_ARG(ctx, w && (w->N[1] == 0 || b1), "wgrad_push_b_at: null argument");
   DYB_CHECK_ARG(ctx, (uint64_t)col + k <= w->Kcap, "wgrad_push_b_at: columns [%u, %u) exceed the capacity %u", col, col + k, w->Kcap);
-  int rc = pack(ctx, b0, ldb0, 0, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + col, w->B[0].lo + col, w->Kcap, batch);
+  int rc = b0 ? pack(ctx, b0, ldb0, 0, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + col, w->B[0].lo + col, w->Kcap, batch) : DYB200_OK;
   if (rc) return rc;
   if (w->N[1]) {
     rc = pack(ctx, b1, ldb1, 0, w->N[1], k, mask1, ldb1, mask1_full, w->B[1].hi + col, w->B[1].lo + col, w->Kcap, batch);
@@ -1337,6 +1351,29 @@ int dyb200_wgrad_pack_a_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const floa
   if (col + k > w->k) w->k = col + k;
   return DYB200_OK;
 }
+bool dyb200_wgrad_x_planes(const dyb200_wgrad* w, uint32_t col, uint32_t k, PackedOp* out) {
+  if (!w || !w->X.hi || k != w->step || (uint64_t)col + k > w->x_cols) return false;
+  *out = w->X;
+  out->rows = k; out->K = w->N[0];
+  out->hi += (size_t)col * w->X.pitch; out->lo += (size_t)col * w->X.pitch;
+  return true;
+}
+bool dyb200_wgrad_h_planes(const dyb200_wgrad* w, uint32_t col, uint32_t k, PackedOp* out) {
+  if (!w || !w->Hs.hi || k != w->step || w->h_col != col || (uint64_t)col + k > w->x_cols) return false;
+  *out = w->Hs;
+  out->rows = k; out->K = w->N[1];
+  out->hi += (size_t)col * w->Hs.pitch; out->lo += (size_t)col * w->Hs.pitch;
+  return true;
+}
+bool dyb200_wgrad_next_h(dyb200_wgrad* w, uint32_t col, uint32_t k, GemmEpilogue* epi) {
+  if (!w || !w->Hs.hi || k != w->step || (uint64_t)col + 2 * (uint64_t)k > w->x_cols) return false;
+  const uint32_t next = col + k;
+  epi->hn_hi = w->Hs.hi + (size_t)next * w->Hs.pitch; epi->hn_lo = w->Hs.lo + (size_t)next * w->Hs.pitch; epi->hn_pitch = w->Hs.pitch;
+  epi->ht_hi = w->B[1].hi + next; epi->ht_lo = w->B[1].lo + next; epi->ht_pitch = w->Kcap;
+  w->h_col = next;
+  if (next + k > w->kb) w->kb = next + k;
+  return true;
+}
 uint32_t dyb200_wgrad_rows(const dyb200_wgrad* w) { return w->M; }
 uint32_t dyb200_wgrad_fill(const dyb200_wgrad* w) { return w->k; }
 
@@ -1347,6 +1384,7 @@ int dyb200_wgrad_create(dyb200_ctx* ctx, uint32_t M, uint32_t N0, uint32_t N1, u
   dyb200_wgrad* w = (dyb200_wgrad*)calloc(1, sizeof(dyb200_wgrad));
   if (!w) return dyb200_fail(ctx, DYB200_ENOMEM, "wgrad_create: host allocation failed");
   w->M = M; w->N[0] = N0; w->N[1] = N1; w->Kcap = round_up(Kcap, 32); w->k = 0; w->kb = 0;
+  w->x_cols = 0; w->h_col = 0xffffffffu; w->step = 0;
   auto alloc = [&](PackedOp* p, uint32_t rows) -> bool {
     p->rows = rows; p->K = 0; p->pitch = w->Kcap;
     size_t bytes = (size_t)rows * w->Kcap * sizeof(float);
@@ -1366,7 +1404,7 @@ int dyb200_wgrad_create(dyb200_ctx* ctx, uint32_t M, uint32_t N0, uint32_t N1, u
 
 int dyb200_wgrad_destroy(dyb200_wgrad* w) {
   if (!w) return DYB200_OK;
-  for (PackedOp* p : {&w->A, &w->B[0], &w->B[1]}) { if (p->hi) cudaFree(p->hi); if (p->lo) cudaFree(p->lo); }
+  for (PackedOp* p : {&w->A, &w->B[0], &w->B[1], &w->X, &w->Hs}) { if (p->hi) cudaFree(p->hi); if (p->lo) cudaFree(p->lo); }
   free(w);
   return DYB200_OK;
 }
@@ -1384,6 +1422,40 @@ int dyb200_wgrad_push(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda,
 }
 
 // C0 += A * B0^T (and C1 += A * B1^T) over everything pushed since the last flush; empties the accumulator.
+int dyb200_wgrad_pack_inputs(dyb200_wgrad* w, const dyb200_tensor* x_all, const dyb200_tensor* mask_x, uint32_t step, dyb200_ctx* ctx) {
+  { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
+  DYB_CHECK_ARG(ctx, w && x_all && x_all->v && step > 0, "wgrad_pack_inputs: null argument");
+  const uint32_t I = t_rows(x_all), n = x_all->bd;
+  DYB_CHECK_ARG(ctx, t_cols(x_all) == 1 && I == w->N[0] && w->N[1] > 0 && n <= w->Kcap && n % step == 0,
+                "wgrad_pack_inputs: x is %u x %u, the accumulator expects %u rows, at most %u columns, whole steps of %u", I, n, w->N[0], w->Kcap, step);
+  DYB_CHECK_ARG(ctx, !mask_x || (t_rows(mask_x) == I && (mask_x->bd == step || mask_x->bd == 1)), "wgrad_pack_inputs: mask shape mismatch");
+  if (!w->X.hi) {   // first use: planes for the forward operands of every column
+    auto alloc = [&](PackedOp* p, uint32_t K) -> bool {
+      p->rows = w->Kcap; p->K = K; p->pitch = round_up(K, 32);
+      const size_t bytes = (size_t)w->Kcap * p->pitch * sizeof(float);
+      if (cudaMalloc((void**)&p->hi, bytes) != cudaSuccess) { cudaGetLastError(); p->hi = nullptr; return false; }
+      if (cudaMalloc((void**)&p->lo, bytes) != cudaSuccess) { cudaGetLastError(); cudaFree(p->hi); p->hi = nullptr; p->lo = nullptr; return false; }
+      return true;
+    };
+    if (!alloc(&w->X, w->N[0]) || !alloc(&w->Hs, w->N[1])) {
+      if (w->X.hi) { cudaFree(w->X.hi); cudaFree(w->X.lo); w->X.hi = w->X.lo = nullptr; }
+      return dyb200_fail(ctx, DYB200_ENOMEM, "wgrad_pack_inputs: cudaMalloc failed for %u columns", w->Kcap);
+    }
+  }
+  const float* mk = mask_x ? mask_x->v : nullptr;
+  const int full = mask_x ? mask_x->bd == step : 0;
+  PackJobs batch;
+  dyb200_tc_pack_begin(&batch);
+  // forward operand: row = column of the sequence, reduction index = input feature; weight-gradient operand: the transpose
+  int rc = pack(ctx, x_all->v, I, 1, n, I, mk, I, full, w->X.hi, w->X.lo, w->X.pitch, &batch, step);
+  if (!rc) rc = pack(ctx, x_all->v, I, 0, I, n, mk, I, full, w->B[0].hi, w->B[0].lo, w->Kcap, &batch, step);
+  if (!rc) rc = pack_flush_impl(ctx, &batch);
+  if (rc) return rc;
+  w->x_cols = n; w->step = step; w->h_col = 0xffffffffu;
+  if (n > w->kb) w->kb = n;
+  return DYB200_OK;
+}
+
 int dyb200_wgrad_flush(dyb200_wgrad* w, float* C0, uint32_t ldc0, float* C1, uint32_t ldc1, dyb200_ctx* ctx) {
   { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   DYB_CHECK_ARG(ctx, w && C0 && (w->N[1] == 0 || C1), "wgrad_flush: null argument");

@@ -554,16 +554,22 @@ int dyb200_vanilla_lstm_fwd_fused_at(const dyb200_tensor* x, const dyb200_tensor
       dyb200_tc_pack_begin(&batch);
       const float* mx = attrs->dropout ? mask_x->v : nullptr;
       const float* mh = attrs->dropout ? mask_h->v : nullptr;
-      if ((rc = dyb200_tc_pack(ctx, x->v, I, true, B, I, mx, I, mx ? mask_x->bd == B : 0, &Bp[0], &batch))) return rc;
-      if ((rc = dyb200_tc_pack(ctx, h_tm1->v, H, true, B, H, mh, H, mh ? mask_h->bd == B : 0, &Bp[1], &batch))) return rc;
-      if (deferred) {   // the same inputs, transposed, are the B operands of this step's weight-gradient products
-        DYB_CHECK_ARG(ctx, dyb200_wgrad_rows(deferred) == G, "lstm_fwd_fused: the deferred accumulator has %u rows, the layer %u", dyb200_wgrad_rows(deferred), G);
-        if ((rc = dyb200_wgrad_push_b_at(deferred, deferred_col, B, x->v, I, mx, mx ? mask_x->bd == B : 0, h_tm1->v, H, mh,
-                                         mh ? mask_h->bd == B : 0, ctx, &batch))) return rc;
+      const int mx_full = mx ? mask_x->bd == B : 0, mh_full = mh ? mask_h->bd == B : 0;
+      if (deferred) DYB_CHECK_ARG(ctx, dyb200_wgrad_rows(deferred) == G, "lstm_fwd_fused: the deferred accumulator has %u rows, the layer %u", dyb200_wgrad_rows(deferred), G);
+      // Inputs that dyb200_wgrad_pack_inputs (x, all steps at once) or the previous step's epilogue (h) already wrote as
+      // operand planes are used as they are; the others are split here, also into the weight-gradient accumulator.
+      const bool x_pre = deferred && dyb200_wgrad_x_planes(deferred, deferred_col, B, &Bp[0]);
+      const bool h_pre = x_pre && dyb200_wgrad_h_planes(deferred, deferred_col, B, &Bp[1]);
+      if (!x_pre && (rc = dyb200_tc_pack(ctx, x->v, I, true, B, I, mx, I, mx_full, &Bp[0], &batch))) return rc;
+      if (!h_pre && (rc = dyb200_tc_pack(ctx, h_tm1->v, H, true, B, H, mh, H, mh_full, &Bp[1], &batch))) return rc;
+      if (deferred && !(x_pre && h_pre)) {   // the same inputs, transposed, are the B operands of this step's weight-gradient products
+        if ((rc = dyb200_wgrad_push_b_at(deferred, deferred_col, B, x_pre ? nullptr : x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx, &batch))) return rc;
       }
       if ((rc = dyb200_tc_pack_flush(ctx, &batch))) return rc;
       GemmEpilogue e{EPI_LSTM_CELL, gates->v, G, b->v, H, attrs->forget_gate_bias, nullptr, 0, 0};
       e.c_prev = c_tm1->v; e.c_out = c_t->v; e.h_out = h_t->v;
+      // with pre-split inputs this step's epilogue also writes h_t .* mask_h as the operand planes of the next step
+      if (x_pre && (!mh || aligned16(mh)) && dyb200_wgrad_next_h(deferred, deferred_col, B, &e)) { e.hmask = mh; e.hmask_ld = H; e.hmask_full = mh_full; }
       return dyb200_tc_gemm_packed(ctx, G, B, 2, A, Bp, e);
     }
   }

@@ -192,6 +192,13 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   const bool layer_major = c.fused && !time_major_env;
   for (uint32_t pass = 0; pass < (layer_major ? L : 1u); ++pass)
   for (uint32_t t = 0; t < T; ++t) {
+    if (layer_major && t == 0) {
+      // the inputs of this layer for all time steps are complete (embeddings, or the layer below): split them in one launch
+      const uint32_t l = pass, I = l == 0 ? E : H;
+      Tensor xall(Dim({I}, TB), l == 0 ? m.x : m.hs + at(0, l - 1) * HB), mxl(Dim({I}, B), c.dropout ? const_cast<float*>(masks[2 * l]) : nullptr);
+      dyb200_tensor cxa = to_c(xall), cmx = to_c(mxl);
+      throw_status(dev, dyb200_wgrad_pack_inputs(m.wg_layer[l], &cxa, c.dropout ? &cmx : nullptr, B, dev.ctx));
+    }
     if (!c.fused) {
       LookupNode look(tC, nullptr, B);
       look.aux_mem = m.tok + (size_t)t * B;

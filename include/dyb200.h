@@ -279,6 +279,15 @@ int dyb200_wgrad_destroy(dyb200_wgrad* w);
 int dyb200_wgrad_push(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda, const float* b0, uint32_t ldb0,
                       const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1,
                       int mask1_full, dyb200_ctx* ctx);
+/* Optional, for a layer whose inputs of ALL time steps exist before its first step runs (any layer of a stack that is
+ * run layer by layer): x_all = Dim({I}, n) holds the inputs of the n / step time steps side by side (`step` columns
+ * each), mask_x = Dim({I}, step) or Dim({I}, 1) is the layer's input dropout mask (the same for every time step, as in
+ * dynet/lstm.cc:1010-1030) or NULL.  One launch splits x_all .* mask_x into the operand planes of the gate products and
+ * of the weight-gradient product (columns [0, n) of the accumulator).  Afterwards dyb200_vanilla_lstm_fwd_fused_at, called
+ * with this accumulator for deferred_col = 0, step, 2 step, ... in order, launches no operand split of its own except
+ * for h_tm1 of the first step: each step's epilogue also writes h_t .* mask_h as the next step's operand planes.  The x
+ * argument of those calls must be the matching columns of x_all.  Results are bitwise those of the calls without it. */
+int dyb200_wgrad_pack_inputs(dyb200_wgrad* w, const dyb200_tensor* x_all, const dyb200_tensor* mask_x, uint32_t step, dyb200_ctx* ctx);
 int dyb200_wgrad_flush(dyb200_wgrad* w, float* C0, uint32_t ldc0, float* C1, uint32_t ldc1, dyb200_ctx* ctx);
 
 /* ---- A14 autobatch ragged movers (same argument meaning as dynet/gpu-ops.h:14-15;

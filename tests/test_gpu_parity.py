@@ -1144,6 +1144,59 @@ def test_lstm_fused_at_columns_equals_append(g, capi, I, H, B):
     assert g.ctx().device_errors() == 0
 
 
+@pytest.mark.parametrize("I,H,B,T,full", [(512, 1024, 256, 3, True), (256, 512, 64, 4, False), (128, 256, 32, 3, True)])
+def test_lstm_presplit_inputs_equal_per_step_splits(g, capi, I, H, B, T, full):
+    """dyb200_wgrad_pack_inputs (x of all steps split in one launch, h handed from epilogue to epilogue as operand planes)
+    gives bitwise the states, gates and weight gradients of the same calls without it: tensor-pipe shapes with one tile
+    per CTA, with K splits (batch 64) and a shape that takes the split through the workspace."""
+    import torch
+    r = rng(157)
+    Wx, Wh, b = glorot(r, 4 * H, I), glorot(r, 4 * H, H), randn(r, 4 * H, scale=0.1)
+    mB = B if full else 1
+    mx = ((r.random((mB, I)) < 0.8) / 0.8).astype(np.float32)
+    mh = ((r.random((mB, H)) < 0.8) / 0.8).astype(np.float32)
+    xall = randn(r, T * B, I)
+    dhs = [randn(r, B, H) for _ in range(T)]
+    at = capi.LstmGatesAttrs(1, 0.0, 1.0)
+    D = {k: g.dev(v) for k, v in dict(Wx=Wx, Wh=Wh, b=b, mx=mx, mh=mh, x=xall).items()}
+    tWx, tWh, tb, tmx, tmh = g.T(D["Wx"], [4 * H, I], 1), g.T(D["Wh"], [4 * H, H], 1), g.T(D["b"], [4 * H], 1), g.T(D["mx"]), g.T(D["mh"])
+
+    def run(presplit):
+        ctx = g.ctx()
+        w = ctx.wgrad_create(4 * H, I, H, T * B)
+        try:
+            launches0 = ctx.launches()
+            if presplit:
+                ctx.wgrad_pack_inputs(w, g.T(D["x"], [I], T * B), tmx, B)
+            h = [torch.zeros(B, H, device="cuda")] + [torch.empty(B, H, device="cuda") for _ in range(T)]
+            c = [torch.zeros(B, H, device="cuda")] + [torch.empty(B, H, device="cuda") for _ in range(T)]
+            gates = [torch.empty(B, 4 * H, device="cuda") for _ in range(T)]
+            xd = [D["x"][t * B:(t + 1) * B] for t in range(T)]
+            for t in range(T):
+                ctx.lstm_fwd_fused_at(g.T(xd[t]), g.T(h[t]), g.T(c[t]), tWx, tWh, tb, tmx, tmh, at, g.T(gates[t]), g.T(c[t + 1]), g.T(h[t + 1]), w, t * B)
+            fwd_launches = ctx.launches() - launches0
+            dh = [g.dev(d) for d in dhs]
+            dc = [torch.zeros(B, H, device="cuda") for _ in range(T)]
+            dx = [torch.zeros(B, I, device="cuda") for _ in range(T)]
+            db = torch.zeros(4 * H, device="cuda")
+            for t in range(T - 1, -1, -1):
+                ctx.lstm_bwd_fused_at(g.T(xd[t]), g.T(h[t]), g.T(c[t]), tWx, tWh, tmx, tmh, g.T(gates[t]), g.T(c[t + 1]), g.T(dh[t]), g.T(dc[t]),
+                                      g.T(dx[t]), None if t == 0 else g.T(dh[t - 1]), None if t == 0 else g.T(dc[t - 1]), None, None,
+                                      g.T(db, [4 * H], 1), at, w, t * B)
+            dWx, dWh = torch.zeros(I, 4 * H, device="cuda"), torch.zeros(H, 4 * H, device="cuda")
+            ctx.wgrad_flush(w, dWx.data_ptr(), 4 * H, dWh.data_ptr(), 4 * H)
+            torch.cuda.synchronize()
+            return [g.host(v) for v in [dWx, dWh, db] + dx + h[1:] + c[1:] + gates], fwd_launches
+        finally:
+            ctx.wgrad_destroy(w)
+
+    (a, la), (p, lp) = run(True), run(False)
+    for k, (u, v) in enumerate(zip(a, p)):
+        assert np.array_equal(u, v), k
+    assert la < lp, (la, lp)          # fewer launches: no operand split per step after the first
+    assert g.ctx().device_errors() == 0
+
+
 def test_new_entry_points_reject_bad_arguments(g, capi):
     """Argument errors come back as the reference's exception class (std::invalid_argument), never as a fault."""
     r = rng(616)
