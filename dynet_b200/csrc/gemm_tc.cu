@@ -1128,7 +1128,7 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   float* part = nullptr;
   // K splits as one thread-block cluster per tile (partial tiles meet in distributed shared memory) when every cluster
   // of the launch can be resident at once; dyb200_ctx_cluster_splitk(ctx, 0) keeps the workspace + second-kernel form.
-  if (S > 1 && S <= 8 && ctx->cluster_splitk) {
+  if (S > 1 && ctx->cluster_splitk) {
     static bool attr_set3 = false;
     if (!attr_set3) {
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -1137,22 +1137,41 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     }
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(grid.x, grid.y, S); cfg.blockDim = dim3(kThreads, 1, 1); cfg.dynamicSmemBytes = SMEM_BYTES; cfg.stream = ctx->stream;
+    cfg.blockDim = dim3(kThreads, 1, 1); cfg.dynamicSmemBytes = SMEM_BYTES; cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = S;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    static int max_clusters[2][9];   // [tile width][S], 0 = not asked yet
-    int& mc = max_clusters[bn == 64 ? 0 : 1][S];
-    if (mc == 0) {
-      int n = 0;
-      cudaError_t e = bn == 64 ? cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<64, true>, &cfg)
-                               : cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<128, true>, &cfg);
-      if (e != cudaSuccess) { (void)cudaGetLastError(); n = -1; }
-      mc = n > 0 ? n : -1;
+    static int max_clusters[2][9];   // [tile width][cluster size], 0 = not asked yet
+    auto fits = [&](uint32_t Sc) -> bool {
+      int& mc = max_clusters[bn == 64 ? 0 : 1][Sc];
+      if (mc == 0) {
+        cfg.gridDim = dim3(grid.x, grid.y, Sc);
+        attr[0].val.clusterDim.z = Sc;
+        int n = 0;
+        cudaError_t e = bn == 64 ? cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<64, true>, &cfg)
+                                 : cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<128, true>, &cfg);
+        if (e != cudaSuccess) { (void)cudaGetLastError(); n = -1; }
+        mc = n > 0 ? n : -1;
+      }
+      return mc > 0 && grid.x * grid.y <= (uint32_t)mc;
+    };
+    // The model's split count, or the nearest smaller one whose clusters all fit on the GPU (cluster sizes 3, 5 .. 8 leave
+    // SMs of a GPC unused), if the cluster form of that count still beats the workspace form of the model's count.
+    const double t_kb = bn == 64 ? 0.40 : 0.66, mn_bytes = 4.0 * (double)M * (double)N;
+    const double ws_cost = split_cost((double)ctx->sm_count, grid.x * grid.y, kb_total, S, t_kb, mn_bytes);
+    uint32_t Sc = 0;
+    for (uint32_t cand = S < 8 ? S : 8; cand >= 2 && cand + 2 >= S; --cand) {
+      const uint32_t kbs = (kb_total + cand - 1) / cand;
+      if ((kb_total + kbs - 1) / kbs != cand || !fits(cand)) continue;
+      if (kbs * t_kb + 9.0 + 2.0 < ws_cost || cand == S) Sc = cand;
+      break;
     }
-    if (mc > 0 && grid.x * grid.y <= (uint32_t)mc) {
+    if (Sc) {
+      kb_per_split = (kb_total + Sc - 1) / Sc;
+      cfg.gridDim = dim3(grid.x, grid.y, Sc);
+      attr[0].val.clusterDim.z = Sc;
       GemmProfScope scope(ctx, flops, 1, M, N, kb_total * BK, (uint32_t)epi.mode);
       if (bn == 64) cudaLaunchKernelEx(&cfg, k_gemm_tc<64, true>, tm, M, N, kb0, kb1, kb_per_split, epi, ctx->dev_flags);
       else cudaLaunchKernelEx(&cfg, k_gemm_tc<128, true>, tm, M, N, kb0, kb1, kb_per_split, epi, ctx->dev_flags);
