@@ -1478,8 +1478,11 @@ int dyb200_wgrad_pack_inputs(dyb200_wgrad* w, const dyb200_tensor* x_all, const 
 int dyb200_wgrad_flush(dyb200_wgrad* w, float* C0, uint32_t ldc0, float* C1, uint32_t ldc1, dyb200_ctx* ctx) {
   { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
   DYB_CHECK_ARG(ctx, w && C0 && (w->N[1] == 0 || C1), "wgrad_flush: null argument");
+  // (pre-split inputs belong to one sequence: the next one has to call dyb200_wgrad_pack_inputs again)
+  const uint32_t kb_seen = w->kb;
+  w->x_cols = 0; w->h_col = 0xffffffffu;
   if (w->k == 0) { w->kb = 0; return DYB200_OK; }
-  DYB_CHECK_ARG(ctx, w->kb >= w->k, "wgrad_flush: the B operands cover %u columns, the A operand %u", w->kb, w->k);
+  DYB_CHECK_ARG(ctx, kb_seen >= w->k, "wgrad_flush: the B operands cover %u columns, the A operand %u", kb_seen, w->k);
   PackedOp A = w->A;
   A.K = w->k;
   for (int j = 0; j < 2; ++j) {
