@@ -20,6 +20,15 @@ constexpr int kWarpVals = kWarpRowsMax / 32;
 constexpr int kBlockVec = 4;        // float4 per thread in the CTA-per-column path
 constexpr int kBlockRowsMax = kBlock * 4 * kBlockVec;
 
+// One ex2.approx per element (relative error ~2^-22 plus |x - m| * 2^-24 from the scaled argument),
+// one rescale test per 16 elements; four 128-bit loads are in flight per thread.
+constexpr float kLog2e = 1.4426950408889634f;
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 enum Mode { M_SOFTMAX, M_LOGSOFTMAX, M_LSE, M_PNLS };
 
 struct ColArgs {
@@ -110,7 +119,9 @@ __global__ void __launch_bounds__(kBlock) k_col_block_vec(ColArgs a) {
     for (int k = 0; k < kBlockVec; ++k) {
       uint32_t i = threadIdx.x + kBlock * k;
       if (i < rows4) {
-        float4 e = make_float4(expf(v[k].x - mx), expf(v[k].y - mx), expf(v[k].z - mx), expf(v[k].w - mx));
+        const float ml = mx * kLog2e;
+        float4 e = make_float4(ex2_approx(fmaf(v[k].x, kLog2e, -ml)), ex2_approx(fmaf(v[k].y, kLog2e, -ml)),
+                               ex2_approx(fmaf(v[k].z, kLog2e, -ml)), ex2_approx(fmaf(v[k].w, kLog2e, -ml)));
         s += (e.x + e.y) + (e.z + e.w);
         if (MODE == M_SOFTMAX) v[k] = e;
       }
@@ -119,12 +130,13 @@ __global__ void __launch_bounds__(kBlock) k_col_block_vec(ColArgs a) {
     finish_column<MODE>(a, c, mx, s, threadIdx.x == 0);
     if (MODE == M_SOFTMAX || MODE == M_LOGSOFTMAX) {
       float z = logf(s) + mx;
+      const float inv = 1.f / s;   // one division per column
       float* yc = a.y + c * a.rows;
 #pragma unroll
       for (int k = 0; k < kBlockVec; ++k) {
         uint32_t i = threadIdx.x + kBlock * k;
         if (i < rows4) {
-          float4 r = MODE == M_SOFTMAX ? make_float4(v[k].x / s, v[k].y / s, v[k].z / s, v[k].w / s)
+          float4 r = MODE == M_SOFTMAX ? make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv)
                                        : make_float4(v[k].x - z, v[k].y - z, v[k].z - z, v[k].w - z);
           st4_stream(yc + 4 * i, r);
         }
@@ -136,14 +148,6 @@ __global__ void __launch_bounds__(kBlock) k_col_block_vec(ColArgs a) {
 
 // ---- CTA per column, any length: streaming online (max, sum) -------------------
 // The running sum is kept in base 2 relative to the running max: s = sum 2^((x - m) * log2(e)).
-// One ex2.approx per element (relative error ~2^-22 plus |x - m| * 2^-24 from the scaled argument),
-// one rescale test per 16 elements; four 128-bit loads are in flight per thread.
-constexpr float kLog2e = 1.4426950408889634f;
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 __device__ __forceinline__ void online_add(float& m, float& s, float v) {
   if (v > m) { s = s * ex2_approx((m - v) * kLog2e) + 1.f; m = v; }
   else s += ex2_approx((v - m) * kLog2e);
