@@ -117,6 +117,7 @@ OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200
          "dyb200_lookup_accumulate_grads_noalloc",
          "dyb200_parallel_memcpy", "dyb200_parallel_accumulate", "dyb200_gemm", "dyb200_fill", "dyb200_sum_all",
          "dyb200_squared_norm", "dyb200_sgd_update", "dyb200_trainer_update", "dyb200_ctx_profile_begin", "dyb200_ctx_profile_end",
+         "dyb200_ctx_profile_count", "dyb200_ctx_profile_launch",
          "dyb200_ctx_param_cache", "dyb200_ctx_params_changed", "dyb200_ctx_dependent_launch", "dyb200_ctx_cluster_splitk", "dyb200_vanilla_lstm_fwd_fused",
          "dyb200_vanilla_lstm_bwd_fused", "dyb200_vanilla_lstm_fwd_fused_at", "dyb200_vanilla_lstm_bwd_fused_at", "dyb200_wgrad_create", "dyb200_wgrad_destroy", "dyb200_wgrad_push",
          "dyb200_wgrad_flush", "dyb200_wgrad_pack_inputs", "dyb200_softmax_output_bwd_fused"]
@@ -193,6 +194,11 @@ def lib():
         L.dyb200_ctx_profile_begin.argtypes = [C.c_void_p, C.c_int]
         L.dyb200_ctx_profile_end.restype = C.c_int
         L.dyb200_ctx_profile_end.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_double)]
+        L.dyb200_ctx_profile_count.restype = C.c_int
+        L.dyb200_ctx_profile_count.argtypes = [C.c_void_p]
+        L.dyb200_ctx_profile_launch.restype = C.c_int
+        L.dyb200_ctx_profile_launch.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_int), C.POINTER(C.c_float),
+                                                C.POINTER(C.c_double)]
         L.dyb200_lookup_accumulate_grads.restype = C.c_int
         L.dyb200_lookup_accumulate_grads.argtypes = [C.c_uint, C.POINTER(C.c_uint32), C.c_void_p, C.c_void_p,
                                                      C.c_void_p, C.c_uint, C.c_uint, C.c_void_p]
@@ -263,6 +269,15 @@ class Context:
         ms, n, fl = (C.c_double * 2)(), (C.c_uint64 * 2)(), (C.c_double * 2)()
         self.check(self.L.dyb200_ctx_profile_end(self.h, ms, n, fl))
         return {"simt": (ms[0], int(n[0]), fl[0]), "tensor": (ms[1], int(n[1]), fl[1])}
+
+    def profile_launches(self):
+        """Per recorded GEMM launch (call between profile_begin and profile_end): (M, N, K, epilogue mode, path, ms, flops)."""
+        out = []
+        for k in range(int(self.L.dyb200_ctx_profile_count(self.h))):
+            shape, path, ms, fl = (C.c_uint32 * 4)(), C.c_int(0), C.c_float(0), C.c_double(0)
+            self.check(self.L.dyb200_ctx_profile_launch(self.h, k, shape, C.byref(path), C.byref(ms), C.byref(fl)))
+            out.append((shape[0], shape[1], shape[2], shape[3], path.value, ms.value, fl.value))
+        return out
 
     def device_errors(self):
         f = C.c_uint32(0)

@@ -35,6 +35,10 @@ struct dyb200_ctx {
   int pdl;               // launch kernels with programmatic stream serialization (see dyb_launch)
   int cluster_splitk;    // K splits of a tensor-pipe product as one thread-block cluster per tile (see dyb200_ctx_cluster_splitk)
   int param_cache_on;
+  // per-device facts this context has established on its device: kernels whose dynamic shared-memory limit is raised
+  // (bit per kernel family) and how many thread-block clusters of each size fit on the GPU at once
+  uint32_t func_attr_done;
+  int max_clusters[2][9];
   uint64_t param_version, param_tick;
   struct ParamPack {
     const float* src; const float* src2; uint32_t ld, rows, rows2, K, pitch; int k_is_fast;   // src2 / rows2: a second matrix stacked below the first

@@ -82,7 +82,7 @@ int dyb200_ctx_create(int device, void* stream, dyb200_ctx** out) {
   c->device = device;
   c->stream = (cudaStream_t)stream;
   c->sm_count = prop.multiProcessorCount;
-  { const char* e = getenv("DYB200_CLUSTER_SPLITK"); c->cluster_splitk = (e && e[0] == '0') ? 0 : 1; }
+  c->cluster_splitk = 1;
   if (cudaMalloc((void**)&c->dev_flags, DYB200_DEV_WORDS * 4) != cudaSuccess || cudaMemset(c->dev_flags, 0, DYB200_DEV_WORDS * 4) != cudaSuccess) {
     free(c);
     return DYB200_ENOMEM;
@@ -140,22 +140,32 @@ int dyb200_ctx_profile_begin(dyb200_ctx* ctx, int capacity) {
   return DYB200_OK;
 }
 
+int dyb200_ctx_profile_launch(dyb200_ctx* ctx, int k, uint32_t shape_out[4], int* path_out, float* ms_out, double* flops_out) {
+  if (!ctx->prof_ev) return dyb200_fail(ctx, DYB200_ERUNTIME, "profile_launch: profiling is not on");
+  DYB_CHECK_ARG(ctx, k >= 0 && k < ctx->prof_n, "profile_launch: index %d out of range (%d launches recorded)", k, ctx->prof_n);
+  DYB_CUDA(ctx, cudaEventSynchronize(ctx->prof_ev[2 * k + 1]));
+  float t = 0.f;
+  DYB_CUDA(ctx, cudaEventElapsedTime(&t, ctx->prof_ev[2 * k], ctx->prof_ev[2 * k + 1]));
+  if (shape_out) for (int q = 0; q < 4; ++q) shape_out[q] = ctx->prof_shape[4 * k + q];
+  if (path_out) *path_out = ctx->prof_path[k];
+  if (ms_out) *ms_out = t;
+  if (flops_out) *flops_out = ctx->prof_flops[k];
+  return DYB200_OK;
+}
+
+int dyb200_ctx_profile_count(const dyb200_ctx* ctx) { return ctx && ctx->prof_ev ? ctx->prof_n : 0; }
+
 int dyb200_ctx_profile_end(dyb200_ctx* ctx, double* ms_out, uint64_t* launches_out, double* flops_out) {
   if (!ctx->prof_ev) return dyb200_fail(ctx, DYB200_ERUNTIME, "profile_end: profiling is not on");
   DYB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   double ms[2] = {0, 0}, fl[2] = {0, 0};
   uint64_t cnt[2] = {0, 0};
-  const char* dump = getenv("DYB200_GEMM_PROFILE_DUMP");   // optional CSV of every recorded launch
-  FILE* df = dump ? fopen(dump, "a") : nullptr;
   for (int k = 0; k < ctx->prof_n; ++k) {
     float t = 0.f;
     DYB_CUDA(ctx, cudaEventElapsedTime(&t, ctx->prof_ev[2 * k], ctx->prof_ev[2 * k + 1]));
     int p = ctx->prof_path[k] ? 1 : 0;
     ms[p] += t; fl[p] += ctx->prof_flops[k]; cnt[p]++;
-    if (df) fprintf(df, "%d,%u,%u,%u,%u,%.6f,%.0f\n", p, ctx->prof_shape[4 * k], ctx->prof_shape[4 * k + 1], ctx->prof_shape[4 * k + 2],
-                    ctx->prof_shape[4 * k + 3], t, ctx->prof_flops[k]);
   }
-  if (df) fclose(df);
   for (int k = 0; k < 2 * ctx->prof_cap; ++k) cudaEventDestroy(ctx->prof_ev[k]);
   free(ctx->prof_ev); free(ctx->prof_flops); free(ctx->prof_path); free(ctx->prof_shape);
   ctx->prof_ev = nullptr; ctx->prof_flops = nullptr; ctx->prof_path = nullptr; ctx->prof_shape = nullptr;

@@ -1087,11 +1087,11 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   EncodeTiledFn enc;
   int rc = get_encoder(ctx, &enc);
   if (rc) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // (function attributes are per device: the context remembers what it has set on its own device)
+  if (!(ctx->func_attr_done & 1u)) {
     DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    attr_set = true;
+    ctx->func_attr_done |= 1u;
   }
   const uint32_t bn = tile_cols(N);
   TmapPack tm;
@@ -1122,11 +1122,10 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   // K splits as one thread-block cluster per tile (partial tiles meet in distributed shared memory) when every cluster
   // of the launch can be resident at once; dyb200_ctx_cluster_splitk(ctx, 0) keeps the workspace + second-kernel form.
   if (S > 1 && ctx->cluster_splitk) {
-    static bool attr_set3 = false;
-    if (!attr_set3) {
+    if (!(ctx->func_attr_done & 2u)) {
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      attr_set3 = true;
+      ctx->func_attr_done |= 2u;
     }
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -1136,9 +1135,8 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    static int max_clusters[2][9];   // [tile width][cluster size], 0 = not asked yet
     auto fits = [&](uint32_t Sc) -> bool {
-      int& mc = max_clusters[bn == 64 ? 0 : 1][Sc];
+      int& mc = ctx->max_clusters[bn == 64 ? 0 : 1][Sc];   // [tile width][cluster size], 0 = not asked yet on this device
       if (mc == 0) {
         cfg.gridDim = dim3(grid.x, grid.y, Sc);
         attr[0].val.clusterDim.z = Sc;
@@ -1172,9 +1170,7 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     kepi = GemmEpilogue{EPI_STORE, part, M, nullptr, 0, 0.f, nullptr, 0, 0};   // (no second destination)
     grid.z = S;
   }
-  static int persist = -1;   // DYB200_PERSISTENT=0: one CTA per tile for every product
-  if (persist < 0) { const char* e = getenv("DYB200_PERSISTENT"); persist = (e && e[0] == '0') ? 0 : 1; }
-  if (persist && S == 1 && grid.x * grid.y > (uint32_t)ctx->sm_count) {
+  if (S == 1 && grid.x * grid.y > (uint32_t)ctx->sm_count) {
     // A partly filled last round (dR: 632 tiles = 4 rounds of 148 + 40) would keep 108 SMs idle for a whole tile time.
     // When those last tiles lie in one column of tiles and K is long, the persistent kernel stops before them and they
     // run as a product of their own (the sub-matrices of the same operands), which the cost model splits along K.
@@ -1183,20 +1179,16 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     const bool plain_epi = (epi.mode == EPI_STORE || epi.mode == EPI_ACCUM || epi.mode == EPI_BIAS) && epi.split_m == 0;
     const bool tail_apart = plain_epi && tail_can_run_apart(ctx, grid.x, tiles_run, kb_total, bn);
     if (tail_apart) tiles_run -= tail;
-    static bool attr_set2 = false;
-    if (!attr_set2) {
+    if (!(ctx->func_attr_done & 4u)) {
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_persist<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PERSIST_BYTES));
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_persist<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PERSIST_BYTES));
-      attr_set2 = true;
+      ctx->func_attr_done |= 4u;
     }
     {
       GemmProfScope scope(ctx, flops * ((double)tiles_run / (grid.x * grid.y)), 1, M, N, kb_total * BK, (uint32_t)epi.mode);
       // grouped tile order when the A operand has many row blocks (unless the last round runs apart, which relies on the
-      // row-block-fastest order); DYB200_PERSIST_GROUP overrides the group height (0 = row block fastest)
-      static int group_env = -2;
-      if (group_env == -2) { const char* e = getenv("DYB200_PERSIST_GROUP"); group_env = e ? atoi(e) : -1; }
-      uint32_t gm = (!tail_apart && grid.x > 16) ? 16u : 0u;
-      if (group_env >= 0 && !tail_apart) gm = (uint32_t)group_env;
+      // row-block-fastest order)
+      const uint32_t gm = (!tail_apart && grid.x > 16) ? 16u : 0u;
       if (bn == 64) dyb_launch(k_gemm_persist<64>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, gm, epi, ctx->dev_flags);
       else dyb_launch(k_gemm_persist<128>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, gm, epi, ctx->dev_flags);
       DYB_LAUNCHED(ctx);

@@ -406,10 +406,20 @@ int dyb200_lookup_accumulate_grads_noalloc(unsigned n, const unsigned* ids_host,
       DYB_CHECK_ARG(ctx, ids_host[b] < vocab, "Out-of-bounds attempt to access index %u for LookupParameter of size %u", ids_host[b], vocab);
   DYB_CHECK_ARG(ctx, ctx->device >= 0 && ctx->device < kMaxDevices, "accumulate_grads_noalloc: device id %d not supported", ctx->device);
   if (n == 0 || dim_size == 0) return DYB200_OK;
+  // The array exists once per device and its address belongs to the device that is current when it is looked up; the
+  // kernels below run on the context's stream.  Both must be the same device, on every call: with another device current
+  // the launches would go there carrying a pointer into this device's copy.  The caller's current device is not changed.
+  int cur = -1;
+  DYB_CUDA(ctx, cudaGetDevice(&cur));
+  DYB_CHECK_ARG(ctx, cur == ctx->device, "accumulate_grads_noalloc: the current device is %d, the context belongs to device %d "
+                "(make it current with cudaSetDevice before the call)", cur, ctx->device);
   if (g_noalloc_addr[ctx->device] == nullptr) {   // first call on this device: one-time set-up
-    int cur = -1;
-    DYB_CUDA(ctx, cudaGetDevice(&cur));
-    if (cur != ctx->device) DYB_CUDA(ctx, cudaSetDevice(ctx->device));
+    // (looking the symbol up may initialise the module on this device, which is not allowed while a capture is open)
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    DYB_CUDA(ctx, cudaStreamIsCapturing(ctx->stream, &cap));
+    if (cap != cudaStreamCaptureStatusNone)
+      return dyb200_fail(ctx, DYB200_ERUNTIME, "accumulate_grads_noalloc: the first call on a device does a one-time set-up and "
+                                              "must come before any stream capture");
     void* addr = nullptr;
     DYB_CUDA(ctx, cudaGetSymbolAddress(&addr, g_noalloc_scratch));
     g_noalloc_addr[ctx->device] = addr;
@@ -435,10 +445,9 @@ int dyb200_lookup_fwd(DYB200_FWD_ARGS) {
   const bool al = aligned16(a->all_values) && aligned16(fx->v) && E % 4 == 0;
   if (al && E * 4u <= (uint32_t)kGatherRowBytesMax) {
     size_t smem = (size_t)kGatherWarps * 2 * E * 4;
-    static bool attr_set = false;
-    if (!attr_set) {
+    if (!(ctx->func_attr_done & 8u)) {   // (per device: remembered by the context)
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gather_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, kGatherWarps * 2 * kGatherRowBytesMax));
-      attr_set = true;
+      ctx->func_attr_done |= 8u;
     }
     unsigned grid = stream_grid(ctx, n, kGatherWarps, 3);
     dyb_launch(k_gather_bulk, grid, kGatherWarps * 32, smem, ctx, a->all_values, ids_dev, n, E, a->vocab, a->weight_decay_scale, fx->v, ctx->dev_flags);

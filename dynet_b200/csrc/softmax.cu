@@ -148,10 +148,13 @@ __global__ void __launch_bounds__(kBlock) k_col_block_vec(ColArgs a) {
 
 // ---- CTA per column, any length: streaming online (max, sum) -------------------
 // The running sum is kept in base 2 relative to the running max: s = sum 2^((x - m) * log2(e)).
+// A -inf entry contributes nothing (the reference subtracts the column maximum first, so it sees exp(-inf) = 0); while the
+// running maximum itself is still -inf the exponent would be inf - inf, so such entries are skipped / the shift is 0.
 __device__ __forceinline__ void online_add(float& m, float& s, float v) {
   if (v > m) { s = s * ex2_approx((m - v) * kLog2e) + 1.f; m = v; }
-  else s += ex2_approx((v - m) * kLog2e);
+  else if (v != -INFINITY) s += ex2_approx((v - m) * kLog2e);
 }
+__device__ __forceinline__ float shift_log2(float m) { return m == -INFINITY ? 0.f : m * kLog2e; }
 __device__ __forceinline__ float max4(float4 v) { return fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)); }
 __device__ __forceinline__ float sumexp4(float4 v, float ml) {
   return (ex2_approx(fmaf(v.x, kLog2e, -ml)) + ex2_approx(fmaf(v.y, kLog2e, -ml))) +
@@ -176,14 +179,14 @@ __global__ void __launch_bounds__(kBlock) k_col_stream(ColArgs a) {
       float4 v2 = ld4_stream(xb + 4 * (i + 2 * kBlock)), v3 = ld4_stream(xb + 4 * (i + 3 * kBlock));
       float vm = fmaxf(fmaxf(max4(v0), max4(v1)), fmaxf(max4(v2), max4(v3)));
       if (vm > m) { s *= ex2_approx((m - vm) * kLog2e); m = vm; }
-      const float ml = m * kLog2e;
+      const float ml = shift_log2(m);
       s += (sumexp4(v0, ml) + sumexp4(v1, ml)) + (sumexp4(v2, ml) + sumexp4(v3, ml));
     }
     for (; i < body4; i += kBlock) {
       float4 v = ld4_stream(xb + 4 * i);
       float vm = max4(v);
       if (vm > m) { s *= ex2_approx((m - vm) * kLog2e); m = vm; }
-      s += sumexp4(v, m * kLog2e);
+      s += sumexp4(v, shift_log2(m));
     }
     uint32_t t = head + 4 * body4 + threadIdx.x;
     if (t < a.rows) online_add(m, s, xc[t]);

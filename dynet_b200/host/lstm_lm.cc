@@ -78,6 +78,7 @@ struct Lm {
   // CUDA-graph replay of the whole forward + backward pass (optional): the ~1400 launches of a step are
   // captured once and re-issued with one cudaGraphLaunch; inputs live at fixed addresses (tok, mask_buf).
   bool use_graph = false;
+  bool time_major = false;               // fused driver: time step by time step (the reference's order) instead of layer by layer
   cudaGraphExec_t graph_exec = nullptr;
   float* graph_loss = nullptr;
   uint64_t graph_launches = 0;
@@ -187,9 +188,9 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   // graph.  The fused driver finishes a layer over all time steps before it starts the next one (layer l at step t needs
   // layer l - 1 at step t and layer l at step t - 1, which both orders provide): the split weight planes of one layer
   // (50 and 67 MB) then stay in the 126 MB L2 from step to step instead of alternating with the other layer's, which
-  // matters when the per-GPU batch is small and the products are bound by weight traffic.  Same values either way.
-  static const bool time_major_env = getenv("DYB200_LM_TIME_MAJOR") != nullptr;
-  const bool layer_major = c.fused && !time_major_env;
+  // matters when the per-GPU batch is small and the products are bound by weight traffic.  Same values either way
+  // (dyb200h_lm_set_time_major restores the reference's order).
+  const bool layer_major = c.fused && !m.time_major;
   for (uint32_t pass = 0; pass < (layer_major ? L : 1u); ++pass)
   for (uint32_t t = 0; t < T; ++t) {
     if (layer_major && t == 0) {
@@ -358,6 +359,10 @@ void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float*
   if (!m.graph_exec) {
     if (st == nullptr) throw std::runtime_error("graph mode needs a non-default stream (the legacy stream cannot be captured)");
     uint64_t l0 = dyb200_ctx_launch_count(m.dev.ctx);
+    // The launches that split the weights into operand planes are issued only when the parameter cache is stale, a
+    // decision taken on the host while capturing.  Marking the cache stale here puts them into every graph, whatever
+    // happened before the capture, so a replay after an update never multiplies with the planes of old weights.
+    dyb200_ctx_params_changed(m.dev.ctx);
     CU(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
     cudaGraph_t graph = nullptr;
     try {
@@ -411,11 +416,8 @@ int dyb200h_lm_create(const dyb200h_lm_config* c, float* params, float* grads, v
   // copies of the weights can be reused across the time steps of a training step
   dyb200_ctx_param_cache(ctx, 1);
   // Programmatic dependent launch measured no gain for this step (the graph replay already chains the kernels
-  // tightly: 5.95 vs 6.00 ms at batch 64, 19.9 vs 20.1 ms at batch 512), so it stays off unless DYB200_PDL=1 asks for it.
-  {
-    const char* e = getenv("DYB200_PDL");
-    dyb200_ctx_dependent_launch(ctx, (e && atoi(e) == 1) ? 1 : 0);
-  }
+  // tightly: 5.95 vs 6.00 ms at batch 64, 19.9 vs 20.1 ms at batch 512), so this driver leaves it as the caller set it
+  // on the context (dyb200_ctx_dependent_launch; off by default).
   int rc = DYB200_OK;
   if (c->fused) {
     for (uint32_t l = 0; l < c->L && !rc; ++l) {
@@ -489,6 +491,14 @@ int dyb200h_lm_set_graph(void* h, int enable) {
   return DYB200_OK;
 }
 uint64_t dyb200h_lm_graph_launches(void* h) { return ((Lm*)h)->graph_launches; }
+// Fused driver only: 1 = run the (time step, layer) calls time step by time step, as the reference's graph orders them;
+// 0 (default) = layer by layer.  Same values either way; drops a captured graph.
+int dyb200h_lm_set_time_major(void* h, int enable) {
+  Lm* m = (Lm*)h;
+  m->time_major = enable != 0;
+  if (m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
+  return DYB200_OK;
+}
 // Device pointers of the 2L mask buffers the graph reads (write the masks there to avoid the staging copy).
 int dyb200h_lm_mask_buffers(void* h, float** out, int cap) {
   Lm* m = (Lm*)h;

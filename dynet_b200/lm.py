@@ -48,6 +48,8 @@ def host_lib():
         L.dyb200h_lm_update.argtypes = [C.c_void_p]
         L.dyb200h_lm_set_graph.restype = C.c_int
         L.dyb200h_lm_set_graph.argtypes = [C.c_void_p, C.c_int]
+        L.dyb200h_lm_set_time_major.restype = C.c_int
+        L.dyb200h_lm_set_time_major.argtypes = [C.c_void_p, C.c_int]
         L.dyb200h_lm_graph_launches.restype = C.c_uint64
         L.dyb200h_lm_graph_launches.argtypes = [C.c_void_p]
         L.dyb200h_lm_mask_buffers.restype = C.c_int
@@ -178,6 +180,10 @@ class LstmLm:
     def set_graph(self, enable):
         """Replay forward + backward as one CUDA graph (needs a non-default stream and one eager step before)."""
         self._check(self.H.dyb200h_lm_set_graph(self.h, int(enable)))
+
+    def set_time_major(self, enable):
+        """Fused driver: run the (time step, layer) calls time step by time step (the reference's order) instead of layer by layer."""
+        self._check(self.H.dyb200h_lm_set_time_major(self.h, int(enable)))
 
     def graph_launches(self):
         return int(self.H.dyb200h_lm_graph_launches(self.h))

@@ -73,6 +73,10 @@ uint64_t dyb200_ctx_launch_count(const dyb200_ctx* ctx);
  * device time in ms, the launch count and the useful FLOPs (2*M*N*K per product). */
 int dyb200_ctx_profile_begin(dyb200_ctx* ctx, int capacity);
 int dyb200_ctx_profile_end(dyb200_ctx* ctx, double ms_out[2], uint64_t launches_out[2], double flops_out[2]);
+/* Between begin and end: the number of GEMM launches recorded so far, and launch k of them: shape = {M, N, sum of K,
+ * epilogue mode}, path = 1 for the tensor-pipe kernels, its device time (waits for that launch) and its useful FLOPs. */
+int dyb200_ctx_profile_count(const dyb200_ctx* ctx);
+int dyb200_ctx_profile_launch(dyb200_ctx* ctx, int k, uint32_t shape_out[4], int* path_out, float* ms_out, double* flops_out);
 /* Parameter cache for the tensor-pipe GEMM (off by default).  The GEMM splits every operand into
  * TF32 hi/lo planes first; with the cache on, the planes of a PARAMETER matrix (the LSTM's Wx / Wh, or
  * the A operand of dyb200_gemm called with DYB200_GEMM_A_IS_PARAM) are kept and reused until the
@@ -86,7 +90,7 @@ int dyb200_ctx_param_cache(dyb200_ctx* ctx, int enable);
  * code puts into the same stream between two calls is ordered as usual. */
 int dyb200_ctx_dependent_launch(dyb200_ctx* ctx, int enable);
 /* K splits of a tensor-pipe product as one thread-block cluster per output tile, reduced through distributed shared memory
- * (on by default; the environment variable DYB200_CLUSTER_SPLITK=0 changes the default of new contexts).  Off: the splits
+ * (on by default).  Off: the splits
  * go through a workspace and a second kernel.  Results are bitwise the same either way. */
 int dyb200_ctx_cluster_splitk(dyb200_ctx* ctx, int enable);
 int dyb200_ctx_params_changed(dyb200_ctx* ctx);
@@ -196,13 +200,19 @@ int dyb200_lookup_accumulate_grads(unsigned n, const unsigned* ids_host, const u
 /* Allocation-free variant of dyb200_lookup_accumulate_grads (no counterpart in the reference).
  * For hosts that must not allocate device memory while training -- e.g. a DyNet-style process whose
  * device memory is a few pools reserved at start-up, or any caller inside a region where cudaMalloc
- * is forbidden.  Same arguments and same result as dyb200_lookup_accumulate_grads, but the sort /
- * segment tables live in a fixed array inside the library image instead of the context's growable
- * arena, and the call performs no cudaMalloc / cudaFree and calls no allocating routine.
+ * is forbidden.  Same arguments as dyb200_lookup_accumulate_grads, but the sort / segment tables live
+ * in a fixed array inside the library image instead of the context's growable arena, and the call
+ * performs no cudaMalloc / cudaFree and calls no allocating routine.
+ *  - Result: every table row receives its gradient rows one after the other in ascending position,
+ *    i.e. bit for bit what the sequential CPU loop of the reference gives.  dyb200_lookup_accumulate_grads
+ *    adds an id's rows in chunks of 32 positions, so for an id that occurs more than 32 times the two
+ *    entry points may differ by rounding.
  *  - Limit: n <= DYB200_NOALLOC_MAX_IDS ids per call; a larger n returns DYB200_EINVAL.
  *  - Cost: every GPU that loads the library keeps 49,408 bytes for that array until exit.
- *  - The first call on a device looks up the array's device address (a one-time set-up with that
- *    device made current); make that first call before starting any stream capture.
+ *  - The context's device must be the current device of the calling thread (DYB200_EINVAL otherwise;
+ *    the call never switches devices).
+ *  - The first call on a device looks up the array's device address (a one-time set-up); make that
+ *    first call before starting any stream capture: during a capture it returns DYB200_ERUNTIME.
  *  - All calls on a device share the array: two calls that can overlap on the GPU (different
  *    streams, contexts or host threads) race on it.  Calls on one stream are safe, and each call
  *    rewrites everything it reads, so nothing carries over between calls. */

@@ -1,6 +1,6 @@
 """Per-kernel timing of the memory-bound nodes at the sizes of BASELINE configs 2 and 3.
 
-    python -m dynet_b200.kernel_bench [--only NAME] [--iters 20] [--small]
+    python kernel_bench.py [--only NAME] [--iters 20] [--small]
 
 Each case is called through the C ABI `iters` times on ROTATING buffer sets whose total footprint
 exceeds the 126 MB L2 (so every call reads its inputs from HBM).  The calls are captured once into a
@@ -15,11 +15,16 @@ import ctypes as C
 import json
 import os
 
+import sys
+
 import numpy as np
 
-from . import capi
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+from dynet_b200 import capi  # noqa: E402
+
 L2_BYTES = 126 * 1024 * 1024
 
 

@@ -389,6 +389,30 @@ def matmul_bwd(a, b, dEdf, i, dxi):
     return affine_bwd([None, a, b], dEdf, i + 1, dxi)
 
 
+def vanilla_lstm_builder_step(x, h_tm1, c_tm1, Wx, Wh, b, forget_bias=1.0):
+    """One time step of one layer of VanillaLSTMBuilder::add_input_impl (dynet/lstm.cc:477-546; no dropout, no layer norm):
+    the NON-fused graph  tmp = affine_transform({b, Wx, x, Wh, h_tm1});  four pick_range slices;  logistic / tanh;
+    c = cmult(f, c_tm1) + cmult(i, g);  h = cmult(o, tanh(c)),  every node evaluated by its own oracle.
+    x: (B, I), h_tm1 / c_tm1: (B, H) or None (no previous state), Wx: (I, 4H), Wh: (H, 4H), b: (4H,) -- C-order arrays of the
+    column-major tensors.  Returns (h, c, nodes) with `nodes` the intermediate values by name."""
+    B, I = x.shape
+    H = Wx.shape[1] // 4
+    xs = [b.reshape(1, 1, 4 * H), Wx.reshape(1, I, 4 * H), np.ascontiguousarray(x.reshape(B, 1, I))]
+    if h_tm1 is not None:
+        xs += [Wh.reshape(1, H, 4 * H), np.ascontiguousarray(h_tm1.reshape(B, 1, H))]
+    tmp = affine_fwd(xs).reshape(B, 4 * H)
+    a_i, a_f, a_o, a_g = (pick_range_fwd(tmp, k * H, (k + 1) * H, 0) for k in range(4))
+    i_t = unary_fwd("logistic", a_i)
+    f_t = unary_fwd("logistic", (a_f + np.float32(forget_bias)).astype(np.float32) if forget_bias != 0.0 else a_f)
+    o_t = unary_fwd("logistic", a_o)
+    g_t = unary_fwd("tanh", a_g)
+    ig = cwise_fwd("cmult", i_t, g_t)
+    c_t = sum_fwd([cwise_fwd("cmult", f_t, c_tm1), ig]) if h_tm1 is not None else ig
+    tc = unary_fwd("tanh", c_t)
+    h_t = cwise_fwd("cmult", o_t, tc)
+    return h_t, c_t, dict(tmp=tmp, i=i_t, f=f_t, o=o_t, g=g_t, tanh_c=tc)
+
+
 # ---------------- LSTM language model step ----------------
 class LmDims(C.Structure):
     _fields_ = [(k, C.c_uint32) for k in ("V", "E", "H", "L", "T", "B")]

@@ -18,3 +18,16 @@ def oracle():
     orc.build()
     orc.lib()
     return orc
+
+
+def pytest_terminal_summary(terminalreporter):
+    """One line per test with the worst error it measured relative to its bar (see util.assert_close)."""
+    try:
+        import util
+    except ImportError:
+        return
+    if not util.RECORDS:
+        return
+    terminalreporter.write_line("measured parity margins (worst |err| / bound per test; 1.0 = at the bar):")
+    for test, (ratio, err, what) in sorted(util.RECORDS.items()):
+        terminalreporter.write_line("  %-100s %8.3g  (|err| %.3g, %s)" % (test, ratio, err, what))

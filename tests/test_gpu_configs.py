@@ -10,7 +10,9 @@ import ctypes as C
 import numpy as np
 import pytest
 
-from util import TOL_REDUCE, assert_close, glorot, randn, rng, zipf_ids
+from util import TOL_REDUCE, assert_close, glorot, randn, rng, row_floor, zipf_ids
+
+GEMM_FLOOR = 0.1   # states are O(1) sums of hundreds of products: see tests/test_gpu_parity.py
 
 pytestmark = pytest.mark.gpu
 
@@ -32,6 +34,61 @@ def _release(g):
 def capi():
     from dynet_b200 import capi as c
     return c
+
+
+def test_config1_builder_graph_pins_the_fused_chain(oracle, g, capi):
+    """Config 1 the way the reference's CPU build runs it: VanillaLSTMBuilder's non-fused graph (dynet/lstm.cc:477-546:
+    affine_transform -> 4 x pick_range -> logistic / tanh -> cmult / +) evaluated by the CPU oracle is the target.  On the
+    device both forms run through the C ABI: the same node sequence (AffineTransform, PickRange, ConstantPlusX,
+    LogisticSigmoid, Tanh, CwiseMultiply, Sum) and the fused chain (VanillaLSTMGates -> C -> H).  Both must give the
+    builder graph's h_t and c_t; the bar between the two builders is the reference's own (tests/test-rnn.cc:155-184)."""
+    r = rng(4321)
+    I, H, B, T = 128, 256, 32, 8
+    Wx, Wh, b = glorot(r, 4 * H, I), glorot(r, 4 * H, H), np.zeros(4 * H, np.float32)
+    xs = [randn(r, B, I) for _ in range(T)]
+    ctx = g.ctx()
+    Wx_, Wh_, b_ = g.dev(Wx), g.dev(Wh), g.dev(b)
+    tW = [g.T(Wx_, [4 * H, I], 1), g.T(Wh_, [4 * H, H], 1), g.T(b_, [4 * H], 1)]
+    at = capi.LstmGatesAttrs(0, 0.0, 1.0)
+    zeros = lambda n: g.dev(np.zeros((B, n), np.float32))
+    h_ref, c_ref = np.zeros((B, H), np.float32), np.zeros((B, H), np.float32)
+    hu, cu = zeros(H), zeros(H)          # device, non-fused node sequence
+    hf, cf = zeros(H), zeros(H)          # device, fused chain
+    for t in range(T):
+        h_ref, c_ref, _ = oracle.vanilla_lstm_builder_step(xs[t], h_ref, c_ref, Wx, Wh, b)
+        x_ = g.dev(xs[t])
+        # non-fused graph on the device
+        tmp = zeros(4 * H)
+        ctx.fwd("affine_transform", [tW[2], tW[0], g.T(x_), tW[1], g.T(hu)], g.T(tmp))
+        parts = []
+        for k in range(4):
+            pk = zeros(H)
+            ctx.fwd("pick_range", [g.T(tmp)], g.T(pk), capi.PickRangeAttrs(k * H, (k + 1) * H, 0))
+            parts.append(pk)
+        af = zeros(H)
+        ctx.fwd("constant_plus_x", [g.T(parts[1])], g.T(af), capi.ConstAttrs(1.0))
+        it, ft, ot, gt = zeros(H), zeros(H), zeros(H), zeros(H)
+        ctx.fwd("logistic", [g.T(parts[0])], g.T(it))
+        ctx.fwd("logistic", [g.T(af)], g.T(ft))
+        ctx.fwd("logistic", [g.T(parts[2])], g.T(ot))
+        ctx.fwd("tanh", [g.T(parts[3])], g.T(gt))
+        fc, ig, cn, tc, hn = zeros(H), zeros(H), zeros(H), zeros(H), zeros(H)
+        ctx.fwd("cmult", [g.T(ft), g.T(cu)], g.T(fc))
+        ctx.fwd("cmult", [g.T(it), g.T(gt)], g.T(ig))
+        ctx.fwd("sum", [g.T(fc), g.T(ig)], g.T(cn))
+        ctx.fwd("tanh", [g.T(cn)], g.T(tc))
+        ctx.fwd("cmult", [g.T(ot), g.T(tc)], g.T(hn))
+        hu, cu = hn, cn
+        # fused chain on the device
+        gates, cn2, hn2 = zeros(4 * H), zeros(H), zeros(H)
+        ctx.fwd("vanilla_lstm_gates", [g.T(x_), g.T(hf)] + tW, g.T(gates), at)
+        ctx.fwd("vanilla_lstm_c", [g.T(cf), g.T(gates)], g.T(cn2))
+        ctx.fwd("vanilla_lstm_h", [g.T(cn2), g.T(gates)], g.T(hn2))
+        hf, cf = hn2, cn2
+        for name, got in (("non-fused graph", (hu, cu)), ("fused chain", (hf, cf))):
+            assert_close(g.host(got[0]), h_ref, 1e-5, floor=GEMM_FLOOR, what="h_%d, %s vs builder-graph oracle" % (t, name))
+            assert_close(g.host(got[1]), c_ref, 1e-5, floor=GEMM_FLOOR, what="c_%d, %s vs builder-graph oracle" % (t, name))
+    assert ctx.device_errors() == 0
 
 
 def test_config1_single_layer_lstm_fwd_bwd(oracle, g, capi):
@@ -95,9 +152,11 @@ def test_config1_single_layer_lstm_fwd_bwd(oracle, g, capi):
         for i, tgt in enumerate((g.T(dx_[t - 1]), g.T(dh_[t - 1]), tgW[0], tgW[1], tgW[2])):
             ctx.bwd("vanilla_lstm_gates", xs_t, g.T(g_[t - 1]), g.T(dg), i, tgt, at)
     for name, got, want in (("dWx", gW[0], dWx), ("dWh", gW[1], dWh), ("db", gW[2], db)):
-        assert_close(g.host(got), want, TOL_REDUCE, floor=float(np.abs(want).max()) * 0.05, what=name)
+        # per gate row: every row of dWx / dWh is held to its own magnitude (the bias gradient to 1 % of its largest entry)
+        floor = row_floor(want, 0, rel=1e-3) if want.ndim == 2 else float(np.abs(want).max()) * 0.01
+        assert_close(g.host(got), want, TOL_REDUCE, floor=floor, what=name + " (per-row scale)")
     for t in (0, 1, 25, 49):
-        assert_close(g.host(dx_[t]), dxs[t], TOL_REDUCE, floor=float(np.abs(dxs[t]).max()) * 0.05, what="dx_%d" % t)
+        assert_close(g.host(dx_[t]), dxs[t], TOL_REDUCE, floor=row_floor(dxs[t], 1, rel=1e-3), what="dx_%d (per-column scale)" % t)
     assert ctx.device_errors() == 0
 
 

@@ -233,6 +233,58 @@ def test_pickneglogsoftmax(oracle, g, capi, rows, bd):
     assert g.ctx().device_errors() == 0
 
 
+@pytest.mark.parametrize("rows", [45, 301, 4096, 4099, 10000])
+def test_softmax_family_with_minus_infinity_entries(oracle, g, capi, rows):
+    """Logits of -inf (RestrictedLogSoftmax writes them, dynet/nodes-softmaxes.cc:261) carry no probability mass: the
+    reference subtracts the column maximum first, so exp(-inf - max) = 0.  Covers the warp, register and streaming
+    kernels (rows > 4096, rows % 4 != 0), including a thread whose whole share of a column is -inf."""
+    r = rng(126 + rows)
+    bd = 3
+    x = randn(r, bd, rows, scale=2.0)
+    x[0, r.random(rows) < 0.3] = -np.inf
+    x[1, : rows - 2] = -np.inf                     # only two finite entries, at the end of the column
+    x[2, 5:] = -np.inf                             # only five finite entries, at the start
+    ids = np.array([int(np.flatnonzero(np.isfinite(x[b]))[0]) for b in range(bd)], np.uint32)
+    x_ = g.dev(x)
+    fin = np.isfinite(x)
+    # softmax
+    y_ref = oracle.softmax_fwd(x.reshape(bd, 1, rows), 0).reshape(bd, rows)
+    y_ = g.dev(np.zeros_like(x))
+    g.ctx().fwd("softmax", [g.T(x_, [rows], bd)], g.T(y_, [rows], bd), capi.DimAttrs(0))
+    got = g.host(y_)
+    assert np.all(got[~fin] == 0.0)
+    assert_close(got, y_ref, TOL_REDUCE, floor=1e-6, what="softmax with -inf")
+    # log_softmax
+    ly_ref = oracle.log_softmax_fwd(x.reshape(bd, 1, rows)).reshape(bd, rows)
+    ly_ = g.dev(np.zeros_like(x))
+    aux = g.dev(np.zeros(2 * bd, np.float32))
+    g.ctx().fwd("log_softmax", [g.T(x_, [rows], bd)], g.T(ly_, [rows], bd), None, aux.data_ptr())
+    got = g.host(ly_)
+    assert np.all(got[~fin] == -np.inf) and np.all(ly_ref[~fin] == -np.inf)
+    assert_close(got[fin], ly_ref[fin], TOL_REDUCE, what="log_softmax with -inf")
+    # logsumexp along dim 0
+    z_ref, _ = oracle.logsumexp_dim_fwd(x.reshape(bd, 1, rows), 0)
+    z_ = g.dev(np.zeros_like(z_ref))
+    g.ctx().fwd("logsumexp_dim", [g.T(x_, [rows, 1], bd)], g.T(z_, [1], bd), capi.DimAttrs(0))
+    assert_close(g.host(z_).ravel(), z_ref.ravel(), TOL_REDUCE, what="logsumexp with -inf")
+    # PickNegLogSoftmax forward and backward (picked entries are finite)
+    loss_ref, zr = oracle.pnls_fwd(x, ids)
+    loss_ = g.dev(np.zeros(bd, np.float32))
+    aux = g.dev(np.zeros(3 * bd, np.float32))
+    ids_np, ids_p = g.u32(ids)
+    at = capi.PickAttrs(ids_p, bd)
+    g.ctx().fwd("pickneglogsoftmax", [g.T(x_, [rows], bd)], g.T(loss_, [1], bd), at, aux.data_ptr())
+    assert_close(g.host(loss_), loss_ref, TOL_REDUCE, what="pnls fwd with -inf")
+    dE, d0 = randn(r, bd), randn(r, bd, rows)
+    want = oracle.pnls_bwd(x, ids, zr, dE, d0.copy())
+    d_ = g.dev(d0)
+    g.ctx().bwd("pickneglogsoftmax", [g.T(x_, [rows], bd)], g.T(loss_, [1], bd), g.T(g.dev(dE), [1], bd), 0,
+                g.T(d_, [rows], bd), at, aux.data_ptr())
+    assert np.array_equal(g.host(d_)[~fin], d0[~fin])        # no gradient reaches a -inf logit
+    assert_close(g.host(d_), want, TOL_REDUCE, floor=ACC_FLOOR, what="pnls bwd with -inf")
+    assert g.ctx().device_errors() == 0
+
+
 @pytest.mark.parametrize("V,H,n", [(1000, 256, 192), (1001, 250, 67), (2100, 128, 1300), (40, 16, 8)])
 def test_softmax_output_bwd_fused(oracle, g, capi, V, H, n):
     """dyb200_softmax_output_bwd_fused == PickNegLogSoftmax backward into a zeroed d(x), then AffineTransform backward

@@ -292,6 +292,30 @@ def test_fused_chain_equals_unfused_builder_math(oracle):
         assert_close(c, c2, 1e-5, floor=1e-2, what="c_%d" % t)
 
 
+def test_builder_graph_oracle_equals_fused_chain_oracle(oracle):
+    """The restatement of VanillaLSTMBuilder's non-fused graph (dynet/lstm.cc:477-546), node oracle by node oracle,
+    against the fused-node chain, at the reference test's bar (tests/test-rnn.cc:155-184: 1e-5 relative) and at the
+    sizes of the single-layer benchmark configuration."""
+    for (I, H, B, T) in [(3, 5, 1, 3), (128, 256, 32, 6)]:
+        r = rng(17 + I)
+        a = np.sqrt(6.0 / (4 * H + I))
+        Wx = r.uniform(-a, a, (I, 4 * H)).astype(np.float32)
+        a = np.sqrt(6.0 / (4 * H + H))
+        Wh = r.uniform(-a, a, (H, 4 * H)).astype(np.float32)
+        b = np.zeros(4 * H, np.float32)
+        h = np.zeros((B, H), np.float32); c = np.zeros((B, H), np.float32)
+        hb, cb = h.copy(), c.copy()
+        for t in range(T):
+            x = randn(r, B, I)
+            g = oracle.lstm_gates_fwd([x], h, Wx, Wh, b)
+            c = oracle.lstm_c_fwd(c, g)
+            h = oracle.lstm_h_fwd(c, g)
+            hb, cb, _ = oracle.vanilla_lstm_builder_step(x, hb, cb, Wx, Wh, b)
+            # (states are O(1) sums of O(1) products: one float32 ulp of those, ~1e-7, is the floor of any agreement)
+            assert_close(h, hb, 1e-5, floor=0.1, what="h_%d builder graph vs fused chain" % t)
+            assert_close(c, cb, 1e-5, floor=0.1, what="c_%d builder graph vs fused chain" % t)
+
+
 # ---------------------------------------------------------------- MatrixMultiply / AffineTransform
 def _np_affine(xs):
     """float64 numpy statement of bias + sum A_k B_k with DyNet's batch rules (arrays are (bd, cols, rows))."""

@@ -7,8 +7,12 @@ give what `dyb200_lookup_accumulate_grads` gives: here both are called through t
 inputs, twice in a row (the second call reuses the array the first one left behind), and the size
 limit is checked.  Both add the rows of one id in ascending position; the regular entry point sums a
 very frequent id chunk-wise, so the two agree to rounding (the 1e-4 class of the other gradient
-tests) and bit for bit on ids that occur once.  This file sorts last so a run that stops at the first failure has already
-covered everything else."""
+tests) and bit for bit on ids that occur once.  The allocation-free entry point adds strictly one row
+after the other, so it is also compared bit for bit with the CPU oracle's sequential loop, for every id.
+This file sorts last so a run that stops at the first failure has already covered everything else."""
+import subprocess
+import sys
+import os
 import numpy as np
 import pytest
 
@@ -61,6 +65,77 @@ def test_noalloc_scatter_add_matches_regular_entry_point():
     assert torch.cuda.mem_get_info()[0] == free_before
     _same(acc.cpu().numpy(), want, ids, "third call")
     assert ctx.device_errors() == 0
+    ctx.close()
+
+
+@pytest.mark.parametrize("E,V,n", [(512, 5000, 4096), (30, 211, 4096), (64, 300, 777), (7, 5, 33)])
+def test_noalloc_scatter_add_is_the_sequential_cpu_sum(oracle, E, V, n):
+    """All ids, repeated ones included, bit for bit against the reference's CPU loop (dynet/model.cc:735-741);
+    E = 30 and E = 7 take the scalar path (rows that are not whole 16-byte vectors), n = 4096 fills the array."""
+    from dynet_b200 import capi
+    ctx = capi.Context(0)
+    r = rng(901 + E)
+    ids = zipf_ids(r, n, V)
+    grad = randn(r, n, E)
+    acc0 = randn(r, V, E)
+    want = oracle.lookup_accumulate_grads(acc0.copy(), ids, grad)
+    for call in range(2):
+        got = _run(ctx, ctx.lookup_accumulate_grads_noalloc, ids, grad, acc0)
+        assert np.array_equal(got, want), "call %d: %d elements differ" % (call, int((got != want).sum()))
+    assert ctx.device_errors() == 0
+    ctx.close()
+
+
+_CAPTURE_PROBE = r"""
+import numpy as np, torch
+from dynet_b200 import capi
+s = torch.cuda.Stream()
+ctx = capi.Context(0, s.cuda_stream)
+ids = np.arange(8, dtype=np.uint32)
+ids_dev = torch.from_numpy(ids.view(np.int32)).cuda()
+g = torch.ones(8, 4, device="cuda"); acc = torch.zeros(8, 4, device="cuda")
+torch.cuda.synchronize()
+graph = torch.cuda.CUDAGraph()
+err = None
+with torch.cuda.graph(graph, stream=s):
+    try:
+        ctx.lookup_accumulate_grads_noalloc(ids, ids_dev.data_ptr(), g.data_ptr(), acc.data_ptr(), 4, 8)
+    except capi.RuntimeErr as e:
+        err = str(e)
+assert err and "before any stream capture" in err, err
+# outside a capture the same call works, and the gradient rows arrive
+ctx.lookup_accumulate_grads_noalloc(ids, ids_dev.data_ptr(), g.data_ptr(), acc.data_ptr(), 4, 8)
+torch.cuda.synchronize()
+assert float(acc.sum()) == 32.0
+print("ok")
+"""
+
+
+def test_noalloc_first_call_inside_a_capture_is_refused():
+    """The one-time set-up of the first call on a device must not happen while a stream capture is open: the entry
+    point says so with a status instead of breaking the capture.  Runs in a fresh process, where no earlier test has
+    done the set-up."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-c", _CAPTURE_PROBE], cwd=root, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and "ok" in p.stdout, p.stdout + p.stderr
+
+
+def test_noalloc_needs_the_contexts_device_current():
+    import torch
+    from dynet_b200 import capi
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = capi.Context(0)
+    ids = np.zeros(4, np.uint32)
+    ids_dev = torch.zeros(4, dtype=torch.int32, device="cuda:0")
+    g = torch.zeros(4, 4, device="cuda:0")
+    acc = torch.zeros(8, 4, device="cuda:0")
+    torch.cuda.set_device(1)
+    try:
+        with pytest.raises(capi.InvalidArgument, match="current device"):
+            ctx.lookup_accumulate_grads_noalloc(ids, ids_dev.data_ptr(), g.data_ptr(), acc.data_ptr(), 4, 8)
+    finally:
+        torch.cuda.set_device(0)
     ctx.close()
 
 
