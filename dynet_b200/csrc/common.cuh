@@ -39,6 +39,10 @@ struct dyb200_ctx {
   // (bit per kernel family) and how many thread-block clusters of each size fit on the GPU at once
   uint32_t func_attr_done;
   int max_clusters[2][9];
+  // sequence-persistent LSTM kernels (one launch per layer instead of one per time step): on by default
+  int seq_kernels;
+  int seq_max_clusters[2][9];   // thread-block clusters of each size that fit at once, per tile width (0 = not asked yet)
+  int seq_coop;                 // 0 = not tried, 1 = launched with the cooperative attribute, -1 = the driver refused it
   uint64_t param_version, param_tick;
   struct ParamPack {
     const float* src; const float* src2; uint32_t ld, rows, rows2, K, pitch; int k_is_fast;   // src2 / rows2: a second matrix stacked below the first
@@ -70,6 +74,7 @@ struct GemmProfScope {
 };
 
 #define DYB200_DEV_WORDS 2048
+#define DYB200_DEV_SEQ0 16      // 32 words: hand-over counters of the sequence kernels (zeroed before each launch)
 #define DYB200_DEV_COUNTER0 64
 #define DYB200_DEV_COUNTERS (DYB200_DEV_WORDS - DYB200_DEV_COUNTER0)
 // Device error bits written into ctx->dev_flags.

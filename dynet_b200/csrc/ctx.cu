@@ -83,6 +83,7 @@ int dyb200_ctx_create(int device, void* stream, dyb200_ctx** out) {
   c->stream = (cudaStream_t)stream;
   c->sm_count = prop.multiProcessorCount;
   c->cluster_splitk = 1;
+  c->seq_kernels = 1;
   if (cudaMalloc((void**)&c->dev_flags, DYB200_DEV_WORDS * 4) != cudaSuccess || cudaMemset(c->dev_flags, 0, DYB200_DEV_WORDS * 4) != cudaSuccess) {
     free(c);
     return DYB200_ENOMEM;
@@ -112,6 +113,12 @@ int dyb200_ctx_dependent_launch(dyb200_ctx* ctx, int enable) {
 int dyb200_ctx_cluster_splitk(dyb200_ctx* ctx, int enable) {
   if (!ctx) return DYB200_EINVAL;
   ctx->cluster_splitk = enable ? 1 : 0;
+  return DYB200_OK;
+}
+
+int dyb200_ctx_sequence_kernels(dyb200_ctx* ctx, int enable) {
+  if (!ctx) return DYB200_EINVAL;
+  ctx->seq_kernels = enable ? 1 : 0;
   return DYB200_OK;
 }
 

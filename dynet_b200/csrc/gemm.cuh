@@ -137,3 +137,16 @@ uint32_t dyb200_wgrad_fill(const dyb200_wgrad* w);
 int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda, const float* b0, uint32_t ldb0,
                               const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1,
                               int mask1_full, dyb200_ctx* ctx, PackJobs* batch);
+
+// ---- sequence kernels (lstm_seq.cu) ----
+// Operand planes of a whole sequence held by an accumulator after dyb200_wgrad_pack_inputs: X = x .* mask_x (row = column
+// of the sequence, K = I), Hs = h_tm1 .* mask_h (row = column, K = H; rows [c, c + step) are the input of the step that
+// starts at column c), B1 = the transposed h planes of the weight-gradient product.  False when they are not in place for
+// `steps` steps of `step` columns.
+struct SeqPlanes { PackedOp X, Hs, B1; };
+bool dyb200_wgrad_seq_planes(const dyb200_wgrad* w, uint32_t steps, uint32_t step, SeqPlanes* out);
+int dyb200_wgrad_seq_h0(dyb200_wgrad* w, const float* h0, const float* mh, int mh_full, dyb200_ctx* ctx, PackJobs* batch);
+void dyb200_wgrad_seq_done(dyb200_wgrad* w);
+// A 2-D tensor map (CUtensorMap, 128 bytes at `map`) over a K-major plane: box = 32 floats of K x box_rows rows, 128-byte swizzle.
+int dyb200_tc_make_tmap(dyb200_ctx* ctx, void* map, float* plane, uint32_t rows, uint32_t K, uint32_t pitch, uint32_t box_rows);
+uint32_t dyb200_tc_tile_cols(uint32_t N);   // width of the output tile the tensor path uses for N columns (64 or 128)

@@ -1,0 +1,481 @@
+// One LSTM layer over ALL time steps of a sequence in one kernel (forward): the call pattern of
+// CompactVanillaLSTMBuilder::add_input_impl (dynet/lstm.cc:1044-1080) driven through RNNBuilder::add_input
+// (dynet/rnn.h:120) for a batch of equally long sequences, i.e. T times
+//     gates_t = VanillaLSTMGates(x_t, h_{t-1}, Wx, Wh, b [, masks]);  c_t = VanillaLSTMC(c_{t-1}, gates_t);
+//     h_t = VanillaLSTMH(c_t, gates_t).
+// The per-step form (dyb200_vanilla_lstm_fwd_fused_at) launches one 3xTF32 product per step.  Here the CTAs of that
+// product stay resident for the whole sequence: CTA (mt, nt[, split]) owns the same 128 interleaved gate rows (32 hidden
+// units) x BNT batch columns in every step.  What that buys per step: no launch gap, no TMEM allocation / barrier set-up /
+// tensor-map fetch, and the Wx x_{t+1} share of a step's k-blocks (which does not depend on h_t) runs while the epilogue of
+// step t is still writing and handing over.  The weights are not kept in shared memory; their split planes stay in L2.
+//
+// Hand-over of h_t: the epilogue writes h_t .* mask_h as TF32 hi / lo operand planes (rows = batch columns) and then
+// adds 1 to a counter of its column block; the TMA warp of every CTA of that column block waits for the count of the
+// previous step before its first Wh h k-block.  The wait is bounded like every other wait of these kernels: on expiry
+// the CTA sets DYB200_FLAG_WAIT_TIMEOUT, skips its stores, keeps taking part in the hand-shakes so that nothing else
+// stalls, frees its TMEM and returns.
+//
+// Values are bit for bit those of the per-step calls: the same k-blocks in the same accumulation chains (cut every
+// kChunkKB k-blocks), the same K split (k_split) reduced in split order through distributed shared memory, the same epilogue.
+#include "tc_dev.cuh"
+
+namespace {
+
+constexpr uint32_t kPollLimit = 1u << 22;      // polls of a global counter before a CTA gives up (~ seconds)
+constexpr uint32_t kSeqBufs = 4;               // TMEM accumulators (4 x 128 columns)
+constexpr int SMEM_SEQ_BYTES = SMEM_BYTES + BM * 64 * 4;   // operand ring + a 64-column parking buffer
+
+struct SeqFwd {
+  uint32_t T, B, H;                 // time steps, batch columns per step, hidden units (M = 4H gate rows)
+  uint32_t kb0, kb1;                // k-blocks of Wx x and of Wh h
+  float* gates; float* cs; float* hs;   // outputs of step t at + t * 4H * B / + t * H * B
+  const float* c0;                  // cell state before the first step
+  const float* bias; float forget_bias;
+  float *hn_hi, *hn_lo; uint32_t hn_pitch;   // operand planes of h .* mask_h for the gate products: row = column of the sequence
+  float *ht_hi, *ht_lo; uint32_t ht_pitch;   // the same values transposed for the weight-gradient product: row = hidden unit
+  const float* hmask; uint32_t hmask_ld; int hmask_full;
+  uint32_t* ready;                  // one arrival counter per column block, zero at launch
+  uint32_t* flags;
+};
+
+__device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target) {
+  for (uint32_t i = 0; i < kPollLimit; ++i) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    if (v >= target) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void signal_counter(uint32_t* p) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
+}
+// mbarrier wait that also orders after arrivals from other CTAs of the cluster
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t done = 0;
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+// arrive on the same barrier of CTA `rank` of this cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(bar)), "r"(rank));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(ra) : "memory");
+}
+__device__ __forceinline__ uint32_t bar_and(uint32_t id, uint32_t count, bool pred) {
+  uint32_t r;
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, %2, %3, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(r) : "r"((uint32_t)pred), "r"(id), "r"(count) : "memory");
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// grid = (4H / 128, B / BNT, S); with S > 1 the S CTAs of a tile are one thread-block cluster (1 x 1 x S).
+template <int BNT>
+__global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_constant__ TmapPack tm, const SeqFwd a) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[kSeqBufs], acc_empty[kSeqBufs], park_full, park_free;
+  __shared__ uint32_t tmem_base_slot, split_ok;
+  unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* park = reinterpret_cast<float*>(ring + (size_t)STAGES * STAGE_BYTES);   // 64 columns x BM rows
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int TILE_B_BYTES = BNT * BK * 4;
+  constexpr int STAGE_TX = 2 * TILE_BYTES + 2 * TILE_B_BYTES;
+  const uint32_t S = gridDim.z, rank = blockIdx.z;
+  const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * BNT;
+  const KSplit ks = k_split(a.kb0, a.kb1, rank, S);
+  const uint32_t total = ks.n0 + ks.n1;          // k-blocks of this CTA per time step
+  const uint32_t M = 4 * a.H, N = a.B;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (uint32_t q = 0; q < kSeqBufs; ++q) { mbar_init(&acc_full[q], 1); mbar_init(&acc_empty[q], kEpiWarps); }
+    mbar_init(&park_full, S); mbar_init(&park_free, S);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (threadIdx.x == 32 * 2) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) asm volatile("prefetch.tensormap [%0];" ::"l"(&tm.t[q]) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kSeqBufs * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+  if (S > 1) cluster_sync_all();   // every CTA's barriers exist before anyone arrives on them remotely
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // TMA producer.  Step t reads Wx / Wh rows [m0, m0 + 128) and the operand planes of columns [t B + n0, + BNT).
+      uint32_t s = 0, ph = 0;
+      bool fail = false;
+      const uint32_t per_step = gridDim.x * S;   // arrivals per column block and step: every CTA that writes a piece of h_t
+      for (uint32_t t = 0; t < a.T && !fail; ++t) {
+        const int brow = (int)(t * a.B + n0);
+        for (uint32_t it = 0; it < total; ++it) {
+          if (it == ks.n0 && t > 0) {
+            // first Wh h k-block of this step: the planes of h_{t-1} must be complete for this column block
+            if (!wait_counter(a.ready + blockIdx.y, t * per_step)) { fail = true; break; }
+            asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy stores of other CTAs -> this CTA's TMA reads
+          }
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) { fail = true; break; }
+          const uint32_t pair = it < ks.n0 ? 0 : 1, kblk = pair ? ks.b1 + (it - ks.n0) : ks.b0 + it;
+          unsigned char* st = ring + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_TX);
+          tma_load_2d(st, &tm.t[4 * pair + 0], &full_bar[s], (int)(kblk * BK), (int)m0);
+          tma_load_2d(st + TILE_BYTES, &tm.t[4 * pair + 1], &full_bar[s], (int)(kblk * BK), (int)m0);
+          tma_load_2d(st + 2 * TILE_BYTES, &tm.t[4 * pair + 2], &full_bar[s], (int)(kblk * BK), brow);
+          tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), brow);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (fail) atomicOr(a.flags, DYB200_FLAG_WAIT_TIMEOUT);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      uint64_t d_a_hi[STAGES], d_a_lo[STAGES], d_b_hi[STAGES], d_b_lo[STAGES];
+#pragma unroll
+      for (int q = 0; q < STAGES; ++q) {
+        const uint32_t base = smem_u32(ring + (size_t)q * STAGE_BYTES);
+        d_a_hi[q] = umma_desc(base); d_a_lo[q] = umma_desc(base + TILE_BYTES);
+        d_b_hi[q] = umma_desc(base + 2 * TILE_BYTES); d_b_lo[q] = umma_desc(base + 2 * TILE_BYTES + TILE_B_BYTES);
+      }
+      // stage, phase and chunk counters run on across time steps; an accumulation chain never crosses a step
+      uint32_t s = 0, ph = 0, chunk = 0, buf = 0;
+      bool fail = false;
+      for (uint32_t t = 0; t < a.T && !fail; ++t) {
+        uint32_t in_chunk = 0;
+        for (uint32_t it = 0; it < total; ++it) {
+          if (in_chunk == 0 && chunk >= kSeqBufs) {
+            if (!mbar_wait(&acc_empty[buf], ((chunk / kSeqBufs) - 1) & 1)) { fail = true; break; }
+          }
+          if (!mbar_wait(&full_bar[s], ph)) { fail = true; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          uint64_t a_hi, a_lo, b_hi, b_lo;
+          if (s == 0) { a_hi = d_a_hi[0]; a_lo = d_a_lo[0]; b_hi = d_b_hi[0]; b_lo = d_b_lo[0]; }
+          else if (s == 1) { a_hi = d_a_hi[1]; a_lo = d_a_lo[1]; b_hi = d_b_hi[1]; b_lo = d_b_lo[1]; }
+          else { a_hi = d_a_hi[2]; a_lo = d_a_lo[2]; b_hi = d_b_hi[2]; b_lo = d_b_lo[2]; }
+          issue_kblock(tmem_base + buf * BN, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk);
+          umma_commit(&empty_bar[s]);
+          const bool chunk_ends = in_chunk == kChunkKB - 1 || it == total - 1;
+          if (chunk_ends) { umma_commit(&acc_full[buf]); in_chunk = 0; ++chunk; buf = chunk % kSeqBufs; }
+          else ++in_chunk;
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (fail) atomicOr(a.flags, DYB200_FLAG_WAIT_TIMEOUT);
+    }
+  } else {
+    // epilogue warps 2..9: TMEM lanes 32 (warp % 4) .. +31; warps 2-5 hold columns 0-63 of the tile, warps 6-9 columns 64-127
+    const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
+    const uint32_t te = threadIdx.x - 64;
+    const bool has_cols = 64 * half < BNT;
+    const uint32_t nchunks = (total + kChunkKB - 1) / kChunkKB;
+    const uint32_t u = blockIdx.x * 32 + 4 * (te & 7);   // this thread's four hidden units in the cooperative pass
+    uint32_t cg = 0, pf_phase = 0, pr_phase = 0;
+    bool ok = true;   // the same for all 256 epilogue threads after every bar_and below
+    GemmEpilogue e{};
+    e.mode = EPI_LSTM_CELL; e.ldc = M; e.bias = a.bias; e.H = a.H; e.forget_bias = a.forget_bias;
+    e.hn_pitch = a.hn_pitch; e.ht_pitch = a.ht_pitch; e.hmask = a.hmask; e.hmask_ld = a.hmask_ld; e.hmask_full = a.hmask_full;
+    const size_t HB = (size_t)a.H * a.B;
+#pragma unroll 1
+    for (uint32_t t = 0; t < a.T; ++t) {
+      e.C = a.gates + (size_t)t * 4 * HB;
+      e.c_prev = t ? a.cs + (size_t)(t - 1) * HB : a.c0;
+      e.c_out = a.cs + (size_t)t * HB;
+      e.h_out = a.hs + (size_t)t * HB;
+      const bool emit = t + 1 < a.T;   // h_t is the next step's input
+      e.hn_hi = emit ? a.hn_hi + (size_t)(t + 1) * a.B * a.hn_pitch : nullptr;
+      e.hn_lo = emit ? a.hn_lo + (size_t)(t + 1) * a.B * a.hn_pitch : nullptr;
+      e.ht_hi = a.ht_hi + (size_t)(t + 1) * a.B;
+      e.ht_lo = a.ht_lo + (size_t)(t + 1) * a.B;
+      // previous cell states of the columns this thread finishes (written by this same thread one step earlier)
+      float4 cp[BNT / 64][4];
+#pragma unroll
+      for (int hh = 0; hh < BNT / 64; ++hh)
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const uint32_t n = n0 + 64 * hh + (te >> 3) + 32 * k;
+          cp[hh][k] = n < N ? ld4(e.c_prev + u + (size_t)a.H * n) : make_float4(0.f, 0.f, 0.f, 0.f);
+          cp[hh][k + 2] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      float sum[64];
+#pragma unroll
+      for (int q = 0; q < 64; ++q) sum[q] = 0.f;
+#pragma unroll 1
+      for (uint32_t c = 0; c < nchunks; ++c, ++cg) {
+        const uint32_t buf = cg % kSeqBufs;
+        if (!ok) continue;
+        if (!mbar_wait(&acc_full[buf], (cg / kSeqBufs) & 1)) { ok = false; continue; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (has_cols) {
+          float v[32];
+          const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32) << 16) + 2 * half * 32;
+          tmem_ld32(taddr, v);
+#pragma unroll
+          for (int q = 0; q < 32; ++q) sum[q] += v[q];
+          tmem_ld32(taddr + 32, v);
+#pragma unroll
+          for (int q = 0; q < 32; ++q) sum[32 + q] += v[q];
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      }
+#pragma unroll
+      for (int hh = 0; hh < BNT / 64; ++hh) {
+        // the parking buffer is free once every CTA of the cluster has read its slice of the previous pass (S > 1), or
+        // once this CTA's own threads have left the previous pass (the barrier at its end)
+        if (S > 1 && ok && !mbar_wait_cluster(&park_free, pr_phase ^ 1)) ok = false;
+        if (half == (uint32_t)hh) {
+          float* col = park + quarter * 32 + lane;
+#pragma unroll
+          for (int q = 0; q < 64; ++q) col[(size_t)q * BM] = sum[q];
+        }
+        ok = bar_and(1, 256, ok) != 0;
+        const uint32_t nh = n0 + 64 * hh;
+        if (S > 1) {
+          if (te == 0) {
+            split_ok = ok ? 1u : 0u;
+            for (uint32_t r = 0; r < S; ++r) mbar_arrive_remote(&park_full, r);   // (release: the parked tile and split_ok)
+          }
+          const bool got = mbar_wait_cluster(&park_full, pf_phase);
+          ok = bar_and(1, 256, ok && got) != 0;
+          // rank r finishes columns [c_lo, c_hi) of these 64: partial tiles added in split order, then the epilogue
+          const uint32_t w = ((64 + S - 1) / S + 7) & ~7u;
+          const uint32_t c_lo = min(rank * w, 64u), c_hi = min(c_lo + w, 64u);
+          uint32_t all = ok ? 1u : 0u, base[8];
+          for (uint32_t r = 0; r < S; ++r) {
+            uint32_t ra, v;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(&split_ok)), "r"(r));
+            asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(ra) : "memory");
+            all &= v;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base[r & 7]) : "r"(smem_u32(park)), "r"(r));
+          }
+          if (all) {
+            const uint32_t f_lo = c_lo * (BM / 4), f_hi = c_hi * (BM / 4);
+            float4* t4 = reinterpret_cast<float4*>(park);
+            for (uint32_t f = f_lo + te; f < f_hi; f += 256) {
+              float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (uint32_t r = 0; r < S; ++r) {
+                float4 pv;
+                asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(pv.x), "=f"(pv.y), "=f"(pv.z), "=f"(pv.w) : "r"(base[r & 7] + 16u * f) : "memory");
+                if (r == 0) acc = pv;
+                else { acc.x += pv.x; acc.y += pv.y; acc.z += pv.z; acc.w += pv.w; }
+              }
+              t4[f] = acc;
+            }
+          }
+          bar_sync(1, 256);   // the pass below reads other threads' pieces
+          if (all) epilogue_pass<64, 256>(e, park, te, blockIdx.x, m0, nh, M, N, cp[hh], c_lo, c_hi);
+          else if (ok) { ok = false; if (te == 0) atomicOr(a.flags, DYB200_FLAG_WAIT_TIMEOUT); }
+          bar_sync(1, 256);   // this CTA has read everything it needs from the other tiles
+          if (te == 0) for (uint32_t r = 0; r < S; ++r) mbar_arrive_remote(&park_free, r);
+          pf_phase ^= 1; pr_phase ^= 1;
+        } else {
+          if (ok) epilogue_pass<64, 256>(e, park, te, blockIdx.x, m0, nh, M, N, cp[hh]);
+          bar_sync(1, 256);
+        }
+      }
+      if (emit) {
+        // h_t .* mask_h is in global memory as far as this thread is concerned: make it visible to the TMA engines of the
+        // other CTAs, then count this CTA in
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+        bar_sync(1, 256);
+        if (te == 0) signal_counter(a.ready + blockIdx.y);
+      }
+    }
+    if (!ok && lane == 0) atomicOr(a.flags, DYB200_FLAG_WAIT_TIMEOUT);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (S > 1) cluster_sync_all();   // no CTA leaves while another may still arrive on its barriers
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kSeqBufs * BN) : "memory");
+  }
+}
+
+}  // namespace
+
+// ---- host side ---------------------------------------------------------------------------------------------------------
+namespace {
+
+// How many clusters of S CTAs of the sequence kernel fit on the GPU at once (remembered per context = per device).
+template <int BNT>
+int seq_clusters_that_fit(dyb200_ctx* ctx, uint32_t S) {
+  int& mc = ctx->seq_max_clusters[BNT == 64 ? 0 : 1][S];
+  if (mc == 0) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(1, 1, S); cfg.blockDim = dim3(kThreads, 1, 1); cfg.dynamicSmemBytes = SMEM_SEQ_BYTES; cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = S;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, k_lstm_seq_fwd<BNT>, &cfg) != cudaSuccess) { (void)cudaGetLastError(); n = -1; }
+    mc = n > 0 ? n : -1;
+  }
+  return mc;
+}
+
+template <int BNT>
+int launch_seq_fwd(dyb200_ctx* ctx, const TmapPack& tm, const SeqFwd& a, dim3 grid, double flops, uint32_t K) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid; cfg.blockDim = dim3(kThreads, 1, 1); cfg.dynamicSmemBytes = SMEM_SEQ_BYTES; cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (grid.z > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = grid.z;
+    ++na;
+  }
+  // All CTAs wait on one another, so they have to be resident together.  The grid never exceeds what the GPU holds at
+  // once (checked by the caller); the cooperative attribute additionally makes the driver schedule them as one gang.  A
+  // driver that refuses the attribute for this launch shape gets a plain launch (the waits are bounded either way).
+  if (ctx->seq_coop >= 0) {
+    attr[na].id = cudaLaunchAttributeCooperative;
+    attr[na].val.cooperative = 1;
+    cfg.attrs = attr; cfg.numAttrs = na + 1;
+    GemmProfScope scope(ctx, flops, 1, 4 * a.H, a.B * a.T, K, EPI_LSTM_CELL);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, k_lstm_seq_fwd<BNT>, tm, a);
+    if (e == cudaSuccess) { ctx->seq_coop = 1; ctx->launches++; return DYB200_OK; }
+    (void)cudaGetLastError();
+    if (ctx->seq_coop == 1) return dyb200_fail(ctx, DYB200_ECUDA, "sequence kernel launch failed: %s", cudaGetErrorString(e));
+    ctx->seq_coop = -1;
+  }
+  cfg.attrs = attr; cfg.numAttrs = na;
+  GemmProfScope scope(ctx, flops, 1, 4 * a.H, a.B * a.T, K, EPI_LSTM_CELL);
+  cudaLaunchKernelEx(&cfg, k_lstm_seq_fwd<BNT>, tm, a);
+  DYB_LAUNCHED(ctx);
+  return DYB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dyb200_vanilla_lstm_seq_fwd(const dyb200_tensor* x_all, const dyb200_tensor* h0, const dyb200_tensor* c0,
+                                const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* b,
+                                const dyb200_tensor* mask_x, const dyb200_tensor* mask_h, const dyb200_lstm_gates_attrs* attrs,
+                                dyb200_tensor* gates_all, dyb200_tensor* c_all, dyb200_tensor* h_all, dyb200_wgrad* deferred,
+                                uint32_t steps, dyb200_ctx* ctx) {
+  DYB_CHECK_ARG(ctx, x_all && h0 && c0 && Wx && Wh && b && attrs && gates_all && c_all && h_all && steps > 0, "lstm_seq_fwd: null argument");
+  DYB_CHECK_ARG(ctx, (attrs->dropout != 0) == (mask_x != nullptr && mask_h != nullptr), "lstm_seq_fwd: masks must be given exactly when dropout is set");
+  DYB_CHECK_ARG(ctx, x_all->nd == 1 && x_all->bd % steps == 0, "lstm_seq_fwd: x_all must be Dim({I}, steps * batch)");
+  const uint32_t T = steps, B = x_all->bd / T, I = t_dim(x_all, 0), H = t_dim(h0, 0), G = 4 * H;
+  const size_t HB = (size_t)H * B;
+  DYB_CHECK_ARG(ctx, h0->nd == 1 && h0->bd == B && c0->bd == B && t_dim(c0, 0) == H, "lstm_seq_fwd: h0 / c0 must be Dim({H}, batch)");
+  DYB_CHECK_ARG(ctx, t_size(gates_all) == 4 * HB * T && t_size(c_all) == HB * T && t_size(h_all) == HB * T, "lstm_seq_fwd: outputs must hold all %u steps", T);
+  if (HB == 0) return DYB200_OK;
+  int rc;
+  if (deferred && (rc = dyb200_wgrad_pack_inputs(deferred, x_all, mask_x, B, ctx))) return rc;
+  const float* mx = attrs->dropout ? mask_x->v : nullptr;
+  const float* mh = attrs->dropout ? mask_h->v : nullptr;
+  const int mh_full = mh ? mask_h->bd == B : 0;
+  (void)mx;
+
+  // ---- one kernel for the whole sequence, when its CTAs can all be resident ----
+  const uint32_t bn = dyb200_tc_tile_cols(B);
+  const uint32_t kb0 = (I + 31) / 32, kb1 = (H + 31) / 32, kb_total = kb0 + kb1;
+  bool persistent = ctx->seq_kernels && deferred && T >= 2 && attrs->weightnoise_std == 0.f && H % 32 == 0 && I % 4 == 0 && B % bn == 0 &&
+                    dyb200_tc_eligible(G, B, 2.0 * G * B * (I + H)) && Wx->nd == 2 && Wx->d[0] == G && Wx->d[1] == I && Wh->nd == 2 &&
+                    Wh->d[0] == G && Wh->d[1] == H && t_size(b) == G && aligned16(gates_all->v) && aligned16(b->v) && aligned16(c0->v) &&
+                    aligned16(c_all->v) && aligned16(h_all->v) && (!mh || aligned16(mh)) &&
+                    (!attrs->dropout || ((mask_h->bd == B || mask_h->bd == 1) && t_dim(mask_h, 0) == H));
+  uint32_t S = 1;
+  SeqPlanes pl;
+  if (persistent) {
+    S = dyb200_tc_splits(ctx, G, B, kb_total);
+    const uint32_t per = (kb_total + S - 1) / S;
+    S = (kb_total + per - 1) / per;
+    const uint32_t tiles = (G / BM) * (B / bn);
+    if (S > 8 || (S > 1 && !ctx->cluster_splitk)) persistent = false;
+    else if (S > 1) {
+      const int fit = bn == 64 ? seq_clusters_that_fit<64>(ctx, S) : seq_clusters_that_fit<128>(ctx, S);
+      persistent = fit > 0 && tiles <= (uint32_t)fit;
+    } else {
+      persistent = tiles <= (uint32_t)ctx->sm_count;   // one CTA per SM (225 KB of shared memory each)
+    }
+    if (B / bn > 32) persistent = false;                // one hand-over counter per column block
+    if (persistent) persistent = dyb200_wgrad_seq_planes(deferred, T, B, &pl);
+  }
+  if (persistent) {
+    { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
+    DYB_CHECK_ARG(ctx, dyb200_wgrad_rows(deferred) == G, "lstm_seq_fwd: the deferred accumulator has %u rows, the layer %u", dyb200_wgrad_rows(deferred), G);
+    PackedOp A[2];
+    if ((rc = dyb200_tc_param_gates(ctx, Wx->v, G, G, I, &A[0]))) return rc;
+    if ((rc = dyb200_tc_param_gates(ctx, Wh->v, G, G, H, &A[1]))) return rc;
+    PackJobs batch;
+    dyb200_tc_pack_begin(&batch);
+    if ((rc = dyb200_wgrad_seq_h0(deferred, h0->v, mh, mh_full, ctx, &batch))) return rc;
+    if ((rc = dyb200_tc_pack_flush(ctx, &batch))) return rc;
+    TmapPack tm;
+    memset(&tm, 0, sizeof(tm));
+    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[0], A[0].hi, G, I, A[0].pitch, BM))) return rc;
+    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[1], A[0].lo, G, I, A[0].pitch, BM))) return rc;
+    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[2], pl.X.hi, T * B, I, pl.X.pitch, bn))) return rc;
+    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[3], pl.X.lo, T * B, I, pl.X.pitch, bn))) return rc;
+    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[4], A[1].hi, G, H, A[1].pitch, BM))) return rc;
+    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[5], A[1].lo, G, H, A[1].pitch, BM))) return rc;
+    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[6], pl.Hs.hi, T * B, H, pl.Hs.pitch, bn))) return rc;
+    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[7], pl.Hs.lo, T * B, H, pl.Hs.pitch, bn))) return rc;
+    SeqFwd a;
+    memset(&a, 0, sizeof(a));
+    a.T = T; a.B = B; a.H = H; a.kb0 = kb0; a.kb1 = kb1;
+    a.gates = gates_all->v; a.cs = c_all->v; a.hs = h_all->v; a.c0 = c0->v; a.bias = b->v; a.forget_bias = attrs->forget_gate_bias;
+    a.hn_hi = pl.Hs.hi; a.hn_lo = pl.Hs.lo; a.hn_pitch = pl.Hs.pitch;
+    a.ht_hi = pl.B1.hi; a.ht_lo = pl.B1.lo; a.ht_pitch = pl.B1.pitch;
+    a.hmask = mh; a.hmask_ld = H; a.hmask_full = mh_full;
+    a.ready = ctx->dev_flags + DYB200_DEV_SEQ0;
+    a.flags = ctx->dev_flags;
+    DYB_CUDA(ctx, cudaMemsetAsync(a.ready, 0, 32 * sizeof(uint32_t), ctx->stream));
+    const uint32_t bit = bn == 64 ? 16u : 32u;
+    if (!(ctx->func_attr_done & bit)) {
+      if (bn == 64) DYB_CUDA(ctx, cudaFuncSetAttribute(k_lstm_seq_fwd<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_SEQ_BYTES));
+      else DYB_CUDA(ctx, cudaFuncSetAttribute(k_lstm_seq_fwd<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_SEQ_BYTES));
+      ctx->func_attr_done |= bit;
+    }
+    const dim3 grid(G / BM, B / bn, S);
+    const double flops = 2.0 * G * (double)B * (I + H) * T;
+    rc = bn == 64 ? launch_seq_fwd<64>(ctx, tm, a, grid, flops, I + H) : launch_seq_fwd<128>(ctx, tm, a, grid, flops, I + H);
+    if (rc) return rc;
+    dyb200_wgrad_seq_done(deferred);
+    return DYB200_OK;
+  }
+
+  // ---- the same sequence as one call per time step ----
+  for (uint32_t t = 0; t < T; ++t) {
+    dyb200_tensor x = *x_all, hp = *h0, cp = *c0, g = *gates_all, c = *c_all, h = *h_all;
+    x.bd = B; x.v = x_all->v + (size_t)t * I * B;
+    g.bd = B; g.v = gates_all->v + (size_t)t * 4 * HB;
+    c.bd = B; c.v = c_all->v + (size_t)t * HB;
+    h.bd = B; h.v = h_all->v + (size_t)t * HB;
+    if (t > 0) { hp.v = h_all->v + (size_t)(t - 1) * HB; cp.v = c_all->v + (size_t)(t - 1) * HB; }
+    if ((rc = dyb200_vanilla_lstm_fwd_fused_at(&x, &hp, &cp, Wx, Wh, b, mask_x, mask_h, attrs, &g, &c, &h, deferred, t * B, ctx))) return rc;
+  }
+  return DYB200_OK;
+}
+
+}  // extern "C"

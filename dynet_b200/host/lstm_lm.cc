@@ -191,22 +191,31 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   // matters when the per-GPU batch is small and the products are bound by weight traffic.  Same values either way
   // (dyb200h_lm_set_time_major restores the reference's order).
   const bool layer_major = c.fused && !m.time_major;
-  for (uint32_t pass = 0; pass < (layer_major ? L : 1u); ++pass)
-  for (uint32_t t = 0; t < T; ++t) {
-    if (layer_major && t == 0) {
-      // the inputs of this layer for all time steps are complete (embeddings, or the layer below): split them in one launch
-      const uint32_t l = pass, I = l == 0 ? E : H;
-      Tensor xall(Dim({I}, TB), l == 0 ? m.x : m.hs + at(0, l - 1) * HB), mxl(Dim({I}, B), c.dropout ? const_cast<float*>(masks[2 * l]) : nullptr);
-      dyb200_tensor cxa = to_c(xall), cmx = to_c(mxl);
-      throw_status(dev, dyb200_wgrad_pack_inputs(m.wg_layer[l], &cxa, c.dropout ? &cmx : nullptr, B, dev.ctx));
+  if (layer_major) {
+    // One call per layer: the inputs of a layer for all time steps are complete before it starts (embeddings, or the layer
+    // below), so they are split into operand planes in one launch and the T steps run inside one kernel whose CTAs hand
+    // h_t over on the device (dyb200_vanilla_lstm_seq_fwd; it makes the per-step calls itself when the shape does not allow that).
+    for (uint32_t l = 0; l < L; ++l) {
+      const uint32_t I = l == 0 ? E : H;
+      Tensor xall(Dim({I}, TB), l == 0 ? m.x : m.hs + at(0, l - 1) * HB);
+      Tensor gall(Dim({4 * H}, TB), m.gates + at(0, l) * GB), call(Dim({H}, TB), m.cs + at(0, l) * HB), hall_l(Dim({H}, TB), m.hs + at(0, l) * HB);
+      Tensor tWx(Dim({4 * H, I}), m.p[1 + 3 * l]), tWh(Dim({4 * H, H}), m.p[2 + 3 * l]), tb(Dim({4 * H}), m.p[3 + 3 * l]);
+      Tensor mxl(Dim({I}, B), c.dropout ? const_cast<float*>(masks[2 * l]) : nullptr), mhl(Dim({H}, B), c.dropout ? const_cast<float*>(masks[2 * l + 1]) : nullptr);
+      dyb200_tensor cxa = to_c(xall), ch0 = to_c(tZero), cc0 = to_c(tZero), cWx = to_c(tWx), cWh = to_c(tWh), cb = to_c(tb), cmx = to_c(mxl),
+                    cmh = to_c(mhl), cg = to_c(gall), cc = to_c(call), ch = to_c(hall_l);
+      dyb200_lstm_gates_attrs at = {c.dropout ? 1 : 0, 0.f, 1.f};
+      throw_status(dev, dyb200_vanilla_lstm_seq_fwd(&cxa, &ch0, &cc0, &cWx, &cWh, &cb, c.dropout ? &cmx : nullptr, c.dropout ? &cmh : nullptr,
+                                                    &at, &cg, &cc, &ch, m.wg_layer[l], T, dev.ctx));
     }
+  }
+  for (uint32_t t = 0; t < (layer_major ? 0u : T); ++t) {
     if (!c.fused) {
       LookupNode look(tC, nullptr, B);
       look.aux_mem = m.tok + (size_t)t * B;
       Tensor xt(Dim({E}, B), m.x + t * EB);
       look.forward_dev_impl(dev, {}, xt);
     }
-    for (uint32_t l = layer_major ? pass : 0u; l < (layer_major ? pass + 1 : L); ++l) {
+    for (uint32_t l = 0; l < L; ++l) {
       size_t idx = at(t, l);
       Tensor store[7];
       std::vector<const Tensor*> xs;

@@ -301,6 +301,25 @@ int dyb200_wgrad_push(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda,
 int dyb200_wgrad_pack_inputs(dyb200_wgrad* w, const dyb200_tensor* x_all, const dyb200_tensor* mask_x, uint32_t step, dyb200_ctx* ctx);
 int dyb200_wgrad_flush(dyb200_wgrad* w, float* C0, uint32_t ldc0, float* C1, uint32_t ldc1, dyb200_ctx* ctx);
 
+/* One LSTM layer over all time steps of a batch of equally long sequences: the calls RNNBuilder::add_input (dynet/rnn.h:120)
+ * makes into CompactVanillaLSTMBuilder::add_input_impl (dynet/lstm.cc:1044-1080) for t = 0 .. steps - 1, in one call.
+ * x_all = Dim({I}, steps * batch) holds the layer inputs of all steps side by side (batch columns each), gates_all / c_all /
+ * h_all = Dim({4H} / {H} / {H}, steps * batch) receive every step's gates, c_t and h_t; h0 / c0 = Dim({H}, batch) are the state
+ * before the first step; masks as in dyb200_vanilla_lstm_fwd_fused (the same mask for every step, dynet/lstm.cc:1010-1030).
+ * Equivalent, bit for bit, to dyb200_wgrad_pack_inputs(deferred, x_all, mask_x, batch) followed by steps calls of
+ * dyb200_vanilla_lstm_fwd_fused_at with deferred_col = t * batch, h_tm1 / c_tm1 = the previous step's outputs.  When the shape
+ * allows (tensor-path sizes, whole tiles, every CTA resident at once) the steps run inside ONE kernel whose CTAs stay on the
+ * GPU for the whole sequence and hand h_t over through device memory; otherwise the per-step calls are made.
+ * dyb200_ctx_sequence_kernels(ctx, 0) forces the per-step form.  deferred may be NULL (per-step form, nothing recorded for
+ * the weight gradients). */
+int dyb200_vanilla_lstm_seq_fwd(const dyb200_tensor* x_all, const dyb200_tensor* h0, const dyb200_tensor* c0,
+                                const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* b,
+                                const dyb200_tensor* mask_x, const dyb200_tensor* mask_h, const dyb200_lstm_gates_attrs* attrs,
+                                dyb200_tensor* gates_all, dyb200_tensor* c_all, dyb200_tensor* h_all, struct dyb200_wgrad* deferred,
+                                uint32_t steps, dyb200_ctx* ctx);
+/* Sequence-persistent kernels (on by default): off makes dyb200_vanilla_lstm_seq_* issue one call per time step. */
+int dyb200_ctx_sequence_kernels(dyb200_ctx* ctx, int enable);
+
 /* ---- A14 autobatch ragged movers (same argument meaning as dynet/gpu-ops.h:14-15;
  * src/trg/len are DEVICE arrays of num_seqs entries, as dynet/exec.cc:346-356 uploads them) ---- */
 int dyb200_parallel_memcpy(int num_seqs, int max_len, float** src, float** trg, size_t* len, dyb200_ctx* ctx);

@@ -85,9 +85,12 @@ def test_config1_builder_graph_pins_the_fused_chain(oracle, g, capi):
         ctx.fwd("vanilla_lstm_c", [g.T(cf), g.T(gates)], g.T(cn2))
         ctx.fwd("vanilla_lstm_h", [g.T(cn2), g.T(gates)], g.T(hn2))
         hf, cf = hn2, cn2
-        for name, got in (("non-fused graph", (hu, cu)), ("fused chain", (hf, cf))):
-            assert_close(g.host(got[0]), h_ref, 1e-5, floor=GEMM_FLOOR, what="h_%d, %s vs builder-graph oracle" % (t, name))
-            assert_close(g.host(got[1]), c_ref, 1e-5, floor=GEMM_FLOOR, what="c_%d, %s vs builder-graph oracle" % (t, name))
+        # The states are O(1); 1e-5 of 0.1 is the reach of the node kernels.  The fused chain forms the gate activations in
+        # the GEMM epilogue from ex2.approx / rcp (sigmoid good to 1.5e-6 relative), which puts an absolute 1 - 2e-6 on c and
+        # h: its states are held to 1e-5 of 0.25.
+        for name, got, floor in (("non-fused graph", (hu, cu), GEMM_FLOOR), ("fused chain", (hf, cf), 0.25)):
+            assert_close(g.host(got[0]), h_ref, 1e-5, floor=floor, what="h_%d, %s vs builder-graph oracle" % (t, name))
+            assert_close(g.host(got[1]), c_ref, 1e-5, floor=floor, what="c_%d, %s vs builder-graph oracle" % (t, name))
     assert ctx.device_errors() == 0
 
 
