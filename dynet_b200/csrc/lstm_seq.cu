@@ -407,6 +407,13 @@ int dyb200_vanilla_lstm_seq_fwd(const dyb200_tensor* x_all, const dyb200_tensor*
   uint32_t S = 1;
   SeqPlanes pl;
   if (persistent) {
+    // (the shared-memory limit of the kernel has to be raised before its occupancy is asked for)
+    const uint32_t bit = bn == 64 ? 16u : 32u;
+    if (!(ctx->func_attr_done & bit)) {
+      if (bn == 64) DYB_CUDA(ctx, cudaFuncSetAttribute(k_lstm_seq_fwd<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_SEQ_BYTES));
+      else DYB_CUDA(ctx, cudaFuncSetAttribute(k_lstm_seq_fwd<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_SEQ_BYTES));
+      ctx->func_attr_done |= bit;
+    }
     S = dyb200_tc_splits(ctx, G, B, kb_total);
     const uint32_t per = (kb_total + S - 1) / S;
     S = (kb_total + per - 1) / per;
@@ -451,12 +458,6 @@ int dyb200_vanilla_lstm_seq_fwd(const dyb200_tensor* x_all, const dyb200_tensor*
     a.ready = ctx->dev_flags + DYB200_DEV_SEQ0;
     a.flags = ctx->dev_flags;
     DYB_CUDA(ctx, cudaMemsetAsync(a.ready, 0, 32 * sizeof(uint32_t), ctx->stream));
-    const uint32_t bit = bn == 64 ? 16u : 32u;
-    if (!(ctx->func_attr_done & bit)) {
-      if (bn == 64) DYB_CUDA(ctx, cudaFuncSetAttribute(k_lstm_seq_fwd<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_SEQ_BYTES));
-      else DYB_CUDA(ctx, cudaFuncSetAttribute(k_lstm_seq_fwd<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_SEQ_BYTES));
-      ctx->func_attr_done |= bit;
-    }
     const dim3 grid(G / BM, B / bn, S);
     const double flops = 2.0 * G * (double)B * (I + H) * T;
     rc = bn == 64 ? launch_seq_fwd<64>(ctx, tm, a, grid, flops, I + H) : launch_seq_fwd<128>(ctx, tm, a, grid, flops, I + H);

@@ -84,7 +84,8 @@ def _run(g, capi, D, I, H, B, T, dropout, seq, dhs):
     (512, 1024, 64, 5, True, False, True),      # layer 1 on 8 GPUs, batch-1 masks
     (1024, 1024, 128, 3, True, True, True),     # 4 GPUs: 128-column tiles, 4 K splits per cluster
     (512, 1024, 256, 3, False, True, True),     # 2 GPUs: 2 K splits per cluster, no dropout
-    (256, 512, 384, 3, True, True, True),       # three column blocks, 16 row blocks
+    (256, 1024, 384, 3, True, True, True),      # three column blocks, one tile per CTA
+    (256, 512, 384, 3, True, True, False),      # 3 K splits: 48 clusters of 3 do not fit on the GPU at once -> per-step calls
     (128, 256, 96, 3, True, True, False),       # 96 columns are not whole tiles: per-step calls inside
     (32, 64, 8, 3, True, True, False),          # far below the tensor path
 ])
@@ -114,7 +115,7 @@ def test_sequence_forward_equals_per_step_calls(oracle, g, capi, I, H, B, T, dro
     if one_kernel:
         assert l_seq == 3 < l_per, (l_seq, l_per)      # operand split of x, of h0 (the counter reset is a memset), one kernel
     else:
-        assert l_seq == l_per
+        assert l_seq <= l_per
     # and the values themselves: the oracle's node chain
     h = np.zeros((B, H), np.float32)
     c = np.zeros((B, H), np.float32)
