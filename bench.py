@@ -32,6 +32,28 @@ DROPOUT = 0.2
 METRIC = "LSTM-LM training tokens/sec (2-layer LSTM, V=10k E=512 H=1024 T=35, global batch 512, fwd+bwd+allreduce+SGD)"
 
 
+def config_dict(world, graph=True):
+    """The `config` object of the JSON line: the same for this implementation and for the reference arm."""
+    V, E, H, L, T = (WORKLOAD[k] for k in "VEHLT")
+    return {"workload": "lstm_lm_2x1024_v10k_t35", "global_batch": GLOBAL_BATCH, "per_gpu_batch": GLOBAL_BATCH // world,
+            "seq_len": T, "vocab": V, "embed": E, "hidden": H, "layers": L, "dropout": DROPOUT,
+            "parallelism": "dp%d" % world, "l2": "per-step working set (~2.5 GB of activations) exceeds the 126 MB L2",
+            "cuda_graph": bool(graph)}
+
+
+def cpu_model():
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.lower().startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown CPU"
+
+
+FLOPS_PER_TOKEN = None   # filled below (useful FLOPs of fwd + bwd per token of the workload)
+
+
 def flops_per_step(B):
     V, E, H, L, T = (WORKLOAD[k] for k in "VEHLT")
     fwd = 0
@@ -39,6 +61,9 @@ def flops_per_step(B):
         fwd += 2 * 4 * H * ((E if l == 0 else H) + H) * B
     fwd += 2 * V * H * B
     return 3 * fwd * T   # backward = 2x forward
+
+
+FLOPS_PER_TOKEN = flops_per_step(1) / WORKLOAD["T"]
 
 
 class ClockSampler:
@@ -157,25 +182,43 @@ def cpu_baseline_sample(threads, seqs_per_thread, steps=1):
     return tokens_per_step / sec, sec, tokens_per_step
 
 
+def cpu_baseline_record(single_seqs, steps, multi=True):
+    """The reference's CPU path is single-threaded (Eigen DefaultDevice, no OpenMP in its build, dynet/devices.cc:150), so
+    the baseline is ONE host thread running the oracle port on a bounded sample of the step (single_seqs of the 512
+    sequences, all 35 time steps, full model size); tokens/s scales linearly in the sequences.  A second, labelled figure
+    uses all host threads as independent shards (the reference's dynet/mp.h process-level data parallelism)."""
+    ncpu = os.cpu_count() or 1
+    tps, sec, toks = cpu_baseline_sample(1, single_seqs, steps=steps)
+    rec = {"value": tps, "unit": "tokens/s", "cores": 1, "kind": "port", "cpu_model": cpu_model(), "nproc": ncpu,
+           "sample": "1 host thread x %d sequences x T=35 per step (of the 512-sequence batch; tokens/s is linear in the sequences), "
+                     "fwd+bwd+update at full model size, %.1f s per step" % (single_seqs, sec),
+           "gflops_per_thread": tps * FLOPS_PER_TOKEN / 1e9,
+           "note": "oracle port of the reference's CPU algorithm (the reference itself needs Eigen b2e267dc99d4, absent here); its "
+                   "matrix products are plain blocked loops without FMA contraction, several times slower than Eigen's GEBP kernel"}
+    if multi and ncpu > 1:
+        threads = min(ncpu, 32)
+        mtps, msec, _ = cpu_baseline_sample(threads, 16, steps=1)
+        rec["multi_thread"] = {"value": mtps, "unit": "tokens/s", "cores": threads,
+                               "sample": "%d host threads x 16 sequences each, one step, %.1f s" % (threads, msec)}
+    return rec
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    ncpu = os.cpu_count() or 1
-    threads = max(1, min(ncpu, 32))
-    seqs = 16   # per thread: enough columns that each weight matrix is reused, as in the real batch
-    # warm-up (builds the oracle, touches memory) then K bounded steps
+    seqs = 8    # per step: ~2 s of one core, so that K steps stay within a few minutes
     for _ in range(max(1, min(args.warmup, 1))):
-        cpu_baseline_sample(threads, 1, steps=1)
-    tps, sec, toks = cpu_baseline_sample(threads, seqs, steps=max(1, args.steps))
-    sample = "%d host threads x %d sequences x T=35 per step (of the 512-sequence batch), full model size" % (threads, seqs)
+        cpu_baseline_sample(1, 1, steps=1)           # builds the oracle, touches memory
+    rec = cpu_baseline_record(seqs, max(1, args.steps))
+    tps = rec["value"]
+    world = max(1, args.gpus)
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "lstm_lm_2x1024_v10k_t35", "global_batch": GLOBAL_BATCH, "seq_len": WORKLOAD["T"],
-                   "note": "reference CPU algorithm (oracle port; the reference itself needs Eigen b2e267dc99d4, absent here)"},
-        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "warmup": args.warmup, "ms_per_step": GLOBAL_BATCH * WORKLOAD["T"] / tps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(world),
+        "ms_per_step_note": "the full 512-sequence step extrapolated linearly from the sample",
+        "cpu_baseline": rec,
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -226,6 +269,8 @@ def run_gpu(args):
         model.allreduce_grads()
         model.update()
 
+    closed = [False]
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -271,6 +316,7 @@ def run_gpu(args):
     model.set_graph(False)
     model.ctx.profile_begin(1 << 16)
     ms_prof, _ = timed(args.steps, dev_tokens, read_loss=False)
+    per_launch = model.ctx.profile_launches()      # (M, N, K, epilogue mode, path, ms, flops) of every product
     prof = model.ctx.profile_end()
     errs = model.ctx.device_errors()
     launches = launches_per_step * args.steps
@@ -293,6 +339,17 @@ def run_gpu(args):
         phases += [ev[q].elapsed_time(ev[q + 1]) for q in range(4)]
     phases /= 5
 
+    # replicas must hold bit-identical parameters after the same number of updates (deterministic kernels, the same reduced
+    # gradient on every rank): max over ranks and elements of |theta_r - theta_0|
+    replica_diff = 0.0
+    if world > 1:
+        ref = model.params.clone()
+        dist.broadcast(ref, src=0)
+        d = (model.params - ref).abs().max().reshape(1)
+        dist.all_reduce(d, op=dist.ReduceOp.MAX)
+        replica_diff = float(d.item())
+        del ref
+
     tokens_per_step = GLOBAL_BATCH * T
     value = tokens_per_step * args.steps / (ms * 1e-3)
     e2e = tokens_per_step * args.steps / (ms_e2e * 1e-3)
@@ -305,45 +362,66 @@ def run_gpu(args):
         g_ms, g_n, g_fl = prof[which]
         achieved = g_fl / (g_ms * 1e-3) / 1e12 if g_ms > 0 else 0.0
         peak = tf32 / 3.0
+        # per shape: launches per step, device time, useful TFLOP/s, and the bytes one launch has to move at least (the split
+        # operand planes once, the result once; read-modify-write for the accumulating epilogues)
+        shapes = {}
+        for (M_, N_, K_, mode, path, t_ms, fl) in per_launch:
+            rec = shapes.setdefault((M_, N_, K_, mode), [0, 0.0, 0.0])
+            rec[0] += 1; rec[1] += t_ms; rec[2] += fl
+        by_shape = []
+        for (M_, N_, K_, mode), (cnt, t_ms, fl) in sorted(shapes.items(), key=lambda kv: -kv[1][1]):
+            operand = 8.0 * K_ * (M_ + N_)
+            result = 4.0 * M_ * N_ * (2 if mode in (1, 3) else 1) * (5.0 / 4.0 if mode == 5 else 1.0)   # LSTM epilogue: + c and h
+            by_shape.append({"M": M_, "N": N_, "K": K_, "epilogue": int(mode), "launches_per_step": cnt / args.steps,
+                             "us_per_launch": 1e3 * t_ms / cnt, "useful_tflops": fl / (t_ms * 1e-3) / 1e12 if t_ms > 0 else None,
+                             "algorithmic_bytes_per_launch": operand + result})
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                     "frac": achieved / peak if peak else None,
-                    # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the most frequent GEMM shape (the fused
-                    # LSTM forward, M4096 N512 K2048), from the ncu capture summarised under profiles/; `achieved` averages all shapes
-                    "traffic": 81.97e6,
+                    # DRAM bytes are a per-launch quantity of ONE shape, and this figure averages some ten shapes: the captured
+                    # traffic is therefore given per shape below, next to the bytes that shape has to move at least
+                    "traffic": None,
+                    "traffic_captured_per_launch": {
+                        "output_layer_M10000_N17920_K1024": 1.54e9,
+                        "note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch from the committed ncu summaries "
+                                "(0.82 GB read + 0.72 GB written; algorithmic 0.83 GB); tensor-bound kernels, DRAM at 15-19 % of peak"},
                     "kernel": "gemm_3xtf32_tcgen05" if which == "tensor" else "gemm_fp32_cuda_core",
                     "launches": g_n, "share_of_step_time": g_ms / ms_prof if ms_prof else None,
+                    "by_shape": by_shape[:12],
                     "measured_over": "the same %d steps issued launch by launch (%.2f ms/step) right after the timed region, "
                                      "which replays them as one CUDA graph" % (args.steps, ms_prof / args.steps),
-                    "traffic_note": "bytes per launch of the LSTM-forward GEMM shape (ncu: 77.7 MB read + 4.3 MB written = packed operands "
-                                    "and c_prev exactly once; algorithmic operand bytes 77.6 MB); tensor-bound kernel, DRAM at 19 % of peak",
                     "peak_source": "cuBLAS TF32 8192^3 measured in this run (%.0f TFLOP/s) / 3; bf16 peak of %s: %s TFLOP/s"
                                    % (tf32, peaks["source"], peaks["bf16_tflops"]),
                     "useful_tflop_per_step": flops_per_step(B) * world / 1e12}
-        cb_threads = max(1, min(os.cpu_count() or 1, 32))
-        cb_tps, cb_sec, cb_tok = cpu_baseline_sample(cb_threads, 16, steps=1) if not args.no_cpu_baseline else (None, None, None)
+        cpu_rec = None if args.no_cpu_baseline else cpu_baseline_record(32, 1)
+        # the memory-bound kernels one by one (CUDA-graph timed, rotating buffers): the other half of the metric
+        hbm = None
+        if world == 1 and not args.no_hbm_kernels:
+            import kernel_bench
+            model.close()
+            closed[0] = True
+            res = kernel_bench.run(iters=10, quiet=True, device=local_rank, skip_tensor_bound=True)
+            hbm = {"peak_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
+                   "kernels": [{"name": r_["kernel"], "algorithmic_bytes": r_["algorithmic_bytes"], "us": 1e3 * r_["ms"],
+                                "GBps": r_["GBps"], "frac": r_["GBps"] / peaks["hbm_gbs"]} for r_ in res]}
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "lstm_lm_2x1024_v10k_t35", "global_batch": GLOBAL_BATCH, "per_gpu_batch": B,
-                       "seq_len": T, "vocab": V, "embed": E, "hidden": H, "layers": L, "dropout": DROPOUT,
-                       "parallelism": "dp%d" % world, "l2": "per-step working set (~2.5 GB of activations) exceeds the 126 MB L2",
-                       "cuda_graph": not args.no_graph},
+            "dtype": "f32", "data": "synthetic", "config": config_dict(world, not args.no_graph),
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": int((T + 1) * B * 4 * world),
                     "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps, "last_loss": losses[-1] if losses else None},
             "gpu_launches": int(launches),
             "phases_ms": {"mask_draw": float(phases[0]), "fwd_bwd": float(phases[1]), "allreduce": float(phases[2]),
                           "clip_update": float(phases[3]), "note": "rank 0, 5 extra steps after the timed regions"},
+            "replica_max_abs_diff": replica_diff,
             "roofline": roofline,
-            "cpu_baseline": None if cb_tps is None else {
-                "value": cb_tps, "unit": "tokens/s", "cores": cb_threads, "kind": "port",
-                "sample": "%d host threads x 16 sequences x T=35 (of the 512-sequence batch), one fwd+bwd+update step at full "
-                          "model size, %.1f s; each thread is the reference's single-threaded CPU path on its shard" % (cb_threads, cb_sec)},
+            "cpu_baseline": cpu_rec,
+            "hbm_kernels": hbm,
             "device_error_flags": errs,
         }
         print(json.dumps(line), flush=True)
-    model.close()
+    if not closed[0]:
+        model.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -355,6 +433,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="dyb200", choices=["dyb200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-hbm-kernels", action="store_true", help="skip the per-kernel pass over the memory-bound kernels (N = 1 only)")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

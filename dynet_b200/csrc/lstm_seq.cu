@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[kSeqBufs], acc_empty[kSeqBufs], park_full, park_free;
-  __shared__ uint32_t tmem_base_slot, split_ok;
+  __shared__ uint32_t tmem_base_slot;
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   float* park = reinterpret_cast<float*>(ring + (size_t)STAGES * STAGE_BYTES);   // 64 columns x BM rows
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -128,11 +128,32 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
       const uint32_t per_step = gridDim.x * S;   // arrivals per column block and step: every CTA that writes a piece of h_t
       for (uint32_t t = 0; t < a.T && !fail; ++t) {
         const int brow = (int)(t * a.B + n0);
-        for (uint32_t it = 0; it < total; ++it) {
+        for (uint32_t it = 0; it < total;) {
           if (it == ks.n0 && t > 0) {
-            // first Wh h k-block of this step: the planes of h_{t-1} must be complete for this column block
+            // The Wh h share of this step needs the planes of h_{t-1}, complete for this column block.  The weight tiles
+            // of its first k-blocks do not: they are requested before the wait (a stage's barrier completes when both its
+            // weight and its activation tiles have arrived), so only the small activation tiles are still to come afterwards.
+            const uint32_t pre = min((uint32_t)STAGES, ks.n1);
+            uint32_t s2 = s, ph2 = ph;
+            for (uint32_t j = 0; j < pre && !fail; ++j) {
+              if (!mbar_wait(&empty_bar[s2], ph2 ^ 1)) { fail = true; break; }
+              unsigned char* st = ring + (size_t)s2 * STAGE_BYTES;
+              mbar_expect_tx(&full_bar[s2], STAGE_TX);
+              tma_load_2d(st, &tm.t[4], &full_bar[s2], (int)((ks.b1 + j) * BK), (int)m0);
+              tma_load_2d(st + TILE_BYTES, &tm.t[5], &full_bar[s2], (int)((ks.b1 + j) * BK), (int)m0);
+              if (++s2 == STAGES) { s2 = 0; ph2 ^= 1; }
+            }
+            if (fail) break;
             if (!wait_counter(a.ready + blockIdx.y, t * per_step)) { fail = true; break; }
             asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy stores of other CTAs -> this CTA's TMA reads
+            for (uint32_t j = 0; j < pre; ++j) {
+              unsigned char* st = ring + (size_t)s * STAGE_BYTES;
+              tma_load_2d(st + 2 * TILE_BYTES, &tm.t[6], &full_bar[s], (int)((ks.b1 + j) * BK), brow);
+              tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[7], &full_bar[s], (int)((ks.b1 + j) * BK), brow);
+              if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+            it += pre;
+            continue;
           }
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) { fail = true; break; }
           const uint32_t pair = it < ks.n0 ? 0 : 1, kblk = pair ? ks.b1 + (it - ks.n0) : ks.b0 + it;
@@ -143,6 +164,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
           tma_load_2d(st + 2 * TILE_BYTES, &tm.t[4 * pair + 2], &full_bar[s], (int)(kblk * BK), brow);
           tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), brow);
           if (++s == STAGES) { s = 0; ph ^= 1; }
+          ++it;
         }
       }
       if (fail) atomicOr(a.flags, DYB200_FLAG_WAIT_TIMEOUT);
@@ -252,43 +274,37 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
         ok = bar_and(1, 256, ok) != 0;
         const uint32_t nh = n0 + 64 * hh;
         if (S > 1) {
-          if (te == 0) {
-            split_ok = ok ? 1u : 0u;
-            for (uint32_t r = 0; r < S; ++r) mbar_arrive_remote(&park_full, r);   // (release: the parked tile and split_ok)
-          }
+          if (te < S) mbar_arrive_remote(&park_full, te);   // (release: this CTA's parked tile) one thread per destination
           const bool got = mbar_wait_cluster(&park_full, pf_phase);
           ok = bar_and(1, 256, ok && got) != 0;
-          // rank r finishes columns [c_lo, c_hi) of these 64: partial tiles added in split order, then the epilogue
+          // rank r finishes columns [c_lo, c_hi) of these 64: partial tiles added in split order, then the epilogue.  (A CTA
+          // whose waits ran out has raised the error flag; its tile is then meaningless, and so is the step.)
           const uint32_t w = ((64 + S - 1) / S + 7) & ~7u;
           const uint32_t c_lo = min(rank * w, 64u), c_hi = min(c_lo + w, 64u);
-          uint32_t all = ok ? 1u : 0u, base[8];
-          for (uint32_t r = 0; r < S; ++r) {
-            uint32_t ra, v;
-            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(&split_ok)), "r"(r));
-            asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(ra) : "memory");
-            all &= v;
-            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base[r & 7]) : "r"(smem_u32(park)), "r"(r));
-          }
-          if (all) {
+          if (ok) {
+            uint32_t base[8];
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r)
+              if (r < S) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base[r]) : "r"(smem_u32(park)), "r"(r));
             const uint32_t f_lo = c_lo * (BM / 4), f_hi = c_hi * (BM / 4);
             float4* t4 = reinterpret_cast<float4*>(park);
             for (uint32_t f = f_lo + te; f < f_hi; f += 256) {
-              float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (uint32_t r = 0; r < S; ++r) {
-                float4 pv;
-                asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                             : "=f"(pv.x), "=f"(pv.y), "=f"(pv.z), "=f"(pv.w) : "r"(base[r & 7] + 16u * f) : "memory");
-                if (r == 0) acc = pv;
-                else { acc.x += pv.x; acc.y += pv.y; acc.z += pv.z; acc.w += pv.w; }
-              }
+              float4 pv[8];
+#pragma unroll
+              for (uint32_t r = 0; r < 8; ++r)   // all partial tiles requested before the first add
+                if (r < S) asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                        : "=f"(pv[r].x), "=f"(pv[r].y), "=f"(pv[r].z), "=f"(pv[r].w) : "r"(base[r] + 16u * f));
+              float4 acc = pv[0];
+#pragma unroll
+              for (uint32_t r = 1; r < 8; ++r)
+                if (r < S) { acc.x += pv[r].x; acc.y += pv[r].y; acc.z += pv[r].z; acc.w += pv[r].w; }
               t4[f] = acc;
             }
           }
           bar_sync(1, 256);   // the pass below reads other threads' pieces
-          if (all) epilogue_pass<64, 256>(e, park, te, blockIdx.x, m0, nh, M, N, cp[hh], c_lo, c_hi);
-          else if (ok) { ok = false; if (te == 0) atomicOr(a.flags, DYB200_FLAG_WAIT_TIMEOUT); }
+          if (ok) epilogue_pass<64, 256>(e, park, te, blockIdx.x, m0, nh, M, N, cp[hh], c_lo, c_hi);
           bar_sync(1, 256);   // this CTA has read everything it needs from the other tiles
-          if (te == 0) for (uint32_t r = 0; r < S; ++r) mbar_arrive_remote(&park_free, r);
+          if (te < S) mbar_arrive_remote(&park_free, te);
           pf_phase ^= 1; pr_phase ^= 1;
         } else {
           if (ok) epilogue_pass<64, 256>(e, park, te, blockIdx.x, m0, nh, M, N, cp[hh]);
@@ -296,12 +312,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
         }
       }
       if (emit) {
-        // h_t .* mask_h is in global memory as far as this thread is concerned: make it visible to the TMA engines of the
-        // other CTAs, then count this CTA in
-        asm volatile("fence.proxy.async;" ::: "memory");
-        __threadfence();
-        bar_sync(1, 256);
-        if (te == 0) signal_counter(a.ready + blockIdx.y);
+        // Every epilogue thread has issued its stores of h_t .* mask_h (the barrier that ends the last pass).  One thread
+        // publishes them: the fences order all stores it has observed, through that barrier, before the counter update
+        // (cumulativity), for the generic and for the async proxy (the readers are TMA loads).
+        if (te == 0) {
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __threadfence();
+          signal_counter(a.ready + blockIdx.y);
+        }
       }
     }
     if (!ok && lane == 0) atomicOr(a.flags, DYB200_FLAG_WAIT_TIMEOUT);

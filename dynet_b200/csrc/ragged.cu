@@ -2,9 +2,11 @@
 // (parallel_accumulate).  The pointer/length tables live in device memory, exactly as
 // BatchedExecutionEngine uploads them (dynet/exec.cc:346-356, :398-408).
 //
-// Copy: one CTA per slice, 128-bit loads/stores when both ends are 16-byte aligned.
+// Copy: one warp per slice when the slices are short (the autobatch case: 128-1024 floats, where a CTA per slice would
+// leave most of its lanes without work), one CTA per slice otherwise; 128-bit loads/stores when both ends are 16-byte
+// aligned, up to four vectors per lane in flight.
 // Accumulate: slices are grouped by target pointer (in-CTA sort, <= 4096 slices per pass); one
-// CTA per distinct target adds that target's sources in ascending slice order, so slices that
+// warp (short slices) or CTA per distinct target adds that target's sources in ascending slice order, so slices that
 // share a target are summed deterministically and without atomics.
 #include "common.cuh"
 #include "sortseg.cuh"
@@ -30,6 +32,32 @@ __global__ void __launch_bounds__(kThreads) k_ragged_copy(int num_seqs, float* c
   }
 }
 
+// Short slices: warp w of the grid moves slices w, w + warps, ...  A lane owns the float4 pieces lane, lane + 32, ...
+constexpr int kWarpSliceMax = 4096;   // floats: up to this length a slice is one warp's work
+__global__ void __launch_bounds__(256) k_ragged_copy_warp(int num_seqs, float* const* __restrict__ src,
+                                                         float* const* __restrict__ trg, const size_t* __restrict__ len) {
+  dyb_grid_dep_sync();
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * 8;
+  for (int s = blockIdx.x * 8 + (threadIdx.x >> 5); s < num_seqs; s += warps) {
+    const float* a = src[s];
+    float* b = trg[s];
+    const size_t n = len[s];
+    if (aligned16(a) && aligned16(b)) {
+      const size_t n4 = n / 4;
+      size_t i = lane;
+      for (; i + 96 < n4; i += 128) {   // four vectors in flight
+        const float4 v0 = ld4_stream(a + 4 * i), v1 = ld4_stream(a + 4 * (i + 32)), v2 = ld4_stream(a + 4 * (i + 64)), v3 = ld4_stream(a + 4 * (i + 96));
+        st4(b + 4 * i, v0); st4(b + 4 * (i + 32), v1); st4(b + 4 * (i + 64), v2); st4(b + 4 * (i + 96), v3);
+      }
+      for (; i < n4; i += 32) st4(b + 4 * i, ld4_stream(a + 4 * i));
+      for (size_t j = 4 * n4 + lane; j < n; j += 32) b[j] = a[j];
+    } else {
+      for (size_t j = lane; j < n; j += 32) b[j] = a[j];
+    }
+  }
+}
+
 // key = (target address / 4) << 18 | slice index (slice index < 2^18 within a pass)
 __global__ void __launch_bounds__(kSortThreads) k_sort_targets(float* const* __restrict__ trg, uint32_t n, uint32_t base,
                                                               uint32_t* __restrict__ slice_sorted,
@@ -49,14 +77,18 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_targets(float* const* __r
   sort_and_segment(keys, scan, n, npow, 18, slice_sorted, group_sorted, seg_start, nseg);
 }
 
-__global__ void __launch_bounds__(kThreads) k_ragged_accumulate(float* const* __restrict__ src, float* const* __restrict__ trg,
-                                                               const size_t* __restrict__ len, uint32_t base,
-                                                               const uint32_t* __restrict__ slice_sorted,
-                                                               const uint32_t* __restrict__ seg_start,
-                                                               const uint32_t* __restrict__ nseg) {
+// One thread group (a CTA of kThreads threads, or a warp of a 256-thread CTA when WARP) per distinct target.
+template <bool WARP>
+__global__ void __launch_bounds__(WARP ? 256 : kThreads) k_ragged_accumulate(float* const* __restrict__ src, float* const* __restrict__ trg,
+                                                                            const size_t* __restrict__ len, uint32_t base,
+                                                                            const uint32_t* __restrict__ slice_sorted,
+                                                                            const uint32_t* __restrict__ seg_start,
+                                                                            const uint32_t* __restrict__ nseg) {
   dyb_grid_dep_sync();
   const uint32_t U = *nseg;
-  for (uint32_t u = blockIdx.x; u < U; u += gridDim.x) {
+  const uint32_t group = WARP ? blockIdx.x * 8 + (threadIdx.x >> 5) : blockIdx.x, groups = WARP ? gridDim.x * 8 : gridDim.x;
+  const uint32_t me = WARP ? (threadIdx.x & 31) : threadIdx.x, width = WARP ? 32 : kThreads;
+  for (uint32_t u = group; u < U; u += groups) {
     const uint32_t k0 = seg_start[u], k1 = seg_start[u + 1];
     float* t = trg[base + slice_sorted[k0]];
     size_t nmax = 0;
@@ -66,8 +98,22 @@ __global__ void __launch_bounds__(kThreads) k_ragged_accumulate(float* const* __
       nmax = max(nmax, len[s]);
       al = al && aligned16(src[s]) && (len[s] % 4 == 0);
     }
-    if (al) {
-      for (size_t i = threadIdx.x; i < nmax / 4; i += kThreads) {
+    if (al && k1 == k0 + 1) {
+      // the usual case, one source per target: two vectors per lane in flight
+      const float* a = src[base + slice_sorted[k0]];
+      const size_t n4 = nmax / 4;
+      size_t i = me;
+      for (; i + width < n4; i += 2 * width) {
+        const float4 o0 = ld4(t + 4 * i), o1 = ld4(t + 4 * (i + width)), v0 = ld4_stream(a + 4 * i), v1 = ld4_stream(a + 4 * (i + width));
+        st4(t + 4 * i, make_float4(o0.x + v0.x, o0.y + v0.y, o0.z + v0.z, o0.w + v0.w));
+        st4(t + 4 * (i + width), make_float4(o1.x + v1.x, o1.y + v1.y, o1.z + v1.z, o1.w + v1.w));
+      }
+      for (; i < n4; i += width) {
+        const float4 o = ld4(t + 4 * i), v = ld4_stream(a + 4 * i);
+        st4(t + 4 * i, make_float4(o.x + v.x, o.y + v.y, o.z + v.z, o.w + v.w));
+      }
+    } else if (al) {
+      for (size_t i = me; i < nmax / 4; i += width) {
         float4 acc = ld4(t + 4 * i);
         for (uint32_t k = k0; k < k1; ++k) {
           uint32_t s = base + slice_sorted[k];
@@ -79,7 +125,7 @@ __global__ void __launch_bounds__(kThreads) k_ragged_accumulate(float* const* __
         st4(t + 4 * i, acc);
       }
     } else {
-      for (size_t i = threadIdx.x; i < nmax; i += kThreads) {
+      for (size_t i = me; i < nmax; i += width) {
         float acc = t[i];
         for (uint32_t k = k0; k < k1; ++k) {
           uint32_t s = base + slice_sorted[k];
@@ -96,18 +142,20 @@ __global__ void __launch_bounds__(kThreads) k_ragged_accumulate(float* const* __
 extern "C" {
 
 int dyb200_parallel_memcpy(int num_seqs, int max_len, float** src, float** trg, size_t* len, dyb200_ctx* ctx) {
-  (void)max_len;
   DYB_CHECK_ARG(ctx, num_seqs >= 0, "parallel_memcpy: negative slice count");
   if (num_seqs == 0) return DYB200_OK;
   DYB_CHECK_ARG(ctx, src && trg && len, "parallel_memcpy: null table");
-  dyb_launch(k_ragged_copy, stream_grid(ctx, (size_t)num_seqs, 1, 16), kThreads, 0, ctx, num_seqs, src, trg, len);
+  // max_len (the longest slice, as the reference passes it, dynet/exec.cc:357) picks the work split
+  if (max_len > 0 && max_len <= kWarpSliceMax)
+    dyb_launch(k_ragged_copy_warp, stream_grid(ctx, (size_t)num_seqs, 8, 8), 256, 0, ctx, num_seqs, src, trg, len);
+  else
+    dyb_launch(k_ragged_copy, stream_grid(ctx, (size_t)num_seqs, 1, 16), kThreads, 0, ctx, num_seqs, src, trg, len);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
 
 int dyb200_parallel_accumulate(int num_seqs, int max_len, float** src, float** trg, size_t* len, dyb200_ctx* ctx) {
   { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
-  (void)max_len;
   DYB_CHECK_ARG(ctx, num_seqs >= 0, "parallel_accumulate: negative slice count");
   if (num_seqs == 0) return DYB200_OK;
   DYB_CHECK_ARG(ctx, src && trg && len, "parallel_accumulate: null table");
@@ -123,7 +171,10 @@ int dyb200_parallel_accumulate(int num_seqs, int max_len, float** src, float** t
     uint32_t* nseg = seg_start + n + 1;
     dyb_launch(k_sort_targets, 1, kSortThreads, 0, ctx, trg, n, base, slice_sorted, group_sorted, seg_start, nseg);
     DYB_LAUNCHED(ctx);
-    dyb_launch(k_ragged_accumulate, stream_grid(ctx, n, 1, 16), kThreads, 0, ctx, src, trg, len, base, slice_sorted, seg_start, nseg);
+    if (max_len > 0 && max_len <= kWarpSliceMax)
+      dyb_launch(k_ragged_accumulate<true>, stream_grid(ctx, n, 8, 8), 256, 0, ctx, src, trg, len, base, slice_sorted, seg_start, nseg);
+    else
+      dyb_launch(k_ragged_accumulate<false>, stream_grid(ctx, n, 1, 16), kThreads, 0, ctx, src, trg, len, base, slice_sorted, seg_start, nseg);
     DYB_LAUNCHED(ctx);
   }
   return DYB200_OK;

@@ -205,6 +205,26 @@ def build_cases(torch, ctx, small):
                            T(b["out"], [4 * Hh], Bb), T(b["c"], [Hh], Bb), T(b["hh"], [Hh], Bb))
     cases.append(Case("lstm_fwd_fused_gates_c_h_4096x512x2048", 0, mk_fused, fused_fwd, 10 ** 9))
     cases[-1].flops = fl_g
+    # a whole LSTM layer over T = 35 time steps in one call (layer 2 of config 4: I = H = 1024) at the per-GPU batches of 1 and
+    # 8 GPUs: one sequence-persistent kernel, or (--per-step) the 35 per-step products it replaces
+    Tt = 35 if not small else 4
+    for Bq in (512, 64):
+        def mk_seq(Bq=Bq):
+            sc = (6.0 / (4 * Hh + Ig)) ** 0.5
+            d = dict(x=torch.randn(Tt * Bq, Ig, device=dev), z=torch.zeros(Bq, Hh, device=dev),
+                     Wx=(torch.rand(Ig, 4 * Hh, device=dev) * 2 - 1) * sc, Wh=(torch.rand(Hh, 4 * Hh, device=dev) * 2 - 1) * sc,
+                     b=torch.zeros(4 * Hh, device=dev), mx=(torch.rand(Bq, Ig, device=dev) < 0.8).float() / 0.8,
+                     mh=(torch.rand(Bq, Hh, device=dev) < 0.8).float() / 0.8, gates=torch.empty(Tt * Bq, 4 * Hh, device=dev),
+                     c=torch.empty(Tt * Bq, Hh, device=dev), h=torch.empty(Tt * Bq, Hh, device=dev))
+            d["w"] = ctx.wgrad_create(4 * Hh, Ig, Hh, Tt * Bq)
+            return d
+        def seq_fwd(b, Bq=Bq):
+            ctx.lstm_seq_fwd(T(b["x"], [Ig], Tt * Bq), T(b["z"], [Hh], Bq), T(b["z"], [Hh], Bq), T(b["Wx"], [4 * Hh, Ig], 1),
+                             T(b["Wh"], [4 * Hh, Hh], 1), T(b["b"], [4 * Hh], 1), T(b["mx"], [Ig], Bq), T(b["mh"], [Hh], Bq), gat,
+                             T(b["gates"], [4 * Hh], Tt * Bq), T(b["c"], [Hh], Tt * Bq), T(b["h"], [Hh], Tt * Bq), b["w"], Tt)
+        cases.append(Case("lstm_seq_fwd_I1024_H1024_B%d_T%d" % (Bq, Tt), 0, mk_seq, seq_fwd, 10 ** 9))
+        cases[-1].flops = 2.0 * 4 * Hh * (Ig + Hh) * Bq * Tt
+
     # output layer of config 4 over all time steps: r = bias + R h, M = V = 10000, N = T*B = 17920, K = H = 1024
     Vv, TB = 10000, 17920
     def mk_aff():
@@ -231,6 +251,25 @@ def build_cases(torch, ctx, small):
                                      T(b["dR"], [Vv, Hh], 1), T(b["db"], [Vv], 1), T(b["dh"], [Hh], nB))
     cases.append(Case("softmax_output_bwd_fused_10000x%dx1024" % nB, 0, mk_outbwd, outbwd, 10 ** 9))
     cases[-1].flops = 4.0 * Vv * nB * Hh
+
+    # autobatch movers at the tagger's size (config 5): 2048 slices of 256 floats (one hidden state per token) gathered
+    # from ragged positions into a token-major matrix and scattered back with +=; and the same kernels on 65536 slices of
+    # 1024 floats, where the transfer (268 MB each way) is long enough to show what they sustain
+    for (nsl, ln, tag) in ([(2048, 256, "tagger_2048x256"), (65536, 1024, "65536x1024")] if not small else [(2048, 256, "tagger_2048x256")]):
+        def mk_ragged(nsl=nsl, ln=ln):
+            pool = torch.randn(2 * nsl, ln, device=dev)                 # slices sit at every other row (ragged source positions)
+            dense = torch.zeros(nsl, ln, device=dev)
+            perm = torch.randperm(nsl, device=dev)
+            src = (pool.data_ptr() + (2 * perm.to(torch.int64)) * (4 * ln))
+            trg = (dense.data_ptr() + torch.arange(nsl, device=dev, dtype=torch.int64) * (4 * ln))
+            lens = torch.full((nsl,), ln, dtype=torch.int64, device=dev)
+            return dict(pool=pool, dense=dense, src=src, trg=trg, lens=lens)
+        nb = 4 * nsl * ln
+        cases.append(Case("parallel_memcpy_" + tag, 2 * nb + 24 * nsl, mk_ragged,
+                          lambda b, nsl=nsl, ln=ln: ctx.parallel_memcpy(nsl, ln, b["src"].data_ptr(), b["trg"].data_ptr(), b["lens"].data_ptr()), 3 * nb))
+        # accumulate the other way round: dense rows added into the ragged positions (distinct targets, the autobatch case)
+        cases.append(Case("parallel_accumulate_" + tag, 3 * nb + 24 * nsl, mk_ragged,
+                          lambda b, nsl=nsl, ln=ln: ctx.parallel_accumulate(nsl, ln, b["trg"].data_ptr(), b["src"].data_ptr(), b["lens"].data_ptr()), 3 * nb))
 
     # trainer update rules over the config-4 parameter buffer (30.06 M floats)
     NP = 30_060_000 if not small else 1 << 20
@@ -263,15 +302,19 @@ def build_cases(torch, ctx, small):
     return cases
 
 
-def run(only=None, iters=20, small=False, out=None, graph_mode=True):
+def run(only=None, iters=20, small=False, out=None, graph_mode=True, quiet=False, device=0, skip_tensor_bound=False, per_step=False):
     import torch
     stream = torch.cuda.Stream()
-    ctx = capi.Context(0, stream.cuda_stream)
+    ctx = capi.Context(device, stream.cuda_stream)
+    if per_step:
+        ctx.sequence_kernels(False)
     ctx.param_cache(True)   # as in training: weight matrices are split once (during warm-up), not in every timed call
     peak, src = peaks()
     results = []
     for case in build_cases(torch, ctx, small):
         if only and only not in case.name:
+            continue
+        if skip_tensor_bound and getattr(case, "flops", None):
             continue
         nsets = max(2, min(24, int(np.ceil(2.0 * L2_BYTES / max(case.footprint, 1)))))
         if small or getattr(case, "flops", None):
@@ -310,10 +353,12 @@ def run(only=None, iters=20, small=False, out=None, graph_mode=True):
         if getattr(case, "flops", None):
             rec["useful_TFLOPs"] = case.flops / (ms * 1e-3) / 1e12   # whole call, operand packing included
         results.append(rec)
-        print(json.dumps(rec), flush=True)
+        if not quiet:
+            print(json.dumps(rec), flush=True)
         del sets, graph
         torch.cuda.empty_cache()
     assert ctx.device_errors() == 0
+    ctx.close()
     if out:
         with open(out, "w") as f:
             json.dump(results, f, indent=1)
@@ -327,5 +372,6 @@ if __name__ == "__main__":
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--out", default=None)
     ap.add_argument("--eager", action="store_true", help="no CUDA graph: plain launches (for profiler captures)")
+    ap.add_argument("--per-step", action="store_true", help="sequence entry points issue one call per time step (dyb200_ctx_sequence_kernels off)")
     a = ap.parse_args()
-    run(a.only, a.iters, a.small, a.out, graph_mode=not a.eager)
+    run(a.only, a.iters, a.small, a.out, graph_mode=not a.eager, per_step=a.per_step)
