@@ -187,11 +187,18 @@ __device__ __forceinline__ void st4_stream(float* p, float4 v) { __stcs(reinterp
 
 __device__ __forceinline__ float sigmoidf_dev(float x) { return 1.0f / (1.0f + expf(-x)); }
 // Gate non-linearities of the LSTM products.  They run in GEMM epilogues, 64 per thread with 8 warps per SM, where the
-// IEEE division and the accurate expf / tanhf made the epilogue take 11 us of a 56 us tile; ex2.approx and rcp.rn cut
+// IEEE division and the accurate expf / tanhf made the epilogue take 11 us of a 56 us tile; ex2.approx and rcp.approx cut
 // that.  Errors: sigmoid <= ~1.5e-6 relative for |x| <= 20; tanh <= 2.4e-7 absolute (1 - 2/(1 + e^2x) cancels near 0),
 // both far inside the 1e-4 class of LSTM states; the stand-alone Tanh / LogisticSigmoid nodes keep the accurate forms.
-__device__ __forceinline__ float gate_sigmoid(float x) { return __frcp_rn(1.0f + __expf(-x)); }
-__device__ __forceinline__ float gate_tanh(float x) { return 1.0f - 2.0f * __frcp_rn(1.0f + __expf(2.0f * x)); }
+// (rcp.approx: 1 ulp; the correctly rounded __frcp_rn is a ~20-instruction sequence that cost 2 - 3 us per time step in the
+// epilogues of the LSTM products, where 16 of these run per thread and column on the step's critical path)
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float gate_sigmoid(float x) { return rcp_approx(1.0f + __expf(-x)); }
+__device__ __forceinline__ float gate_tanh(float x) { return 1.0f - 2.0f * rcp_approx(1.0f + __expf(2.0f * x)); }
 // x = hi + lo with hi = tf32(x) and lo = tf32(x - hi): the two operand planes of the 3xTF32 products
 __device__ __forceinline__ void split_tf32(float v, float& hi, float& lo) {
   uint32_t h, l;

@@ -23,7 +23,7 @@ namespace {
 
 constexpr uint32_t kPollLimit = 1u << 22;      // polls of a global counter before a CTA gives up (~ seconds)
 constexpr uint32_t kSeqBufs = 4;               // TMEM accumulators (4 x 128 columns)
-constexpr int SMEM_SEQ_BYTES = SMEM_BYTES + BM * 64 * 4;   // operand ring + a 64-column parking buffer
+constexpr int SMEM_SEQ_BYTES = SMEM_BYTES + BM * 64 * 4;   // operand ring (3 x 64 KiB or 4 x 48 KiB) + a 64-column exchange buffer
 
 struct SeqFwd {
   uint32_t T, B, H;                 // time steps, batch columns per step, hidden units (M = 4H gate rows)
@@ -80,28 +80,33 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// grid = (4H / 128, B / BNT, S); with S > 1 the S CTAs of a tile are one thread-block cluster (1 x 1 x S).
-template <int BNT>
+// grid = (4H / 128, B / BNT, S); with S > 1 the S CTAs of a tile are one thread-block cluster (1 x 1 x S).  S (1, 2, 4 or 8) is
+// a template parameter so that the column exchange indexes registers statically.
+template <int BNT, uint32_t S>
 __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_constant__ TmapPack tm, const SeqFwd a) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // 64-column tiles need 48 KiB per stage, so the ring holds four of them: at 0.4 us per k-block three stages do not cover
+  // the latency of a tile fetch
+  constexpr int kStages = BNT == 64 ? 4 : 3;
+  constexpr int kStageBytes = 2 * TILE_BYTES + 2 * BNT * BK * 4;
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[kSeqBufs], acc_empty[kSeqBufs], park_full, park_free;
+  __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], acc_full[kSeqBufs], acc_empty[kSeqBufs], park_full, park_free;
   __shared__ uint32_t tmem_base_slot;
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* park = reinterpret_cast<float*>(ring + (size_t)STAGES * STAGE_BYTES);   // 64 columns x BM rows
+  float* park = reinterpret_cast<float*>(ring + (size_t)kStages * kStageBytes);   // 64 columns x BM rows
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int TILE_B_BYTES = BNT * BK * 4;
   constexpr int STAGE_TX = 2 * TILE_BYTES + 2 * TILE_B_BYTES;
-  const uint32_t S = gridDim.z, rank = blockIdx.z;
+  const uint32_t rank = blockIdx.z;
   const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * BNT;
   const KSplit ks = k_split(a.kb0, a.kb1, rank, S);
   const uint32_t total = ks.n0 + ks.n1;          // k-blocks of this CTA per time step
   const uint32_t M = 4 * a.H, N = a.B;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (uint32_t q = 0; q < kSeqBufs; ++q) { mbar_init(&acc_full[q], 1); mbar_init(&acc_empty[q], kEpiWarps); }
-    mbar_init(&park_full, S); mbar_init(&park_free, S);
+    mbar_init(&park_full, 4 * S); mbar_init(&park_free, S);   // arrivals: the 4 sending warps of every CTA / one per CTA
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -133,37 +138,37 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
             // The Wh h share of this step needs the planes of h_{t-1}, complete for this column block.  The weight tiles
             // of its first k-blocks do not: they are requested before the wait (a stage's barrier completes when both its
             // weight and its activation tiles have arrived), so only the small activation tiles are still to come afterwards.
-            const uint32_t pre = min((uint32_t)STAGES, ks.n1);
+            const uint32_t pre = min((uint32_t)kStages, ks.n1);
             uint32_t s2 = s, ph2 = ph;
             for (uint32_t j = 0; j < pre && !fail; ++j) {
               if (!mbar_wait(&empty_bar[s2], ph2 ^ 1)) { fail = true; break; }
-              unsigned char* st = ring + (size_t)s2 * STAGE_BYTES;
+              unsigned char* st = ring + (size_t)s2 * kStageBytes;
               mbar_expect_tx(&full_bar[s2], STAGE_TX);
               tma_load_2d(st, &tm.t[4], &full_bar[s2], (int)((ks.b1 + j) * BK), (int)m0);
               tma_load_2d(st + TILE_BYTES, &tm.t[5], &full_bar[s2], (int)((ks.b1 + j) * BK), (int)m0);
-              if (++s2 == STAGES) { s2 = 0; ph2 ^= 1; }
+              if (++s2 == kStages) { s2 = 0; ph2 ^= 1; }
             }
             if (fail) break;
             if (!wait_counter(a.ready + blockIdx.y, t * per_step)) { fail = true; break; }
-            asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy stores of other CTAs -> this CTA's TMA reads
+            asm volatile("fence.proxy.async.global;" ::: "memory");   // generic-proxy stores of other CTAs -> this CTA's TMA reads
             for (uint32_t j = 0; j < pre; ++j) {
-              unsigned char* st = ring + (size_t)s * STAGE_BYTES;
+              unsigned char* st = ring + (size_t)s * kStageBytes;
               tma_load_2d(st + 2 * TILE_BYTES, &tm.t[6], &full_bar[s], (int)((ks.b1 + j) * BK), brow);
               tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[7], &full_bar[s], (int)((ks.b1 + j) * BK), brow);
-              if (++s == STAGES) { s = 0; ph ^= 1; }
+              if (++s == kStages) { s = 0; ph ^= 1; }
             }
             it += pre;
             continue;
           }
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) { fail = true; break; }
           const uint32_t pair = it < ks.n0 ? 0 : 1, kblk = pair ? ks.b1 + (it - ks.n0) : ks.b0 + it;
-          unsigned char* st = ring + (size_t)s * STAGE_BYTES;
+          unsigned char* st = ring + (size_t)s * kStageBytes;
           mbar_expect_tx(&full_bar[s], STAGE_TX);
           tma_load_2d(st, &tm.t[4 * pair + 0], &full_bar[s], (int)(kblk * BK), (int)m0);
           tma_load_2d(st + TILE_BYTES, &tm.t[4 * pair + 1], &full_bar[s], (int)(kblk * BK), (int)m0);
           tma_load_2d(st + 2 * TILE_BYTES, &tm.t[4 * pair + 2], &full_bar[s], (int)(kblk * BK), brow);
           tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), brow);
-          if (++s == STAGES) { s = 0; ph ^= 1; }
+          if (++s == kStages) { s = 0; ph ^= 1; }
           ++it;
         }
       }
@@ -172,10 +177,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      uint64_t d_a_hi[STAGES], d_a_lo[STAGES], d_b_hi[STAGES], d_b_lo[STAGES];
+      uint64_t d_a_hi[kStages], d_a_lo[kStages], d_b_hi[kStages], d_b_lo[kStages];
 #pragma unroll
-      for (int q = 0; q < STAGES; ++q) {
-        const uint32_t base = smem_u32(ring + (size_t)q * STAGE_BYTES);
+      for (int q = 0; q < kStages; ++q) {
+        const uint32_t base = smem_u32(ring + (size_t)q * kStageBytes);
         d_a_hi[q] = umma_desc(base); d_a_lo[q] = umma_desc(base + TILE_BYTES);
         d_b_hi[q] = umma_desc(base + 2 * TILE_BYTES); d_b_lo[q] = umma_desc(base + 2 * TILE_BYTES + TILE_B_BYTES);
       }
@@ -190,16 +195,17 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
           }
           if (!mbar_wait(&full_bar[s], ph)) { fail = true; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          uint64_t a_hi, a_lo, b_hi, b_lo;
+          uint64_t a_hi, a_lo, b_hi, b_lo;   // select without dynamic register indexing
           if (s == 0) { a_hi = d_a_hi[0]; a_lo = d_a_lo[0]; b_hi = d_b_hi[0]; b_lo = d_b_lo[0]; }
           else if (s == 1) { a_hi = d_a_hi[1]; a_lo = d_a_lo[1]; b_hi = d_b_hi[1]; b_lo = d_b_lo[1]; }
-          else { a_hi = d_a_hi[2]; a_lo = d_a_lo[2]; b_hi = d_b_hi[2]; b_lo = d_b_lo[2]; }
+          else if (s == 2 || kStages == 3) { a_hi = d_a_hi[2]; a_lo = d_a_lo[2]; b_hi = d_b_hi[2]; b_lo = d_b_lo[2]; }
+          else { a_hi = d_a_hi[kStages - 1]; a_lo = d_a_lo[kStages - 1]; b_hi = d_b_hi[kStages - 1]; b_lo = d_b_lo[kStages - 1]; }
           issue_kblock(tmem_base + buf * BN, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk);
           umma_commit(&empty_bar[s]);
           const bool chunk_ends = in_chunk == kChunkKB - 1 || it == total - 1;
           if (chunk_ends) { umma_commit(&acc_full[buf]); in_chunk = 0; ++chunk; buf = chunk % kSeqBufs; }
           else ++in_chunk;
-          if (++s == STAGES) { s = 0; ph ^= 1; }
+          if (++s == kStages) { s = 0; ph ^= 1; }
         }
       }
       if (fail) atomicOr(a.flags, DYB200_FLAG_WAIT_TIMEOUT);
@@ -210,33 +216,54 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
     const uint32_t te = threadIdx.x - 64;
     const bool has_cols = 64 * half < BNT;
     const uint32_t nchunks = (total + kChunkKB - 1) / kChunkKB;
-    const uint32_t u = blockIdx.x * 32 + 4 * (te & 7);   // this thread's four hidden units in the cooperative pass
+    // In the cooperative pass over a finished 64-column half this thread owns hidden units [u, u + 4) (rows 32 q + l of the
+    // tile are gate q of unit 32 mt + l) for the columns te / 8 and te / 8 + 32 of that half.
+    const uint32_t l = 4 * (te & 7), u = blockIdx.x * 32 + l;
+    // The 64 columns of a half are finished by the S CTAs of the cluster, w columns each (S is a power of two here): rank r
+    // takes columns [r w, r w + w).  Every CTA sends its partial sums of those columns straight into rank r's exchange
+    // buffer (slot = sender's rank), so the owner adds S slots from its own shared memory - no remote loads, whose round
+    // trips would sit on the step's critical path.  Without a K split (S = 1) the buffer is simply the parked half tile.
+    constexpr uint32_t w = 64 / S;
+    const uint32_t c_lo = rank * w, c_hi = c_lo + w;
+    uint32_t peer[8];   // this CTA's exchange buffer as seen ... and the peers': shared::cluster addresses
+#pragma unroll
+    for (uint32_t r = 0; r < 8; ++r) {
+      peer[r] = smem_u32(park);
+      if (S > 1 && r < S) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[r]) : "r"(smem_u32(park)), "r"(r));
+    }
+    float4 bias[4];   // the same for every step
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      bias[q] = ld4(a.bias + (size_t)q * a.H + u);
+      if (q == 1) { bias[q].x += a.forget_bias; bias[q].y += a.forget_bias; bias[q].z += a.forget_bias; bias[q].w += a.forget_bias; }
+    }
     uint32_t cg = 0, pf_phase = 0, pr_phase = 0;
     bool ok = true;   // the same for all 256 epilogue threads after every bar_and below
-    GemmEpilogue e{};
-    e.mode = EPI_LSTM_CELL; e.ldc = M; e.bias = a.bias; e.H = a.H; e.forget_bias = a.forget_bias;
-    e.hn_pitch = a.hn_pitch; e.ht_pitch = a.ht_pitch; e.hmask = a.hmask; e.hmask_ld = a.hmask_ld; e.hmask_full = a.hmask_full;
     const size_t HB = (size_t)a.H * a.B;
 #pragma unroll 1
     for (uint32_t t = 0; t < a.T; ++t) {
-      e.C = a.gates + (size_t)t * 4 * HB;
-      e.c_prev = t ? a.cs + (size_t)(t - 1) * HB : a.c0;
-      e.c_out = a.cs + (size_t)t * HB;
-      e.h_out = a.hs + (size_t)t * HB;
+      float* const gates_t = a.gates + (size_t)t * 4 * HB;
+      const float* const c_prev = t ? a.cs + (size_t)(t - 1) * HB : a.c0;
+      float* const c_out = a.cs + (size_t)t * HB;
+      float* const h_out = a.hs + (size_t)t * HB;
       const bool emit = t + 1 < a.T;   // h_t is the next step's input
-      e.hn_hi = emit ? a.hn_hi + (size_t)(t + 1) * a.B * a.hn_pitch : nullptr;
-      e.hn_lo = emit ? a.hn_lo + (size_t)(t + 1) * a.B * a.hn_pitch : nullptr;
-      e.ht_hi = a.ht_hi + (size_t)(t + 1) * a.B;
-      e.ht_lo = a.ht_lo + (size_t)(t + 1) * a.B;
-      // previous cell states of the columns this thread finishes (written by this same thread one step earlier)
-      float4 cp[BNT / 64][4];
+      // h_t .* mask_h as operand planes of step t + 1: rows (t + 1) B .. of the gate product's planes, columns (t + 1) B .. of
+      // the transposed planes
+      float* const hn_hi = a.hn_hi + (size_t)(t + 1) * a.B * a.hn_pitch;
+      float* const hn_lo = a.hn_lo + (size_t)(t + 1) * a.B * a.hn_pitch;
+      float* const ht_hi = a.ht_hi + (size_t)(t + 1) * a.B;
+      float* const ht_lo = a.ht_lo + (size_t)(t + 1) * a.B;
+      // previous cell states and mask values of the columns this thread finishes (c_prev was written by this same thread one
+      // step earlier); fetched now, while the products of the step run
+      float4 cp[BNT / 64][2], hm[BNT / 64][2];
 #pragma unroll
       for (int hh = 0; hh < BNT / 64; ++hh)
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
-          const uint32_t n = n0 + 64 * hh + (te >> 3) + 32 * k;
-          cp[hh][k] = n < N ? ld4(e.c_prev + u + (size_t)a.H * n) : make_float4(0.f, 0.f, 0.f, 0.f);
-          cp[hh][k + 2] = make_float4(0.f, 0.f, 0.f, 0.f);
+          const uint32_t c = (te >> 3) + 32 * k, n = n0 + 64 * hh + c;
+          const bool mine = n < N && c >= c_lo && c < c_hi;
+          cp[hh][k] = mine ? ld4(c_prev + u + (size_t)a.H * n) : make_float4(0.f, 0.f, 0.f, 0.f);
+          hm[hh][k] = (mine && a.hmask) ? ld4(a.hmask + u + (a.hmask_full ? (size_t)a.hmask_ld * n : 0)) : make_float4(1.f, 1.f, 1.f, 1.f);
         }
       float sum[64];
 #pragma unroll
@@ -263,62 +290,95 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
       }
 #pragma unroll
       for (int hh = 0; hh < BNT / 64; ++hh) {
-        // the parking buffer is free once every CTA of the cluster has read its slice of the previous pass (S > 1), or
-        // once this CTA's own threads have left the previous pass (the barrier at its end)
+        // Every CTA's exchange buffer is free once its owner has read the previous pass: the owners say so on park_free
+        // (S > 1), or this CTA's own threads have left the previous pass (the barrier at its end).
         if (S > 1 && ok && !mbar_wait_cluster(&park_free, pr_phase ^ 1)) ok = false;
         if (half == (uint32_t)hh) {
-          float* col = park + quarter * 32 + lane;
+          // column q of this half goes to rank q / w, slot = this rank, as column q % w; 32 consecutive rows per warp store
+          const uint32_t row = quarter * 32 + lane;
 #pragma unroll
-          for (int q = 0; q < 64; ++q) col[(size_t)q * BM] = sum[q];
+          for (int q = 0; q < 64; ++q) {
+            const uint32_t dst = peer[(uint32_t)q / w] + 4u * (((rank * w + (uint32_t)q % w) * BM) + row);
+            if (S > 1) asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(sum[q]) : "memory");
+            else park[(size_t)q * BM + row] = sum[q];
+          }
         }
-        ok = bar_and(1, 256, ok) != 0;
-        const uint32_t nh = n0 + 64 * hh;
         if (S > 1) {
-          if (te < S) mbar_arrive_remote(&park_full, te);   // (release: this CTA's parked tile) one thread per destination
+          // each sending warp reports on its own: its lanes' stores are ordered before the arrivals by the warp barrier,
+          // so a receiver can start as soon as the 4 S sending warps of the cluster are through
+          if (half == (uint32_t)hh) {
+            __syncwarp();
+            if (lane < S) mbar_arrive_remote(&park_full, lane);   // (release at cluster scope)
+          }
           const bool got = mbar_wait_cluster(&park_full, pf_phase);
           ok = bar_and(1, 256, ok && got) != 0;
-          // rank r finishes columns [c_lo, c_hi) of these 64: partial tiles added in split order, then the epilogue.  (A CTA
-          // whose waits ran out has raised the error flag; its tile is then meaningless, and so is the step.)
-          const uint32_t w = ((64 + S - 1) / S + 7) & ~7u;
-          const uint32_t c_lo = min(rank * w, 64u), c_hi = min(c_lo + w, 64u);
-          if (ok) {
-            uint32_t base[8];
-#pragma unroll
-            for (uint32_t r = 0; r < 8; ++r)
-              if (r < S) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base[r]) : "r"(smem_u32(park)), "r"(r));
-            const uint32_t f_lo = c_lo * (BM / 4), f_hi = c_hi * (BM / 4);
-            float4* t4 = reinterpret_cast<float4*>(park);
-            for (uint32_t f = f_lo + te; f < f_hi; f += 256) {
-              float4 pv[8];
-#pragma unroll
-              for (uint32_t r = 0; r < 8; ++r)   // all partial tiles requested before the first add
-                if (r < S) asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                                        : "=f"(pv[r].x), "=f"(pv[r].y), "=f"(pv[r].z), "=f"(pv[r].w) : "r"(base[r] + 16u * f));
-              float4 acc = pv[0];
-#pragma unroll
-              for (uint32_t r = 1; r < 8; ++r)
-                if (r < S) { acc.x += pv[r].x; acc.y += pv[r].y; acc.z += pv[r].z; acc.w += pv[r].w; }
-              t4[f] = acc;
-            }
-          }
-          bar_sync(1, 256);   // the pass below reads other threads' pieces
-          if (ok) epilogue_pass<64, 256>(e, park, te, blockIdx.x, m0, nh, M, N, cp[hh], c_lo, c_hi);
-          bar_sync(1, 256);   // this CTA has read everything it needs from the other tiles
-          if (te < S) mbar_arrive_remote(&park_free, te);
           pf_phase ^= 1; pr_phase ^= 1;
         } else {
-          if (ok) epilogue_pass<64, 256>(e, park, te, blockIdx.x, m0, nh, M, N, cp[hh]);
-          bar_sync(1, 256);
+          ok = bar_and(1, 256, ok) != 0;
         }
-      }
-      if (emit) {
-        // Every epilogue thread has issued its stores of h_t .* mask_h (the barrier that ends the last pass).  One thread
-        // publishes them: the fences order all stores it has observed, through that barrier, before the counter update
-        // (cumulativity), for the generic and for the async proxy (the readers are TMA loads).
-        if (te == 0) {
-          asm volatile("fence.proxy.async;" ::: "memory");
-          __threadfence();
+        // ---- the LSTM epilogue on this CTA's columns of the half: the arithmetic of epilogue_pass (EPI_LSTM_CELL), the S
+        // partial sums added in split order, c / h / the operand planes of h.  The planes of h, which the next step waits for,
+        // go out first and are published before the other stores are issued.
+        const uint32_t nh = n0 + 64 * hh;
+        const bool last_pass = hh == BNT / 64 - 1;
+        float4 g[2][4], cn[2], hv[2], phi[2], plo[2];
+        bool live[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const uint32_t c = (te >> 3) + 32 * k, n = nh + c;
+          live[k] = ok && n < N && c >= c_lo && c < c_hi;
+          if (!live[k]) continue;
+          const float* col = park + (size_t)(c - c_lo) * BM + l;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float4 acc = ld4(col + 32 * q);
+#pragma unroll
+            for (uint32_t r = 1; r < 8; ++r)
+              if (r < S) { const float4 pv = ld4(col + (size_t)r * w * BM + 32 * q); acc.x += pv.x; acc.y += pv.y; acc.z += pv.z; acc.w += pv.w; }
+            const float4 x = make_float4(acc.x + bias[q].x, acc.y + bias[q].y, acc.z + bias[q].z, acc.w + bias[q].w);
+            g[k][q] = q == 3 ? make_float4(gate_tanh(x.x), gate_tanh(x.y), gate_tanh(x.z), gate_tanh(x.w))
+                             : make_float4(gate_sigmoid(x.x), gate_sigmoid(x.y), gate_sigmoid(x.z), gate_sigmoid(x.w));
+          }
+          const float4 cv = cp[hh][k];
+          cn[k] = make_float4(lstm_cell_c(g[k][0].x, g[k][3].x, g[k][1].x, cv.x), lstm_cell_c(g[k][0].y, g[k][3].y, g[k][1].y, cv.y),
+                              lstm_cell_c(g[k][0].z, g[k][3].z, g[k][1].z, cv.z), lstm_cell_c(g[k][0].w, g[k][3].w, g[k][1].w, cv.w));
+          hv[k] = make_float4(lstm_cell_h(g[k][2].x, cn[k].x), lstm_cell_h(g[k][2].y, cn[k].y), lstm_cell_h(g[k][2].z, cn[k].z), lstm_cell_h(g[k][2].w, cn[k].w));
+          if (emit) {
+            // h .* mask_h as the next step's operand planes (the values of epi_emit_h); the transposed copies for the
+            // weight-gradient product wait until the hand-over is out
+            const float4 mk = hm[hh][k];
+            const float4 hmk = a.hmask ? make_float4(hv[k].x * mk.x, hv[k].y * mk.y, hv[k].z * mk.z, hv[k].w * mk.w) : hv[k];
+            split_tf32(hmk.x, phi[k].x, plo[k].x); split_tf32(hmk.y, phi[k].y, plo[k].y);
+            split_tf32(hmk.z, phi[k].z, plo[k].z); split_tf32(hmk.w, phi[k].w, plo[k].w);
+            st4(hn_hi + (size_t)n * a.hn_pitch + u, phi[k]);
+            st4(hn_lo + (size_t)n * a.hn_pitch + u, plo[k]);
+          }
+        }
+        // all reads of the exchange buffer are done (the next pass may overwrite it) and, in the last pass, every thread has
+        // issued its stores of the operand planes
+        bar_sync(1, 256);
+        if (S > 1 && te < S) mbar_arrive_remote(&park_free, te);
+        if (last_pass && emit && te == 0) {
+          // One thread publishes: its release orders all stores it has observed, through the barrier, before the counter
+          // update (cumulativity), for the generic and for the async proxy (the readers are TMA loads).
+          asm volatile("fence.proxy.async.global;" ::: "memory");
           signal_counter(a.ready + blockIdx.y);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (!live[k]) continue;
+          const uint32_t n = nh + (te >> 3) + 32 * k;
+          if (emit) {
+            float* th = ht_hi + (size_t)u * a.ht_pitch + n;
+            float* tl = ht_lo + (size_t)u * a.ht_pitch + n;
+            th[0] = phi[k].x; th[a.ht_pitch] = phi[k].y; th[2 * (size_t)a.ht_pitch] = phi[k].z; th[3 * (size_t)a.ht_pitch] = phi[k].w;
+            tl[0] = plo[k].x; tl[a.ht_pitch] = plo[k].y; tl[2 * (size_t)a.ht_pitch] = plo[k].z; tl[3 * (size_t)a.ht_pitch] = plo[k].w;
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) st4(gates_t + (size_t)q * a.H + u + (size_t)M * n, g[k][q]);
+          const size_t ei = u + (size_t)a.H * n;
+          st4(c_out + ei, cn[k]);
+          st4(h_out + ei, hv[k]);
         }
       }
     }
@@ -339,8 +399,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
 namespace {
 
 // How many clusters of S CTAs of the sequence kernel fit on the GPU at once (remembered per context = per device).
-template <int BNT>
-int seq_clusters_that_fit(dyb200_ctx* ctx, uint32_t S) {
+template <int BNT, uint32_t S>
+int seq_clusters_that_fit(dyb200_ctx* ctx) {
   int& mc = ctx->seq_max_clusters[BNT == 64 ? 0 : 1][S];
   if (mc == 0) {
     cudaLaunchConfig_t cfg;
@@ -351,13 +411,13 @@ int seq_clusters_that_fit(dyb200_ctx* ctx, uint32_t S) {
     attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = S;
     cfg.attrs = attr; cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, k_lstm_seq_fwd<BNT>, &cfg) != cudaSuccess) { (void)cudaGetLastError(); n = -1; }
+    if (cudaOccupancyMaxActiveClusters(&n, k_lstm_seq_fwd<BNT, S>, &cfg) != cudaSuccess) { (void)cudaGetLastError(); n = -1; }
     mc = n > 0 ? n : -1;
   }
   return mc;
 }
 
-template <int BNT>
+template <int BNT, uint32_t S>
 int launch_seq_fwd(dyb200_ctx* ctx, const TmapPack& tm, const SeqFwd& a, dim3 grid, double flops, uint32_t K) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -377,7 +437,7 @@ int launch_seq_fwd(dyb200_ctx* ctx, const TmapPack& tm, const SeqFwd& a, dim3 gr
     attr[na].val.cooperative = 1;
     cfg.attrs = attr; cfg.numAttrs = na + 1;
     GemmProfScope scope(ctx, flops, 1, 4 * a.H, a.B * a.T, K, EPI_LSTM_CELL);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, k_lstm_seq_fwd<BNT>, tm, a);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, k_lstm_seq_fwd<BNT, S>, tm, a);
     if (e == cudaSuccess) { ctx->seq_coop = 1; ctx->launches++; return DYB200_OK; }
     (void)cudaGetLastError();
     if (ctx->seq_coop == 1) return dyb200_fail(ctx, DYB200_ECUDA, "sequence kernel launch failed: %s", cudaGetErrorString(e));
@@ -385,9 +445,43 @@ int launch_seq_fwd(dyb200_ctx* ctx, const TmapPack& tm, const SeqFwd& a, dim3 gr
   }
   cfg.attrs = attr; cfg.numAttrs = na;
   GemmProfScope scope(ctx, flops, 1, 4 * a.H, a.B * a.T, K, EPI_LSTM_CELL);
-  cudaLaunchKernelEx(&cfg, k_lstm_seq_fwd<BNT>, tm, a);
+  cudaLaunchKernelEx(&cfg, k_lstm_seq_fwd<BNT, S>, tm, a);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
+}
+
+// the (tile width, K splits) instantiations behind one switch
+enum SeqOp { SEQ_SET_SMEM, SEQ_FIT, SEQ_LAUNCH };
+template <int BNT, uint32_t S>
+int seq_fwd_do(SeqOp op, dyb200_ctx* ctx, const TmapPack* tm, const SeqFwd* a, dim3 grid, double flops, uint32_t K) {
+  if (op == SEQ_SET_SMEM) {
+    // (the shared-memory limit of the kernel has to be raised before its occupancy is asked for)
+    const uint32_t bit = (BNT == 64 ? 16u : 256u) << (S == 1 ? 0 : S == 2 ? 1 : S == 4 ? 2 : 3);
+    if (!(ctx->func_attr_done & bit)) {
+      DYB_CUDA(ctx, cudaFuncSetAttribute(k_lstm_seq_fwd<BNT, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_SEQ_BYTES));
+      ctx->func_attr_done |= bit;
+    }
+    return DYB200_OK;
+  }
+  if (op == SEQ_FIT) return seq_clusters_that_fit<BNT, S>(ctx);
+  return launch_seq_fwd<BNT, S>(ctx, *tm, *a, grid, flops, K);
+}
+int seq_fwd_dispatch(SeqOp op, uint32_t bn, uint32_t S, dyb200_ctx* ctx, const TmapPack* tm = nullptr, const SeqFwd* a = nullptr,
+                     dim3 grid = dim3(), double flops = 0, uint32_t K = 0) {
+  if (bn == 64) {
+    switch (S) {
+      case 1: return seq_fwd_do<64, 1>(op, ctx, tm, a, grid, flops, K);
+      case 2: return seq_fwd_do<64, 2>(op, ctx, tm, a, grid, flops, K);
+      case 4: return seq_fwd_do<64, 4>(op, ctx, tm, a, grid, flops, K);
+      default: return seq_fwd_do<64, 8>(op, ctx, tm, a, grid, flops, K);
+    }
+  }
+  switch (S) {
+    case 1: return seq_fwd_do<128, 1>(op, ctx, tm, a, grid, flops, K);
+    case 2: return seq_fwd_do<128, 2>(op, ctx, tm, a, grid, flops, K);
+    case 4: return seq_fwd_do<128, 4>(op, ctx, tm, a, grid, flops, K);
+    default: return seq_fwd_do<128, 8>(op, ctx, tm, a, grid, flops, K);
+  }
 }
 
 }  // namespace
@@ -425,23 +519,19 @@ int dyb200_vanilla_lstm_seq_fwd(const dyb200_tensor* x_all, const dyb200_tensor*
   uint32_t S = 1;
   SeqPlanes pl;
   if (persistent) {
-    // (the shared-memory limit of the kernel has to be raised before its occupancy is asked for)
-    const uint32_t bit = bn == 64 ? 16u : 32u;
-    if (!(ctx->func_attr_done & bit)) {
-      if (bn == 64) DYB_CUDA(ctx, cudaFuncSetAttribute(k_lstm_seq_fwd<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_SEQ_BYTES));
-      else DYB_CUDA(ctx, cudaFuncSetAttribute(k_lstm_seq_fwd<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_SEQ_BYTES));
-      ctx->func_attr_done |= bit;
-    }
     S = dyb200_tc_splits(ctx, G, B, kb_total);
     const uint32_t per = (kb_total + S - 1) / S;
     S = (kb_total + per - 1) / per;
     const uint32_t tiles = (G / BM) * (B / bn);
-    if (S > 8 || (S > 1 && !ctx->cluster_splitk)) persistent = false;
-    else if (S > 1) {
-      const int fit = bn == 64 ? seq_clusters_that_fit<64>(ctx, S) : seq_clusters_that_fit<128>(ctx, S);
-      persistent = fit > 0 && tiles <= (uint32_t)fit;
-    } else {
-      persistent = tiles <= (uint32_t)ctx->sm_count;   // one CTA per SM (225 KB of shared memory each)
+    if (S > 8 || (S & (S - 1)) != 0 || (S > 1 && !ctx->cluster_splitk)) persistent = false;   // (the column exchange wants a power of two)
+    else {
+      if ((rc = seq_fwd_dispatch(SEQ_SET_SMEM, bn, S, ctx))) return rc;
+      if (S > 1) {
+        const int fit = seq_fwd_dispatch(SEQ_FIT, bn, S, ctx);
+        persistent = fit > 0 && tiles <= (uint32_t)fit;
+      } else {
+        persistent = tiles <= (uint32_t)ctx->sm_count;   // one CTA per SM (225 KB of shared memory each)
+      }
     }
     if (B / bn > 32) persistent = false;                // one hand-over counter per column block
     if (persistent) persistent = dyb200_wgrad_seq_planes(deferred, T, B, &pl);
@@ -478,7 +568,7 @@ int dyb200_vanilla_lstm_seq_fwd(const dyb200_tensor* x_all, const dyb200_tensor*
     DYB_CUDA(ctx, cudaMemsetAsync(a.ready, 0, 32 * sizeof(uint32_t), ctx->stream));
     const dim3 grid(G / BM, B / bn, S);
     const double flops = 2.0 * G * (double)B * (I + H) * T;
-    rc = bn == 64 ? launch_seq_fwd<64>(ctx, tm, a, grid, flops, I + H) : launch_seq_fwd<128>(ctx, tm, a, grid, flops, I + H);
+    rc = seq_fwd_dispatch(SEQ_LAUNCH, bn, S, ctx, &tm, &a, grid, flops, I + H);
     if (rc) return rc;
     dyb200_wgrad_seq_done(deferred);
     return DYB200_OK;
