@@ -265,8 +265,8 @@ def run_gpu(args):
 
     def step(tokens):
         draw_masks()
-        model.launch_forward_backward(tokens, masks)
-        model.allreduce_grads()
+        # forward + backward; with several ranks the gradient buckets are summed on a side stream as they become final
+        model.launch_forward_backward_overlapped(tokens, masks)
         model.update()
 
     closed = [False]
@@ -325,18 +325,20 @@ def run_gpu(args):
         model.set_graph(True)
     phases = np.zeros(4)
     for k in range(5):
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
         ev[0].record(stream)
         draw_masks()
         ev[1].record(stream)
-        model.launch_forward_backward(dev_tokens[k % n_batches], masks)
+        model._after_last_phase = None
+        model.launch_forward_backward_overlapped(dev_tokens[k % n_batches], masks)
         ev[2].record(stream)
-        model.allreduce_grads()
-        ev[3].record(stream)
         model.update()
-        ev[4].record(stream)
+        ev[3].record(stream)
         torch.cuda.synchronize()
-        phases += [ev[q].elapsed_time(ev[q + 1]) for q in range(4)]
+        mid = model._after_last_phase           # recorded after the last backward phase, before the waits for the sums
+        fb = ev[1].elapsed_time(mid) if mid is not None else ev[1].elapsed_time(ev[2])
+        ar = mid.elapsed_time(ev[2]) if mid is not None else 0.0
+        phases += [ev[0].elapsed_time(ev[1]), fb, ar, ev[2].elapsed_time(ev[3])]
     phases /= 5
 
     # replicas must hold bit-identical parameters after the same number of updates (deterministic kernels, the same reduced
@@ -412,7 +414,10 @@ def run_gpu(args):
                     "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps, "last_loss": losses[-1] if losses else None},
             "gpu_launches": int(launches),
             "phases_ms": {"mask_draw": float(phases[0]), "fwd_bwd": float(phases[1]), "allreduce": float(phases[2]),
-                          "clip_update": float(phases[3]), "note": "rank 0, 5 extra steps after the timed regions"},
+                          "clip_update": float(phases[3]),
+                          "note": "rank 0, 5 extra steps after the timed regions; allreduce = what is left of the gradient sums after the "
+                                  "last backward phase (the buckets of the output layer and of the upper LSTM layers are reduced on a side "
+                                  "stream while the backward pass continues)"},
             "replica_max_abs_diff": replica_diff,
             "roofline": roofline,
             "cpu_baseline": cpu_rec,

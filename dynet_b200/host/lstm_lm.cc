@@ -79,12 +79,15 @@ struct Lm {
   // captured once and re-issued with one cudaGraphLaunch; inputs live at fixed addresses (tok, mask_buf).
   bool use_graph = false;
   bool time_major = false;               // fused driver: time step by time step (the reference's order) instead of layer by layer
-  cudaGraphExec_t graph_exec = nullptr;
+  std::vector<cudaGraphExec_t> graph_exec;   // [0]: the whole step; [1 + p]: phase p (see step_body)
   float* graph_loss = nullptr;
   uint64_t graph_launches = 0;
   std::vector<float*> mask_buf;          // 2L buffers: mask_x_l (I_l x B), mask_h_l (H x B)
+  void drop_graphs() {
+    for (auto& g : graph_exec) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
+  }
   ~Lm() {
-    if (graph_exec) cudaGraphExecDestroy(graph_exec);
+    drop_graphs();
     for (auto w : wg_layer) dyb200_wgrad_destroy(w);
   }
 };
@@ -134,7 +137,13 @@ size_t plan(const dyb200h_lm_config& c, Lm* m, char* base, size_t size) {
   } while (0)
 
 // Everything of a step after its inputs are in place (token ids in m.tok, masks at `masks`).
-void step_body(Lm& m, const float* const* masks, float* loss_dev) {
+// phase < 0: the whole step.  The fused layer-by-layer driver can also run it in L + 1 pieces, so that a data-parallel
+// caller can start reducing the gradients that are already final while the rest of the backward pass runs:
+//   phase 0      forward, loss, backward of the output layer   -> gradients of R and bias final
+//   phase p >= 1 backward of layer L - p over all time steps and its weight-gradient products -> that layer's gradients final
+//   phase L      also scatters the embedding gradients         -> gradients of the table final
+void step_body(Lm& m, const float* const* masks, float* loss_dev, int phase = -1) {
+  const bool do_fwd = phase <= 0;
   const dyb200h_lm_config& c = m.c;
   const uint32_t V = c.V, E = c.E, H = c.H, L = c.L, T = c.T, B = c.B;
   const size_t HB = (size_t)H * B, GB = 4 * HB, VB = (size_t)V * B, EB = (size_t)E * B;
@@ -145,7 +154,8 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   auto at = [T](uint32_t t, uint32_t l) { return (size_t)l * T + t; };
   // place the target ids where PickNegLogSoftmax expects them: aux = {z[n], m[n], ids[n]} with n = B per step,
   // or n = T*B when the output layer runs once over all time steps
-  if (c.fused)
+  if (!do_fwd) {}
+  else if (c.fused)
     CU(cudaMemcpyAsync(m.aux + 2 * (size_t)TB, m.tok + B, (size_t)TB * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st));
   else
     CU(cudaMemcpy2DAsync(m.aux + 2 * (size_t)B, 3 * (size_t)B * sizeof(float), m.tok + B, (size_t)B * sizeof(uint32_t),
@@ -178,7 +188,7 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   };
 
   // ---------------- forward ----------------
-  if (c.fused) {   // the T lookups read one table: one gather over the T*B ids
+  if (do_fwd && c.fused) {   // the T lookups read one table: one gather over the T*B ids
     LookupNode look(tC, nullptr, TB);
     look.aux_mem = m.tok;
     Tensor xall(Dim({E}, TB), m.x);
@@ -191,7 +201,8 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   // matters when the per-GPU batch is small and the products are bound by weight traffic.  Same values either way
   // (dyb200h_lm_set_time_major restores the reference's order).
   const bool layer_major = c.fused && !m.time_major;
-  if (layer_major) {
+  if (phase > 0 && !layer_major) throw std::invalid_argument("the step runs in phases only in the fused layer-by-layer driver");
+  if (do_fwd && layer_major) {
     // One call per layer: the inputs of a layer for all time steps are complete before it starts (embeddings, or the layer
     // below), so they are split into operand planes in one launch and the T steps run inside one kernel whose CTAs hand
     // h_t over on the device (dyb200_vanilla_lstm_seq_fwd; it makes the per-step calls itself when the shape does not allow that).
@@ -208,7 +219,7 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
                                                     &at, &cg, &cc, &ch, m.wg_layer[l], T, dev.ctx));
     }
   }
-  for (uint32_t t = 0; t < (layer_major ? 0u : T); ++t) {
+  for (uint32_t t = 0; t < ((layer_major || !do_fwd) ? 0u : T); ++t) {
     if (!c.fused) {
       LookupNode look(tC, nullptr, B);
       look.aux_mem = m.tok + (size_t)t * B;
@@ -248,19 +259,19 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   // H x (T*B) matrix of top-layer states (same values per column as the per-step nodes).
   Tensor hall(Dim({H}, TB), m.hs + at(0, L - 1) * HB), rall(Dim({V}, TB), m.r), eall(Dim({1}, TB), m.errs);
   const dyb200_affine_attrs R_is_param = {DYB200_GEMM_A_IS_PARAM};
-  if (c.fused) {
+  if (do_fwd && c.fused) {
     dyb200_tensor cxs[3] = {to_c(tbias), to_c(tR), to_c(hall)}, cr = to_c(rall);
     throw_status(dev, dyb200_affine_transform_fwd(cxs, 3, &cr, &R_is_param, nullptr, dev.ctx));
     pnls.dim = Dim({1}, TB);
     pnls.aux_mem = m.aux;
     pnls.forward_dev_impl(dev, {&rall}, eall);
   }
-  throw_status(dev, dyb200_sum_all(m.errs, (size_t)T * B, loss_dev, 0, dev.ctx));
+  if (do_fwd) throw_status(dev, dyb200_sum_all(m.errs, (size_t)T * B, loss_dev, 0, dev.ctx));
 
   // ---------------- backward ----------------
-  CU(cudaMemsetAsync(m.dact, 0, m.dact_bytes, st));
+  if (do_fwd) CU(cudaMemsetAsync(m.dact, 0, m.dact_bytes, st));
   Tensor tgR(Dim({V, H}), m.g[1 + 3 * L]), tgbias(Dim({V}), m.g[2 + 3 * L]);
-  if (c.fused) {
+  if (do_fwd && c.fused) {
     Tensor tones(Dim({1}, TB), m.ones), tdr(Dim({V}, TB), m.dr), tdhall(Dim({H}, TB), m.dh + at(0, L - 1) * HB);
     // PickNegLogSoftmax backward and the three AffineTransform backward calls (dbias += sum_columns dr, dR += dr h^T,
     // dh += R^T dr) in one: dr is written straight into the operand layouts of the two products
@@ -269,7 +280,8 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
     throw_status(dev, dyb200_softmax_output_bwd_fused(&cr, &ch, &cR, &cones, m.aux, &cgR, &cgb, &cdh, &cdr, DYB200_GEMM_A_IS_PARAM, dev.ctx));
   }
   Tensor tones(Dim({1}, B), m.ones);
-  for (uint32_t pass = 0; pass < (layer_major ? L : 1u); ++pass)
+  const uint32_t pass0 = phase < 0 ? 0u : (phase == 0 ? L : (uint32_t)phase - 1), pass1 = phase < 0 ? (layer_major ? L : 1u) : (phase == 0 ? L : (uint32_t)phase);
+  for (uint32_t pass = pass0; pass < pass1; ++pass) {
   for (uint32_t tt = T; tt-- > 0;) {
     if (!c.fused) {
       Tensor rt(Dim({V}, B), m.r + tt * VB), et(Dim({1}, B), m.errs + (size_t)tt * B), tdr(Dim({V}, B), m.dr);
@@ -325,11 +337,18 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
       gates_node.backward_dev_impl(dev, xs, tg, tdg, 4, gb);
     }
   }
+    // the deferred weight-gradient products of the layer whose reverse pass just ended: one per parameter matrix, K = T * B
+    if (layer_major) {
+      const uint32_t l = L - 1 - pass;
+      throw_status(dev, dyb200_wgrad_flush(m.wg_layer[l], m.g[1 + 3 * l], 4 * H, m.g[2 + 3 * l], 4 * H, dev.ctx));
+    }
+  }
+  if (phase >= 0 && (uint32_t)phase != L) return;
   Tensor tgC(Dim({E}, V), m.g[0]);
   if (c.fused) {
-    // the deferred weight-gradient products: one per parameter matrix, K = T * B
-    for (uint32_t l = 0; l < L; ++l)
-      throw_status(dev, dyb200_wgrad_flush(m.wg_layer[l], m.g[1 + 3 * l], 4 * H, m.g[2 + 3 * l], 4 * H, dev.ctx));
+    if (!layer_major)
+      for (uint32_t l = 0; l < L; ++l)
+        throw_status(dev, dyb200_wgrad_flush(m.wg_layer[l], m.g[1 + 3 * l], 4 * H, m.g[2 + 3 * l], 4 * H, dev.ctx));
     // All T lookups share the table, so their accumulate_grads calls fold into one over the T*B ids in time
     // order: each table row still receives its rows in the order of the per-step calls.
     LookupNode look(tC, nullptr, T * B);
@@ -346,12 +365,14 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev) {
   }
 }
 
-void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float* const* masks, float* loss_dev) {
+void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float* const* masks, float* loss_dev, int phase = -1) {
   const dyb200h_lm_config& c = m.c;
   cudaStream_t st = m.stream;
+  if (phase > (int)c.L) throw std::invalid_argument("phase out of range");
   if (c.dropout && !masks) throw std::invalid_argument("dropout is on but no masks were given");
-  CU(cudaMemcpyAsync(m.tok, tokens, (size_t)(c.T + 1) * c.B * sizeof(uint32_t), on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st));
-  if (!m.use_graph) { step_body(m, masks, loss_dev); return; }
+  if (phase <= 0)
+    CU(cudaMemcpyAsync(m.tok, tokens, (size_t)(c.T + 1) * c.B * sizeof(uint32_t), on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st));
+  if (!m.use_graph) { step_body(m, masks, loss_dev, phase); return; }
 
   // graph mode: masks are staged into the driver's own buffers so that the captured kernels see fixed addresses
   std::vector<const float*> fixed;
@@ -360,12 +381,14 @@ void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float*
       for (int k = 0; k < 2; ++k) {
         float* dst = m.mask_buf[2 * l + k];
         size_t n = (size_t)(k == 0 ? (l == 0 ? c.E : c.H) : c.H) * c.B;
-        if (masks[2 * l + k] != dst) CU(cudaMemcpyAsync(dst, masks[2 * l + k], n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+        if (phase <= 0 && masks[2 * l + k] != dst) CU(cudaMemcpyAsync(dst, masks[2 * l + k], n * sizeof(float), cudaMemcpyDeviceToDevice, st));
         fixed.push_back(dst);
       }
   }
-  if (m.graph_exec && m.graph_loss != loss_dev) { cudaGraphExecDestroy(m.graph_exec); m.graph_exec = nullptr; }
-  if (!m.graph_exec) {
+  if (m.graph_loss != loss_dev) m.drop_graphs();
+  if (m.graph_exec.size() < c.L + 2) m.graph_exec.resize(c.L + 2, nullptr);
+  cudaGraphExec_t& gexec = m.graph_exec[phase + 1];
+  if (!gexec) {
     if (st == nullptr) throw std::runtime_error("graph mode needs a non-default stream (the legacy stream cannot be captured)");
     uint64_t l0 = dyb200_ctx_launch_count(m.dev.ctx);
     // The launches that split the weights into operand planes are issued only when the parameter cache is stale, a
@@ -375,20 +398,21 @@ void forward_backward(Lm& m, const uint32_t* tokens, int on_device, const float*
     CU(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
     cudaGraph_t graph = nullptr;
     try {
-      step_body(m, c.dropout ? fixed.data() : nullptr, loss_dev);
+      step_body(m, c.dropout ? fixed.data() : nullptr, loss_dev, phase);
     } catch (...) {
       cudaStreamEndCapture(st, &graph);
       if (graph) cudaGraphDestroy(graph);
       throw;
     }
     CU(cudaStreamEndCapture(st, &graph));
-    cudaError_t e = cudaGraphInstantiate(&m.graph_exec, graph, 0);
+    cudaError_t e = cudaGraphInstantiate(&gexec, graph, 0);
     cudaGraphDestroy(graph);
     if (e != cudaSuccess) throw cuda_exception(std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
     m.graph_loss = loss_dev;
-    m.graph_launches = dyb200_ctx_launch_count(m.dev.ctx) - l0;
+    if (phase <= 0) m.graph_launches = 0;
+    m.graph_launches += dyb200_ctx_launch_count(m.dev.ctx) - l0;
   }
-  CU(cudaGraphLaunch(m.graph_exec, st));
+  CU(cudaGraphLaunch(gexec, st));
 }
 
 }  // namespace
@@ -457,17 +481,53 @@ static int guarded(Lm* m, void (*fn)(Lm&, void*), void* arg) {
   } catch (const std::exception& e) { m->err = e.what(); return DYB200_ERUNTIME; }
 }
 
-struct FbArgs { const uint32_t* tokens; int on_device; const float* const* masks; float* loss_dev; };
+struct FbArgs { const uint32_t* tokens; int on_device; const float* const* masks; float* loss_dev; int phase; };
 
 // tokens: (T+1) x B ids (host, or device when tokens_on_device); masks: 2L device pointers
 // {mask_x_0, mask_h_0, mask_x_1, ...} each I_l x B / H x B, or NULL when dropout is off;
 // loss_dev: device scalar that receives sum_batches(sum_t err_t).  Gradients accumulate into `grads`.
 int dyb200h_lm_forward_backward(void* h, const uint32_t* tokens, int tokens_on_device, const float* const* masks,
                                 float* loss_dev) {
-  FbArgs a{tokens, tokens_on_device, masks, loss_dev};
+  FbArgs a{tokens, tokens_on_device, masks, loss_dev, -1};
   return guarded((Lm*)h, [](Lm& m, void* p) {
     FbArgs* a = (FbArgs*)p;
-    forward_backward(m, a->tokens, a->on_device, a->masks, a->loss_dev);
+    forward_backward(m, a->tokens, a->on_device, a->masks, a->loss_dev, a->phase);
+  }, &a);
+}
+
+// The same step in pieces, for a data-parallel caller that reduces gradients while the backward pass still runs (fused
+// layer-by-layer driver only).  dyb200h_lm_num_phases returns L + 1, or 1 when the driver cannot split the step.  Call the
+// phases 0 .. L in order with the same arguments; after phase p the gradients of the tensors dyb200h_lm_phase_grad_range
+// names are final: phase 0 -> R and bias (the tail of the flat buffer), phase p (0 < p < L) -> Wx, Wh, b of layer L - p,
+// phase L -> the embedding table and layer 0 (the head of the buffer).  Results are those of dyb200h_lm_forward_backward.
+int dyb200h_lm_num_phases(void* h) {
+  Lm* m = (Lm*)h;
+  return (m->c.fused && !m->time_major) ? (int)m->c.L + 1 : 1;
+}
+int dyb200h_lm_phase_grad_range(void* h, int phase, size_t* offset, size_t* count) {
+  Lm* m = (Lm*)h;
+  const uint32_t L = m->c.L;
+  if (phase < 0 || phase > (int)L || !offset || !count) return DYB200_EINVAL;
+  std::vector<size_t> sz;
+  param_sizes(m->c, &sz);
+  std::vector<size_t> off(sz.size() + 1, 0);
+  for (size_t k = 0; k < sz.size(); ++k) off[k + 1] = off[k] + sz[k];
+  size_t first, last;   // tensor indices [first, last)
+  if (phase == 0) { first = 1 + 3 * L; last = 3 + 3 * L; }
+  else if ((uint32_t)phase == L) { first = 0; last = 4; }
+  else { first = 1 + 3 * (L - phase); last = first + 3; }
+  *offset = off[first];
+  *count = off[last] - off[first];
+  return DYB200_OK;
+}
+int dyb200h_lm_forward_backward_phase(void* h, int phase, const uint32_t* tokens, int tokens_on_device, const float* const* masks,
+                                      float* loss_dev) {
+  Lm* m = (Lm*)h;
+  if (phase < 0 || phase >= dyb200h_lm_num_phases(h)) { m->err = "phase out of range"; return DYB200_EINVAL; }
+  FbArgs a{tokens, tokens_on_device, masks, loss_dev, dyb200h_lm_num_phases(h) == 1 ? -1 : phase};
+  return guarded(m, [](Lm& mm, void* p) {
+    FbArgs* a = (FbArgs*)p;
+    forward_backward(mm, a->tokens, a->on_device, a->masks, a->loss_dev, a->phase);
   }, &a);
 }
 
@@ -496,7 +556,7 @@ int dyb200h_lm_update(void* h) {
 int dyb200h_lm_set_graph(void* h, int enable) {
   Lm* m = (Lm*)h;
   m->use_graph = enable != 0;
-  if (!enable && m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
+  if (!enable) m->drop_graphs();
   return DYB200_OK;
 }
 uint64_t dyb200h_lm_graph_launches(void* h) { return ((Lm*)h)->graph_launches; }
@@ -505,7 +565,7 @@ uint64_t dyb200h_lm_graph_launches(void* h) { return ((Lm*)h)->graph_launches; }
 int dyb200h_lm_set_time_major(void* h, int enable) {
   Lm* m = (Lm*)h;
   m->time_major = enable != 0;
-  if (m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
+  m->drop_graphs();
   return DYB200_OK;
 }
 // Device pointers of the 2L mask buffers the graph reads (write the masks there to avoid the staging copy).

@@ -42,6 +42,12 @@ def host_lib():
         L.dyb200h_lm_error.argtypes = [C.c_void_p]
         L.dyb200h_lm_forward_backward.restype = C.c_int
         L.dyb200h_lm_forward_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.c_void_p]
+        L.dyb200h_lm_num_phases.restype = C.c_int
+        L.dyb200h_lm_num_phases.argtypes = [C.c_void_p]
+        L.dyb200h_lm_phase_grad_range.restype = C.c_int
+        L.dyb200h_lm_phase_grad_range.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
+        L.dyb200h_lm_forward_backward_phase.restype = C.c_int
+        L.dyb200h_lm_forward_backward_phase.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.c_void_p]
         L.dyb200h_lm_grad_sumsq.restype = C.c_int
         L.dyb200h_lm_grad_sumsq.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
         L.dyb200h_lm_update.restype = C.c_int
@@ -169,6 +175,58 @@ class LstmLm:
         if masks_dev is not None:
             mp = (C.c_void_p * len(masks_dev))(*[m.data_ptr() for m in masks_dev])
         self._check(self.H.dyb200h_lm_forward_backward(self.h, ptr, on_dev, mp, self.loss_dev.data_ptr()))
+
+    def _token_ptr(self, tokens):
+        if isinstance(tokens, np.ndarray):
+            assert tokens.dtype == np.uint32 and tokens.flags["C_CONTIGUOUS"]
+            return tokens.ctypes.data, 0
+        return tokens.data_ptr(), 1 if tokens.is_cuda else 0
+
+    def num_phases(self):
+        return int(self.H.dyb200h_lm_num_phases(self.h))
+
+    def phase_grad_range(self, phase):
+        """(offset, count) in floats of the gradients that are final after `phase`."""
+        off, n = C.c_size_t(0), C.c_size_t(0)
+        self._check(self.H.dyb200h_lm_phase_grad_range(self.h, phase, C.byref(off), C.byref(n)))
+        return int(off.value), int(n.value)
+
+    def launch_phase(self, phase, tokens, masks_dev):
+        ptr, on_dev = self._token_ptr(tokens)
+        mp = None
+        if masks_dev is not None:
+            mp = (C.c_void_p * len(masks_dev))(*[m.data_ptr() for m in masks_dev])
+        self._check(self.H.dyb200h_lm_forward_backward_phase(self.h, phase, ptr, on_dev, mp, self.loss_dev.data_ptr()))
+
+    def launch_forward_backward_overlapped(self, tokens, masks_dev):
+        """Data-parallel step: forward + backward in phases; the gradients that a phase makes final (output layer first,
+        then the LSTM layers top down, the embedding table last) are summed over the ranks on a side stream while the next
+        phase runs.  The current stream waits for the sums at the end.  Same results as launch_forward_backward followed
+        by allreduce_grads (a sum per bucket instead of one over the whole buffer: the same additions per element)."""
+        import torch.distributed as dist
+        torch = self.torch
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+        n = self.num_phases()
+        if not multi or n == 1:
+            self.launch_forward_backward(tokens, masks_dev)
+            self.allreduce_grads()
+            return
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        main = torch.cuda.current_stream()
+        works = []
+        for p in range(n):
+            self.launch_phase(p, tokens, masks_dev)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            off, cnt = self.phase_grad_range(p)
+            with torch.cuda.stream(self._side):
+                self._side.wait_event(ev)
+                works.append(dist.all_reduce(self.grads[off:off + cnt], op=dist.ReduceOp.SUM, async_op=True))
+        self._after_last_phase = torch.cuda.Event(enable_timing=True)
+        self._after_last_phase.record(main)
+        for w in works:
+            w.wait()          # the current stream waits for the collective
 
     def forward_backward(self, tokens, masks=None):
         """Synchronous convenience wrapper used by the tests: returns the loss as a float."""

@@ -148,6 +148,47 @@ def test_lm_graph_captured_with_a_fresh_parameter_cache_sees_later_updates(oracl
         other.close()
 
 
+@pytest.mark.parametrize("graph", [False, True])
+def test_lm_step_in_phases_equals_the_whole_step(graph):
+    """The step split into L + 1 phases (forward + output layer, then one LSTM layer's backward pass each; what a data-parallel
+    caller uses to reduce finished gradient buckets early) gives bit for bit the loss and gradients of the one-call step, and
+    the gradient ranges the phases report tile the flat buffer."""
+    import torch
+    from dynet_b200 import lm
+    dims = dict(V=2000, E=256, H=256, L=2, T=4, B=64)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        model = lm.LstmLm(device=0, seed=31, dropout=True, stream=stream.cuda_stream, **dims)
+        tokens, masks = lm.synthetic_batch(dims, seed=32, dropout=0.2)
+        loss_whole = model.forward_backward(tokens, masks)
+        g_whole = model.grads_host()
+        model.grads.zero_()
+        n = model.num_phases()
+        assert n == dims["L"] + 1
+        ranges = sorted(model.phase_grad_range(p) for p in range(n))
+        assert ranges[0][0] == 0 and ranges[-1][0] + ranges[-1][1] == model.n_params
+        assert all(a[0] + a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+        model.set_graph(graph)
+        md = model.masks_to_device(masks)
+        for rep in range(2):                       # (graph: captured in the first round, replayed in the second)
+            model.grads.zero_()
+            final = {}
+            for p in range(n):
+                model.launch_phase(p, tokens, md)
+                off, cnt = model.phase_grad_range(p)
+                torch.cuda.synchronize()
+                final[p] = model.grads[off:off + cnt].clone()     # must not change in later phases
+            loss = float(model.loss_dev.item())
+            assert loss == loss_whole
+            for a, b in zip(model.grads_host(), g_whole):
+                assert np.array_equal(a, b)
+            for p in range(n):
+                off, cnt = model.phase_grad_range(p)
+                assert torch.equal(final[p], model.grads[off:off + cnt])
+        assert model.ctx.device_errors() == 0
+        model.close()
+
+
 @pytest.mark.parametrize("rule", ["momentum", "adam"])
 def test_lm_training_with_other_trainers(oracle, rule):
     """Three training steps with MomentumSGD / Adam: the gradients come from the LM driver, the clipped update from
