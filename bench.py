@@ -431,6 +431,182 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# Second workload (--workload tagger): the autobatched BiLSTM tagger, 2 048 ragged sentences per step.
+TAGGER = dict(V=20000, E=128, H=256, TH=32, NT=45, sentences=2048, lo=5, hi=100)
+TAGGER_METRIC = ("BiLSTM tagger training tokens/sec (autobatched: 2048 sentences of 5..100 words per step, V=20k E=128 H=256/direction, "
+                 "45 tags, fwd+bwd+allreduce+SGD)")
+
+
+def tagger_config(world):
+    c = dict(TAGGER)
+    c.update({"workload": "bilstm_tagger_autobatch_2048x5-100", "parallelism": "dp%d" % world, "sentences_per_gpu": TAGGER["sentences"] // world,
+              "l2": "per-step working set (~1.5 GB of step-major activations at one GPU) exceeds the 126 MB L2"})
+    return c
+
+
+def tagger_cpu_record(n_sent=96):
+    """The oracle runs the tagger as the reference's CPU build does: sentence by sentence, batch size 1, one thread."""
+    import oracle
+    from dynet_b200 import tagger as tg
+    oracle.build()
+    V, E, H, TH, NT = (TAGGER[k] for k in ("V", "E", "H", "TH", "NT"))
+    shapes = tg.param_shapes(V, E, H, TH, NT)
+    flat = tg.init_params(V, E, H, TH, NT, seed=1)
+    P = {n: a.reshape(cols, rows) if cols > 1 else a for n, a, (rows, cols) in zip(tg.NAMES, flat, shapes)}
+    lens, words, tags = tg.synthetic_corpus(TAGGER["sentences"], V, NT, seed=2000, lo=TAGGER["lo"], hi=TAGGER["hi"])
+    off = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    idx = np.linspace(0, len(lens) - 1, n_sent).astype(int)           # long, medium and short sentences
+    sents = [[int(v) for v in words[off[s]:off[s + 1]]] for s in idx]
+    tgs = [[int(v) for v in tags[off[s]:off[s + 1]]] for s in idx]
+    oracle.tagger_fwdbwd(P, sents[:1], tgs[:1])
+    t0 = time.perf_counter()
+    oracle.tagger_fwdbwd(P, sents, tgs)
+    sec = time.perf_counter() - t0
+    toks = sum(len(x) for x in sents)
+    return {"value": toks / sec, "unit": "tokens/s", "cores": 1, "kind": "port", "cpu_model": cpu_model(), "nproc": os.cpu_count() or 1,
+            "sample": "1 host thread, %d of the 2048 sentences (%d tokens), sentence by sentence at batch size 1 as the reference's CPU "
+                      "build runs this example, %.1f s" % (n_sent, toks, sec),
+            "note": "oracle port driven node by node from Python (the reference itself needs Eigen b2e267dc99d4, absent here)"}
+
+
+def run_tagger_reference(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    recs = [tagger_cpu_record() for _ in range(max(1, min(args.steps, 3)))]
+    rec = recs[-1]
+    tps = float(np.mean([r_["value"] for r_ in recs]))
+    rec["value"] = tps
+    world = max(1, args.gpus)
+    ntok = float(np.mean([sum(range(TAGGER["lo"], TAGGER["hi"] + 1)) / (TAGGER["hi"] - TAGGER["lo"] + 1)])) * TAGGER["sentences"]
+    print(json.dumps({"impl": "reference", "metric": TAGGER_METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": ntok / tps * 1e3, "higher_is_better": True, "scaling": "strong",
+                      "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": tagger_config(world),
+                      "ms_per_step_note": "the full 2048-sentence step extrapolated linearly from the sample", "cpu_baseline": rec,
+                      "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+
+
+def run_tagger_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from dynet_b200 import dp, tagger as tg
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback for this arm")
+    rank, world = dp.init_process_group("nccl") if int(os.environ.get("WORLD_SIZE", "1")) > 1 else (0, 1)
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    V, E, H, TH, NT = (TAGGER[k] for k in ("V", "E", "H", "TH", "NT"))
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    # synthetic corpus: a few batches of 2048 sentences; this rank takes every world-th sentence of the length-sorted batch
+    batches, total_tokens = [], []
+    for k in range(3):
+        lens, words, tags = tg.synthetic_corpus(TAGGER["sentences"], V, NT, seed=2000 + k, lo=TAGGER["lo"], hi=TAGGER["hi"])
+        off = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        mine = np.arange(rank, len(lens), world)
+        batches.append((np.ascontiguousarray(lens[mine]), np.ascontiguousarray(np.concatenate([words[off[i]:off[i + 1]] for i in mine])),
+                        np.ascontiguousarray(np.concatenate([tags[off[i]:off[i + 1]] for i in mine]))))
+        total_tokens.append(int(lens.sum()))
+    max_tok = max(int(b[0].sum()) for b in batches)
+    model = tg.Tagger(V, E, H, TH, NT, max_sentences=len(batches[0][0]), max_tokens=max_tok, max_len=TAGGER["hi"], device=local_rank,
+                      seed=1, lr=0.1, clip=5.0, stream=stream.cuda_stream)
+
+    def step(k, read_loss=False):
+        model.launch_forward_backward(*batches[k % len(batches)])
+        model.allreduce_grads()
+        model.update()
+        return float(model.loss_dev.item()) if read_loss else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(K, read_loss):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        toks, last = 0, None
+        for k in range(K):
+            last = step(k, read_loss)
+            toks += total_tokens[k % len(batches)]
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, toks, last
+
+    l0 = model.ctx.launches()
+    W = max(3, args.warmup)
+    for k in range(W):
+        step(k)
+    torch.cuda.synchronize()
+    launches_per_step = (model.ctx.launches() - l0) // W
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, toks, _ = timed(args.steps, read_loss=False)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e, toks_e2e, last_loss = timed(args.steps, read_loss=True)
+    # the ragged movers, bracketed by CUDA events on the launch stream in a few extra passes
+    model.time_movers(True)
+    mv = np.zeros(4)
+    host_ms = 0.0
+    reps = 3
+    for k in range(reps):
+        model.launch_forward_backward(*batches[k % len(batches)])
+        m4, hm = model.mover_ms()
+        mv += m4
+        host_ms += hm
+        model.grads.zero_()
+    model.time_movers(False)
+    mv /= reps
+    host_ms /= reps
+    errs = model.ctx.device_errors()
+    n_local = float(np.mean([int(b[0].sum()) for b in batches]))
+    replica_diff = 0.0
+    if world > 1:
+        ref = model.params.clone()
+        dist.broadcast(ref, src=0)
+        d = (model.params - ref).abs().max().reshape(1)
+        dist.all_reduce(d, op=dist.ReduceOp.MAX)
+        replica_diff = float(d.item())
+    if rank == 0:
+        peaks = measured_peaks()
+        slice_bytes = 4.0 * H * n_local
+        algo = 2 * (2 * slice_bytes) + 2 * (3 * slice_bytes)         # two copies (read + write), two accumulates (2 reads + write)
+        t_mv = float(mv.sum()) * 1e-3
+        achieved = algo / t_mv / 1e9 if t_mv > 0 else 0.0
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                    "traffic": None, "kernel": "k_ragged_copy_warp + k_sort_targets + k_ragged_accumulate (the autobatch movers)",
+                    "algorithmic_bytes": algo, "us": {"copy_fwd_dir": 1e3 * mv[0], "copy_bwd_dir": 1e3 * mv[1], "accumulate_fwd_dir": 1e3 * mv[2],
+                                                      "accumulate_bwd_dir": 1e3 * mv[3]},
+                    "note": "%d slices of %d floats per call (%.1f MB each way): the transfers are a few microseconds long, so launch "
+                            "latency and, for the accumulate, the sort of the target pointers bound them, not HBM; the same kernels on "
+                            "268 MB are in hbm_kernels of the LSTM-LM line" % (int(n_local), H, slice_bytes / 1e6),
+                    "peak_source": peaks["source"]}
+        cpu_rec = None if args.no_cpu_baseline else tagger_cpu_record()
+        tok_step = float(np.mean(total_tokens))
+        line = {"metric": TAGGER_METRIC, "value": toks / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": W,
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": tagger_config(world), "clocks": clocks,
+                "e2e": {"value": toks_e2e / (ms_e2e * 1e-3), "unit": "tokens/s",
+                        "h2d_bytes_per_step": int(world * n_local * (8 * 8 + 8 + 3 * 4)), "d2h_bytes_per_step": 4 * world,
+                        "ms_per_step": ms_e2e / args.steps, "last_loss": last_loss,
+                        "note": "every pass takes host arrays (lengths, word ids, tags): the pointer tables of the movers and the ids are "
+                                "built on the host and copied to the device inside the timed region in both figures; e2e also reads the loss back"},
+                "gpu_launches": int(launches_per_step * args.steps), "tokens_per_step": tok_step,
+                "host_schedule_ms_per_step": host_ms, "replica_max_abs_diff": replica_diff,
+                "roofline": roofline, "cpu_baseline": cpu_rec, "device_error_flags": errs}
+        print(json.dumps(line), flush=True)
+    model.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -440,8 +616,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-hbm-kernels", action="store_true", help="skip the per-kernel pass over the memory-bound kernels (N = 1 only)")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--workload", default="lm", choices=["lm", "tagger"],
+                    help="lm: the 2-layer LSTM language model the headline metric is quoted on; tagger: the autobatched BiLSTM tagger")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "tagger":
+        run_tagger_reference(args) if args.impl == "reference" else run_tagger_gpu(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

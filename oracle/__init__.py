@@ -413,6 +413,76 @@ def vanilla_lstm_builder_step(x, h_tm1, c_tm1, Wx, Wh, b, forget_bias=1.0):
     return h_t, c_t, dict(tmp=tmp, i=i_t, f=f_t, o=o_t, g=g_t, tanh_c=tc)
 
 
+# ---------------- BiLSTM tagger, sentence by sentence ----------------
+def _mat(a):
+    """(rows, cols) parameter stored column-major -> the oracle's (bd=1, cols, rows) view of the same memory."""
+    return a.reshape(1, a.shape[0], a.shape[1])
+
+
+def tagger_fwdbwd(P, sents, tags):
+    """The BiLSTM tagger of examples/tagger/train_tag-bilstm.cc:60-117 (without the input noise) the way the reference's CPU
+    build runs it: one sentence at a time, node oracle by node oracle, batch size 1.  P: dict of parameters (numpy arrays,
+    column-major tensors as (cols, rows)); sents / tags: lists of id lists.  Returns (summed loss, dict of gradients)."""
+    H = P["b_f"].size // 4
+    G = {k: np.zeros_like(v) for k, v in P.items()}
+    loss = 0.0
+    for sent, tg in zip(sents, tags):
+        n = len(sent)
+        states = {}
+        for d in ("f", "r"):
+            order = range(n) if d == "f" else range(n - 1, -1, -1)
+            h = c = np.zeros((1, H), np.float32)
+            for t in order:
+                x = lookup_fwd(P["emb"], np.array([sent[t]], np.uint32))
+                gates = lstm_gates_fwd([x], h, P["Wx_" + d], P["Wh_" + d], P["b_" + d])
+                c_new = lstm_c_fwd(c, gates)
+                h_new = lstm_h_fwd(c_new, gates)
+                states[(d, t)] = (x, h, c, gates, c_new, h_new)
+                h, c = h_new, c_new
+        dh_tok = {}
+        for t in range(n):
+            hf, hr = states[("f", t)][5], states[("r", t)][5]
+            xs1 = [P["thbias"].reshape(1, 1, -1), _mat(P["l2th"]), hf.reshape(1, 1, H), _mat(P["r2th"]), hr.reshape(1, 1, H)]
+            pre = affine_fwd(xs1)
+            th = unary_fwd("tanh", pre)
+            xs2 = [P["tbias"].reshape(1, 1, -1), _mat(P["th2t"]), th]
+            logits = affine_fwd(xs2)
+            ids = np.array([tg[t]], np.uint32)
+            l, z = pnls_fwd(logits.reshape(1, -1), ids)
+            loss += float(l[0])
+            dlog = pnls_bwd(logits.reshape(1, -1), ids, z, np.ones(1, np.float32), np.zeros((1, logits.size), np.float32))
+            dlog = dlog.reshape(logits.shape)
+            affine_bwd(xs2, dlog, 0, G["tbias"].reshape(1, 1, -1))
+            affine_bwd(xs2, dlog, 1, _mat(G["th2t"]))
+            dth = affine_bwd(xs2, dlog, 2, np.zeros_like(th))
+            dpre = unary_bwd("tanh", pre, th, dth, np.zeros_like(pre))
+            affine_bwd(xs1, dpre, 0, G["thbias"].reshape(1, 1, -1))
+            affine_bwd(xs1, dpre, 1, _mat(G["l2th"]))
+            affine_bwd(xs1, dpre, 3, _mat(G["r2th"]))
+            dh_tok[("f", t)] = affine_bwd(xs1, dpre, 2, np.zeros((1, 1, H), np.float32)).reshape(1, H)
+            dh_tok[("r", t)] = affine_bwd(xs1, dpre, 4, np.zeros((1, 1, H), np.float32)).reshape(1, H)
+        for d in ("f", "r"):
+            order = list(range(n)) if d == "f" else list(range(n - 1, -1, -1))
+            dh_c = np.zeros((1, H), np.float32)
+            dc_c = np.zeros((1, H), np.float32)
+            for t in reversed(order):
+                x, h_prev, c_prev, gates, c_new, h_new = states[(d, t)]
+                dh = dh_tok[(d, t)] + dh_c
+                dc = dc_c.copy()
+                lstm_h_bwd(c_new, gates, dh, 0, dc)
+                dg = np.zeros_like(gates)
+                lstm_h_bwd(c_new, gates, dh, 1, dg)
+                dc_c = lstm_c_bwd(c_prev, gates, dc, 0, np.zeros((1, H), np.float32))
+                lstm_c_bwd(c_prev, gates, dc, 1, dg)
+                dx = lstm_gates_bwd([x], h_prev, P["Wx_" + d], P["Wh_" + d], gates, dg, 0, np.zeros_like(x))
+                dh_c = lstm_gates_bwd([x], h_prev, P["Wx_" + d], P["Wh_" + d], gates, dg, 1, np.zeros((1, H), np.float32))
+                lstm_gates_bwd([x], h_prev, P["Wx_" + d], P["Wh_" + d], gates, dg, 2, G["Wx_" + d])
+                lstm_gates_bwd([x], h_prev, P["Wx_" + d], P["Wh_" + d], gates, dg, 3, G["Wh_" + d])
+                lstm_gates_bwd([x], h_prev, P["Wx_" + d], P["Wh_" + d], gates, dg, 4, G["b_" + d])
+                lookup_accumulate_grads(G["emb"], np.array([sent[t]], np.uint32), dx)
+    return loss, G
+
+
 # ---------------- LSTM language model step ----------------
 class LmDims(C.Structure):
     _fields_ = [(k, C.c_uint32) for k in ("V", "E", "H", "L", "T", "B")]

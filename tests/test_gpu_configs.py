@@ -85,10 +85,11 @@ def test_config1_builder_graph_pins_the_fused_chain(oracle, g, capi):
         ctx.fwd("vanilla_lstm_c", [g.T(cf), g.T(gates)], g.T(cn2))
         ctx.fwd("vanilla_lstm_h", [g.T(cn2), g.T(gates)], g.T(hn2))
         hf, cf = hn2, cn2
-        # The states are O(1); 1e-5 of 0.1 is the reach of the node kernels.  The fused chain forms the gate activations in
-        # the GEMM epilogue from ex2.approx / rcp (sigmoid good to 1.5e-6 relative), which puts an absolute 1 - 2e-6 on c and
-        # h: its states are held to 1e-5 of 0.25.
-        for name, got, floor in (("non-fused graph", (hu, cu), GEMM_FLOOR), ("fused chain", (hf, cf), 0.25)):
+        # The states are O(1) and every step adds its own rounding to the cell state it inherits: after a few steps the
+        # node kernels (expf / tanhf of the device against the oracle's libm and rational sigmoid) sit at ~1e-6 absolute,
+        # and the fused chain, whose gate activations come from ex2.approx / rcp.approx in the GEMM epilogue (sigmoid good to
+        # 1.5e-6 relative), at 1 - 2e-6: both are held to 1e-5 of 0.25.
+        for name, got, floor in (("non-fused graph", (hu, cu), 0.25), ("fused chain", (hf, cf), 0.25)):
             assert_close(g.host(got[0]), h_ref, 1e-5, floor=floor, what="h_%d, %s vs builder-graph oracle" % (t, name))
             assert_close(g.host(got[1]), c_ref, 1e-5, floor=floor, what="c_%d, %s vs builder-graph oracle" % (t, name))
     assert ctx.device_errors() == 0

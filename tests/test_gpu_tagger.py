@@ -35,71 +35,8 @@ def capi():
     return c
 
 
-def _mat(a):
-    """(rows, cols) parameter stored column-major -> the oracle's (bd=1, cols, rows) view of the same memory."""
-    return a.reshape(1, a.shape[0], a.shape[1])
-
-
 def oracle_tagger(oracle, P, sents, tags):
-    """Loss and gradients, one sentence at a time.  P: dict of parameters (numpy, column-major as (cols, rows))."""
-    H = P["b_f"].size // 4
-    G = {k: np.zeros_like(v) for k, v in P.items()}
-    loss = 0.0
-    for sent, tg in zip(sents, tags):
-        n = len(sent)
-        states = {}
-        for d in ("f", "r"):
-            order = range(n) if d == "f" else range(n - 1, -1, -1)
-            h = c = np.zeros((1, H), np.float32)
-            for t in order:
-                x = oracle.lookup_fwd(P["emb"], np.array([sent[t]], np.uint32))
-                gates = oracle.lstm_gates_fwd([x], h, P["Wx_" + d], P["Wh_" + d], P["b_" + d])
-                c_new = oracle.lstm_c_fwd(c, gates)
-                h_new = oracle.lstm_h_fwd(c_new, gates)
-                states[(d, t)] = (x, h, c, gates, c_new, h_new)
-                h, c = h_new, c_new
-        dh_tok = {}
-        for t in range(n):
-            hf, hr = states[("f", t)][5], states[("r", t)][5]
-            xs1 = [P["thbias"].reshape(1, 1, -1), _mat(P["l2th"]), hf.reshape(1, 1, H), _mat(P["r2th"]), hr.reshape(1, 1, H)]
-            pre = oracle.affine_fwd(xs1)
-            th = oracle.unary_fwd("tanh", pre)
-            xs2 = [P["tbias"].reshape(1, 1, -1), _mat(P["th2t"]), th]
-            logits = oracle.affine_fwd(xs2)
-            ids = np.array([tg[t]], np.uint32)
-            l, z = oracle.pnls_fwd(logits.reshape(1, -1), ids)
-            loss += float(l[0])
-            dlog = oracle.pnls_bwd(logits.reshape(1, -1), ids, z, np.ones(1, np.float32), np.zeros((1, logits.size), np.float32))
-            dlog = dlog.reshape(logits.shape)
-            oracle.affine_bwd(xs2, dlog, 0, G["tbias"].reshape(1, 1, -1))
-            oracle.affine_bwd(xs2, dlog, 1, _mat(G["th2t"]))
-            dth = oracle.affine_bwd(xs2, dlog, 2, np.zeros_like(th))
-            dpre = oracle.unary_bwd("tanh", pre, th, dth, np.zeros_like(pre))
-            oracle.affine_bwd(xs1, dpre, 0, G["thbias"].reshape(1, 1, -1))
-            oracle.affine_bwd(xs1, dpre, 1, _mat(G["l2th"]))
-            oracle.affine_bwd(xs1, dpre, 3, _mat(G["r2th"]))
-            dh_tok[("f", t)] = oracle.affine_bwd(xs1, dpre, 2, np.zeros((1, 1, H), np.float32)).reshape(1, H)
-            dh_tok[("r", t)] = oracle.affine_bwd(xs1, dpre, 4, np.zeros((1, 1, H), np.float32)).reshape(1, H)
-        for d in ("f", "r"):
-            order = list(range(n)) if d == "f" else list(range(n - 1, -1, -1))
-            dh_c = np.zeros((1, H), np.float32)
-            dc_c = np.zeros((1, H), np.float32)
-            for t in reversed(order):
-                x, h_prev, c_prev, gates, c_new, h_new = states[(d, t)]
-                dh = dh_tok[(d, t)] + dh_c
-                dc = dc_c.copy()
-                oracle.lstm_h_bwd(c_new, gates, dh, 0, dc)
-                dg = np.zeros_like(gates)
-                oracle.lstm_h_bwd(c_new, gates, dh, 1, dg)
-                dc_c = oracle.lstm_c_bwd(c_prev, gates, dc, 0, np.zeros((1, H), np.float32))
-                oracle.lstm_c_bwd(c_prev, gates, dc, 1, dg)
-                dx = oracle.lstm_gates_bwd([x], h_prev, P["Wx_" + d], P["Wh_" + d], gates, dg, 0, np.zeros_like(x))
-                dh_c = oracle.lstm_gates_bwd([x], h_prev, P["Wx_" + d], P["Wh_" + d], gates, dg, 1, np.zeros((1, H), np.float32))
-                oracle.lstm_gates_bwd([x], h_prev, P["Wx_" + d], P["Wh_" + d], gates, dg, 2, G["Wx_" + d])
-                oracle.lstm_gates_bwd([x], h_prev, P["Wx_" + d], P["Wh_" + d], gates, dg, 3, G["Wh_" + d])
-                oracle.lstm_gates_bwd([x], h_prev, P["Wx_" + d], P["Wh_" + d], gates, dg, 4, G["b_" + d])
-                oracle.lookup_accumulate_grads(G["emb"], np.array([sent[t]], np.uint32), dx)
-    return loss, G
+    return oracle.tagger_fwdbwd(P, sents, tags)
 
 
 def _tables(torch, ptrs_src, ptrs_trg, n, length):
@@ -233,3 +170,117 @@ def test_bilstm_tagger_autobatched_vs_per_sentence(oracle, g, capi, dims):
     assert abs(got_loss - want_loss) <= 1e-4 * abs(want_loss)
     for k in sorted(want):
         assert_close(got[k], want[k], TOL_REDUCE, floor=tagger_floor(k, want[k]), what="d" + k + " (per-row scale)")
+
+
+# ------------------------------------------------------------------ the C++ driver (host/tagger.cc)
+def _params(r, V, E, H, TH, NT):
+    P = {"emb": glorot(r, E, V)}
+    for d in ("f", "r"):
+        P["Wx_" + d], P["Wh_" + d], P["b_" + d] = glorot(r, 4 * H, E), glorot(r, 4 * H, H), randn(r, 4 * H, scale=0.1)
+    P["l2th"], P["r2th"], P["thbias"] = glorot(r, TH, H), glorot(r, TH, H), randn(r, TH, scale=0.1)
+    P["th2t"], P["tbias"] = glorot(r, NT, TH), randn(r, NT, scale=0.1)
+    return P
+
+
+def _driver(tg, P, dims, S, N, Lmax):
+    V, E, H, TH, NT = dims
+    return tg.Tagger(V, E, H, TH, NT, max_sentences=S, max_tokens=N, max_len=Lmax, device=0, params=[P[k] for k in tg.NAMES])
+
+
+def _split(lens, words, tags):
+    off = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    return ([[int(v) for v in words[off[s]:off[s + 1]]] for s in range(len(lens))],
+            [[int(v) for v in tags[off[s]:off[s + 1]]] for s in range(len(lens))])
+
+
+@pytest.mark.parametrize("dims,S,lo,hi", [((50, 16, 8, 6, 5), 7, 1, 6), ((2000, 128, 256, 32, 45), 48, 5, 30)])
+def test_tagger_driver_matches_per_sentence_oracle(oracle, dims, S, lo, hi):
+    """The C++ driver (autobatched schedule, deferred weight-gradient products, folded embedding scatter) against the oracle
+    running every sentence on its own: loss and all 12 gradient tensors, every row at its own scale.  Two passes in a row:
+    gradients accumulate, the second pass reuses every buffer."""
+    from dynet_b200 import tagger as tg
+    V, E, H, TH, NT = dims
+    r = rng(800 + S)
+    P = _params(r, V, E, H, TH, NT)
+    lens, words, tags = tg.synthetic_corpus(S, V, NT, seed=5 + S, lo=lo, hi=hi)
+    sents, tgs = _split(lens, words, tags)
+    want_loss, want = oracle.tagger_fwdbwd(P, sents, tgs)
+    m = _driver(tg, P, dims, S, int(lens.sum()), int(lens[0]))
+    loss = m.forward_backward(lens, words, tags)
+    got = m.grads_host()
+    assert abs(loss - want_loss) <= 1e-4 * abs(want_loss)
+    for k in sorted(want):
+        assert_close(got[k].reshape(want[k].shape), want[k], TOL_REDUCE, floor=tagger_floor(k, want[k]), what="d" + k + " (per-row scale)")
+    loss2 = m.forward_backward(lens, words, tags)          # accumulates: twice the gradient
+    assert loss2 == loss
+    got2 = m.grads_host()
+    for k in sorted(want):
+        assert_close(got2[k].reshape(want[k].shape), 2.0 * want[k], TOL_REDUCE, floor=2.0 * tagger_floor(k, want[k]), what="2 x d" + k)
+    assert m.ctx.device_errors() == 0
+    m.close()
+
+
+def test_tagger_driver_at_the_benchmark_size(oracle):
+    """2 048 sentences of 5 .. 100 words, V = 20 000, E = 128, H = 256, 45 tags in ONE pass (107 k tokens).  The oracle would
+    need minutes for that, so: (1) parity on a sample of 24 of the sentences run as their own mini-batch; (2) additivity,
+    which does not depend on the size: the loss and gradients of the full batch equal those of its even- plus its
+    odd-numbered sentences (each half still sorted by length), to the 1e-4 class."""
+    from dynet_b200 import tagger as tg
+    dims = (20000, 128, 256, 32, 45)
+    V, E, H, TH, NT = dims
+    S = 2048
+    r = rng(900)
+    P = _params(r, V, E, H, TH, NT)
+    lens, words, tags = tg.synthetic_corpus(S, V, NT, seed=77)
+    N, Lmax = int(lens.sum()), int(lens[0])
+    off = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+
+    def subset(idx):
+        idx = np.asarray(idx)
+        return (np.ascontiguousarray(lens[idx]), np.ascontiguousarray(np.concatenate([words[off[s]:off[s + 1]] for s in idx])),
+                np.ascontiguousarray(np.concatenate([tags[off[s]:off[s + 1]] for s in idx])))
+
+    m = _driver(tg, P, dims, S, N, Lmax)
+    loss_full = m.forward_backward(lens, words, tags)
+    g_full = m.grads_host()
+    assert m.ctx.device_errors() == 0
+    m.grads.zero_()
+    halves = [subset(np.arange(0, S, 2)), subset(np.arange(1, S, 2))]
+    loss_sum = sum(m.forward_backward(*h) for h in halves)          # gradients accumulate over the two passes
+    g_sum = m.grads_host()
+    assert abs(loss_full - loss_sum) <= 1e-4 * abs(loss_full)
+    for k in sorted(g_full):
+        shape = (-1, g_full[k].size) if g_full[k].ndim == 1 else g_full[k].shape
+        a, b = g_full[k].reshape(shape), g_sum[k].reshape(shape)
+        assert_close(a, b, TOL_REDUCE, floor=max(float(np.abs(b).max()) * 0.01, 1e-6), what="additivity of d" + k)
+    # parity on a sample
+    m.grads.zero_()
+    idx = np.sort(rng(901).choice(S, 24, replace=False))
+    sl, sw, st = subset(idx)
+    loss_s = m.forward_backward(sl, sw, st)
+    got = m.grads_host()
+    sents, tgs = _split(sl, sw, st)
+    want_loss, want = oracle.tagger_fwdbwd(P, sents, tgs)
+    assert abs(loss_s - want_loss) <= 1e-4 * abs(want_loss)
+    for k in sorted(want):
+        assert_close(got[k].reshape(want[k].shape), want[k], TOL_REDUCE, floor=tagger_floor(k, want[k]), what="sample: d" + k)
+    ms, host_ms = m.mover_ms()
+    assert m.ctx.device_errors() == 0
+    m.close()
+
+
+def test_tagger_driver_rejects_bad_input():
+    from dynet_b200 import capi, tagger as tg
+    dims = (50, 16, 8, 6, 5)
+    m = tg.Tagger(*dims, max_sentences=4, max_tokens=16, max_len=8, device=0, seed=1)
+    lens = np.array([2, 3], np.uint32)                                 # not sorted, longest first
+    words = np.zeros(5, np.uint32)
+    with pytest.raises(capi.InvalidArgument, match="sorted"):
+        m.launch_forward_backward(lens, words, words.copy())
+    lens = np.array([3, 2], np.uint32)
+    bad = words.copy(); bad[1] = 50
+    with pytest.raises(capi.InvalidArgument, match="Out-of-bounds"):
+        m.launch_forward_backward(lens, bad, words.copy())
+    with pytest.raises(capi.InvalidArgument, match="tokens"):
+        m.launch_forward_backward(np.array([8, 8, 8], np.uint32), np.zeros(24, np.uint32), np.zeros(24, np.uint32))
+    m.close()
