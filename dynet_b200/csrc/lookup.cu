@@ -220,11 +220,14 @@ __global__ void __launch_bounds__(256) k_segment_add(const float* __restrict__ g
 // ---- scatter-add, chunked (load-balanced) variant ------------------------------------------------
 constexpr uint32_t kChunk = 32;
 
-__global__ void __launch_bounds__(kSortThreads) k_sort_ids(const uint32_t* __restrict__ ids, uint32_t n, uint32_t base,
+// CTA p sorts the ids of pass p (positions [p kSortMax, ...)): the passes of a long id list are sorted side by side in one launch.
+__global__ void __launch_bounds__(kSortThreads) k_sort_ids(const uint32_t* __restrict__ ids, uint32_t n_total,
                                                           uint32_t vocab, uint32_t* __restrict__ pos_sorted,
                                                           uint32_t* __restrict__ id_at, uint32_t* flags) {
   dyb_grid_dep_sync();
   __shared__ unsigned long long keys[kSortMax];
+  const uint32_t base = blockIdx.x * kSortMax;
+  const uint32_t n = min((uint32_t)kSortMax, n_total - base);
   uint32_t npow = 1;
   while (npow < n) npow <<= 1;
   for (uint32_t k = threadIdx.x; k < npow; k += kSortThreads) {
@@ -239,8 +242,8 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_ids(const uint32_t* __res
   __syncthreads();
   bitonic_sort_keys(keys, npow);
   for (uint32_t k = threadIdx.x; k < n; k += kSortThreads) {
-    pos_sorted[k] = (uint32_t)keys[k];
-    id_at[k] = (uint32_t)(keys[k] >> 32);
+    pos_sorted[base + k] = (uint32_t)keys[k];
+    id_at[base + k] = (uint32_t)(keys[k] >> 32);
   }
 }
 
@@ -327,24 +330,31 @@ __global__ void __launch_bounds__(256) k_chunk_combine(float* __restrict__ all_g
 
 }  // namespace
 
-// Load-balanced path (rows that are multiples of 4 floats): scratch holds pos_sorted[np], id_at[np] and two
-// partial buffers of nchunks * slices * 128 floats.
-static size_t chunked_scratch_bytes(uint32_t np, uint32_t E) {
+// Load-balanced path (rows that are multiples of 4 floats): scratch holds pos_sorted[n], id_at[n] (all passes side by side) and
+// two partial buffers of nchunks * slices * 128 floats for one pass of at most kSortMax ids.
+static size_t chunked_scratch_bytes(uint32_t n, uint32_t E) {
+  const uint32_t np = n < (uint32_t)kSortMax ? n : (uint32_t)kSortMax;
   uint32_t nchunks = (np + kChunk - 1) / kChunk, slices = (E + 127) / 128;
-  return ((size_t)2 * np * sizeof(uint32_t) + 512) + (size_t)2 * nchunks * slices * 128 * sizeof(float) + 512;
+  return ((size_t)2 * n * sizeof(uint32_t) + 512) + (size_t)2 * nchunks * slices * 128 * sizeof(float) + 512;
 }
 static int scatter_run_chunked(dyb200_ctx* ctx, unsigned n, const unsigned* ids_dev, const float* g, float* all_grads,
                                unsigned E, unsigned vocab, void* scratch) {
   const uint32_t slices = (E + 127) / 128;
+  const uint32_t npass = (n + kSortMax - 1) / kSortMax;
+  uint32_t* pos_all = (uint32_t*)scratch;
+  uint32_t* id_all = pos_all + n;
+  const uint32_t np_max = n < (uint32_t)kSortMax ? n : (uint32_t)kSortMax;
+  float* head = (float*)(((uintptr_t)(id_all + n) + 255) & ~(uintptr_t)255);
+  float* tail = head + (size_t)((np_max + kChunk - 1) / kChunk) * slices * 128;
+  // every pass's ids are sorted in the same launch (one CTA each); the adds then run pass after pass, so that a table row
+  // that several passes touch receives their sums in pass order
+  dyb_launch(k_sort_ids, npass, kSortThreads, 0, ctx, ids_dev, n, vocab, pos_all, id_all, ctx->dev_flags);
+  DYB_LAUNCHED(ctx);
   for (uint32_t base = 0; base < n; base += kSortMax) {
     uint32_t np = n - base < (uint32_t)kSortMax ? n - base : (uint32_t)kSortMax;
     uint32_t nchunks = (np + kChunk - 1) / kChunk;
-    uint32_t* pos_sorted = (uint32_t*)scratch;
-    uint32_t* id_at = pos_sorted + np;
-    float* head = (float*)(((uintptr_t)(id_at + np) + 255) & ~(uintptr_t)255);
-    float* tail = head + (size_t)nchunks * slices * 128;
-    dyb_launch(k_sort_ids, 1, kSortThreads, 0, ctx, ids_dev, np, base, vocab, pos_sorted, id_at, ctx->dev_flags);
-    DYB_LAUNCHED(ctx);
+    uint32_t* pos_sorted = pos_all + base;
+    uint32_t* id_at = id_all + base;
     size_t work = (size_t)nchunks * slices;
     dyb_launch(k_chunk_add, stream_grid(ctx, work, 8), 256, 0, ctx, g, all_grads, E, pos_sorted, id_at, np, slices, head, tail);
     DYB_LAUNCHED(ctx);
@@ -469,7 +479,7 @@ int dyb200_lookup_accumulate_grads(unsigned n, const unsigned* ids_host, const u
   uint32_t np = n < (unsigned)kSortMax ? n : (unsigned)kSortMax;
   void* scratch;
   if (dim_size % 4 == 0 && aligned16(g) && aligned16(all_grads)) {
-    int rc = dyb200_scratch(ctx, chunked_scratch_bytes(np, dim_size), &scratch);
+    int rc = dyb200_scratch(ctx, chunked_scratch_bytes(n, dim_size), &scratch);
     if (rc) return rc;
     return scatter_run_chunked(ctx, n, ids_dev, g, all_grads, dim_size, vocab, scratch);
   }
