@@ -119,6 +119,9 @@ int dyb200_ctx_cluster_splitk(dyb200_ctx* ctx, int enable) {
 int dyb200_ctx_sequence_kernels(dyb200_ctx* ctx, int enable) {
   if (!ctx) return DYB200_EINVAL;
   ctx->seq_kernels = enable ? 1 : 0;
+  // enable == 2: launch them without the cooperative attribute (for tools that cannot replay cooperative launches; the
+  // grid still never exceeds what the GPU holds at once, and every wait in the kernels is bounded)
+  ctx->seq_coop = enable == 2 ? -1 : 0;
   return DYB200_OK;
 }
 

@@ -1009,8 +1009,10 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
 }
 
 bool dyb200_tc_eligible(uint32_t M, uint32_t N, double flops) {
-  // Small products stay on the CUDA-core kernel: packing + a 128x128 tile would mostly move padding.
-  return !(flops < 8.0e6 || M < 64 || (M + BM - 1) / BM > 65535u || (N + BN - 1) / BN > 65535u);
+  // Small products stay on the CUDA-core kernel: packing + a 128x128 tile would mostly move padding.  A product with few
+  // rows but many columns or a long reduction (the tag layer of a tagger: 32 or 45 rows times 100 000 tokens) is still far
+  // better off here - most of a tile's rows are padding, but the work is bound by reading the long operand once.
+  return !(flops < 8.0e6 || M < 16 || (M + BM - 1) / BM > 65535u || (N + BN - 1) / BN > 65535u);
 }
 
 int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const GemmPair* pairs, const GemmEpilogue& epi,

@@ -230,12 +230,14 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __rest
 #pragma unroll
   for (int half = 0; half < kCols; ++half) {
     const uint32_t bl = tb + kLanes * half, b = b0 + bl;
-    const size_t e = (size_t)b * H + j;
-    const float* g = gates + (size_t)b * 4 * H + j;
-    const float4 gi = ld4(g), gf = ld4(g + H), go = ld4(g + 2 * H), gg = ld4(g + 3 * H);
-    const float4 c = ld4(c_t + e), cp = ld4(c_tm1 + e), dh = ld4(dEdh + e);
-    const float4 dcin = dEdc ? ld4(dEdc + e) : make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 dcp = dc_tm1 ? ld4(dc_tm1 + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const bool live = b < B;   // (the last tile of a batch that is not a multiple of 32 columns: zeros in, nothing out)
+    const size_t e = (size_t)(live ? b : 0) * H + j;
+    const float* g = gates + (size_t)(live ? b : 0) * 4 * H + j;
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 gi = live ? ld4(g) : z4, gf = live ? ld4(g + H) : z4, go = live ? ld4(g + 2 * H) : z4, gg = live ? ld4(g + 3 * H) : z4;
+    const float4 c = live ? ld4(c_t + e) : z4, cp = live ? ld4(c_tm1 + e) : z4, dh = live ? ld4(dEdh + e) : z4;
+    const float4 dcin = (dEdc && live) ? ld4(dEdc + e) : z4;
+    float4 dcp = (dc_tm1 && live) ? ld4(dc_tm1 + e) : z4;
     float pi[4], pf[4], po[4], pg[4];
     const float gi_[4] = {gi.x, gi.y, gi.z, gi.w}, gf_[4] = {gf.x, gf.y, gf.z, gf.w}, go_[4] = {go.x, go.y, go.z, go.w},
                 gg_[4] = {gg.x, gg.y, gg.z, gg.w}, c_[4] = {c.x, c.y, c.z, c.w}, cp_[4] = {cp.x, cp.y, cp.z, cp.w},
@@ -254,13 +256,13 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __rest
       tile[0][4 * tq + q][bl] = pi[q]; tile[1][4 * tq + q][bl] = pf[q];
       tile[2][4 * tq + q][bl] = po[q]; tile[3][4 * tq + q][bl] = pg[q];
     }
-    if (dc_tm1) st4(dc_tm1 + e, make_float4(dcp_[0], dcp_[1], dcp_[2], dcp_[3]));
-    if (dpre) {
+    if (dc_tm1 && live) st4(dc_tm1 + e, make_float4(dcp_[0], dcp_[1], dcp_[2], dcp_[3]));
+    if (dpre && live) {
       float* o = dpre + (size_t)b * 4 * H + j;
       st4(o, make_float4(pi[0], pi[1], pi[2], pi[3])); st4(o + H, make_float4(pf[0], pf[1], pf[2], pf[3]));
       st4(o + 2 * H, make_float4(po[0], po[1], po[2], po[3])); st4(o + 3 * H, make_float4(pg[0], pg[1], pg[2], pg[3]));
     }
-    if (dn_hi) {
+    if (dn_hi && live) {
       const size_t o = (size_t)b * dn_pitch + j;
       float hi[4], lo[4];
 #pragma unroll
@@ -284,7 +286,7 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __rest
     const uint32_t gate = r / JT, jl = r % JT;
     const float v = tile[gate][jl][lane];
     const size_t row = (size_t)gate * H + j0 + jl;
-    if (dt_hi) {
+    if (dt_hi && b0 + lane < B) {
       float hi, lo;
       split_tf32(v, hi, lo);
       dt_hi[row * dt_pitch + b0 + lane] = hi;
@@ -640,9 +642,10 @@ int dyb200_vanilla_lstm_bwd_fused_at(const dyb200_tensor* x, const dyb200_tensor
   dyb200_tc_pack_begin(&batch);
   PackedOp dn, dt, wxT, whT, xt, ht;
   // Bandwidth-shaped pass for whole tiles: it writes the split planes of the gate gradient itself.
-  const bool tiled = tensor_path && H % kCT_J == 0 && B % kCT_B == 0 && H / kCT_J <= DYB200_DEV_COUNTERS && aligned16(c_t->v) &&
+  // (any batch size: the last 32-column tile may be partly filled; any column position in the accumulator)
+  const bool tiled = tensor_path && H % kCT_J == 0 && H / kCT_J <= DYB200_DEV_COUNTERS && aligned16(c_t->v) &&
                      aligned16(c_tm1->v) && aligned16(gates->v) && aligned16(dEdh->v) && (!dEdc || aligned16(dEdc->v)) &&
-                     (!dc_tm1 || aligned16(dc_tm1->v)) && (!deferred || (at_col ? deferred_col : dyb200_wgrad_fill(deferred)) % 32 == 0);
+                     (!dc_tm1 || aligned16(dc_tm1->v));
   float* dpre = nullptr;
   if (tiled) {
     if ((rc = dyb200_tc_planes(ctx, B, G, &dn))) return rc;
@@ -658,15 +661,16 @@ int dyb200_vanilla_lstm_bwd_fused_at(const dyb200_tensor* x, const dyb200_tensor
       a_hi = dt.hi; a_lo = dt.lo; a_pitch = dt.pitch;
     }
     void* pp;
-    if ((rc = dyb200_scratch(ctx, (size_t)(B / kCT_B) * G * sizeof(float), &pp))) return rc;
+    const uint32_t btiles = (B + kCT_B - 1) / kCT_B;
+    if ((rc = dyb200_scratch(ctx, (size_t)btiles * G * sizeof(float), &pp))) return rc;
     // half-height tiles when full ones would leave most SMs without a CTA (small per-GPU batches)
-    const bool small_grid = (H / kCT_J) * (B / kCT_B) < (uint32_t)ctx->sm_count && H / 32 <= DYB200_DEV_COUNTERS;
+    const bool small_grid = (H / kCT_J) * btiles < (uint32_t)ctx->sm_count && H / 32 <= DYB200_DEV_COUNTERS;
     if (small_grid)
-      dyb_launch(k_lstm_cell_bwd_tiled<32>, dim3(H / 32, B / kCT_B), 256, 0, ctx,
+      dyb_launch(k_lstm_cell_bwd_tiled<32>, dim3(H / 32, btiles), 256, 0, ctx,
                  c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr, dc_tm1 ? dc_tm1->v : nullptr, nullptr, dn.hi, dn.lo, dn.pitch,
                  a_hi, a_lo, a_pitch, db->v, (float*)pp, ctx->dev_flags + DYB200_DEV_COUNTER0, H, B);
     else
-      dyb_launch(k_lstm_cell_bwd_tiled<kCT_J>, dim3(H / kCT_J, B / kCT_B), 256, 0, ctx,
+      dyb_launch(k_lstm_cell_bwd_tiled<kCT_J>, dim3(H / kCT_J, btiles), 256, 0, ctx,
                  c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr, dc_tm1 ? dc_tm1->v : nullptr, nullptr, dn.hi, dn.lo, dn.pitch,
                  a_hi, a_lo, a_pitch, db->v, (float*)pp, ctx->dev_flags + DYB200_DEV_COUNTER0, H, B);
     DYB_LAUNCHED(ctx);

@@ -206,17 +206,6 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_fwd(const float* __restri
   for (size_t c = blockIdx.x; c < ncols; c += gridDim.x) {
     LnLoad L;
     L.xc = x + c * n; L.n = n; L.cached = cached;
-    // gain and bias are requested before the two block reductions of the statistics, not after them: their latency then
-    // hides behind the reductions instead of following them
-    float4 gq[kVec], bq[kVec];
-    if (cached) {
-      const uint32_t n4 = n / 4;
-#pragma unroll
-      for (int k = 0; k < kVec; ++k) {
-        uint32_t i = threadIdx.x + kBlock * k;
-        if (i < n4) { gq[k] = ld4(g + 4 * i); bq[k] = ld4(b + 4 * i); }
-      }
-    }
     float mean, sigma;
     ln_stats(L, red, mean, sigma);
     const float neg = -mean, inv = 1.f / (sigma + 1e-8f);   // one reciprocal per column instead of n divisions
@@ -227,7 +216,7 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_fwd(const float* __restri
       for (int k = 0; k < kVec; ++k) {
         uint32_t i = threadIdx.x + kBlock * k;
         if (i < n4) {
-          float4 gg = gq[k], bb = bq[k], v = L.v[k];
+          float4 gg = ld4(g + 4 * i), bb = ld4(b + 4 * i), v = L.v[k];
           float4 r = make_float4(gg.x * ((v.x + neg) * inv) + bb.x, gg.y * ((v.y + neg) * inv) + bb.y,
                                  gg.z * ((v.z + neg) * inv) + bb.z, gg.w * ((v.w + neg) * inv) + bb.w);
           st4_stream(yc + 4 * i, r);
@@ -249,25 +238,12 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_bwd_x(const float* __rest
   for (size_t c = blockIdx.x; c < ncols; c += gridDim.x) {
     LnLoad L;
     L.xc = x + c * n; L.n = n; L.cached = cached;
-    const float* dc = dy + c * n;
-    float* oc = dx + c * n;
-    // dy * g and the gradient to accumulate into are requested before the block reductions of the statistics
-    float4 dq[kVec], oq[kVec];
-    if (cached) {
-      const uint32_t n4 = n / 4;
-#pragma unroll
-      for (int k = 0; k < kVec; ++k) {
-        uint32_t i = threadIdx.x + kBlock * k;
-        if (i < n4) {
-          const float4 d = ld4_stream(dc + 4 * i), gg = ld4(g + 4 * i);
-          dq[k] = make_float4(d.x * gg.x, d.y * gg.y, d.z * gg.z, d.w * gg.w);
-          oq[k] = ld4_stream(oc + 4 * i);
-        }
-      }
-    }
     float mean, sigma;
     ln_stats(L, red, mean, sigma);
     const float neg = -mean, s2 = sigma + 1e-8f, inv = 1.f / s2;
+    const float* dc = dy + c * n;
+    float* oc = dx + c * n;
+    float4 dq[kVec];
     float A = 0.f, Bs = 0.f;  // A = sum dq*xc (divided by s2^2 once) ; Bs = sum dq (divided by s2 once)
     if (cached) {
       const uint32_t n4 = n / 4;
@@ -275,7 +251,8 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_bwd_x(const float* __rest
       for (int k = 0; k < kVec; ++k) {
         uint32_t i = threadIdx.x + kBlock * k;
         if (i < n4) {
-          const float4 v = L.v[k];
+          float4 d = ld4_stream(dc + 4 * i), gg = ld4(g + 4 * i), v = L.v[k];
+          dq[k] = make_float4(d.x * gg.x, d.y * gg.y, d.z * gg.z, d.w * gg.w);
           A += (dq[k].x * (v.x + neg) + dq[k].y * (v.y + neg)) + (dq[k].z * (v.z + neg) + dq[k].w * (v.w + neg));
           Bs += (dq[k].x + dq[k].y) + (dq[k].z + dq[k].w);
         }
@@ -296,7 +273,7 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_bwd_x(const float* __rest
       for (int k = 0; k < kVec; ++k) {
         uint32_t i = threadIdx.x + kBlock * k;
         if (i < n4) {
-          float4 o = oq[k], v = L.v[k];
+          float4 o = ld4_stream(oc + 4 * i), v = L.v[k];
           o.x = ((o.x + two_n * (v.x - mean) * sb) + dq[k].x * inv) + dmu_n;
           o.y = ((o.y + two_n * (v.y - mean) * sb) + dq[k].y * inv) + dmu_n;
           o.z = ((o.z + two_n * (v.z - mean) * sb) + dq[k].z * inv) + dmu_n;

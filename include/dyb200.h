@@ -317,7 +317,8 @@ int dyb200_vanilla_lstm_seq_fwd(const dyb200_tensor* x_all, const dyb200_tensor*
                                 const dyb200_tensor* mask_x, const dyb200_tensor* mask_h, const dyb200_lstm_gates_attrs* attrs,
                                 dyb200_tensor* gates_all, dyb200_tensor* c_all, dyb200_tensor* h_all, struct dyb200_wgrad* deferred,
                                 uint32_t steps, dyb200_ctx* ctx);
-/* Sequence-persistent kernels (on by default): off makes dyb200_vanilla_lstm_seq_* issue one call per time step. */
+/* Sequence-persistent kernels (1, the default): 0 makes dyb200_vanilla_lstm_seq_* issue one call per time step; 2 keeps the
+ * kernels but launches them without the cooperative-launch attribute (profilers that cannot replay cooperative launches). */
 int dyb200_ctx_sequence_kernels(dyb200_ctx* ctx, int enable);
 
 /* ---- A14 autobatch ragged movers (same argument meaning as dynet/gpu-ops.h:14-15;

@@ -307,7 +307,7 @@ def run(only=None, iters=20, small=False, out=None, graph_mode=True, quiet=False
     stream = torch.cuda.Stream()
     ctx = capi.Context(device, stream.cuda_stream)
     if per_step:
-        ctx.sequence_kernels(False)
+        ctx.sequence_kernels(0 if per_step is True else per_step)
     ctx.param_cache(True)   # as in training: weight matrices are split once (during warm-up), not in every timed call
     peak, src = peaks()
     results = []
@@ -373,5 +373,6 @@ if __name__ == "__main__":
     ap.add_argument("--out", default=None)
     ap.add_argument("--eager", action="store_true", help="no CUDA graph: plain launches (for profiler captures)")
     ap.add_argument("--per-step", action="store_true", help="sequence entry points issue one call per time step (dyb200_ctx_sequence_kernels off)")
+    ap.add_argument("--plain-launch", action="store_true", help="sequence kernels without the cooperative-launch attribute (for ncu)")
     a = ap.parse_args()
-    run(a.only, a.iters, a.small, a.out, graph_mode=not a.eager, per_step=a.per_step)
+    run(a.only, a.iters, a.small, a.out, graph_mode=not a.eager, per_step=(True if a.per_step else (2 if a.plain_launch else False)))
