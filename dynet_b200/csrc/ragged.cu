@@ -5,9 +5,10 @@
 // Copy: one warp per slice when the slices are short (the autobatch case: 128-1024 floats, where a CTA per slice would
 // leave most of its lanes without work), one CTA per slice otherwise; 128-bit loads/stores when both ends are 16-byte
 // aligned, up to four vectors per lane in flight.
-// Accumulate: slices are grouped by target pointer (in-CTA sort, <= 4096 slices per pass); one
-// warp (short slices) or CTA per distinct target adds that target's sources in ascending slice order, so slices that
-// share a target are summed deterministically and without atomics.
+// Accumulate: when all targets are distinct (checked on the device with an address table) every slice is added by one warp
+// (short slices) or CTA, in any order.  Otherwise slices are grouped by target pointer (in-CTA sort, <= 4096 slices per pass,
+// all passes sorted in one launch) and one warp or CTA per distinct target adds that target's sources in ascending slice
+// order, so slices that share a target are summed deterministically and without atomics.
 #include "common.cuh"
 #include "sortseg.cuh"
 
@@ -58,14 +59,38 @@ __global__ void __launch_bounds__(256) k_ragged_copy_warp(int num_seqs, float* c
   }
 }
 
-// key = (target address / 4) << 18 | slice index (slice index < 2^18 within a pass)
-__global__ void __launch_bounds__(kSortThreads) k_sort_targets(float* const* __restrict__ trg, uint32_t n, uint32_t base,
+// ---- are the targets distinct? ------------------------------------------------------------------------------------------
+// In the executor's accumulate_tensors the targets are almost always distinct (one gradient slot per node argument); then
+// no ordering is needed at all and every slice can be added by whichever warp gets to it.  Each slice inserts its target
+// address into an open-addressing table (zeroed before the launch); meeting its own address again raises *dup, and the
+// sorted path below runs instead.
+__global__ void __launch_bounds__(256) k_ragged_probe(float* const* __restrict__ trg, uint32_t n, unsigned long long* __restrict__ table,
+                                                     uint32_t mask, uint32_t* __restrict__ dup) {
+  dyb_grid_dep_sync();
+  for (uint32_t s = blockIdx.x * 256 + threadIdx.x; s < n; s += gridDim.x * 256) {
+    const unsigned long long key = (unsigned long long)(uintptr_t)trg[s];
+    uint32_t h = (uint32_t)(((key >> 2) * 0x9E3779B97F4A7C15ull) >> 32) & mask;
+    for (uint32_t it = 0; it <= mask; ++it) {
+      const unsigned long long old = atomicCAS(&table[h], 0ull, key);
+      if (old == 0ull) break;
+      if (old == key) { atomicOr(dup, 1u); break; }
+      h = (h + 1) & mask;
+    }
+  }
+}
+
+// key = (target address / 4) << 18 | slice index (slice index < 2^18 within a pass).  CTA p sorts pass p (slices
+// [p kSortMax, ...)); nothing to do when the targets are distinct.
+__global__ void __launch_bounds__(kSortThreads) k_sort_targets(float* const* __restrict__ trg, uint32_t n_total,
                                                               uint32_t* __restrict__ slice_sorted,
                                                               uint32_t* __restrict__ group_sorted,
-                                                              uint32_t* __restrict__ seg_start, uint32_t* __restrict__ nseg) {
+                                                              uint32_t* __restrict__ seg_start, uint32_t* __restrict__ nseg,
+                                                              const uint32_t* __restrict__ dup) {
   dyb_grid_dep_sync();
+  if (*dup == 0) return;
   __shared__ unsigned long long keys[kSortMax];
   __shared__ uint32_t scan[kSortThreads];
+  const uint32_t base = blockIdx.x * kSortMax, n = min((uint32_t)kSortMax, n_total - base);
   uint32_t npow = 1;
   while (npow < n) npow <<= 1;
   for (uint32_t k = threadIdx.x; k < npow; k += kSortThreads) {
@@ -74,7 +99,41 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_targets(float* const* __r
     keys[k] = key;
   }
   __syncthreads();
-  sort_and_segment(keys, scan, n, npow, 18, slice_sorted, group_sorted, seg_start, nseg);
+  // (per pass: n entries of slice_sorted / group_sorted, n + 1 of seg_start)
+  sort_and_segment(keys, scan, n, npow, 18, slice_sorted + base, group_sorted + base, seg_start + base + blockIdx.x, nseg + blockIdx.x);
+}
+
+// Distinct targets: slice s is one warp's (or one CTA's) work, in any order.
+template <bool WARP>
+__global__ void __launch_bounds__(WARP ? 256 : kThreads) k_ragged_accumulate_direct(int num_seqs, float* const* __restrict__ src,
+                                                                                   float* const* __restrict__ trg,
+                                                                                   const size_t* __restrict__ len,
+                                                                                   const uint32_t* __restrict__ dup) {
+  dyb_grid_dep_sync();
+  if (*dup != 0) return;
+  const int group = WARP ? blockIdx.x * 8 + (threadIdx.x >> 5) : blockIdx.x, groups = WARP ? gridDim.x * 8 : gridDim.x;
+  const uint32_t me = WARP ? (threadIdx.x & 31) : threadIdx.x, width = WARP ? 32 : kThreads;
+  for (int s = group; s < num_seqs; s += groups) {
+    const float* a = src[s];
+    float* t = trg[s];
+    const size_t n = len[s];
+    if (aligned16(a) && aligned16(t)) {
+      const size_t n4 = n / 4;
+      size_t i = me;
+      for (; i + width < n4; i += 2 * width) {   // two vectors per lane in flight
+        const float4 o0 = ld4(t + 4 * i), o1 = ld4(t + 4 * (i + width)), v0 = ld4_stream(a + 4 * i), v1 = ld4_stream(a + 4 * (i + width));
+        st4(t + 4 * i, make_float4(o0.x + v0.x, o0.y + v0.y, o0.z + v0.z, o0.w + v0.w));
+        st4(t + 4 * (i + width), make_float4(o1.x + v1.x, o1.y + v1.y, o1.z + v1.z, o1.w + v1.w));
+      }
+      for (; i < n4; i += width) {
+        const float4 o = ld4(t + 4 * i), v = ld4_stream(a + 4 * i);
+        st4(t + 4 * i, make_float4(o.x + v.x, o.y + v.y, o.z + v.z, o.w + v.w));
+      }
+      for (size_t j = 4 * n4 + me; j < n; j += width) t[j] += a[j];
+    } else {
+      for (size_t j = me; j < n; j += width) t[j] += a[j];
+    }
+  }
 }
 
 // One thread group (a CTA of kThreads threads, or a warp of a 256-thread CTA when WARP) per distinct target.
@@ -83,8 +142,10 @@ __global__ void __launch_bounds__(WARP ? 256 : kThreads) k_ragged_accumulate(flo
                                                                             const size_t* __restrict__ len, uint32_t base,
                                                                             const uint32_t* __restrict__ slice_sorted,
                                                                             const uint32_t* __restrict__ seg_start,
-                                                                            const uint32_t* __restrict__ nseg) {
+                                                                            const uint32_t* __restrict__ nseg,
+                                                                            const uint32_t* __restrict__ dup) {
   dyb_grid_dep_sync();
+  if (*dup == 0) return;   // (distinct targets: k_ragged_accumulate_direct has done the work)
   const uint32_t U = *nseg;
   const uint32_t group = WARP ? blockIdx.x * 8 + (threadIdx.x >> 5) : blockIdx.x, groups = WARP ? gridDim.x * 8 : gridDim.x;
   const uint32_t me = WARP ? (threadIdx.x & 31) : threadIdx.x, width = WARP ? 32 : kThreads;
@@ -159,22 +220,37 @@ int dyb200_parallel_accumulate(int num_seqs, int max_len, float** src, float** t
   DYB_CHECK_ARG(ctx, num_seqs >= 0, "parallel_accumulate: negative slice count");
   if (num_seqs == 0) return DYB200_OK;
   DYB_CHECK_ARG(ctx, src && trg && len, "parallel_accumulate: null table");
-  uint32_t np = (uint32_t)num_seqs < (uint32_t)kSortMax ? (uint32_t)num_seqs : (uint32_t)kSortMax;
+  const uint32_t n = (uint32_t)num_seqs, npass = (n + kSortMax - 1) / kSortMax;
+  uint32_t cap = 1024;
+  while (cap < 2 * n) cap <<= 1;
+  // scratch: the address table + the flag (zeroed), then the sort tables of all passes
+  const size_t table_bytes = (size_t)cap * sizeof(unsigned long long) + 256;
   void* scratch;
-  int rc = dyb200_scratch(ctx, ((size_t)3 * np + 8) * sizeof(uint32_t), &scratch);
+  int rc = dyb200_scratch(ctx, table_bytes + ((size_t)3 * n + 2 * npass + 8) * sizeof(uint32_t), &scratch);
   if (rc) return rc;
-  for (uint32_t base = 0; base < (uint32_t)num_seqs; base += kSortMax) {
-    uint32_t n = (uint32_t)num_seqs - base < (uint32_t)kSortMax ? (uint32_t)num_seqs - base : (uint32_t)kSortMax;
-    uint32_t* slice_sorted = (uint32_t*)scratch;
-    uint32_t* group_sorted = slice_sorted + n;
-    uint32_t* seg_start = group_sorted + n;
-    uint32_t* nseg = seg_start + n + 1;
-    dyb_launch(k_sort_targets, 1, kSortThreads, 0, ctx, trg, n, base, slice_sorted, group_sorted, seg_start, nseg);
-    DYB_LAUNCHED(ctx);
-    if (max_len > 0 && max_len <= kWarpSliceMax)
-      dyb_launch(k_ragged_accumulate<true>, stream_grid(ctx, n, 8, 8), 256, 0, ctx, src, trg, len, base, slice_sorted, seg_start, nseg);
+  unsigned long long* table = (unsigned long long*)scratch;
+  uint32_t* dup = (uint32_t*)(table + cap);
+  uint32_t* slice_sorted = (uint32_t*)((char*)scratch + table_bytes);
+  uint32_t* group_sorted = slice_sorted + n;
+  uint32_t* seg_start = group_sorted + n;          // n + npass entries: pass p starts at p kSortMax + p
+  uint32_t* nseg = seg_start + n + npass;
+  DYB_CUDA(ctx, cudaMemsetAsync(scratch, 0, table_bytes, ctx->stream));
+  const bool warp = max_len > 0 && max_len <= kWarpSliceMax;
+  dyb_launch(k_ragged_probe, stream_grid(ctx, n, 256), 256, 0, ctx, trg, n, table, cap - 1, dup);
+  DYB_LAUNCHED(ctx);
+  // distinct targets (the usual case): one pass, no order needed
+  if (warp) dyb_launch(k_ragged_accumulate_direct<true>, stream_grid(ctx, n, 8, 8), 256, 0, ctx, num_seqs, src, trg, len, dup);
+  else dyb_launch(k_ragged_accumulate_direct<false>, stream_grid(ctx, n, 1, 16), kThreads, 0, ctx, num_seqs, src, trg, len, dup);
+  DYB_LAUNCHED(ctx);
+  // shared targets: grouped by target, added in ascending slice order (these launches return at once otherwise)
+  dyb_launch(k_sort_targets, npass, kSortThreads, 0, ctx, trg, n, slice_sorted, group_sorted, seg_start, nseg, dup);
+  DYB_LAUNCHED(ctx);
+  for (uint32_t p = 0; p < npass; ++p) {
+    const uint32_t base = p * kSortMax, np = n - base < (uint32_t)kSortMax ? n - base : (uint32_t)kSortMax;
+    if (warp)
+      dyb_launch(k_ragged_accumulate<true>, stream_grid(ctx, np, 8, 8), 256, 0, ctx, src, trg, len, base, slice_sorted + base, seg_start + base + p, nseg + p, dup);
     else
-      dyb_launch(k_ragged_accumulate<false>, stream_grid(ctx, n, 1, 16), kThreads, 0, ctx, src, trg, len, base, slice_sorted, seg_start, nseg);
+      dyb_launch(k_ragged_accumulate<false>, stream_grid(ctx, np, 1, 16), kThreads, 0, ctx, src, trg, len, base, slice_sorted + base, seg_start + base + p, nseg + p, dup);
     DYB_LAUNCHED(ctx);
   }
   return DYB200_OK;
