@@ -225,6 +225,26 @@ def build_cases(torch, ctx, small):
         cases.append(Case("lstm_seq_fwd_I1024_H1024_B%d_T%d" % (Bq, Tt), 0, mk_seq, seq_fwd, 10 ** 9))
         cases[-1].flops = 2.0 * 4 * Hh * (Ig + Hh) * Bq * Tt
 
+    # one backward time step of an LSTM layer (layer 2 of config 4) through the fused entry point: the tiled cell pass
+    # (H, C and gate derivatives, operand planes of the gate gradient) + the product for dx and dh_tm1
+    for Bq in (512, 64):
+        def mk_bwd(Bq=Bq):
+            d = mk_gates()
+            d.update(x=torch.randn(Bq, Ig, device=dev), h=torch.randn(Bq, Hh, device=dev) * 0.5, c_prev=torch.randn(Bq, Hh, device=dev) * 0.5,
+                     c=torch.randn(Bq, Hh, device=dev) * 0.5, gates=torch.rand(Bq, 4 * Hh, device=dev), dh=torch.randn(Bq, Hh, device=dev),
+                     dc=torch.randn(Bq, Hh, device=dev), dx=torch.zeros(Bq, Ig, device=dev), dhp=torch.zeros(Bq, Hh, device=dev),
+                     dcp=torch.zeros(Bq, Hh, device=dev), db=torch.zeros(4 * Hh, device=dev),
+                     mx=(torch.rand(Bq, Ig, device=dev) < 0.8).float() / 0.8, mh=(torch.rand(Bq, Hh, device=dev) < 0.8).float() / 0.8)
+            d["w"] = ctx.wgrad_create(4 * Hh, Ig, Hh, Bq)
+            return d
+        def bwd_step(b, Bq=Bq):
+            ctx.lstm_bwd_fused_at(T(b["x"], [Ig], Bq), T(b["h"], [Hh], Bq), T(b["c_prev"], [Hh], Bq), T(b["Wx"], [4 * Hh, Ig], 1),
+                                  T(b["Wh"], [4 * Hh, Hh], 1), T(b["mx"], [Ig], Bq), T(b["mh"], [Hh], Bq), T(b["gates"], [4 * Hh], Bq),
+                                  T(b["c"], [Hh], Bq), T(b["dh"], [Hh], Bq), T(b["dc"], [Hh], Bq), T(b["dx"], [Ig], Bq), T(b["dhp"], [Hh], Bq),
+                                  T(b["dcp"], [Hh], Bq), None, None, T(b["db"], [4 * Hh], 1), gat, b["w"], 0)
+        cases.append(Case("lstm_bwd_fused_step_I1024_H1024_B%d" % Bq, 0, mk_bwd, bwd_step, 10 ** 9))
+        cases[-1].flops = 2.0 * 4 * Hh * (Ig + Hh) * Bq
+
     # output layer of config 4 over all time steps: r = bias + R h, M = V = 10000, N = T*B = 17920, K = H = 1024
     Vv, TB = 10000, 17920
     def mk_aff():
