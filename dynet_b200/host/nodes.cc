@@ -128,6 +128,7 @@ Dim LogSumExpDimension::dim_forward(const std::vector<Dim>& xs) const {  // dyne
                                       << ") to be smaller than the number of elements in the input");
   Dim d;
   for (unsigned k = 0; k < xs[0].nd; ++k) if (k != dimension) d.d[d.nd++] = xs[0].d[k];
+  if (d.nd == 0) d.d[d.nd++] = 1;   // Dim::delete_dim of the only dimension leaves a size-1 vector (dynet/dim.h:212-228)
   d.bd = xs[0].bd;
   return d;
 }
@@ -158,6 +159,7 @@ static Dim moment_dim(const Dim& x, const std::vector<unsigned>& dims, bool incl
   ARG_CHECK(x.nd <= 3, name << " implemented up to tensors of order 3 (with minibatch) for now");
   ARG_CHECK(dims.size() <= 2, "Number of dimensions to reduce (excluding batch dimension) implemented up to 2 in " << name);
   if (dims.empty()) ARG_CHECK(include_batch, "At least one dimension has to be reduced (including batch dimension) in " << name);
+  for (unsigned d : dims) ARG_CHECK(d < x.nd, "dimension " << d << " is out of bounds of tensor of order " << x.nd << " in " << name);
   Dim r;
   for (unsigned k = 0; k < x.nd; ++k)
     if (std::find(dims.begin(), dims.end(), k) == dims.end()) r.d[r.nd++] = x.d[k];
@@ -277,11 +279,13 @@ Dim SumDimension::dim_forward(const std::vector<Dim>& xs) const {      // dynet/
   ARG_CHECK(dims.size() <= 2, "Number of dimensions to reduce (excluding batch dimension) implemented up to 2 in SumDimension");
   ARG_CHECK(!dims.empty() || include_batch_dim, "At least one dimension has to be reduced (including batch dimension) in SumDimension");
   Dim ret;
+  for (unsigned d : dims) ARG_CHECK(d < xs[0].nd, "dimension " << d << " is out of bounds of tensor of order " << xs[0].nd << " in SumDimension");
   for (unsigned k = 0; k < xs[0].nd; ++k) {
     bool removed = false;
-    for (unsigned d : dims) { ARG_CHECK(d <= xs[0].nd, "dimension " << d << " is out of bounds in SumDimension"); removed = removed || d == k; }
+    for (unsigned d : dims) removed = removed || d == k;
     if (!removed) ret.d[ret.nd++] = xs[0].d[k];
   }
+  if (ret.nd == 0) ret.d[ret.nd++] = 1;   // Dim::delete_dims keeps a size-1 vector (dynet/dim.h:234-256)
   ret.bd = include_batch_dim ? 1 : xs[0].bd;
   return ret;
 }
@@ -334,3 +338,65 @@ void parallel_accumulate(const Device_GPU& dev, int num_seqs, int max_len, float
 }  // namespace gpu
 
 }  // namespace dynet_b200
+
+// ---- shape rules without a device: dim_forward of a node by name --------------------------------------------------------
+// xs: the argument shapes (the `v` fields are ignored); iargs: the node's integer constructor arguments (Softmax /
+// LogSumExpDimension / Concatenate: dimension; PickRange: start, end, dim; SumDimension: include_batch_dim, dims...;
+// MomentDimension: order, include_batch_dim, dims...; StdDimension: include_batch_dim, dims...; VanillaLSTMGates: dropout;
+// LookupNode: E, n).  Returns DYB200_OK and the result shape, or DYB200_EINVAL with the reference's message in `err`.
+extern "C" int dyb200h_dim_forward(const char* node, const dyb200_tensor* xs, int nxs, const int32_t* iargs, int niargs,
+                                   dyb200_tensor* out, char* err, size_t errlen) {
+  using namespace dynet_b200;
+  auto arg = [&](int k) -> unsigned { return k < niargs ? (unsigned)iargs[k] : 0u; };
+  std::vector<Dim> dims;
+  for (int k = 0; k < nxs; ++k) {
+    Dim d;
+    d.nd = xs[k].nd; d.bd = xs[k].bd;
+    for (unsigned q = 0; q < d.nd && q < 7; ++q) d.d[q] = xs[k].d[q];
+    dims.push_back(d);
+  }
+  const std::string n = node ? node : "";
+  try {
+    Dim r;
+    std::vector<unsigned> rest;
+    if (n == "Tanh") r = Tanh().dim_forward(dims);
+    else if (n == "LogisticSigmoid") r = LogisticSigmoid().dim_forward(dims);
+    else if (n == "Rectify") r = Rectify().dim_forward(dims);
+    else if (n == "ExponentialLinearUnit") r = ExponentialLinearUnit().dim_forward(dims);
+    else if (n == "CwiseMultiply") r = CwiseMultiply().dim_forward(dims);
+    else if (n == "CwiseSum") r = CwiseSum().dim_forward(dims);
+    else if (n == "CwiseQuotient") r = CwiseQuotient().dim_forward(dims);
+    else if (n == "Softmax") r = Softmax(arg(0)).dim_forward(dims);
+    else if (n == "LogSoftmax") r = LogSoftmax().dim_forward(dims);
+    else if (n == "LogSumExp") r = LogSumExp().dim_forward(dims);
+    else if (n == "LogSumExpDimension") r = LogSumExpDimension(arg(0)).dim_forward(dims);
+    else if (n == "PickNegLogSoftmax") { std::vector<unsigned> ids(arg(0), 0u); r = PickNegLogSoftmax(&ids).dim_forward(dims); }
+    else if (n == "WeightNormalization") r = WeightNormalization().dim_forward(dims);
+    else if (n == "MomentDimension") { for (int k = 2; k < niargs; ++k) rest.push_back(arg(k)); r = MomentDimension(rest, arg(0), arg(1) != 0).dim_forward(dims); }
+    else if (n == "StdDimension") { for (int k = 1; k < niargs; ++k) rest.push_back(arg(k)); r = StdDimension(rest, arg(0) != 0).dim_forward(dims); }
+    else if (n == "LayerNormFused") r = LayerNormFused().dim_forward(dims);
+    else if (n == "LookupNode") { Tensor t(Dim({arg(0)}, 1), nullptr); r = LookupNode(t, nullptr, arg(1)).dim_forward(dims); }
+    else if (n == "VanillaLSTMGates") r = VanillaLSTMGates(arg(0) != 0).dim_forward(dims);
+    else if (n == "VanillaLSTMC") r = VanillaLSTMC().dim_forward(dims);
+    else if (n == "VanillaLSTMH") r = VanillaLSTMH().dim_forward(dims);
+    else if (n == "PickRange") r = PickRange(arg(0), arg(1), arg(2)).dim_forward(dims);
+    else if (n == "Concatenate") r = Concatenate(arg(0)).dim_forward(dims);
+    else if (n == "Sum") r = Sum().dim_forward(dims);
+    else if (n == "SumDimension") { for (int k = 1; k < niargs; ++k) rest.push_back(arg(k)); r = SumDimension(rest, arg(0) != 0).dim_forward(dims); }
+    else if (n == "SquaredNorm") r = SquaredNorm().dim_forward(dims);
+    else if (n == "Negate") r = Negate().dim_forward(dims);
+    else if (n == "ConstantPlusX") r = ConstantPlusX(0.f).dim_forward(dims);
+    else if (n == "ConstantMinusX") r = ConstantMinusX(0.f).dim_forward(dims);
+    else if (n == "MatrixMultiply") r = MatrixMultiply().dim_forward(dims);
+    else if (n == "AffineTransform") r = AffineTransform().dim_forward(dims);
+    else { if (err && errlen) snprintf(err, errlen, "unknown node %s", n.c_str()); return DYB200_ERUNTIME; }
+    if (out) {
+      out->v = nullptr; out->nd = r.nd; out->bd = r.bd;
+      for (unsigned q = 0; q < 7; ++q) out->d[q] = q < r.nd ? r.d[q] : 0;
+    }
+    return DYB200_OK;
+  } catch (const std::invalid_argument& e) {
+    if (err && errlen) snprintf(err, errlen, "%s", e.what());
+    return DYB200_EINVAL;
+  }
+}
