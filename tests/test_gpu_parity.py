@@ -1273,3 +1273,28 @@ def test_new_entry_points_reject_bad_arguments(g, capi):
     with pytest.raises(ValueError):     # a zero weight-decay divisor
         g.ctx().trainer_update("sgd", p_.data_ptr(), g_.data_ptr(), [], 16, capi.TrainerHyper(0.1, 5.0, 0.0, 0.9, 1e-8, 0.95, 0.9, 0.999, 0))
     assert g.ctx().device_errors() == 0
+
+
+def test_two_devices_in_one_process(capi):
+    """DyNet allows several devices per process (--dynet-devices).  What a context establishes on its device (shared-memory
+    limits of the tensor-pipe kernels, cluster occupancy) must not leak to a second device: one tensor-path product on each."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r = rng(1600)
+    M, N, K = 512, 256, 2048
+    A, Bm = randn(r, K, M), randn(r, N, K)
+    ref = Bm.astype(np.float64) @ A.astype(np.float64)
+    try:
+        for dev in (0, 1):
+            torch.cuda.set_device(dev)
+            ctx = capi.Context(dev)
+            A_, B_ = torch.from_numpy(A).cuda(dev), torch.from_numpy(Bm).cuda(dev)
+            C_ = torch.zeros(N, M, device="cuda:%d" % dev)
+            ctx.gemm(0, 0, M, N, K, A_.data_ptr(), M, B_.data_ptr(), K, C_.data_ptr(), M, 0)
+            torch.cuda.synchronize(dev)
+            assert_close(C_.cpu().numpy(), ref, TOL_REDUCE, floor=0.1 * K ** 0.5 + 1.0, what="product on device %d" % dev)
+            assert ctx.device_errors() == 0
+            ctx.close()
+    finally:
+        torch.cuda.set_device(0)
