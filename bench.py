@@ -244,6 +244,8 @@ def run_gpu(args):
     stream = torch.cuda.Stream()          # a capturable (non-legacy) stream for the whole step
     torch.cuda.set_stream(stream)
     model = lm.LstmLm(device=local_rank, seed=1, lr=0.1, clip=5.0, dropout=True, stream=stream.cuda_stream, **dims)
+    if args.plain_launch:
+        model.ctx.sequence_kernels(2)
 
     # synthetic corpus: a few global batches of Zipf(1.1) ids; this rank keeps its columns
     n_batches = 4
@@ -616,6 +618,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-hbm-kernels", action="store_true", help="skip the per-kernel pass over the memory-bound kernels (N = 1 only)")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--plain-launch", action="store_true",
+                    help="launch the sequence-persistent kernels without the cooperative attribute (profilers that cannot replay such launches)")
     ap.add_argument("--workload", default="lm", choices=["lm", "tagger"],
                     help="lm: the 2-layer LSTM language model the headline metric is quoted on; tagger: the autobatched BiLSTM tagger")
     args = ap.parse_args()

@@ -120,7 +120,7 @@ OTHER = ["dyb200_ctx_create", "dyb200_ctx_destroy", "dyb200_last_error", "dyb200
          "dyb200_ctx_profile_count", "dyb200_ctx_profile_launch",
          "dyb200_ctx_param_cache", "dyb200_ctx_params_changed", "dyb200_ctx_dependent_launch", "dyb200_ctx_cluster_splitk", "dyb200_vanilla_lstm_fwd_fused",
          "dyb200_vanilla_lstm_bwd_fused", "dyb200_vanilla_lstm_fwd_fused_at", "dyb200_vanilla_lstm_bwd_fused_at",
-         "dyb200_vanilla_lstm_seq_fwd", "dyb200_ctx_sequence_kernels", "dyb200_wgrad_create", "dyb200_wgrad_destroy", "dyb200_wgrad_push",
+         "dyb200_vanilla_lstm_seq_fwd", "dyb200_vanilla_lstm_seq_bwd", "dyb200_ctx_sequence_kernels", "dyb200_wgrad_create", "dyb200_wgrad_destroy", "dyb200_wgrad_push",
          "dyb200_wgrad_flush", "dyb200_wgrad_pack_inputs", "dyb200_softmax_output_bwd_fused"]
 
 
@@ -176,6 +176,8 @@ def lib():
         L.dyb200_vanilla_lstm_bwd_fused_at.argtypes = [tp] * 17 + [C.POINTER(LstmGatesAttrs), C.c_void_p, C.c_uint32, C.c_void_p]
         L.dyb200_vanilla_lstm_seq_fwd.restype = C.c_int
         L.dyb200_vanilla_lstm_seq_fwd.argtypes = [tp] * 8 + [C.POINTER(LstmGatesAttrs)] + [tp] * 3 + [C.c_void_p, C.c_uint32, C.c_void_p]
+        L.dyb200_vanilla_lstm_seq_bwd.restype = C.c_int
+        L.dyb200_vanilla_lstm_seq_bwd.argtypes = [tp] * 7 + [C.POINTER(LstmGatesAttrs)] + [tp] * 9 + [C.c_void_p, C.c_uint32, C.c_void_p]
         L.dyb200_ctx_sequence_kernels.restype = C.c_int
         L.dyb200_ctx_sequence_kernels.argtypes = [C.c_void_p, C.c_int]
         L.dyb200_wgrad_create.restype = C.c_int
@@ -357,6 +359,13 @@ class Context:
         o = self._opt
         self.check(self.L.dyb200_vanilla_lstm_seq_fwd(o(x_all), o(h0), o(c0), o(Wx), o(Wh), o(b), o(mask_x), o(mask_h), C.byref(attrs),
                                                       o(gates_all), o(c_all), o(h_all), deferred, steps, self.h))
+
+    def lstm_seq_bwd(self, x_all, h0, c0, Wx, Wh, mask_x, mask_h, attrs, gates_all, c_all, h_all, dh_all, dc_all, dx_all, dWx, dWh, db,
+                     deferred, steps):
+        o = self._opt
+        self.check(self.L.dyb200_vanilla_lstm_seq_bwd(o(x_all), o(h0), o(c0), o(Wx), o(Wh), o(mask_x), o(mask_h), C.byref(attrs),
+                                                      o(gates_all), o(c_all), o(h_all), o(dh_all), o(dc_all), o(dx_all), o(dWx), o(dWh),
+                                                      o(db), deferred, steps, self.h))
 
     def sequence_kernels(self, enable):
         self.check(self.L.dyb200_ctx_sequence_kernels(self.h, int(enable)))

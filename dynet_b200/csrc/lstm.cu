@@ -9,6 +9,7 @@
 // reduction (db).  C and H are single-pass 128-bit elementwise kernels over gate slices.
 #include "common.cuh"
 #include "gemm.cuh"
+#include "lstm_cell.cuh"
 #include "reduce.cuh"
 
 namespace {
@@ -245,14 +246,7 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __rest
     float dcp_[4] = {dcp.x, dcp.y, dcp.z, dcp.w};
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const float t = tanhf(c_[q]);
-      float dc = dh_[q] * go_[q] * (1.f - t * t);
-      if (dEdc) dc += dci_[q];
-      dcp_[q] += dc * gf_[q];
-      pi[q] = gate_deriv(gi_[q], dc * gg_[q], false);
-      pf[q] = gate_deriv(gf_[q], dc * cp_[q], false);
-      po[q] = gate_deriv(go_[q], dh_[q] * t, false);
-      pg[q] = gate_deriv(gg_[q], dc * gi_[q], true);
+      lstm_cell_grad(gi_[q], gf_[q], go_[q], gg_[q], c_[q], cp_[q], dh_[q], dci_[q], dEdc != nullptr, dcp_[q], pi[q], pf[q], po[q], pg[q]);
       tile[0][4 * tq + q][bl] = pi[q]; tile[1][4 * tq + q][bl] = pf[q];
       tile[2][4 * tq + q][bl] = po[q]; tile[3][4 * tq + q][bl] = pg[q];
     }

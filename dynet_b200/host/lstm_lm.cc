@@ -282,6 +282,25 @@ void step_body(Lm& m, const float* const* masks, float* loss_dev, int phase = -1
   Tensor tones(Dim({1}, B), m.ones);
   const uint32_t pass0 = phase < 0 ? 0u : (phase == 0 ? L : (uint32_t)phase - 1), pass1 = phase < 0 ? (layer_major ? L : 1u) : (phase == 0 ? L : (uint32_t)phase);
   for (uint32_t pass = pass0; pass < pass1; ++pass) {
+  if (layer_major) {
+    // One call per layer, top layer first: dE/dh of all its steps is complete (output layer, or the layer above), and the
+    // steps T-1 .. 1 run inside one kernel whose CTAs hand dE/dh_{t-1} over on the device (dyb200_vanilla_lstm_seq_bwd; it
+    // makes the per-step calls itself when the shape does not allow that).
+    const uint32_t l = L - 1 - pass, I = l == 0 ? E : H;
+    Tensor xall(Dim({I}, TB), l == 0 ? m.x : m.hs + at(0, l - 1) * HB);
+    Tensor gall(Dim({4 * H}, TB), m.gates + at(0, l) * GB), call(Dim({H}, TB), m.cs + at(0, l) * HB), hall_l(Dim({H}, TB), m.hs + at(0, l) * HB);
+    Tensor dhall(Dim({H}, TB), m.dh + at(0, l) * HB), dcall(Dim({H}, TB), m.dc + at(0, l) * HB);
+    Tensor dxall(Dim({I}, TB), l == 0 ? m.dx : m.dh + at(0, l - 1) * HB);
+    Tensor tWx(Dim({4 * H, I}), m.p[1 + 3 * l]), tWh(Dim({4 * H, H}), m.p[2 + 3 * l]);
+    Tensor gWx(Dim({4 * H, I}), m.g[1 + 3 * l]), gWh(Dim({4 * H, H}), m.g[2 + 3 * l]), gb(Dim({4 * H}), m.g[3 + 3 * l]);
+    Tensor mxl(Dim({I}, B), c.dropout ? const_cast<float*>(masks[2 * l]) : nullptr), mhl(Dim({H}, B), c.dropout ? const_cast<float*>(masks[2 * l + 1]) : nullptr);
+    dyb200_tensor cxa = to_c(xall), ch0 = to_c(tZero), cc0 = to_c(tZero), cWx = to_c(tWx), cWh = to_c(tWh), cmx = to_c(mxl), cmh = to_c(mhl),
+                  cg = to_c(gall), cc = to_c(call), ch = to_c(hall_l), cdh = to_c(dhall), cdc = to_c(dcall), cdx = to_c(dxall),
+                  cgWx = to_c(gWx), cgWh = to_c(gWh), cgb = to_c(gb);
+    dyb200_lstm_gates_attrs at = {c.dropout ? 1 : 0, 0.f, 1.f};
+    throw_status(dev, dyb200_vanilla_lstm_seq_bwd(&cxa, &ch0, &cc0, &cWx, &cWh, c.dropout ? &cmx : nullptr, c.dropout ? &cmh : nullptr, &at,
+                                                  &cg, &cc, &ch, &cdh, &cdc, &cdx, &cgWx, &cgWh, &cgb, m.wg_layer[l], T, dev.ctx));
+  } else
   for (uint32_t tt = T; tt-- > 0;) {
     if (!c.fused) {
       Tensor rt(Dim({V}, B), m.r + tt * VB), et(Dim({1}, B), m.errs + (size_t)tt * B), tdr(Dim({V}, B), m.dr);

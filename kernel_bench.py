@@ -225,6 +225,27 @@ def build_cases(torch, ctx, small):
         cases.append(Case("lstm_seq_fwd_I1024_H1024_B%d_T%d" % (Bq, Tt), 0, mk_seq, seq_fwd, 10 ** 9))
         cases[-1].flops = 2.0 * 4 * Hh * (Ig + Hh) * Bq * Tt
 
+    # the backward pass of the same layer over all time steps in one call: one sequence-persistent kernel for steps T-1 .. 1
+    # (cell pass + [Wx; Wh]^T dgates product per step) + the per-step form of step 0, or (--per-step) T per-step calls
+    for Bq in (512, 64):
+        def mk_seqb(Bq=Bq):
+            sc = (6.0 / (4 * Hh + Ig)) ** 0.5
+            d = dict(x=torch.randn(Tt * Bq, Ig, device=dev), z=torch.zeros(Bq, Hh, device=dev),
+                     Wx=(torch.rand(Ig, 4 * Hh, device=dev) * 2 - 1) * sc, Wh=(torch.rand(Hh, 4 * Hh, device=dev) * 2 - 1) * sc,
+                     mx=(torch.rand(Bq, Ig, device=dev) < 0.8).float() / 0.8, mh=(torch.rand(Bq, Hh, device=dev) < 0.8).float() / 0.8,
+                     gates=torch.rand(Tt * Bq, 4 * Hh, device=dev), c=torch.randn(Tt * Bq, Hh, device=dev) * 0.5,
+                     h=torch.randn(Tt * Bq, Hh, device=dev) * 0.5, dh=torch.randn(Tt * Bq, Hh, device=dev) * 0.01,
+                     dc=torch.zeros(Tt * Bq, Hh, device=dev), dx=torch.zeros(Tt * Bq, Ig, device=dev), db=torch.zeros(4 * Hh, device=dev))
+            d["w"] = ctx.wgrad_create(4 * Hh, Ig, Hh, Tt * Bq)
+            return d
+        def seq_bwd(b, Bq=Bq):
+            ctx.lstm_seq_bwd(T(b["x"], [Ig], Tt * Bq), T(b["z"], [Hh], Bq), T(b["z"], [Hh], Bq), T(b["Wx"], [4 * Hh, Ig], 1),
+                             T(b["Wh"], [4 * Hh, Hh], 1), T(b["mx"], [Ig], Bq), T(b["mh"], [Hh], Bq), gat, T(b["gates"], [4 * Hh], Tt * Bq),
+                             T(b["c"], [Hh], Tt * Bq), T(b["h"], [Hh], Tt * Bq), T(b["dh"], [Hh], Tt * Bq), T(b["dc"], [Hh], Tt * Bq),
+                             T(b["dx"], [Ig], Tt * Bq), None, None, T(b["db"], [4 * Hh], 1), b["w"], Tt)
+        cases.append(Case("lstm_seq_bwd_I1024_H1024_B%d_T%d" % (Bq, Tt), 0, mk_seqb, seq_bwd, 10 ** 9))
+        cases[-1].flops = 2.0 * 4 * Hh * (Ig + Hh) * Bq * Tt
+
     # one backward time step of an LSTM layer (layer 2 of config 4) through the fused entry point: the tiled cell pass
     # (H, C and gate derivatives, operand planes of the gate gradient) + the product for dx and dh_tm1
     for Bq in (512, 64):

@@ -1,12 +1,15 @@
-"""The sequence-persistent LSTM kernels (one launch per layer for all time steps) against the per-step calls they replace:
-gates, cell and hidden states of every step, and the weight gradients that the recorded operand planes produce, must agree
-BIT FOR BIT, and the whole thing must match the CPU oracle.  Shapes: one tile per CTA (batch 512 and 384), K splits reduced
-inside a thread-block cluster with 128-column tiles (batch 256: 2 splits, batch 128: 4) and with 64-column tiles (batch 64),
-batch-1 masks, a layer whose input is narrower than its state, and a shape the kernel declines (per-step calls inside)."""
+"""The sequence-persistent LSTM kernels (one launch per layer and direction for all time steps) against the per-step calls
+they replace.  Forward: gates, cell and hidden states of every step agree BIT FOR BIT, and match the CPU oracle.  Backward:
+dE/dx, dE/dh and dE/dc of every step, the bias gradient and the weight gradients that the recorded operand planes produce
+agree with the per-step calls row by row within 2e-5 (the kernel splits K differently, so fp32 sums associate differently;
+the per-step calls themselves are checked against the oracle in test_gpu_parity.py / test_gpu_lm.py), and two runs of the
+kernel give the same bits.  Shapes: one tile per CTA (batch 512 and 384), K splits reduced inside a thread-block cluster with
+128-column tiles (batch 256: 2 splits, batch 128: 4) and with 64-column tiles (batch 64), batch-1 masks, a layer whose input
+is narrower than its state, and shapes the kernels decline (per-step calls inside)."""
 import numpy as np
 import pytest
 
-from util import assert_close, glorot, randn, rng
+from util import assert_close, glorot, randn, rng, row_floor
 
 pytestmark = pytest.mark.gpu
 
@@ -57,39 +60,61 @@ def _run(g, capi, D, I, H, B, T, dropout, seq, dhs):
                 ctx.lstm_fwd_fused_at(g.T(D["x"][sl]), g.T(hp), g.T(cp), tWx, tWh, tb, tmx, tmh, at, g.T(gates[sl]), g.T(cs[sl]),
                                       g.T(hs[sl]), w, t * B)
         fwd_launches = ctx.launches() - l0
-        dh = [g.dev(d) for d in dhs]
-        dc = [torch.zeros(B, H, device="cuda") for _ in range(T)]
-        dx = [torch.zeros(B, I, device="cuda") for _ in range(T)]
+        dh = g.dev(np.concatenate(dhs))                      # dE/dh_t of every step, step t in rows [t B, (t + 1) B)
+        dc = torch.zeros(T * B, H, device="cuda")
+        dx = torch.zeros(T * B, I, device="cuda")
         db = torch.zeros(4 * H, device="cuda")
-        for t in range(T - 1, -1, -1):
-            sl = slice(t * B, (t + 1) * B)
-            hp = zeros if t == 0 else hs[(t - 1) * B:t * B]
-            cp = zeros if t == 0 else cs[(t - 1) * B:t * B]
-            ctx.lstm_bwd_fused_at(g.T(D["x"][sl]), g.T(hp), g.T(cp), tWx, tWh, tmx, tmh, g.T(gates[sl]), g.T(cs[sl]), g.T(dh[t]), g.T(dc[t]),
-                                  g.T(dx[t]), None if t == 0 else g.T(dh[t - 1]), None if t == 0 else g.T(dc[t - 1]), None, None,
-                                  g.T(db, [4 * H], 1), at, w, t * B)
+        l1 = ctx.launches()
+        if seq:
+            ctx.lstm_seq_bwd(g.T(D["x"], [I], T * B), g.T(zeros), g.T(zeros), tWx, tWh, tmx, tmh, at, g.T(gates, [4 * H], T * B),
+                             g.T(cs, [H], T * B), g.T(hs, [H], T * B), g.T(dh, [H], T * B), g.T(dc, [H], T * B), g.T(dx, [I], T * B),
+                             None, None, g.T(db, [4 * H], 1), w, T)
+        else:
+            for t in range(T - 1, -1, -1):
+                sl, pr = slice(t * B, (t + 1) * B), slice((t - 1) * B, t * B)
+                hp = zeros if t == 0 else hs[pr]
+                cp = zeros if t == 0 else cs[pr]
+                ctx.lstm_bwd_fused_at(g.T(D["x"][sl]), g.T(hp), g.T(cp), tWx, tWh, tmx, tmh, g.T(gates[sl]), g.T(cs[sl]), g.T(dh[sl]),
+                                      g.T(dc[sl]), g.T(dx[sl]), None if t == 0 else g.T(dh[pr]), None if t == 0 else g.T(dc[pr]), None, None,
+                                      g.T(db, [4 * H], 1), at, w, t * B)
+        bwd_launches = ctx.launches() - l1
         dWx, dWh = torch.zeros(I, 4 * H, device="cuda"), torch.zeros(H, 4 * H, device="cuda")
         ctx.wgrad_flush(w, dWx.data_ptr(), 4 * H, dWh.data_ptr(), 4 * H)
         torch.cuda.synchronize()
         out = dict(gates=g.host(gates), c=g.host(cs), h=g.host(hs), dWx=g.host(dWx), dWh=g.host(dWh), db=g.host(db),
-                   dx=np.stack([g.host(v) for v in dx]))
-        return out, fwd_launches
+                   dx=g.host(dx), dh=g.host(dh), dc=g.host(dc))
+        return out, (fwd_launches, bwd_launches)
     finally:
         ctx.wgrad_destroy(w)
 
 
-@pytest.mark.parametrize("I,H,B,T,dropout,full,one_kernel", [
-    (512, 1024, 512, 4, True, True, True),      # benchmark layer 1 on one GPU: one tile per CTA, 128 CTAs
-    (1024, 1024, 64, 6, True, True, True),      # benchmark layer 2 on 8 GPUs: 64-column tiles, 4 K splits per cluster
-    (512, 1024, 64, 5, True, False, True),      # layer 1 on 8 GPUs, batch-1 masks
-    (1024, 1024, 128, 3, True, True, True),     # 4 GPUs: 128-column tiles, 4 K splits per cluster
-    (512, 1024, 256, 3, False, True, True),     # 2 GPUs: 2 K splits per cluster, no dropout
-    (256, 1024, 384, 3, True, True, True),      # three column blocks, one tile per CTA
-    (256, 512, 384, 3, True, True, False),      # 3 K splits: 48 clusters of 3 do not fit on the GPU at once -> per-step calls
-    (128, 256, 96, 3, True, True, False),       # 96 columns are not whole tiles: per-step calls inside
-    (32, 64, 8, 3, True, True, False),          # far below the tensor path
+FORWARD = ("gates", "c", "h")
+
+
+def _same(seq, per, bwd_kernel):
+    """Forward values and everything the per-step calls inside the entry points produce: bit for bit.  The backward kernel
+    splits K differently from the per-step product (it chooses the splits that keep all its CTAs resident), so its sums
+    associate differently: every row of every gradient within 2e-5 of its largest entry."""
+    for k in sorted(seq):
+        if k in FORWARD or not bwd_kernel:
+            assert np.array_equal(seq[k], per[k]), "%s: the sequence call differs from the per-step calls (max |diff| %.3g)" % (
+                k, float(np.abs(seq[k] - per[k]).max()))
+        else:
+            assert_close(seq[k], per[k], 2e-5, floor=row_floor(per[k], axis=-1, rel=1e-3), what="seq vs per-step " + k)
+
+
+@pytest.mark.parametrize("I,H,B,T,dropout,full,one_kernel,bwd_kernel", [
+    (512, 1024, 512, 4, True, True, True, True),      # benchmark layer 1 on one GPU: one tile per CTA, 128 CTAs
+    (1024, 1024, 64, 6, True, True, True, True),      # benchmark layer 2 on 8 GPUs: 64-column tiles, 4 K splits per cluster
+    (512, 1024, 64, 5, True, False, True, True),      # layer 1 on 8 GPUs, batch-1 masks
+    (1024, 1024, 128, 3, True, True, True, True),     # 4 GPUs: 128-column tiles, 4 K splits per cluster
+    (512, 1024, 256, 3, False, True, True, True),     # 2 GPUs: 2 K splits per cluster, no dropout
+    (256, 1024, 384, 3, True, True, True, True),      # three column blocks, one tile per CTA
+    (256, 512, 384, 3, True, True, False, True),      # 3 K splits: 48 clusters of 3 do not fit on the GPU at once -> per-step calls
+    (128, 256, 96, 3, True, True, False, False),       # 96 columns are not whole tiles: per-step calls inside
+    (32, 64, 8, 3, True, True, False, False),          # far below the tensor path
 ])
-def test_sequence_forward_equals_per_step_calls(oracle, g, capi, I, H, B, T, dropout, full, one_kernel):
+def test_sequence_calls_equal_per_step_calls(oracle, g, capi, I, H, B, T, dropout, full, one_kernel, bwd_kernel):
     r = rng(700 + B + I)
     Wx, Wh, b = glorot(r, 4 * H, I), glorot(r, 4 * H, H), randn(r, 4 * H, scale=0.1)
     mB = B if full else 1
@@ -109,13 +134,18 @@ def test_sequence_forward_equals_per_step_calls(oracle, g, capi, I, H, B, T, dro
         ctx.sequence_kernels(True)
         ctx.param_cache(False)
     assert ctx.device_errors() == 0
+    _same(seq, per, bwd_kernel)
     for k in sorted(seq):
-        assert np.array_equal(seq[k], per[k]), "%s: the sequence call differs from the per-step calls" % k
         assert np.array_equal(off[k], per[k]), "%s: the sequence call (kernel off) differs from the per-step calls" % k
     if one_kernel:
-        assert l_seq == 3 < l_per, (l_seq, l_per)      # operand split of x, of h0 (the counter reset is a memset), one kernel
+        assert l_seq[0] == 3 < l_per[0], (l_seq, l_per)   # operand split of x, of h0 (the counter reset is a memset), one kernel
     else:
-        assert l_seq <= l_per
+        assert l_seq[0] <= l_per[0]
+    if bwd_kernel:
+        # the kernel, the sum of its bias-gradient partials, and the per-step form of step 0
+        assert l_seq[1] < l_per[1] and l_seq[1] <= 2 + 4, (l_seq, l_per)
+    else:
+        assert l_seq[1] <= l_per[1]
     # and the values themselves: the oracle's node chain
     h = np.zeros((B, H), np.float32)
     c = np.zeros((B, H), np.float32)
@@ -148,4 +178,5 @@ def test_sequence_forward_twice_in_a_row_and_many_steps(g, capi):
         ctx.param_cache(False)
     assert ctx.device_errors() == 0
     for k in sorted(a):
-        assert np.array_equal(a[k], per[k]) and np.array_equal(b2[k], per[k]), k
+        assert np.array_equal(a[k], b2[k]), k     # the same call twice: the same bits
+    _same(a, per, True)
