@@ -111,8 +111,15 @@ uint32_t dyb200_tc_splits(const dyb200_ctx* ctx, uint32_t M, uint32_t N, uint32_
 // rows [rows, rows + rows2) from src2.
 int dyb200_tc_param2(dyb200_ctx* ctx, const float* src, uint32_t rows, const float* src2, uint32_t rows2, uint32_t ld,
                      bool k_is_fast, uint32_t K, PackedOp* out);
+// force_splits > 0: that many K splits (normalised so that no split is empty) instead of the cost model's choice.
 int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const PackedOp* A, const PackedOp* B,
-                          const GemmEpilogue& epi);
+                          const GemmEpilogue& epi, uint32_t force_splits = 0);
+// Tiling of the backward recurrence of an LSTM layer (dx_t, dh_{t-1} += [Wx; Wh]^T dgates_t), shared by the per-step call
+// and the sequence kernel so that both add the same partial sums: tile width, batch-column blocks per CTA of the sequence
+// kernel (1 or 2) and K splits.  False when the shape does not suit the sequence kernel (the per-step call then lets the
+// cost model choose).
+struct LstmBwdTiling { uint32_t bn, ncb, S; };
+bool dyb200_lstm_bwd_tiling(const dyb200_ctx* ctx, uint32_t I, uint32_t H, uint32_t B, LstmBwdTiling* out);
 bool dyb200_tc_eligible(uint32_t M, uint32_t N, double flops);
 // Planes of `rows x K` taken from the scratch arena, left for the caller's kernel to fill.
 int dyb200_tc_planes(dyb200_ctx* ctx, uint32_t rows, uint32_t K, PackedOp* out);

@@ -843,6 +843,25 @@ uint32_t dyb200_tc_splits(const dyb200_ctx* ctx, uint32_t M, uint32_t N, uint32_
   return S;
 }
 
+bool dyb200_lstm_bwd_tiling(const dyb200_ctx* ctx, uint32_t I, uint32_t H, uint32_t B, LstmBwdTiling* out) {
+  // 128-column tiles from 256 columns up; two column blocks per CTA whenever the batch has an even number of them (128
+  // columns: two blocks of 64), so that each CTA of the sequence kernel alternates between two independent chains
+  const uint32_t bn = (B >= 256 && B % 128 == 0) ? 128u : 64u;
+  if (B == 0 || B % bn != 0 || B / bn > 32 || H % 64 != 0 || I % 4 != 0) return false;
+  const uint32_t tiles_m = (I + H + BM - 1) / BM, tiles_n = B / bn, kb = 4 * H / 32;
+  const uint32_t ncb = tiles_n % 2 == 0 ? 2u : 1u;
+  // as many K splits as keep every CTA of the sequence kernel resident (one per SM), at least 8 k-blocks each
+  const uint32_t groups = tiles_m * (tiles_n / ncb);
+  uint32_t S = (uint32_t)ctx->sm_count / groups;
+  if (S == 0 || tiles_m * tiles_n > 160) return false;
+  if (S > 8) S = 8;
+  while (S > 1 && kb / S < 8) --S;
+  const uint32_t per = (kb + S - 1) / S;
+  S = (kb + per - 1) / per;
+  out->bn = bn; out->ncb = ncb; out->S = S;
+  return true;
+}
+
 int dyb200_tc_param2(dyb200_ctx* ctx, const float* src, uint32_t rows, const float* src2, uint32_t rows2, uint32_t ld,
                      bool k_is_fast, uint32_t K, PackedOp* out) {
   const uint32_t pitch = round_up(K, 32);
@@ -862,7 +881,7 @@ int dyb200_tc_param2(dyb200_ctx* ctx, const float* src, uint32_t rows, const flo
 }
 
 int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const PackedOp* A, const PackedOp* B,
-                          const GemmEpilogue& epi) {
+                          const GemmEpilogue& epi, uint32_t force_splits) {
   EncodeTiledFn enc;
   int rc = get_encoder(ctx, &enc);
   if (rc) return rc;
@@ -893,7 +912,7 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
                                                       aligned16(epi.bias) && aligned16(epi.c_prev) && aligned16(epi.c_out) && aligned16(epi.h_out)),
                 "tensor GEMM: the LSTM-cell epilogue needs whole tiles of interleaved gate rows and 16-byte aligned tensors");
   // Split K when the output has too few tiles to occupy the SMs (e.g. dx = W^T dgate: 16-32 tiles, K = 4096).
-  uint32_t S = dyb200_tc_splits(ctx, M, N, kb_total);
+  uint32_t S = force_splits ? (force_splits < kb_total ? force_splits : kb_total) : dyb200_tc_splits(ctx, M, N, kb_total);
   uint32_t kb_per_split = (kb_total + S - 1) / S;
   S = (kb_total + kb_per_split - 1) / kb_per_split;
   GemmEpilogue kepi = epi;

@@ -247,6 +247,32 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_ids(const uint32_t* __res
   }
 }
 
+// Merges the sorted runs of k_sort_ids (run p = positions [p kSortMax, ...), sorted by (id, position)) into one sorted list:
+// one thread per element, whose place is the number of smaller keys in every run.  Positions grow with the run number, so
+// among equal ids the earlier run comes first: runs before the element's own count their ids <= id, later runs their ids < id.
+__global__ void __launch_bounds__(256) k_merge_runs(const uint32_t* __restrict__ pos_run, const uint32_t* __restrict__ id_run,
+                                                   uint32_t n, uint32_t* __restrict__ pos_out, uint32_t* __restrict__ id_out) {
+  dyb_grid_dep_sync();
+  const uint32_t e = blockIdx.x * 256 + threadIdx.x;
+  if (e >= n) return;
+  const uint32_t p = e / kSortMax, id = id_run[e];
+  const uint32_t npass = (n + kSortMax - 1) / kSortMax;
+  uint32_t rank = e - p * kSortMax;
+  for (uint32_t q = 0; q < npass; ++q) {
+    if (q == p) continue;
+    const uint32_t* run = id_run + (size_t)q * kSortMax;
+    uint32_t lo = 0, hi = min((uint32_t)kSortMax, n - q * kSortMax);
+    const uint32_t bound = q < p ? id + 1 : id;   // count ids < bound  (id + 1 does not wrap: ids are below the vocabulary size)
+    while (lo < hi) {
+      const uint32_t mid = (lo + hi) >> 1;
+      if (run[mid] < bound) lo = mid + 1; else hi = mid;
+    }
+    rank += lo;
+  }
+  pos_out[rank] = pos_run[e];
+  id_out[rank] = id;
+}
+
 __device__ __forceinline__ void add4(float4& a, const float4& b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
 
 // Pass A: one warp per (chunk, slice).  A run that starts in the chunk begins from the table row
@@ -322,34 +348,64 @@ __global__ void __launch_bounds__(256) k_chunk_combine(float* __restrict__ all_g
     if (id_at[k1] != id) continue;                         // last run of the chunk does not continue
     if (id_at[k0] == id && k0 > 0 && id_at[k0 - 1] == id) continue;   // it started earlier: not the owner
     float4 acc = ld4(tail + ((size_t)c * slices + sl) * 128 + lane * 4);
-    for (uint32_t c2 = c + 1; c2 < nchunks && id_at[c2 * kChunk] == id; ++c2)
-      add4(acc, ld4(head + ((size_t)c2 * slices + sl) * 128 + lane * 4));
+    // (a frequent id runs over hundreds of chunks: eight pieces are requested together, the adds stay in chunk order)
+    uint32_t c2 = c + 1;
+    while (c2 < nchunks && id_at[c2 * kChunk] == id) {
+      float4 piece[8];
+      uint32_t m = 0;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool more = c2 + u < nchunks && id_at[(c2 + u) * kChunk] == id && m == (uint32_t)u;
+        if (more) { piece[u] = ld4(head + ((size_t)(c2 + u) * slices + sl) * 128 + lane * 4); ++m; }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if ((uint32_t)u < m) add4(acc, piece[u]);
+      c2 += m;
+    }
     st4(all_grads + (size_t)id * E + col, acc);
   }
 }
 
 }  // namespace
 
-// Load-balanced path (rows that are multiples of 4 floats): scratch holds pos_sorted[n], id_at[n] (all passes side by side) and
-// two partial buffers of nchunks * slices * 128 floats for one pass of at most kSortMax ids.
+// Load-balanced path (rows that are multiples of 4 floats).  Up to kMergeMaxIds ids the sorted runs of the passes are merged
+// into one sorted list and added in ONE pair of launches; scratch then holds pos / id of the runs and of the merged list and
+// two partial buffers of nchunks * slices * 128 floats for all n ids.  Longer lists go pass after pass (scratch: the runs and
+// the partial buffers of one pass).
+constexpr uint32_t kMergeMaxIds = 1u << 18;
 static size_t chunked_scratch_bytes(uint32_t n, uint32_t E) {
-  const uint32_t np = n < (uint32_t)kSortMax ? n : (uint32_t)kSortMax;
+  const bool merged = n > (uint32_t)kSortMax && n <= kMergeMaxIds;
+  const uint32_t np = (n < (uint32_t)kSortMax || merged) ? n : (uint32_t)kSortMax;
   uint32_t nchunks = (np + kChunk - 1) / kChunk, slices = (E + 127) / 128;
-  return ((size_t)2 * n * sizeof(uint32_t) + 512) + (size_t)2 * nchunks * slices * 128 * sizeof(float) + 512;
+  return ((size_t)(merged ? 4 : 2) * n * sizeof(uint32_t) + 512) + (size_t)2 * nchunks * slices * 128 * sizeof(float) + 512;
 }
 static int scatter_run_chunked(dyb200_ctx* ctx, unsigned n, const unsigned* ids_dev, const float* g, float* all_grads,
                                unsigned E, unsigned vocab, void* scratch) {
   const uint32_t slices = (E + 127) / 128;
   const uint32_t npass = (n + kSortMax - 1) / kSortMax;
+  const bool merged = npass > 1 && n <= kMergeMaxIds;
   uint32_t* pos_all = (uint32_t*)scratch;
   uint32_t* id_all = pos_all + n;
-  const uint32_t np_max = n < (uint32_t)kSortMax ? n : (uint32_t)kSortMax;
-  float* head = (float*)(((uintptr_t)(id_all + n) + 255) & ~(uintptr_t)255);
+  uint32_t* pos_m = id_all + n;                      // (merged only)
+  uint32_t* id_m = pos_m + n;
+  const uint32_t np_max = (n < (uint32_t)kSortMax || merged) ? n : (uint32_t)kSortMax;
+  float* head = (float*)(((uintptr_t)(id_all + (merged ? 3 : 1) * (size_t)n) + 255) & ~(uintptr_t)255);
   float* tail = head + (size_t)((np_max + kChunk - 1) / kChunk) * slices * 128;
-  // every pass's ids are sorted in the same launch (one CTA each); the adds then run pass after pass, so that a table row
-  // that several passes touch receives their sums in pass order
+  // every pass's ids are sorted in the same launch (one CTA each)
   dyb_launch(k_sort_ids, npass, kSortThreads, 0, ctx, ids_dev, n, vocab, pos_all, id_all, ctx->dev_flags);
   DYB_LAUNCHED(ctx);
+  if (merged) {
+    dyb_launch(k_merge_runs, (n + 255) / 256, 256, 0, ctx, (const uint32_t*)pos_all, (const uint32_t*)id_all, n, pos_m, id_m);
+    DYB_LAUNCHED(ctx);
+    const size_t work = (size_t)((n + kChunk - 1) / kChunk) * slices;
+    dyb_launch(k_chunk_add, stream_grid(ctx, work, 8), 256, 0, ctx, g, all_grads, E, pos_m, id_m, n, slices, head, tail);
+    DYB_LAUNCHED(ctx);
+    dyb_launch(k_chunk_combine, stream_grid(ctx, work, 8), 256, 0, ctx, all_grads, E, id_m, n, slices, head, tail);
+    DYB_LAUNCHED(ctx);
+    return DYB200_OK;
+  }
+  // the adds run pass after pass, so that a table row that several passes touch receives their sums in pass order
   for (uint32_t base = 0; base < n; base += kSortMax) {
     uint32_t np = n - base < (uint32_t)kSortMax ? n - base : (uint32_t)kSortMax;
     uint32_t nchunks = (np + kChunk - 1) / kChunk;

@@ -690,16 +690,20 @@ int dyb200_vanilla_lstm_bwd_fused_at(const dyb200_tensor* x, const dyb200_tensor
   if ((rc = dyb200_tc_pack_flush(ctx, &batch))) return rc;
   if (tensor_path) {
     // the gate gradient is split once per layout and shared by the four products
+    // (K splits: those of the sequence kernel where it could run this shape, so that the two forms add the same partial
+    // sums in the same order and agree bit for bit; the cost model's choice otherwise)
+    LstmBwdTiling tl;
+    const uint32_t fs = (tiled && attrs->weightnoise_std == 0.f && dyb200_lstm_bwd_tiling(ctx, I, H, B, &tl)) ? tl.S : 0;
     if (dx && dh_tm1) {
       // dx and dh_tm1 in one product: [Wx; Wh]^T (I + H rows) times the gate gradient, rows routed to the two tensors
       if ((rc = dyb200_tc_param2(ctx, Wx->v, I, Wh->v, H, G, true, G, &wxT))) return rc;
       GemmEpilogue e{mx ? EPI_ACCUM_MASK : EPI_ACCUM, dx->v, I, nullptr, 0, 0.f, mx, I, mx_full};
       e.split_m = I; e.C2 = dh_tm1->v; e.ldc2 = H; e.maskC2 = mh; e.maskc2_ld = H; e.maskc2_full = mh_full;
-      if ((rc = dyb200_tc_gemm_packed(ctx, I + H, B, 1, &wxT, &dn, e))) return rc;
+      if ((rc = dyb200_tc_gemm_packed(ctx, I + H, B, 1, &wxT, &dn, e, fs))) return rc;
     } else if (dx) {
       if ((rc = dyb200_tc_param(ctx, Wx->v, G, true, I, G, &wxT))) return rc;
       GemmEpilogue e{mx ? EPI_ACCUM_MASK : EPI_ACCUM, dx->v, I, nullptr, 0, 0.f, mx, I, mx_full};
-      if ((rc = dyb200_tc_gemm_packed(ctx, I, B, 1, &wxT, &dn, e))) return rc;
+      if ((rc = dyb200_tc_gemm_packed(ctx, I, B, 1, &wxT, &dn, e, fs))) return rc;
     } else if (dh_tm1) {
       if ((rc = dyb200_tc_param(ctx, Wh->v, G, true, H, G, &whT))) return rc;
       GemmEpilogue e{mh ? EPI_ACCUM_MASK : EPI_ACCUM, dh_tm1->v, H, nullptr, 0, 0.f, mh, H, mh_full};

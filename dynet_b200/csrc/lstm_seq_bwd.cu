@@ -17,10 +17,10 @@
 // Every wait is bounded: on expiry the CTA sets DYB200_FLAG_WAIT_TIMEOUT, stops storing, keeps signalling so that nothing
 // else stalls longer than its own bound, frees its TMEM and returns.
 //
-// Values: the cell arithmetic is that of the per-step pass (lstm_cell.cuh), the products use the same k-blocks and
-// accumulation chains (cut every kChunkKB k-blocks) but their own number of K splits (as many as keep all CTAs resident),
-// added in split order; the bias gradient adds per-tile row sums in a fixed order.  So results are reproducible from run
-// to run and agree with the per-step calls up to the rounding of differently associated fp32 sums.
+// Values are bit for bit those of the per-step calls: the cell arithmetic of the per-step pass (lstm_cell.cuh), per-tile row
+// sums of dgates added per step in tile order and the steps in sweep order (k_seq_db_reduce), the same k-blocks in the same
+// accumulation chains (cut every kChunkKB k-blocks), the same K splits (dyb200_lstm_bwd_tiling, which the per-step call
+// also asks) added in split order, the epilogue of the product kernels (epilogue_pass).
 #include "lstm_cell.cuh"
 #include "seq_dev.cuh"
 
@@ -577,32 +577,18 @@ int dyb200_vanilla_lstm_seq_bwd(const dyb200_tensor* x_all, const dyb200_tensor*
 
   // ---- all steps in one kernel, when its CTAs can all be resident ----
   uint32_t first = T;   // steps [0, first) run as per-step calls below
-  // Tile width and chains per CTA: two column blocks per CTA whenever the batch has an even number of them (128 columns:
-  // two blocks of 64), so that each CTA alternates between two independent chains.
-  const uint32_t bn = (B >= 256 && B % 128 == 0) ? 128u : 64u;
+  LstmBwdTiling tl{64, 1, 1};
   const uint32_t Imin = I < H ? I : H;
   const double flops_small = 2.0 * Imin * (double)B * G;
-  bool persistent = ctx->seq_kernels && deferred && dx_all && T >= 2 && T <= kDbMaxSteps && attrs->weightnoise_std == 0.f && H % 64 == 0 && I % 4 == 0 &&
-                    B % bn == 0 && B / bn <= 32 && dyb200_tc_eligible(Imin, B, flops_small) && dyb200_tc_eligible(G, Imin, flops_small) &&
-                    Wx->nd == 2 && Wx->d[0] == G && Wx->d[1] == I && Wh->nd == 2 && Wh->d[0] == G && Wh->d[1] == H && t_size(db) == G &&
-                    aligned16(gates_all->v) && aligned16(c_all->v) && aligned16(c0->v) && aligned16(dh_all->v) && aligned16(dc_all->v) && aligned16(dx_all->v) &&
-                    (!mx || (aligned16(mx) && aligned16(mh) && (mask_x->bd == B || mask_x->bd == 1) && (mask_h->bd == B || mask_h->bd == 1) &&
-                             t_dim(mask_x, 0) == I && t_dim(mask_h, 0) == H));
-  uint32_t S = 1;
+  const bool persistent = ctx->seq_kernels && deferred && dx_all && T >= 2 && T <= kDbMaxSteps && attrs->weightnoise_std == 0.f &&
+                          dyb200_lstm_bwd_tiling(ctx, I, H, B, &tl) && dyb200_tc_eligible(Imin, B, flops_small) &&
+                          dyb200_tc_eligible(G, Imin, flops_small) && Wx->nd == 2 && Wx->d[0] == G && Wx->d[1] == I && Wh->nd == 2 &&
+                          Wh->d[0] == G && Wh->d[1] == H && t_size(db) == G && aligned16(gates_all->v) && aligned16(c_all->v) &&
+                          aligned16(c0->v) && aligned16(dh_all->v) && aligned16(dc_all->v) && aligned16(dx_all->v) &&
+                          (!mx || (aligned16(mx) && aligned16(mh) && (mask_x->bd == B || mask_x->bd == 1) &&
+                                   (mask_h->bd == B || mask_h->bd == 1) && t_dim(mask_x, 0) == I && t_dim(mask_h, 0) == H));
+  const uint32_t bn = tl.bn, ncb = tl.ncb, S = tl.S;
   const uint32_t tiles_m = (I + H + BM - 1) / BM, tiles_n = B / bn, kb = G / 32;
-  const uint32_t ncb = tiles_n % 2 == 0 ? 2u : 1u;
-  if (persistent) {
-    // as many K splits as keep every CTA resident (one per SM), at least 8 k-blocks each
-    const uint32_t groups = tiles_m * (tiles_n / ncb);
-    S = groups ? (uint32_t)ctx->sm_count / groups : 0;
-    if (S > 8) S = 8;
-    while (S > 1 && kb / S < 8) --S;
-    if (S >= 1) {
-      const uint32_t per = (kb + S - 1) / S;
-      S = (kb + per - 1) / per;
-    }
-    persistent = S >= 1 && tiles_m * tiles_n <= 160;
-  }
   if (persistent) {
     { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
     DYB_CHECK_ARG(ctx, dyb200_wgrad_rows(deferred) == G, "lstm_seq_bwd: the deferred accumulator has %u rows, the layer %u", dyb200_wgrad_rows(deferred), G);

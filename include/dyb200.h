@@ -318,18 +318,17 @@ int dyb200_vanilla_lstm_seq_fwd(const dyb200_tensor* x_all, const dyb200_tensor*
                                 dyb200_tensor* gates_all, dyb200_tensor* c_all, dyb200_tensor* h_all, struct dyb200_wgrad* deferred,
                                 uint32_t steps, dyb200_ctx* ctx);
 /* The backward pass of the same layer over all time steps, in sweep order (dynet/exec.cc:96-140 visits the nodes of step
- * steps - 1 first): equivalent to calling dyb200_vanilla_lstm_bwd_fused_at for t = steps - 1 .. 0 with
+ * steps - 1 first): equivalent, bit for bit, to calling dyb200_vanilla_lstm_bwd_fused_at for t = steps - 1 .. 0 with
  * gates / c_t / dEdh / dEdc = the columns of step t of gates_all / c_all / dh_all / dc_all, dx = the columns of step t of
  * dx_all, dh_tm1 / dc_tm1 = the columns of step t - 1 of dh_all / dc_all (NULL at t = 0; h_tm1 / c_tm1 are h0 / c0 there) and
- * deferred_col = t * batch (the same values up to fp32 rounding, see below).  dh_all / dc_all hold dE/dh_t and dE/dc_t of every
+ * deferred_col = t * batch.  dh_all / dc_all hold dE/dh_t and dE/dc_t of every
  * step as left by the layers above (the recurrent parts are accumulated into them on the way); dx_all accumulates.  With deferred the columns of the accumulator must hold the
  * layer inputs placed by dyb200_vanilla_lstm_seq_fwd / _fwd_fused_at, and dWx / dWh may be NULL; without it every step adds
  * its weight gradients to dWx / dWh at once.  When the shape allows (as for the forward call; deferred and dx_all given), the
  * steps run inside ONE kernel whose CTAs stay on the GPU: the cell pass and the [Wx; Wh]^T dgates product of a step hand
  * over through counters in device memory, and every CTA alternates between two independent blocks of batch columns so that
- * one block's hand-overs hide behind the other's products.  The kernel chooses its own number of K splits, so its results
- * agree with the per-step calls up to the rounding of differently associated fp32 sums (the forward call is bit-identical).
- * dyb200_ctx_sequence_kernels(ctx, 0) forces the per-step form. */
+ * one block's hand-overs hide behind the other's products (the per-step call uses the same K splits for such shapes, which
+ * keeps the two forms bit-identical).  dyb200_ctx_sequence_kernels(ctx, 0) forces the per-step form. */
 int dyb200_vanilla_lstm_seq_bwd(const dyb200_tensor* x_all, const dyb200_tensor* h0, const dyb200_tensor* c0,
                                 const dyb200_tensor* Wx, const dyb200_tensor* Wh, const dyb200_tensor* mask_x,
                                 const dyb200_tensor* mask_h, const dyb200_lstm_gates_attrs* attrs, const dyb200_tensor* gates_all,

@@ -501,7 +501,8 @@ def test_lookup_errors(g, capi):
         g.ctx().fwd("lookup", [], g.T(out_, [4], 2), capi.LookupAttrs(tab_.data_ptr(), 9, p, 1, 1.0), aux.data_ptr())
 
 
-@pytest.mark.parametrize("E,V,n", [(4, 9, 1), (4, 9, 5), (128, 1000, 512), (512, 5000, 4096), (6, 50, 77), (64, 300, 9000)])
+@pytest.mark.parametrize("E,V,n", [(4, 9, 1), (4, 9, 5), (128, 1000, 512), (512, 5000, 4096), (6, 50, 77), (64, 300, 9000),
+                                   (128, 2000, 50000)])   # (the last: 13 sorted runs merged, the most frequent id spans ~150 chunks)
 def test_lookup_scatter_add(oracle, g, E, V, n):
     r = rng(141)
     ids = zipf_ids(r, n, V)
