@@ -541,12 +541,12 @@ def run_tagger_gpu(args):
             ms = float(t.item())
         return ms, toks, last
 
-    l0 = model.ctx.launches()
+    l0 = model.launches()
     W = max(3, args.warmup)
     for k in range(W):
         step(k)
     torch.cuda.synchronize()
-    launches_per_step = (model.ctx.launches() - l0) // W
+    launches_per_step = (model.launches() - l0) // W
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -567,7 +567,7 @@ def run_tagger_gpu(args):
     model.time_movers(False)
     mv /= reps
     host_ms /= reps
-    errs = model.ctx.device_errors()
+    errs = model.device_errors()
     n_local = float(np.mean([int(b[0].sum()) for b in batches]))
     replica_diff = 0.0
     if world > 1:

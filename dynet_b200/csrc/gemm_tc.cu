@@ -1148,21 +1148,22 @@ int dyb200_wgrad_pack_a_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const floa
   return DYB200_OK;
 }
 bool dyb200_wgrad_x_planes(const dyb200_wgrad* w, uint32_t col, uint32_t k, PackedOp* out) {
-  if (!w || !w->X.hi || k != w->step || (uint64_t)col + k > w->x_cols) return false;
+  if (!w || !w->X.hi || (w->step && k != w->step) || (uint64_t)col + k > w->x_cols) return false;
   *out = w->X;
   out->rows = k; out->K = w->N[0];
   out->hi += (size_t)col * w->X.pitch; out->lo += (size_t)col * w->X.pitch;
   return true;
 }
 bool dyb200_wgrad_h_planes(const dyb200_wgrad* w, uint32_t col, uint32_t k, PackedOp* out) {
-  if (!w || !w->Hs.hi || k != w->step || w->h_col != col || (uint64_t)col + k > w->x_cols) return false;
+  if (!w || !w->Hs.hi || (w->step && k != w->step) || w->h_col != col || (uint64_t)col + k > w->x_cols) return false;
   *out = w->Hs;
   out->rows = k; out->K = w->N[1];
   out->hi += (size_t)col * w->Hs.pitch; out->lo += (size_t)col * w->Hs.pitch;
   return true;
 }
 bool dyb200_wgrad_next_h(dyb200_wgrad* w, uint32_t col, uint32_t k, GemmEpilogue* epi) {
-  if (!w || !w->Hs.hi || k != w->step || (uint64_t)col + 2 * (uint64_t)k > w->x_cols) return false;
+  // (all k columns of h_t are written at the next step's position; with steps of varying width the next step may use fewer)
+  if (!w || !w->Hs.hi || (w->step && k != w->step) || (uint64_t)col + 2 * (uint64_t)k > w->x_cols) return false;
   const uint32_t next = col + k;
   epi->hn_hi = w->Hs.hi + (size_t)next * w->Hs.pitch; epi->hn_lo = w->Hs.lo + (size_t)next * w->Hs.pitch; epi->hn_pitch = w->Hs.pitch;
   epi->ht_hi = w->B[1].hi + next; epi->ht_lo = w->B[1].lo + next; epi->ht_pitch = w->Kcap;
@@ -1247,9 +1248,10 @@ int dyb200_wgrad_push(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda,
 // C0 += A * B0^T (and C1 += A * B1^T) over everything pushed since the last flush; empties the accumulator.
 int dyb200_wgrad_pack_inputs(dyb200_wgrad* w, const dyb200_tensor* x_all, const dyb200_tensor* mask_x, uint32_t step, dyb200_ctx* ctx) {
   { int rc0__ = dyb200_scratch_begin(ctx); if (rc0__) return rc0__; }
-  DYB_CHECK_ARG(ctx, w && x_all && x_all->v && step > 0, "wgrad_pack_inputs: null argument");
+  DYB_CHECK_ARG(ctx, w && x_all && x_all->v, "wgrad_pack_inputs: null argument");
+  DYB_CHECK_ARG(ctx, step > 0 || !mask_x, "wgrad_pack_inputs: steps of varying width (step = 0) take no mask");
   const uint32_t I = t_rows(x_all), n = x_all->bd;
-  DYB_CHECK_ARG(ctx, t_cols(x_all) == 1 && I == w->N[0] && w->N[1] > 0 && n <= w->Kcap && n % step == 0,
+  DYB_CHECK_ARG(ctx, t_cols(x_all) == 1 && I == w->N[0] && w->N[1] > 0 && n <= w->Kcap && (step == 0 || n % step == 0),
                 "wgrad_pack_inputs: x is %u x %u, the accumulator expects %u rows, at most %u columns, whole steps of %u", I, n, w->N[0], w->Kcap, step);
   DYB_CHECK_ARG(ctx, !mask_x || (t_rows(mask_x) == I && (mask_x->bd == step || mask_x->bd == 1)), "wgrad_pack_inputs: mask shape mismatch");
   if (!w->X.hi) {   // first use: planes for the forward operands of every column
@@ -1270,8 +1272,8 @@ int dyb200_wgrad_pack_inputs(dyb200_wgrad* w, const dyb200_tensor* x_all, const 
   PackJobs batch;
   dyb200_tc_pack_begin(&batch);
   // forward operand: row = column of the sequence, reduction index = input feature; weight-gradient operand: the transpose
-  int rc = pack(ctx, x_all->v, I, 1, n, I, mk, I, full, w->X.hi, w->X.lo, w->X.pitch, &batch, step);
-  if (!rc) rc = pack(ctx, x_all->v, I, 0, I, n, mk, I, full, w->B[0].hi, w->B[0].lo, w->Kcap, &batch, step);
+  int rc = pack(ctx, x_all->v, I, 1, n, I, mk, I, full, w->X.hi, w->X.lo, w->X.pitch, &batch, step ? step : n);
+  if (!rc) rc = pack(ctx, x_all->v, I, 0, I, n, mk, I, full, w->B[0].hi, w->B[0].lo, w->Kcap, &batch, step ? step : n);
   if (!rc) rc = pack_flush_impl(ctx, &batch);
   if (rc) return rc;
   w->x_cols = n; w->step = step; w->h_col = 0xffffffffu;

@@ -90,12 +90,21 @@ struct Tagger {
   cudaEvent_t ev[8];
   cudaEvent_t upload_ev = nullptr;
   bool upload_pending = false;
+  // The two directions are independent chains of small launches: the reverse direction runs on a stream (and a library
+  // context: scratch arena, split-weight cache) of its own, beside the forward direction on the caller's stream.
+  Device_GPU dev2;
+  cudaStream_t stream2 = nullptr;
+  cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
   double host_schedule_ms = 0.0;
   ~Tagger() {
     for (int k = 0; k < 2; ++k) if (d[k].wg) dyb200_wgrad_destroy(d[k].wg);
     if (tbl_host) cudaFreeHost(tbl_host);
     for (auto& e : ev) if (e) cudaEventDestroy(e);
     if (upload_ev) cudaEventDestroy(upload_ev);
+    if (fork_ev) cudaEventDestroy(fork_ev);
+    if (join_ev) cudaEventDestroy(join_ev);
+    if (dev2.ctx) dyb200_ctx_destroy(dev2.ctx);
+    if (stream2) cudaStreamDestroy(stream2);
   }
 };
 
@@ -141,6 +150,8 @@ void tagger_pass(Tagger& m, const PassArgs& a) {
   const dyb200h_tagger_config& c = m.c;
   const uint32_t E = c.E, H = c.H, TH = c.TH, NT = c.NT, V = c.V, S = a.S;
   const Device_GPU& dev = m.dev;
+  const Device_GPU* dv[2] = {&m.dev, &m.dev2};   // library context of each direction
+  const cudaStream_t st2 = m.stream2;
   cudaStream_t st = m.stream;
   if (S == 0) throw std::invalid_argument("tagger: empty mini-batch");
   if (S > m.max_sent) throw std::invalid_argument("tagger: more sentences than the workspace was planned for");
@@ -200,12 +211,20 @@ void tagger_pass(Tagger& m, const PassArgs& a) {
   auto col = [](float* base, uint32_t rows, uint32_t c0, uint32_t n) { return Tensor(Dim({rows}, n), base + (size_t)c0 * rows); };
 
   // ---------------- forward ----------------
+  CU(cudaEventRecord(m.fork_ev, st));          // (the uploads above are on the caller's stream)
+  CU(cudaStreamWaitEvent(st2, m.fork_ev, 0));
   for (int dr = 0; dr < 2; ++dr) {
     Dir& d = m.d[dr];
+    const Device_GPU& dev = *dv[dr];
     LookupNode look(tEmb, nullptr, N);       // all lookups of a direction are one batched node
     look.aux_mem = d.ids;
     Tensor xall(Dim({E}, N), d.x);
     look.forward_dev_impl(dev, {}, xall);
+    // the inputs of all steps of the direction exist now: one launch splits them into the operand planes of the gate products
+    // and of the weight-gradient product; each step's epilogue then leaves h_t as the next step's operand planes, so the
+    // steps launch no operand split of their own
+    const dyb200_tensor cxall = to_c(xall);
+    throw_status(dev, dyb200_wgrad_pack_inputs(d.wg, &cxall, nullptr, 0, dev.ctx));
     Tensor tWx(Dim({4 * H, E}), m.p[P_WXF + 3 * dr]), tWh(Dim({4 * H, H}), m.p[P_WHF + 3 * dr]), tb(Dim({4 * H}), m.p[P_BF + 3 * dr]);
     const dyb200_tensor cWx = to_c(tWx), cWh = to_c(tWh), cb = to_c(tb);
     for (uint32_t k = 0; k < Lmax; ++k) {
@@ -214,9 +233,11 @@ void tagger_pass(Tagger& m, const PassArgs& a) {
       const dyb200_tensor chp = to_c(k ? col(d.h, H, prefix[k - 1], B) : Tensor(Dim({H}, B), m.zeros));
       const dyb200_tensor ccp = to_c(k ? col(d.c, H, prefix[k - 1], B) : Tensor(Dim({H}, B), m.zeros));
       dyb200_tensor cg = to_c(col(d.gates, 4 * H, prefix[k], B)), cc = to_c(col(d.c, H, prefix[k], B)), ch = to_c(col(d.h, H, prefix[k], B));
-      throw_status(dev, dyb200_vanilla_lstm_fwd_fused(&cx, &chp, &ccp, &cWx, &cWh, &cb, nullptr, nullptr, &at, &cg, &cc, &ch, dev.ctx));
+      throw_status(dev, dyb200_vanilla_lstm_fwd_fused_at(&cx, &chp, &ccp, &cWx, &cWh, &cb, nullptr, nullptr, &at, &cg, &cc, &ch, d.wg, prefix[k], dev.ctx));
     }
   }
+  CU(cudaEventRecord(m.join_ev, st2));
+  CU(cudaStreamWaitEvent(st, m.join_ev, 0));
   // combine_tensors: the hidden states of all tokens, token-major
   for (int dr = 0; dr < 2; ++dr) {
     if (m.time_movers) CU(cudaEventRecord(m.ev[2 * dr], st));
@@ -261,8 +282,11 @@ void tagger_pass(Tagger& m, const PassArgs& a) {
     if (m.time_movers) CU(cudaEventRecord(m.ev[5 + 2 * dr], st));
   }
   Tensor gEmb(Dim({E}, V), m.g[P_EMB]);
+  CU(cudaEventRecord(m.fork_ev, st));
+  CU(cudaStreamWaitEvent(st2, m.fork_ev, 0));
   for (int dr = 0; dr < 2; ++dr) {
     Dir& d = m.d[dr];
+    const Device_GPU& dev = *dv[dr];
     Tensor tWx(Dim({4 * H, E}), m.p[P_WXF + 3 * dr]), tWh(Dim({4 * H, H}), m.p[P_WHF + 3 * dr]);
     Tensor gb(Dim({4 * H}), m.g[P_BF + 3 * dr]);
     const dyb200_tensor cWx = to_c(tWx), cWh = to_c(tWh);
@@ -276,12 +300,20 @@ void tagger_pass(Tagger& m, const PassArgs& a) {
       const dyb200_tensor cdh = to_c(col(d.dh, H, prefix[k], B)), cdc = to_c(col(d.dc, H, prefix[k], B));
       dyb200_tensor cdx = to_c(col(d.dx, E, prefix[k], B));
       dyb200_tensor cdhp = to_c(k ? col(d.dh, H, prefix[k - 1], B) : Tensor()), cdcp = to_c(k ? col(d.dc, H, prefix[k - 1], B) : Tensor());
-      // (weight gradients: the operands of this step are appended to the direction's accumulator, one product at the end)
-      throw_status(dev, dyb200_vanilla_lstm_bwd_fused(&cx, &chp, &ccp, &cWx, &cWh, nullptr, nullptr, &cg, &cc, &cdh, &cdc, &cdx,
-                                                      k ? &cdhp : nullptr, k ? &cdcp : nullptr, nullptr, nullptr, &cgb, &at, d.wg, dev.ctx));
+      // (weight gradients: the gate gradient of this step goes to the step's columns of the direction's accumulator, where the
+      // forward pass left the inputs; one product at the end)
+      throw_status(dev, dyb200_vanilla_lstm_bwd_fused_at(&cx, &chp, &ccp, &cWx, &cWh, nullptr, nullptr, &cg, &cc, &cdh, &cdc, &cdx,
+                                                         k ? &cdhp : nullptr, k ? &cdcp : nullptr, nullptr, nullptr, &cgb, &at, d.wg,
+                                                         prefix[k], dev.ctx));
     }
     throw_status(dev, dyb200_wgrad_flush(d.wg, m.g[P_WXF + 3 * dr], 4 * H, m.g[P_WHF + 3 * dr], 4 * H, dev.ctx));
-    // the lookups' accumulate_grad calls, folded into one over the direction's columns (step order)
+  }
+  CU(cudaEventRecord(m.join_ev, st2));
+  CU(cudaStreamWaitEvent(st, m.join_ev, 0));
+  // the lookups' accumulate_grad calls, folded into one per direction over its columns (step order); both add into the one
+  // table gradient, so they run one after the other on the caller's stream
+  for (int dr = 0; dr < 2; ++dr) {
+    Dir& d = m.d[dr];
     LookupNode look(tEmb, nullptr, N);
     look.aux_mem = d.ids;
     Tensor tdx(Dim({E}, N), d.dx);
@@ -331,7 +363,14 @@ int dyb200h_tagger_create(const dyb200h_tagger_config* c, float* params, float* 
   plan(*c, max_sentences, max_tokens, m, (char*)workspace);
   dyb200_ctx_param_cache(ctx, 1);   // this driver owns the updates (dyb200h_tagger_update), so split weights can be reused
   int rc = DYB200_OK;
-  for (int k = 0; k < 2 && !rc; ++k) rc = dyb200_wgrad_create(ctx, 4 * c->H, c->E, c->H, max_tokens, &m->d[k].wg);
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) rc = DYB200_ECUDA;
+  if (!rc && cudaStreamCreateWithFlags(&m->stream2, cudaStreamNonBlocking) != cudaSuccess) rc = DYB200_ECUDA;
+  if (!rc) rc = dyb200_ctx_create(device, m->stream2, &m->dev2.ctx);
+  if (!rc) dyb200_ctx_param_cache(m->dev2.ctx, 1);
+  if (!rc && (cudaEventCreateWithFlags(&m->fork_ev, cudaEventDisableTiming) != cudaSuccess ||
+              cudaEventCreateWithFlags(&m->join_ev, cudaEventDisableTiming) != cudaSuccess)) rc = DYB200_ECUDA;
+  for (int k = 0; k < 2 && !rc; ++k) rc = dyb200_wgrad_create(k ? m->dev2.ctx : ctx, 4 * c->H, c->E, c->H, max_tokens, &m->d[k].wg);
   const size_t host_bytes = 8 * (size_t)max_tokens * sizeof(float*) + (size_t)max_tokens * sizeof(size_t) + 3 * (size_t)max_tokens * sizeof(uint32_t);
   if (!rc && cudaMallocHost((void**)&m->tbl_host, host_bytes) != cudaSuccess) { cudaGetLastError(); rc = DYB200_ENOMEM; }
   for (auto& e : m->ev) if (!rc && cudaEventCreate(&e) != cudaSuccess) rc = DYB200_ECUDA;
@@ -366,7 +405,17 @@ int dyb200h_tagger_update(void* h) {
   Tagger* m = (Tagger*)h;
   int rc = dyb200_sgd_update(m->params, m->grads, tagger_sizes(m->c, nullptr), m->c.lr, m->c.clip, m->scalars, m->dev.ctx);
   if (rc) m->err = dyb200_last_error(m->dev.ctx);
+  dyb200_ctx_params_changed(m->dev2.ctx);   // (the second direction's context keeps its own split weights)
   return rc;
+}
+
+// Launch count and device error flags of the second direction's context (the caller's context reports its own).
+int dyb200h_tagger_side_stats(void* h, uint64_t* launches, uint32_t* error_flags) {
+  Tagger* m = (Tagger*)h;
+  if (!m) return DYB200_EINVAL;
+  if (launches) *launches = dyb200_ctx_launch_count(m->dev2.ctx);
+  if (error_flags) return dyb200_ctx_check_device_errors(m->dev2.ctx, error_flags);
+  return DYB200_OK;
 }
 
 // Measurement hooks: with timing on, the four mover calls of a pass are bracketed by CUDA events; dyb200h_tagger_mover_ms

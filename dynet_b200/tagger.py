@@ -45,6 +45,8 @@ def _bind(L):
     L.dyb200h_tagger_time_movers.argtypes = [C.c_void_p, C.c_int]
     L.dyb200h_tagger_mover_ms.restype = C.c_int
     L.dyb200h_tagger_mover_ms.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_double)]
+    L.dyb200h_tagger_side_stats.restype = C.c_int
+    L.dyb200h_tagger_side_stats.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]
     L._tagger_bound = True
     return L
 
@@ -158,6 +160,18 @@ class Tagger:
         ms, host = (C.c_float * 4)(), C.c_double(0)
         self._check(self.H.dyb200h_tagger_mover_ms(self.h, ms, C.byref(host)))
         return [float(v) for v in ms], float(host.value)
+
+    def launches(self):
+        """Kernel launches so far, both directions' contexts together."""
+        n = C.c_uint64(0)
+        self._check(self.H.dyb200h_tagger_side_stats(self.h, C.byref(n), None))
+        return self.ctx.launches() + int(n.value)
+
+    def device_errors(self):
+        """Device error flags of both contexts (waits for the work issued so far)."""
+        f = C.c_uint32(0)
+        self._check(self.H.dyb200h_tagger_side_stats(self.h, None, C.byref(f)))
+        return self.ctx.device_errors() | int(f.value)
 
     def grads_host(self):
         flat = self.grads.cpu().numpy()

@@ -297,7 +297,10 @@ int dyb200_wgrad_push(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda,
  * with this accumulator for deferred_col = 0, step, 2 step, ... in order, launches no operand split of its own except
  * for h_tm1 of the first step: each step's epilogue also writes h_t .* mask_h as the next step's operand planes.  The pre-split
  * inputs are dropped by dyb200_wgrad_flush (one call per sequence).  The x
- * argument of those calls must be the matching columns of x_all.  Results are bitwise those of the calls without it. */
+ * argument of those calls must be the matching columns of x_all.  Results are bitwise those of the calls without it.
+ * step = 0 (mask_x must be NULL): the time steps have varying widths that never grow - the schedule of the batched executor
+ * for sentences sorted by length (dynet/exec.cc:481-895), where step t uses the first B_t columns of the states of step
+ * t - 1; the calls then pass deferred_col = the sum of the widths before their step. */
 int dyb200_wgrad_pack_inputs(dyb200_wgrad* w, const dyb200_tensor* x_all, const dyb200_tensor* mask_x, uint32_t step, dyb200_ctx* ctx);
 int dyb200_wgrad_flush(dyb200_wgrad* w, float* C0, uint32_t ldc0, float* C1, uint32_t ldc1, dyb200_ctx* ctx);
 
