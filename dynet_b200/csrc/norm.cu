@@ -289,6 +289,107 @@ __global__ void __launch_bounds__(kBlock) k_layer_norm_bwd_x(const float* __rest
   }
 }
 
+// Columns of at most 1024 elements (n % 128 == 0): one WARP per column, the column in the lanes' registers (NV float4 each),
+// both statistics by warp shuffles only - no CTA barrier, eight columns in flight per CTA.  With a CTA per column a
+// 4 KB column paid two block reductions (four barriers) for one 16-byte load per thread.
+template <int NV>
+__global__ void __launch_bounds__(kBlock) k_layer_norm_fwd_warp(const float* __restrict__ x, const float* __restrict__ g,
+                                                                const float* __restrict__ b, float* __restrict__ y,
+                                                                uint32_t n, size_t ncols) {
+  dyb_grid_dep_sync();
+  const uint32_t lane = threadIdx.x & 31, n4 = n / 4;
+  const float fn = (float)n;
+  for (size_t c = (size_t)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); c < ncols; c += (size_t)gridDim.x * (kBlock / 32)) {
+    const float* xc = x + c * n;
+    float4 v[NV];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const uint32_t i = lane + 32 * k;
+      v[k] = i < n4 ? ld4_stream(xc + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    const float mean = warp_sum(s) / fn;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+      if (lane + 32 * k < n4) {
+        const float a = v[k].x - mean, bq = v[k].y - mean, cq = v[k].z - mean, d = v[k].w - mean;
+        q += (a * a + bq * bq) + (cq * cq + d * d);
+      }
+    const float sigma = sqrtf(warp_sum(q) / fn);
+    const float neg = -mean, inv = 1.f / (sigma + 1e-8f);
+    float* yc = y + c * n;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const uint32_t i = lane + 32 * k;
+      if (i < n4) {
+        const float4 gg = ld4(g + 4 * i), bb = ld4(b + 4 * i);
+        st4_stream(yc + 4 * i, make_float4(gg.x * ((v[k].x + neg) * inv) + bb.x, gg.y * ((v[k].y + neg) * inv) + bb.y,
+                                           gg.z * ((v[k].z + neg) * inv) + bb.z, gg.w * ((v[k].w + neg) * inv) + bb.w));
+      }
+    }
+  }
+}
+template <int NV>
+__global__ void __launch_bounds__(kBlock) k_layer_norm_bwd_x_warp(const float* __restrict__ x, const float* __restrict__ g,
+                                                                  const float* __restrict__ dy, float* __restrict__ dx,
+                                                                  uint32_t n, size_t ncols) {
+  dyb_grid_dep_sync();
+  const uint32_t lane = threadIdx.x & 31, n4 = n / 4;
+  const float fn = (float)n;
+  for (size_t c = (size_t)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); c < ncols; c += (size_t)gridDim.x * (kBlock / 32)) {
+    const float* xc = x + c * n;
+    const float* dc = dy + c * n;
+    float* oc = dx + c * n;
+    float4 v[NV], dq[NV];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {   // x and dy of the column are requested together
+      const uint32_t i = lane + 32 * k;
+      v[k] = i < n4 ? ld4_stream(xc + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      dq[k] = i < n4 ? ld4_stream(dc + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    const float mean = warp_sum(s) / fn;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+      if (lane + 32 * k < n4) {
+        const float a = v[k].x - mean, bq = v[k].y - mean, cq = v[k].z - mean, d = v[k].w - mean;
+        q += (a * a + bq * bq) + (cq * cq + d * d);
+      }
+    const float sigma = sqrtf(warp_sum(q) / fn);
+    const float neg = -mean, s2 = sigma + 1e-8f, inv = 1.f / s2;
+    float A = 0.f, Bs = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const uint32_t i = lane + 32 * k;
+      if (i < n4) {
+        const float4 gg = ld4(g + 4 * i);
+        dq[k] = make_float4(dq[k].x * gg.x, dq[k].y * gg.y, dq[k].z * gg.z, dq[k].w * gg.w);
+        A += (dq[k].x * (v[k].x + neg) + dq[k].y * (v[k].y + neg)) + (dq[k].z * (v[k].z + neg) + dq[k].w * (v[k].w + neg));
+        Bs += (dq[k].x + dq[k].y) + (dq[k].z + dq[k].w);
+      }
+    }
+    A = warp_sum(A) * inv * inv;
+    Bs = warp_sum(Bs) * inv;
+    const float sb = (-A) / (2.f * sigma), dmu_n = (-Bs) / fn, two_n = 2.f / fn;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const uint32_t i = lane + 32 * k;
+      if (i < n4) {
+        float4 o = ld4_stream(oc + 4 * i);
+        o.x = ((o.x + two_n * (v[k].x - mean) * sb) + dq[k].x * inv) + dmu_n;
+        o.y = ((o.y + two_n * (v[k].y - mean) * sb) + dq[k].y * inv) + dmu_n;
+        o.z = ((o.z + two_n * (v[k].z - mean) * sb) + dq[k].z * inv) + dmu_n;
+        o.w = ((o.w + two_n * (v[k].w - mean) * sb) + dq[k].w * inv) + dmu_n;
+        st4_stream(oc + 4 * i, o);
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kBlock) k_layer_norm_stats(const float* __restrict__ x, float* __restrict__ stats,
                                                             uint32_t n, size_t ncols, int cached) {
   dyb_grid_dep_sync();
@@ -464,6 +565,13 @@ int dyb200_layer_norm_fwd(DYB200_FWD_ARGS) {
   DYB_CHECK_ARG(ctx, t_size(fx) == n * ncols, "layer_norm: output size mismatch");
   if (n * ncols == 0) return DYB200_OK;
   cached = cached && aligned16(fx->v);
+  if (cached && n % 128 == 0 && n <= 1024 && aligned16(xs[1].v) && aligned16(xs[2].v)) {   // a warp per column
+    const unsigned grid = stream_grid(ctx, (ncols + 7) / 8, 1);
+    if (n <= 256) dyb_launch(k_layer_norm_fwd_warp<2>, grid, kBlock, 0, ctx, xs[0].v, xs[1].v, xs[2].v, fx->v, (uint32_t)n, ncols);
+    else dyb_launch(k_layer_norm_fwd_warp<8>, grid, kBlock, 0, ctx, xs[0].v, xs[1].v, xs[2].v, fx->v, (uint32_t)n, ncols);
+    DYB_LAUNCHED(ctx);
+    return DYB200_OK;
+  }
   dyb_launch(k_layer_norm_fwd, stream_grid(ctx, ncols, 1), kBlock, 0, ctx, xs[0].v, xs[1].v, xs[2].v, fx->v, (uint32_t)n, ncols, cached);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
@@ -480,6 +588,13 @@ int dyb200_layer_norm_bwd(DYB200_BWD_ARGS) {
   if (n * ncols == 0) return DYB200_OK;
   if (i == 0) {
     cached = cached && aligned16(dEdf->v) && aligned16(dEdxi->v);
+    if (cached && n % 128 == 0 && n <= 1024 && aligned16(xs[1].v)) {   // a warp per column (1024: 20.5 us against 25.8 us for a CTA per column, 4096 columns)
+      const unsigned grid = stream_grid(ctx, (ncols + 7) / 8, 1);
+      if (n <= 256) dyb_launch(k_layer_norm_bwd_x_warp<2>, grid, kBlock, 0, ctx, xs[0].v, xs[1].v, dEdf->v, dEdxi->v, (uint32_t)n, ncols);
+      else dyb_launch(k_layer_norm_bwd_x_warp<8>, grid, kBlock, 0, ctx, xs[0].v, xs[1].v, dEdf->v, dEdxi->v, (uint32_t)n, ncols);
+      DYB_LAUNCHED(ctx);
+      return DYB200_OK;
+    }
     dyb_launch(k_layer_norm_bwd_x, stream_grid(ctx, ncols, 1), kBlock, 0, ctx, xs[0].v, xs[1].v, dEdf->v, dEdxi->v, (uint32_t)n, ncols, cached);
     DYB_LAUNCHED(ctx);
     return DYB200_OK;

@@ -486,17 +486,20 @@ __global__ void __launch_bounds__(kRT * kCL) k_row(const float* __restrict__ x, 
       for (uint32_t c = cj; c < cols; c += kCL) mx = fmaxf(mx, xb[(size_t)c * rows]);
     }
     mx = tile_reduce(mx, sm, ri, cj, true);
+    // one ex2.approx per element and one reciprocal per row, as in the kernels along dim 0 (expf and a division per element
+    // made this kernel bound by instruction issue: 32 values per thread, 1024 threads per CTA)
+    const float ml = shift_log2(mx);
     float s = 0.f;
     if (cached) {
 #pragma unroll
       for (int k = 0; k < kRowVals; ++k) {
         uint32_t c = cj + kCL * k;
-        float e = (live && c < cols) ? expf(v[k] - mx) : 0.f;
+        float e = (live && c < cols) ? ex2_approx(fmaf(v[k], kLog2e, -ml)) : 0.f;
         v[k] = e;
         s += e;
       }
     } else if (live) {
-      for (uint32_t c = cj; c < cols; c += kCL) s += expf(xb[(size_t)c * rows] - mx);
+      for (uint32_t c = cj; c < cols; c += kCL) s += ex2_approx(fmaf(xb[(size_t)c * rows], kLog2e, -ml));
     }
     s = tile_reduce(s, sm, ri, cj, false);
     if (MODE == R_LSE) {
@@ -506,14 +509,15 @@ __global__ void __launch_bounds__(kRT * kCL) k_row(const float* __restrict__ x, 
       }
     } else if (live) {
       float* yb = out + boff + r;
+      const float inv = 1.f / s;
       if (cached) {
 #pragma unroll
         for (int k = 0; k < kRowVals; ++k) {
           uint32_t c = cj + kCL * k;
-          if (c < cols) yb[(size_t)c * rows] = v[k] / s;
+          if (c < cols) yb[(size_t)c * rows] = v[k] * inv;
         }
       } else {
-        for (uint32_t c = cj; c < cols; c += kCL) yb[(size_t)c * rows] = expf(xb[(size_t)c * rows] - mx) / s;
+        for (uint32_t c = cj; c < cols; c += kCL) yb[(size_t)c * rows] = ex2_approx(fmaf(xb[(size_t)c * rows], kLog2e, -ml)) * inv;
       }
     }
   } else if (MODE == R_SOFTMAX_BWD) {  // x = y, aux_in = dy, out = dx

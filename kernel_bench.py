@@ -117,6 +117,15 @@ def build_cases(torch, ctx, small):
     cases.append(Case("layer_norm_fwd", 2 * S, mk_ln, lambda b: ctx.fwd("layer_norm", ln_xs(b), T(b["y"], [Ccols], R)), 4 * S))
     cases.append(Case("layer_norm_bwd_x", 4 * S, mk_ln,
                       lambda b: ctx.bwd("layer_norm", ln_xs(b), T(b["y"], [Ccols], R), T(b["dy"], [Ccols], R), 0, T(b["dx"], [Ccols], R)), 4 * S))
+    # the same 16.8 MB tensor as 4096 columns of 1024 elements (a hidden layer of 1024 units, 4096 batch columns): a warp per column
+    def mk_ln2():
+        return dict(x=torch.randn(Ccols, R, device=dev), g=torch.rand(R, device=dev) + 0.5, b=torch.randn(R, device=dev) * 0.1,
+                    y=torch.empty(Ccols, R, device=dev), dy=torch.randn(Ccols, R, device=dev), dx=torch.zeros(Ccols, R, device=dev))
+    def ln2_xs(b):
+        return [T(b["x"], [R], Ccols), T(b["g"], [R], 1), T(b["b"], [R], 1)]
+    cases.append(Case("layer_norm_fwd_cols1024", 2 * S, mk_ln2, lambda b: ctx.fwd("layer_norm", ln2_xs(b), T(b["y"], [R], Ccols)), 4 * S))
+    cases.append(Case("layer_norm_bwd_x_cols1024", 4 * S, mk_ln2,
+                      lambda b: ctx.bwd("layer_norm", ln2_xs(b), T(b["y"], [R], Ccols), T(b["dy"], [R], Ccols), 0, T(b["dx"], [R], Ccols)), 4 * S))
 
     def mk_wn():
         return dict(w=torch.randn(R, Ccols, device=dev), g=torch.full((1,), 1.3, device=dev), y=torch.empty(R, Ccols, device=dev),

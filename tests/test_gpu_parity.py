@@ -415,7 +415,8 @@ def test_std_dim_value_golden(g, capi):
     assert abs(float(g.host(z)[0]) - want) <= c["tol_rel"] * want
 
 
-@pytest.mark.parametrize("n,bd", [(3, 1), (10, 1), (130, 5), (4096, 16), (4100, 3), (9001, 2)])
+@pytest.mark.parametrize("n,bd", [(3, 1), (10, 1), (130, 5), (4096, 16), (4100, 3), (9001, 2),
+                                  (128, 37), (256, 9), (640, 21), (1024, 300)])   # (the last four: a warp per column)
 def test_layer_norm(oracle, g, n, bd):
     r = rng(132)
     x = randn(r, bd, n)
