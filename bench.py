@@ -583,12 +583,13 @@ def run_tagger_gpu(args):
         t_mv = float(mv.sum()) * 1e-3
         achieved = algo / t_mv / 1e9 if t_mv > 0 else 0.0
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                    "traffic": None, "kernel": "k_ragged_copy_warp + k_sort_targets + k_ragged_accumulate (the autobatch movers)",
+                    "traffic": None, "kernel": "k_ragged_copy_warp; k_ragged_probe + k_ragged_accumulate_direct (the autobatch movers)",
                     "algorithmic_bytes": algo, "us": {"copy_fwd_dir": 1e3 * mv[0], "copy_bwd_dir": 1e3 * mv[1], "accumulate_fwd_dir": 1e3 * mv[2],
                                                       "accumulate_bwd_dir": 1e3 * mv[3]},
-                    "note": "%d slices of %d floats per call (%.1f MB each way): the transfers are a few microseconds long, so launch "
-                            "latency and, for the accumulate, the sort of the target pointers bound them, not HBM; the same kernels on "
-                            "268 MB are in hbm_kernels of the LSTM-LM line" % (int(n_local), H, slice_bytes / 1e6),
+                    "note": "%d slices of %d floats per call (%.1f MB each way), timed with CUDA events around the four mover calls of a "
+                            "step: a copy moves 2x and an accumulate 3x those bytes; the accumulate also runs the probe that checks its "
+                            "targets for repeats (5 launches per call); the same kernels on 268 MB slices of 4 KB are in hbm_kernels of "
+                            "the LSTM-LM line" % (int(n_local), H, slice_bytes / 1e6),
                     "peak_source": peaks["source"]}
         cpu_rec = None if args.no_cpu_baseline else tagger_cpu_record()
         tok_step = float(np.mean(total_tokens))

@@ -136,64 +136,94 @@ __global__ void __launch_bounds__(WARP ? 256 : kThreads) k_ragged_accumulate_dir
   }
 }
 
-// One thread group (a CTA of kThreads threads, or a warp of a 256-thread CTA when WARP) per distinct target.
+// Shared targets, all sort passes in one launch.  A thread group (a CTA of kThreads threads, or a warp of a 256-thread
+// CTA when WARP) takes segment u of pass blockIdx.y; it OWNS the segment's target if no earlier pass holds that target
+// (binary searches in the earlier passes' sorted segment lists), and then adds the target's slices of this pass and of
+// every later pass that holds it, in pass order and ascending slice order inside a pass - the order of the one-slice-at-a-time
+// loop, whichever pass a slice falls into.  A target is written by exactly one group: no barrier between passes, no atomics.
+struct RaggedPasses {
+  float* const* src; float* const* trg; const size_t* len;
+  const uint32_t* slice_sorted; const uint32_t* seg_start; const uint32_t* nseg;   // per pass p: at + p kSortMax, + p kSortMax + p, + p
+  uint32_t n, npass;
+};
+// the segment of pass q whose target is t, or -1
+__device__ __forceinline__ int find_target(const RaggedPasses& a, uint32_t q, const float* t) {
+  const uint32_t base = q * kSortMax;
+  const uint32_t* ss = a.slice_sorted + base;
+  const uint32_t* st = a.seg_start + base + q;
+  uint32_t lo = 0, hi = a.nseg[q];
+  while (lo < hi) {
+    const uint32_t mid = (lo + hi) >> 1;
+    const float* tm = a.trg[base + ss[st[mid]]];
+    if (tm < t) lo = mid + 1; else hi = mid;
+  }
+  return (lo < a.nseg[q] && a.trg[base + ss[st[lo]]] == t) ? (int)lo : -1;
+}
 template <bool WARP>
-__global__ void __launch_bounds__(WARP ? 256 : kThreads) k_ragged_accumulate(float* const* __restrict__ src, float* const* __restrict__ trg,
-                                                                            const size_t* __restrict__ len, uint32_t base,
-                                                                            const uint32_t* __restrict__ slice_sorted,
-                                                                            const uint32_t* __restrict__ seg_start,
-                                                                            const uint32_t* __restrict__ nseg,
-                                                                            const uint32_t* __restrict__ dup) {
+__global__ void __launch_bounds__(WARP ? 256 : kThreads) k_ragged_accumulate(const RaggedPasses a, const uint32_t* __restrict__ dup) {
   dyb_grid_dep_sync();
   if (*dup == 0) return;   // (distinct targets: k_ragged_accumulate_direct has done the work)
-  const uint32_t U = *nseg;
+  const uint32_t p = blockIdx.y;
+  const uint32_t U = a.nseg[p];
   const uint32_t group = WARP ? blockIdx.x * 8 + (threadIdx.x >> 5) : blockIdx.x, groups = WARP ? gridDim.x * 8 : gridDim.x;
   const uint32_t me = WARP ? (threadIdx.x & 31) : threadIdx.x, width = WARP ? 32 : kThreads;
   for (uint32_t u = group; u < U; u += groups) {
-    const uint32_t k0 = seg_start[u], k1 = seg_start[u + 1];
-    float* t = trg[base + slice_sorted[k0]];
+    const uint32_t base = p * kSortMax;
+    float* t = a.trg[base + a.slice_sorted[base + a.seg_start[base + p + u]]];
+    bool owner = true;
+    for (uint32_t q = 0; q < p && owner; ++q) owner = find_target(a, q, t) < 0;
+    if (!owner) continue;
+    // the widest slice and the common alignment over all passes that hold the target
     size_t nmax = 0;
     bool al = aligned16(t);
-    for (uint32_t k = k0; k < k1; ++k) {
-      uint32_t s = base + slice_sorted[k];
-      nmax = max(nmax, len[s]);
-      al = al && aligned16(src[s]) && (len[s] % 4 == 0);
-    }
-    if (al && k1 == k0 + 1) {
-      // the usual case, one source per target: two vectors per lane in flight
-      const float* a = src[base + slice_sorted[k0]];
-      const size_t n4 = nmax / 4;
-      size_t i = me;
-      for (; i + width < n4; i += 2 * width) {
-        const float4 o0 = ld4(t + 4 * i), o1 = ld4(t + 4 * (i + width)), v0 = ld4_stream(a + 4 * i), v1 = ld4_stream(a + 4 * (i + width));
-        st4(t + 4 * i, make_float4(o0.x + v0.x, o0.y + v0.y, o0.z + v0.z, o0.w + v0.w));
-        st4(t + 4 * (i + width), make_float4(o1.x + v1.x, o1.y + v1.y, o1.z + v1.z, o1.w + v1.w));
-      }
-      for (; i < n4; i += width) {
-        const float4 o = ld4(t + 4 * i), v = ld4_stream(a + 4 * i);
-        st4(t + 4 * i, make_float4(o.x + v.x, o.y + v.y, o.z + v.z, o.w + v.w));
-      }
-    } else if (al) {
-      for (size_t i = me; i < nmax / 4; i += width) {
-        float4 acc = ld4(t + 4 * i);
+    int seg_of[32];   // (at most 32 passes are looked at per round; longer lists go round by round below)
+    for (uint32_t q0 = p; q0 < a.npass; q0 += 32) {
+      const uint32_t q1 = min(a.npass, q0 + 32);
+      nmax = 0;
+      for (uint32_t q = q0; q < q1; ++q) {
+        const int uq = q == p ? (int)u : find_target(a, q, t);
+        seg_of[q - q0] = uq;
+        if (uq < 0) continue;
+        const uint32_t bq = q * kSortMax, k0 = a.seg_start[bq + q + uq], k1 = a.seg_start[bq + q + uq + 1];
         for (uint32_t k = k0; k < k1; ++k) {
-          uint32_t s = base + slice_sorted[k];
-          if (4 * i < len[s]) {
-            float4 v = ld4_stream(src[s] + 4 * i);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          const uint32_t sidx = bq + a.slice_sorted[bq + k];
+          nmax = max(nmax, a.len[sidx]);
+          al = al && aligned16(a.src[sidx]) && (a.len[sidx] % 4 == 0);
+        }
+      }
+      if (al) {
+        for (size_t i = me; i < nmax / 4; i += width) {
+          float4 acc = ld4(t + 4 * i);
+          for (uint32_t q = q0; q < q1; ++q) {
+            const int uq = seg_of[q - q0];
+            if (uq < 0) continue;
+            const uint32_t bq = q * kSortMax, k0 = a.seg_start[bq + q + uq], k1 = a.seg_start[bq + q + uq + 1];
+            for (uint32_t k = k0; k < k1; ++k) {
+              const uint32_t sidx = bq + a.slice_sorted[bq + k];
+              if (4 * i < a.len[sidx]) {
+                const float4 v = ld4_stream(a.src[sidx] + 4 * i);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+              }
+            }
           }
+          st4(t + 4 * i, acc);
         }
-        st4(t + 4 * i, acc);
-      }
-    } else {
-      for (size_t i = me; i < nmax; i += width) {
-        float acc = t[i];
-        for (uint32_t k = k0; k < k1; ++k) {
-          uint32_t s = base + slice_sorted[k];
-          if (i < len[s]) acc += src[s][i];
+      } else {
+        for (size_t i = me; i < nmax; i += width) {
+          float acc = t[i];
+          for (uint32_t q = q0; q < q1; ++q) {
+            const int uq = seg_of[q - q0];
+            if (uq < 0) continue;
+            const uint32_t bq = q * kSortMax, k0 = a.seg_start[bq + q + uq], k1 = a.seg_start[bq + q + uq + 1];
+            for (uint32_t k = k0; k < k1; ++k) {
+              const uint32_t sidx = bq + a.slice_sorted[bq + k];
+              if (i < a.len[sidx]) acc += a.src[sidx][i];
+            }
+          }
+          t[i] = acc;
         }
-        t[i] = acc;
       }
+      if (WARP) __syncwarp(); else __syncthreads();   // (a later round re-reads what this one wrote)
     }
   }
 }
@@ -245,14 +275,12 @@ int dyb200_parallel_accumulate(int num_seqs, int max_len, float** src, float** t
   // shared targets: grouped by target, added in ascending slice order (these launches return at once otherwise)
   dyb_launch(k_sort_targets, npass, kSortThreads, 0, ctx, trg, n, slice_sorted, group_sorted, seg_start, nseg, dup);
   DYB_LAUNCHED(ctx);
-  for (uint32_t p = 0; p < npass; ++p) {
-    const uint32_t base = p * kSortMax, np = n - base < (uint32_t)kSortMax ? n - base : (uint32_t)kSortMax;
-    if (warp)
-      dyb_launch(k_ragged_accumulate<true>, stream_grid(ctx, np, 8, 8), 256, 0, ctx, src, trg, len, base, slice_sorted + base, seg_start + base + p, nseg + p, dup);
-    else
-      dyb_launch(k_ragged_accumulate<false>, stream_grid(ctx, np, 1, 16), kThreads, 0, ctx, src, trg, len, base, slice_sorted + base, seg_start + base + p, nseg + p, dup);
-    DYB_LAUNCHED(ctx);
-  }
+  // one launch for all passes: blockIdx.y = pass
+  RaggedPasses ra{src, trg, len, slice_sorted, seg_start, nseg, n, npass};
+  const uint32_t np = n < (uint32_t)kSortMax ? n : (uint32_t)kSortMax;
+  if (warp) dyb_launch(k_ragged_accumulate<true>, dim3(stream_grid(ctx, np, 8, 8), npass), 256, 0, ctx, ra, (const uint32_t*)dup);
+  else dyb_launch(k_ragged_accumulate<false>, dim3(stream_grid(ctx, np, 1, 16), npass), kThreads, 0, ctx, ra, (const uint32_t*)dup);
+  DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
 
