@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(uint32_t M, uint32_t N, int n
         if (m >= epi.H && m < 2 * epi.H) v += epi.forget_bias;
         *c = m < 3 * epi.H ? gate_sigmoid(v) : gate_tanh(v);
       } else {
-        *c += v * epi.maskC[m + (epi.maskc_full ? (size_t)epi.maskc_ld * n : 0)];
+        *c = __fmaf_rn(v, epi.maskC[m + (epi.maskc_full ? (size_t)epi.maskc_ld * n : 0)], *c);
       }
     }
   }

@@ -479,7 +479,7 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
         st4(dst, make_float4(o.x + acc.x, o.y + acc.y, o.z + acc.z, o.w + acc.w));
       } else {   // EPI_ACCUM_MASK
         float4 o = ld4(dst), mk = ld4(row.mask + (row.mask_full ? (size_t)row.mask_ld * n : 0));
-        st4(dst, make_float4(o.x + acc.x * mk.x, o.y + acc.y * mk.y, o.z + acc.z * mk.z, o.w + acc.w * mk.w));
+        st4(dst, make_float4(__fmaf_rn(acc.x, mk.x, o.x), __fmaf_rn(acc.y, mk.y, o.y), __fmaf_rn(acc.z, mk.z, o.z), __fmaf_rn(acc.w, mk.w, o.w)));
       }
     }
     return;
@@ -497,7 +497,7 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__
       acc += epi.bias[m] + ((m >= epi.H && m < 2 * epi.H) ? epi.forget_bias : 0.f);
       *dst = m < 3 * epi.H ? gate_sigmoid(acc) : gate_tanh(acc);   // (the activations of every gate epilogue)
     } else {
-      *dst += acc * row.mask[row.mask_full ? (size_t)row.mask_ld * n : 0];
+      *dst = __fmaf_rn(acc, row.mask[row.mask_full ? (size_t)row.mask_ld * n : 0], *dst);
     }
   }
 }

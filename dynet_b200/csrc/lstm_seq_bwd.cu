@@ -359,6 +359,23 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_bwd(const __grid_const
           if ((te & 7) == 0)
             for (uint32_t c = c_lo + (te >> 5); c < c_hi; c += 8) prefetch_l2(base + ld * (n0 + c));
         }
+        // With at most 32 columns per CTA (4 per thread in the epilogue's layout: row quad te % 32, columns c_lo + te / 32 + 8 k)
+        // the current dx / dh values and the mask values are fetched into registers now, so that the epilogue after the exchange
+        // only waits for shared memory.
+        const bool pre_epi = SPLIT && c_hi - c_lo <= 32;
+        float4 old4[4];
+        const uint32_t m_epi = m0 + 4 * (te & 31);
+        const bool epi_row_live = pre_epi && m_epi < (t ? a.I + a.H : a.I);
+        const bool to_dx = m_epi < a.I;
+        float* const cbase = to_dx ? a.dx + (size_t)t * IB + m_epi : a.dh + (size_t)(t ? t - 1 : 0) * HB + (m_epi - a.I);
+        const uint32_t ld_epi = to_dx ? a.I : a.H;
+        if (epi_row_live) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t c = c_lo + (te >> 5) + 8 * k, n = n0 + c;
+            old4[k] = (c < c_hi && n < N) ? __ldcg(reinterpret_cast<const float4*>(cbase + (size_t)ld_epi * n)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
         // ---- drain the accumulation chains of this product ----
         float sum[64];
 #pragma unroll
@@ -441,7 +458,34 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_bwd(const __grid_const
             }
           }
           ok = bar_and(1, 256, ok) != 0;
-          if (ok) epilogue_pass<BNT, 256>(epi, park - (size_t)c_lo * BM, te, blockIdx.x, m0, n0, M, N, no_cprev, c_lo, c_hi);
+          if (ok && pre_epi) {
+            // dx / dh = old + sum .* mask (the arithmetic of epilogue_pass for EPI_ACCUM / EPI_ACCUM_MASK) on the prefetched values
+            if (epi_row_live) {
+              const float* mbase = to_dx ? a.mx : a.mh;
+              const uint32_t mrow = to_dx ? m_epi : m_epi - a.I;
+              const bool mfull = to_dx ? a.mx_full : a.mh_full;
+              float4 mk4[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint32_t c = c_lo + (te >> 5) + 8 * k, n = n0 + c;
+                mk4[k] = (mbase && c < c_hi && n < N) ? ld4(mbase + mrow + (mfull ? (size_t)ld_epi * n : 0)) : make_float4(1.f, 1.f, 1.f, 1.f);
+              }
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint32_t cs = (te >> 5) + 8 * k, n = n0 + c_lo + cs;   // cs: column within the slice
+                if (c_lo + cs < c_hi && n < N) {
+                  const float4 v = ld4(park + (size_t)cs * BM + 4 * (te & 31));
+                  float4 r;
+                  if (mbase) r = make_float4(__fmaf_rn(v.x, mk4[k].x, old4[k].x), __fmaf_rn(v.y, mk4[k].y, old4[k].y),
+                                             __fmaf_rn(v.z, mk4[k].z, old4[k].z), __fmaf_rn(v.w, mk4[k].w, old4[k].w));
+                  else r = make_float4(v.x + old4[k].x, v.y + old4[k].y, v.z + old4[k].z, v.w + old4[k].w);
+                  st4(cbase + (size_t)ld_epi * n, r);
+                }
+              }
+            }
+          } else if (ok) {
+            epilogue_pass<BNT, 256>(epi, park - (size_t)c_lo * BM, te, blockIdx.x, m0, n0, M, N, no_cprev, c_lo, c_hi);
+          }
           bar_sync(1, 256);   // the exchange buffer may be overwritten; every thread's stores of dx / dh are issued
         } else {
 #pragma unroll 1

@@ -204,7 +204,8 @@ __device__ __forceinline__ void epilogue_pass(const GemmEpilogue& epi, const flo
                           : make_float4(gate_sigmoid(r.x), gate_sigmoid(r.y), gate_sigmoid(r.z), gate_sigmoid(r.w));
             } else if (epi.mode == EPI_ACCUM) { r.x += old[k].x; r.y += old[k].y; r.z += old[k].z; r.w += old[k].w; }
             else if (epi.mode == EPI_ACCUM_MASK) {
-              r = make_float4(old[k].x + r.x * mk[k].x, old[k].y + r.y * mk[k].y, old[k].z + r.z * mk[k].z, old[k].w + r.w * mk[k].w);
+              // (explicit fused multiply-adds: every kernel that applies this epilogue rounds alike)
+              r = make_float4(__fmaf_rn(r.x, mk[k].x, old[k].x), __fmaf_rn(r.y, mk[k].y, old[k].y), __fmaf_rn(r.z, mk[k].z, old[k].z), __fmaf_rn(r.w, mk[k].w, old[k].w));
             }
             st4(row.c + ldc * n, r);
           }
@@ -231,7 +232,7 @@ __device__ __forceinline__ void epilogue_pass(const GemmEpilogue& epi, const flo
           else if (epi.mode == EPI_BIAS) *dst = v + bias;
           else if (epi.mode == EPI_GATES) *dst = is_tanh ? gate_tanh(v + bias) : gate_sigmoid(v + bias);
           else if (epi.mode == EPI_ACCUM) *dst += v;
-          else *dst += v * row.mask[mstep * n];
+          else *dst = __fmaf_rn(v, row.mask[mstep * n], *dst);
         }
       }
     }
