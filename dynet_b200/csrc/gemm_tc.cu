@@ -1031,6 +1031,9 @@ bool dyb200_tc_eligible(uint32_t M, uint32_t N, double flops) {
   // Small products stay on the CUDA-core kernel: packing + a 128x128 tile would mostly move padding.  A product with few
   // rows but many columns or a long reduction (the tag layer of a tagger: 32 or 45 rows times 100 000 tokens) is still far
   // better off here - most of a tile's rows are padding, but the work is bound by reading the long operand once.
+  // (Between 2 and 8 MFLOP the CUDA-core kernel is slow when its grid is one or two CTAs - 190 us for the 128 x 21 x 1024
+  // products of a tagger batch's last time steps - but it is plain fp32: a lower limit here was measured to cost accuracy
+  // margin in small-batch recurrences (1.5e-4 of a row's scale after 100 steps of 3xTF32 products), so the limit stays.)
   return !(flops < 8.0e6 || M < 16 || (M + BM - 1) / BM > 65535u || (N + BN - 1) / BN > 65535u);
 }
 

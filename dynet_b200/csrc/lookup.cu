@@ -348,20 +348,23 @@ __global__ void __launch_bounds__(256) k_chunk_combine(float* __restrict__ all_g
     if (id_at[k1] != id) continue;                         // last run of the chunk does not continue
     if (id_at[k0] == id && k0 > 0 && id_at[k0 - 1] == id) continue;   // it started earlier: not the owner
     float4 acc = ld4(tail + ((size_t)c * slices + sl) * 128 + lane * 4);
-    // (a frequent id runs over hundreds of chunks: eight pieces are requested together, the adds stay in chunk order)
-    uint32_t c2 = c + 1;
-    while (c2 < nchunks && id_at[c2 * kChunk] == id) {
-      float4 piece[8];
-      uint32_t m = 0;
+    // A frequent id runs over hundreds of chunks (the most frequent word of a 107 k-token batch: ~500).  The last chunk of
+    // the run is found by a binary search over the chunk heads (ids are sorted), then sixteen pieces are requested at a
+    // time; the adds stay in chunk order.
+    uint32_t lo = c + 1, hi = nchunks;   // first chunk in [lo, hi) whose head is another id
+    while (lo < hi) {
+      const uint32_t mid = (lo + hi) >> 1;
+      if (id_at[mid * kChunk] == id) lo = mid + 1; else hi = mid;
+    }
+    const uint32_t c_end = lo;
+    for (uint32_t c2 = c + 1; c2 < c_end; c2 += 16) {
+      float4 piece[16];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const bool more = c2 + u < nchunks && id_at[(c2 + u) * kChunk] == id && m == (uint32_t)u;
-        if (more) { piece[u] = ld4(head + ((size_t)(c2 + u) * slices + sl) * 128 + lane * 4); ++m; }
-      }
+      for (int u = 0; u < 16; ++u)
+        if (c2 + u < c_end) piece[u] = ld4(head + ((size_t)(c2 + u) * slices + sl) * 128 + lane * 4);
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
-        if ((uint32_t)u < m) add4(acc, piece[u]);
-      c2 += m;
+      for (int u = 0; u < 16; ++u)
+        if (c2 + u < c_end) add4(acc, piece[u]);
     }
     st4(all_grads + (size_t)id * E + col, acc);
   }

@@ -35,6 +35,26 @@ static __global__ void __launch_bounds__(128) k_batch_reduce_final(const float* 
   for (uint32_t s = 0; s < S; ++s) acc += partial[(size_t)s * n + r];
   out[r] += acc;
 }
+// The same for few outputs and many partial sums (a bias gradient over 100 000 columns: n = 45, S = 2368): a warp per
+// output, lane l adds the partials l, l + 32, ... in ascending order (four loads in flight), then the lanes are added by a
+// butterfly - a fixed order, so the result is reproducible.
+static __global__ void __launch_bounds__(128) k_batch_reduce_final_warp(const float* __restrict__ partial, uint32_t S,
+                                                                        size_t n, float* __restrict__ out) {
+  dyb_grid_dep_sync();
+  const size_t r = (size_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (r >= n) return;
+  const uint32_t lane = threadIdx.x & 31;
+  float acc = 0.f;
+  uint32_t s = lane;
+  for (; s + 96 < S; s += 128) {
+    const float v0 = partial[(size_t)s * n + r], v1 = partial[(size_t)(s + 32) * n + r], v2 = partial[(size_t)(s + 64) * n + r],
+                v3 = partial[(size_t)(s + 96) * n + r];
+    acc += v0; acc += v1; acc += v2; acc += v3;
+  }
+  for (; s < S; s += 32) acc += partial[(size_t)s * n + r];
+  acc = warp_sum(acc);
+  if (lane == 0) out[r] += acc;
+}
 
 template <class F>
 static int batch_reduce_add(dyb200_ctx* ctx, F f, size_t n, uint32_t B, float* out) {
@@ -56,7 +76,8 @@ static int batch_reduce_add(dyb200_ctx* ctx, F f, size_t n, uint32_t B, float* o
   if (rc) return rc;
   dyb_launch(k_batch_reduce_partial<F>, dim3(gx, S), 128, 0, ctx, f, n, B, chunk, (float*)scratch, out, 0);
   DYB_LAUNCHED(ctx);
-  dyb_launch(k_batch_reduce_final, gx, 128, 0, ctx, (const float*)scratch, S, n, out);
+  if (n <= 512 && S >= 64) dyb_launch(k_batch_reduce_final_warp, (unsigned)((n + 3) / 4), 128, 0, ctx, (const float*)scratch, S, n, out);
+  else dyb_launch(k_batch_reduce_final, gx, 128, 0, ctx, (const float*)scratch, S, n, out);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }
