@@ -114,6 +114,7 @@ int dyb200_tc_param2(dyb200_ctx* ctx, const float* src, uint32_t rows, const flo
 // force_splits > 0: that many K splits (normalised so that no split is empty) instead of the cost model's choice.
 int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const PackedOp* A, const PackedOp* B,
                           const GemmEpilogue& epi, uint32_t force_splits = 0);
+int dyb200_splitk_reduce(dyb200_ctx* ctx, const float* part, uint32_t S, uint32_t M, uint32_t N, const GemmEpilogue& epi);
 // Tiling of the backward recurrence of an LSTM layer (dx_t, dh_{t-1} += [Wx; Wh]^T dgates_t), shared by the per-step call
 // and the sequence kernel so that both add the same partial sums: tile width, batch-column blocks per CTA of the sequence
 // kernel (1 or 2) and K splits.  False when the shape does not suit the sequence kernel (the per-step call then lets the

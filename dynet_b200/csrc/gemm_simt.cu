@@ -18,9 +18,12 @@ __device__ __forceinline__ float load_b(const GemmPair& p, uint32_t k, uint32_t 
   return v;
 }
 
+// gridDim.z > 1 (one pair only): split z covers k in [z kc, (z + 1) kc) and stores its partial product at epi.C + z M N
+// (epi is then a plain store with leading dimension M); dyb200_splitk_reduce adds the splits and applies the real epilogue.
 __global__ void __launch_bounds__(256) k_gemm_simt(uint32_t M, uint32_t N, int npairs, GemmPair p0, GemmPair p1,
-                                                  GemmEpilogue epi) {
+                                                  GemmEpilogue epi, uint32_t kc) {
   dyb_grid_dep_sync();
+  if (gridDim.z > 1) epi.C += (size_t)blockIdx.z * M * N;
   __shared__ float As[TK][TM + 4];
   __shared__ float Bs[TK][TN + 4];
   const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
@@ -28,7 +31,8 @@ __global__ void __launch_bounds__(256) k_gemm_simt(uint32_t M, uint32_t N, int n
   float acc[4][4] = {};
   for (int pi = 0; pi < npairs; ++pi) {
     const GemmPair& p = pi == 0 ? p0 : p1;
-    for (uint32_t k0 = 0; k0 < p.K; k0 += TK) {
+    const uint32_t k_lo = gridDim.z > 1 ? blockIdx.z * kc : 0u, k_hi = gridDim.z > 1 ? min(p.K, k_lo + kc) : p.K;
+    for (uint32_t k0 = k_lo; k0 < k_hi; k0 += TK) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (p.transA) { int k = tid % 16, m = tid / 16 + 16 * j; As[k][m] = load_a(p, m0 + m, k0 + k, M); }
@@ -81,7 +85,24 @@ int dyb200_gemm_simt(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const 
   GemmPair p0 = pairs[0], p1 = npairs > 1 ? pairs[1] : pairs[0];
   dim3 grid((M + TM - 1) / TM, (N + TN - 1) / TN);
   DYB_CHECK_ARG(ctx, grid.y <= 65535, "gemm: N too large for the CUDA-core path");
-  dyb_launch(k_gemm_simt, grid, 256, 0, ctx, M, N, npairs, p0, p1, epi);
+  // A long reduction over a handful of tiles (the last time steps of a ragged batch: 128 x 21 x 1024 on two CTAs took
+  // 190 us) is split along K: up to 32 splits of at least 64 k each, partial products to scratch, added in split order.
+  const uint32_t K = pairs[0].K;
+  if (npairs == 1 && grid.x * grid.y <= 16 && K >= 256 && epi.mode != EPI_GATES) {
+    uint32_t S = K / 64;
+    if (S > 32) S = 32;
+    uint32_t kc = ((K + S - 1) / S + TK - 1) / TK * TK;   // whole k steps per split
+    S = (K + kc - 1) / kc;
+    void* part;
+    int rc = dyb200_scratch(ctx, (size_t)S * M * N * sizeof(float), &part);
+    if (rc) return rc;
+    GemmEpilogue store{EPI_STORE, (float*)part, M, nullptr, 0, 0.f, nullptr, 0, 0};
+    grid.z = S;
+    dyb_launch(k_gemm_simt, grid, 256, 0, ctx, M, N, npairs, p0, p1, store, kc);
+    DYB_LAUNCHED(ctx);
+    return dyb200_splitk_reduce(ctx, (const float*)part, S, M, N, epi);
+  }
+  dyb_launch(k_gemm_simt, grid, 256, 0, ctx, M, N, npairs, p0, p1, epi, 0u);
   DYB_LAUNCHED(ctx);
   return DYB200_OK;
 }

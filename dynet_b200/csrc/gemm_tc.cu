@@ -1027,6 +1027,19 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   return DYB200_OK;
 }
 
+// Second stage of a K split for callers outside this file: C = epilogue(sum over s of part[s]), the S partial products
+// (M x N each, leading dimension M) added in ascending order.
+int dyb200_splitk_reduce(dyb200_ctx* ctx, const float* part, uint32_t S, uint32_t M, uint32_t N, const GemmEpilogue& epi) {
+  int vec = M % 4 == 0 && epi.ldc % 4 == 0 && aligned16(epi.C) && epi.mode != EPI_GATES && (epi.mode != EPI_BIAS || aligned16(epi.bias)) &&
+            (epi.mode != EPI_ACCUM_MASK || (aligned16(epi.maskC) && (!epi.maskc_full || epi.maskc_ld % 4 == 0)));
+  if (epi.split_m)
+    vec = vec && epi.split_m % 4 == 0 && epi.ldc2 % 4 == 0 && aligned16(epi.C2) &&
+          (epi.mode != EPI_ACCUM_MASK || (aligned16(epi.maskC2) && (!epi.maskc2_full || epi.maskc2_ld % 4 == 0)));
+  dyb_launch(k_splitk_reduce, stream_grid(ctx, (size_t)M * N / 4 + 1, 256), 256, 0, ctx, part, S, M, N, epi, vec);
+  DYB_LAUNCHED(ctx);
+  return DYB200_OK;
+}
+
 bool dyb200_tc_eligible(uint32_t M, uint32_t N, double flops) {
   // Small products stay on the CUDA-core kernel: packing + a 128x128 tile would mostly move padding.  A product with few
   // rows but many columns or a long reduction (the tag layer of a tagger: 32 or 45 rows times 100 000 tokens) is still far
