@@ -277,19 +277,21 @@ __device__ __forceinline__ void persist_tile_coords(uint32_t tile, uint32_t tile
 template <int BNT>
 __device__ __noinline__ void persist_producer(const TmapPack* tm, unsigned char* ring, uint64_t* full_bar, uint64_t* empty_bar,
                                               uint32_t tiles, uint32_t tiles_m, uint32_t tiles_n, uint32_t gm, uint32_t kb0,
-                                              uint32_t kb1, uint32_t* flags) {
+                                              uint32_t kb1, uint32_t S, uint32_t* flags) {
   constexpr int TILE_B_BYTES = BNT * BK * 4;
   constexpr int STAGE_TX = 2 * TILE_BYTES + 2 * TILE_B_BYTES;
-  const uint32_t kb = kb0 + kb1;
   uint32_t s = 0, ph = 0;
   bool fail = false;
-  for (uint32_t tile = blockIdx.x; tile < tiles && !fail; tile += gridDim.x) {
+  // work item w = (K split z, tile): all tiles of split 0 first, so that the CTAs of a round share operand k-blocks
+  for (uint32_t w = blockIdx.x; w < tiles * S && !fail; w += gridDim.x) {
+    const uint32_t z = w / tiles, tile = w - z * tiles;
+    const KSplit ks = k_split(kb0, kb1, z, S);
     uint32_t mt, nt;
     persist_tile_coords(tile, tiles_m, tiles_n, gm, mt, nt);
     const uint32_t m0 = mt * BM, n0 = nt * BNT;
-    for (uint32_t g = 0; g < kb; ++g) {
+    for (uint32_t g = 0; g < ks.n0 + ks.n1; ++g) {
       if (!mbar_wait(&empty_bar[s], ph ^ 1)) { fail = true; break; }
-      const uint32_t pair = g < kb0 ? 0 : 1, kblk = pair ? g - kb0 : g;
+      const uint32_t pair = g < ks.n0 ? 0 : 1, kblk = pair ? ks.b1 + (g - ks.n0) : ks.b0 + g;
       unsigned char* st = ring + (size_t)s * STAGE_BYTES;
       mbar_expect_tx(&full_bar[s], STAGE_TX);
       tma_load_2d(st, &tm->t[4 * pair + 0], &full_bar[s], (int)(kblk * BK), (int)m0);
@@ -304,7 +306,8 @@ __device__ __noinline__ void persist_producer(const TmapPack* tm, unsigned char*
 
 template <int BNT>
 __device__ __noinline__ void persist_issue(unsigned char* ring, uint64_t* full_bar, uint64_t* empty_bar, uint64_t* acc_full,
-                                           uint64_t* acc_empty, uint32_t tmem_base, uint32_t tiles, uint32_t kb, uint32_t* flags) {
+                                           uint64_t* acc_empty, uint32_t tmem_base, uint32_t tiles, uint32_t kb0, uint32_t kb1, uint32_t S,
+                                           uint32_t* flags) {
   constexpr int TILE_B_BYTES = BNT * BK * 4;
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   uint64_t d_a_hi[STAGES], d_a_lo[STAGES], d_b_hi[STAGES], d_b_lo[STAGES];
@@ -317,7 +320,9 @@ __device__ __noinline__ void persist_issue(unsigned char* ring, uint64_t* full_b
   // stage, phase and chunk counters run on across tiles; an accumulation chain never crosses a tile boundary
   uint32_t s = 0, ph = 0, chunk = 0, buf = 0;
   bool fail = false;
-  for (uint32_t tile = blockIdx.x; tile < tiles && !fail; tile += gridDim.x) {
+  for (uint32_t w = blockIdx.x; w < tiles * S && !fail; w += gridDim.x) {
+    const KSplit ks = k_split(kb0, kb1, w / tiles, S);
+    const uint32_t kb = ks.n0 + ks.n1;
     uint32_t in_chunk = 0;
     for (uint32_t it = 0; it < kb; ++it) {
       if (in_chunk == 0 && chunk >= kPersistBufs) {
@@ -345,7 +350,7 @@ __device__ __noinline__ void persist_issue(unsigned char* ring, uint64_t* full_b
 template <int BNT>
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_persist(const __grid_constant__ TmapPack tm, uint32_t M, uint32_t N,
                                                               uint32_t kb0, uint32_t kb1, uint32_t tiles_m, uint32_t tiles,
-                                                              uint32_t gm, GemmEpilogue epi, uint32_t* flags) {
+                                                              uint32_t gm, uint32_t S, GemmEpilogue epi, uint32_t* flags) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[kPersistBufs], acc_empty[kPersistBufs];
@@ -353,7 +358,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_persist(const __grid_const
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   float* stage = reinterpret_cast<float*>(ring + (size_t)STAGES * STAGE_BYTES);   // 64 columns x BM rows
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t kb = kb0 + kb1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -372,19 +376,23 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_persist(const __grid_const
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
-    if (lane == 0) persist_producer<BNT>(&tm, ring, full_bar, empty_bar, tiles, tiles_m, (N + BNT - 1) / BNT, gm, kb0, kb1, flags);
+    if (lane == 0) persist_producer<BNT>(&tm, ring, full_bar, empty_bar, tiles, tiles_m, (N + BNT - 1) / BNT, gm, kb0, kb1, S, flags);
   } else if (warp == 1) {
-    if (lane == 0) persist_issue<BNT>(ring, full_bar, empty_bar, acc_full, acc_empty, tmem_base, tiles, kb, flags);
+    if (lane == 0) persist_issue<BNT>(ring, full_bar, empty_bar, acc_full, acc_empty, tmem_base, tiles, kb0, kb1, S, flags);
   } else {
     // epilogue warps 2..9: TMEM lanes 32 (warp % 4) .. +31; warps 2-5 hold columns 0-63 of the tile, warps 6-9 columns 64-127
     const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
     const uint32_t th = (threadIdx.x - 64) & 127;   // 0..127 within this half's four warps
     const bool has_cols = 64 * half < BNT;
-    const uint32_t nchunks = (kb + kChunkKB - 1) / kChunkKB;
     uint32_t cg = 0;   // chunks drained so far (selects the TMEM buffer and the barrier phase)
     bool ok = true;
 #pragma unroll 1
-    for (uint32_t tile = blockIdx.x, j = 0; tile < tiles; tile += gridDim.x, ++j) {
+    for (uint32_t w = blockIdx.x, j = 0; w < tiles * S; w += gridDim.x, ++j) {
+      const uint32_t z = w / tiles, tile = w - z * tiles;
+      const KSplit ks = k_split(kb0, kb1, z, S);
+      const uint32_t nchunks = (ks.n0 + ks.n1 + kChunkKB - 1) / kChunkKB;
+      // (K splits: epi is a plain store with ldc = M into S partial products side by side, so split z writes columns z N ..)
+      const uint32_t n_shift = z * N;
       uint32_t mt, nt;
       persist_tile_coords(tile, tiles_m, (N + BNT - 1) / BNT, gm, mt, nt);
       const uint32_t m0 = mt * BM, n0 = nt * BNT + 64 * half;
@@ -437,10 +445,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_persist(const __grid_const
       uint32_t all_ok;
       asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, %2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                    : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1u + 2u * half) : "memory");
-      if (all_ok) epilogue_pass<64, 128>(epi, stage, th, mt, m0, n0, M, N, cprev);
+      if (all_ok) epilogue_pass<64, 128>(epi, stage, th, mt, m0, n0 + n_shift, M, N + n_shift, cprev);
       if (BNT == 128) {
         if (half == 0) bar_arrive(2, 256);
-        else if (tile + gridDim.x < tiles) bar_arrive(4, 256);
+        else if (w + gridDim.x < tiles * S) bar_arrive(4, 256);
       }
     }
     if (!ok && lane == 0) atomicOr(flags, DYB200_FLAG_WAIT_TIMEOUT);
@@ -982,14 +990,39 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_persist<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PERSIST_BYTES));
       ctx->func_attr_done |= 4u;
     }
+    // A long reduction whose tiles fill the last round badly (the deferred weight gradients: 256 tiles of 560 k-blocks on
+    // 148 SMs = two rounds, the second 73 % full) is cut into Sp K splits as further work items of the same persistent
+    // launch: 1024 items of 140 k-blocks make seven nearly full rounds.  The partial products go to a workspace and
+    // k_splitk_reduce adds them in split order and applies the epilogue.  Same cost form as dyb200_tc_splits, with the 3 us
+    // that a persistent CTA spends between items.
+    uint32_t Sp = 1;
+    if (!tail_apart && epi.mode != EPI_LSTM_CELL && epi.mode != EPI_GATES) {
+      const double sms = (double)ctx->sm_count, t_kb = bn == 64 ? 0.40 : 0.66, mn_bytes = 4.0 * (double)M * (double)N;
+      auto est = [&](uint32_t q) {
+        const double rounds = ceil((double)tiles_run * q / sms);
+        return rounds * ((double)((kb_total + q - 1) / q) * t_kb + 3.0) + (q > 1 ? (q + 2) * mn_bytes / 5.0e6 + 8.0 : 0.0);
+      };
+      double best = est(1);
+      for (uint32_t q = 2; q <= 4; ++q)
+        if (kb_total / q >= 64 && est(q) < 0.95 * best && est(q) < 0.95 * est(1)) { best = est(q); Sp = q; }
+    }
+    GemmEpilogue pepi = epi;
+    float* ppart = nullptr;
+    if (Sp > 1) {
+      void* pw;
+      if ((rc = dyb200_scratch(ctx, (size_t)Sp * M * N * sizeof(float), &pw))) return rc;
+      ppart = (float*)pw;
+      pepi = GemmEpilogue{EPI_STORE, ppart, M, nullptr, 0, 0.f, nullptr, 0, 0};
+    }
     {
       GemmProfScope scope(ctx, flops * ((double)tiles_run / (grid.x * grid.y)), 1, M, N, kb_total * BK, (uint32_t)epi.mode);
       // grouped tile order when the A operand has many row blocks (unless the last round runs apart, which relies on the
       // row-block-fastest order)
       const uint32_t gm = (!tail_apart && grid.x > 16) ? 16u : 0u;
-      if (bn == 64) dyb_launch(k_gemm_persist<64>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, gm, epi, ctx->dev_flags);
-      else dyb_launch(k_gemm_persist<128>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, gm, epi, ctx->dev_flags);
+      if (bn == 64) dyb_launch(k_gemm_persist<64>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, gm, Sp, pepi, ctx->dev_flags);
+      else dyb_launch(k_gemm_persist<128>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, gm, Sp, pepi, ctx->dev_flags);
       DYB_LAUNCHED(ctx);
+      if (Sp > 1 && (rc = dyb200_splitk_reduce(ctx, ppart, Sp, M, N, epi))) return rc;
     }
     if (!tail_apart) return DYB200_OK;
     // the last `tail` row blocks of the last column of tiles
