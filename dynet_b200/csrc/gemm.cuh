@@ -83,7 +83,10 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
 int dyb200_gemm_fused(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const GemmPair* pairs, const GemmEpilogue& epi);
 
 // ---- pieces of the tensor path, for entry points that reuse one packed operand in several products ----
-struct PackedOp { float* hi; float* lo; uint32_t rows, K, pitch; };   // K-major TF32 hi / lo planes
+// TF32 hi / lo planes of an operand: `rows` rows (m or n) of K values.  K-major (mn_major = 0): element (r, k) at
+// plane[r * pitch + k].  MN-major (left operands of dyb200_tc_gemm_packed only): element (r, k) at plane[k * pitch + r] -
+// the K-major planes of the transposed matrix, used as they are.
+struct PackedOp { float* hi; float* lo; uint32_t rows, K, pitch; uint32_t mn_major = 0; };
 // A queue of packing work that one kernel launch executes (several small operands per launch).
 constexpr int kMaxPackJobs = 8;
 constexpr int kLayoutGates = 2;

@@ -84,8 +84,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         const uint32_t pair = it < ks.n0 ? 0 : 1, kblk = pair ? ks.b1 + (it - ks.n0) : ks.b0 + it;
         unsigned char* st = ring + (size_t)s * STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], STAGE_TX);
-        tma_load_2d(st, &tm.t[4 * pair + 0], &full_bar[s], (int)(kblk * BK), (int)m0);
-        tma_load_2d(st + TILE_BYTES, &tm.t[4 * pair + 1], &full_bar[s], (int)(kblk * BK), (int)m0);
+        load_a_tile(st, &tm.t[4 * pair + 0], &full_bar[s], kblk, m0, tm.a_mn);
+        load_a_tile(st + TILE_BYTES, &tm.t[4 * pair + 1], &full_bar[s], kblk, m0, tm.a_mn);
         tma_load_2d(st + 2 * TILE_BYTES, &tm.t[4 * pair + 2], &full_bar[s], (int)(kblk * BK), (int)n0);
         tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), (int)n0);
         if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -102,12 +102,17 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
       // descriptors of the three stages are built once, stage / phase / chunk counters are carried instead of divided,
       // and the 12 MMAs of a k-block go out in one block of PTX.
       // instruction descriptor: D = f32, A = B = tf32, both K-major, N = BNT, M = 128
-      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      // (bit 15: A is MN-major)
+      const uint32_t a_mn = tm.a_mn;
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24) |
+                             (a_mn ? 1u << 15 : 0u);
+      const uint64_t a_step = a_mn ? 64 : 2;
       uint64_t d_a_hi[STAGES], d_a_lo[STAGES], d_b_hi[STAGES], d_b_lo[STAGES];
 #pragma unroll
       for (int q = 0; q < STAGES; ++q) {
         const uint32_t base = smem_u32(ring + (size_t)q * STAGE_BYTES);
-        d_a_hi[q] = umma_desc(base); d_a_lo[q] = umma_desc(base + TILE_BYTES);
+        d_a_hi[q] = a_mn ? umma_desc_mn(base) : umma_desc(base);
+        d_a_lo[q] = a_mn ? umma_desc_mn(base + TILE_BYTES) : umma_desc(base + TILE_BYTES);
         d_b_hi[q] = umma_desc(base + 2 * TILE_BYTES); d_b_lo[q] = umma_desc(base + 2 * TILE_BYTES + TILE_B_BYTES);
       }
       // The tensor core truncates when it aligns addends to the accumulator, a bias that grows with the length of
@@ -125,7 +130,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         else if (s == 1) { a_hi = d_a_hi[1]; a_lo = d_a_lo[1]; b_hi = d_b_hi[1]; b_lo = d_b_lo[1]; }
         else { a_hi = d_a_hi[2]; a_lo = d_a_lo[2]; b_hi = d_b_hi[2]; b_lo = d_b_lo[2]; }
         const uint32_t acc = tmem_base + buf * BN;
-        issue_kblock(acc, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk);
+        issue_kblock(acc, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk, a_step);
         umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
         const bool chunk_ends = in_chunk == kChunkKB - 1 || it == total - 1;
         if (chunk_ends) { umma_commit(&acc_full[buf]); in_chunk = 0; ++chunk; buf ^= 1; }
@@ -294,8 +299,8 @@ __device__ __noinline__ void persist_producer(const TmapPack* tm, unsigned char*
       const uint32_t pair = g < ks.n0 ? 0 : 1, kblk = pair ? ks.b1 + (g - ks.n0) : ks.b0 + g;
       unsigned char* st = ring + (size_t)s * STAGE_BYTES;
       mbar_expect_tx(&full_bar[s], STAGE_TX);
-      tma_load_2d(st, &tm->t[4 * pair + 0], &full_bar[s], (int)(kblk * BK), (int)m0);
-      tma_load_2d(st + TILE_BYTES, &tm->t[4 * pair + 1], &full_bar[s], (int)(kblk * BK), (int)m0);
+      load_a_tile(st, &tm->t[4 * pair + 0], &full_bar[s], kblk, m0, tm->a_mn);
+      load_a_tile(st + TILE_BYTES, &tm->t[4 * pair + 1], &full_bar[s], kblk, m0, tm->a_mn);
       tma_load_2d(st + 2 * TILE_BYTES, &tm->t[4 * pair + 2], &full_bar[s], (int)(kblk * BK), (int)n0);
       tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm->t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), (int)n0);
       if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -307,14 +312,17 @@ __device__ __noinline__ void persist_producer(const TmapPack* tm, unsigned char*
 template <int BNT>
 __device__ __noinline__ void persist_issue(unsigned char* ring, uint64_t* full_bar, uint64_t* empty_bar, uint64_t* acc_full,
                                            uint64_t* acc_empty, uint32_t tmem_base, uint32_t tiles, uint32_t kb0, uint32_t kb1, uint32_t S,
-                                           uint32_t* flags) {
+                                           uint32_t a_mn, uint32_t* flags) {
   constexpr int TILE_B_BYTES = BNT * BK * 4;
-  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24) |
+                         (a_mn ? 1u << 15 : 0u);
+  const uint64_t a_step = a_mn ? 64 : 2;
   uint64_t d_a_hi[STAGES], d_a_lo[STAGES], d_b_hi[STAGES], d_b_lo[STAGES];
 #pragma unroll
   for (int q = 0; q < STAGES; ++q) {
     const uint32_t base = smem_u32(ring + (size_t)q * STAGE_BYTES);
-    d_a_hi[q] = umma_desc(base); d_a_lo[q] = umma_desc(base + TILE_BYTES);
+    d_a_hi[q] = a_mn ? umma_desc_mn(base) : umma_desc(base);
+    d_a_lo[q] = a_mn ? umma_desc_mn(base + TILE_BYTES) : umma_desc(base + TILE_BYTES);
     d_b_hi[q] = umma_desc(base + 2 * TILE_BYTES); d_b_lo[q] = umma_desc(base + 2 * TILE_BYTES + TILE_B_BYTES);
   }
   // stage, phase and chunk counters run on across tiles; an accumulation chain never crosses a tile boundary
@@ -335,7 +343,7 @@ __device__ __noinline__ void persist_issue(unsigned char* ring, uint64_t* full_b
       else if (s == 1) { a_hi = d_a_hi[1]; a_lo = d_a_lo[1]; b_hi = d_b_hi[1]; b_lo = d_b_lo[1]; }
       else { a_hi = d_a_hi[2]; a_lo = d_a_lo[2]; b_hi = d_b_hi[2]; b_lo = d_b_lo[2]; }
       const uint32_t acc = tmem_base + buf * BN;
-      issue_kblock(acc, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk);
+      issue_kblock(acc, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk, a_step);
       umma_commit(&empty_bar[s]);
       const bool chunk_ends = in_chunk == kChunkKB - 1 || it == kb - 1;
       if (chunk_ends) { umma_commit(&acc_full[buf]); in_chunk = 0; ++chunk; buf = chunk % kPersistBufs; }
@@ -378,7 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_persist(const __grid_const
   if (warp == 0) {
     if (lane == 0) persist_producer<BNT>(&tm, ring, full_bar, empty_bar, tiles, tiles_m, (N + BNT - 1) / BNT, gm, kb0, kb1, S, flags);
   } else if (warp == 1) {
-    if (lane == 0) persist_issue<BNT>(ring, full_bar, empty_bar, acc_full, acc_empty, tmem_base, tiles, kb0, kb1, S, flags);
+    if (lane == 0) persist_issue<BNT>(ring, full_bar, empty_bar, acc_full, acc_empty, tmem_base, tiles, kb0, kb1, S, tm.a_mn, flags);
   } else {
     // epilogue warps 2..9: TMEM lanes 32 (warp % 4) .. +31; warps 2-5 hold columns 0-63 of the tile, warps 6-9 columns 64-127
     const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
@@ -662,6 +670,19 @@ int make_map(dyb200_ctx* ctx, EncodeTiledFn enc, CUtensorMap* map, float* plane,
   return DYB200_OK;
 }
 
+// MN-major plane: element (m, k) at plane[k * pitch + m], `rows` valid m and K valid k; box = 32 (m) x 32 (k), in the
+// 128-byte swizzle with 32-byte atoms that umma_desc_mn describes.
+int make_map_mn(dyb200_ctx* ctx, EncodeTiledFn enc, CUtensorMap* map, float* plane, uint32_t rows, uint32_t K, uint32_t pitch) {
+  cuuint64_t dims[2] = {rows, K};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
+  cuuint32_t box[2] = {32, BK};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, plane, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return dyb200_fail(ctx, DYB200_ECUDA, "cuTensorMapEncodeTiled failed with code %d (MN-major, rows %u, K %u, pitch %u)", (int)r, rows, K, pitch);
+  return DYB200_OK;
+}
+
 int pack_flush_impl(dyb200_ctx* ctx, PackJobs* jobs) {
   if (jobs->n == 0) return DYB200_OK;
   const uint32_t total = jobs->start[jobs->n];
@@ -903,12 +924,21 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   TmapPack tm;
   memset(&tm, 0, sizeof(tm));
   double flops = 0;
+  const bool a_mn = A[0].mn_major != 0;
+  DYB_CHECK_ARG(ctx, !a_mn || (npairs == 1 && A[0].pitch % 4 == 0 && aligned16(A[0].hi) && aligned16(A[0].lo) && !B[0].mn_major),
+                "tensor GEMM: an MN-major left operand needs a single pair, a pitch that is a multiple of 4 and 16-byte aligned planes");
+  tm.a_mn = a_mn ? 1u : 0u;
   for (int p = 0; p < npairs; ++p) {
-    DYB_CHECK_ARG(ctx, A[p].rows == M && B[p].rows == N && A[p].K == B[p].K && A[p].pitch % 32 == 0 && B[p].pitch % 32 == 0,
+    DYB_CHECK_ARG(ctx, A[p].rows == M && B[p].rows == N && A[p].K == B[p].K && (a_mn || A[p].pitch % 32 == 0) && B[p].pitch % 32 == 0,
                   "tensor GEMM: packed operand shapes do not match (M %u, N %u)", M, N);
     flops += 2.0 * M * N * A[p].K;
-    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 0], A[p].hi, M, A[p].K, A[p].pitch))) return rc;
-    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 1], A[p].lo, M, A[p].K, A[p].pitch))) return rc;
+    if (a_mn) {
+      if ((rc = make_map_mn(ctx, enc, &tm.t[0], A[0].hi, M, A[0].K, A[0].pitch))) return rc;
+      if ((rc = make_map_mn(ctx, enc, &tm.t[1], A[0].lo, M, A[0].K, A[0].pitch))) return rc;
+    } else {
+      if ((rc = make_map(ctx, enc, &tm.t[4 * p + 0], A[p].hi, M, A[p].K, A[p].pitch))) return rc;
+      if ((rc = make_map(ctx, enc, &tm.t[4 * p + 1], A[p].lo, M, A[p].K, A[p].pitch))) return rc;
+    }
     if ((rc = make_map(ctx, enc, &tm.t[4 * p + 2], B[p].hi, N, B[p].K, B[p].pitch, bn))) return rc;
     if ((rc = make_map(ctx, enc, &tm.t[4 * p + 3], B[p].lo, N, B[p].K, B[p].pitch, bn))) return rc;
   }
@@ -1029,7 +1059,8 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     const uint32_t m_off = (grid.x - tail) * BM, n_off = (grid.y - 1) * bn;
     PackedOp A2[2], B2[2];
     for (int p = 0; p < npairs; ++p) {
-      A2[p] = A[p]; A2[p].rows = M - m_off; A2[p].hi += (size_t)m_off * A[p].pitch; A2[p].lo += (size_t)m_off * A[p].pitch;
+      A2[p] = A[p]; A2[p].rows = M - m_off;   // (MN-major planes: the rows are the fast index)
+      A2[p].hi += a_mn ? (size_t)m_off : (size_t)m_off * A[p].pitch; A2[p].lo += a_mn ? (size_t)m_off : (size_t)m_off * A[p].pitch;
       B2[p] = B[p]; B2[p].rows = N - n_off; B2[p].hi += (size_t)n_off * B[p].pitch; B2[p].lo += (size_t)n_off * B[p].pitch;
     }
     GemmEpilogue e2 = epi;

@@ -351,10 +351,10 @@ int run_expsub_bwd(dyb200_ctx* ctx, const float* x, const float* z, const float*
 // ---- PickNegLogSoftmax backward written directly as GEMM operands ------------------------------------------------------
 // d[r, c] = exp(x[r, c] - z[c]) dz[c]  (- dz[c] at the picked row): the same value k_expsub_bwd adds into a zeroed tensor,
 // but stored only as the hi / lo TF32 planes of the two products that consume it in the backward pass of
-// x = b + R h:  "straight" planes bh / bl [c][r] (reduction index = r, for dh += R^T d) and transposed planes ah / al
-// [r][c] (reduction index = c, for dR += d h^T), plus the sums over the 64 columns of the tile for the bias gradient.
-// One 64 x 64 tile per CTA: 16-byte accesses along r on the way in, along c on the way out, transposed through shared
-// memory.  x is read once; nothing else of d reaches HBM (the fp32 tensor, its zero fill and two packing passes go).
+// x = b + R h:  planes bh / bl [c][r] - K-major right operand of dh += R^T d (reduction index = r) and, as they are, the
+// MN-major left operand of dR += d h^T (reduction index = c) - plus the sums over the 64 columns of the tile for the bias
+// gradient (transposed through shared memory).  One 64 x 64 tile per CTA, 16-byte accesses along r.  x is read once;
+// nothing else of d reaches HBM (the fp32 tensor, its zero fill, two packing passes and a transposed copy of the planes go).
 struct ChunkOfPart {   // f(r, b) = v[r + n * b]
   const float* v; size_t n;
   __device__ float operator()(size_t r, uint32_t b) const { return v[r + n * (size_t)b]; }
@@ -363,9 +363,8 @@ struct ChunkOfPart {   // f(r, b) = v[r + n * b]
 __global__ void __launch_bounds__(256) k_softmax_bwd_split(const float* __restrict__ x, const float* __restrict__ z,
                                                            const float* __restrict__ dz, const uint32_t* __restrict__ ids,
                                                            uint32_t rows, uint32_t ncols, float* __restrict__ bh,
-                                                           float* __restrict__ bl, uint32_t pitch_b, float* __restrict__ ah,
-                                                           float* __restrict__ al, uint32_t pitch_a,
-                                                           float* __restrict__ colsum_part, int vec_in, int vec_out) {
+                                                           float* __restrict__ bl, uint32_t pitch_b,
+                                                           float* __restrict__ colsum_part, int vec_in) {
   dyb_grid_dep_sync();
   __shared__ float tile[64][65];   // [column][row]
   const uint32_t r0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
@@ -416,7 +415,6 @@ __global__ void __launch_bounds__(256) k_softmax_bwd_split(const float* __restri
   __syncthreads();
   {
     const uint32_t cq = threadIdx.x & 15, rl = threadIdx.x >> 4;
-    const uint32_t c = c0 + 4 * cq;
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
       const uint32_t rr = rl + 16 * p, r = r0 + rr;
@@ -428,18 +426,6 @@ __global__ void __launch_bounds__(256) k_softmax_bwd_split(const float* __restri
       s += __shfl_xor_sync(0xffffffffu, s, 8);
       if (r >= rows) continue;
       if (cq == 0) colsum_part[(size_t)blockIdx.y * rows + r] = s;
-      if (c >= ncols) continue;
-      float4 h, l;
-      split_tf32(d.x, h.x, l.x); split_tf32(d.y, h.y, l.y); split_tf32(d.z, h.z, l.z); split_tf32(d.w, h.w, l.w);
-      float* ph = ah + (size_t)r * pitch_a + c;
-      float* pl = al + (size_t)r * pitch_a + c;
-      if (vec_out) { st4(ph, h); st4(pl, l); }   // ncols % 4 == 0: the four columns exist
-      else {
-        ph[0] = h.x; pl[0] = l.x;
-        if (c + 1 < ncols) { ph[1] = h.y; pl[1] = l.y; }
-        if (c + 2 < ncols) { ph[2] = h.z; pl[2] = l.z; }
-        if (c + 3 < ncols) { ph[3] = h.w; pl[3] = l.w; }
-      }
     }
   }
 }
@@ -756,15 +742,15 @@ int dyb200_softmax_output_bwd_fused(const dyb200_tensor* x, const dyb200_tensor*
   }
   int rc;
   PackedOp dA, dB, hT, RT;
-  if ((rc = dyb200_tc_planes(ctx, V, n, &dA))) return rc;   // rows = vocabulary, reduction over the columns
   if ((rc = dyb200_tc_planes(ctx, n, V, &dB))) return rc;   // rows = columns, reduction over the vocabulary
+  dA = dB; dA.rows = V; dA.K = n; dA.mn_major = 1;           // the same planes read with the vocabulary as rows
   const dim3 grid((V + 63) / 64, (n + 63) / 64);
   void* part;
   if ((rc = dyb200_scratch(ctx, (size_t)grid.y * V * sizeof(float), &part))) return rc;
-  const int vec_in = V % 4 == 0 && aligned16(x->v), vec_out = n % 4 == 0;
+  const int vec_in = V % 4 == 0 && aligned16(x->v);
   DYB_CHECK_ARG(ctx, grid.y <= 65535u, "softmax_output_bwd_fused: too many columns (%u)", n);
-  dyb_launch(k_softmax_bwd_split, grid, 256, 0, ctx, x->v, z, dEdf->v, ids_dev, V, n, dB.hi, dB.lo, dB.pitch, dA.hi, dA.lo, dA.pitch,
-             (float*)part, vec_in, vec_out);
+  dyb_launch(k_softmax_bwd_split, grid, 256, 0, ctx, x->v, z, dEdf->v, ids_dev, V, n, dB.hi, dB.lo, dB.pitch,
+             (float*)part, vec_in);
   DYB_LAUNCHED(ctx);
   if ((rc = batch_reduce_add(ctx, ChunkOfPart{(const float*)part, V}, V, grid.y, db->v))) return rc;   // db += sum over column tiles
   // dR += d h^T : M = V, N = H, K = n

@@ -24,7 +24,10 @@ constexpr uint32_t kTmemCols = 256;       // two 128-column accumulators, used a
 constexpr uint32_t kChunkKB = 8;
 constexpr uint32_t kEpiWarps = 8;
 
-struct TmapPack { CUtensorMap t[8]; };   // pair p: t[4p] = A_hi, A_lo, B_hi, B_lo
+// pair p: t[4p] = A_hi, A_lo, B_hi, B_lo.  a_mn != 0 (one pair only): the A planes are MN-major - element (m, k) at
+// plane[k * pitch + m], the layout of a K x M row-major matrix - and t[0], t[1] are maps over (m fastest, k) with a box of
+// 32 m x 32 k; see load_a_tile / umma_desc_mn.
+struct TmapPack { CUtensorMap t[8]; uint32_t a_mn; };
 
 // The k-blocks of K split z of S: [b0, b0 + n0) of pair 0, then [b1, b1 + n1) of pair 1 (each pair cut into S equal shares).
 struct KSplit { uint32_t b0, n0, b1, n1; };
@@ -74,6 +77,32 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                        // layout: SWIZZLE_128B
   return d;
 }
+// Same for an MN-major A tile of 128 m x 32 k as load_a_tile lays it out: four boxes of 32 m (128 bytes) x 32 k rows, 4096
+// bytes apart (the leading byte offset = distance between 32-element groups along m).  32-bit MN-major operands exist in
+// one shared-memory layout only, the 128-byte swizzle with 32-byte atoms (layout type 1; the tensor map's
+// SWIZZLE_128B_ATOM_32B): its pattern repeats every 4 k rows, so the stride byte offset - the distance between 4-k groups -
+// is 512 bytes, and one MMA (k = 8) advances the start address by 1024 bytes.
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(4096 >> 4) << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)1 << 61;
+  return d;
+}
+// One plane of the A tile (m0 .., k-block kblk) into `st`: one box for a K-major plane; for an MN-major plane four boxes of
+// 32 m each (a box is at most one 128-byte swizzle span wide), 16 KB in either case.  Rows past the plane's extent arrive
+// as zeros.
+__device__ __forceinline__ void load_a_tile(unsigned char* st, const CUtensorMap* map, uint64_t* bar, uint32_t kblk, uint32_t m0,
+                                            uint32_t a_mn) {
+  if (a_mn) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) tma_load_2d(st + g * 4096, map, bar, (int)(m0 + 32 * g), (int)(kblk * 32));
+  } else {
+    tma_load_2d(st, map, bar, (int)(kblk * 32), (int)m0);
+  }
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -97,29 +126,30 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 
 // The 12 MMAs of one 32-wide k-block (3 products x 4 k-steps of 8) as one block of PTX.  The first MMA accumulates iff
-// `accumulate` is non-zero (0 opens a new accumulation chain).
+// `accumulate` is non-zero (0 opens a new accumulation chain).  a_step: what one k-step adds to the A descriptors, in
+// descriptor units of 16 bytes (2 = 32 bytes of a K-major row; 64 = one 8-k group of an MN-major tile).
 __device__ __forceinline__ void issue_kblock(uint32_t acc, uint64_t a_hi, uint64_t a_lo, uint64_t b_hi, uint64_t b_lo,
-                                             uint32_t idesc, uint32_t accumulate) {
-  // one MMA consumes 8 tf32 = 32 bytes of K: +2 in descriptor units per k8 step
+                                             uint32_t idesc, uint32_t accumulate, uint64_t a_step = 2) {
+  // one MMA consumes 8 tf32 = 32 bytes of K: +2 in descriptor units per k8 step of a K-major operand
   asm volatile(
       "{\n\t.reg .pred pf, pt;\n\t.reg .b64 xa, xb, ya, yb;\n\t"
       "setp.ne.b32 pf, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %2, %3, %5, pf;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %4, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %3, %5, pt;\n\t"
-      "add.s64 xa, %1, 2;\n\tadd.s64 xb, %2, 2;\n\tadd.s64 ya, %3, 2;\n\tadd.s64 yb, %4, 2;\n\t"
+      "add.s64 xa, %1, %7;\n\tadd.s64 xb, %2, %7;\n\tadd.s64 ya, %3, 2;\n\tadd.s64 yb, %4, 2;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t"
-      "add.s64 xa, %1, 4;\n\tadd.s64 xb, %2, 4;\n\tadd.s64 ya, %3, 4;\n\tadd.s64 yb, %4, 4;\n\t"
+      "add.s64 xa, xa, %7;\n\tadd.s64 xb, xb, %7;\n\tadd.s64 ya, %3, 4;\n\tadd.s64 yb, %4, 4;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t"
-      "add.s64 xa, %1, 6;\n\tadd.s64 xb, %2, 6;\n\tadd.s64 ya, %3, 6;\n\tadd.s64 yb, %4, 6;\n\t"
+      "add.s64 xa, xa, %7;\n\tadd.s64 xb, xb, %7;\n\tadd.s64 ya, %3, 6;\n\tadd.s64 yb, %4, 6;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t}"
-      ::"r"(acc), "l"(a_hi), "l"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(accumulate)
+      ::"r"(acc), "l"(a_hi), "l"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(accumulate), "l"(a_step)
       : "memory");
 }
 

@@ -286,7 +286,7 @@ def build_cases(torch, ctx, small):
     cases[-1].flops = 2.0 * Vv * TB * Hh
 
     # backward of the same output layer in one call: PickNegLogSoftmax gradient written as the operands of dR and dh
-    # (k_softmax_bwd_split: 4 V n bytes in, 16 V n bytes out), then the two products
+    # (k_softmax_bwd_split: 4 V n bytes in, 8 V n bytes out), then the two products
     nB = TB if not small else 4096
     def mk_outbwd():
         tgt = rng.integers(0, Vv, size=nB).astype(np.uint32)
