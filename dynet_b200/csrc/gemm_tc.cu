@@ -846,11 +846,15 @@ static uint32_t best_split(double sms, uint32_t tiles, uint32_t kb_total, double
   if (cost) *cost = best_t;
   return best;
 }
-// The partly filled last round of a many-tile product can run as a product of its own (see dyb200_tc_gemm_packed) when its
-// tiles lie in one column of tiles and K is long.
-static bool tail_can_run_apart(const dyb200_ctx* ctx, uint32_t tiles_m, uint32_t tiles, uint32_t kb_total, uint32_t bn) {
-  const uint32_t tail = tiles % (uint32_t)ctx->sm_count;
-  return tiles > (uint32_t)ctx->sm_count && tail > 0 && tail <= tiles_m && 2 * tail <= (uint32_t)ctx->sm_count && kb_total >= 64 && bn == BN;
+// The partly filled last round of a many-tile product can run as a product of its own (see dyb200_tc_gemm_packed) when K is
+// long and its tiles form a rectangle: 2 = the last tail / tiles_n row blocks of every column of tiles (the persistent kernel
+// keeps its grouped tile order on the row blocks before them), 1 = the last `tail` row blocks of the last column of tiles
+// (row-block-fastest order), 0 = neither.
+static int tail_can_run_apart(const dyb200_ctx* ctx, uint32_t tiles_m, uint32_t tiles, uint32_t kb_total, uint32_t bn) {
+  const uint32_t tail = tiles % (uint32_t)ctx->sm_count, tiles_n = tiles / tiles_m;
+  if (!(tiles > (uint32_t)ctx->sm_count && tail > 0 && 2 * tail <= (uint32_t)ctx->sm_count && kb_total >= 64 && bn == BN)) return 0;
+  if (tail % tiles_n == 0 && tail / tiles_n < tiles_m) return 2;
+  return tail <= tiles_m ? 1 : 0;
 }
 
 // Number of K splits of a product: the one the cost model says is fastest.  For a product with more tiles than SMs the
@@ -1008,13 +1012,17 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   }
   if (S == 1 && grid.x * grid.y > (uint32_t)ctx->sm_count) {
     // A partly filled last round (dR: 632 tiles = 4 rounds of 148 + 40) would keep 108 SMs idle for a whole tile time.
-    // When those last tiles lie in one column of tiles and K is long, the persistent kernel stops before them and they
-    // run as a product of their own (the sub-matrices of the same operands), which the cost model splits along K.
+    // When those last tiles form a rectangle (dR: the last 5 row blocks of all 8 columns of tiles) and K is long, the
+    // persistent kernel stops before them and they run as a product of their own (the sub-matrices of the same operands),
+    // which the cost model splits along K.
     uint32_t tiles_run = grid.x * grid.y;
     const uint32_t tail = tiles_run % (uint32_t)ctx->sm_count;
     const bool plain_epi = (epi.mode == EPI_STORE || epi.mode == EPI_ACCUM || epi.mode == EPI_BIAS) && epi.split_m == 0;
-    const bool tail_apart = plain_epi && tail_can_run_apart(ctx, grid.x, tiles_run, kb_total, bn);
+    const int tail_form = plain_epi ? tail_can_run_apart(ctx, grid.x, tiles_run, kb_total, bn) : 0;
+    const bool tail_apart = tail_form != 0;
     if (tail_apart) tiles_run -= tail;
+    // row blocks the persistent launch covers (all of them, unless the last ones run apart in every column of tiles)
+    const uint32_t rows_run = tail_form == 2 ? grid.x - tail / grid.y : grid.x;
     if (!(ctx->func_attr_done & 4u)) {
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_persist<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PERSIST_BYTES));
       DYB_CUDA(ctx, cudaFuncSetAttribute(k_gemm_persist<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PERSIST_BYTES));
@@ -1046,17 +1054,17 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     }
     {
       GemmProfScope scope(ctx, flops * ((double)tiles_run / (grid.x * grid.y)), 1, M, N, kb_total * BK, (uint32_t)epi.mode);
-      // grouped tile order when the A operand has many row blocks (unless the last round runs apart, which relies on the
-      // row-block-fastest order)
-      const uint32_t gm = (!tail_apart && grid.x > 16) ? 16u : 0u;
-      if (bn == 64) dyb_launch(k_gemm_persist<64>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, gm, Sp, pepi, ctx->dev_flags);
-      else dyb_launch(k_gemm_persist<128>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, grid.x, tiles_run, gm, Sp, pepi, ctx->dev_flags);
+      // grouped tile order when the A operand has many row blocks (unless the last round runs apart as part of the last
+      // column of tiles, which relies on the row-block-fastest order)
+      const uint32_t gm = (tail_form != 1 && rows_run > 16) ? 16u : 0u;
+      if (bn == 64) dyb_launch(k_gemm_persist<64>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, rows_run, tiles_run, gm, Sp, pepi, ctx->dev_flags);
+      else dyb_launch(k_gemm_persist<128>, dim3(ctx->sm_count), kThreads, SMEM_PERSIST_BYTES, ctx, tm, M, N, kb0, kb1, rows_run, tiles_run, gm, Sp, pepi, ctx->dev_flags);
       DYB_LAUNCHED(ctx);
       if (Sp > 1 && (rc = dyb200_splitk_reduce(ctx, ppart, Sp, M, N, epi))) return rc;
     }
     if (!tail_apart) return DYB200_OK;
-    // the last `tail` row blocks of the last column of tiles
-    const uint32_t m_off = (grid.x - tail) * BM, n_off = (grid.y - 1) * bn;
+    // the last `tail` row blocks of the last column of tiles, or the last tail / tiles_n row blocks of every column
+    const uint32_t m_off = (tail_form == 2 ? rows_run : grid.x - tail) * BM, n_off = tail_form == 2 ? 0u : (grid.y - 1) * bn;
     PackedOp A2[2], B2[2];
     for (int p = 0; p < npairs; ++p) {
       A2[p] = A[p]; A2[p].rows = M - m_off;   // (MN-major planes: the rows are the fast index)
