@@ -52,8 +52,7 @@ __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefe
 // its row, which keeps both the element-wise writes (8 or 16 units per warp, one column) and the row-wise reads (one unit,
 // 32 columns) free of bank conflicts.
 template <int JT>
-__device__ __forceinline__ void cell_bwd_tile(const SeqBwd& a, uint32_t t, uint32_t step, uint32_t j0, uint32_t b0, uint32_t tid, float* tile,
-                                              uint32_t* done) {
+__device__ __forceinline__ void cell_bwd_tile(const SeqBwd& a, uint32_t t, uint32_t step, uint32_t j0, uint32_t b0, uint32_t tid, float* tile) {
   constexpr int kQuads = JT / 4, kLanes = 256 / kQuads, kCols = kCellB / kLanes;   // 8 x 32 x 1 or 16 x 16 x 2
   const uint32_t H = a.H, B = a.B;
   const size_t HB = (size_t)H * B;
@@ -111,14 +110,6 @@ __device__ __forceinline__ void cell_bwd_tile(const SeqBwd& a, uint32_t t, uint3
     st4(a.dn_hi + o + 3 * H, make_float4(hi[0], hi[1], hi[2], hi[3])); st4(a.dn_lo + o + 3 * H, make_float4(lo[0], lo[1], lo[2], lo[3]));
   }
   bar_sync(1, 256);
-  // What the next product of this column block reads - the dgates planes, and dE/dc of the earlier step - has been issued by
-  // all 256 threads: the tile is published now, and the transposed planes and the row sums, which only kernels after this
-  // one read, follow.  One thread publishes: its release orders all stores it has observed, through the barrier, before the
-  // counter update (cumulativity), for the generic and for the async proxy (the readers are TMA loads).
-  if (tid == 0) {
-    asm volatile("fence.proxy.async.global;" ::: "memory");
-    signal_counter(done);
-  }
   // transposed write-out: warp w takes rows w, w + 8, ... of the 4 JT (gate, unit) rows; lane = batch column
   const uint32_t warp = tid >> 5, lane = tid & 31;
   float* dt_hi = a.dt_hi + (size_t)t * B + b0 + lane;
@@ -325,19 +316,21 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_bwd(const __grid_const
     uint32_t cg = 0;
     bool ok = true;   // the same for all 256 threads after every bar_and below
 
-    // the cell tiles of column block nt for `step` that fall to this CTA; each tile is published on its own, by the tile
-    // function, as soon as what the recurrence reads of it is out
+    // the cell tiles of column block nt for `step` that fall to this CTA; each finished tile is published on its own
     auto cell_pass = [&](uint32_t nt, uint32_t step) {
       const uint32_t t = a.T - 1 - step;
       for (uint32_t blk = my_cta; blk < n_cell; blk += n_cta) {
         const uint32_t j0 = (blk / (BNT / kCellB)) * cell_j, b0 = nt * BNT + (blk % (BNT / kCellB)) * kCellB;
-        if (!ok) {   // (keeps the hand-shake going: the tile function's barrier and its arrival on the counter)
-          bar_sync(1, 256);
-          if (te == 0) signal_counter(a.cell_done + nt);
+        if (!ok) bar_sync(1, 256);
+        else if (cell_j == 64) cell_bwd_tile<64>(a, t, step, j0, b0, te, park);
+        else cell_bwd_tile<32>(a, t, step, j0, b0, te, park);
+        bar_sync(1, 256);   // all stores of the tile are issued; the tile buffer may be reused
+        if (te == 0) {
+          // One thread publishes: its release orders all stores it has observed, through the barrier, before the counter
+          // update (cumulativity), for the generic and for the async proxy (the readers are TMA loads).
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          signal_counter(a.cell_done + nt);
         }
-        else if (cell_j == 64) cell_bwd_tile<64>(a, t, step, j0, b0, te, park, a.cell_done + nt);
-        else cell_bwd_tile<32>(a, t, step, j0, b0, te, park, a.cell_done + nt);
-        bar_sync(1, 256);   // the tile buffer may be reused
       }
     };
     for (uint32_t cb = 0; cb < ncb; ++cb) cell_pass(blockIdx.y * ncb + cb, 0);
