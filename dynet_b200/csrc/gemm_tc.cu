@@ -670,14 +670,16 @@ int make_map(dyb200_ctx* ctx, EncodeTiledFn enc, CUtensorMap* map, float* plane,
   return DYB200_OK;
 }
 
-// MN-major plane: element (m, k) at plane[k * pitch + m], `rows` valid m and K valid k; box = 32 (m) x 32 (k), in the
-// 128-byte swizzle with 32-byte atoms that umma_desc_mn describes.
+// MN-major plane: element (m, k) at plane[k * pitch + m], `rows` valid m and K valid k, as a 3-D tensor (m within a group
+// of 32, k, group): one box = 4 groups x 32 k x 32 m, in the 128-byte swizzle with 32-byte atoms that umma_desc_mn describes.
+// The last group may reach past `rows` into the pitch (those rows of the product are never stored).
 int make_map_mn(dyb200_ctx* ctx, EncodeTiledFn enc, CUtensorMap* map, float* plane, uint32_t rows, uint32_t K, uint32_t pitch) {
-  cuuint64_t dims[2] = {rows, K};
-  cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
-  cuuint32_t box[2] = {32, BK};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, plane, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  // (32 m, k, group of 32 m): one box brings 4 groups x 32 k rows x 128 bytes, group after group
+  cuuint64_t dims[3] = {32, K, (rows + 31) / 32};
+  cuuint64_t strides[2] = {(cuuint64_t)pitch * sizeof(float), 128};
+  cuuint32_t box[3] = {32, BK, 4};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, plane, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return dyb200_fail(ctx, DYB200_ECUDA, "cuTensorMapEncodeTiled failed with code %d (MN-major, rows %u, K %u, pitch %u)", (int)r, rows, K, pitch);
   return DYB200_OK;
@@ -929,11 +931,12 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   memset(&tm, 0, sizeof(tm));
   double flops = 0;
   const bool a_mn = A[0].mn_major != 0;
-  DYB_CHECK_ARG(ctx, !a_mn || (npairs == 1 && A[0].pitch % 4 == 0 && aligned16(A[0].hi) && aligned16(A[0].lo) && !B[0].mn_major),
-                "tensor GEMM: an MN-major left operand needs a single pair, a pitch that is a multiple of 4 and 16-byte aligned planes");
+  // (an MN-major plane is read in groups of 32 rows: its pitch covers the rows rounded up to 32)
+  DYB_CHECK_ARG(ctx, !a_mn || (npairs == 1 && A[0].pitch % 32 == 0 && A[0].pitch >= M && aligned16(A[0].hi) && aligned16(A[0].lo) && !B[0].mn_major),
+                "tensor GEMM: an MN-major left operand needs a single pair, a pitch that is a multiple of 32 and covers the rows, and 16-byte aligned planes");
   tm.a_mn = a_mn ? 1u : 0u;
   for (int p = 0; p < npairs; ++p) {
-    DYB_CHECK_ARG(ctx, A[p].rows == M && B[p].rows == N && A[p].K == B[p].K && (a_mn || A[p].pitch % 32 == 0) && B[p].pitch % 32 == 0,
+    DYB_CHECK_ARG(ctx, A[p].rows == M && B[p].rows == N && A[p].K == B[p].K && A[p].pitch % 32 == 0 && B[p].pitch % 32 == 0,
                   "tensor GEMM: packed operand shapes do not match (M %u, N %u)", M, N);
     flops += 2.0 * M * N * A[p].K;
     if (a_mn) {

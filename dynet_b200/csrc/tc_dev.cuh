@@ -25,8 +25,8 @@ constexpr uint32_t kChunkKB = 8;
 constexpr uint32_t kEpiWarps = 8;
 
 // pair p: t[4p] = A_hi, A_lo, B_hi, B_lo.  a_mn != 0 (one pair only): the A planes are MN-major - element (m, k) at
-// plane[k * pitch + m], the layout of a K x M row-major matrix - and t[0], t[1] are maps over (m fastest, k) with a box of
-// 32 m x 32 k; see load_a_tile / umma_desc_mn.
+// plane[k * pitch + m], the layout of a K x M row-major matrix - and t[0], t[1] are 3-D maps over (m within a group of 32,
+// k, group) with a box of 32 x 32 x 4; see load_a_tile / umma_desc_mn.
 struct TmapPack { CUtensorMap t[8]; uint32_t a_mn; };
 
 // The k-blocks of K split z of S: [b0, b0 + n0) of pair 0, then [b1, b1 + n1) of pair 1 (each pair cut into S equal shares).
@@ -67,6 +67,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   uint64_t d = 0;
@@ -77,7 +84,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                        // layout: SWIZZLE_128B
   return d;
 }
-// Same for an MN-major A tile of 128 m x 32 k as load_a_tile lays it out: four boxes of 32 m (128 bytes) x 32 k rows, 4096
+// Same for an MN-major A tile of 128 m x 32 k as load_a_tile lays it out: four groups of 32 m (128 bytes) x 32 k rows, 4096
 // bytes apart (the leading byte offset = distance between 32-element groups along m).  32-bit MN-major operands exist in
 // one shared-memory layout only, the 128-byte swizzle with 32-byte atoms (layout type 1; the tensor map's
 // SWIZZLE_128B_ATOM_32B): its pattern repeats every 4 k rows, so the stride byte offset - the distance between 4-k groups -
@@ -91,14 +98,13 @@ __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr) {
   d |= (uint64_t)1 << 61;
   return d;
 }
-// One plane of the A tile (m0 .., k-block kblk) into `st`: one box for a K-major plane; for an MN-major plane four boxes of
-// 32 m each (a box is at most one 128-byte swizzle span wide), 16 KB in either case.  Rows past the plane's extent arrive
-// as zeros.
+// One plane of the A tile (m0 .., k-block kblk) into `st`: one box of 16 KB in either layout (MN-major: the box's innermost
+// extent is one 128-byte swizzle span = 32 m, its outermost the four groups of the tile).  k rows past the plane's extent
+// arrive as zeros.
 __device__ __forceinline__ void load_a_tile(unsigned char* st, const CUtensorMap* map, uint64_t* bar, uint32_t kblk, uint32_t m0,
                                             uint32_t a_mn) {
   if (a_mn) {
-#pragma unroll
-    for (int g = 0; g < 4; ++g) tma_load_2d(st + g * 4096, map, bar, (int)(m0 + 32 * g), (int)(kblk * 32));
+    tma_load_3d(st, map, bar, 0, (int)(kblk * 32), (int)(m0 / 32));
   } else {
     tma_load_2d(st, map, bar, (int)(kblk * 32), (int)m0);
   }
