@@ -1158,8 +1158,13 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
 // T small products with K = batch, the packed K-major planes of every step are appended along K and ONE
 // product with K = sum k_t runs at the end: the tensor pipe sees a long reduction and C is read and
 // written once.  One A operand can serve two B operands (dWx and dWh share the gate gradient).
+// The A planes are MN-major: one row of Mp = M rounded up to 32 floats per COLUMN of the accumulator, element (m, col) at
+// plane[col * Mp + m].  For an LSTM layer that is the layout of the gate-gradient planes which the backward recurrence
+// reads as the K-major right operand of dx / dh = [Wx; Wh]^T dgates, so one set of planes, written once by the cell pass,
+// serves both products and no transposed copy exists.  The B planes are K-major (row = row of B, K = column of the
+// accumulator, pitch Kcap).
 struct dyb200_wgrad {
-  uint32_t M, N[2], Kcap;
+  uint32_t M, Mp, N[2], Kcap;
   uint32_t k;    // columns of A filled so far (the product at flush time runs over [0, k))
   uint32_t kb;   // columns of the B operands filled so far
   PackedOp A, B[2];
@@ -1178,7 +1183,8 @@ int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint3
   DYB_CHECK_ARG(ctx, w && a && b0 && (w->N[1] == 0 || b1), "wgrad_push: null argument");
   DYB_CHECK_ARG(ctx, w->k + k <= w->Kcap, "wgrad_push: %u + %u columns exceed the capacity %u", w->k, k, w->Kcap);
   if (k == 0) return DYB200_OK;
-  int rc = pack(ctx, a, lda, false, w->M, k, nullptr, 0, 0, w->A.hi + w->k, w->A.lo + w->k, w->Kcap, batch);
+  // (a is M x k column-major: the k rows of the MN-major planes, each M contiguous values)
+  int rc = pack(ctx, a, lda, true, k, w->M, nullptr, 0, 0, w->A.hi + (size_t)w->k * w->Mp, w->A.lo + (size_t)w->k * w->Mp, w->Mp, batch);
   if (rc) return rc;
   rc = pack(ctx, b0, ldb0, false, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + w->k, w->B[0].lo + w->k, w->Kcap, batch);
   if (rc) return rc;
@@ -1191,14 +1197,15 @@ int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint3
   return DYB200_OK;
 }
 
-// For a producer that writes the A planes of the next k columns itself: where they go, and the B operands queued as in
-// dyb200_wgrad_push_batched.  The accumulator advances by k.
+// For a producer that writes the A planes of the next k columns itself: where they go (k rows of `pitch` floats: row =
+// column of the accumulator, M values each), and the B operands queued as in dyb200_wgrad_push_batched.  The accumulator
+// advances by k.
 int dyb200_wgrad_reserve(dyb200_wgrad* w, uint32_t k, float** a_hi, float** a_lo, uint32_t* pitch, const float* b0, uint32_t ldb0,
                          const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1, int mask1_full,
                          dyb200_ctx* ctx, PackJobs* batch) {
   DYB_CHECK_ARG(ctx, w && b0 && (w->N[1] == 0 || b1), "wgrad_reserve: null argument");
   DYB_CHECK_ARG(ctx, w->k + k <= w->Kcap, "wgrad_reserve: %u + %u columns exceed the capacity %u", w->k, k, w->Kcap);
-  *a_hi = w->A.hi + w->k; *a_lo = w->A.lo + w->k; *pitch = w->Kcap;
+  *a_hi = w->A.hi + (size_t)w->k * w->Mp; *a_lo = w->A.lo + (size_t)w->k * w->Mp; *pitch = w->Mp;
   int rc = pack(ctx, b0, ldb0, 0, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + w->k, w->B[0].lo + w->k, w->Kcap, batch);
   if (rc) return rc;
   if (w->N[1]) {
@@ -1227,13 +1234,13 @@ int dyb200_wgrad_push_b_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const floa
 }
 int dyb200_wgrad_reserve_a_at(dyb200_wgrad* w, uint32_t col, uint32_t k, float** a_hi, float** a_lo, uint32_t* pitch, dyb200_ctx* ctx) {
   DYB_CHECK_ARG(ctx, w && (uint64_t)col + k <= w->Kcap, "wgrad_reserve_a_at: columns [%u, %u) exceed the capacity", col, col + k);
-  *a_hi = w->A.hi + col; *a_lo = w->A.lo + col; *pitch = w->Kcap;
+  *a_hi = w->A.hi + (size_t)col * w->Mp; *a_lo = w->A.lo + (size_t)col * w->Mp; *pitch = w->Mp;
   if (col + k > w->k) w->k = col + k;
   return DYB200_OK;
 }
 int dyb200_wgrad_pack_a_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const float* a, uint32_t lda, dyb200_ctx* ctx, PackJobs* batch) {
   DYB_CHECK_ARG(ctx, w && a && (uint64_t)col + k <= w->Kcap, "wgrad_pack_a_at: columns [%u, %u) exceed the capacity", col, col + k);
-  int rc = pack(ctx, a, lda, 0, w->M, k, nullptr, 0, 0, w->A.hi + col, w->A.lo + col, w->Kcap, batch);
+  int rc = pack(ctx, a, lda, 1, k, w->M, nullptr, 0, 0, w->A.hi + (size_t)col * w->Mp, w->A.lo + (size_t)col * w->Mp, w->Mp, batch);
   if (rc) return rc;
   if (col + k > w->k) w->k = col + k;
   return DYB200_OK;
@@ -1298,7 +1305,7 @@ int dyb200_wgrad_create(dyb200_ctx* ctx, uint32_t M, uint32_t N0, uint32_t N1, u
   DYB_CHECK_ARG(ctx, out && M > 0 && N0 > 0 && Kcap > 0, "wgrad_create: bad shape");
   dyb200_wgrad* w = (dyb200_wgrad*)calloc(1, sizeof(dyb200_wgrad));
   if (!w) return dyb200_fail(ctx, DYB200_ENOMEM, "wgrad_create: host allocation failed");
-  w->M = M; w->N[0] = N0; w->N[1] = N1; w->Kcap = round_up(Kcap, 32); w->k = 0; w->kb = 0;
+  w->M = M; w->Mp = round_up(M, 32); w->N[0] = N0; w->N[1] = N1; w->Kcap = round_up(Kcap, 32); w->k = 0; w->kb = 0;
   w->x_cols = 0; w->h_col = 0xffffffffu; w->step = 0;
   auto alloc = [&](PackedOp* p, uint32_t rows) -> bool {
     p->rows = rows; p->K = 0; p->pitch = w->Kcap;
@@ -1307,7 +1314,14 @@ int dyb200_wgrad_create(dyb200_ctx* ctx, uint32_t M, uint32_t N0, uint32_t N1, u
     if (cudaMalloc((void**)&p->lo, bytes) != cudaSuccess) { cudaGetLastError(); p->lo = nullptr; return false; }
     return true;
   };
-  bool ok = alloc(&w->A, M) && alloc(&w->B[0], N0) && (N1 == 0 || alloc(&w->B[1], N1));
+  // (A: Kcap rows of Mp floats, the same bytes as Mp rows of Kcap; zeroed once so that the padding beyond M stays finite)
+  bool ok = alloc(&w->A, w->Mp) && alloc(&w->B[0], N0) && (N1 == 0 || alloc(&w->B[1], N1));
+  if (ok) {
+    w->A.rows = M; w->A.pitch = w->Mp; w->A.mn_major = 1;
+    const size_t bytes = (size_t)w->Mp * w->Kcap * sizeof(float);
+    ok = cudaMemset(w->A.hi, 0, bytes) == cudaSuccess && cudaMemset(w->A.lo, 0, bytes) == cudaSuccess;
+    if (!ok) cudaGetLastError();
+  }
   if (!ok) {
     for (PackedOp* p : {&w->A, &w->B[0], &w->B[1]}) { if (p->hi) cudaFree(p->hi); if (p->lo) cudaFree(p->lo); }
     free(w);

@@ -206,10 +206,10 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd(const float* __restrict__
 
 // The same pass for shapes with H % 64 == 0 and B % 32 == 0, laid out for bandwidth: a CTA owns a tile of 64 hidden
 // units x 32 batch columns; threads read float4 along the hidden index (coalesced), and the tile of gate gradients
-// goes through shared memory so that it can also be written transposed.  Outputs, each optional except dc_tm1's
-// accumulate: dpre (fp32, [4H x B]); the K-major TF32 hi / lo planes of dpre in both layouts the products need
-// (dn: rows = batch, K = 4H, same indexing as dpre; dt: rows = 4H, K = batch, at column k0 of planes with pitch
-// dt_pitch), which saves the packing pass over dpre; db += row sums, formed as per-tile partial sums that the last
+// goes through shared memory for its row sums.  Outputs, each optional except dc_tm1's accumulate: dpre (fp32,
+// [4H x B]); the TF32 hi / lo planes of dpre (dn: rows = batch, K = 4H, same indexing as dpre - the K-major right operand
+// of the dx / dh product and, read MN-major, the left operand of the weight-gradient products), which saves the packing
+// pass over dpre; db += row sums, formed as per-tile partial sums that the last
 // CTA of each 64-unit stripe to arrive adds in ascending tile order (deterministic; counters[] returns to zero).
 constexpr int kCT_J = 64, kCT_B = 32;
 // JT = hidden units per tile: 64 (two columns per thread) or, for grids that would leave most SMs idle, 32 (one column)
@@ -218,8 +218,7 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __rest
                                                             const float* __restrict__ gates, const float* __restrict__ dEdh,
                                                             const float* __restrict__ dEdc, float* __restrict__ dc_tm1,
                                                             float* __restrict__ dpre, float* __restrict__ dn_hi, float* __restrict__ dn_lo,
-                                                            uint32_t dn_pitch, float* __restrict__ dt_hi, float* __restrict__ dt_lo,
-                                                            uint32_t dt_pitch, float* __restrict__ db, float* __restrict__ part,
+                                                            uint32_t dn_pitch, float* __restrict__ db, float* __restrict__ part,
                                                             uint32_t* __restrict__ counters, uint32_t H, uint32_t B) {
   dyb_grid_dep_sync();
   __shared__ float tile[4][JT][kCT_B + 1];
@@ -274,18 +273,12 @@ __global__ void __launch_bounds__(256) k_lstm_cell_bwd_tiled(const float* __rest
     }
   }
   __syncthreads();
-  // transposed write-out and row sums: warp w takes rows w, w + 8, ... of the 256 (gate, unit) rows; lane = batch column
+  // row sums: warp w takes rows w, w + 8, ... of the 256 (gate, unit) rows; lane = batch column
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (uint32_t r = warp; r < 4 * JT; r += 8) {
     const uint32_t gate = r / JT, jl = r % JT;
     const float v = tile[gate][jl][lane];
     const size_t row = (size_t)gate * H + j0 + jl;
-    if (dt_hi && b0 + lane < B) {
-      float hi, lo;
-      split_tf32(v, hi, lo);
-      dt_hi[row * dt_pitch + b0 + lane] = hi;
-      dt_lo[row * dt_pitch + b0 + lane] = lo;
-    }
     const float s = warp_sum(v);
     if (lane == 0) part[(size_t)blockIdx.y * 4 * H + row] = s;
   }
@@ -642,17 +635,17 @@ int dyb200_vanilla_lstm_bwd_fused_at(const dyb200_tensor* x, const dyb200_tensor
                      (!dc_tm1 || aligned16(dc_tm1->v));
   float* dpre = nullptr;
   if (tiled) {
-    if ((rc = dyb200_tc_planes(ctx, B, G, &dn))) return rc;
-    float *a_hi = nullptr, *a_lo = nullptr;
-    uint32_t a_pitch = 0;
+    // The planes of the gate gradient (row = batch column, K = 4H) are the right operand of the dx / dh product below and,
+    // read MN-major, the left operand of the weight-gradient products: with a deferred accumulator they are written straight
+    // into its A planes at this step's columns.
     if (deferred) {
       DYB_CHECK_ARG(ctx, dyb200_wgrad_rows(deferred) == G, "lstm_bwd_fused: the deferred accumulator has %u rows, the layer %u", dyb200_wgrad_rows(deferred), G);
-      if (at_col) rc = dyb200_wgrad_reserve_a_at(deferred, deferred_col, B, &a_hi, &a_lo, &a_pitch, ctx);
-      else rc = dyb200_wgrad_reserve(deferred, B, &a_hi, &a_lo, &a_pitch, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx, &batch);
+      dn.rows = B; dn.K = G;
+      if (at_col) rc = dyb200_wgrad_reserve_a_at(deferred, deferred_col, B, &dn.hi, &dn.lo, &dn.pitch, ctx);
+      else rc = dyb200_wgrad_reserve(deferred, B, &dn.hi, &dn.lo, &dn.pitch, x->v, I, mx, mx_full, h_tm1->v, H, mh, mh_full, ctx, &batch);
       if (rc) return rc;
     } else {
-      if ((rc = dyb200_tc_planes(ctx, G, B, &dt))) return rc;
-      a_hi = dt.hi; a_lo = dt.lo; a_pitch = dt.pitch;
+      if ((rc = dyb200_tc_planes(ctx, B, G, &dn))) return rc;
     }
     void* pp;
     const uint32_t btiles = (B + kCT_B - 1) / kCT_B;
@@ -662,11 +655,11 @@ int dyb200_vanilla_lstm_bwd_fused_at(const dyb200_tensor* x, const dyb200_tensor
     if (small_grid)
       dyb_launch(k_lstm_cell_bwd_tiled<32>, dim3(H / 32, btiles), 256, 0, ctx,
                  c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr, dc_tm1 ? dc_tm1->v : nullptr, nullptr, dn.hi, dn.lo, dn.pitch,
-                 a_hi, a_lo, a_pitch, db->v, (float*)pp, ctx->dev_flags + DYB200_DEV_COUNTER0, H, B);
+                 db->v, (float*)pp, ctx->dev_flags + DYB200_DEV_COUNTER0, H, B);
     else
       dyb_launch(k_lstm_cell_bwd_tiled<kCT_J>, dim3(H / kCT_J, btiles), 256, 0, ctx,
                  c_t->v, c_tm1->v, gates->v, dEdh->v, dEdc ? dEdc->v : nullptr, dc_tm1 ? dc_tm1->v : nullptr, nullptr, dn.hi, dn.lo, dn.pitch,
-                 a_hi, a_lo, a_pitch, db->v, (float*)pp, ctx->dev_flags + DYB200_DEV_COUNTER0, H, B);
+                 db->v, (float*)pp, ctx->dev_flags + DYB200_DEV_COUNTER0, H, B);
     DYB_LAUNCHED(ctx);
   } else {
     void* sp;
@@ -710,7 +703,9 @@ int dyb200_vanilla_lstm_bwd_fused_at(const dyb200_tensor* x, const dyb200_tensor
       if ((rc = dyb200_tc_gemm_packed(ctx, H, B, 1, &whT, &dn, e))) return rc;
     }
     if (deferred) return DYB200_OK;
-    if (!tiled) {   // (the tiled pass has written dt, and xt / ht went out with the batch above)
+    if (tiled) {    // (the planes of the tiled pass, read MN-major; xt / ht went out with the batch above)
+      dt = dn; dt.rows = G; dt.K = B; dt.mn_major = 1;
+    } else {
       if ((rc = dyb200_tc_pack(ctx, dpre, G, false, G, B, nullptr, 0, 0, &dt))) return rc;   // rows = 4H, K = batch
       if ((rc = dyb200_tc_pack(ctx, x->v, I, false, I, B, mx, I, mx_full, &xt))) return rc;       // (x .* mask_x)^T : rows = I, K = batch
       if ((rc = dyb200_tc_pack(ctx, h_tm1->v, H, false, H, B, mh, H, mh_full, &ht))) return rc;

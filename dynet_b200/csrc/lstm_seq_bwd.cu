@@ -33,8 +33,9 @@ struct SeqBwd {
   const float* gates; const float* cs;      // saved by the forward pass: step t at + t * 4H * B / + t * H * B
   const float* c0;                  // the cell state before step 0
   float* dh; float* dc; float* dx;          // H x (T B), H x (T B), I x (T B); all accumulate
-  float *dn_hi, *dn_lo; uint32_t dn_pitch;  // operand planes of dgates_t: row = batch column, K = 4H (one step at a time)
-  float *dt_hi, *dt_lo; uint32_t dt_pitch;  // the same values transposed for the weight gradients: row = gate row, column t B + b
+  // operand planes of dgates of all steps: row = t B + batch column, K = 4H.  The K-major right operand of each step's
+  // product and, read MN-major by the deferred weight-gradient products, their left operand (the accumulator's A planes).
+  float *dn_hi, *dn_lo; uint32_t dn_pitch;
   float* part;                      // per-tile row sums of dgates: [step][B / 32][4H]
   const float* mx; int mx_full; const float* mh; int mh_full;   // dropout masks of the layer's inputs (null: none)
   float* ws;                        // split exchange: [tile][split][BNT columns][128 rows]
@@ -48,9 +49,9 @@ __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefe
 
 // The cell pass of one tile (JT = 32 or 64 hidden units from j0, 32 batch columns from b0) of step t, by the 256 epilogue
 // threads (tid = 0..255); the arithmetic of k_lstm_cell_bwd_tiled, minus its sum over batch tiles (the per-tile row sums
-// go to a.part).  `tile` holds 4 x JT x 32 floats, un-padded; element (gate, unit, column) sits at column ^ (unit & 31) of
-// its row, which keeps both the element-wise writes (8 or 16 units per warp, one column) and the row-wise reads (one unit,
-// 32 columns) free of bank conflicts.
+// go to a.part).  `tile` holds 4 x JT x 32 floats, un-padded, for those row sums; element (gate, unit, column) sits at
+// column ^ (unit & 31) of its row, which keeps both the element-wise writes (8 or 16 units per warp, one column) and the
+// row-wise reads (one unit, 32 columns) free of bank conflicts.
 template <int JT>
 __device__ __forceinline__ void cell_bwd_tile(const SeqBwd& a, uint32_t t, uint32_t step, uint32_t j0, uint32_t b0, uint32_t tid, float* tile) {
   constexpr int kQuads = JT / 4, kLanes = 256 / kQuads, kCols = kCellB / kLanes;   // 8 x 32 x 1 or 16 x 16 x 2
@@ -94,7 +95,7 @@ __device__ __forceinline__ void cell_bwd_tile(const SeqBwd& a, uint32_t t, uint3
       tile[(2 * JT + u) * kCellB + col] = po[q]; tile[(3 * JT + u) * kCellB + col] = pg[q];
     }
     if (t) st4(dc_tm1 + e, make_float4(dcp_[0], dcp_[1], dcp_[2], dcp_[3]));
-    const size_t o = (size_t)b * a.dn_pitch + j;
+    const size_t o = ((size_t)t * B + b) * a.dn_pitch + j;
     float hi[4], lo[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) split_tf32(pi[q], hi[q], lo[q]);
@@ -110,20 +111,6 @@ __device__ __forceinline__ void cell_bwd_tile(const SeqBwd& a, uint32_t t, uint3
     st4(a.dn_hi + o + 3 * H, make_float4(hi[0], hi[1], hi[2], hi[3])); st4(a.dn_lo + o + 3 * H, make_float4(lo[0], lo[1], lo[2], lo[3]));
   }
   bar_sync(1, 256);
-  // transposed write-out: warp w takes rows w, w + 8, ... of the 4 JT (gate, unit) rows; lane = batch column
-  const uint32_t warp = tid >> 5, lane = tid & 31;
-  float* dt_hi = a.dt_hi + (size_t)t * B + b0 + lane;
-  float* dt_lo = a.dt_lo + (size_t)t * B + b0 + lane;
-#pragma unroll 8
-  for (uint32_t r = warp; r < 4 * JT; r += 8) {
-    const uint32_t gate = r / JT, jl = r % JT;
-    const float v = tile[(size_t)r * kCellB + (lane ^ (jl & 31))];
-    const size_t row = (size_t)gate * H + j0 + jl;
-    float hi, lo;
-    split_tf32(v, hi, lo);
-    dt_hi[row * a.dt_pitch] = hi;
-    dt_lo[row * a.dt_pitch] = lo;
-  }
   // row sums over the 32 columns, one row per thread, added in the order of a butterfly reduction over the columns (the
   // order of the per-step pass's warp_sum, seen from lane 0)
   if (tid < 4 * JT) {
@@ -208,13 +195,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_bwd(const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {
-      // TMA producer.  Every product reads rows [m0, m0 + 128) of [Wx; Wh]^T and rows [n0, n0 + BNT) of the dgates planes.
+      // TMA producer.  Every product reads rows [m0, m0 + 128) of [Wx; Wh]^T and rows [t B + n0, + BNT) of the dgates planes.
       uint32_t s = 0, ph = 0;
       bool fail = false;
       bool ready = false;   // the cell pass of the product about to start has already been seen complete
       for (uint32_t step = 0; step < steps && !fail; ++step) {
         for (uint32_t cb = 0; cb < ncb && !fail; ++cb) {
           const uint32_t nt = blockIdx.y * ncb + cb, n0 = nt * BNT;
+          const int brow = (int)((a.T - 1 - step) * a.B + n0);   // this step's rows of the dgates planes
           uint32_t it0 = 0;
           if (!ready) {
             // the weight tiles of the first k-blocks do not depend on this step's cell pass: request them before the wait
@@ -233,8 +221,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_bwd(const __grid_const
             asm volatile("fence.proxy.async.global;" ::: "memory");   // generic-proxy stores of other CTAs -> this CTA's TMA reads
             for (uint32_t j = 0; j < pre; ++j) {
               unsigned char* st = ring + (size_t)s * kStageBytes;
-              tma_load_2d(st + 2 * TILE_BYTES, &tm.t[2], &full_bar[s], (int)((ks.b0 + j) * BK), (int)n0);
-              tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[3], &full_bar[s], (int)((ks.b0 + j) * BK), (int)n0);
+              tma_load_2d(st + 2 * TILE_BYTES, &tm.t[2], &full_bar[s], (int)((ks.b0 + j) * BK), brow);
+              tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[3], &full_bar[s], (int)((ks.b0 + j) * BK), brow);
               if (++s == kStages) { s = 0; ph ^= 1; }
             }
             it0 = pre;
@@ -256,8 +244,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_bwd(const __grid_const
             mbar_expect_tx(&full_bar[s], STAGE_TX);
             tma_load_2d(st, &tm.t[0], &full_bar[s], (int)(kblk * BK), (int)m0);
             tma_load_2d(st + TILE_BYTES, &tm.t[1], &full_bar[s], (int)(kblk * BK), (int)m0);
-            tma_load_2d(st + 2 * TILE_BYTES, &tm.t[2], &full_bar[s], (int)(kblk * BK), (int)n0);
-            tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[3], &full_bar[s], (int)(kblk * BK), (int)n0);
+            tma_load_2d(st + 2 * TILE_BYTES, &tm.t[2], &full_bar[s], (int)(kblk * BK), brow);
+            tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[3], &full_bar[s], (int)(kblk * BK), brow);
             if (++s == kStages) { s = 0; ph ^= 1; }
           }
         }
@@ -502,7 +490,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_bwd(const __grid_const
         }
         if (te == 0) signal_counter(a.gemm_done + nt);
         // ---- the cell pass of this chain's next step: needs dh complete (every product CTA of the column block through
-        // with this step), which also frees the dgates planes of the block ----
+        // with this step) ----
         if (step + 1 < steps) {
           if (my_cta < n_cell) {
             bool got = true;
@@ -638,10 +626,9 @@ int dyb200_vanilla_lstm_seq_bwd(const dyb200_tensor* x_all, const dyb200_tensor*
     DYB_CHECK_ARG(ctx, dyb200_wgrad_rows(deferred) == G, "lstm_seq_bwd: the deferred accumulator has %u rows, the layer %u", dyb200_wgrad_rows(deferred), G);
     PackedOp wT, dn;
     if ((rc = dyb200_tc_param2(ctx, Wx->v, I, Wh->v, H, G, true, G, &wT))) return rc;
-    if ((rc = dyb200_tc_planes(ctx, B, G, &dn))) return rc;
-    float *a_hi = nullptr, *a_lo = nullptr;
-    uint32_t a_pitch = 0;
-    if ((rc = dyb200_wgrad_reserve_a_at(deferred, 0, T * B, &a_hi, &a_lo, &a_pitch, ctx))) return rc;
+    // the gate-gradient planes of all steps are the accumulator's A planes (columns [0, T B))
+    dn.rows = T * B; dn.K = G;
+    if ((rc = dyb200_wgrad_reserve_a_at(deferred, 0, T * B, &dn.hi, &dn.lo, &dn.pitch, ctx))) return rc;
     const uint32_t btiles = B / 32, tiles = tiles_m * tiles_n;
     void *pp, *pw = nullptr, *pc;
     if ((rc = dyb200_scratch(ctx, (size_t)T * btiles * G * sizeof(float), &pp))) return rc;
@@ -652,14 +639,13 @@ int dyb200_vanilla_lstm_seq_bwd(const dyb200_tensor* x_all, const dyb200_tensor*
     memset(&tm, 0, sizeof(tm));
     if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[0], wT.hi, I + H, G, wT.pitch, BM))) return rc;
     if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[1], wT.lo, I + H, G, wT.pitch, BM))) return rc;
-    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[2], dn.hi, B, G, dn.pitch, bn))) return rc;
-    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[3], dn.lo, B, G, dn.pitch, bn))) return rc;
+    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[2], dn.hi, T * B, G, dn.pitch, bn))) return rc;
+    if ((rc = dyb200_tc_make_tmap(ctx, &tm.t[3], dn.lo, T * B, G, dn.pitch, bn))) return rc;
     SeqBwd a;
     memset(&a, 0, sizeof(a));
     a.T = T; a.B = B; a.H = H; a.I = I; a.kb = kb; a.ncb = ncb;
     a.gates = gates_all->v; a.cs = c_all->v; a.c0 = c0->v; a.dh = dh_all->v; a.dc = dc_all->v; a.dx = dx_all->v;
     a.dn_hi = dn.hi; a.dn_lo = dn.lo; a.dn_pitch = dn.pitch;
-    a.dt_hi = a_hi; a.dt_lo = a_lo; a.dt_pitch = a_pitch;
     a.part = (float*)pp;
     a.mx = mx; a.mx_full = mx_full; a.mh = mh; a.mh_full = mh_full;
     a.ws = (float*)pw;
