@@ -765,10 +765,12 @@ def test_gemm_3xtf32_accuracy(g):
     assert rel.max() < 2e-6, rel.max()
 
 
-def test_deferred_weight_gradient(g):
-    """dyb200_wgrad: T pushes of (A_t, B0_t .* mask, B1_t) then one flush == sum_t A_t B_t^T added to C (float64 reference)."""
-    r = rng(162)
-    M, N0, N1, T = 192, 96, 40, 5
+@pytest.mark.parametrize("M,N0,N1", [(192, 96, 40), (77, 96, 40), (300, 33, 130)])
+def test_deferred_weight_gradient(g, M, N0, N1):
+    """dyb200_wgrad: T pushes of (A_t, B0_t .* mask, B1_t) then one flush == sum_t A_t B_t^T added to C (float64 reference).
+    The accumulator keeps A MN-major in rows of M rounded up to 32: M = 77 and 300 leave padding in every row and a last
+    group of 32 rows that is partly beyond M."""
+    r = rng(162 + M)
     ks = [32, 32, 32, 32, 20]
     w = g.ctx().wgrad_create(M, N0, N1, sum(ks))
     C0, C1 = randn(r, N0, M), randn(r, N1, M)
