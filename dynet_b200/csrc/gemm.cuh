@@ -128,6 +128,9 @@ bool dyb200_tc_eligible(uint32_t M, uint32_t N, double flops);
 // Planes of `rows x K` taken from the scratch arena, left for the caller's kernel to fill.
 int dyb200_tc_planes(dyb200_ctx* ctx, uint32_t rows, uint32_t K, PackedOp* out);
 struct dyb200_wgrad;
+// The accumulator's A planes (dgates of all columns) are MN-major: one row of `pitch` floats per column, M values each.  The
+// reserve calls hand out the rows of k columns for the caller's kernel to fill (a_hi / a_lo point at the first of them);
+// the same rows are a K-major right operand (rows = columns, K = M) for the caller's own products.
 int dyb200_wgrad_reserve(dyb200_wgrad* w, uint32_t k, float** a_hi, float** a_lo, uint32_t* pitch, const float* b0, uint32_t ldb0,
                          const float* mask0, int mask0_full, const float* b1, uint32_t ldb1, const float* mask1, int mask1_full,
                          dyb200_ctx* ctx, PackJobs* batch);
