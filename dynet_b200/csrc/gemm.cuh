@@ -39,11 +39,10 @@ struct GemmEpilogue {
   const float* maskC2 = nullptr; uint32_t maskc2_ld = 0; int maskc2_full = 0;
   // EPI_LSTM_CELL only: previous cell state and the two outputs, all H x N with leading dimension H
   const float* c_prev = nullptr; float* c_out = nullptr; float* h_out = nullptr;
-  // EPI_LSTM_CELL, optional: h .* hmask also goes out as the split operands of its consumers: straight planes (row =
-  // batch column, reduction index = hidden unit) for the next time step's gate product and transposed planes (row = hidden
-  // unit, reduction index = batch column) for the layer's weight-gradient product.  All 16-byte aligned, H % 4 == 0.
+  // EPI_LSTM_CELL, optional: h .* hmask also goes out as split operand planes (row = batch column, H values each): the
+  // K-major right operand of the next time step's gate product and, read MN-major, the right operand of the layer's
+  // weight-gradient product.  16-byte aligned, H % 4 == 0.
   float* hn_hi = nullptr; float* hn_lo = nullptr; uint32_t hn_pitch = 0;
-  float* ht_hi = nullptr; float* ht_lo = nullptr; uint32_t ht_pitch = 0;
   const float* hmask = nullptr; uint32_t hmask_ld = 0; int hmask_full = 0;
 };
 #ifdef __CUDACC__
@@ -57,10 +56,6 @@ __device__ __forceinline__ void epi_emit_h(const GemmEpilogue& epi, uint32_t u, 
   split_tf32(h.x, hi.x, lo.x); split_tf32(h.y, hi.y, lo.y); split_tf32(h.z, hi.z, lo.z); split_tf32(h.w, hi.w, lo.w);
   *reinterpret_cast<float4*>(epi.hn_hi + (size_t)n * epi.hn_pitch + u) = hi;
   *reinterpret_cast<float4*>(epi.hn_lo + (size_t)n * epi.hn_pitch + u) = lo;
-  float* th = epi.ht_hi + (size_t)u * epi.ht_pitch + n;
-  float* tl = epi.ht_lo + (size_t)u * epi.ht_pitch + n;
-  th[0] = hi.x; th[epi.ht_pitch] = hi.y; th[2 * (size_t)epi.ht_pitch] = hi.z; th[3 * (size_t)epi.ht_pitch] = hi.w;
-  tl[0] = lo.x; tl[epi.ht_pitch] = lo.y; tl[2 * (size_t)epi.ht_pitch] = lo.z; tl[3 * (size_t)epi.ht_pitch] = lo.w;
 }
 #endif
 // Row m of the product -> destination pointer of column 0, leading dimension and mask of that row.
@@ -155,9 +150,8 @@ int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint3
 // ---- sequence kernels (lstm_seq.cu) ----
 // Operand planes of a whole sequence held by an accumulator after dyb200_wgrad_pack_inputs: X = x .* mask_x (row = column
 // of the sequence, K = I), Hs = h_tm1 .* mask_h (row = column, K = H; rows [c, c + step) are the input of the step that
-// starts at column c), B1 = the transposed h planes of the weight-gradient product.  False when they are not in place for
-// `steps` steps of `step` columns.
-struct SeqPlanes { PackedOp X, Hs, B1; };
+// starts at column c).  False when they are not in place for `steps` steps of `step` columns.
+struct SeqPlanes { PackedOp X, Hs; };
 bool dyb200_wgrad_seq_planes(const dyb200_wgrad* w, uint32_t steps, uint32_t step, SeqPlanes* out);
 int dyb200_wgrad_seq_h0(dyb200_wgrad* w, const float* h0, const float* mh, int mh_full, dyb200_ctx* ctx, PackJobs* batch);
 void dyb200_wgrad_seq_done(dyb200_wgrad* w);

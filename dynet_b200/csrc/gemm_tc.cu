@@ -86,8 +86,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         mbar_expect_tx(&full_bar[s], STAGE_TX);
         load_a_tile(st, &tm.t[4 * pair + 0], &full_bar[s], kblk, m0, tm.a_mn);
         load_a_tile(st + TILE_BYTES, &tm.t[4 * pair + 1], &full_bar[s], kblk, m0, tm.a_mn);
-        tma_load_2d(st + 2 * TILE_BYTES, &tm.t[4 * pair + 2], &full_bar[s], (int)(kblk * BK), (int)n0);
-        tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), (int)n0);
+        load_b_tile(st + 2 * TILE_BYTES, &tm.t[4 * pair + 2], &full_bar[s], kblk, n0, tm.b_mn);
+        load_b_tile(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm.t[4 * pair + 3], &full_bar[s], kblk, n0, tm.b_mn);
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
     }
@@ -102,18 +102,19 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
       // descriptors of the three stages are built once, stage / phase / chunk counters are carried instead of divided,
       // and the 12 MMAs of a k-block go out in one block of PTX.
       // instruction descriptor: D = f32, A = B = tf32, both K-major, N = BNT, M = 128
-      // (bit 15: A is MN-major)
-      const uint32_t a_mn = tm.a_mn;
+      // (bits 15 / 16: A / B is MN-major)
+      const uint32_t a_mn = tm.a_mn, b_mn = tm.b_mn;
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24) |
-                             (a_mn ? 1u << 15 : 0u);
-      const uint64_t a_step = a_mn ? 64 : 2;
+                             (a_mn ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
+      const uint64_t a_step = a_mn ? 64 : 2, b_step = b_mn ? 64 : 2;
       uint64_t d_a_hi[STAGES], d_a_lo[STAGES], d_b_hi[STAGES], d_b_lo[STAGES];
 #pragma unroll
       for (int q = 0; q < STAGES; ++q) {
         const uint32_t base = smem_u32(ring + (size_t)q * STAGE_BYTES);
         d_a_hi[q] = a_mn ? umma_desc_mn(base) : umma_desc(base);
         d_a_lo[q] = a_mn ? umma_desc_mn(base + TILE_BYTES) : umma_desc(base + TILE_BYTES);
-        d_b_hi[q] = umma_desc(base + 2 * TILE_BYTES); d_b_lo[q] = umma_desc(base + 2 * TILE_BYTES + TILE_B_BYTES);
+        d_b_hi[q] = b_mn ? umma_desc_mn(base + 2 * TILE_BYTES) : umma_desc(base + 2 * TILE_BYTES);
+        d_b_lo[q] = b_mn ? umma_desc_mn(base + 2 * TILE_BYTES + TILE_B_BYTES) : umma_desc(base + 2 * TILE_BYTES + TILE_B_BYTES);
       }
       // The tensor core truncates when it aligns addends to the accumulator, a bias that grows with the length of
       // the accumulation chain.  So the chain is cut every kChunkKB k-blocks: chunk c accumulates into TMEM buffer
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         else if (s == 1) { a_hi = d_a_hi[1]; a_lo = d_a_lo[1]; b_hi = d_b_hi[1]; b_lo = d_b_lo[1]; }
         else { a_hi = d_a_hi[2]; a_lo = d_a_lo[2]; b_hi = d_b_hi[2]; b_lo = d_b_lo[2]; }
         const uint32_t acc = tmem_base + buf * BN;
-        issue_kblock(acc, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk, a_step);
+        issue_kblock(acc, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk, a_step, b_step);
         umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
         const bool chunk_ends = in_chunk == kChunkKB - 1 || it == total - 1;
         if (chunk_ends) { umma_commit(&acc_full[buf]); in_chunk = 0; ++chunk; buf ^= 1; }
@@ -301,8 +302,8 @@ __device__ __noinline__ void persist_producer(const TmapPack* tm, unsigned char*
       mbar_expect_tx(&full_bar[s], STAGE_TX);
       load_a_tile(st, &tm->t[4 * pair + 0], &full_bar[s], kblk, m0, tm->a_mn);
       load_a_tile(st + TILE_BYTES, &tm->t[4 * pair + 1], &full_bar[s], kblk, m0, tm->a_mn);
-      tma_load_2d(st + 2 * TILE_BYTES, &tm->t[4 * pair + 2], &full_bar[s], (int)(kblk * BK), (int)n0);
-      tma_load_2d(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm->t[4 * pair + 3], &full_bar[s], (int)(kblk * BK), (int)n0);
+      load_b_tile(st + 2 * TILE_BYTES, &tm->t[4 * pair + 2], &full_bar[s], kblk, n0, tm->b_mn);
+      load_b_tile(st + 2 * TILE_BYTES + TILE_B_BYTES, &tm->t[4 * pair + 3], &full_bar[s], kblk, n0, tm->b_mn);
       if (++s == STAGES) { s = 0; ph ^= 1; }
     }
   }
@@ -312,18 +313,19 @@ __device__ __noinline__ void persist_producer(const TmapPack* tm, unsigned char*
 template <int BNT>
 __device__ __noinline__ void persist_issue(unsigned char* ring, uint64_t* full_bar, uint64_t* empty_bar, uint64_t* acc_full,
                                            uint64_t* acc_empty, uint32_t tmem_base, uint32_t tiles, uint32_t kb0, uint32_t kb1, uint32_t S,
-                                           uint32_t a_mn, uint32_t* flags) {
+                                           uint32_t a_mn, uint32_t b_mn, uint32_t* flags) {
   constexpr int TILE_B_BYTES = BNT * BK * 4;
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24) |
-                         (a_mn ? 1u << 15 : 0u);
-  const uint64_t a_step = a_mn ? 64 : 2;
+                         (a_mn ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
+  const uint64_t a_step = a_mn ? 64 : 2, b_step = b_mn ? 64 : 2;
   uint64_t d_a_hi[STAGES], d_a_lo[STAGES], d_b_hi[STAGES], d_b_lo[STAGES];
 #pragma unroll
   for (int q = 0; q < STAGES; ++q) {
     const uint32_t base = smem_u32(ring + (size_t)q * STAGE_BYTES);
     d_a_hi[q] = a_mn ? umma_desc_mn(base) : umma_desc(base);
     d_a_lo[q] = a_mn ? umma_desc_mn(base + TILE_BYTES) : umma_desc(base + TILE_BYTES);
-    d_b_hi[q] = umma_desc(base + 2 * TILE_BYTES); d_b_lo[q] = umma_desc(base + 2 * TILE_BYTES + TILE_B_BYTES);
+    d_b_hi[q] = b_mn ? umma_desc_mn(base + 2 * TILE_BYTES) : umma_desc(base + 2 * TILE_BYTES);
+    d_b_lo[q] = b_mn ? umma_desc_mn(base + 2 * TILE_BYTES + TILE_B_BYTES) : umma_desc(base + 2 * TILE_BYTES + TILE_B_BYTES);
   }
   // stage, phase and chunk counters run on across tiles; an accumulation chain never crosses a tile boundary
   uint32_t s = 0, ph = 0, chunk = 0, buf = 0;
@@ -343,7 +345,7 @@ __device__ __noinline__ void persist_issue(unsigned char* ring, uint64_t* full_b
       else if (s == 1) { a_hi = d_a_hi[1]; a_lo = d_a_lo[1]; b_hi = d_b_hi[1]; b_lo = d_b_lo[1]; }
       else { a_hi = d_a_hi[2]; a_lo = d_a_lo[2]; b_hi = d_b_hi[2]; b_lo = d_b_lo[2]; }
       const uint32_t acc = tmem_base + buf * BN;
-      issue_kblock(acc, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk, a_step);
+      issue_kblock(acc, a_hi, a_lo, b_hi, b_lo, idesc, in_chunk, a_step, b_step);
       umma_commit(&empty_bar[s]);
       const bool chunk_ends = in_chunk == kChunkKB - 1 || it == kb - 1;
       if (chunk_ends) { umma_commit(&acc_full[buf]); in_chunk = 0; ++chunk; buf = chunk % kPersistBufs; }
@@ -386,7 +388,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_persist(const __grid_const
   if (warp == 0) {
     if (lane == 0) persist_producer<BNT>(&tm, ring, full_bar, empty_bar, tiles, tiles_m, (N + BNT - 1) / BNT, gm, kb0, kb1, S, flags);
   } else if (warp == 1) {
-    if (lane == 0) persist_issue<BNT>(ring, full_bar, empty_bar, acc_full, acc_empty, tmem_base, tiles, kb0, kb1, S, tm.a_mn, flags);
+    if (lane == 0) persist_issue<BNT>(ring, full_bar, empty_bar, acc_full, acc_empty, tmem_base, tiles, kb0, kb1, S, tm.a_mn, tm.b_mn, flags);
   } else {
     // epilogue warps 2..9: TMEM lanes 32 (warp % 4) .. +31; warps 2-5 hold columns 0-63 of the tile, warps 6-9 columns 64-127
     const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
@@ -673,11 +675,12 @@ int make_map(dyb200_ctx* ctx, EncodeTiledFn enc, CUtensorMap* map, float* plane,
 // MN-major plane: element (m, k) at plane[k * pitch + m], `rows` valid m and K valid k, as a 3-D tensor (m within a group
 // of 32, k, group): one box = 4 groups x 32 k x 32 m, in the 128-byte swizzle with 32-byte atoms that umma_desc_mn describes.
 // The last group may reach past `rows` into the pitch (those rows of the product are never stored).
-int make_map_mn(dyb200_ctx* ctx, EncodeTiledFn enc, CUtensorMap* map, float* plane, uint32_t rows, uint32_t K, uint32_t pitch) {
-  // (32 m, k, group of 32 m): one box brings 4 groups x 32 k rows x 128 bytes, group after group
+int make_map_mn(dyb200_ctx* ctx, EncodeTiledFn enc, CUtensorMap* map, float* plane, uint32_t rows, uint32_t K, uint32_t pitch,
+                uint32_t box_rows = BM) {
+  // (32 m, k, group of 32 m): one box brings box_rows / 32 groups x 32 k rows x 128 bytes, group after group
   cuuint64_t dims[3] = {32, K, (rows + 31) / 32};
   cuuint64_t strides[2] = {(cuuint64_t)pitch * sizeof(float), 128};
-  cuuint32_t box[3] = {32, BK, 4};
+  cuuint32_t box[3] = {32, BK, box_rows / 32};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, plane, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -930,11 +933,14 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
   TmapPack tm;
   memset(&tm, 0, sizeof(tm));
   double flops = 0;
-  const bool a_mn = A[0].mn_major != 0;
+  const bool a_mn = A[0].mn_major != 0, b_mn = B[0].mn_major != 0;
   // (an MN-major plane is read in groups of 32 rows: its pitch covers the rows rounded up to 32)
-  DYB_CHECK_ARG(ctx, !a_mn || (npairs == 1 && A[0].pitch % 32 == 0 && A[0].pitch >= M && aligned16(A[0].hi) && aligned16(A[0].lo) && !B[0].mn_major),
+  DYB_CHECK_ARG(ctx, !a_mn || (npairs == 1 && A[0].pitch % 32 == 0 && A[0].pitch >= M && aligned16(A[0].hi) && aligned16(A[0].lo)),
                 "tensor GEMM: an MN-major left operand needs a single pair, a pitch that is a multiple of 32 and covers the rows, and 16-byte aligned planes");
+  DYB_CHECK_ARG(ctx, !b_mn || (npairs == 1 && B[0].pitch % 32 == 0 && B[0].pitch >= N && aligned16(B[0].hi) && aligned16(B[0].lo)),
+                "tensor GEMM: an MN-major right operand needs a single pair, a pitch that is a multiple of 32 and covers the rows, and 16-byte aligned planes");
   tm.a_mn = a_mn ? 1u : 0u;
+  tm.b_mn = b_mn ? 1u : 0u;
   for (int p = 0; p < npairs; ++p) {
     DYB_CHECK_ARG(ctx, A[p].rows == M && B[p].rows == N && A[p].K == B[p].K && A[p].pitch % 32 == 0 && B[p].pitch % 32 == 0,
                   "tensor GEMM: packed operand shapes do not match (M %u, N %u)", M, N);
@@ -946,8 +952,13 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
       if ((rc = make_map(ctx, enc, &tm.t[4 * p + 0], A[p].hi, M, A[p].K, A[p].pitch))) return rc;
       if ((rc = make_map(ctx, enc, &tm.t[4 * p + 1], A[p].lo, M, A[p].K, A[p].pitch))) return rc;
     }
-    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 2], B[p].hi, N, B[p].K, B[p].pitch, bn))) return rc;
-    if ((rc = make_map(ctx, enc, &tm.t[4 * p + 3], B[p].lo, N, B[p].K, B[p].pitch, bn))) return rc;
+    if (b_mn) {
+      if ((rc = make_map_mn(ctx, enc, &tm.t[2], B[0].hi, N, B[0].K, B[0].pitch, bn))) return rc;
+      if ((rc = make_map_mn(ctx, enc, &tm.t[3], B[0].lo, N, B[0].K, B[0].pitch, bn))) return rc;
+    } else {
+      if ((rc = make_map(ctx, enc, &tm.t[4 * p + 2], B[p].hi, N, B[p].K, B[p].pitch, bn))) return rc;
+      if ((rc = make_map(ctx, enc, &tm.t[4 * p + 3], B[p].lo, N, B[p].K, B[p].pitch, bn))) return rc;
+    }
   }
   if (npairs == 1) for (int k = 0; k < 4; ++k) tm.t[4 + k] = tm.t[k];
   uint32_t kb0 = round_up(A[0].K, 32) / BK, kb1 = npairs > 1 ? round_up(A[1].K, 32) / BK : 0;
@@ -1072,7 +1083,8 @@ int dyb200_tc_gemm_packed(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, c
     for (int p = 0; p < npairs; ++p) {
       A2[p] = A[p]; A2[p].rows = M - m_off;   // (MN-major planes: the rows are the fast index)
       A2[p].hi += a_mn ? (size_t)m_off : (size_t)m_off * A[p].pitch; A2[p].lo += a_mn ? (size_t)m_off : (size_t)m_off * A[p].pitch;
-      B2[p] = B[p]; B2[p].rows = N - n_off; B2[p].hi += (size_t)n_off * B[p].pitch; B2[p].lo += (size_t)n_off * B[p].pitch;
+      B2[p] = B[p]; B2[p].rows = N - n_off;
+      B2[p].hi += b_mn ? (size_t)n_off : (size_t)n_off * B[p].pitch; B2[p].lo += b_mn ? (size_t)n_off : (size_t)n_off * B[p].pitch;
     }
     GemmEpilogue e2 = epi;
     e2.C += m_off + (size_t)epi.ldc * n_off;
@@ -1158,23 +1170,29 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
 // T small products with K = batch, the packed K-major planes of every step are appended along K and ONE
 // product with K = sum k_t runs at the end: the tensor pipe sees a long reduction and C is read and
 // written once.  One A operand can serve two B operands (dWx and dWh share the gate gradient).
-// The A planes are MN-major: one row of Mp = M rounded up to 32 floats per COLUMN of the accumulator, element (m, col) at
-// plane[col * Mp + m].  For an LSTM layer that is the layout of the gate-gradient planes which the backward recurrence
-// reads as the K-major right operand of dx / dh = [Wx; Wh]^T dgates, so one set of planes, written once by the cell pass,
-// serves both products and no transposed copy exists.  The B planes are K-major (row = row of B, K = column of the
-// accumulator, pitch Kcap).
+// All planes are MN-major for that product: one row per COLUMN of the accumulator - Mp = M rounded up to 32 floats in A,
+// Np[j] in B[j] - element (m, col) at plane[col * Mp + m].  For an LSTM layer these are the layouts the recurrence reads
+// K-major: A = the gate-gradient planes, right operand of dx / dh = [Wx; Wh]^T dgates in the backward pass; B[0] = x .*
+// mask_x and B[1] = h_tm1 .* mask_h, right operands of the gate product in the forward pass.  So every set of planes is
+// written once, by whoever produces the values (a packing launch, the LSTM epilogue, the cell pass), serves both products,
+// and no transposed copy exists.
 struct dyb200_wgrad {
-  uint32_t M, Mp, N[2], Kcap;
+  uint32_t M, Mp, N[2], Np[2], Kcap;
   uint32_t k;    // columns of A filled so far (the product at flush time runs over [0, k))
   uint32_t kb;   // columns of the B operands filled so far
   PackedOp A, B[2];
-  // Pre-split sequence inputs (dyb200_wgrad_pack_inputs): forward operand planes, one row per column of the sequence.
-  // X: x .* mask_x of all columns; Hs: h_tm1 .* mask_h, rows [c, c + batch) = input of the step that starts at column c,
-  // written by the LSTM epilogue of the step before.  x_cols = columns of X that are valid; h_col = the column whose Hs
-  // rows (and B[1] columns) the last forward call wrote; step = columns per step of that sequence.
-  PackedOp X, Hs;
+  // Pre-split sequence inputs (dyb200_wgrad_pack_inputs): x_cols = columns of B[0] that hold a whole sequence's x .* mask_x
+  // (0: none); rows [c, c + batch) of B[1] are the h input of the step that starts at column c, written by the LSTM
+  // epilogue of the step before; h_col = the column whose B[1] rows the last forward call wrote; step = columns per step
+  // of that sequence (0: varying).
   uint32_t x_cols, h_col, step;
 };
+// natural pack of the k columns [col, col + k) of operand j (b is N[j] x k column-major; the mask is indexed like b)
+static int pack_b_rows(dyb200_ctx* ctx, dyb200_wgrad* w, int j, uint32_t col, uint32_t k, const float* b, uint32_t ldb, const float* mask,
+                       int mask_full, PackJobs* batch) {
+  return pack(ctx, b, ldb, 1, k, w->N[j], mask, ldb, mask_full, w->B[j].hi + (size_t)col * w->Np[j], w->B[j].lo + (size_t)col * w->Np[j],
+              w->Np[j], batch);
+}
 
 // Same as dyb200_wgrad_push, but the packing work is queued in `batch` (the caller launches it).
 int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda, const float* b0, uint32_t ldb0,
@@ -1186,10 +1204,10 @@ int dyb200_wgrad_push_batched(dyb200_wgrad* w, uint32_t k, const float* a, uint3
   // (a is M x k column-major: the k rows of the MN-major planes, each M contiguous values)
   int rc = pack(ctx, a, lda, true, k, w->M, nullptr, 0, 0, w->A.hi + (size_t)w->k * w->Mp, w->A.lo + (size_t)w->k * w->Mp, w->Mp, batch);
   if (rc) return rc;
-  rc = pack(ctx, b0, ldb0, false, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + w->k, w->B[0].lo + w->k, w->Kcap, batch);
+  rc = pack_b_rows(ctx, w, 0, w->k, k, b0, ldb0, mask0, mask0_full, batch);
   if (rc) return rc;
   if (w->N[1]) {
-    rc = pack(ctx, b1, ldb1, false, w->N[1], k, mask1, ldb1, mask1_full, w->B[1].hi + w->k, w->B[1].lo + w->k, w->Kcap, batch);
+    rc = pack_b_rows(ctx, w, 1, w->k, k, b1, ldb1, mask1, mask1_full, batch);
     if (rc) return rc;
   }
   w->k += k;
@@ -1206,10 +1224,10 @@ int dyb200_wgrad_reserve(dyb200_wgrad* w, uint32_t k, float** a_hi, float** a_lo
   DYB_CHECK_ARG(ctx, w && b0 && (w->N[1] == 0 || b1), "wgrad_reserve: null argument");
   DYB_CHECK_ARG(ctx, w->k + k <= w->Kcap, "wgrad_reserve: %u + %u columns exceed the capacity %u", w->k, k, w->Kcap);
   *a_hi = w->A.hi + (size_t)w->k * w->Mp; *a_lo = w->A.lo + (size_t)w->k * w->Mp; *pitch = w->Mp;
-  int rc = pack(ctx, b0, ldb0, 0, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + w->k, w->B[0].lo + w->k, w->Kcap, batch);
+  int rc = pack_b_rows(ctx, w, 0, w->k, k, b0, ldb0, mask0, mask0_full, batch);
   if (rc) return rc;
   if (w->N[1]) {
-    rc = pack(ctx, b1, ldb1, 0, w->N[1], k, mask1, ldb1, mask1_full, w->B[1].hi + w->k, w->B[1].lo + w->k, w->Kcap, batch);
+    rc = pack_b_rows(ctx, w, 1, w->k, k, b1, ldb1, mask1, mask1_full, batch);
     if (rc) return rc;
   }
   w->k += k;
@@ -1223,10 +1241,10 @@ int dyb200_wgrad_push_b_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const floa
   // (b0 == nullptr: the first operand's columns are already in place, see dyb200_wgrad_pack_inputs)
   DYB_CHECK_ARG(ctx, w && (w->N[1] == 0 || b1), "wgrad_push_b_at: null argument");
   DYB_CHECK_ARG(ctx, (uint64_t)col + k <= w->Kcap, "wgrad_push_b_at: columns [%u, %u) exceed the capacity %u", col, col + k, w->Kcap);
-  int rc = b0 ? pack(ctx, b0, ldb0, 0, w->N[0], k, mask0, ldb0, mask0_full, w->B[0].hi + col, w->B[0].lo + col, w->Kcap, batch) : DYB200_OK;
+  int rc = b0 ? pack_b_rows(ctx, w, 0, col, k, b0, ldb0, mask0, mask0_full, batch) : DYB200_OK;
   if (rc) return rc;
   if (w->N[1]) {
-    rc = pack(ctx, b1, ldb1, 0, w->N[1], k, mask1, ldb1, mask1_full, w->B[1].hi + col, w->B[1].lo + col, w->Kcap, batch);
+    rc = pack_b_rows(ctx, w, 1, col, k, b1, ldb1, mask1, mask1_full, batch);
     if (rc) return rc;
   }
   if (col + k > w->kb) w->kb = col + k;
@@ -1246,44 +1264,39 @@ int dyb200_wgrad_pack_a_at(dyb200_wgrad* w, uint32_t col, uint32_t k, const floa
   return DYB200_OK;
 }
 bool dyb200_wgrad_x_planes(const dyb200_wgrad* w, uint32_t col, uint32_t k, PackedOp* out) {
-  if (!w || !w->X.hi || (w->step && k != w->step) || (uint64_t)col + k > w->x_cols) return false;
-  *out = w->X;
-  out->rows = k; out->K = w->N[0];
-  out->hi += (size_t)col * w->X.pitch; out->lo += (size_t)col * w->X.pitch;
+  if (!w || (w->step && k != w->step) || (uint64_t)col + k > w->x_cols) return false;
+  *out = w->B[0];
+  out->rows = k; out->K = w->N[0]; out->mn_major = 0;
+  out->hi += (size_t)col * w->Np[0]; out->lo += (size_t)col * w->Np[0];
   return true;
 }
 bool dyb200_wgrad_h_planes(const dyb200_wgrad* w, uint32_t col, uint32_t k, PackedOp* out) {
-  if (!w || !w->Hs.hi || (w->step && k != w->step) || w->h_col != col || (uint64_t)col + k > w->x_cols) return false;
-  *out = w->Hs;
-  out->rows = k; out->K = w->N[1];
-  out->hi += (size_t)col * w->Hs.pitch; out->lo += (size_t)col * w->Hs.pitch;
+  if (!w || w->N[1] == 0 || (w->step && k != w->step) || w->h_col != col || (uint64_t)col + k > w->x_cols) return false;
+  *out = w->B[1];
+  out->rows = k; out->K = w->N[1]; out->mn_major = 0;
+  out->hi += (size_t)col * w->Np[1]; out->lo += (size_t)col * w->Np[1];
   return true;
 }
 bool dyb200_wgrad_next_h(dyb200_wgrad* w, uint32_t col, uint32_t k, GemmEpilogue* epi) {
   // (all k columns of h_t are written at the next step's position; with steps of varying width the next step may use fewer)
-  if (!w || !w->Hs.hi || (w->step && k != w->step) || (uint64_t)col + 2 * (uint64_t)k > w->x_cols) return false;
+  if (!w || w->N[1] == 0 || w->x_cols == 0 || (w->step && k != w->step) || (uint64_t)col + 2 * (uint64_t)k > w->x_cols) return false;
   const uint32_t next = col + k;
-  epi->hn_hi = w->Hs.hi + (size_t)next * w->Hs.pitch; epi->hn_lo = w->Hs.lo + (size_t)next * w->Hs.pitch; epi->hn_pitch = w->Hs.pitch;
-  epi->ht_hi = w->B[1].hi + next; epi->ht_lo = w->B[1].lo + next; epi->ht_pitch = w->Kcap;
+  epi->hn_hi = w->B[1].hi + (size_t)next * w->Np[1]; epi->hn_lo = w->B[1].lo + (size_t)next * w->Np[1]; epi->hn_pitch = w->Np[1];
   w->h_col = next;
   if (next + k > w->kb) w->kb = next + k;
   return true;
 }
 // ---- sequence kernels (lstm_seq.cu): the operand planes the accumulator holds for a whole sequence ----
 bool dyb200_wgrad_seq_planes(const dyb200_wgrad* w, uint32_t steps, uint32_t step, SeqPlanes* out) {
-  if (!w || !w->X.hi || !w->Hs.hi || w->N[1] == 0 || w->step != step || w->x_cols != (uint64_t)steps * step) return false;
-  out->X = w->X; out->X.rows = w->x_cols; out->X.K = w->N[0];
-  out->Hs = w->Hs; out->Hs.rows = w->x_cols; out->Hs.K = w->N[1];
-  out->B1 = w->B[1];
+  if (!w || w->N[1] == 0 || w->x_cols == 0 || w->step != step || w->x_cols != (uint64_t)steps * step) return false;
+  out->X = w->B[0]; out->X.rows = w->x_cols; out->X.K = w->N[0]; out->X.mn_major = 0;
+  out->Hs = w->B[1]; out->Hs.rows = w->x_cols; out->Hs.K = w->N[1]; out->Hs.mn_major = 0;
   return true;
 }
-// h of the first step (h0 .* mask_h): operand planes of columns [0, step) for the gate product and, transposed, for the
-// weight-gradient product.  The same values dyb200_vanilla_lstm_fwd_fused_at splits at deferred_col = 0.
+// h of the first step (h0 .* mask_h): operand planes of columns [0, step).  The same values
+// dyb200_vanilla_lstm_fwd_fused_at splits at deferred_col = 0.
 int dyb200_wgrad_seq_h0(dyb200_wgrad* w, const float* h0, const float* mh, int mh_full, dyb200_ctx* ctx, PackJobs* batch) {
-  const uint32_t H = w->N[1], B = w->step;
-  int rc = pack(ctx, h0, H, 1, B, H, mh, H, mh_full, w->Hs.hi, w->Hs.lo, w->Hs.pitch, batch);
-  if (rc) return rc;
-  return pack(ctx, h0, H, 0, H, B, mh, H, mh_full, w->B[1].hi, w->B[1].lo, w->Kcap, batch);
+  return pack_b_rows(ctx, w, 1, 0, w->step, h0, w->N[1], mh, mh_full, batch);
 }
 void dyb200_wgrad_seq_done(dyb200_wgrad* w) {
   w->h_col = w->x_cols - w->step;   // the planes of the last step's h input are the most recent ones
@@ -1305,7 +1318,8 @@ int dyb200_wgrad_create(dyb200_ctx* ctx, uint32_t M, uint32_t N0, uint32_t N1, u
   DYB_CHECK_ARG(ctx, out && M > 0 && N0 > 0 && Kcap > 0, "wgrad_create: bad shape");
   dyb200_wgrad* w = (dyb200_wgrad*)calloc(1, sizeof(dyb200_wgrad));
   if (!w) return dyb200_fail(ctx, DYB200_ENOMEM, "wgrad_create: host allocation failed");
-  w->M = M; w->Mp = round_up(M, 32); w->N[0] = N0; w->N[1] = N1; w->Kcap = round_up(Kcap, 32); w->k = 0; w->kb = 0;
+  w->M = M; w->Mp = round_up(M, 32); w->N[0] = N0; w->N[1] = N1; w->Np[0] = round_up(N0, 32); w->Np[1] = round_up(N1, 32);
+  w->Kcap = round_up(Kcap, 32); w->k = 0; w->kb = 0;
   w->x_cols = 0; w->h_col = 0xffffffffu; w->step = 0;
   auto alloc = [&](PackedOp* p, uint32_t rows) -> bool {
     p->rows = rows; p->K = 0; p->pitch = w->Kcap;
@@ -1314,12 +1328,18 @@ int dyb200_wgrad_create(dyb200_ctx* ctx, uint32_t M, uint32_t N0, uint32_t N1, u
     if (cudaMalloc((void**)&p->lo, bytes) != cudaSuccess) { cudaGetLastError(); p->lo = nullptr; return false; }
     return true;
   };
-  // (A: Kcap rows of Mp floats, the same bytes as Mp rows of Kcap; zeroed once so that the padding beyond M stays finite)
-  bool ok = alloc(&w->A, w->Mp) && alloc(&w->B[0], N0) && (N1 == 0 || alloc(&w->B[1], N1));
+  // (Kcap rows of Mp / Np floats, the same bytes as Mp / Np rows of Kcap; zeroed once so that the padding beyond M / N stays
+  // finite)
+  bool ok = alloc(&w->A, w->Mp) && alloc(&w->B[0], w->Np[0]) && (N1 == 0 || alloc(&w->B[1], w->Np[1]));
   if (ok) {
     w->A.rows = M; w->A.pitch = w->Mp; w->A.mn_major = 1;
-    const size_t bytes = (size_t)w->Mp * w->Kcap * sizeof(float);
-    ok = cudaMemset(w->A.hi, 0, bytes) == cudaSuccess && cudaMemset(w->A.lo, 0, bytes) == cudaSuccess;
+    for (int j = 0; j < 2; ++j) { w->B[j].rows = w->N[j]; w->B[j].pitch = w->Np[j]; w->B[j].mn_major = 1; }
+    PackedOp* ps[3] = {&w->A, &w->B[0], &w->B[1]};
+    for (int q = 0; q < 3 && ok; ++q) {
+      if (!ps[q]->hi) continue;
+      const size_t bytes = (size_t)ps[q]->pitch * w->Kcap * sizeof(float);
+      ok = cudaMemset(ps[q]->hi, 0, bytes) == cudaSuccess && cudaMemset(ps[q]->lo, 0, bytes) == cudaSuccess;
+    }
     if (!ok) cudaGetLastError();
   }
   if (!ok) {
@@ -1333,7 +1353,7 @@ int dyb200_wgrad_create(dyb200_ctx* ctx, uint32_t M, uint32_t N0, uint32_t N1, u
 
 int dyb200_wgrad_destroy(dyb200_wgrad* w) {
   if (!w) return DYB200_OK;
-  for (PackedOp* p : {&w->A, &w->B[0], &w->B[1], &w->X, &w->Hs}) { if (p->hi) cudaFree(p->hi); if (p->lo) cudaFree(p->lo); }
+  for (PackedOp* p : {&w->A, &w->B[0], &w->B[1]}) { if (p->hi) cudaFree(p->hi); if (p->lo) cudaFree(p->lo); }
   free(w);
   return DYB200_OK;
 }
@@ -1359,26 +1379,12 @@ int dyb200_wgrad_pack_inputs(dyb200_wgrad* w, const dyb200_tensor* x_all, const 
   DYB_CHECK_ARG(ctx, t_cols(x_all) == 1 && I == w->N[0] && w->N[1] > 0 && n <= w->Kcap && (step == 0 || n % step == 0),
                 "wgrad_pack_inputs: x is %u x %u, the accumulator expects %u rows, at most %u columns, whole steps of %u", I, n, w->N[0], w->Kcap, step);
   DYB_CHECK_ARG(ctx, !mask_x || (t_rows(mask_x) == I && (mask_x->bd == step || mask_x->bd == 1)), "wgrad_pack_inputs: mask shape mismatch");
-  if (!w->X.hi) {   // first use: planes for the forward operands of every column
-    auto alloc = [&](PackedOp* p, uint32_t K) -> bool {
-      p->rows = w->Kcap; p->K = K; p->pitch = round_up(K, 32);
-      const size_t bytes = (size_t)w->Kcap * p->pitch * sizeof(float);
-      if (cudaMalloc((void**)&p->hi, bytes) != cudaSuccess) { cudaGetLastError(); p->hi = nullptr; return false; }
-      if (cudaMalloc((void**)&p->lo, bytes) != cudaSuccess) { cudaGetLastError(); cudaFree(p->hi); p->hi = nullptr; p->lo = nullptr; return false; }
-      return true;
-    };
-    if (!alloc(&w->X, w->N[0]) || !alloc(&w->Hs, w->N[1])) {
-      if (w->X.hi) { cudaFree(w->X.hi); cudaFree(w->X.lo); w->X.hi = w->X.lo = nullptr; }
-      return dyb200_fail(ctx, DYB200_ENOMEM, "wgrad_pack_inputs: cudaMalloc failed for %u columns", w->Kcap);
-    }
-  }
   const float* mk = mask_x ? mask_x->v : nullptr;
   const int full = mask_x ? mask_x->bd == step : 0;
   PackJobs batch;
   dyb200_tc_pack_begin(&batch);
-  // forward operand: row = column of the sequence, reduction index = input feature; weight-gradient operand: the transpose
-  int rc = pack(ctx, x_all->v, I, 1, n, I, mk, I, full, w->X.hi, w->X.lo, w->X.pitch, &batch, step ? step : n);
-  if (!rc) rc = pack(ctx, x_all->v, I, 0, I, n, mk, I, full, w->B[0].hi, w->B[0].lo, w->Kcap, &batch, step ? step : n);
+  // row = column of the sequence, reduction index of the forward product = input feature
+  int rc = pack(ctx, x_all->v, I, 1, n, I, mk, I, full, w->B[0].hi, w->B[0].lo, w->Np[0], &batch, step ? step : n);
   if (!rc) rc = pack_flush_impl(ctx, &batch);
   if (rc) return rc;
   w->x_cols = n; w->step = step; w->h_col = 0xffffffffu;
@@ -1398,7 +1404,7 @@ int dyb200_wgrad_flush(dyb200_wgrad* w, float* C0, uint32_t ldc0, float* C1, uin
   A.K = w->k;
   for (int j = 0; j < 2; ++j) {
     if (w->N[j] == 0) continue;
-    PackedOp B = w->B[j];
+    PackedOp B = w->B[j];   // (MN-major: rows = N[j], one plane row per column)
     B.K = w->k;
     GemmEpilogue e{EPI_ACCUM, j == 0 ? C0 : C1, j == 0 ? ldc0 : ldc1, nullptr, 0, 0.f, nullptr, 0, 0};
     int rc = dyb200_tc_gemm_packed(ctx, w->M, w->N[j], 1, &A, &B, e);

@@ -27,8 +27,9 @@ struct SeqFwd {
   float* gates; float* cs; float* hs;   // outputs of step t at + t * 4H * B / + t * H * B
   const float* c0;                  // cell state before the first step
   const float* bias; float forget_bias;
-  float *hn_hi, *hn_lo; uint32_t hn_pitch;   // operand planes of h .* mask_h for the gate products: row = column of the sequence
-  float *ht_hi, *ht_lo; uint32_t ht_pitch;   // the same values transposed for the weight-gradient product: row = hidden unit
+  // operand planes of h .* mask_h: row = column of the sequence (K-major right operand of the gate products; the layer's
+  // weight-gradient product reads the same planes MN-major)
+  float *hn_hi, *hn_lo; uint32_t hn_pitch;
   const float* hmask; uint32_t hmask_ld; int hmask_full;
   uint32_t* ready;                  // one arrival counter per column block, zero at launch
   uint32_t* flags;
@@ -201,12 +202,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
       float* const c_out = a.cs + (size_t)t * HB;
       float* const h_out = a.hs + (size_t)t * HB;
       const bool emit = t + 1 < a.T;   // h_t is the next step's input
-      // h_t .* mask_h as operand planes of step t + 1: rows (t + 1) B .. of the gate product's planes, columns (t + 1) B .. of
-      // the transposed planes
+      // h_t .* mask_h as operand planes of step t + 1: rows (t + 1) B .. of the planes
       float* const hn_hi = a.hn_hi + (size_t)(t + 1) * a.B * a.hn_pitch;
       float* const hn_lo = a.hn_lo + (size_t)(t + 1) * a.B * a.hn_pitch;
-      float* const ht_hi = a.ht_hi + (size_t)(t + 1) * a.B;
-      float* const ht_lo = a.ht_lo + (size_t)(t + 1) * a.B;
       // previous cell states and mask values of the columns this thread finishes (c_prev was written by this same thread one
       // step earlier); fetched now, while the products of the step run
       float4 cp[BNT / 64][2], hm[BNT / 64][2];
@@ -298,8 +296,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
                               lstm_cell_c(g[k][0].z, g[k][3].z, g[k][1].z, cv.z), lstm_cell_c(g[k][0].w, g[k][3].w, g[k][1].w, cv.w));
           hv[k] = make_float4(lstm_cell_h(g[k][2].x, cn[k].x), lstm_cell_h(g[k][2].y, cn[k].y), lstm_cell_h(g[k][2].z, cn[k].z), lstm_cell_h(g[k][2].w, cn[k].w));
           if (emit) {
-            // h .* mask_h as the next step's operand planes (the values of epi_emit_h); the transposed copies for the
-            // weight-gradient product wait until the hand-over is out
+            // h .* mask_h as the next step's operand planes (the values of epi_emit_h)
             const float4 mk = hm[hh][k];
             const float4 hmk = a.hmask ? make_float4(hv[k].x * mk.x, hv[k].y * mk.y, hv[k].z * mk.z, hv[k].w * mk.w) : hv[k];
             split_tf32(hmk.x, phi[k].x, plo[k].x); split_tf32(hmk.y, phi[k].y, plo[k].y);
@@ -322,12 +319,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_lstm_seq_fwd(const __grid_const
         for (int k = 0; k < 2; ++k) {
           if (!live[k]) continue;
           const uint32_t n = nh + (te >> 3) + 32 * k;
-          if (emit) {
-            float* th = ht_hi + (size_t)u * a.ht_pitch + n;
-            float* tl = ht_lo + (size_t)u * a.ht_pitch + n;
-            th[0] = phi[k].x; th[a.ht_pitch] = phi[k].y; th[2 * (size_t)a.ht_pitch] = phi[k].z; th[3 * (size_t)a.ht_pitch] = phi[k].w;
-            tl[0] = plo[k].x; tl[a.ht_pitch] = plo[k].y; tl[2 * (size_t)a.ht_pitch] = plo[k].z; tl[3 * (size_t)a.ht_pitch] = plo[k].w;
-          }
 #pragma unroll
           for (int q = 0; q < 4; ++q) st4(gates_t + (size_t)q * a.H + u + (size_t)M * n, g[k][q]);
           const size_t ei = u + (size_t)a.H * n;
@@ -515,7 +506,6 @@ int dyb200_vanilla_lstm_seq_fwd(const dyb200_tensor* x_all, const dyb200_tensor*
     a.T = T; a.B = B; a.H = H; a.kb0 = kb0; a.kb1 = kb1;
     a.gates = gates_all->v; a.cs = c_all->v; a.hs = h_all->v; a.c0 = c0->v; a.bias = b->v; a.forget_bias = attrs->forget_gate_bias;
     a.hn_hi = pl.Hs.hi; a.hn_lo = pl.Hs.lo; a.hn_pitch = pl.Hs.pitch;
-    a.ht_hi = pl.B1.hi; a.ht_lo = pl.B1.lo; a.ht_pitch = pl.B1.pitch;
     a.hmask = mh; a.hmask_ld = H; a.hmask_full = mh_full;
     a.ready = ctx->dev_flags + DYB200_DEV_SEQ0;
     a.flags = ctx->dev_flags;

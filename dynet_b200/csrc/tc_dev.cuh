@@ -26,8 +26,9 @@ constexpr uint32_t kEpiWarps = 8;
 
 // pair p: t[4p] = A_hi, A_lo, B_hi, B_lo.  a_mn != 0 (one pair only): the A planes are MN-major - element (m, k) at
 // plane[k * pitch + m], the layout of a K x M row-major matrix - and t[0], t[1] are 3-D maps over (m within a group of 32,
-// k, group) with a box of 32 x 32 x 4; see load_a_tile / umma_desc_mn.
-struct TmapPack { CUtensorMap t[8]; uint32_t a_mn; };
+// k, group) with a box of 32 x 32 x 4; see load_a_tile / umma_desc_mn.  b_mn: the same for the B planes (t[2], t[3]; the
+// box holds as many groups as the tile has columns / 32).
+struct TmapPack { CUtensorMap t[8]; uint32_t a_mn, b_mn; };
 
 // The k-blocks of K split z of S: [b0, b0 + n0) of pair 0, then [b1, b1 + n1) of pair 1 (each pair cut into S equal shares).
 struct KSplit { uint32_t b0, n0, b1, n1; };
@@ -109,6 +110,11 @@ __device__ __forceinline__ void load_a_tile(unsigned char* st, const CUtensorMap
     tma_load_2d(st, map, bar, (int)(kblk * 32), (int)m0);
   }
 }
+__device__ __forceinline__ void load_b_tile(unsigned char* st, const CUtensorMap* map, uint64_t* bar, uint32_t kblk, uint32_t n0,
+                                            uint32_t b_mn) {
+  if (b_mn) tma_load_3d(st, map, bar, 0, (int)(kblk * 32), (int)(n0 / 32));
+  else tma_load_2d(st, map, bar, (int)(kblk * 32), (int)n0);
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -133,9 +139,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 
 // The 12 MMAs of one 32-wide k-block (3 products x 4 k-steps of 8) as one block of PTX.  The first MMA accumulates iff
 // `accumulate` is non-zero (0 opens a new accumulation chain).  a_step: what one k-step adds to the A descriptors, in
-// descriptor units of 16 bytes (2 = 32 bytes of a K-major row; 64 = one 8-k group of an MN-major tile).
+// descriptor units of 16 bytes (2 = 32 bytes of a K-major row; 64 = one 8-k group of an MN-major tile); b_step: the same
+// for the B descriptors.
 __device__ __forceinline__ void issue_kblock(uint32_t acc, uint64_t a_hi, uint64_t a_lo, uint64_t b_hi, uint64_t b_lo,
-                                             uint32_t idesc, uint32_t accumulate, uint64_t a_step = 2) {
+                                             uint32_t idesc, uint32_t accumulate, uint64_t a_step = 2, uint64_t b_step = 2) {
   // one MMA consumes 8 tf32 = 32 bytes of K: +2 in descriptor units per k8 step of a K-major operand
   asm volatile(
       "{\n\t.reg .pred pf, pt;\n\t.reg .b64 xa, xb, ya, yb;\n\t"
@@ -143,19 +150,19 @@ __device__ __forceinline__ void issue_kblock(uint32_t acc, uint64_t a_hi, uint64
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %2, %3, %5, pf;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %4, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %3, %5, pt;\n\t"
-      "add.s64 xa, %1, %7;\n\tadd.s64 xb, %2, %7;\n\tadd.s64 ya, %3, 2;\n\tadd.s64 yb, %4, 2;\n\t"
+      "add.s64 xa, %1, %7;\n\tadd.s64 xb, %2, %7;\n\tadd.s64 ya, %3, %8;\n\tadd.s64 yb, %4, %8;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t"
-      "add.s64 xa, xa, %7;\n\tadd.s64 xb, xb, %7;\n\tadd.s64 ya, %3, 4;\n\tadd.s64 yb, %4, 4;\n\t"
+      "add.s64 xa, xa, %7;\n\tadd.s64 xb, xb, %7;\n\tadd.s64 ya, ya, %8;\n\tadd.s64 yb, yb, %8;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t"
-      "add.s64 xa, xa, %7;\n\tadd.s64 xb, xb, %7;\n\tadd.s64 ya, %3, 6;\n\tadd.s64 yb, %4, 6;\n\t"
+      "add.s64 xa, xa, %7;\n\tadd.s64 xb, xb, %7;\n\tadd.s64 ya, ya, %8;\n\tadd.s64 yb, yb, %8;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xb, ya, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, yb, %5, pt;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], xa, ya, %5, pt;\n\t}"
-      ::"r"(acc), "l"(a_hi), "l"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(accumulate), "l"(a_step)
+      ::"r"(acc), "l"(a_hi), "l"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(accumulate), "l"(a_step), "l"(b_step)
       : "memory");
 }
 
