@@ -753,8 +753,9 @@ int dyb200_softmax_output_bwd_fused(const dyb200_tensor* x, const dyb200_tensor*
              (float*)part, vec_in);
   DYB_LAUNCHED(ctx);
   if ((rc = batch_reduce_add(ctx, ChunkOfPart{(const float*)part, V}, V, grid.y, db->v))) return rc;   // db += sum over column tiles
-  // dR += d h^T : M = V, N = H, K = n
-  if ((rc = dyb200_tc_pack(ctx, h->v, H, false, H, n, nullptr, 0, 0, &hT, nullptr))) return rc;
+  // dR += d h^T : M = V, N = H, K = n; both operands MN-major (h split as it lies: row = column, H values)
+  if ((rc = dyb200_tc_pack(ctx, h->v, H, true, n, H, nullptr, 0, 0, &hT, nullptr))) return rc;
+  hT.rows = H; hT.K = n; hT.mn_major = 1;
   {
     GemmEpilogue e{EPI_ACCUM, dR->v, V, nullptr, 0, 0.f, nullptr, 0, 0};
     if ((rc = dyb200_tc_gemm_packed(ctx, V, H, 1, &dA, &hT, e))) return rc;
