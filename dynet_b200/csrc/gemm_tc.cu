@@ -1151,12 +1151,27 @@ int dyb200_gemm_tc(dyb200_ctx* ctx, uint32_t M, uint32_t N, int npairs, const Ge
   dyb200_tc_pack_begin(&batch);
   for (int p = 0; p < npairs; ++p) {
     const GemmPair& g = pairs[p];
-    // A: rows = m. op(A)(m,k) = transA ? A[k + lda*m] : A[m + lda*k]  -> k is fast iff transA
-    int rc = g.a_is_param ? dyb200_tc_param(ctx, g.A, g.lda, g.transA != 0, M, g.K, &A[p])
-                          : dyb200_tc_pack(ctx, g.A, g.lda, g.transA != 0, M, g.K, nullptr, 0, 0, &A[p], &batch);
+    // A: rows = m. op(A)(m,k) = transA ? A[k + lda*m] : A[m + lda*k]  -> k is fast iff transA.  An operand whose rows are
+    // the fast index is split as it lies (K rows of M values) and read MN-major (single products only): no transposing
+    // pass, and a parameter then has ONE set of planes for this product and for the one that uses it transposed.
+    const bool a_mn = npairs == 1 && g.transA == 0, b_mn = npairs == 1 && g.transB != 0;
+    int rc;
+    if (a_mn) {
+      rc = g.a_is_param ? dyb200_tc_param(ctx, g.A, g.lda, true, g.K, M, &A[p])
+                        : dyb200_tc_pack(ctx, g.A, g.lda, true, g.K, M, nullptr, 0, 0, &A[p], &batch);
+      A[p].rows = M; A[p].K = g.K; A[p].mn_major = 1;
+    } else {
+      rc = g.a_is_param ? dyb200_tc_param(ctx, g.A, g.lda, g.transA != 0, M, g.K, &A[p])
+                        : dyb200_tc_pack(ctx, g.A, g.lda, g.transA != 0, M, g.K, nullptr, 0, 0, &A[p], &batch);
+    }
     if (rc) return rc;
     // B: rows = n. op(B)(k,n) = transB ? B[n + ldb*k] : B[k + ldb*n]  -> k is fast iff !transB
-    rc = dyb200_tc_pack(ctx, g.B, g.ldb, g.transB == 0, N, g.K, g.maskB, g.mask_ld, g.mask_full, &B[p], &batch);
+    if (b_mn) {
+      rc = dyb200_tc_pack(ctx, g.B, g.ldb, true, g.K, N, g.maskB, g.mask_ld, g.mask_full, &B[p], &batch);
+      B[p].rows = N; B[p].K = g.K; B[p].mn_major = 1;
+    } else {
+      rc = dyb200_tc_pack(ctx, g.B, g.ldb, g.transB == 0, N, g.K, g.maskB, g.mask_ld, g.mask_full, &B[p], &batch);
+    }
     if (rc) return rc;
   }
   int rcf = dyb200_tc_pack_flush(ctx, &batch);
