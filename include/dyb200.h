@@ -292,8 +292,8 @@ int dyb200_wgrad_push(dyb200_wgrad* w, uint32_t k, const float* a, uint32_t lda,
 /* Optional, for a layer whose inputs of ALL time steps exist before its first step runs (any layer of a stack that is
  * run layer by layer): x_all = Dim({I}, n) holds the inputs of the n / step time steps side by side (`step` columns
  * each), mask_x = Dim({I}, step) or Dim({I}, 1) is the layer's input dropout mask (the same for every time step, as in
- * dynet/lstm.cc:1010-1030) or NULL.  One launch splits x_all .* mask_x into the operand planes of the gate products and
- * of the weight-gradient product (columns [0, n) of the accumulator).  Afterwards dyb200_vanilla_lstm_fwd_fused_at, called
+ * dynet/lstm.cc:1010-1030) or NULL.  One launch splits x_all .* mask_x into operand planes (one row per column; columns
+ * [0, n) of the accumulator) that the gate products and the weight-gradient product both read.  Afterwards dyb200_vanilla_lstm_fwd_fused_at, called
  * with this accumulator for deferred_col = 0, step, 2 step, ... in order, launches no operand split of its own except
  * for h_tm1 of the first step: each step's epilogue also writes h_t .* mask_h as the next step's operand planes.  The pre-split
  * inputs are dropped by dyb200_wgrad_flush (one call per sequence).  The x
